@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF quantized-matmul decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the Q4_0 decode mat-vec at the 7B FFN shape -- weight
+11008 x 4096 stored as GGUF Q4_0 blocks, fp16 activation, batch 1 (the second
+benchmark configuration).  One step = one pass over REPLICAS distinct weight
+tensors (a 32-layer stack's worth, 811 MB), one kernel launch per tensor,
+replayed from a CUDA graph; cycling distinct tensors keeps the 25 MB weights
+from being served by the 126 MB L2.  The metric is algorithmic bytes (weights
++ activations + output, each counted once) per second, in GB/s.
+
+N > 1: every rank holds its own 11008-row shard of a [N x 11008, 4096] weight
+(row sharding: weights never move), computes its output slice and an NCCL
+all-gather assembles the full output on every rank once per step ("weak"
+scaling: per-GPU work is fixed).
+
+Besides the device-resident number (`value`) the line carries `e2e` (same
+metric through the host-buffer call: activations copied from pinned host memory
+and results copied back every launch), `roofline` (achieved GB/s of the mat-vec
+kernel against the measured HBM copy peak), `cpu_baseline` (the CPU checker
+timed on this host) and the SM clocks sampled during the timed region.
+
+`--impl reference` times the reference's own CPU implementation of the path
+instead (its GGUF reader's dequantiser + the scalar contraction of its test
+harness) on a bounded sample and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+FMT_NAME = "Q4_0"
+N_ROWS, K_COLS, BATCH = 11008, 4096, 1
+REPLICAS = 32
+METRIC = "qgemv_hbm_gbs"
+UNIT = "GB/s"
+
+# DRAM bytes (read + write) per mat-vec launch seen by ncu for this workload
+# (profiles/qgemv_q4_0_11008x4096.md); None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def algorithmic_bytes(n_rows: int, k: int, batch: int) -> int:
+    """Weights once + fp16 activations + fp32 output (what the roofline counts)."""
+    return n_rows * (k // 32) * 18 + batch * k * 2 + batch * n_rows * 4
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Polls SM clock, power and throttle reasons through NVML while the timed
+    region runs (read-only queries)."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.power = [], set(), []
+        self.max_mhz = None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._halt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._halt.set()
+        if self.is_alive():
+            self.join(timeout=1.0)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+            "power_w_max": max(self.power) if self.power else None,
+        }
+
+
+def cpu_port_throughput(budget_s: float):
+    """The CPU checker's mat-vec (all host threads) on the same workload, bounded
+    to about `budget_s` seconds; returns (GB/s, threads, description)."""
+    from cut_b200 import synth
+    from oracle import oracle as O
+
+    n_rep = 4
+    ws = [synth.make_weights(synth.Q4_0, N_ROWS, K_COLS, seed=9000 + i) for i in range(n_rep)]
+    a = synth.make_activations(BATCH, K_COLS, 77, np.float16).astype(np.float32)
+    O.qmatmul_blocks_fast(synth.Q4_0, a, ws[0], BATCH, K_COLS, N_ROWS)
+    t0 = time.perf_counter()
+    calls = 0
+    while time.perf_counter() - t0 < budget_s:
+        O.qmatmul_blocks_fast(synth.Q4_0, a, ws[calls % n_rep], BATCH, K_COLS, N_ROWS)
+        calls += 1
+    dt = time.perf_counter() - t0
+    gbs = calls * algorithmic_bytes(N_ROWS, K_COLS, BATCH) / dt / 1e9
+    return gbs, O.num_threads(), f"{calls} mat-vecs of {N_ROWS}x{K_COLS} {FMT_NAME} over {n_rep} weight copies in {dt:.1f} s"
+
+
+def run_reference(args) -> None:
+    """Reference arm: the reference's CPU code for the path on this host's cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from cut_b200 import synth
+    from oracle import oracle as O
+
+    sample_rows = 2752  # a quarter of the 11008 rows per step keeps K steps within minutes
+    w = synth.make_weights(synth.Q4_0, sample_rows, K_COLS, seed=9100)
+    a = synth.make_activations(BATCH, K_COLS, 77, np.float16).astype(np.float32)
+    use_ref = O.have_ref()
+    path = O.ref_write_file(synth.Q4_0, w, sample_rows, K_COLS) if use_ref else None
+
+    def one_step():
+        if use_ref:
+            # the reference's own reader + dequantiser (single-threaded, as it runs)
+            wf = O.ref_dequant_path(path, sample_rows, K_COLS)
+        else:
+            wf = O.dequant_rows(synth.Q4_0, w, sample_rows, K_COLS)
+        # scalar float contraction of the reference's test harness, rows spread over all threads
+        return O.matmul_dense(a, wf)
+
+    for _ in range(args.warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one_step()
+    dt = time.perf_counter() - t0
+    if path:
+        os.unlink(path)
+    bytes_per_step = algorithmic_bytes(sample_rows, K_COLS, BATCH)
+    val = args.steps * bytes_per_step / dt / 1e9
+    kind = "reference" if use_ref else "port"
+    sample = (f"{args.steps} steps of {sample_rows}x{K_COLS} {FMT_NAME} rows (1/4 of the workload): "
+              + ("dequantised by the reference's gguf_reader.cpp (1 thread), " if use_ref else "dequantised by the C port, ")
+              + "contracted by the restated scalar loop of its test harness (all threads)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"configs[1]: {FMT_NAME} decode mat-vec {N_ROWS}x{K_COLS}, fp16 activation, batch {BATCH}",
+                   "host": "cpu"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": O.num_threads(), "kind": kind, "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the quantized-matmul path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L.lib()  # fail loudly if libcutb.so is missing
+
+    # ---- synthetic, device-resident inputs: REPLICAS distinct shards per rank ----
+    base = synth.make_weights(synth.Q4_0, N_ROWS, K_COLS, seed=1234 + rank)
+    W = torch.empty((REPLICAS, base.size), dtype=torch.uint8, device=dev)
+    Wb = torch.from_numpy(base).to(dev)
+    for r in range(REPLICAS):
+        # distinct bytes per replica without generating 800 MB on the host
+        W[r] = torch.roll(Wb, shifts=18 * 7 * r)
+    a_host = torch.from_numpy(synth.make_activations(BATCH, K_COLS, 77, np.float16)).pin_memory()
+    A = a_host.to(dev)
+    C_all = torch.zeros((REPLICAS, BATCH, N_ROWS), dtype=torch.float32, device=dev)
+    gathered = torch.zeros((world, REPLICAS, BATCH, N_ROWS), dtype=torch.float32, device=dev) if world > 1 else None
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    descs, keep = [], []
+    for r in range(REPLICAS):
+        d, _, k = ops.make_desc(A, W[r], L.Q4_0, N_ROWS, C_out=C_all[r], status=status)
+        assert ops.select_variant(d) == L.VARIANT_GEMV_MMA and ops.workspace_bytes(d) == 0
+        descs.append(d)
+        keep.append(k)
+
+    def sweep():
+        for d in descs:
+            ops.launch(d)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), C_all.view(-1))
+
+    # correctness of what is being timed (first rows of replica 0 against the CPU checker)
+    sweep()
+    torch.cuda.synchronize()
+    from oracle import oracle as O  # checker only
+
+    rows = 256
+    ref = O.qmatmul_blocks(synth.Q4_0, a_host.numpy().astype(np.float32), base[: rows * (K_COLS // 32) * 18], BATCH,
+                           K_COLS, rows)
+    got = C_all[0, :, :rows].cpu().numpy()
+    rel = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+    if not rel <= 1e-3 or int(status.item()) != 0:
+        raise SystemExit(f"bench: kernel output disagrees with the checker (rel-L2 {rel}, status {int(status.item())})")
+
+    # ---- device-resident timing: CUDA-graph replay of one sweep per step ----
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        sweep()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            sweep()
+        step = graph.replay
+    except Exception:
+        graph, step = None, sweep
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    bytes_per_launch = algorithmic_bytes(N_ROWS, K_COLS, BATCH)
+    launches = REPLICAS * args.steps
+    value = world * launches * bytes_per_launch / (ms * 1e-3) / 1e9
+
+    # ---- kernel-only duration for the roofline (no collective), events on the launch stream ----
+    def kernels_only():
+        for d in descs:
+            ops.launch(d)
+
+    g2 = None
+    try:
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2):
+            kernels_only()
+        kstep = g2.replay
+    except Exception:
+        kstep = kernels_only
+    for _ in range(3):
+        kstep()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ksteps = max(args.steps, 20)
+    k0.record()
+    for _ in range(ksteps):
+        kstep()
+    k1.record()
+    torch.cuda.synchronize()
+    us_per_launch = k0.elapsed_time(k1) * 1e3 / (ksteps * REPLICAS)
+    achieved = bytes_per_launch / (us_per_launch * 1e-6) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+
+    # ---- end to end through the host-buffer call: pinned activations in, result out, every launch ----
+    c_host = torch.empty((BATCH, N_ROWS), dtype=torch.float32).pin_memory()
+    e2e_steps = max(1, min(args.steps, 50))
+
+    def e2e_step():
+        for r, d in enumerate(descs):
+            A.copy_(a_host, non_blocking=True)
+            ops.launch(d)
+            c_host.copy_(C_all[r], non_blocking=True)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), C_all.view(-1))
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * e2e_steps * REPLICAS * bytes_per_launch / e2e_s / 1e9
+
+    if int(status.item()) != 0:
+        raise SystemExit(f"bench: device status word = {int(status.item())}")
+
+    cpu = None
+    if rank == 0 and world == 1:
+        v, cores, sample = cpu_port_throughput(args.cpu_seconds)
+        cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": f"configs[1]: {FMT_NAME} decode mat-vec {N_ROWS}x{K_COLS} (GGUF blocks), fp16 activation, batch {BATCH}",
+                "replicas_per_step": REPLICAS,
+                "l2": f"{REPLICAS} distinct weight tensors cycled ({REPLICAS * base.size / 1e6:.0f} MB > 126 MB L2)",
+                "parallelism": "single GPU" if world == 1 else f"rows sharded over {world} GPUs, NCCL all-gather of output slices per step",
+                "graph": graph is not None,
+                "pct_of_8TBs": 100.0 * value / world / 8000.0,
+            },
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",
+                         "us_per_launch": us_per_launch, "algorithmic_bytes_per_launch": bytes_per_launch},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": REPLICAS * BATCH * K_COLS * 2,
+                    "d2h_bytes_per_step": REPLICAS * BATCH * N_ROWS * 4, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="budget of the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps == 2000:
+            args.steps, args.warmup = 20, 3
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

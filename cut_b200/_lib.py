@@ -1,0 +1,84 @@
+"""ctypes view of libcutb.so, laid out exactly as include/cutb.h declares it.
+
+There is no fallback: if the library has not been built, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libcutb.so")
+
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT = range(6)
+Q8_0, Q4_0, Q4_K = 0, 1, 2
+F32, F16 = 0, 1
+LAYOUT_GGUF_BLOCKS, LAYOUT_KN_PLANES = 0, 1
+FUSION_NONE, FUSION_UNARY, FUSION_BINARY = 0, 1, 2
+VARIANT_AUTO, VARIANT_GENERIC, VARIANT_GEMV_MMA, VARIANT_GEMM_TC = -1, 0, 1, 2
+
+# every symbol include/cutb.h declares
+EXPORTS = [
+    "cutb_qmatmul_workspace_bytes", "cutb_qmatmul_select_variant", "cutb_qmatmul", "cutb_dequant",
+    "cutb_transpose_q4", "cutb_version", "cutb_status_string", "cutb_last_error", "cutb_device_sm_count",
+    "cutb_variant_name",
+]
+
+
+class QMatmulDesc(C.Structure):
+    _fields_ = [
+        ("format", C.c_int32), ("layout", C.c_int32), ("affine", C.c_int32), ("a_dtype", C.c_int32),
+        ("M", C.c_uint32), ("K", C.c_uint32), ("N", C.c_uint32),
+        ("A", C.c_void_p), ("lda", C.c_uint32),
+        ("W", C.c_void_p), ("W_bytes", C.c_uint64),
+        ("scales", C.c_void_p), ("ldb", C.c_uint32), ("lds", C.c_uint32),
+        ("C", C.c_void_p), ("ldc", C.c_uint32),
+        ("D", C.c_void_p), ("ldd", C.c_uint32),
+        ("fusion_type", C.c_int32), ("fusion_op", C.c_int32), ("variant", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
+        ("status", C.c_void_p),
+    ]
+
+
+class CutbError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"cutb status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m cut_b200.build` (there is no CPU fallback)")
+        l = C.CDLL(LIB_PATH)
+        l.cutb_qmatmul_workspace_bytes.restype = C.c_uint64
+        l.cutb_qmatmul_workspace_bytes.argtypes = [C.POINTER(QMatmulDesc)]
+        l.cutb_qmatmul_select_variant.restype = C.c_int
+        l.cutb_qmatmul_select_variant.argtypes = [C.POINTER(QMatmulDesc)]
+        l.cutb_qmatmul.restype = C.c_int
+        l.cutb_qmatmul.argtypes = [C.POINTER(QMatmulDesc), C.c_void_p]
+        l.cutb_dequant.restype = C.c_int
+        l.cutb_dequant.argtypes = [C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                   C.c_void_p]
+        l.cutb_transpose_q4.restype = C.c_int
+        l.cutb_transpose_q4.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                        C.c_void_p]
+        l.cutb_version.restype = C.c_int
+        l.cutb_status_string.restype = C.c_char_p
+        l.cutb_status_string.argtypes = [C.c_int]
+        l.cutb_last_error.restype = C.c_char_p
+        l.cutb_device_sm_count.restype = C.c_int
+        l.cutb_variant_name.restype = C.c_char_p
+        l.cutb_variant_name.argtypes = [C.c_int]
+        _lib = l
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise CutbError(status, lib().cutb_last_error().decode() or lib().cutb_status_string(status).decode())

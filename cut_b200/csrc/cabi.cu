@@ -1,0 +1,231 @@
+// extern "C" entry points of libcutb.so: argument validation, variant choice,
+// launch.  No allocation, no synchronisation, no CPU fallback.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace cutb {
+const char *last_error();
+
+namespace {
+
+int validate(const cutb_qmatmul_desc *d) {
+  if (!d) {
+    set_last_error("qmatmul: null descriptor");
+    return CUTB_ERR_INVALID;
+  }
+  if (d->format < CUTB_Q8_0 || d->format > CUTB_Q4_K) {
+    set_last_error("qmatmul: unknown format %d", d->format);
+    return CUTB_ERR_INVALID;
+  }
+  if (d->layout != CUTB_LAYOUT_GGUF_BLOCKS && d->layout != CUTB_LAYOUT_KN_PLANES) {
+    set_last_error("qmatmul: unknown layout %d", d->layout);
+    return CUTB_ERR_INVALID;
+  }
+  if (d->a_dtype != CUTB_F32 && d->a_dtype != CUTB_F16) {
+    set_last_error("qmatmul: unknown activation dtype %d", d->a_dtype);
+    return CUTB_ERR_INVALID;
+  }
+  if (d->M == 0 || d->K == 0 || d->N == 0) {
+    set_last_error("qmatmul: empty shape M=%u K=%u N=%u", d->M, d->K, d->N);
+    return CUTB_ERR_INVALID;
+  }
+  if (!d->A || !d->W || !d->C) {
+    set_last_error("qmatmul: null A, W or C");
+    return CUTB_ERR_INVALID;
+  }
+  if (d->lda < d->K || d->ldc < d->N) {
+    set_last_error("qmatmul: lda (%u) < K (%u) or ldc (%u) < N (%u)", d->lda, d->K, d->ldc, d->N);
+    return CUTB_ERR_INVALID;
+  }
+  if (d->fusion_type < CUTB_FUSION_NONE || d->fusion_type > CUTB_FUSION_BINARY) {
+    set_last_error("qmatmul: unknown fusion type %d", d->fusion_type);
+    return CUTB_ERR_INVALID;
+  }
+  if (d->fusion_type == CUTB_FUSION_BINARY && (!d->D || d->ldd < d->N)) {
+    set_last_error("qmatmul: binary fusion needs D with ldd >= N");
+    return CUTB_ERR_INVALID;
+  }
+  if (d->layout == CUTB_LAYOUT_GGUF_BLOCKS) {
+    if (d->K % block_elems(d->format) != 0) {
+      set_last_error("qmatmul: K=%u is not a multiple of the block size %u", d->K, block_elems(d->format));
+      return CUTB_ERR_INVALID;
+    }
+    const uint64_t need = (uint64_t)d->N * row_bytes(d->format, d->K);
+    if (d->W_bytes < need) {
+      set_last_error("qmatmul: W holds %llu bytes, shape needs %llu", (unsigned long long)d->W_bytes, (unsigned long long)need);
+      return CUTB_ERR_INVALID;
+    }
+    if (d->affine) {
+      set_last_error("qmatmul: affine applies to the plane layout only");
+      return CUTB_ERR_INVALID;
+    }
+  } else {
+    if (d->format == CUTB_Q4_K) {
+      set_last_error("qmatmul: the plane layout carries Q8 or Q4 (+affine), not Q4_K super-blocks");
+      return CUTB_ERR_INVALID;
+    }
+    if (!d->scales) {
+      set_last_error("qmatmul: plane layout needs a scales plane");
+      return CUTB_ERR_INVALID;
+    }
+    const uint32_t vals_cols = d->format == CUTB_Q4_0 ? (d->N + 1) / 2 : d->N;
+    if (d->ldb < vals_cols || d->lds < d->N) {
+      set_last_error("qmatmul: ldb (%u) or lds (%u) too small for N=%u", d->ldb, d->lds, d->N);
+      return CUTB_ERR_INVALID;
+    }
+    if (d->format == CUTB_Q4_0 && (d->N & 1)) {
+      set_last_error("qmatmul: Q4 plane layout needs an even N");
+      return CUTB_ERR_INVALID;
+    }
+    if (d->affine && d->format != CUTB_Q4_0) {
+      set_last_error("qmatmul: affine applies to Q4 only");
+      return CUTB_ERR_INVALID;
+    }
+    const uint64_t need = (uint64_t)(d->K - 1) * d->ldb + vals_cols;
+    if (d->W_bytes < need) {
+      set_last_error("qmatmul: W holds %llu bytes, shape needs %llu", (unsigned long long)d->W_bytes, (unsigned long long)need);
+      return CUTB_ERR_INVALID;
+    }
+  }
+  if (d->variant < CUTB_VARIANT_AUTO || d->variant > CUTB_VARIANT_GEMM_TC) {
+    set_last_error("qmatmul: unknown variant %d", d->variant);
+    return CUTB_ERR_INVALID;
+  }
+  return CUTB_OK;
+}
+
+// Decode shapes go to the bulk-copy MMA mat-vec, prefill shapes to the
+// tensor-core GEMM, everything else to the SIMT kernel.  The reference makes
+// the same split on M (operators/impl/matmul/MatMulOp.cpp:335-380).
+int select(const cutb_qmatmul_desc &d) {
+  if (d.variant != CUTB_VARIANT_AUTO) return d.variant;
+  if (d.layout == CUTB_LAYOUT_GGUF_BLOCKS) {
+    if (qgemv_blocks_supported(d)) return CUTB_VARIANT_GEMV_MMA;
+    if (qgemm_tc_supported(d)) return CUTB_VARIANT_GEMM_TC;
+  }
+  return CUTB_VARIANT_GENERIC;
+}
+
+}  // namespace
+}  // namespace cutb
+
+using namespace cutb;
+
+extern "C" {
+
+int cutb_version(void) { return CUTB_VERSION; }
+
+const char *cutb_status_string(int status) {
+  switch (status) {
+    case CUTB_OK: return "ok";
+    case CUTB_ERR_INVALID: return "invalid argument";
+    case CUTB_ERR_UNSUPPORTED: return "unsupported request";
+    case CUTB_ERR_CUDA: return "CUDA error";
+    case CUTB_ERR_WORKSPACE: return "workspace missing or too small";
+    case CUTB_ERR_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+const char *cutb_last_error(void) { return cutb::last_error(); }
+
+const char *cutb_variant_name(int variant) {
+  switch (variant) {
+    case CUTB_VARIANT_GENERIC: return "QMatMulGeneric";
+    case CUTB_VARIANT_GEMV_MMA: return "QGemvBulkMma";
+    case CUTB_VARIANT_GEMM_TC: return "QGemmTcgen05";
+    default: return "Unknown";
+  }
+}
+
+int cutb_device_sm_count(void) {
+  DeviceInfo di;
+  if (get_device_info(&di) != CUTB_OK) return -1;
+  return di.sm_count;
+}
+
+int cutb_qmatmul_select_variant(const cutb_qmatmul_desc *desc) {
+  if (validate(desc) != CUTB_OK) return -1;
+  return select(*desc);
+}
+
+uint64_t cutb_qmatmul_workspace_bytes(const cutb_qmatmul_desc *desc) {
+  if (validate(desc) != CUTB_OK) return 0;
+  if (select(*desc) == CUTB_VARIANT_GEMV_MMA) return qgemv_blocks_workspace(*desc);
+  return 0;
+}
+
+int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
+  if (int rc = validate(desc)) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int v = select(*desc);
+  switch (v) {
+    case CUTB_VARIANT_GEMV_MMA:
+      if (!qgemv_blocks_supported(*desc)) {
+        set_last_error("qmatmul: variant %s needs GGUF blocks, K %% 256 == 0, 16-byte aligned W and M <= 32 (fp16) / 16 (fp32)",
+                       cutb_variant_name(v));
+        return CUTB_ERR_UNSUPPORTED;
+      }
+      return qgemv_blocks_launch(*desc, s);
+    case CUTB_VARIANT_GEMM_TC:
+      if (!qgemm_tc_supported(*desc)) {
+        set_last_error("qmatmul: variant %s does not cover this shape/layout", cutb_variant_name(v));
+        return CUTB_ERR_UNSUPPORTED;
+      }
+      return qgemm_tc_launch(*desc, s);
+    default:
+      return qmatmul_generic_launch(*desc, s);
+  }
+}
+
+int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
+                 void *stream) {
+  if (format < CUTB_Q8_0 || format > CUTB_Q4_K) {
+    set_last_error("dequant: unknown format %d", format);
+    return CUTB_ERR_INVALID;
+  }
+  if (rows == 0 || cols == 0) return CUTB_OK;
+  if (!raw || !out) {
+    set_last_error("dequant: null pointer");
+    return CUTB_ERR_INVALID;
+  }
+  if (cols % block_elems(format) != 0) {
+    set_last_error("dequant: cols=%u is not a multiple of the block size %u", cols, block_elems(format));
+    return CUTB_ERR_INVALID;
+  }
+  if (ldo < cols) {
+    set_last_error("dequant: ldo (%u) < cols (%u)", ldo, cols);
+    return CUTB_ERR_INVALID;
+  }
+  const uint64_t need = (uint64_t)rows * row_bytes(format, cols);
+  if (raw_bytes < need) {
+    set_last_error("dequant: raw holds %llu bytes, shape needs %llu", (unsigned long long)raw_bytes, (unsigned long long)need);
+    return CUTB_ERR_INVALID;
+  }
+  return dequant_launch(format, raw, out, rows, cols, ldo, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_transpose_q4(const void *in, void *out, uint32_t N, uint32_t K, uint32_t stride_in, uint32_t stride_out,
+                      void *stream) {
+  // same argument checks as TransposeQ4NibbleOpNode (TransposeQ4NibbleOp.cpp:15-20)
+  if (N % 2 != 0) {
+    set_last_error("TransposeQ4: N must be even");
+    return CUTB_ERR_INVALID;
+  }
+  if (K % 32 != 0) {
+    set_last_error("TransposeQ4: K must be a multiple of 32");
+    return CUTB_ERR_INVALID;
+  }
+  if (N == 0 || K == 0) return CUTB_OK;
+  if (!in || !out) {
+    set_last_error("TransposeQ4: null pointer");
+    return CUTB_ERR_INVALID;
+  }
+  if (stride_in < K / 2 || stride_out < N / 2) {
+    set_last_error("TransposeQ4: strides (%u, %u) too small for N=%u K=%u", stride_in, stride_out, N, K);
+    return CUTB_ERR_INVALID;
+  }
+  return transpose_q4_launch(in, out, N, K, stride_in, stride_out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,168 @@
+// Shared device/host helpers of the sm_100a quantized-matmul kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/cutb.h"
+
+namespace cutb {
+
+// ---------------------------------------------------------------------------
+// Host-side error plumbing (the C ABI never throws).
+// ---------------------------------------------------------------------------
+void set_last_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define CUTB_CUDA_TRY(expr)                                   \
+  do {                                                        \
+    cudaError_t _e = (expr);                                  \
+    if (_e != cudaSuccess) return ::cutb::cuda_fail(_e, #expr); \
+  } while (0)
+
+// Block geometry of the three GGUF formats the path covers
+// (interface/loader/gguf/gguf_types.hpp:109-150).
+__host__ __device__ constexpr uint32_t block_elems(int fmt) { return fmt == CUTB_Q4_K ? 256u : 32u; }
+__host__ __device__ constexpr uint32_t block_bytes(int fmt) {
+  return fmt == CUTB_Q8_0 ? 34u : (fmt == CUTB_Q4_0 ? 18u : 144u);
+}
+// Bytes of 256 consecutive weights of one row: the copy granule of the decode
+// kernel (a multiple of 16 bytes in all three formats).
+__host__ __device__ constexpr uint32_t granule_bytes(int fmt) { return fmt == CUTB_Q8_0 ? 272u : 144u; }
+
+inline uint64_t row_bytes(int fmt, uint32_t K) {
+  return (uint64_t)((K + block_elems(fmt) - 1) / block_elems(fmt)) * block_bytes(fmt);
+}
+
+// Cached device properties of the current device.
+struct DeviceInfo {
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  size_t smem_optin = 0;
+};
+int get_device_info(DeviceInfo *out);
+
+// ---------------------------------------------------------------------------
+// Device helpers.
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// fp16 bits -> float, subnormals decoded, exactly as the reference's loader does
+// (interface/loader/gguf/gguf_reader.cpp:515-539); the hardware conversion is
+// exact for every fp16 value, subnormals included.
+__device__ __forceinline__ float h2f_bits(uint32_t bits) {
+  return __half2float(__ushort_as_half((unsigned short)bits));
+}
+
+// Fused epilogue of the reference's quantized matmul
+// (operators/impl/matmul/MatMulQ4Common.cuh:63-114): unary ops on the result,
+// or binary ops against the D operand.
+__device__ __forceinline__ float apply_epilogue(float v, int type, int op, float d) {
+  if (type == CUTB_FUSION_UNARY) {
+    float x = v;
+    switch (op) {
+      case 100: x = -x; break;
+      case 101: x = fabsf(x); break;
+      case 102: x = sqrtf(x); break;
+      case 103: x = x * x; break;
+      case 104: x = 1.0f / x; break;
+      case 106: x = expf(x); break;
+      case 109: x = logf(x); break;
+      case 121: x = tanhf(x); break;
+      case 122: x = floorf(x); break;
+      case 123: x = ceilf(x); break;
+      case 124: x = roundf(x); break;
+      case 130: x = fmaxf(0.0f, x); break;
+      case 131: x = 1.0f / (1.0f + expf(-x)); break;
+      case 132: x = x * 0.5f * (1.0f + tanhf(sqrtf(2.0f / 3.14159265f) * (x + 0.044715f * x * x * x))); break;
+      case 133: x = x / (1.0f + expf(-x)); break;
+      case 134: x = logf(1.0f + expf(x)); break;
+      case 137: x = fminf(fmaxf(x, 0.0f), 6.0f); break;
+      case 141: x = x * tanhf(logf(1.0f + expf(x))); break;
+      case 142: x = x * fminf(fmaxf(x / 6.0f + 0.5f, 0.0f), 1.0f); break;
+      case 143: x = fminf(fmaxf(x / 6.0f + 0.5f, 0.0f), 1.0f); break;
+      case 148: x = rsqrtf(x); break;
+      default: break;
+    }
+    return x;
+  }
+  if (type == CUTB_FUSION_BINARY) {
+    float a = v, b = d;
+    switch (op) {
+      case 0: return a + b;
+      case 1: return a - b;
+      case 2: return a * b;
+      case 3: return a / b;
+      case 4: return a - b * floorf(a / b);
+      case 5: return powf(a, b);
+      case 6: return floorf(a / b);
+      case 13: return fminf(a, b);
+      case 14: return fmaxf(a, b);
+      default: return a + b;
+    }
+  }
+  return v;
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// ---- mbarrier + bulk async copy (TMA engine, untiled form) ------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls and returns false; the caller
+// records CUTB_ERR_TIMEOUT and drains instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(32);
+  }
+  return false;
+}
+// global -> this CTA's shared memory, completion counted in bytes on `bar`.
+// dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// ---- warp-level MMA m16n8k16, fp16 x fp16 -> fp32 ---------------------------
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+
+#endif  // __CUDACC__
+
+}  // namespace cutb

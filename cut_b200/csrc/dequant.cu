@@ -1,0 +1,130 @@
+// Raw GGUF blocks -> fp32 [rows, ldo], bit-exact with the reference.
+//
+// Replaces DequantQ4K.cu (operators/impl/dequant/DequantQ4K.cu:6-50, helpers
+// DequantCommon.cuh:16-70) and adds the Q8_0 / Q4_0 cases the reference only
+// has on the CPU (interface/loader/gguf/gguf_reader.cpp:541-572, 826-850).
+//
+// The op is write-bound (4 bytes out per 0.56-1.06 bytes in).  Each thread
+// decodes 8 consecutive weights of one block -- the block header is read once
+// per thread through the read-only path instead of once per element -- and
+// stores them as two 16-byte vectors, so a warp writes 1 KB of contiguous
+// output per instruction pair.  Grid = a multiple of the SM count, grid-stride.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace cutb {
+namespace {
+
+__device__ __forceinline__ uint32_t ldg8(const uint8_t *p) { return __ldg(p); }
+__device__ __forceinline__ uint32_t ldg16(const uint8_t *p) { return ldg8(p) | (ldg8(p + 1) << 8); }
+// 32-bit little-endian read at any byte alignment
+__device__ __forceinline__ uint32_t ldg32u(const uint8_t *p) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  if ((a & 3) == 0) return __ldg(reinterpret_cast<const uint32_t *>(p));
+  if ((a & 1) == 0) {
+    const uint16_t *q = reinterpret_cast<const uint16_t *>(p);
+    return (uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16);
+  }
+  return ldg8(p) | (ldg8(p + 1) << 8) | (ldg8(p + 2) << 16) | (ldg8(p + 3) << 24);
+}
+
+// 8 weights [8*oct, 8*oct+8) of the 32-weight (Q8_0, Q4_0) or 256-weight (Q4_K)
+// block at `b`.
+template <int FMT> __device__ __forceinline__ void decode8(const uint8_t *b, uint32_t oct, float (&v)[8]) {
+  if constexpr (FMT == CUTB_Q8_0) {
+    const float d = h2f_bits(ldg16(b));
+    const uint32_t w0 = ldg32u(b + 2 + 8 * oct), w1 = ldg32u(b + 6 + 8 * oct);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = (float)(int8_t)((w0 >> (8 * i)) & 0xFF) * d;
+      v[4 + i] = (float)(int8_t)((w1 >> (8 * i)) & 0xFF) * d;
+    }
+  } else if constexpr (FMT == CUTB_Q4_0) {
+    const float d = h2f_bits(ldg16(b));
+    // elements 8*oct.. live in bytes (8*oct & 15).. ; low nibbles for oct < 2, high for oct >= 2
+    const uint32_t sh = (oct >> 1) * 4;
+    const uint32_t w0 = ldg32u(b + 2 + 8 * (oct & 1)), w1 = ldg32u(b + 6 + 8 * (oct & 1));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = (float)((int)((w0 >> (8 * i + sh)) & 0xF) - 8) * d;
+      v[4 + i] = (float)((int)((w1 >> (8 * i + sh)) & 0xF) - 8) * d;
+    }
+  } else {
+    const uint32_t j = oct >> 2, l0 = (oct & 3) * 8;  // sub-block, first element inside it
+    const uint32_t hdr = __ldg(reinterpret_cast<const uint32_t *>(b));
+    const float d = h2f_bits(hdr & 0xFFFF), dmin = h2f_bits(hdr >> 16);
+    const uint8_t *sc = b + 4;
+    uint32_t s, m;
+    if (j < 4) {
+      s = ldg8(sc + j) & 63;
+      m = ldg8(sc + j + 4) & 63;
+    } else {
+      s = (ldg8(sc + j + 4) & 0xF) | ((ldg8(sc + j - 4) >> 6) << 4);
+      m = (ldg8(sc + j + 4) >> 4) | ((ldg8(sc + j) >> 6) << 4);
+    }
+    // value = (d * sc) * q - dmin * m, each product rounded on its own
+    // (gguf_reader.cpp:700-718, DequantQ4K.cu:39-46); both products are exact.
+    const float d1 = __fmul_rn(d, (float)s), dm = __fmul_rn(dmin, (float)m);
+    const uint8_t *q = b + 16 + (j >> 1) * 32 + l0;
+    const uint32_t sh = (j & 1) * 4;
+    const uint32_t w0 = __ldg(reinterpret_cast<const uint32_t *>(q)), w1 = __ldg(reinterpret_cast<const uint32_t *>(q + 4));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = __fsub_rn(__fmul_rn(d1, (float)((w0 >> (8 * i + sh)) & 0xF)), dm);
+      v[4 + i] = __fsub_rn(__fmul_rn(d1, (float)((w1 >> (8 * i + sh)) & 0xF)), dm);
+    }
+  }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict__ raw, float *__restrict__ out, uint32_t rows,
+                                                      uint32_t cols, uint32_t ldo, uint64_t row_bytes_, int vec_ok) {
+  constexpr uint32_t BE = block_elems(FMT), BB = block_bytes(FMT);
+  const uint32_t octs_per_row = (cols + 7) / 8;
+  const uint64_t total = (uint64_t)rows * octs_per_row;
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t r = (uint32_t)(i / octs_per_row), o = (uint32_t)(i % octs_per_row);
+    const uint32_t k = o * 8;
+    const uint8_t *b = raw + (uint64_t)r * row_bytes_ + (uint64_t)(k / BE) * BB;
+    float v[8];
+    decode8<FMT>(b, (k % BE) / 8, v);
+    float *dst = out + (uint64_t)r * ldo + k;
+    if (vec_ok && k + 8 <= cols) {
+      reinterpret_cast<float4 *>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+      reinterpret_cast<float4 *>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (k + e < cols) dst[e] = v[e];
+    }
+  }
+}
+
+}  // namespace
+
+int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
+                   cudaStream_t stream) {
+  DeviceInfo di;
+  if (int rc = get_device_info(&di)) return rc;
+  const uint64_t total = (uint64_t)rows * ((cols + 7) / 8);
+  if (total == 0) return CUTB_OK;
+  uint64_t blocks = (total + 255) / 256;
+  const uint64_t cap = (uint64_t)di.sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (ldo % 4 == 0);
+  const uint8_t *r = reinterpret_cast<const uint8_t *>(raw);
+  const uint64_t rb = row_bytes(format, cols);
+  if (format == CUTB_Q4_K && (reinterpret_cast<uintptr_t>(raw) % 4 != 0)) {
+    set_last_error("dequant: Q4_K blocks must be 4-byte aligned");
+    return CUTB_ERR_INVALID;
+  }
+  switch (format) {
+    case CUTB_Q8_0: dequant_kernel<CUTB_Q8_0><<<(unsigned)blocks, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    case CUTB_Q4_0: dequant_kernel<CUTB_Q4_0><<<(unsigned)blocks, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    default: dequant_kernel<CUTB_Q4_K><<<(unsigned)blocks, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+  }
+  CUTB_CUDA_TRY(cudaGetLastError());
+  return CUTB_OK;
+}
+
+}  // namespace cutb

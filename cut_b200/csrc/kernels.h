@@ -1,0 +1,27 @@
+// Internal launchers behind the C ABI (one per kernel family).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/cutb.h"
+
+namespace cutb {
+
+// Decode mat-vec over GGUF blocks (bulk-copy ring + warp MMA).
+bool qgemv_blocks_supported(const cutb_qmatmul_desc &d);
+uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d);
+int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
+
+// Any-shape SIMT matmul over GGUF blocks or the reference's [K,N] planes.
+int qmatmul_generic_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
+
+// Prefill GEMM over GGUF blocks on tcgen05 tensor cores.
+bool qgemm_tc_supported(const cutb_qmatmul_desc &d);
+int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
+
+int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
+                   cudaStream_t stream);
+int transpose_q4_launch(const void *in, void *out, uint32_t N, uint32_t K, uint32_t stride_in, uint32_t stride_out,
+                        cudaStream_t stream);
+
+}  // namespace cutb

@@ -1,0 +1,101 @@
+"""Python harness over the C ABI: torch supplies device memory and streams only.
+
+These wrappers mirror the reference's operator entry points for the path
+(runtime/Operations.h:65-93 matmul / matmulUnary / matmulBinary, :459
+transposeQ4, :467 dequantize): outputs are allocated by the op, shape errors
+raise, and nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+def make_desc(A: torch.Tensor, W: torch.Tensor, fmt: int, N: int, *, layout=L.LAYOUT_GGUF_BLOCKS, scales=None,
+              affine=False, ldb=0, lds=0, C_out: torch.Tensor | None = None, D: torch.Tensor | None = None,
+              fusion_type=L.FUSION_NONE, fusion_op=0, variant=L.VARIANT_AUTO, workspace: torch.Tensor | None = None,
+              status: torch.Tensor | None = None):
+    """Builds a cutb_qmatmul_desc over torch CUDA tensors; returns (desc, C, keepalive)."""
+    if A.dim() == 1:
+        A = A.unsqueeze(0)
+    if A.dim() != 2:
+        raise RuntimeError("matmul: A must be 1D or 2D")
+    if A.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("matmul: A must be float32 or float16")
+    if A.stride(1) != 1:
+        A = A.contiguous()
+    M, K = A.shape
+    if C_out is None:
+        C_out = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    d = L.QMatmulDesc()
+    d.format, d.layout, d.affine = fmt, layout, int(affine)
+    d.a_dtype = L.F32 if A.dtype == torch.float32 else L.F16
+    d.M, d.K, d.N = M, K, N
+    d.A, d.lda = A.data_ptr(), A.stride(0) if M > 1 else max(A.stride(0), K)
+    d.W, d.W_bytes = W.data_ptr(), W.numel() * W.element_size()
+    d.scales = scales.data_ptr() if scales is not None else None
+    d.ldb, d.lds = ldb, lds
+    d.C, d.ldc = C_out.data_ptr(), C_out.stride(0)
+    d.D, d.ldd = (D.data_ptr(), D.stride(0)) if D is not None else (None, 0)
+    d.fusion_type, d.fusion_op, d.variant = fusion_type, fusion_op, variant
+    d.workspace, d.workspace_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) \
+        if workspace is not None else (None, 0)
+    d.status = status.data_ptr() if status is not None else None
+    return d, C_out, (A, W, scales, D, workspace, status)
+
+
+def workspace_bytes(desc) -> int:
+    return int(L.lib().cutb_qmatmul_workspace_bytes(C.byref(desc)))
+
+
+def select_variant(desc) -> int:
+    return int(L.lib().cutb_qmatmul_select_variant(C.byref(desc)))
+
+
+def qmatmul(A, W, fmt, N, **kw) -> torch.Tensor:
+    """C[M,N] = epilogue(A[M,K] * dequant(W)); allocates C and, if needed, the workspace."""
+    d, C_out, keep = make_desc(A, W, fmt, N, **kw)
+    need = workspace_bytes(d)
+    if need and not d.workspace:
+        ws = torch.empty(need, dtype=torch.uint8, device=A.device)
+        d.workspace, d.workspace_bytes = ws.data_ptr(), need
+        keep = keep + (ws,)
+    L.check(L.lib().cutb_qmatmul(C.byref(d), _stream_ptr()))
+    return C_out
+
+
+def launch(desc) -> None:
+    """Re-launch a prepared descriptor on the current stream (benchmark inner loop)."""
+    L.check(L.lib().cutb_qmatmul(C.byref(desc), _stream_ptr()))
+
+
+def dequantize(raw: torch.Tensor, fmt: int, rows: int, cols: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Raw GGUF bytes -> float32 [rows, cols]; the row stride is padded to 4 as the
+    reference's DequantOpNode does (operators/impl/dequant/DequantOp.cpp:15-17)."""
+    ldo = _pad4(cols)
+    if out is None:
+        out = torch.empty((rows, ldo), dtype=torch.float32, device=raw.device)
+    L.check(L.lib().cutb_dequant(fmt, raw.data_ptr(), raw.numel() * raw.element_size(), out.data_ptr(), rows, cols,
+                                 out.stride(0), _stream_ptr()))
+    return out[:, :cols]
+
+
+def transpose_q4(packed: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """[N, pad4(K/2)] GGML nibbles -> [K, pad4(N/2)] with even n in the low nibble."""
+    if packed.dim() != 2:
+        raise RuntimeError("TransposeQ4: input must be 2D")
+    out = torch.zeros((K, _pad4(N // 2)), dtype=torch.uint8, device=packed.device)
+    L.check(L.lib().cutb_transpose_q4(packed.data_ptr(), out.data_ptr(), N, K, packed.stride(0), out.stride(0),
+                                      _stream_ptr()))
+    return out

@@ -1,0 +1,149 @@
+/*
+ * cutb.h -- C ABI of the B200 quantized-matmul backend for the CUT toolkit.
+ *
+ * One shared library (libcutb.so), plain pointers and sizes, no C++ or torch
+ * types.  Every pointer named "device" is a CUDA device pointer on the current
+ * device; `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ * Calls enqueue work on `stream` and return without synchronising.  They
+ * return CUTB_OK or an error code (never throw, never abort); a human-readable
+ * message for the last error on the calling thread is kept in
+ * cutb_last_error().  There is no CPU fallback: without a CUDA device every
+ * compute entry point returns CUTB_ERR_CUDA.
+ *
+ * The entry points stand in for the kernels the reference reaches through
+ * Dispatcher::encode -> ComputeInterface::encode -> cuLaunchKernel
+ * (runtime/Dispatcher.cpp:18-75, core/backends/cuda/CudaCommandBuffer.cpp:128-245);
+ * each declaration cites the reference interface it replaces.
+ */
+#ifndef CUTB_H
+#define CUTB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CUTB_VERSION 100
+
+/* Exported symbols: the library is built with hidden default visibility. */
+#if defined(__GNUC__)
+#define CUTB_API __attribute__((visibility("default")))
+#else
+#define CUTB_API
+#endif
+
+/* Status codes. */
+enum {
+  CUTB_OK = 0,
+  CUTB_ERR_INVALID = 1,     /* bad shape, stride, pointer or enum value */
+  CUTB_ERR_UNSUPPORTED = 2, /* valid request no kernel covers */
+  CUTB_ERR_CUDA = 3,        /* a CUDA runtime call failed (no device, launch error) */
+  CUTB_ERR_WORKSPACE = 4,   /* workspace missing or smaller than cutb_qmatmul_workspace_bytes() */
+  CUTB_ERR_TIMEOUT = 5      /* a bounded device-side wait ran out (read from the status word) */
+};
+
+/* GGUF block formats (interface/loader/gguf/gguf_types.hpp:109-150). */
+enum { CUTB_Q8_0 = 0, CUTB_Q4_0 = 1, CUTB_Q4_K = 2 };
+
+/* Activation element types (core/api/include/ComputeCommon.h:107-113). */
+enum { CUTB_F32 = 0, CUTB_F16 = 1 };
+
+/* Weight layouts.
+ *   CUTB_LAYOUT_GGUF_BLOCKS: N rows of native GGUF blocks along K, exactly the
+ *     bytes GGUFReader::read_tensor_raw returns (gguf_reader.cpp:312-324).
+ *   CUTB_LAYOUT_KN_PLANES: the reference's runtime layout -- values [K, N] int8
+ *     (Q8) or [K, N/2] nibbles, low nibble = even n (Q4), plus fp16 scales
+ *     [K/32, N]; with `affine` the scales plane has 2*K/32 rows, the lower half
+ *     holding per-block mins (operators/impl/matmul/MatMulOp.cpp:309-329,
+ *     MatMulQ4Common.cuh:126-153). */
+enum { CUTB_LAYOUT_GGUF_BLOCKS = 0, CUTB_LAYOUT_KN_PLANES = 1 };
+
+/* Fused epilogue selector = the reference's specialisation constants 1 and 2
+ * (operators/impl/matmul/MatMulOp.cpp:484-498): 0 none, 1 unary, 2 binary with
+ * the [M, N] operand D; `fusion_op` is the reference's OP_UNARY_* / OP_BINARY_*
+ * code (operators/runtime/ComputeOpsShared.h:22-66, 118-186). */
+enum { CUTB_FUSION_NONE = 0, CUTB_FUSION_UNARY = 1, CUTB_FUSION_BINARY = 2 };
+
+/* Kernel variants of cutb_qmatmul (variant = -1 lets the library choose). */
+enum {
+  CUTB_VARIANT_AUTO = -1,
+  CUTB_VARIANT_GENERIC = 0, /* any shape, SIMT, exact fp32 dequant + FMA */
+  CUTB_VARIANT_GEMV_MMA = 1, /* decode: bulk-copy ring + warp MMA, M <= 32 (fp16 A) / 16 (fp32 A) */
+  CUTB_VARIANT_GEMM_TC = 2  /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory */
+};
+
+/*
+ * C[M, N] = epilogue(A[M, K] * dequant(W)), fp32 accumulate, fp32 output.
+ * Replaces the quantized MatMulOpNode dispatch: bindings (A, packedB, scalesB,
+ * D, C) + push constants {M, K, N, strideA, strideB, strideC, scaleStride}
+ * (operators/impl/matmul/MatMulOp.cpp:507-575, MatMulQ4Common.cuh:22-30).
+ * Strides are in elements (bytes for W planes), as in the reference.
+ */
+typedef struct cutb_qmatmul_desc {
+  int32_t format;      /* CUTB_Q8_0 / CUTB_Q4_0 / CUTB_Q4_K */
+  int32_t layout;      /* CUTB_LAYOUT_* ; KN_PLANES supports Q8_0 and Q4_0 (+affine) */
+  int32_t affine;      /* KN_PLANES + Q4 only: scales plane carries mins */
+  int32_t a_dtype;     /* CUTB_F32 or CUTB_F16 */
+  uint32_t M, K, N;
+  const void *A;       /* device, [M, lda] */
+  uint32_t lda;
+  const void *W;       /* device: GGUF blocks, or the values plane */
+  uint64_t W_bytes;    /* size of the W allocation, checked against the shape */
+  const void *scales;  /* device, KN_PLANES only: fp16 [K/32 (x2 if affine), lds] */
+  uint32_t ldb;        /* KN_PLANES: row stride of the values plane in bytes */
+  uint32_t lds;        /* KN_PLANES: row stride of the scales plane in elements */
+  float *C;            /* device, [M, ldc] */
+  uint32_t ldc;
+  const float *D;      /* device, [M, ldd]; only read when fusion_type == 2 */
+  uint32_t ldd;
+  int32_t fusion_type; /* CUTB_FUSION_* */
+  int32_t fusion_op;   /* reference op code */
+  int32_t variant;     /* CUTB_VARIANT_* */
+  void *workspace;     /* device scratch, >= cutb_qmatmul_workspace_bytes(desc), 256-byte aligned; may be NULL if that is 0 */
+  uint64_t workspace_bytes;
+  int32_t *status;     /* optional device int: kernels store CUTB_ERR_TIMEOUT here if a bounded wait gives up */
+} cutb_qmatmul_desc;
+
+/* Scratch bytes cutb_qmatmul needs for this descriptor (0 for most shapes;
+ * split-K decode shapes stage partial sums there).  Never allocates. */
+CUTB_API uint64_t cutb_qmatmul_workspace_bytes(const cutb_qmatmul_desc *desc);
+
+/* Variant the library would run for this descriptor (resolves CUTB_VARIANT_AUTO);
+ * negative on an invalid descriptor.  Mirrors the variant choice made in the
+ * MatMulOpNode constructor (operators/impl/matmul/MatMulOp.cpp:335-380). */
+CUTB_API int cutb_qmatmul_select_variant(const cutb_qmatmul_desc *desc);
+
+CUTB_API int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream);
+
+/*
+ * Raw GGUF blocks -> fp32 [rows, cols] with row stride ldo (elements).
+ * Replaces DequantOpNode's dispatch (operators/impl/dequant/DequantOp.cpp:7-61,
+ * DequantQ4K.cu:6-50); Q8_0 and Q4_0 follow the loader's CPU dequantisers
+ * (interface/loader/gguf/gguf_reader.cpp:541-572, 826-850).  Bit-exact.
+ */
+CUTB_API int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows,
+                 uint32_t cols, uint32_t ldo, void *stream);
+
+/*
+ * GGML-packed Q4_0 nibbles [N, stride_in bytes] -> [K, stride_out bytes] with
+ * the low nibble holding even n.  Replaces TransposeQ4NibbleOpNode's dispatch
+ * (operators/impl/q4transpose/TransposeQ4NibbleOp.cpp:7-59,
+ * TransposeQ4Nibble.cu:36-61).  N even, K a multiple of 32.
+ */
+CUTB_API int cutb_transpose_q4(const void *in, void *out, uint32_t N, uint32_t K, uint32_t stride_in,
+                      uint32_t stride_out, void *stream);
+
+/* Library / device information. */
+CUTB_API int cutb_version(void);
+CUTB_API const char *cutb_status_string(int status);
+CUTB_API const char *cutb_last_error(void);
+/* Number of streaming multiprocessors of the current device, or -1. */
+CUTB_API int cutb_device_sm_count(void);
+CUTB_API const char *cutb_variant_name(int variant);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUTB_H */

@@ -544,6 +544,30 @@ ORC_API void orc_qmatmul_blocks_fast(int fmt, const float *A, const uint8_t *W, 
   }
 }
 
+/* Dense float contraction C[M,N] = A[M,K] * Wf[N,K]^T on already dequantised
+ * weights: the scalar loop of the reference's tests (tests/harness/OpRegistry.h:2043-2050
+ * float accumulator; tests/runtime/RuntimeTests.cpp:2907-2920 double accumulator),
+ * output rows spread over the OpenMP threads. */
+ORC_API void orc_matmul_dense(const float *A, const float *Wf, float *C, size_t M, size_t K, size_t N,
+                              size_t lda, size_t ldw, size_t ldc, int acc64) {
+#pragma omp parallel for schedule(static)
+  for (long nn = 0; nn < (long)N; ++nn) {
+    const float *w = Wf + (size_t)nn * ldw;
+    for (size_t m = 0; m < M; ++m) {
+      const float *a = A + m * lda;
+      if (acc64) {
+        double sum = 0.0;
+        for (size_t k = 0; k < K; ++k) sum += (double)a[k] * (double)w[k];
+        C[m * ldc + (size_t)nn] = (float)sum;
+      } else {
+        float sum = 0.0f;
+        for (size_t k = 0; k < K; ++k) sum += a[k] * w[k];
+        C[m * ldc + (size_t)nn] = sum;
+      }
+    }
+  }
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -202,6 +202,18 @@ def qmatmul_blocks_fast(fmt: int, A, W, M: int, K: int, N: int) -> np.ndarray:
     return Cm
 
 
+def matmul_dense(A, Wf, *, acc64=False) -> np.ndarray:
+    """C[M,N] = A[M,K] * Wf[N,K]^T with the reference tests' scalar loop."""
+    A = np.ascontiguousarray(A, dtype=np.float32)
+    Wf = np.ascontiguousarray(Wf, dtype=np.float32)
+    M, K = A.shape
+    N = Wf.shape[0]
+    Cm = np.zeros((M, N), dtype=np.float32)
+    lib().orc_matmul_dense(_p(A), _p(Wf), _p(Cm), C.c_size_t(M), C.c_size_t(K), C.c_size_t(N), C.c_size_t(K),
+                           C.c_size_t(K), C.c_size_t(N), C.c_int(int(acc64)))
+    return Cm
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 
@@ -225,6 +237,26 @@ def _with_gguf(fmt: int, raw, rows: int, cols: int, fn):
         return fn(path.encode())
     finally:
         os.unlink(path)
+
+
+def ref_write_file(fmt: int, raw, rows: int, cols: int) -> str:
+    """Writes a one-tensor GGUF file for the reference's reader; caller unlinks it."""
+    from .gguf_file import write_gguf
+
+    d = "/dev/shm" if os.path.isdir("/dev/shm") else None
+    fd, path = tempfile.mkstemp(suffix=".gguf", dir=d)
+    os.close(fd)
+    write_gguf(path, [("w", _TYPE_NAME[fmt], (rows, cols), _u8(raw))])
+    return path
+
+
+def ref_dequant_path(path: str, rows: int, cols: int) -> np.ndarray:
+    """GGUFReader(path).read_tensor_f32("w"): the reference's file read + CPU dequantiser."""
+    out = np.empty(rows * cols, dtype=np.float32)
+    rc = ref().cutref_read_f32(path.encode(), b"w", _p(out), C.c_size_t(out.size))
+    if rc:
+        raise RuntimeError(ref().cutref_last_error().decode())
+    return out.reshape(rows, cols)
 
 
 def ref_dequant(fmt: int, raw, rows: int, cols: int) -> np.ndarray:

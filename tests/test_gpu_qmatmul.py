@@ -1,0 +1,329 @@
+"""GPU parity: cutb_qmatmul against the CPU checker on the same seeded inputs.
+
+Tolerance: rel-L2 <= 1e-3 against the exact-dequant, double-accumulated
+reference (fp32 accumulate on the device); the reference's own per-element
+tolerances are used where its tests are replayed."""
+import numpy as np
+import pytest
+
+import refdata as R
+from cut_b200 import _lib as L
+from cut_b200 import synth
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+FMTS = [synth.Q8_0, synth.Q4_0, synth.Q4_K]
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu():
+    import torch
+
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+
+
+def _inputs(fmt, M, K, N, dtype, seed):
+    W = synth.make_weights(fmt, N, K, seed)
+    A = synth.make_activations(M, K, seed + 1, dtype)
+    return A, W
+
+
+def _ref(fmt, A, W, M, K, N, **kw):
+    return O.qmatmul_blocks(fmt, A.astype(np.float32), W, M, K, N, **kw)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("M", [1, 2, 5, 8])
+@pytest.mark.parametrize("K,N", [(256, 16), (512, 40), (1024, 1000), (4096, 2368)])
+def test_gemv_mma_matches_checker(fmt, dtype, M, K, N):
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M * 1000 + K + N + fmt)
+    got, used, st = run_blocks(fmt, A, W, N)
+    assert used == L.VARIANT_GEMV_MMA and st == 0
+    assert rel_l2(got, _ref(fmt, A, W, M, K, N)) <= TOL
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("dtype,M", [(np.float16, 16), (np.float16, 32), (np.float32, 12), (np.float32, 16)])
+def test_gemv_mma_wide_batches(fmt, dtype, M):
+    from gpu_util import rel_l2, run_blocks
+
+    K, N = 1024, 264
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M + fmt)
+    got, used, st = run_blocks(fmt, A, W, N)
+    assert used == L.VARIANT_GEMV_MMA and st == 0
+    assert rel_l2(got, _ref(fmt, A, W, M, K, N)) <= TOL
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("M,K,N", [(1, 32 * 8, 3), (3, 32 * 24, 37), (33, 512, 64), (2, 4096, 512)])
+def test_generic_matches_checker(fmt, dtype, M, K, N):
+    from gpu_util import rel_l2, run_blocks
+
+    if fmt == synth.Q4_K and K % 256:
+        K = (K // 256 + 1) * 256
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M + K + N)
+    got, used, st = run_blocks(fmt, A, W, N, variant=L.VARIANT_GENERIC)
+    assert used == L.VARIANT_GENERIC
+    assert rel_l2(got, _ref(fmt, A, W, M, K, N)) <= TOL
+
+
+def test_odd_k_routes_to_generic():
+    from gpu_util import rel_l2, run_blocks
+
+    M, K, N = 2, 32 * 5, 10  # K not a multiple of 256: no bulk-copy path
+    A, W = _inputs(synth.Q4_0, M, K, N, np.float32, seed=3)
+    got, used, _ = run_blocks(synth.Q4_0, A, W, N)
+    assert used == L.VARIANT_GENERIC
+    assert rel_l2(got, _ref(synth.Q4_0, A, W, M, K, N)) <= TOL
+
+
+# ---- the benchmark configurations at full size ----
+def test_config1_q8_0_4096x4096_fp32():
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(synth.Q8_0, 1, 4096, 4096, np.float32, seed=101)
+    got, used, st = run_blocks(synth.Q8_0, A, W, 4096)
+    assert used == L.VARIANT_GEMV_MMA and st == 0
+    assert rel_l2(got, _ref(synth.Q8_0, A, W, 1, 4096, 4096)) <= TOL
+
+
+@pytest.mark.parametrize("B", [1, 8])
+def test_config2_q4_0_11008x4096_fp16(B):
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(synth.Q4_0, B, 4096, 11008, np.float16, seed=202)
+    got, used, st = run_blocks(synth.Q4_0, A, W, 11008)
+    assert used == L.VARIANT_GEMV_MMA and st == 0
+    assert rel_l2(got, _ref(synth.Q4_0, A, W, B, 4096, 11008)) <= TOL
+
+
+@pytest.mark.parametrize("B", [1, 8])
+def test_q4_k_decode_14336x4096_fp16(B):
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(synth.Q4_K, B, 4096, 14336, np.float16, seed=303)
+    got, used, st = run_blocks(synth.Q4_K, A, W, 14336)
+    assert used == L.VARIANT_GEMV_MMA and st == 0
+    assert rel_l2(got, _ref(synth.Q4_K, A, W, B, 4096, 14336)) <= TOL
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_long_k_and_few_rows_use_split_k(fmt):
+    """70B-shape slices: K = 28672 with N/8 rows per GPU -> K is split across CTAs
+    and summed in a fixed order from the workspace."""
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev, rel_l2, run_blocks
+
+    M, K, N = 8, 28672, 1024
+    A, W = _inputs(fmt, M, K, N, np.float16, seed=404 + fmt)
+    d, _, keep = ops.make_desc(dev(A), dev(W), fmt, N)
+    assert ops.workspace_bytes(d) > 0
+    with pytest.raises(L.CutbError) as e:
+        ops.launch(d)  # no workspace supplied
+    assert e.value.status == L.ERR_WORKSPACE
+    got, used, st = run_blocks(fmt, A, W, N)
+    assert used == L.VARIANT_GEMV_MMA and st == 0
+    assert rel_l2(got, _ref(fmt, A, W, M, K, N)) <= TOL
+    got2, _, _ = run_blocks(fmt, A, W, N)
+    assert np.array_equal(got, got2)  # deterministic summation order
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_gemv_agrees_with_generic_and_is_deterministic(fmt):
+    from gpu_util import rel_l2, run_blocks
+
+    M, K, N = 4, 2048, 777
+    A, W = _inputs(fmt, M, K, N, np.float16, seed=55)
+    a, _, _ = run_blocks(fmt, A, W, N)
+    b, _, _ = run_blocks(fmt, A, W, N)
+    g, _, _ = run_blocks(fmt, A, W, N, variant=L.VARIANT_GENERIC)
+    assert np.array_equal(a, b)
+    assert rel_l2(a, g) <= 1e-5
+
+
+@pytest.mark.parametrize("variant", [L.VARIANT_AUTO, L.VARIANT_GENERIC])
+@pytest.mark.parametrize("ftype,fop", [(1, 133), (1, 130), (1, 132), (2, 0), (2, 2)])
+def test_fused_epilogues(variant, ftype, fop):
+    """SiLU / ReLU / GELU and residual add / mul, the epilogues the runner uses
+    (interface/runner/llama/llama.cpp:2461; MatMulQ4Common.cuh:63-114)."""
+    from gpu_util import run_blocks
+
+    M, K, N = 3, 512, 200
+    A, W = _inputs(synth.Q4_0, M, K, N, np.float32, seed=66)
+    D = synth.make_activations(M, N, 67) if ftype == 2 else None
+    got, _, _ = run_blocks(synth.Q4_0, A, W, N, variant=variant, D_np=D, fusion_type=ftype, fusion_op=fop)
+    ref = _ref(synth.Q4_0, A, W, M, K, N, D=D, fusion_type=ftype, fusion_op=fop)
+    assert np.allclose(got, ref, rtol=2e-3, atol=2e-4)
+
+
+def test_large_activation_magnitudes_fp32():
+    """fp32 activations far outside the fp16 range still contract correctly
+    (power-of-two rescale before the hi/lo split)."""
+    from gpu_util import rel_l2, run_blocks
+
+    M, K, N = 2, 1024, 64
+    A, W = _inputs(synth.Q8_0, M, K, N, np.float32, seed=77)
+    A[0] *= 3.0e6
+    A[1] *= 2.0e-7
+    got, used, _ = run_blocks(synth.Q8_0, A, W, N)
+    assert used == L.VARIANT_GEMV_MMA
+    ref = _ref(synth.Q8_0, A, W, M, K, N)
+    assert rel_l2(got[0], ref[0]) <= TOL and rel_l2(got[1], ref[1]) <= TOL
+
+
+def test_invalid_descriptors_return_codes():
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev
+
+    A, W = _inputs(synth.Q4_0, 1, 256, 8, np.float32, seed=1)
+    At, Wt = dev(A), dev(W)
+    with pytest.raises(L.CutbError) as e:
+        ops.qmatmul(At, Wt, synth.Q4_0, 9)  # W too small for N = 9
+    assert e.value.status == L.ERR_INVALID
+    with pytest.raises(L.CutbError) as e:
+        ops.qmatmul(At, Wt, 5, 8)
+    assert e.value.status == L.ERR_INVALID
+    with pytest.raises(L.CutbError) as e:
+        ops.qmatmul(At[:, :100], Wt, synth.Q4_0, 8)  # K not a multiple of 32
+    assert e.value.status == L.ERR_INVALID
+    with pytest.raises(L.CutbError) as e:
+        ops.qmatmul(At, Wt, synth.Q4_0, 8, fusion_type=2)  # binary fusion without D
+    assert e.value.status == L.ERR_INVALID
+    with pytest.raises(L.CutbError) as e:
+        ops.qmatmul(dev(A[:, :32].copy()), Wt, synth.Q4_0, 8, variant=L.VARIANT_GEMV_MMA)  # K = 32: no bulk path
+    assert e.value.status == L.ERR_UNSUPPORTED
+    with pytest.raises(RuntimeError, match="1D or 2D"):
+        ops.qmatmul(torch.zeros((1, 1, 256), device="cuda"), Wt, synth.Q4_0, 8)
+
+
+# ---- the reference's runtime layout ([K,N] planes) and its known-answer tests ----
+def _run_planes(q4, A, B, S, M, K, N, *, affine=False, D=None, ftype=0, fop=0, dtype=np.float32):
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev
+
+    ldb = R.pad4(N // 2 if q4 else N)
+    lds = R.pad4(N)
+    Bp = np.zeros((K, ldb), np.uint8)
+    Bp[:, : B.shape[1]] = B.view(np.uint8)
+    Sp = np.zeros((S.shape[0], lds), np.uint16)
+    Sp[:, :N] = S
+    out = ops.qmatmul(dev(A.astype(dtype)), dev(Bp), L.Q4_0 if q4 else L.Q8_0, N, layout=L.LAYOUT_KN_PLANES,
+                      scales=dev(Sp), affine=affine, ldb=ldb, lds=lds, D=dev(D) if D is not None else None,
+                      fusion_type=ftype, fusion_op=fop)
+    torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+def test_reference_q8_simple_and_withscales():
+    # tests/harness/OpRegistry.h:1995-2026
+    c = _run_planes(False, np.ones((1, 32), np.float32), np.tile(np.array([1, 2], np.int8), (32, 1)),
+                    R.f16_trunc([1.0, 1.0]).reshape(1, 2), 1, 32, 2)
+    assert abs(c[0, 0] - 32.0) <= 1e-3 and abs(c[0, 1] - 64.0) <= 1e-3
+    c = _run_planes(False, np.ones((1, 64), np.float32), np.full((64, 2), 4, np.int8),
+                    R.f16_trunc([0.5, 2.0, 1.0, 0.25]).reshape(2, 2), 1, 64, 2)
+    assert abs(c[0, 0] - 192.0) <= 1.0 and abs(c[0, 1] - 288.0) <= 1.0
+
+
+def test_reference_q4_simple_and_withscales():
+    # tests/harness/OpRegistry.h:2054-2086
+    c = _run_planes(True, np.ones((1, 32), np.float32), np.full((32, 1), R.pack_nibbles(9, 10), np.uint8),
+                    R.f16_trunc([1.0, 1.0]).reshape(1, 2), 1, 32, 2)
+    assert abs(c[0, 0] - 32.0) <= 1e-3 and abs(c[0, 1] - 64.0) <= 1e-3
+    c = _run_planes(True, np.ones((1, 64), np.float32), np.full((64, 1), R.pack_nibbles(12, 12), np.uint8),
+                    R.f16_trunc([0.5, 2.0, 1.0, 0.25]).reshape(2, 2), 1, 64, 2)
+    assert abs(c[0, 0] - 192.0) <= 1.0 and abs(c[0, 1] - 288.0) <= 1.0
+
+
+@pytest.mark.parametrize("M,K,N", [(2, 64, 4), (1, 512, 16)])
+def test_reference_q8_vsregular_and_allvariants(M, K, N):
+    # tests/harness/OpRegistry.h:2028-2052, 2118-2152
+    A, B, sf, sbits = R.case_q8(M, K, N, "rand")
+    got = _run_planes(False, A, B, sbits, M, K, N)
+    ref = A.astype(np.float64) @ (B.astype(np.float64) * np.repeat(sf.astype(np.float64), 32, axis=0))
+    assert np.all(np.abs(got - ref) <= np.abs(ref) * 0.01 + 0.1)
+    assert np.allclose(got, O.qmatmul_planes(False, False, A, B, sbits, M, K, N, acc64=True), rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("M,K,N", [(2, 64, 4), (1, 64, 4)])
+def test_reference_q4_vsreference_and_allvariants(M, K, N):
+    # tests/harness/OpRegistry.h:2088-2116, 2154-2192
+    A, packed, nib, sf, sbits = R.case_q4(M, K, N, "rand")
+    got = _run_planes(True, A, packed, sbits, M, K, N)
+    ref = A.astype(np.float64) @ ((nib.astype(np.float64) - 8) * np.repeat(sf.astype(np.float64), 32, axis=0))
+    assert np.all(np.abs(got - ref) <= np.abs(ref) * 0.01 + 0.1)
+    assert np.allclose(got, O.qmatmul_planes(True, False, A, packed, sbits, M, K, N, acc64=True), rtol=1e-5, atol=1e-4)
+
+
+def test_reference_q8_model_geometry_batched_vs_per_row():
+    # tests/runtime/RuntimeTests.cpp:2861-2938 (M=4, K=5120, N=4096, fp64 CPU reference)
+    M, K, N = 4, 5120, 4096
+    A = R.mt19937_uniform(-1.0, 1.0, 42, M * K).reshape(M, K)
+    i = np.arange(K * N, dtype=np.int64)
+    B = ((i * 7 + 3) % 21 - 10).astype(np.int8).reshape(K, N)
+    sf = ((1.0 + (np.arange((K // 32) * N) % 7)) * 0.03125).astype(np.float32).reshape(K // 32, N)
+    sbits = sf.astype(np.float16).view(np.uint16)  # exactly representable
+    batched = _run_planes(False, A, B, sbits, M, K, N)
+    per_row = np.concatenate([_run_planes(False, A[m:m + 1], B, sbits, 1, K, N) for m in range(M)])
+    ref = A.astype(np.float64) @ (B.astype(np.float64) * np.repeat(sf.astype(np.float64), 32, axis=0))
+    assert np.all(np.abs(batched - ref) <= np.abs(ref) * 2e-3 + 0.05)
+    assert np.all(np.abs(batched - per_row) <= np.abs(per_row) * 2e-3 + 0.05)
+
+
+@pytest.mark.parametrize("M,K,N,silu", [(13, 4096, 5120, False), (13, 5120, 8192, True), (33, 5120, 4096, True)])
+def test_reference_q8_ffn_shapes_with_silu(M, K, N, silu):
+    # tests/runtime/RuntimeTests.cpp:3054-3118 (N trimmed from 32768 to keep the CPU reference quick)
+    A = R.mt19937_uniform(-1.0, 1.0, 42, M * K).reshape(M, K)
+    i = np.arange(K * N, dtype=np.int64)
+    B = ((i * 7 + 3) % 21 - 10).astype(np.int8).reshape(K, N)
+    sf = ((1.0 + (np.arange((K // 32) * N) % 7)) * 0.03125).astype(np.float32).reshape(K // 32, N)
+    sbits = sf.astype(np.float16).view(np.uint16)
+    got = _run_planes(False, A, B, sbits, M, K, N, ftype=1 if silu else 0, fop=133)
+    ref = A.astype(np.float64) @ (B.astype(np.float64) * np.repeat(sf.astype(np.float64), 32, axis=0))
+    if silu:
+        ref = ref / (1.0 + np.exp(-ref))
+    assert np.all(np.abs(got - ref) <= np.abs(ref) * 2e-3 + 0.05)
+
+
+def test_planes_layout_equals_block_layout_through_loader_repack():
+    """GGUF blocks -> the loader's plane separation and the load-time repacks
+    (gguf_reader.cpp:389-501, TransposeQ4Nibble) -> plane kernel == block kernel."""
+    from gpu_util import rel_l2, run_blocks
+
+    N, K, M = 64, 512, 3
+    A = synth.make_activations(M, K, 9)
+    w8 = synth.make_weights(synth.Q8_0, N, K, 21)
+    vals, sc = O.q8_separate(w8, N, K)
+    a = _run_planes(False, A, np.ascontiguousarray(vals.T), np.ascontiguousarray(sc.T), M, K, N)
+    b, _, _ = run_blocks(synth.Q8_0, A, w8, N)
+    assert rel_l2(a, b) <= 1e-5
+    w4 = synth.make_weights(synth.Q4_0, N, K, 22)
+    packed, sc = O.q4_separate(w4, N, K)
+    a = _run_planes(True, A, O.transpose_q4(packed, N, K), np.ascontiguousarray(sc.T), M, K, N)
+    b, _, _ = run_blocks(synth.Q4_0, A, w4, N)
+    assert rel_l2(a, b) <= 1e-5
+
+
+def test_affine_q4_planes_from_q4k():
+    """The runner's Q4_K -> affine re-encode (llama.cpp:573-619) through the plane kernel."""
+    from gpu_util import rel_l2
+
+    N, K, M = 32, 512, 2
+    A = synth.make_activations(M, K, 10)
+    w = synth.make_weights(synth.Q4_K, N, K, 23)
+    packedT, scalesT = O.requant_q4k_affine(w, N, K)
+    got = _run_planes(True, A, packedT, scalesT, M, K, N, affine=True)
+    assert rel_l2(got, O.qmatmul_planes(True, True, A, packedT, scalesT, M, K, N, acc64=True)) <= 1e-5
+    assert rel_l2(got, _ref(synth.Q4_K, A, w, M, K, N)) <= TOL
