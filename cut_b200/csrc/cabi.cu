@@ -162,7 +162,7 @@ int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
   switch (v) {
     case CUTB_VARIANT_GEMV_MMA:
       if (!qgemv_blocks_supported(*desc)) {
-        set_last_error("qmatmul: variant %s needs GGUF blocks, K %% 256 == 0, 16-byte aligned W and M <= 32 (fp16) / 16 (fp32)",
+        set_last_error("qmatmul: variant %s needs GGUF blocks, K %% 256 == 0, 16-byte aligned W and M <= 16 (fp16) / 8 (fp32)",
                        cutb_variant_name(v));
         return CUTB_ERR_UNSUPPORTED;
       }

@@ -70,7 +70,7 @@ enum { CUTB_FUSION_NONE = 0, CUTB_FUSION_UNARY = 1, CUTB_FUSION_BINARY = 2 };
 enum {
   CUTB_VARIANT_AUTO = -1,
   CUTB_VARIANT_GENERIC = 0, /* any shape, SIMT, exact fp32 dequant + FMA */
-  CUTB_VARIANT_GEMV_MMA = 1, /* decode: bulk-copy ring + warp MMA, M <= 32 (fp16 A) / 16 (fp32 A) */
+  CUTB_VARIANT_GEMV_MMA = 1, /* decode: bulk-copy ring + int8 warp MMA, M <= 16 (fp16 A) / 8 (fp32 A) */
   CUTB_VARIANT_GEMM_TC = 2  /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory */
 };
 

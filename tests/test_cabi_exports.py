@@ -78,9 +78,10 @@ def test_select_variant_and_workspace_plan_without_device():
         return d
 
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 1, 4096, 11008))) == L.VARIANT_GEMV_MMA
-    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 32, 4096, 11008))) == L.VARIANT_GEMV_MMA
+    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 16, 4096, 11008))) == L.VARIANT_GEMV_MMA
+    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 17, 4096, 11008))) != L.VARIANT_GEMV_MMA
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 1, 4096, 4096, L.F32))) == L.VARIANT_GEMV_MMA
-    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 17, 4096, 4096, L.F32))) != L.VARIANT_GEMV_MMA
+    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 9, 4096, 4096, L.F32))) != L.VARIANT_GEMV_MMA
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 1, 96, 8))) == L.VARIANT_GENERIC
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 1, 64, 4, L.F32, L.LAYOUT_KN_PLANES))) == L.VARIANT_GENERIC
     assert lib.cutb_qmatmul_workspace_bytes(C.byref(desc(L.Q4_0, 1, 4096, 11008))) == 0

@@ -48,7 +48,7 @@ def test_gemv_mma_matches_checker(fmt, dtype, M, K, N):
 
 
 @pytest.mark.parametrize("fmt", FMTS)
-@pytest.mark.parametrize("dtype,M", [(np.float16, 16), (np.float16, 32), (np.float32, 12), (np.float32, 16)])
+@pytest.mark.parametrize("dtype,M", [(np.float16, 9), (np.float16, 16), (np.float32, 5), (np.float32, 8)])
 def test_gemv_mma_wide_batches(fmt, dtype, M):
     from gpu_util import rel_l2, run_blocks
 
@@ -147,7 +147,7 @@ def test_gemv_agrees_with_generic_and_is_deterministic(fmt):
     b, _, _ = run_blocks(fmt, A, W, N)
     g, _, _ = run_blocks(fmt, A, W, N, variant=L.VARIANT_GENERIC)
     assert np.array_equal(a, b)
-    assert rel_l2(a, g) <= 1e-5
+    assert rel_l2(a, g) <= 2e-4  # 16-bit block floating point activations vs exact fp32
 
 
 @pytest.mark.parametrize("variant", [L.VARIANT_AUTO, L.VARIANT_GENERIC])
