@@ -50,20 +50,17 @@ namespace {
 
 constexpr int GV_ROWS = 16;
 
-// Launch shapes.  WARPS warps per CTA share a row tile and split K; every warp
-// owns STAGES stages of SG granules (256 weights) per row.
-template <int WARPS_, int SG_, int STAGES_, int MINB_> struct GvCfg {
-  static constexpr int WARPS = WARPS_, SG = SG_, STAGES = STAGES_, MINB = MINB_;
-};
+constexpr int GV_WARPS = 16;                      // consumer warps; one more warp issues the copies
+constexpr int GV_THREADS = (GV_WARPS + 1) * 32;
+constexpr int GV_KC = GV_WARPS;                   // granules (256 weights) per row and stage, one per consumer warp
 
-// Shared-memory row stride of a stage (bytes): the smallest multiple of 16 >=
-// SG granules whose word stride keeps the 8 row groups of a warp on disjoint
-// banks for the access pattern of the format (4 consecutive words per row for
-// Q8_0 / Q4_0, 8 for Q4_K).
-__host__ __device__ constexpr int gv_row_stride(int fmt, int sg) {
-  return fmt == CUTB_Q8_0 ? (sg == 1 ? 272 : 560)      // 68 words = 4 (mod 32); 140 = 12 (mod 32)
-         : fmt == CUTB_Q4_0 ? (sg == 1 ? 144 : 304)    // 36 = 4; 76 = 12
-                            : (sg == 1 ? 160 : 288);   // 40 = 8; 72 = 8
+// Shared-memory row stride of a stage (bytes): GV_KC granules plus the padding
+// that keeps the 8 row groups of a warp on disjoint banks for the access
+// pattern of the format (4 consecutive words per row for Q8_0 / Q4_0, 8 for Q4_K).
+__host__ __device__ constexpr int gv_row_stride(int fmt) {
+  return fmt == CUTB_Q8_0 ? 16 * 272 + 16    // 1092 words = 4 (mod 32)
+         : fmt == CUTB_Q4_0 ? 16 * 144 + 16  // 580 words = 4 (mod 32)
+                            : 16 * 144 + 32; // 584 words = 8 (mod 32)
 }
 
 struct GvParams {
@@ -79,6 +76,7 @@ struct GvParams {
   uint32_t M, K, N;
   uint32_t gran_per_split;
   uint32_t ksplit;
+  uint32_t stages;
   int fusion_type, fusion_op;
   int a_f32;
   int *status;
@@ -364,10 +362,9 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     }
 }
 
-template <int FMT, bool AF32, int NT, typename CFG>
-__global__ void __launch_bounds__(CFG::WARPS * 32, CFG::MINB) qgemv_blocks_kernel(const GvParams p) {
-  constexpr int WARPS = CFG::WARPS, SG = CFG::SG, STAGES = CFG::STAGES, THREADS = WARPS * 32;
-  constexpr int RS = gv_row_stride(FMT, SG);
+template <int FMT, bool AF32, int NT>
+__global__ void __launch_bounds__(GV_THREADS, 1) qgemv_blocks_kernel(const GvParams p) {
+  constexpr int RS = gv_row_stride(FMT);
   constexpr uint32_t GB = granule_bytes(FMT);
   constexpr uint32_t STAGE_BYTES = GV_ROWS * RS;
   constexpr uint32_t NV = NT * 4, NC8 = NT * 8;
@@ -378,55 +375,72 @@ __global__ void __launch_bounds__(CFG::WARPS * 32, CFG::MINB) qgemv_blocks_kerne
   const uint32_t ncols = 2 * nvr;
   const uint32_t ncp = (ncols < NC8) ? ncols + 1 : ncols;
   const uint32_t nblk_alloc = p.gran_per_split * 8;
+  const uint32_t S = p.stages;
 
   uint8_t *ring = smem;
-  uint8_t *act = ring + WARPS * STAGES * STAGE_BYTES;
+  uint8_t *act = ring + (size_t)S * STAGE_BYTES;
   float *esc = reinterpret_cast<float *>(act + (size_t)nblk_alloc * ncp * 32);
   float *sx = esc + nblk_alloc * NV;
-  float *red = sx + (FMT == CUTB_Q4_K ? nblk_alloc * NV : 0);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(red + WARPS * GV_ROWS * NV);
+  float *red = sx + (FMT == CUTB_Q4_K ? nblk_alloc * NV : 0);  // two buffers of [GV_WARPS][16][NV]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(red + 2 * GV_WARPS * GV_ROWS * NV);  // full[S], empty[S]
 
-  // rows of this CTA, granules (256 weights) of this K split and of this warp
+  // rows of this CTA and granules (256 weights) of this K split; a stage holds
+  // 16 rows x up to GV_KC granules, one granule per consumer warp
   const uint32_t r0 = (uint32_t)((uint64_t)blockIdx.x * p.N / gridDim.x);
   const uint32_t r1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * p.N / gridDim.x);
   const uint32_t G = p.K >> 8;
   const uint32_t gs0 = blockIdx.y * p.gran_per_split;
   const uint32_t gs1 = min(G, gs0 + p.gran_per_split);
   const uint32_t ng = gs1 - gs0;
-  const uint32_t wg0 = gs0 + ng * warp / WARPS, wg1 = gs0 + ng * (warp + 1) / WARPS;
-  const uint32_t spt = (wg1 - wg0 + SG - 1) / SG;  // stages per row tile for this warp
+  const uint32_t cpt = (ng + GV_KC - 1) / GV_KC;  // K chunks (stages) per row tile
   const uint32_t ntiles = (r1 - r0 + GV_ROWS - 1) / GV_ROWS;
-  const uint32_t total_stages = ntiles * spt;
+  const uint32_t total_stages = ntiles * cpt;
 
-  const uint32_t ring_w = smem_u32(ring) + warp * STAGES * STAGE_BYTES;
-  const uint32_t bar_w = smem_u32(bars) + warp * STAGES * 8;
+  const uint32_t ring_u = smem_u32(ring);
+  const uint32_t full_u = smem_u32(bars), empty_u = full_u + S * 8;
 
-  if (lane == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(bar_w + s * 8, 1);
+  if (tid == 0) {
+    for (uint32_t s = 0; s < S; ++s) {
+      mbar_init(full_u + s * 8, 1);
+      mbar_init(empty_u + s * 8, GV_WARPS);
+    }
     fence_mbar_init();
   }
-  __syncwarp();
-
-  auto issue = [&](uint32_t j) {
-    const uint32_t tile = j / spt, s = j - tile * spt, slot = j % STAGES;
-    const uint32_t gq = wg0 + s * SG;
-    const uint32_t bytes = min((uint32_t)SG, wg1 - gq) * GB;
-    const uint32_t row_base = r0 + tile * GV_ROWS;
-    const uint32_t valid = min((uint32_t)GV_ROWS, r1 - row_base);
-    const uint32_t bar = bar_w + slot * 8;
-    if (lane == 0) mbar_arrive_expect_tx(bar, valid * bytes);
-    __syncwarp();
-    if (lane < valid)
-      bulk_g2s(ring_w + slot * STAGE_BYTES + lane * RS, p.W + (uint64_t)(row_base + lane) * p.row_bytes + (uint64_t)gq * GB,
-               bytes, bar);
-  };
-
-  // Put the first weight bytes in flight before anything else.
-  const uint32_t pre = min((uint32_t)STAGES, total_stages);
-  for (uint32_t j = 0; j < pre; ++j) issue(j);
-
-  stage_activations<FMT, AF32, NT, THREADS>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid);
   __syncthreads();
+
+  if (warp == GV_WARPS) {
+    // ---- producer warp: whole row segments, one bulk copy per row and stage ----
+    bool dead = false;
+    for (uint32_t j = 0; j < total_stages && !dead; ++j) {
+      const uint32_t tile = j / cpt, c = j - tile * cpt, slot = j % S;
+      if (j >= S) {
+        const bool ok = mbar_wait_bounded(empty_u + slot * 8, ((j / S) - 1) & 1u);
+        if (!__all_sync(0xffffffffu, ok)) {
+          dead = true;
+          if (lane == 0 && p.status) atomicExch(p.status, (int)CUTB_ERR_TIMEOUT);
+          break;
+        }
+      }
+      const uint32_t gq = gs0 + c * GV_KC;
+      const uint32_t bytes = min((uint32_t)GV_KC, gs1 - gq) * GB;
+      const uint32_t row_base = r0 + tile * GV_ROWS;
+      const uint32_t valid = min((uint32_t)GV_ROWS, r1 - row_base);
+      const uint32_t bar = full_u + slot * 8;
+      if (lane == 0) mbar_arrive_expect_tx(bar, valid * bytes);
+      __syncwarp();
+      if (lane < valid)
+        bulk_g2s(ring_u + slot * STAGE_BYTES + lane * RS, p.W + (uint64_t)(row_base + lane) * p.row_bytes + (uint64_t)gq * GB,
+                 bytes, bar);
+    }
+    // stay resident until every copy issued here has landed (bounded)
+    const uint32_t first = total_stages > S ? total_stages - S : 0;
+    for (uint32_t j = first; j < total_stages; ++j) (void)mbar_wait_bounded(full_u + (j % S) * 8, (j / S) & 1u, 1u << 18);
+    return;
+  }
+
+  // ---- consumer warps ---------------------------------------------------------
+  stage_activations<FMT, AF32, NT, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid);
+  asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
 
   // per-lane activation fragment offsets (idle lanes read the zero column)
   uint32_t aoff[NT];
@@ -443,48 +457,48 @@ __global__ void __launch_bounds__(CFG::WARPS * 32, CFG::MINB) qgemv_blocks_kerne
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
 
-    for (uint32_t s = 0; s < spt; ++s) {
-      const uint32_t j = tile * spt + s, slot = j % STAGES, parity = (j / STAGES) & 1u;
+    for (uint32_t c = 0; c < cpt; ++c) {
+      const uint32_t j = tile * cpt + c, slot = j % S, parity = (j / S) & 1u;
       if (!dead) {
-        const bool ok = mbar_wait_bounded(bar_w + slot * 8, parity);
+        const bool ok = mbar_wait_bounded(full_u + slot * 8, parity);
         if (!__all_sync(0xffffffffu, ok)) {
           dead = true;
           if (lane == 0 && p.status) atomicExch(p.status, (int)CUTB_ERR_TIMEOUT);
         }
       }
-      if (!dead) {
-        const uint32_t gq = wg0 + s * SG;
-        const uint32_t ngr = min((uint32_t)SG, wg1 - gq);
-        const uint32_t kb0 = (gq - gs0) * 8;  // first 32-weight block of the stage inside the split
-        compute_stage<FMT, NT, RS>(ring_w + slot * STAGE_BYTES, ngr, act_u + kb0 * act_stride, act_stride, aoff,
+      const uint32_t gq = gs0 + c * GV_KC + warp;  // this warp's granule of the chunk
+      if (!dead && gq < gs1) {
+        const uint32_t kb0 = (gq - gs0) * 8;  // first 32-weight block of the granule inside the split
+        compute_stage<FMT, NT, RS>(ring_u + slot * STAGE_BYTES + warp * GB, 1, act_u + kb0 * act_stride, act_stride, aoff,
                                    esc_u + kb0 * NV * 4, sx_u + kb0 * NV * 4, g, t, tot);
       }
       __syncwarp();
-      if (!dead && j + STAGES < total_stages) issue(j + STAGES);
+      if (lane == 0) mbar_arrive(empty_u + slot * 8);
     }
 
-    // meet the other warps' K slices in a fixed order
+    // meet the other warps' K slices in a fixed order (double-buffered: one barrier per tile)
+    float *rbuf = red + (size_t)(tile & 1) * GV_WARPS * GV_ROWS * NV;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      float *r = red + ((size_t)warp * GV_ROWS) * NV + nt * 4 + t;
+      float *r = rbuf + ((size_t)warp * GV_ROWS) * NV + nt * 4 + t;
       r[g * NV] = tot[nt][0];
       r[(g + 8) * NV] = tot[nt][1];
     }
-    __syncthreads();
+    asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
     const uint32_t row_base = r0 + tile * GV_ROWS;
-    for (uint32_t o = tid; o < GV_ROWS * p.M; o += THREADS) {
+    for (uint32_t o = tid; o < GV_ROWS * p.M; o += GV_WARPS * 32) {
       const uint32_t row = o % GV_ROWS, m = o / GV_ROWS, n = row_base + row;
       if (n < r1) {
         float sum = 0.f;
         if constexpr (AF32) {
 #pragma unroll
-          for (int w = 0; w < WARPS; ++w) {
-            const float2 hl = *reinterpret_cast<const float2 *>(red + ((size_t)w * GV_ROWS + row) * NV + 2 * m);
+          for (int w = 0; w < GV_WARPS; ++w) {
+            const float2 hl = *reinterpret_cast<const float2 *>(rbuf + ((size_t)w * GV_ROWS + row) * NV + 2 * m);
             sum += hl.x + hl.y;
           }
         } else {
 #pragma unroll
-          for (int w = 0; w < WARPS; ++w) sum += red[((size_t)w * GV_ROWS + row) * NV + m];
+          for (int w = 0; w < GV_WARPS; ++w) sum += rbuf[((size_t)w * GV_ROWS + row) * NV + m];
         }
         if (p.ksplit > 1) {
           p.partial[((size_t)blockIdx.y * p.M + m) * p.N + n] = sum;
@@ -493,16 +507,6 @@ __global__ void __launch_bounds__(CFG::WARPS * 32, CFG::MINB) qgemv_blocks_kerne
           p.C[(size_t)m * p.ldc + n] = apply_epilogue(sum, p.fusion_type, p.fusion_op, dv);
         }
       }
-    }
-    __syncthreads();
-  }
-
-  // A warp that gave up still owns copies in flight: give them a bounded
-  // chance to land before the CTA's shared memory is released.
-  if (dead) {
-    for (int s = 0; s < STAGES; ++s) {
-      (void)mbar_wait_bounded(bar_w + s * 8, 0, 1u << 16);
-      (void)mbar_wait_bounded(bar_w + s * 8, 1, 1u << 16);
     }
   }
 }
@@ -521,29 +525,18 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *_
 
 // ---- host side ---------------------------------------------------------------
 
-// The two launch shapes in use: 16 warps (decode shapes that give every warp at
-// least one granule per tile) and 8 warps for short K, one CTA per SM.  Q8_0
-// rows are twice as long, so its wide shape keeps two stages per warp.
-template <int FMT, bool WIDE> struct GvCfgFor {
-  using type = GvCfg<WIDE ? 16 : 8, 1, (FMT == CUTB_Q8_0 && WIDE) ? 2 : 4, 1>;
-};
-constexpr int gv_warps(bool wide) { return wide ? 16 : 8; }
-constexpr int gv_stages(int fmt, bool wide) { return (fmt == CUTB_Q8_0 && wide) ? 2 : 4; }
-
 struct GvPlan {
-  uint32_t nt, nvr, ncp, grid_x, ksplit, gran_per_split;
-  bool wide;
+  uint32_t nt, nvr, ncp, grid_x, ksplit, gran_per_split, stages;
   size_t smem;
 };
 
-size_t gv_smem_bytes(int fmt, bool wide, uint32_t nt, uint32_t ncp, uint32_t gran_per_split) {
+size_t gv_smem_bytes(int fmt, uint32_t stages, uint32_t nt, uint32_t ncp, uint32_t gran_per_split) {
   const size_t nblk = (size_t)gran_per_split * 8;
-  const size_t warps = gv_warps(wide), stages = gv_stages(fmt, wide);
-  size_t b = warps * stages * GV_ROWS * gv_row_stride(fmt, 1);
+  size_t b = (size_t)stages * GV_ROWS * gv_row_stride(fmt);
   b += nblk * ncp * 32;
   b += nblk * nt * 4 * 4 * (fmt == CUTB_Q4_K ? 2 : 1);
-  b += warps * GV_ROWS * nt * 4 * 4;
-  b += warps * stages * 8;
+  b += (size_t)2 * GV_WARPS * GV_ROWS * nt * 4 * 4;
+  b += 2 * stages * 8;
   return b;
 }
 
@@ -561,21 +554,24 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
   if (pl->grid_x * 2 <= (uint32_t)di.sm_count) want = (uint32_t)di.sm_count / pl->grid_x;
   if (want > G) want = G;
   const size_t limit = di.smem_optin;
+  // deepest ring that fits; split K further only when two stages do not fit
   for (uint32_t ks = want; ks <= G; ++ks) {
     const uint32_t gps = (G + ks - 1) / ks;
-    pl->wide = gps >= (uint32_t)gv_warps(true);
-    const size_t sm = gv_smem_bytes(d.format, pl->wide, pl->nt, pl->ncp, gps);
-    if (sm <= limit) {
-      pl->gran_per_split = gps;
-      pl->ksplit = (G + gps - 1) / gps;
-      pl->smem = sm;
-      return true;
+    for (uint32_t st = 4; st >= 2; --st) {
+      const size_t sm = gv_smem_bytes(d.format, st, pl->nt, pl->ncp, gps);
+      if (sm <= limit) {
+        pl->gran_per_split = gps;
+        pl->ksplit = (G + gps - 1) / gps;
+        pl->stages = st;
+        pl->smem = sm;
+        return true;
+      }
     }
   }
   return false;
 }
 
-template <int FMT, bool AF32, int NT, typename CFG>
+template <int FMT, bool AF32, int NT>
 int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   static int configured_device = -1;
   int dev = 0;
@@ -583,27 +579,21 @@ int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   if (configured_device != dev) {
     DeviceInfo di;
     if (int rc = get_device_info(&di)) return rc;
-    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AF32, NT, CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AF32, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)di.smem_optin));
     configured_device = dev;
   }
-  qgemv_blocks_kernel<FMT, AF32, NT, CFG><<<dim3(pl.grid_x, pl.ksplit), CFG::WARPS * 32, pl.smem, stream>>>(p);
+  qgemv_blocks_kernel<FMT, AF32, NT><<<dim3(pl.grid_x, pl.ksplit), GV_THREADS, pl.smem, stream>>>(p);
   CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;
-}
-
-template <int FMT, bool AF32, int NT>
-int gv_launch_cfg(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
-  return pl.wide ? gv_launch_inst<FMT, AF32, NT, typename GvCfgFor<FMT, true>::type>(p, pl, stream)
-                 : gv_launch_inst<FMT, AF32, NT, typename GvCfgFor<FMT, false>::type>(p, pl, stream);
 }
 
 template <int FMT, bool AF32>
 int gv_launch_nt(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   switch (pl.nt) {
-    case 1: return gv_launch_cfg<FMT, AF32, 1>(p, pl, stream);
-    case 2: return gv_launch_cfg<FMT, AF32, 2>(p, pl, stream);
-    default: return gv_launch_cfg<FMT, AF32, 4>(p, pl, stream);
+    case 1: return gv_launch_inst<FMT, AF32, 1>(p, pl, stream);
+    case 2: return gv_launch_inst<FMT, AF32, 2>(p, pl, stream);
+    default: return gv_launch_inst<FMT, AF32, 4>(p, pl, stream);
   }
 }
 
@@ -659,6 +649,7 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.N = d.N;
   p.gran_per_split = pl.gran_per_split;
   p.ksplit = pl.ksplit;
+  p.stages = pl.stages;
   p.fusion_type = d.fusion_type;
   p.fusion_op = d.fusion_op;
   p.a_f32 = af32;
