@@ -16,6 +16,7 @@ F32, F16 = 0, 1
 LAYOUT_GGUF_BLOCKS, LAYOUT_KN_PLANES = 0, 1
 FUSION_NONE, FUSION_UNARY, FUSION_BINARY = 0, 1, 2
 VARIANT_AUTO, VARIANT_GENERIC, VARIANT_GEMV_MMA, VARIANT_GEMM_TC = -1, 0, 1, 2
+FLAG_NO_OVERLAP = 1
 
 # every symbol include/cutb.h declares
 EXPORTS = [
@@ -37,6 +38,7 @@ class QMatmulDesc(C.Structure):
         ("fusion_type", C.c_int32), ("fusion_op", C.c_int32), ("variant", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
         ("status", C.c_void_p),
+        ("flags", C.c_uint32),
     ]
 
 

@@ -43,6 +43,7 @@ int get_device_info(DeviceInfo *out) {
     cache[dev].cc_major = prop.major;
     cache[dev].cc_minor = prop.minor;
     cache[dev].smem_optin = prop.sharedMemPerBlockOptin;
+    cache[dev].smem_per_sm = prop.sharedMemPerMultiprocessor;
   }
   *out = cache[dev];
   return CUTB_OK;

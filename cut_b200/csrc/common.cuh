@@ -41,6 +41,7 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0, cc_minor = 0;
   size_t smem_optin = 0;
+  size_t smem_per_sm = 0;
 };
 int get_device_info(DeviceInfo *out);
 

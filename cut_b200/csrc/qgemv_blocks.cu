@@ -57,10 +57,10 @@ constexpr int GV_KC = GV_WARPS;                   // granules (256 weights) per 
 // Shared-memory row stride of a stage (bytes): GV_KC granules plus the padding
 // that keeps the 8 row groups of a warp on disjoint banks for the access
 // pattern of the format (4 consecutive words per row for Q8_0 / Q4_0, 8 for Q4_K).
-__host__ __device__ constexpr int gv_row_stride(int fmt) {
-  return fmt == CUTB_Q8_0 ? 16 * 272 + 16    // 1092 words = 4 (mod 32)
-         : fmt == CUTB_Q4_0 ? 16 * 144 + 16  // 580 words = 4 (mod 32)
-                            : 16 * 144 + 32; // 584 words = 8 (mod 32)
+__host__ __device__ constexpr int gv_row_stride(int fmt, bool diag) {
+  return fmt == CUTB_Q8_0 ? 16 * 272 + 16               // 1092 words = 4 (mod 32)
+         : (fmt == CUTB_Q4_0 || diag) ? 16 * 144 + 16   // 580 words = 4 (mod 32); Q4_K diagonal: 16-byte loads
+                                      : 16 * 144 + 32;  // 584 words = 8 (mod 32); Q4_K: 8-byte loads
 }
 
 struct GvParams {
@@ -82,34 +82,51 @@ struct GvParams {
   int *status;
 };
 
+// Shared-memory loads by 32-bit shared address.  Plain loads through an
+// address-space-qualified pointer rather than inline asm, so the compiler can
+// schedule them freely between the (memory-clobbering) barrier waits.
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
+  return *reinterpret_cast<const uint32_t *>(__cvta_shared_to_generic(addr));
 }
 __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
+  return *reinterpret_cast<const uint2 *>(__cvta_shared_to_generic(addr));
 }
 __device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
+  return *reinterpret_cast<const uint4 *>(__cvta_shared_to_generic(addr));
 }
 
-// int8 MMA, D = A * B with a zero accumulator (passed as four zero registers).
-__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+// int8 MMA, D = A * B with a zero accumulator.  UA: the A operand holds unsigned bytes.
+template <bool UA>
+__device__ __forceinline__ void mma_i8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+  if constexpr (UA)
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+  else
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// int8 MMA accumulating into d.
+template <bool UA>
+__device__ __forceinline__ void mma_i8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                           uint32_t b1) {
+  if constexpr (UA)
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Low / high nibbles of four bytes -> four int8 values 16 * (q - 8).
-__device__ __forceinline__ uint32_t nib_lo_s(uint32_t x) { return ((x << 4) & 0xF0F0F0F0u) ^ 0x80808080u; }
-__device__ __forceinline__ uint32_t nib_hi_s(uint32_t x) { return (x & 0xF0F0F0F0u) ^ 0x80808080u; }
+// Low / high nibbles of four bytes -> four unsigned bytes 16 * q.  The Q4_0
+// offset (q - 8) is applied after the MMA through the staged sum of the
+// activations of the block: sum((q - 8) x) = sum(q x) - 8 sum(x).
+__device__ __forceinline__ uint32_t nib_lo_s(uint32_t x) { return (x << 4) & 0xF0F0F0F0u; }
+__device__ __forceinline__ uint32_t nib_hi_s(uint32_t x) { return x & 0xF0F0F0F0u; }
 
 // Element (0..31) of a 32-weight block that sits in byte i (0..7) of lane t's
 // MMA fragment pair {b0, b1}; the weight side reads its bytes in the same
@@ -134,6 +151,177 @@ template <int FMT> __device__ __forceinline__ uint32_t frag_elem(bool even, uint
   }
 }
 
+// "Diagonal" variant used for one or two activation rows.  Lane t of a quad owns
+// whole blocks (2t and 2t+1 of each 8-block granule) instead of a quarter of
+// every block; its activation column pair is non-zero only in its own k slots,
+// so MMA column pair t ends up holding the dot product of the lane's own block:
+// the block scale is then applied once per block by the lane that loaded it.
+// Element of a 32-weight block in byte b (0..7) of the fragment of MMA i (0..3).
+template <int FMT> __device__ __forceinline__ uint32_t diag_elem(bool even, uint32_t i, uint32_t b) {
+  const uint32_t j = b & 3;
+  if constexpr (FMT == CUTB_Q4_K) {
+    return 8 * i + b;
+  } else if constexpr (FMT == CUTB_Q4_0) {
+    uint32_t byte;
+    if (!even) byte = 4 * i + j;
+    else if (i < 3) byte = 2 + 4 * i + j;
+    else byte = (j < 2) ? j : 12 + j;  // {0, 1, 14, 15}
+    return byte + ((b >> 2) << 4);
+  } else {
+    const uint32_t w = 2 * i + (b >> 2);
+    if (!even) return 4 * w + j;
+    if (w < 7) return 2 + 4 * w + j;
+    return (j < 2) ? j : 28 + j;  // {0, 1, 30, 31}
+  }
+}
+
+// The four MMAs of one block in two independent accumulation chains.  r0* / r1*:
+// first and second A register of MMA i for rows g (a) and g + 8 (b); act: shared
+// address of the lane's 32 staged activation bytes of the block.
+template <bool UA>
+__device__ __forceinline__ void block_mmas(int (&c)[4], int (&c2)[4], const uint32_t (&r0a)[4], const uint32_t (&r0b)[4],
+                                           const uint32_t (&r1a)[4], const uint32_t (&r1b)[4], uint32_t act) {
+  const uint4 x0 = lds_u128(act), x1 = lds_u128(act + 16);
+  mma_i8<UA>(c, r0a[0], r0b[0], r1a[0], r1b[0], x0.x, x0.y);
+  mma_i8<UA>(c2, r0a[1], r0b[1], r1a[1], r1b[1], x0.z, x0.w);
+  mma_i8_acc<UA>(c, r0a[2], r0b[2], r1a[2], r1b[2], x1.x, x1.y);
+  mma_i8_acc<UA>(c2, r0a[3], r0b[3], r1a[3], r1b[3], x1.z, x1.w);
+}
+
+// One granule (8 blocks of 32 weights, or one Q4_K super-block) x 16 rows for
+// the diagonal variant.  `rowA`: shared address of row g's granule; actp/escp/sxp:
+// per-lane shared addresses of the lane's even block (see the kernel), pass_a /
+// pass_e: byte distance to its odd block (0 for lanes whose columns are idle).
+template <int FMT, int NVR, int RS>
+__device__ __forceinline__ void compute_granule_diag(uint32_t rowA, const uint32_t (&actp)[NVR], uint32_t pass_a,
+                                                     const uint32_t (&escp)[NVR], const uint32_t (&sxp)[NVR],
+                                                     uint32_t pass_e, uint32_t t, float (&tot)[NVR][2]) {
+  const uint32_t rowB = rowA + 8 * RS;
+  // c / c2: two independent accumulation chains of the block's four MMAs
+  auto finish = [&](int nt, const int (&c)[4], const int (&c2)[4], float sA, float sB, uint32_t eoff) {
+    const float e = __uint_as_float(lds_u32(escp[nt] + eoff));
+    const float fg = (float)((c[0] + c2[0]) * 256 + (c[1] + c2[1])), fh = (float)((c[2] + c2[2]) * 256 + (c[3] + c2[3]));
+    if constexpr (FMT == CUTB_Q4_0) {
+      // d * (e/16 * sum(16 q x^) - 8 e sum(x^)) = d e sum((q - 8) x^)
+      const float off = __uint_as_float(lds_u32(sxp[nt] + eoff));
+      tot[nt][0] = fmaf(sA, fmaf(e, fg, -off), tot[nt][0]);
+      tot[nt][1] = fmaf(sB, fmaf(e, fh, -off), tot[nt][1]);
+    } else {
+      tot[nt][0] = fmaf(sA * e, fg, tot[nt][0]);
+      tot[nt][1] = fmaf(sB * e, fh, tot[nt][1]);
+    }
+  };
+  if constexpr (FMT == CUTB_Q4_0) {
+    const uint32_t pa = rowA + 36 * t, pb = rowB + 36 * t;
+    uint32_t la[9], lb[9];
+#pragma unroll
+    for (int k = 0; k < 9; ++k) {
+      la[k] = lds_u32(pa + 4 * k);
+      lb[k] = lds_u32(pb + 4 * k);
+    }
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      uint32_t wa[4], wb[4];
+      float dA, dB;
+      if (pass == 0) {
+        wa[0] = la[1]; wa[1] = la[2]; wa[2] = la[3]; wa[3] = __byte_perm(la[0], la[4], 0x5432);
+        wb[0] = lb[1]; wb[1] = lb[2]; wb[2] = lb[3]; wb[3] = __byte_perm(lb[0], lb[4], 0x5432);
+        dA = h2f_bits(la[0] & 0xFFFFu); dB = h2f_bits(lb[0] & 0xFFFFu);
+      } else {
+        wa[0] = la[5]; wa[1] = la[6]; wa[2] = la[7]; wa[3] = la[8];
+        wb[0] = lb[5]; wb[1] = lb[6]; wb[2] = lb[7]; wb[3] = lb[8];
+        dA = h2f_bits(la[4] >> 16); dB = h2f_bits(lb[4] >> 16);
+      }
+      uint32_t al[4], ah[4], bl[4], bh[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        al[i] = nib_lo_s(wa[i]); ah[i] = nib_hi_s(wa[i]);
+        bl[i] = nib_lo_s(wb[i]); bh[i] = nib_hi_s(wb[i]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < NVR; ++nt) {
+        int c[4], c2[4];
+        block_mmas<true>(c, c2, al, bl, ah, bh, actp[nt] + pass * pass_a);
+        finish(nt, c, c2, dA, dB, pass * pass_e);
+      }
+    }
+  } else if constexpr (FMT == CUTB_Q8_0) {
+    const uint32_t pa = rowA + 68 * t, pb = rowB + 68 * t;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      uint32_t wa[8], wb[8];
+      float dA, dB;
+      if (pass == 0) {
+        const uint32_t a0 = lds_u32(pa), b0 = lds_u32(pb), a8 = lds_u32(pa + 32), b8 = lds_u32(pb + 32);
+#pragma unroll
+        for (int k = 0; k < 7; ++k) {
+          wa[k] = lds_u32(pa + 4 + 4 * k);
+          wb[k] = lds_u32(pb + 4 + 4 * k);
+        }
+        wa[7] = __byte_perm(a0, a8, 0x5432);
+        wb[7] = __byte_perm(b0, b8, 0x5432);
+        dA = h2f_bits(a0 & 0xFFFFu); dB = h2f_bits(b0 & 0xFFFFu);
+      } else {
+        dA = h2f_bits(lds_u32(pa + 32) >> 16); dB = h2f_bits(lds_u32(pb + 32) >> 16);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          wa[k] = lds_u32(pa + 36 + 4 * k);
+          wb[k] = lds_u32(pb + 36 + 4 * k);
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < NVR; ++nt) {
+        const uint32_t r0a[4] = {wa[0], wa[2], wa[4], wa[6]}, r1a[4] = {wa[1], wa[3], wa[5], wa[7]};
+        const uint32_t r0b[4] = {wb[0], wb[2], wb[4], wb[6]}, r1b[4] = {wb[1], wb[3], wb[5], wb[7]};
+        int c[4], c2[4];
+        block_mmas<false>(c, c2, r0a, r0b, r1a, r1b, actp[nt] + pass * pass_a);
+        finish(nt, c, c2, dA, dB, pass * pass_e);
+      }
+    }
+  } else {  // Q4_K: lane t owns the 64-weight group t = sub-blocks 2t (low nibbles) and 2t+1 (high nibbles)
+    const uint4 hA = lds_u128(rowA), hB = lds_u128(rowB);
+    const uint4 qa0 = lds_u128(rowA + 16 + 32 * t), qa1 = lds_u128(rowA + 32 + 32 * t);
+    const uint4 qb0 = lds_u128(rowB + 16 + 32 * t), qb1 = lds_u128(rowB + 32 + 32 * t);
+    const uint32_t wa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+    const uint32_t wb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+    const float dA = h2f_bits(hA.x & 0xFFFFu), mA = h2f_bits(hA.x >> 16);
+    const float dB = h2f_bits(hB.x & 0xFFFFu), mB = h2f_bits(hB.x >> 16);
+    // 6-bit (scale, min) fields of this lane's two sub-blocks (gguf_reader.cpp:668-676)
+    const bool upper = t >= 2;  // sub-blocks 4..7 keep their high bits elsewhere
+    const uint32_t scA = upper ? (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u) : hA.y & 0x3F3F3F3Fu;
+    const uint32_t mnA = upper ? ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u) : hA.z & 0x3F3F3F3Fu;
+    const uint32_t scB = upper ? (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u) : hB.y & 0x3F3F3F3Fu;
+    const uint32_t mnB = upper ? ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u) : hB.z & 0x3F3F3F3Fu;
+    const float ndA = -dA * 8388608.f, nmA = -mA * 8388608.f, ndB = -dB * 8388608.f, nmB = -mB * 8388608.f;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const uint32_t sel = 0x7540u | (((2 * t) & 3) + pass);
+      // d * (2^23 + sc) - d * 2^23 == d * sc exactly
+      const float dsA = fmaf(dA, __uint_as_float(__byte_perm(scA, 0x4B000000u, sel)), ndA);
+      const float dmA = fmaf(mA, __uint_as_float(__byte_perm(mnA, 0x4B000000u, sel)), nmA);
+      const float dsB = fmaf(dB, __uint_as_float(__byte_perm(scB, 0x4B000000u, sel)), ndB);
+      const float dmB = fmaf(mB, __uint_as_float(__byte_perm(mnB, 0x4B000000u, sel)), nmB);
+      uint32_t fa[8], fb[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        fa[k] = (pass ? (wa[k] >> 4) : wa[k]) & 0x0F0F0F0Fu;
+        fb[k] = (pass ? (wb[k] >> 4) : wb[k]) & 0x0F0F0F0Fu;
+      }
+#pragma unroll
+      for (int nt = 0; nt < NVR; ++nt) {
+        const uint32_t r0a[4] = {fa[0], fa[2], fa[4], fa[6]}, r1a[4] = {fa[1], fa[3], fa[5], fa[7]};
+        const uint32_t r0b[4] = {fb[0], fb[2], fb[4], fb[6]}, r1b[4] = {fb[1], fb[3], fb[5], fb[7]};
+        int c[4], c2[4];
+        block_mmas<true>(c, c2, r0a, r0b, r1a, r1b, actp[nt] + pass * pass_a);
+        finish(nt, c, c2, dsA, dsB, pass * pass_e);
+        const float sxv = __uint_as_float(lds_u32(sxp[nt] + pass * pass_e));
+        tot[nt][0] = fmaf(-dmA, sxv, tot[nt][0]);
+        tot[nt][1] = fmaf(-dmB, sxv, tot[nt][1]);
+      }
+    }
+  }
+}
+
 // One stage of one warp: 16 rows x ngr granules of raw blocks at shared
 // address `st`.  `actb` / `escb` / `sxb` point at the staged activations,
 // scales and (Q4_K) scaled sums of the first 32-k block of the stage.
@@ -151,10 +339,16 @@ __device__ __forceinline__ void compute_stage(uint32_t st, uint32_t ngr, uint32_
       const uint2 x = lds_u64(actb + kb * act_stride + aoff[nt]);
       const float e = __uint_as_float(lds_u32(escb + (kb * NV + nt * 4 + t) * 4));
       int c[4];
-      mma_s8(c, fa[0], fb[0], fa[1], fb[1], x.x, x.y);
+      mma_i8<FMT == CUTB_Q4_0>(c, fa[0], fb[0], fa[1], fb[1], x.x, x.y);
       const float fg = (float)(c[0] * 256 + c[1]), fh = (float)(c[2] * 256 + c[3]);
-      tot[nt][0] = fmaf(dA * e, fg, tot[nt][0]);
-      tot[nt][1] = fmaf(dB * e, fh, tot[nt][1]);
+      if constexpr (FMT == CUTB_Q4_0) {
+        const float off = __uint_as_float(lds_u32(sxb + (kb * NV + nt * 4 + t) * 4));
+        tot[nt][0] = fmaf(dA, fmaf(e, fg, -off), tot[nt][0]);
+        tot[nt][1] = fmaf(dB, fmaf(e, fh, -off), tot[nt][1]);
+      } else {
+        tot[nt][0] = fmaf(dA * e, fg, tot[nt][0]);
+        tot[nt][1] = fmaf(dB * e, fh, tot[nt][1]);
+      }
     }
   };
 
@@ -233,7 +427,7 @@ __device__ __forceinline__ void compute_stage(uint32_t st, uint32_t ngr, uint32_
             const uint32_t vi = (kb * NV + nt * 4 + t) * 4;
             const float e = __uint_as_float(lds_u32(escb + vi)), sx = __uint_as_float(lds_u32(sxb + vi));
             int c[4];
-            mma_s8(c, a0, a1, a2, a3, x.x, x.y);
+            mma_i8<true>(c, a0, a1, a2, a3, x.x, x.y);
             const float fg = (float)(c[0] * 256 + c[1]), fh = (float)(c[2] * 256 + c[3]);
             tot[nt][0] = fmaf(dsA * e, fg, tot[nt][0]);
             tot[nt][1] = fmaf(dsB * e, fh, tot[nt][1]);
@@ -263,15 +457,19 @@ constexpr float GV_QMAX = 32512.f;
 // as two-digit block floating point in MMA fragment order.
 //   act  : [blk][col][lane t][8 bytes]; col = 2 * vrow + digit (0 = high digit)
 //   esc  : [blk][NV] fp32 scale of the integer dot product (includes the 1/16 of the Q4_0 nibble encoding)
-//   sx   : [blk][NV] fp32 e * sum(x^) (Q4_K only)
-template <int FMT, bool AF32, int NT, int THREADS>
+//   sx   : [blk][NV] fp32 e * sum(x^) (Q4_K), 8 e * sum(x^) (Q4_0: the q - 8 offset)
+//
+// Diagonal variant (DIAG): act is [blk][vrow][digit][MMA i][8 bytes] followed by
+// 32 zero bytes, esc / sx are [blk][NT] (NT = number of virtual rows).
+template <int FMT, bool AF32, int NT, bool DIAG, int THREADS>
 __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *act, float *esc, float *sx, uint32_t k0,
                                                   uint32_t nblk, uint32_t ncp, uint32_t tid) {
-  constexpr uint32_t NV = NT * 4;
+  constexpr uint32_t NV = DIAG ? NT : NT * 4;
   const uint32_t nrows = p.M;
   const uint32_t nvr = AF32 ? 2 * nrows : nrows;
   const uint32_t nchunks = nblk * nrows * 4;
-  const float wscale = (FMT == CUTB_Q4_0) ? 0.0625f : 1.0f;
+  const float wscale = (FMT == CUTB_Q4_0) ? 0.0625f : 1.0f;  // Q4_0 nibbles enter the MMA as 16 q
+  const float sxscale = (FMT == CUTB_Q4_0) ? 8.0f : 1.0f;    // Q4_0: the -8 offset of every weight
   for (uint32_t base = 0; base < nchunks; base += THREADS) {  // uniform trip count: shuffles inside
     const uint32_t id = base + tid;
     const bool live = id < nchunks;
@@ -283,7 +481,7 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     const uint64_t rowbase = (uint64_t)m * p.lda + k0 + kb * 32;
 #pragma unroll
     for (uint32_t i = 0; i < 8; ++i) {
-      x[i] = live ? load_act<AF32>(p.A, rowbase + frag_elem<FMT>(even, ct, i)) : 0.f;
+      x[i] = live ? load_act<AF32>(p.A, rowbase + (DIAG ? diag_elem<FMT>(even, ct, i) : frag_elem<FMT>(even, ct, i))) : 0.f;
       amax = fmaxf(amax, fabsf(x[i]));
     }
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -307,16 +505,21 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
       wlo[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
     }
     const uint32_t vr = AF32 ? 2 * m : m;
-    if constexpr (FMT == CUTB_Q4_K) {
+    if constexpr (FMT != CUTB_Q8_0) {
       isum += __shfl_xor_sync(0xffffffffu, isum, 1);
       isum += __shfl_xor_sync(0xffffffffu, isum, 2);
     }
+    // byte offset of (block, virtual row, digit, chunk) in the staged layout
+    auto act_off = [&](uint32_t vrow, uint32_t digit) -> size_t {
+      if constexpr (DIAG) return (((size_t)kb * NT + vrow) * 2 + digit) * 32 + ct * 8;
+      return ((size_t)(kb * ncp + 2 * vrow + digit) * 4 + ct) * 8;
+    };
     if (live) {
-      *reinterpret_cast<uint2 *>(act + ((size_t)(kb * ncp + 2 * vr) * 4 + ct) * 8) = make_uint2(whi[0], whi[1]);
-      *reinterpret_cast<uint2 *>(act + ((size_t)(kb * ncp + 2 * vr + 1) * 4 + ct) * 8) = make_uint2(wlo[0], wlo[1]);
+      *reinterpret_cast<uint2 *>(act + act_off(vr, 0)) = make_uint2(whi[0], whi[1]);
+      *reinterpret_cast<uint2 *>(act + act_off(vr, 1)) = make_uint2(wlo[0], wlo[1]);
       if (ct == 0) {
         esc[kb * NV + vr] = e * wscale;
-        if constexpr (FMT == CUTB_Q4_K) sx[kb * NV + vr] = e * (float)isum;
+        if constexpr (FMT != CUTB_Q8_0) sx[kb * NV + vr] = sxscale * e * (float)isum;
       }
     }
     if constexpr (AF32) {
@@ -334,19 +537,24 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
         rhi[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
         rlo[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
       }
-      if constexpr (FMT == CUTB_Q4_K) {
+      if constexpr (FMT != CUTB_Q8_0) {
         isum2 += __shfl_xor_sync(0xffffffffu, isum2, 1);
         isum2 += __shfl_xor_sync(0xffffffffu, isum2, 2);
       }
       if (live) {
-        *reinterpret_cast<uint2 *>(act + ((size_t)(kb * ncp + 2 * vr + 2) * 4 + ct) * 8) = make_uint2(rhi[0], rhi[1]);
-        *reinterpret_cast<uint2 *>(act + ((size_t)(kb * ncp + 2 * vr + 3) * 4 + ct) * 8) = make_uint2(rlo[0], rlo[1]);
+        *reinterpret_cast<uint2 *>(act + act_off(vr + 1, 0)) = make_uint2(rhi[0], rhi[1]);
+        *reinterpret_cast<uint2 *>(act + act_off(vr + 1, 1)) = make_uint2(rlo[0], rlo[1]);
         if (ct == 0) {
           esc[kb * NV + vr + 1] = e2 * wscale;
-          if constexpr (FMT == CUTB_Q4_K) sx[kb * NV + vr + 1] = e2 * (float)isum2;
+          if constexpr (FMT != CUTB_Q8_0) sx[kb * NV + vr + 1] = sxscale * e2 * (float)isum2;
         }
       }
     }
+  }
+  if constexpr (DIAG) {
+    // lanes whose MMA columns belong to another lane's block read these zeros
+    if (tid < 8) reinterpret_cast<uint32_t *>(act + (size_t)p.gran_per_split * 8 * NT * 64)[tid] = 0u;
+    return;
   }
   // idle MMA columns read an all-zero column; idle virtual rows get scale 0
   const uint32_t ncols = 2 * nvr;
@@ -358,16 +566,16 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     for (uint32_t id = tid; id < nblk * spare; id += THREADS) {
       const uint32_t o = (id / spare) * NV + nvr + id % spare;
       esc[o] = 0.f;
-      if constexpr (FMT == CUTB_Q4_K) sx[o] = 0.f;
+      if constexpr (FMT != CUTB_Q8_0) sx[o] = 0.f;
     }
 }
 
-template <int FMT, bool AF32, int NT>
-__global__ void __launch_bounds__(GV_THREADS, 1) qgemv_blocks_kernel(const GvParams p) {
-  constexpr int RS = gv_row_stride(FMT);
+template <int FMT, bool AF32, int NT, bool DIAG>
+__global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvParams p) {
+  constexpr int RS = gv_row_stride(FMT, DIAG);
   constexpr uint32_t GB = granule_bytes(FMT);
   constexpr uint32_t STAGE_BYTES = GV_ROWS * RS;
-  constexpr uint32_t NV = NT * 4, NC8 = NT * 8;
+  constexpr uint32_t NV = DIAG ? NT : NT * 4, NC8 = NT * 8;
   extern __shared__ __align__(128) uint8_t smem[];
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -379,9 +587,9 @@ __global__ void __launch_bounds__(GV_THREADS, 1) qgemv_blocks_kernel(const GvPar
 
   uint8_t *ring = smem;
   uint8_t *act = ring + (size_t)S * STAGE_BYTES;
-  float *esc = reinterpret_cast<float *>(act + (size_t)nblk_alloc * ncp * 32);
+  float *esc = reinterpret_cast<float *>(act + (DIAG ? (size_t)nblk_alloc * NT * 64 + 32 : (size_t)nblk_alloc * ncp * 32));
   float *sx = esc + nblk_alloc * NV;
-  float *red = sx + (FMT == CUTB_Q4_K ? nblk_alloc * NV : 0);  // two buffers of [GV_WARPS][16][NV]
+  float *red = sx + (FMT != CUTB_Q8_0 ? nblk_alloc * NV : 0);  // two buffers of [GV_WARPS][16][NV]
   uint64_t *bars = reinterpret_cast<uint64_t *>(red + 2 * GV_WARPS * GV_ROWS * NV);  // full[S], empty[S]
 
   // rows of this CTA and granules (256 weights) of this K split; a stage holds
@@ -398,6 +606,10 @@ __global__ void __launch_bounds__(GV_THREADS, 1) qgemv_blocks_kernel(const GvPar
 
   const uint32_t ring_u = smem_u32(ring);
   const uint32_t full_u = smem_u32(bars), empty_u = full_u + S * 8;
+
+  // Let the next kernel of the stream start its own prologue and weight
+  // prefetch as soon as an SM has room for it (programmatic dependent launch).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (tid == 0) {
     for (uint32_t s = 0; s < S; ++s) {
@@ -439,17 +651,28 @@ __global__ void __launch_bounds__(GV_THREADS, 1) qgemv_blocks_kernel(const GvPar
   }
 
   // ---- consumer warps ---------------------------------------------------------
-  stage_activations<FMT, AF32, NT, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid);
+  // Everything above only read the (constant) weights.  The activations, D and
+  // C may belong to the previous kernel of the stream: wait for it to finish.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  stage_activations<FMT, AF32, NT, DIAG, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid);
   asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
 
-  // per-lane activation fragment offsets (idle lanes read the zero column)
+  const uint32_t act_u = smem_u32(act), act_stride = ncp * 32, esc_u = smem_u32(esc), sx_u = smem_u32(sx);
+  // per-lane activation fragment offsets (idle lanes read zeros)
   uint32_t aoff[NT];
+  // diagonal variant: MMA column g belongs to the block pair of lane g >> 1, digit g & 1
+  const bool mine = (t == (g >> 1));
+  const uint32_t zero_u = act_u + nblk_alloc * NT * 64;
+  const uint32_t pass_a = mine ? NT * 64u : 0u, gran_a = mine ? 8u * NT * 64u : 0u;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
-    const uint32_t col = nt * 8 + g;
-    aoff[nt] = ((col < ncols ? col : ncols) * 4 + t) * 8;
+    if constexpr (DIAG) {
+      aoff[nt] = mine ? (((2 * t) * NT + nt) * 2 + (g & 1)) * 32 : 0u;
+    } else {
+      const uint32_t col = nt * 8 + g;
+      aoff[nt] = ((col < ncols ? col : ncols) * 4 + t) * 8;
+    }
   }
-  const uint32_t act_u = smem_u32(act), act_stride = ncp * 32, esc_u = smem_u32(esc), sx_u = smem_u32(sx);
 
   bool dead = false;
   for (uint32_t tile = 0; tile < ntiles; ++tile) {
@@ -469,8 +692,20 @@ __global__ void __launch_bounds__(GV_THREADS, 1) qgemv_blocks_kernel(const GvPar
       const uint32_t gq = gs0 + c * GV_KC + warp;  // this warp's granule of the chunk
       if (!dead && gq < gs1) {
         const uint32_t kb0 = (gq - gs0) * 8;  // first 32-weight block of the granule inside the split
-        compute_stage<FMT, NT, RS>(ring_u + slot * STAGE_BYTES + warp * GB, 1, act_u + kb0 * act_stride, act_stride, aoff,
-                                   esc_u + kb0 * NV * 4, sx_u + kb0 * NV * 4, g, t, tot);
+        if constexpr (DIAG) {
+          uint32_t actp[NT], escp[NT], sxp[NT];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            actp[nt] = mine ? act_u + (gq - gs0) * gran_a + aoff[nt] : zero_u;
+            escp[nt] = esc_u + ((kb0 + 2 * t) * NT + nt) * 4;
+            sxp[nt] = sx_u + ((kb0 + 2 * t) * NT + nt) * 4;
+          }
+          compute_granule_diag<FMT, NT, RS>(ring_u + slot * STAGE_BYTES + warp * GB + g * RS, actp, pass_a, escp, sxp,
+                                            NT * 4, t, tot);
+        } else {
+          compute_stage<FMT, NT, RS>(ring_u + slot * STAGE_BYTES + warp * GB, 1, act_u + kb0 * act_stride, act_stride,
+                                     aoff, esc_u + kb0 * NV * 4, sx_u + kb0 * NV * 4, g, t, tot);
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_u + slot * 8);
@@ -480,9 +715,23 @@ __global__ void __launch_bounds__(GV_THREADS, 1) qgemv_blocks_kernel(const GvPar
     float *rbuf = red + (size_t)(tile & 1) * GV_WARPS * GV_ROWS * NV;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      float *r = rbuf + ((size_t)warp * GV_ROWS) * NV + nt * 4 + t;
-      r[g * NV] = tot[nt][0];
-      r[(g + 8) * NV] = tot[nt][1];
+      if constexpr (DIAG) {
+        // the four lanes of a quad hold partial sums of the same virtual row
+        float a = tot[nt][0], b = tot[nt][1];
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
+        b += __shfl_xor_sync(0xffffffffu, b, 1);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        b += __shfl_xor_sync(0xffffffffu, b, 2);
+        if (t == 0) {
+          float *r = rbuf + ((size_t)warp * GV_ROWS) * NV + nt;
+          r[g * NV] = a;
+          r[(g + 8) * NV] = b;
+        }
+      } else {
+        float *r = rbuf + ((size_t)warp * GV_ROWS) * NV + nt * 4 + t;
+        r[g * NV] = tot[nt][0];
+        r[(g + 8) * NV] = tot[nt][1];
+      }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
     const uint32_t row_base = r0 + tile * GV_ROWS;
@@ -527,15 +776,17 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *_
 
 struct GvPlan {
   uint32_t nt, nvr, ncp, grid_x, ksplit, gran_per_split, stages;
+  bool diag, overlap;
   size_t smem;
 };
 
-size_t gv_smem_bytes(int fmt, uint32_t stages, uint32_t nt, uint32_t ncp, uint32_t gran_per_split) {
+size_t gv_smem_bytes(int fmt, bool diag, uint32_t stages, uint32_t nt, uint32_t ncp, uint32_t gran_per_split) {
   const size_t nblk = (size_t)gran_per_split * 8;
-  size_t b = (size_t)stages * GV_ROWS * gv_row_stride(fmt);
-  b += nblk * ncp * 32;
-  b += nblk * nt * 4 * 4 * (fmt == CUTB_Q4_K ? 2 : 1);
-  b += (size_t)2 * GV_WARPS * GV_ROWS * nt * 4 * 4;
+  const size_t nv = diag ? nt : nt * 4;
+  size_t b = (size_t)stages * GV_ROWS * gv_row_stride(fmt, diag);
+  b += diag ? nblk * nt * 64 + 32 : nblk * ncp * 32;
+  b += nblk * nv * 4 * (fmt != CUTB_Q8_0 ? 2 : 1);
+  b += (size_t)2 * GV_WARPS * GV_ROWS * nv * 4;
   b += 2 * stages * 8;
   return b;
 }
@@ -544,7 +795,9 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
   const bool af32 = d.a_dtype == CUTB_F32;
   pl->nvr = af32 ? 2 * d.M : d.M;
   if (pl->nvr == 0 || pl->nvr > 16) return false;
-  pl->nt = pl->nvr <= 4 ? 1 : (pl->nvr <= 8 ? 2 : 4);
+  // one or two virtual rows: the diagonal variant (nt = virtual rows); otherwise 4 virtual rows per MMA n-tile
+  pl->diag = pl->nvr <= 2;
+  pl->nt = pl->diag ? pl->nvr : (pl->nvr <= 4 ? 1 : (pl->nvr <= 8 ? 2 : 4));
   const uint32_t ncols = 2 * pl->nvr;
   pl->ncp = ncols < pl->nt * 8 ? ncols + 1 : ncols;
   const uint32_t G = d.K / 256;
@@ -554,11 +807,16 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
   if (pl->grid_x * 2 <= (uint32_t)di.sm_count) want = (uint32_t)di.sm_count / pl->grid_x;
   if (want > G) want = G;
   const size_t limit = di.smem_optin;
-  // deepest ring that fits; split K further only when two stages do not fit
+  // Two CTAs per SM (this launch's and the next one's, which prefetches while
+  // this one computes) need <= half of the SM's shared memory each; when that
+  // cannot hold two stages, take the deepest ring that fits one CTA per SM.
+  // K is split further only when even two stages do not fit.
+  const size_t half = (di.smem_per_sm > 2048 ? di.smem_per_sm / 2 - 1024 : limit / 2);
   for (uint32_t ks = want; ks <= G; ++ks) {
     const uint32_t gps = (G + ks - 1) / ks;
-    for (uint32_t st = 4; st >= 2; --st) {
-      const size_t sm = gv_smem_bytes(d.format, st, pl->nt, pl->ncp, gps);
+    const bool pair = gv_smem_bytes(d.format, pl->diag, 2, pl->nt, pl->ncp, gps) <= half;
+    for (uint32_t st = pair ? 2 : 4; st >= 2; --st) {
+      const size_t sm = gv_smem_bytes(d.format, pl->diag, st, pl->nt, pl->ncp, gps);
       if (sm <= limit) {
         pl->gran_per_split = gps;
         pl->ksplit = (G + gps - 1) / gps;
@@ -571,7 +829,7 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
   return false;
 }
 
-template <int FMT, bool AF32, int NT>
+template <int FMT, bool AF32, int NT, bool DIAG>
 int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   static int configured_device = -1;
   int dev = 0;
@@ -579,21 +837,31 @@ int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   if (configured_device != dev) {
     DeviceInfo di;
     if (int rc = get_device_info(&di)) return rc;
-    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AF32, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AF32, NT, DIAG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)di.smem_optin));
     configured_device = dev;
   }
-  qgemv_blocks_kernel<FMT, AF32, NT><<<dim3(pl.grid_x, pl.ksplit), GV_THREADS, pl.smem, stream>>>(p);
-  CUTB_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.grid_x, pl.ksplit);
+  cfg.blockDim = dim3(GV_THREADS);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pl.overlap ? 1 : 0;
+  CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, qgemv_blocks_kernel<FMT, AF32, NT, DIAG>, p));
   return CUTB_OK;
 }
 
 template <int FMT, bool AF32>
 int gv_launch_nt(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
+  if (pl.diag) return pl.nt == 1 ? gv_launch_inst<FMT, AF32, 1, true>(p, pl, stream) : gv_launch_inst<FMT, AF32, 2, true>(p, pl, stream);
   switch (pl.nt) {
-    case 1: return gv_launch_inst<FMT, AF32, 1>(p, pl, stream);
-    case 2: return gv_launch_inst<FMT, AF32, 2>(p, pl, stream);
-    default: return gv_launch_inst<FMT, AF32, 4>(p, pl, stream);
+    case 1: return gv_launch_inst<FMT, AF32, 1, false>(p, pl, stream);
+    case 2: return gv_launch_inst<FMT, AF32, 2, false>(p, pl, stream);
+    default: return gv_launch_inst<FMT, AF32, 4, false>(p, pl, stream);
   }
 }
 
@@ -634,6 +902,7 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
     return CUTB_ERR_UNSUPPORTED;
   }
   const bool af32 = d.a_dtype == CUTB_F32;
+  pl.overlap = !(d.flags & CUTB_FLAG_NO_OVERLAP);
   GvParams p;
   p.W = reinterpret_cast<const uint8_t *>(d.W);
   p.row_bytes = row_bytes(d.format, d.K);

@@ -25,7 +25,7 @@ def _pad4(n: int) -> int:
 def make_desc(A: torch.Tensor, W: torch.Tensor, fmt: int, N: int, *, layout=L.LAYOUT_GGUF_BLOCKS, scales=None,
               affine=False, ldb=0, lds=0, C_out: torch.Tensor | None = None, D: torch.Tensor | None = None,
               fusion_type=L.FUSION_NONE, fusion_op=0, variant=L.VARIANT_AUTO, workspace: torch.Tensor | None = None,
-              status: torch.Tensor | None = None):
+              status: torch.Tensor | None = None, flags: int = 0):
     """Builds a cutb_qmatmul_desc over torch CUDA tensors; returns (desc, C, keepalive)."""
     if A.dim() == 1:
         A = A.unsqueeze(0)
@@ -52,6 +52,7 @@ def make_desc(A: torch.Tensor, W: torch.Tensor, fmt: int, N: int, *, layout=L.LA
     d.workspace, d.workspace_bytes = (workspace.data_ptr(), workspace.numel() * workspace.element_size()) \
         if workspace is not None else (None, 0)
     d.status = status.data_ptr() if status is not None else None
+    d.flags = flags
     return d, C_out, (A, W, scales, D, workspace, status)
 
 

@@ -74,6 +74,15 @@ enum {
   CUTB_VARIANT_GEMM_TC = 2  /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory */
 };
 
+/* Descriptor flags.
+ *   CUTB_FLAG_NO_OVERLAP: by default the decode mat-vec is launched with
+ *     programmatic stream serialization: its weight prefetch may begin while the
+ *     previous kernel of the stream is still finishing, and it waits for that
+ *     kernel to complete before it reads A or D or writes C.  This is only
+ *     correct if the previous kernel does not write W (weights are constants of
+ *     the model).  Set this flag to launch with plain stream ordering instead. */
+enum { CUTB_FLAG_NO_OVERLAP = 1 };
+
 /*
  * C[M, N] = epilogue(A[M, K] * dequant(W)), fp32 accumulate, fp32 output.
  * Replaces the quantized MatMulOpNode dispatch: bindings (A, packedB, scalesB,
@@ -104,6 +113,7 @@ typedef struct cutb_qmatmul_desc {
   void *workspace;     /* device scratch, >= cutb_qmatmul_workspace_bytes(desc), 256-byte aligned; may be NULL if that is 0 */
   uint64_t workspace_bytes;
   int32_t *status;     /* optional device int: kernels store CUTB_ERR_TIMEOUT here if a bounded wait gives up */
+  uint32_t flags;      /* CUTB_FLAG_* */
 } cutb_qmatmul_desc;
 
 /* Scratch bytes cutb_qmatmul needs for this descriptor (0 for most shapes;
