@@ -61,7 +61,33 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST_LIB = os.path.join(HERE, "libcut_host.so")
+HOST_SOURCES = ["cut_api.cpp", "b200_compute.cpp"]
+
+
+def _cuda_home() -> str:
+    return os.path.dirname(os.path.dirname(_nvcc()))
+
+
+def build_host(force: bool = False) -> str:
+    """Compile the C++ host API (csrc/host) into libcut_host.so on top of libcutb.so."""
+    build(force=force)
+    hdir = os.path.join(CSRC, "host")
+    srcs = [os.path.join(hdir, f) for f in HOST_SOURCES]
+    deps = srcs + [os.path.join(hdir, "cut_api.h"), os.path.join(CSRC, "..", "..", "include", "cutb.h"), LIB]
+    if force or _stale(HOST_LIB, deps):
+        cuda = _cuda_home()
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", HOST_LIB, *srcs, f"-I{cuda}/include",
+               f"-L{cuda}/lib64", f"-L{HERE}", "-lcutb", "-lcudart_static", "-ldl", "-lrt", "-lpthread",
+               "-Wl,-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"host build failed:\n{r.stdout}{r.stderr}")
+    return HOST_LIB
+
+
 if __name__ == "__main__":
     import sys
 
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_host(force="--force" in sys.argv))

@@ -1,0 +1,390 @@
+// B200Compute: the ComputeInterface backend that stands where the reference's
+// core/backends/cuda/CudaCompute stands (CudaCompute.cpp:56-330,
+// CudaCommandBuffer.cpp:128-360), rebuilt for precompiled sm_100a kernels:
+//   * createShaderModule() decodes a kernel descriptor and binds it to a C ABI
+//     entry point -- no SPIR-V hashing, no NVRTC;
+//   * buffers are plain cudaMalloc allocations that honour the reference's
+//     padding rule (inner dimension to 4 elements, size to 16 bytes) and are
+//     zero-filled so padding never holds garbage;
+//   * a command buffer is the recorded dispatch list; submit() launches it on the
+//     backend's stream, submitReusable() captures it into a CUDA graph that
+//     resubmit() replays with one launch;
+//   * a dispatch whose descriptor no kernel covers throws (the reference logs and
+//     skips it).
+// Errors surface as std::runtime_error, like the reference's logErr.
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "../../../include/cutb.h"
+#include "cut_api.h"
+
+namespace cut {
+namespace {
+
+void cudaCheck(cudaError_t e, const char *what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+void cutbCheck(int rc, const char *what) {
+  if (rc != CUTB_OK) throw std::runtime_error(std::string(what) + ": " + cutb_last_error());
+}
+
+struct DeviceBuffer : ComputeBuffer {
+  ~DeviceBuffer() override {
+    if (owned && data) {
+      if (mapped) cudaFreeHost(hostPtr);
+      else cudaFree(data);
+    }
+    if (counter) *counter -= size();
+    if (count) --*count;
+  }
+  bool owned = true, mapped = false;
+  void *hostPtr = nullptr;
+  ComputeHandle parent;  // keeps the parent of a view alive
+  size_t *counter = nullptr, *count = nullptr;
+};
+
+struct ShaderModule : ComputeHandle::Slot {
+  KernelDesc desc;
+};
+
+struct CommandBufferObj : ComputeHandle::Slot {
+  ~CommandBufferObj() override {
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+  }
+  std::vector<ComputeDispatch> dispatches;  // keeps every bound buffer alive until the work is done
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+};
+
+int cutbFormat(uint32_t f) {
+  switch (static_cast<DequantFormat>(f)) {
+    case DequantFormat::Q8_0: return CUTB_Q8_0;
+    case DequantFormat::Q4_0: return CUTB_Q4_0;
+    case DequantFormat::Q4_K: return CUTB_Q4_K;
+    default: throw std::runtime_error("B200Compute: block format has no kernel");
+  }
+}
+
+class B200Compute final : public ComputeInterface {
+public:
+  explicit B200Compute(int device) : device_(device) {
+    int n = 0;
+    cudaCheck(cudaGetDeviceCount(&n), "cudaGetDeviceCount");
+    if (device < 0 || device >= n) throw std::runtime_error("B200Compute: no such CUDA device");
+    cudaCheck(cudaSetDevice(device), "cudaSetDevice");
+    cudaDeviceProp prop;
+    cudaCheck(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+    if (prop.major < 10)
+      throw std::runtime_error("B200Compute: kernels are built for sm_100a; device is sm_" + std::to_string(prop.major) +
+                               std::to_string(prop.minor));
+    totalMem_ = prop.totalGlobalMem;
+    smemOptin_ = (uint32_t)prop.sharedMemPerBlockOptin;
+    cudaCheck(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+    cudaCheck(cudaMalloc(&status_, sizeof(int)), "cudaMalloc(status)");
+    cudaCheck(cudaMemsetAsync(status_, 0, sizeof(int), stream_), "cudaMemset(status)");
+    caps_.backend = ComputeBackend::CUDA;
+    caps_.cooperativeMatrix = true;  // tensor-core variants exist
+    caps_.integerDotProduct = true;
+    caps_.subgroupSize = 32;
+  }
+  ~B200Compute() override {
+    cudaStreamSynchronize(stream_);
+    if (workspace_) cudaFree(workspace_);
+    cudaFree(status_);
+    cudaStreamDestroy(stream_);
+  }
+
+  ComputeHandle createBuffer(const std::vector<uint32_t> &shape, DataType dtype, const void *host, bool) override {
+    auto buf = std::make_shared<DeviceBuffer>();
+    buf->describe(shape, dtype);
+    buf->id = ++nextId_;
+    const size_t bytes = buf->size() ? buf->size() : 16;
+    cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+    cudaCheck(cudaMalloc(&buf->data, bytes), "cudaMalloc");
+    buf->counter = &activeBytes_;
+    buf->count = &bufferCount_;
+    activeBytes_ += buf->size();
+    ++bufferCount_;
+    ComputeHandle h(buf);
+    if (host) upload(*buf, host);
+    else cudaCheck(cudaMemsetAsync(buf->data, 0, bytes, stream_), "cudaMemsetAsync");
+    return h;
+  }
+
+  ComputeHandle createBufferMapped(const std::vector<uint32_t> &shape, DataType dtype, const void *host, bool) override {
+    auto buf = std::make_shared<DeviceBuffer>();
+    buf->describe(shape, dtype);
+    buf->id = ++nextId_;
+    buf->mapped = true;
+    const size_t bytes = buf->size() ? buf->size() : 16;
+    cudaCheck(cudaHostAlloc(&buf->hostPtr, bytes, cudaHostAllocMapped), "cudaHostAlloc");
+    std::memset(buf->hostPtr, 0, bytes);
+    cudaCheck(cudaHostGetDevicePointer(&buf->data, buf->hostPtr, 0), "cudaHostGetDevicePointer");
+    if (host) copyActualToAligned(host, buf->hostPtr, *buf);
+    buf->counter = &activeBytes_;
+    buf->count = &bufferCount_;
+    activeBytes_ += buf->size();
+    ++bufferCount_;
+    return ComputeHandle(buf);
+  }
+
+  ComputeHandle createBufferView(const ComputeHandle &parent, size_t byteOffset, const std::vector<uint32_t> &shape,
+                                 DataType dtype) override {
+    auto *p = parent.as<DeviceBuffer>();
+    if (!p) throw std::runtime_error("createBufferView: parent is not a buffer");
+    if (byteOffset % bufferOffsetAlignment() != 0) throw std::runtime_error("createBufferView: offset must be a multiple of 256");
+    auto buf = std::make_shared<DeviceBuffer>();
+    buf->describe(shape, dtype);
+    if (byteOffset + buf->size() > p->size()) throw std::runtime_error("createBufferView: view exceeds the parent buffer");
+    buf->id = ++nextId_;
+    buf->owned = false;
+    buf->parent = parent;
+    buf->data = (uint8_t *)p->data + byteOffset;
+    return ComputeHandle(buf);
+  }
+
+  void copyDataToBuffer(const void *host, const ComputeHandle &dest, size_t copySize, size_t srcOffset, size_t destOffset,
+                        bool, bool) override {
+    auto *b = dest.as<DeviceBuffer>();
+    if (!b) throw std::runtime_error("copyDataToBuffer: not a buffer");
+    if (srcOffset == 0 && destOffset == 0 && copySize == b->calculateActualSize()) {
+      upload(*b, host);
+      return;
+    }
+    if (b->innerDimSize() != b->innerDimPadded()) throw std::runtime_error("copyDataToBuffer: partial copy into a padded buffer");
+    if (destOffset + copySize > b->size()) throw std::runtime_error("copyDataToBuffer: out of range");
+    cudaCheck(cudaMemcpyAsync((uint8_t *)b->data + destOffset, (const uint8_t *)host + srcOffset, copySize,
+                              cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
+    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+  }
+
+  void copyDataFromBuffer(const ComputeHandle &src, void *host, size_t copySize, size_t srcOffset, size_t destOffset, bool,
+                          bool) override {
+    auto *b = src.as<DeviceBuffer>();
+    if (!b) throw std::runtime_error("copyDataFromBuffer: not a buffer");
+    if (b->innerDimSize() == b->innerDimPadded() || b->getShape().size() <= 1) {
+      if (srcOffset + copySize > b->size()) throw std::runtime_error("copyDataFromBuffer: out of range");
+      cudaCheck(cudaMemcpyAsync((uint8_t *)host + destOffset, (const uint8_t *)b->data + srcOffset, copySize,
+                                cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync(D2H)");
+      cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+      return;
+    }
+    if (srcOffset != 0 || copySize > b->calculateActualSize())
+      throw std::runtime_error("copyDataFromBuffer: partial copy out of a padded buffer");
+    std::vector<uint8_t> bounce(b->size()), dense(b->calculateActualSize());
+    cudaCheck(cudaMemcpyAsync(bounce.data(), b->data, b->size(), cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync(D2H)");
+    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    copyAlignedToActual(bounce.data(), dense.data(), *b);
+    std::memcpy((uint8_t *)host + destOffset, dense.data(), copySize);
+  }
+
+  ComputeHandle createShaderModule(const std::vector<uint32_t> &words) override {
+    auto desc = KernelDesc::decode(words);
+    if (!desc) throw std::runtime_error("B200Compute: not a kernel descriptor");
+    switch (desc->op) {
+      case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case TransposeQ4: break;
+      default: throw std::runtime_error("B200Compute: no kernel for operator " + std::to_string(desc->op));
+    }
+    if (desc->op == Dequantize || desc->op == MatMulQBlocks) (void)cutbFormat(desc->format);
+    auto m = std::make_shared<ShaderModule>();
+    m->desc = *desc;
+    m->id = ++nextId_;
+    return ComputeHandle(m);
+  }
+
+  const ComputeBuffer &getBuffer(const ComputeHandle &h) const override {
+    auto *b = h.as<DeviceBuffer>();
+    if (!b) throw std::runtime_error("getBuffer: invalid buffer handle");
+    return *b;
+  }
+  size_t bufferCount() const override { return bufferCount_; }
+  size_t activeBufferMemoryBytes() const override { return activeBytes_; }
+  uint32_t maxSharedMemoryPerBlock() const override { return smemOptin_; }
+  size_t deviceTotalMemoryBytes() const override { return totalMem_; }
+  void flushTransfers() override { cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize"); }
+
+protected:
+  ComputeHandle executeDispatches(std::vector<ComputeDispatch> &&dispatches, bool reusable) override {
+    auto cb = std::make_shared<CommandBufferObj>();
+    cb->id = ++nextId_;
+    cb->dispatches = std::move(dispatches);
+    cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+    // scratch is sized before anything is launched or captured
+    size_t need = 0;
+    std::vector<cutb_qmatmul_desc> descs(cb->dispatches.size());
+    for (size_t i = 0; i < cb->dispatches.size(); ++i)
+      if (isMatmul(cb->dispatches[i])) {
+        descs[i] = matmulDesc(cb->dispatches[i]);
+        const size_t w = cutb_qmatmul_workspace_bytes(&descs[i]);
+        need = w > need ? w : need;
+      }
+    ensureWorkspace(need);
+    if (reusable) {
+      // warm launch outside capture (first-use kernel attributes), then capture the same list
+      launchAll(*cb, descs);
+      cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+      cudaCheck(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+      try {
+        launchAll(*cb, descs);
+      } catch (...) {
+        cudaGraph_t g = nullptr;
+        cudaStreamEndCapture(stream_, &g);
+        if (g) cudaGraphDestroy(g);
+        throw;
+      }
+      cudaCheck(cudaStreamEndCapture(stream_, &cb->graph), "cudaStreamEndCapture");
+      cudaCheck(cudaGraphInstantiate(&cb->exec, cb->graph, 0), "cudaGraphInstantiate");
+    } else {
+      launchAll(*cb, descs);
+    }
+    return ComputeHandle(cb);
+  }
+
+  void replay(const ComputeHandle &h) override {
+    auto *cb = h.as<CommandBufferObj>();
+    if (!cb || !cb->exec) throw std::runtime_error("resubmit: not a reusable command buffer");
+    cudaCheck(cudaGraphLaunch(cb->exec, stream_), "cudaGraphLaunch");
+  }
+
+  void waitFor(const ComputeHandle &) override {
+    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    int st = 0;
+    cudaCheck(cudaMemcpy(&st, status_, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
+    if (st != 0) {
+      cudaMemset(status_, 0, sizeof(int));
+      throw std::runtime_error(std::string("B200Compute: kernel reported ") + cutb_status_string(st));
+    }
+  }
+
+private:
+  void upload(DeviceBuffer &b, const void *host) {
+    std::vector<uint8_t> bounce(b.size(), 0);
+    copyActualToAligned(host, bounce.data(), b);
+    cudaCheck(cudaMemcpyAsync(b.data, bounce.data(), b.size(), cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
+    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+  }
+
+  void ensureWorkspace(size_t need) {
+    if (need <= workspaceBytes_) return;
+    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    if (workspace_) cudaFree(workspace_);
+    workspace_ = nullptr;
+    cudaCheck(cudaMalloc(&workspace_, need), "cudaMalloc(workspace)");
+    workspaceBytes_ = need;
+  }
+
+  static const KernelDesc &descOf(const ComputeDispatch &d) {
+    auto *m = d.shader.as<ShaderModule>();
+    if (!m) throw std::runtime_error("B200Compute: dispatch without a kernel");
+    return m->desc;
+  }
+  static bool isMatmul(const ComputeDispatch &d) {
+    if (d.isBarrier) return false;
+    const uint32_t op = descOf(d).op;
+    return op == MatMulQ8 || op == MatMulQ4 || op == MatMulQBlocks;
+  }
+
+  const DeviceBuffer &buf(const ComputeDispatch &d, size_t i) const {
+    if (i >= d.bindings.size() || !d.bindings[i].isHandle()) throw std::runtime_error("B200Compute: missing buffer binding");
+    auto *b = d.bindings[i].handle.as<DeviceBuffer>();
+    if (!b) throw std::runtime_error("B200Compute: binding is not a buffer");
+    return *b;
+  }
+  template <typename T> static T pushConstants(const ComputeDispatch &d) {
+    for (const auto &b : d.bindings)
+      if (!b.isHandle() && b.bytes.size() == sizeof(T)) {
+        T v;
+        std::memcpy(&v, b.bytes.data(), sizeof(T));
+        return v;
+      }
+    throw std::runtime_error("B200Compute: dispatch without push constants");
+  }
+
+  // bindings (A, packedB, [scalesB], D, C, push constants) -> C ABI descriptor
+  cutb_qmatmul_desc matmulDesc(const ComputeDispatch &d) const {
+    const KernelDesc &k = descOf(d);
+    struct PC {
+      uint32_t M, K, N, strideA, strideB, strideC, scaleStride;
+    } pc = pushConstants<PC>(d);
+    cutb_qmatmul_desc q{};
+    const bool blocks = k.op == MatMulQBlocks;
+    const DeviceBuffer &A = buf(d, 0), &W = buf(d, 1);
+    size_t i = 2;
+    q.layout = blocks ? CUTB_LAYOUT_GGUF_BLOCKS : CUTB_LAYOUT_KN_PLANES;
+    q.format = blocks ? cutbFormat(k.format) : (k.op == MatMulQ8 ? CUTB_Q8_0 : CUTB_Q4_0);
+    q.affine = (int32_t)k.affine;
+    q.a_dtype = A.getDtype() == DataType::Float16 ? CUTB_F16 : CUTB_F32;
+    if (A.getDtype() != DataType::Float16 && A.getDtype() != DataType::Float32)
+      throw std::runtime_error("matmul: A must be Float32 or Float16");
+    q.M = pc.M; q.K = pc.K; q.N = pc.N;
+    q.A = A.data;
+    q.lda = pc.strideA;
+    q.W = W.data;
+    q.W_bytes = W.size();
+    if (!blocks) {
+      const DeviceBuffer &S = buf(d, i++);
+      q.scales = S.data;
+      q.ldb = pc.strideB;
+      q.lds = pc.scaleStride;
+    }
+    const DeviceBuffer &D = buf(d, i++), &C = buf(d, i++);
+    q.C = (float *)C.data;
+    q.ldc = pc.strideC;
+    q.D = (const float *)D.data;
+    q.ldd = pc.strideC;
+    q.fusion_type = (int32_t)k.fusionType;
+    q.fusion_op = (int32_t)k.fusionOp;
+    // plane-layout variant indices all map onto the one plane kernel; block variants are the C ABI's own
+    q.variant = blocks ? (int32_t)k.variant : CUTB_VARIANT_GENERIC;
+    q.workspace = workspace_;
+    q.workspace_bytes = workspaceBytes_;
+    q.status = status_;
+    q.flags = 0;
+    return q;
+  }
+
+  void launchAll(CommandBufferObj &cb, std::vector<cutb_qmatmul_desc> &descs) {
+    for (size_t i = 0; i < cb.dispatches.size(); ++i) {
+      const ComputeDispatch &d = cb.dispatches[i];
+      if (d.isBarrier) continue;  // one in-order stream: dispatches are already ordered
+      const KernelDesc &k = descOf(d);
+      if (isMatmul(d)) {
+        descs[i].workspace = workspace_;
+        descs[i].workspace_bytes = workspaceBytes_;
+        cutbCheck(cutb_qmatmul(&descs[i], stream_), d.label.c_str());
+      } else if (k.op == Dequantize) {
+        struct PC {
+          uint32_t rows, cols, outputStride;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &raw = buf(d, 0), &out = buf(d, 1);
+        cutbCheck(cutb_dequant(cutbFormat(k.format), raw.data, raw.size(), (float *)out.data, pc.rows, pc.cols,
+                               pc.outputStride, stream_), "Dequantize");
+      } else if (k.op == TransposeQ4) {
+        struct PC {
+          uint32_t N, K, strideInHalf, strideOutHalf;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &in = buf(d, 0), &out = buf(d, 1);
+        cutbCheck(cutb_transpose_q4(in.data, out.data, pc.N, pc.K, pc.strideInHalf, pc.strideOutHalf, stream_), "TransposeQ4");
+      } else {
+        throw std::runtime_error("B200Compute: no kernel for dispatch " + d.label);
+      }
+    }
+  }
+
+  int device_;
+  cudaStream_t stream_ = nullptr;
+  void *workspace_ = nullptr;
+  size_t workspaceBytes_ = 0;
+  int *status_ = nullptr;
+  size_t nextId_ = 0, activeBytes_ = 0, bufferCount_ = 0, totalMem_ = 0;
+  uint32_t smemOptin_ = 0;
+};
+
+}  // namespace
+
+std::unique_ptr<ComputeInterface> createB200Compute(int device) { return std::make_unique<B200Compute>(device); }
+
+}  // namespace cut

@@ -1,0 +1,321 @@
+// CPU tests of the host logic of the operator API slice: shape validation and
+// error messages, variant choice, push constants, bindings, shader keys, kernel
+// descriptors, the Dispatcher's cache and VariantSelector rules.  A recording
+// ComputeInterface stands in for the device: it allocates host memory for
+// buffers and records dispatches without executing anything.
+#include <cstdlib>
+
+#include "check.h"
+#include "cut_api.h"
+
+using namespace cut;
+
+// This executable links the host logic only; the device backend is not part of it.
+namespace cut {
+std::unique_ptr<ComputeInterface> createB200Compute(int) {
+  throw std::runtime_error("host_logic_test is built without the device backend");
+}
+}  // namespace cut
+
+namespace {
+
+struct HostBuffer : ComputeBuffer {
+  std::vector<uint8_t> bytes;
+};
+struct Module : ComputeHandle::Slot {
+  KernelDesc desc;
+};
+struct Batch : ComputeHandle::Slot {
+  std::vector<ComputeDispatch> dispatches;
+};
+
+class RecordingCompute : public ComputeInterface {
+public:
+  RecordingCompute() {
+    caps_.backend = ComputeBackend::CUDA;
+    caps_.cooperativeMatrix = true;
+  }
+  ComputeHandle createBuffer(const std::vector<uint32_t> &shape, DataType dtype, const void *host, bool) override {
+    auto b = std::make_shared<HostBuffer>();
+    b->describe(shape, dtype);
+    b->bytes.assign(b->size(), 0);
+    b->data = b->bytes.data();
+    if (host) copyActualToAligned(host, b->data, *b);
+    ++buffers;
+    return ComputeHandle(b);
+  }
+  ComputeHandle createBufferView(const ComputeHandle &, size_t, const std::vector<uint32_t> &, DataType) override {
+    throw std::runtime_error("views are not part of these tests");
+  }
+  void copyDataToBuffer(const void *, const ComputeHandle &, size_t, size_t, size_t, bool, bool) override {}
+  void copyDataFromBuffer(const ComputeHandle &src, void *dst, size_t n, size_t, size_t, bool, bool) override {
+    auto *b = src.as<HostBuffer>();
+    std::vector<uint8_t> dense(b->calculateActualSize());
+    copyAlignedToActual(b->data, dense.data(), *b);
+    std::memcpy(dst, dense.data(), n);
+  }
+  ComputeHandle createShaderModule(const std::vector<uint32_t> &words) override {
+    auto d = KernelDesc::decode(words);
+    if (!d) throw std::runtime_error("not a kernel descriptor");
+    auto m = std::make_shared<Module>();
+    m->desc = *d;
+    ++modules;
+    return ComputeHandle(m);
+  }
+  const ComputeBuffer &getBuffer(const ComputeHandle &h) const override {
+    auto *b = h.as<HostBuffer>();
+    if (!b) throw std::runtime_error("invalid buffer handle");
+    return *b;
+  }
+  size_t bufferCount() const override { return buffers; }
+  size_t buffers = 0, modules = 0;
+  std::vector<ComputeDispatch> executed;
+
+protected:
+  ComputeHandle executeDispatches(std::vector<ComputeDispatch> &&d, bool) override {
+    auto b = std::make_shared<Batch>();
+    for (auto &x : d) executed.push_back(x);
+    b->dispatches = std::move(d);
+    return ComputeHandle(b);
+  }
+  void replay(const ComputeHandle &) override {}
+  void waitFor(const ComputeHandle &) override {}
+};
+
+struct Fixture {
+  RecordingCompute *raw;
+  Runtime rt;
+  Fixture() : raw(new RecordingCompute()), rt(std::unique_ptr<ComputeInterface>(raw)) {}
+};
+
+struct PC {
+  uint32_t M, K, N, strideA, strideB, strideC, scaleStride;
+};
+PC pcOf(const MatMulOpNode &n) {
+  PC pc;
+  auto b = n.bindings();
+  std::memcpy(&pc, b.back().bytes.data(), sizeof(pc));
+  return pc;
+}
+
+void bufferGeometry() {
+  // core/api/src/ComputeStructs.cpp:99-120: inner dim to 4 elements, bytes to 16
+  CHECK(ComputeBuffer::calculateAlignedElements({3, 5}) == 3 * 8);
+  CHECK(ComputeBuffer::calculateAlignedSize({3, 5}, DataType::Float32) == 96);
+  CHECK(ComputeBuffer::calculateAlignedSize({2, 2}, DataType::Int8) == 16);
+  CHECK(ComputeBuffer::calculateAlignedSize({5}, DataType::Float16) == 16);
+  CHECK(ComputeBuffer::calculateActualSize({3, 5}, DataType::Float32) == 60);
+  CHECK(dataTypeSize(DataType::Float16) == 2 && dataTypeSize(DataType::Int8) == 1);
+  CHECK(widenPrecision(DataType::Float16) == DataType::Float32 && widenPrecision(DataType::Int8) == DataType::Int8);
+  Fixture f;
+  const float src[6] = {1, 2, 3, 4, 5, 6};
+  auto t = f.rt.createTensor({2, 3}, DataType::Float32, src);
+  const float *padded = (const float *)f.rt.getTensor(t).data;
+  CHECK(padded[0] == 1 && padded[2] == 3 && padded[3] == 0 && padded[4] == 4 && padded[6] == 6);
+  float back[6];
+  f.rt.copyFromTensor(t, back, sizeof(back));
+  CHECK(std::memcmp(back, src, sizeof(src)) == 0);
+}
+
+void quantFormatDetectionAndVariants() {
+  Fixture f;
+  auto &s = f.rt.store();
+  const uint32_t K = 64;
+  auto a1 = s.createTensor({K}, DataType::Float32), a4 = s.createTensor({4, K}, DataType::Float32);
+  auto b8 = s.createTensor({K, 16}, DataType::Int8), b8small = s.createTensor({K, 4}, DataType::Int8);
+  auto sc = s.createTensor({K / 32, 16}, DataType::Float16), scSmall = s.createTensor({K / 32, 4}, DataType::Float16);
+  auto b4 = s.createTensor({K, 8}, DataType::Int8);
+  auto scAff = s.createTensor({2 * K / 32, 16}, DataType::Float16);
+  // Q8: B.cols == scales.cols; Q4: 2 * B.cols == scales.cols; affine: scales rows doubled (MatMulOp.cpp:309-329)
+  MatMulOpNode q8(s, a1, b8, sc), q4(s, a1, b4, sc), q4a(s, a1, b4, scAff);
+  CHECK(q8.format() == QuantFormat::Q8 && q8.op() == MatMulQ8 && q8.N() == 16 && q8.M() == 1 && q8.K() == K);
+  CHECK(q4.format() == QuantFormat::Q4 && q4.op() == MatMulQ4 && q4.N() == 16 && !q4.affine());
+  CHECK(q4a.affine());
+  // variant choice (MatMulOp.cpp:335-380): M = 1 -> GemvKPar8 (N >= 8) else GemvKPar; M > 1 -> tensor-core tiled
+  CHECK(*q8.spec() == 4 && *q4.spec() == 3);
+  CHECK(*MatMulOpNode(s, a1, b8small, scSmall).spec() == 3);
+  CHECK(*MatMulOpNode(s, a1, s.createTensor({K, 2}, DataType::Int8), scSmall).spec() == 2);  // Q4, N = 4 < 8
+  auto b8w = s.createTensor({K, 32}, DataType::Int8), scw = s.createTensor({K / 32, 32}, DataType::Float16);
+  CHECK(*MatMulOpNode(s, a4, b8w, scw).spec() == (uint32_t)kMatMulQ8VariantCount - 1);
+  CHECK(*MatMulOpNode(s, a4, s.createTensor({K, 16}, DataType::Int8), scw).spec() == 4);  // Q4 tensor-core tiled
+  CHECK(*MatMulOpNode(s, a4, b8, sc).spec() == (uint32_t)kMatMulQ8DefaultVariant);         // N % 32 != 0
+  CHECK(*MatMulOpNode(s, a4, b8w, scw, 0).spec() == 0);                                    // explicit spec wins
+  CHECK(std::string(getMatMulQ4VariantName(3)) == "MatMulQ4GemvKPar8");
+  CHECK(std::string(getMatMulQ8VariantName(7)) == "MatMulQ8CoopMatTiled");
+  CHECK(std::string(getMatMulQ8VariantName(99)) == "Unknown");
+  CHECK(getCompiledMatMulQ8(4, DataType::Float32, DataType::Float16, DataType::Float32).has_value());
+  CHECK(getCompiledMatMulQ8(4, DataType::Float16, DataType::Float16, DataType::Float32).has_value());
+  CHECK(!getCompiledMatMulQ8(6, DataType::Float32, DataType::Float16, DataType::Float32).has_value());
+  CHECK(!getCompiledMatMulQ4(5, DataType::Float32, DataType::Float16, DataType::Float32).has_value());
+  CHECK(!getCompiledMatMulQ4(3, DataType::Float32, DataType::Float32, DataType::Float32).has_value());
+  // output is allocated by the node: Float32 [M, N]
+  CHECK(f.rt.getTensor(q8.output()).getShape() == (std::vector<uint32_t>{1, 16}));
+  CHECK(f.rt.getTensor(q8.output()).getDtype() == DataType::Float32);
+}
+
+void shapeErrors() {
+  Fixture f;
+  auto &s = f.rt.store();
+  auto a = s.createTensor({64}, DataType::Float32);
+  auto b = s.createTensor({64, 16}, DataType::Int8);
+  auto sc = s.createTensor({2, 16}, DataType::Float16);
+  CHECK_THROWS(MatMulOpNode(s, a, s.createTensor({64}, DataType::Int8), sc), "2D B and scales");
+  CHECK_THROWS(MatMulOpNode(s, s.createTensor({1, 1, 64}, DataType::Float32), b, sc), "A must be 1D or 2D");
+  CHECK_THROWS(MatMulOpNode(s, s.createTensor({32}, DataType::Float32), b, sc), "must match A cols");
+  CHECK_THROWS(MatMulOpNode(s, a, b, s.createTensor({2, 24}, DataType::Float16)), "cannot determine quant format");
+  CHECK_THROWS(MatMulOpNode(s, a, b, sc, 42), "out of range");
+  CHECK_THROWS(TransposeQ4NibbleOpNode(s, b, 3, 32), "N must be even");
+  CHECK_THROWS(TransposeQ4NibbleOpNode(s, b, 4, 24), "multiple of 32");
+  auto raw = s.createTensor({144}, DataType::Int8);
+  CHECK_THROWS(MatMulOpNode(s, s.createTensor({256}, DataType::Float16), raw, DequantFormat::Q4_K, 2), "need");
+  CHECK_THROWS(MatMulOpNode(s, a, raw, DequantFormat::Q4_K, 1), "multiple of the block size");
+  CHECK_THROWS(MatMulOpNode(s, a, raw, DequantFormat::Q6_K, 1), "Q8_0, Q4_0 or Q4_K");
+  CHECK_THROWS(MatMulOpNode(s, a, b, DequantFormat::Q4_0, 1), "1D Int8");
+  MatMulOpNode ok(s, a, b, sc);
+  CHECK_THROWS(ok.setFusion(MatMulFusion::Binary, BinaryAdd), "needs the D operand");
+  CHECK_THROWS(ok.setFusion(MatMulFusion::Binary, BinaryAdd, s.createTensor({1, 8}, DataType::Float32)), "D must be");
+}
+
+void pushConstantsBindingsAndKeys() {
+  Fixture f;
+  auto &s = f.rt.store();
+  const uint32_t M = 3, K = 96, N = 10;
+  auto a = s.createTensor({M, K}, DataType::Float32);
+  auto b8 = s.createTensor({K, N}, DataType::Int8), sc = s.createTensor({K / 32, N}, DataType::Float16);
+  auto b4 = s.createTensor({K, N / 2}, DataType::Int8);
+  MatMulOpNode q8(s, a, b8, sc), q4(s, a, b4, sc);
+  // strides padded to 4 (MatMulOp.cpp:514-541)
+  PC p8 = pcOf(q8), p4 = pcOf(q4);
+  CHECK(p8.M == M && p8.K == K && p8.N == N && p8.strideA == 96 && p8.strideB == 12 && p8.strideC == 12 && p8.scaleStride == 12);
+  CHECK(p4.strideB == 8 && p4.strideC == 12);
+  // bindings: A, B, scales, dummy D (= C), C, push constants (MatMulOp.cpp:543-575)
+  auto bind = q8.bindings();
+  CHECK(bind.size() == 6 && bind[3].handle == q8.output() && bind[4].handle == q8.output() && !bind[5].isHandle());
+  auto d = s.createTensor({M, N}, DataType::Float32);
+  MatMulOpNode fused(s, a, b8, sc);
+  fused.setFusion(MatMulFusion::Binary, BinaryAdd, d);
+  auto fb = fused.bindings();
+  CHECK(fb.size() == 6 && fb[3].handle == d && fb[4].handle == fused.output());
+  // dispatch size = ceil(N / tileN) * wgX x ceil(M / tileM) * wgY (MatMulOp.cpp:507-512)
+  ThreadSize ts = MatMulOpNode(s, s.createTensor({K}, DataType::Float32), b8, sc).dispatchSize();
+  CHECK(ts.x == 2 * 32 && ts.y == 8 && ts.z == 1);
+  // shader keys separate op, dtypes, affine, fusion and variant (MatMulOp.cpp:440-454)
+  MatMulOpNode unary(s, a, b8, sc);
+  unary.setFusion(MatMulFusion::Unary, UnarySilu);
+  MatMulOpNode relu(s, a, b8, sc);
+  relu.setFusion(MatMulFusion::Unary, UnaryRelu);
+  MatMulOpNode half(s, s.createTensor({M, K}, DataType::Float16), b8, sc);
+  CHECK(q8.shaderKey() != q4.shaderKey() && q8.shaderKey() != unary.shaderKey() && unary.shaderKey() != relu.shaderKey());
+  CHECK(q8.shaderKey() != half.shaderKey() && q8.shaderKey() != fused.shaderKey());
+  CHECK(q8.shaderKey() != MatMulOpNode(s, a, b8, sc, 0).shaderKey());
+  auto scAff = s.createTensor({2 * K / 32, N}, DataType::Float16);
+  CHECK(q4.shaderKey() != MatMulOpNode(s, a, b4, scAff).shaderKey());
+  CHECK(q8.displayName() == "MatMulQ8" && unary.displayName() == "MatMulQ8Unary" && fused.displayName() == "MatMulQ8Binary");
+  // the descriptor carries what the reference patches in as specialisation constants 1-3
+  auto kd = KernelDesc::decode(*unary.shader());
+  CHECK(kd && kd->op == MatMulQ8 && kd->fusionType == 1 && kd->fusionOp == UnarySilu && kd->affine == 0);
+  auto ka = KernelDesc::decode(*MatMulOpNode(s, a, b4, scAff).shader());
+  CHECK(ka && ka->op == MatMulQ4 && ka->affine == 1);
+  CHECK(!KernelDesc::decode({1, 2, 3}).has_value());
+  // Float16 activations are kept (kernels exist); D is widened
+  auto r = half.resolveInputDtypes({DataType::Float16, DataType::Int8, DataType::Float16});
+  CHECK(r[0] == DataType::Float16);
+}
+
+void blockNodesAndDequant() {
+  Fixture f;
+  auto &s = f.rt.store();
+  const uint32_t K = 512, N = 6;
+  auto raw = s.createTensor({N * (K / 256) * 144}, DataType::Int8);
+  MatMulOpNode dec(s, s.createTensor({K}, DataType::Float16), raw, DequantFormat::Q4_K, N);
+  CHECK(dec.format() == QuantFormat::Blocks && dec.op() == MatMulQBlocks && *dec.spec() == 1);  // decode mat-vec
+  MatMulOpNode pre(s, s.createTensor({64, K}, DataType::Float16), raw, DequantFormat::Q4_K, N);
+  CHECK(*pre.spec() == 2);  // prefill GEMM
+  auto raw32 = s.createTensor({N * 3 * 18}, DataType::Int8);
+  CHECK(*MatMulOpNode(s, s.createTensor({96}, DataType::Float32), raw32, DequantFormat::Q4_0, N).spec() == 0);
+  auto kd = KernelDesc::decode(*dec.shader());
+  CHECK(kd && kd->format == (uint32_t)DequantFormat::Q4_K && kd->variant == 1 && kd->dtypeA == (uint32_t)DataType::Float16);
+  CHECK(pcOf(dec).strideB == 2 * 144);
+  CHECK(dec.bindings().size() == 5);  // A, raw blocks, dummy D, C, push constants
+  DequantOpNode dq(s, raw, DequantFormat::Q4_K, N, K);
+  CHECK(dq.dispatchSize().x == K && dq.dispatchSize().y == N);
+  CHECK(f.rt.getTensor(dq.output()).getShape() == (std::vector<uint32_t>{N, K}));
+  CHECK(dq.shader().has_value() && !DequantOpNode(s, raw, DequantFormat::Q6_K, N, K).shader().has_value());
+  TransposeQ4NibbleOpNode tq(s, s.createTensor({6, 16}, DataType::Int8), 6, 32);
+  CHECK(f.rt.getTensor(tq.output()).getShape() == (std::vector<uint32_t>{32, 3}));
+  struct {
+    uint32_t N, K, sin, sout;
+  } tp;
+  auto tb = tq.bindings();
+  std::memcpy(&tp, tb.back().bytes.data(), sizeof(tp));
+  CHECK(tp.N == 6 && tp.K == 32 && tp.sin == 16 && tp.sout == 4);
+}
+
+void dispatcherAndOperations() {
+  Fixture f;
+  auto &ops = f.rt.ops();
+  auto &s = f.rt.store();
+  const uint32_t K = 64, N = 8;
+  auto a = s.createTensor({K}, DataType::Float32);
+  auto b = s.createTensor({K, N}, DataType::Int8), sc = s.createTensor({K / 32, N}, DataType::Float16);
+  auto c1 = ops.matmul(a, b, sc);
+  auto c2 = ops.matmul(a, b, sc);
+  auto c3 = ops.matmulUnary(UnarySilu, a, b, sc);
+  auto d = s.createTensor({1, N}, DataType::Float32);
+  auto c4 = ops.matmulBinary(BinaryAdd, a, b, sc, d);
+  CHECK(c1 != c2 && f.raw->modules == 3);  // same kernel cached by shaderKey (Dispatcher.cpp:62-75)
+  CHECK(f.raw->pendingDispatches() == 4 && f.raw->executed.empty());
+  ops.barrier();
+  f.rt.flush();
+  CHECK(f.raw->executed.size() == 5 && f.raw->executed[4].isBarrier && f.raw->executed[0].label == "MatMulQ8");
+  CHECK(f.raw->executed[3].label == "MatMulQ8Binary" && f.raw->executed[3].outputHandle == c4);
+  // a node without a kernel is an error, not a silent skip
+  auto raw = s.createTensor({210}, DataType::Int8);
+  CHECK_THROWS(ops.dequantize(raw, (uint32_t)DequantFormat::Q6_K, 1, 256), "no shader");
+  (void)c3;
+}
+
+void variantSelectorRules() {
+  auto &vs = VariantSelector::instance();
+  vs.clear();
+  CHECK(vs.select("MatMulQ8", {1, 64, 16}, 4, "cuda") == 4);  // not loaded -> default
+  const char *json = R"({"operators": {
+      "MatMulQ8": {"default_variant": 2, "rules": [{"variant": 1, "conditions": {"total_elements_max": 2048}}],
+                   "backends": {"cuda": {"default_variant": 4,
+                                          "rules": [{"variant": 3, "conditions": {"shape": [1, 64, 16]}},
+                                                    {"variant": 0, "conditions": {"total_elements_min": 100000}}]}}},
+      "MatMulQBlocks": {"backends": {"cuda": {"default_variant": 0, "rules": []}}}}})";
+  CHECK(vs.loadFromString(json) && vs.isLoaded());
+  CHECK(vs.select("MatMulQ8", {1, 64, 16}, 7, "cuda") == 3);        // exact shape, backend-specific
+  CHECK(vs.select("MatMulQ8", {1, 64, 8}, 7, "cuda") == 4);         // backend default
+  CHECK(vs.select("MatMulQ8", {64, 64, 64}, 7, "cuda") == 0);       // total_elements_min
+  CHECK(vs.select("MatMulQ8", {1, 64, 16}, 7, "vulkan") == 1);      // falls back to backend-agnostic rules
+  CHECK(vs.select("MatMulQ8", {64, 64, 64}, 7, "") == 2);
+  CHECK(vs.select("MatMulQ4", {1, 64, 16}, 3, "cuda") == 3);        // unknown operator -> caller's default
+  {
+    Fixture f;
+    auto &s = f.rt.store();
+    auto a = s.createTensor({64}, DataType::Float32);
+    auto b = s.createTensor({64, 16}, DataType::Int8), sc = s.createTensor({2, 16}, DataType::Float16);
+    CHECK(*MatMulOpNode(s, a, b, sc).spec() == 3);  // the rule overrides the built-in GemvKPar8
+    auto raw = s.createTensor({2 * 144}, DataType::Int8);
+    CHECK(*MatMulOpNode(s, s.createTensor({256}, DataType::Float16), raw, DequantFormat::Q4_K, 2).spec() == 0);
+  }
+  CHECK(!vs.loadFromString("{ not json"));
+  CHECK(!vs.loadFromFile("/nonexistent/tuning_data.json"));
+  vs.clear();
+  CHECK(!vs.isLoaded());
+}
+
+}  // namespace
+
+int main() {
+  RUN(bufferGeometry);
+  RUN(quantFormatDetectionAndVariants);
+  RUN(shapeErrors);
+  RUN(pushConstantsBindingsAndKeys);
+  RUN(blockNodesAndDequant);
+  RUN(dispatcherAndOperations);
+  RUN(variantSelectorRules);
+  return finish();
+}

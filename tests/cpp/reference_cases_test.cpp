@@ -1,0 +1,360 @@
+// GPU tests through the C++ operator API: the reference's own known-answer cases
+// for the quantized-matmul path, replayed as its tests call them
+// (tests/harness/OpRegistry.h:1929-1957, 1995-2192; tests/runtime/RuntimeTests.cpp:2861-2938;
+// tests/runtime/OpCoverageTests.cpp:255-277), plus the raw-GGUF-block entry point
+// against the CPU checker (oracle/cut_oracle.c, linked here as the checker only).
+#include <cstdint>
+#include <random>
+
+#include "check.h"
+#include "cut_api.h"
+
+using namespace cut;
+
+extern "C" {
+// CPU checker (test infrastructure)
+void orc_qmatmul_blocks(int fmt, const float *A, const uint8_t *W, float *C, const float *D, size_t M, size_t K, size_t N,
+                        size_t lda, size_t ldc, size_t ldd, int fusion_type, int fusion_op, int acc64);
+void orc_dequant_rows(int fmt, const uint8_t *data, float *out, size_t rows, size_t cols, size_t ldo);
+uint16_t orc_f32_to_f16_trunc(float v);
+uint16_t orc_f32_to_f16_runner(float v);
+}
+
+namespace {
+
+uint16_t f32_to_f16(float v) { return orc_f32_to_f16_trunc(v); }  // tests/harness/OpRefs.h:164-177
+uint8_t packNibbles(uint8_t lo, uint8_t hi) { return (lo & 0xFu) | ((hi & 0xFu) << 4); }
+
+std::vector<float> generateTestData(size_t count, uint32_t seed = 42) {  // tests/harness/OpRefs.h:241-266
+  std::mt19937 gen(seed);
+  std::uniform_real_distribution<float> dist(0.1f, 10.0f);
+  std::vector<float> v(count);
+  for (auto &x : v) x = dist(gen);
+  return v;
+}
+
+Runtime *rt = nullptr;
+
+void q8Simple() {
+  const uint32_t M = 1, K = 32, N = 2, blocksK = K / 32;
+  std::vector<float> dataA(M * K, 1.0f);
+  std::vector<int8_t> dataB(K * N);
+  for (uint32_t k = 0; k < K; ++k) { dataB[k * N + 0] = 1; dataB[k * N + 1] = 2; }
+  std::vector<uint16_t> scales(blocksK * N, f32_to_f16(1.0f));
+  auto bufA = rt->createTensor({M, K}, DataType::Float32, dataA.data());
+  auto bufB = rt->createTensor({K, N}, DataType::Int8, dataB.data());
+  auto bufS = rt->createTensor({blocksK, N}, DataType::Float16, scales.data());
+  auto bufC = rt->ops().matmul(bufA, bufB, bufS);
+  std::vector<float> out(M * N);
+  rt->copyFromTensor(bufC, out.data(), M * N * sizeof(float));
+  CHECK_NEAR(out[0], 32.0f, 1e-3f);
+  CHECK_NEAR(out[1], 64.0f, 1e-3f);
+}
+
+void q8WithScales() {
+  const uint32_t M = 1, K = 64, N = 2, blocksK = K / 32;
+  std::vector<float> dataA(M * K, 1.0f);
+  std::vector<int8_t> dataB(K * N, 4);
+  std::vector<uint16_t> scales = {f32_to_f16(0.5f), f32_to_f16(2.0f), f32_to_f16(1.0f), f32_to_f16(0.25f)};
+  auto bufC = rt->ops().matmul(rt->createTensor({M, K}, DataType::Float32, dataA.data()),
+                               rt->createTensor({K, N}, DataType::Int8, dataB.data()),
+                               rt->createTensor({blocksK, N}, DataType::Float16, scales.data()));
+  std::vector<float> out(M * N);
+  rt->copyFromTensor(bufC, out.data(), M * N * sizeof(float));
+  CHECK_NEAR(out[0], 192.0f, 1.0f);
+  CHECK_NEAR(out[1], 288.0f, 1.0f);
+}
+
+void q4SimpleAndWithScales() {
+  {
+    const uint32_t M = 1, K = 32, N = 2;
+    std::vector<float> dataA(M * K, 1.0f);
+    std::vector<uint8_t> packedB(K * (N / 2));
+    for (uint32_t k = 0; k < K; ++k) packedB[k * (N / 2)] = packNibbles(9, 10);
+    std::vector<uint16_t> scales(N, f32_to_f16(1.0f));
+    auto bufC = rt->ops().matmul(rt->createTensor({M, K}, DataType::Float32, dataA.data()),
+                                 rt->createTensor({K, N / 2}, DataType::Int8, packedB.data()),
+                                 rt->createTensor({1, N}, DataType::Float16, scales.data()));
+    std::vector<float> out(M * N);
+    rt->copyFromTensor(bufC, out.data(), M * N * sizeof(float));
+    CHECK_NEAR(out[0], 32.0f, 1e-3f);
+    CHECK_NEAR(out[1], 64.0f, 1e-3f);
+  }
+  {
+    const uint32_t M = 1, K = 64, N = 2;
+    std::vector<float> dataA(M * K, 1.0f);
+    std::vector<uint8_t> packedB(K * (N / 2));
+    for (uint32_t k = 0; k < K; ++k) packedB[k * (N / 2)] = packNibbles(12, 12);
+    std::vector<uint16_t> scales = {f32_to_f16(0.5f), f32_to_f16(2.0f), f32_to_f16(1.0f), f32_to_f16(0.25f)};
+    auto bufC = rt->ops().matmul(rt->createTensor({M, K}, DataType::Float32, dataA.data()),
+                                 rt->createTensor({K, N / 2}, DataType::Int8, packedB.data()),
+                                 rt->createTensor({2, N}, DataType::Float16, scales.data()));
+    std::vector<float> out(M * N);
+    rt->copyFromTensor(bufC, out.data(), M * N * sizeof(float));
+    CHECK_NEAR(out[0], 192.0f, 1.0f);
+    CHECK_NEAR(out[1], 288.0f, 1.0f);
+  }
+}
+
+// q8_vsregular (M=2,K=64,N=4) and q8_allvariants (M=1,K=512,N=16): every compiled variant whose
+// name lacks "Dot", tolerance |ref| * 2% + 0.1 (OpRegistry.h:2028-2052, 2118-2152)
+void q8VsRegularAllVariants(uint32_t M, uint32_t K, uint32_t N) {
+  const uint32_t blocksPerRow = K / 32;
+  auto dataA = generateTestData(M * K, 42);
+  std::vector<int8_t> dataB(K * N);
+  for (size_t i = 0; i < dataB.size(); ++i) dataB[i] = static_cast<int8_t>((i * 7 + 3) % 21 - 10);
+  std::vector<float> scaleFloats(blocksPerRow * N);
+  for (size_t i = 0; i < scaleFloats.size(); ++i) scaleFloats[i] = 0.1f + 0.05f * static_cast<float>(i);
+  std::vector<uint16_t> scaleF16(scaleFloats.size());
+  for (size_t i = 0; i < scaleFloats.size(); ++i) scaleF16[i] = f32_to_f16(scaleFloats[i]);
+  auto bufA = rt->createTensor({M, K}, DataType::Float32, dataA.data());
+  auto bufB = rt->createTensor({K, N}, DataType::Int8, dataB.data());
+  auto bufS = rt->createTensor({blocksPerRow, N}, DataType::Float16, scaleF16.data());
+  std::vector<float> ref(M * N, 0.0f);
+  for (uint32_t m = 0; m < M; ++m)
+    for (uint32_t n = 0; n < N; ++n)
+      for (uint32_t k = 0; k < K; ++k)
+        ref[m * N + n] += dataA[m * K + k] * static_cast<float>(dataB[k * N + n]) * scaleFloats[(k / 32) * N + n];
+  int tested = 0;
+  for (int vi = -1; vi < kMatMulQ8VariantCount; ++vi) {
+    if (vi >= 0 && !getCompiledMatMulQ8(vi, DataType::Float32, DataType::Float16, DataType::Float32).has_value()) continue;
+    if (vi >= 0 && std::string(getMatMulQ8VariantName(vi)).find("Dot") != std::string::npos) continue;
+    auto bufC = vi < 0 ? rt->ops().matmul(bufA, bufB, bufS) : rt->ops().matmul(bufA, bufB, bufS, vi);
+    std::vector<float> got(M * N);
+    rt->copyFromTensor(bufC, got.data(), M * N * sizeof(float));
+    for (uint32_t i = 0; i < M * N; ++i) CHECK_NEAR(got[i], ref[i], std::abs(ref[i]) * 0.01f + 0.1f);
+    ++tested;
+  }
+  CHECK(tested > 2);
+}
+
+void q4VsReferenceAllVariants(uint32_t M, uint32_t K, uint32_t N) {  // OpRegistry.h:2088-2116, 2154-2192
+  const uint32_t blocksPerRow = K / 32;
+  auto dataA = generateTestData(M * K, 42);
+  std::vector<uint8_t> nibbles(K * N);
+  for (size_t i = 0; i < nibbles.size(); ++i) nibbles[i] = static_cast<uint8_t>((i * 7 + 3) % 16);
+  std::vector<uint8_t> packedB(K * (N / 2));
+  for (uint32_t k = 0; k < K; ++k)
+    for (uint32_t n = 0; n < N; n += 2) packedB[k * (N / 2) + n / 2] = packNibbles(nibbles[k * N + n], nibbles[k * N + n + 1]);
+  std::vector<float> scaleFloats(blocksPerRow * N);
+  for (size_t i = 0; i < scaleFloats.size(); ++i) scaleFloats[i] = 0.1f + 0.05f * static_cast<float>(i);
+  std::vector<uint16_t> scaleF16(scaleFloats.size());
+  for (size_t i = 0; i < scaleFloats.size(); ++i) scaleF16[i] = f32_to_f16(scaleFloats[i]);
+  auto bufA = rt->createTensor({M, K}, DataType::Float32, dataA.data());
+  auto bufB = rt->createTensor({K, N / 2}, DataType::Int8, packedB.data());
+  auto bufS = rt->createTensor({blocksPerRow, N}, DataType::Float16, scaleF16.data());
+  std::vector<float> ref(M * N, 0.0f);
+  for (uint32_t m = 0; m < M; ++m)
+    for (uint32_t n = 0; n < N; ++n)
+      for (uint32_t k = 0; k < K; ++k)
+        ref[m * N + n] += dataA[m * K + k] * static_cast<float>(static_cast<int>(nibbles[k * N + n]) - 8) *
+                          scaleFloats[(k / 32) * N + n];
+  for (int vi = -1; vi < kMatMulQ4VariantCount; ++vi) {
+    auto bufC = vi < 0 ? rt->ops().matmul(bufA, bufB, bufS) : rt->ops().matmul(bufA, bufB, bufS, vi);
+    std::vector<float> got(M * N);
+    rt->copyFromTensor(bufC, got.data(), M * N * sizeof(float));
+    for (uint32_t i = 0; i < M * N; ++i) CHECK_NEAR(got[i], ref[i], std::abs(ref[i]) * 0.01f + 0.1f);
+  }
+}
+
+void q8VsRegular() { q8VsRegularAllVariants(2, 64, 4); }
+void q8AllVariants() { q8VsRegularAllVariants(1, 512, 16); }
+void q4VsReference() { q4VsReferenceAllVariants(2, 64, 4); }
+void q4AllVariants() { q4VsReferenceAllVariants(1, 64, 4); }
+
+// tests/runtime/RuntimeTests.cpp:2861-2938, N trimmed to 1024 to keep the scalar CPU reference quick
+void q8ModelGeometryBatchedVsPerRow() {
+  const uint32_t M = 4, K = 5120, N = 1024, blocksPerRow = K / 32;
+  std::vector<float> dataA(M * K);
+  std::mt19937 gen(42);
+  std::uniform_real_distribution<float> dist(-1.0f, 1.0f);
+  for (auto &x : dataA) x = dist(gen);
+  std::vector<int8_t> dataB(K * N);
+  for (size_t i = 0; i < dataB.size(); ++i) dataB[i] = static_cast<int8_t>((i * 7 + 3) % 21 - 10);
+  std::vector<float> scaleFloats(blocksPerRow * N);
+  for (size_t i = 0; i < scaleFloats.size(); ++i) scaleFloats[i] = (1.0f + (float)(i % 7)) * 0.03125f;
+  std::vector<uint16_t> scaleF16(scaleFloats.size());
+  for (size_t i = 0; i < scaleFloats.size(); ++i) scaleF16[i] = f32_to_f16(scaleFloats[i]);
+  auto bufB = rt->createTensor({K, N}, DataType::Int8, dataB.data());
+  auto bufS = rt->createTensor({blocksPerRow, N}, DataType::Float16, scaleF16.data());
+  std::vector<float> batchedOut(M * N), perRowOut(M * N), silu(M * N);
+  {
+    auto bufA = rt->createTensor({M, K}, DataType::Float32, dataA.data());
+    rt->copyFromTensor(rt->ops().matmul(bufA, bufB, bufS), batchedOut.data(), M * N * sizeof(float));
+    rt->copyFromTensor(rt->ops().matmulUnary(UnarySilu, bufA, bufB, bufS), silu.data(), M * N * sizeof(float));
+  }
+  for (uint32_t m = 0; m < M; ++m) {
+    auto bufRow = rt->createTensor({K}, DataType::Float32, dataA.data() + m * K);
+    rt->copyFromTensor(rt->ops().matmul(bufRow, bufB, bufS), perRowOut.data() + m * N, N * sizeof(float));
+  }
+  int bad = 0;
+  for (uint32_t m = 0; m < M; ++m)
+    for (uint32_t n = 0; n < N; ++n) {
+      double sum = 0.0;
+      for (uint32_t k = 0; k < K; ++k)
+        sum += (double)dataA[m * K + k] * (double)dataB[k * N + n] * (double)scaleFloats[(k / 32) * N + n];
+      const float r = (float)sum, b = batchedOut[m * N + n], p = perRowOut[m * N + n];
+      if (!(std::abs(b - r) <= std::abs(r) * 2e-3f + 0.05f)) ++bad;
+      if (!(std::abs(b - p) <= std::abs(p) * 2e-3f + 0.05f)) ++bad;
+      const float sr = r / (1.0f + std::exp(-r));
+      if (!(std::abs(silu[m * N + n] - sr) <= std::abs(sr) * 2e-3f + 0.05f)) ++bad;
+    }
+  CHECK(bad == 0);
+}
+
+void dequantQ4K() {  // OpRegistry.h:1929-1957
+  const uint32_t rows = 1, cols = 256;
+  std::vector<uint8_t> rawBlock(144, 0);
+  uint16_t d_f16 = f32_to_f16(1.0f), dmin_f16 = f32_to_f16(0.0f);
+  std::memcpy(rawBlock.data(), &d_f16, 2);
+  std::memcpy(rawBlock.data() + 2, &dmin_f16, 2);
+  for (int j = 0; j < 4; ++j) { rawBlock[4 + j] = 1; rawBlock[4 + j + 4] = 0; }
+  for (int j = 4; j < 8; ++j) rawBlock[4 + j + 4] = 1;
+  uint8_t *qs = rawBlock.data() + 16;
+  for (int i = 0; i < 128; ++i) qs[i] = static_cast<uint8_t>(((i % 8) & 0xF) | (((i % 8 + 1) & 0xF) << 4));
+  auto raw = rt->createTensor({static_cast<uint32_t>(rawBlock.size())}, DataType::Int8, rawBlock.data());
+  auto result = rt->ops().dequantize(raw, static_cast<uint32_t>(DequantFormat::Q4_K), rows, cols);
+  std::vector<float> out(rows * cols), want(rows * cols);
+  rt->copyFromTensor(result, out.data(), rows * cols * sizeof(float));
+  for (uint32_t i = 0; i < cols; ++i) CHECK(std::isfinite(out[i]));
+  for (uint32_t i = 0; i < 32; ++i) CHECK_NEAR(out[i], (float)(qs[i] & 0xF), 0.01f);
+  orc_dequant_rows(2, rawBlock.data(), want.data(), rows, cols, cols);
+  CHECK(std::memcmp(out.data(), want.data(), out.size() * sizeof(float)) == 0);
+}
+
+void transposeQ4NibbleBitExact() {  // OpCoverageTests.cpp:255-277
+  const uint32_t N = 32, K = 32;
+  auto Mv = [](uint32_t n, uint32_t k) -> uint8_t { return static_cast<uint8_t>((n * K + k) & 0xF); };
+  std::vector<uint8_t> in(N * (K / 2));
+  for (uint32_t n = 0; n < N; ++n)
+    for (uint32_t j = 0; j < K / 2; ++j) in[n * (K / 2) + j] = static_cast<uint8_t>(Mv(n, j) | (Mv(n, j + 16) << 4));
+  auto tIn = rt->createTensor({N, K / 2}, DataType::Int8, in.data());
+  auto out = rt->ops().transposeQ4(tIn, N, K);
+  CHECK(rt->getTensor(out).getShape() == (std::vector<uint32_t>{K, N / 2}));
+  std::vector<uint8_t> got(K * (N / 2));
+  rt->copyFromTensor(out, got.data(), got.size());
+  int bad = 0;
+  for (uint32_t k = 0; k < K; ++k)
+    for (uint32_t n = 0; n < N; n += 2)
+      if (got[k * (N / 2) + n / 2] != static_cast<uint8_t>(Mv(n, k) | (Mv(n + 1, k) << 4))) ++bad;
+  CHECK(bad == 0);
+}
+
+// raw GGUF blocks through Operations::matmulBlocks against the CPU checker
+void blocksAgainstChecker(int fmt, DequantFormat df, uint32_t M, uint32_t K, uint32_t N, bool half, int fusion) {
+  const uint32_t bb = fmt == 0 ? 34 : fmt == 1 ? 18 : 144, be = fmt == 2 ? 256 : 32;
+  std::mt19937 gen(1234 + fmt + M);
+  std::vector<uint8_t> raw((size_t)N * (K / be) * bb);
+  for (auto &b : raw) b = (uint8_t)gen();
+  std::normal_distribution<float> nd(0.f, 0.02f);
+  for (size_t blk = 0; blk < raw.size() / bb; ++blk) {  // sane fp16 scales at the head of every block
+    uint16_t d = orc_f32_to_f16_runner(std::abs(nd(gen)) / 8.f);
+    std::memcpy(&raw[blk * bb], &d, 2);
+    if (fmt == 2) std::memcpy(&raw[blk * bb + 2], &d, 2);
+  }
+  std::normal_distribution<float> na(0.f, 1.f);
+  std::vector<float> A(M * K), D(M * N);
+  for (auto &x : A) x = na(gen);
+  for (auto &x : D) x = na(gen);
+  std::vector<uint16_t> A16(M * K);
+  if (half)
+    for (size_t i = 0; i < A.size(); ++i) {
+      A16[i] = orc_f32_to_f16_runner(A[i]);
+      // the checker sees the rounded activations: decode them back (exact)
+      uint32_t h = A16[i], sign = (h & 0x8000u) << 16, e = (h >> 10) & 0x1F, m = h & 0x3FF;
+      float f;
+      if (e == 0) f = (float)m * 5.960464477539063e-08f;
+      else { uint32_t bits = ((e + 112) << 23) | (m << 13); std::memcpy(&f, &bits, 4); }
+      A[i] = sign ? -f : f;
+    }
+  auto tA = half ? rt->createTensor({M, K}, DataType::Float16, A16.data()) : rt->createTensor({M, K}, DataType::Float32, A.data());
+  auto tW = rt->createTensor({(uint32_t)raw.size()}, DataType::Int8, raw.data());
+  auto tD = rt->createTensor({M, N}, DataType::Float32, D.data());
+  Tensor tC = fusion == 0   ? rt->ops().matmulBlocks(tA, tW, df, N)
+              : fusion == 1 ? rt->ops().matmulBlocksUnary(UnarySilu, tA, tW, df, N)
+                            : rt->ops().matmulBlocksBinary(BinaryAdd, tA, tW, df, N, tD);
+  std::vector<float> got(M * N), ref(M * N);
+  rt->copyFromTensor(tC, got.data(), got.size() * sizeof(float));
+  orc_qmatmul_blocks(fmt, A.data(), raw.data(), ref.data(), D.data(), M, K, N, K, N, N, fusion, fusion == 1 ? 133 : 0, 1);
+  double num = 0, den = 0;
+  for (size_t i = 0; i < got.size(); ++i) {
+    num += (double)(got[i] - ref[i]) * (got[i] - ref[i]);
+    den += (double)ref[i] * ref[i];
+  }
+  CHECK(std::sqrt(num / den) <= 1e-3);  // rel-L2 tolerance of the path
+}
+
+void blocksEntryPoint() {
+  blocksAgainstChecker(0, DequantFormat::Q8_0, 1, 1024, 300, false, 0);
+  blocksAgainstChecker(1, DequantFormat::Q4_0, 1, 1024, 300, true, 0);
+  blocksAgainstChecker(2, DequantFormat::Q4_K, 8, 512, 128, true, 0);
+  blocksAgainstChecker(1, DequantFormat::Q4_0, 3, 512, 64, false, 1);
+  blocksAgainstChecker(2, DequantFormat::Q4_K, 2, 512, 64, true, 2);
+  blocksAgainstChecker(0, DequantFormat::Q8_0, 2, 96, 10, false, 0);   // K % 256 != 0: SIMT variant
+  blocksAgainstChecker(1, DequantFormat::Q4_0, 40, 512, 64, true, 0);  // M too large for the mat-vec
+}
+
+// cached command buffer: record once, replay as one CUDA graph launch
+// (interface/runner/llama/llama.cpp:2109-2126; core/backends/cuda/CudaCommandBuffer.cpp:261-285)
+void reusableCommandBuffer() {
+  const uint32_t K = 512, N = 64;
+  std::vector<uint8_t> raw((size_t)N * (K / 32) * 34);
+  std::mt19937 gen(7);
+  for (auto &b : raw) b = (uint8_t)gen();
+  for (size_t blk = 0; blk < raw.size() / 34; ++blk) { uint16_t d = 0x2000; std::memcpy(&raw[blk * 34], &d, 2); }
+  std::vector<float> A(K, 1.0f), out1(N), out2(N);
+  auto tA = rt->createTensor({K}, DataType::Float32, A.data());
+  auto tW = rt->createTensor({(uint32_t)raw.size()}, DataType::Int8, raw.data());
+  auto tC = rt->ops().matmulBlocks(tA, tW, DequantFormat::Q8_0, N);
+  ComputeHandle cb = rt->iface().submitReusable();
+  rt->iface().wait(cb);
+  rt->copyFromTensor(tC, out1.data(), N * sizeof(float));
+  for (auto &x : A) x = 2.0f;
+  rt->copyToTensor(tA, A.data(), K * sizeof(float));
+  rt->iface().resubmit(cb);
+  rt->iface().wait(cb);
+  rt->copyFromTensor(tC, out2.data(), N * sizeof(float));
+  int bad = 0;
+  for (uint32_t n = 0; n < N; ++n)
+    if (!(std::abs(out2[n] - 2.0f * out1[n]) <= 1e-4f * std::abs(out1[n]) + 1e-6f)) ++bad;
+  CHECK(bad == 0);
+  CHECK_THROWS(rt->iface().resubmit(ComputeHandle()), "not a reusable");
+}
+
+void errorBehaviour() {
+  auto a = rt->createTensor({64}, DataType::Float32);
+  auto b = rt->createTensor({32, 16}, DataType::Int8);
+  auto s = rt->createTensor({1, 16}, DataType::Float16);
+  CHECK_THROWS(rt->ops().matmul(a, b, s), "must match A cols");
+  CHECK_THROWS(rt->ops().transposeQ4(b, 3, 32), "N must be even");
+  auto raw = rt->createTensor({210}, DataType::Int8);
+  CHECK_THROWS(rt->ops().dequantize(raw, (uint32_t)DequantFormat::Q6_K, 1, 256), "no shader");
+  CHECK(rt->iface().caps().backend == ComputeBackend::CUDA && rt->iface().caps().cooperativeMatrix);
+  CHECK(rt->iface().bufferCount() > 0 && rt->iface().deviceTotalMemoryBytes() > (size_t)100 << 30);
+}
+
+}  // namespace
+
+int main() {
+  try {
+    Runtime runtime(0);
+    rt = &runtime;
+    RUN(q8Simple);
+    RUN(q8WithScales);
+    RUN(q4SimpleAndWithScales);
+    RUN(q8VsRegular);
+    RUN(q8AllVariants);
+    RUN(q4VsReference);
+    RUN(q4AllVariants);
+    RUN(q8ModelGeometryBatchedVsPerRow);
+    RUN(dequantQ4K);
+    RUN(transposeQ4NibbleBitExact);
+    RUN(blocksEntryPoint);
+    RUN(reusableCommandBuffer);
+    RUN(errorBehaviour);
+  } catch (const std::exception &e) {
+    std::printf("FAIL: unexpected exception: %s\n", e.what());
+    return 2;
+  }
+  return finish();
+}
