@@ -327,3 +327,59 @@ def test_affine_q4_planes_from_q4k():
     got = _run_planes(True, A, packedT, scalesT, M, K, N, affine=True)
     assert rel_l2(got, O.qmatmul_planes(True, True, A, packedT, scalesT, M, K, N, acc64=True)) <= 1e-5
     assert rel_l2(got, _ref(synth.Q4_K, A, w, M, K, N)) <= TOL
+
+
+# ---- prefill GEMM on the tcgen05 tensor cores ----
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("M,K,N", [(17, 256, 128), (64, 1024, 136), (128, 512, 1000), (200, 768, 264), (512, 1024, 384)])
+def test_gemm_tc_matches_checker(fmt, dtype, M, K, N):
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M + K + N + fmt)
+    got, used, st = run_blocks(fmt, A, W, N)
+    assert used == L.VARIANT_GEMM_TC and st == 0
+    # fp16 operands (activations and dequantised weights), fp32 accumulate in tensor memory
+    assert rel_l2(got, _ref(fmt, A, W, M, K, N)) <= TOL
+
+
+@pytest.mark.parametrize("ftype,fop", [(1, 133), (2, 0)])
+def test_gemm_tc_fused_epilogues(ftype, fop):
+    from gpu_util import run_blocks
+
+    M, K, N = 96, 512, 200
+    A, W = _inputs(synth.Q4_K, M, K, N, np.float16, seed=88)
+    D = synth.make_activations(M, N, 89) if ftype == 2 else None
+    got, used, _ = run_blocks(synth.Q4_K, A, W, N, D_np=D, fusion_type=ftype, fusion_op=fop)
+    assert used == L.VARIANT_GEMM_TC
+    ref = _ref(synth.Q4_K, A, W, M, K, N, D=D, fusion_type=ftype, fusion_op=fop)
+    assert np.allclose(got, ref, rtol=5e-3, atol=5e-2)
+
+
+def test_gemm_tc_agrees_with_generic_on_fp16_rounded_weights():
+    """Q8_0 / Q4_0 weights times fp16 scales are formed in fp16 as the reference's tensor-core
+    variants do; against the exact-fp32 SIMT variant the difference stays at fp16 rounding level."""
+    from gpu_util import rel_l2, run_blocks
+
+    M, K, N = 48, 1024, 256
+    for fmt in FMTS:
+        A, W = _inputs(fmt, M, K, N, np.float16, seed=5 + fmt)
+        a, used, _ = run_blocks(fmt, A, W, N)
+        g, _, _ = run_blocks(fmt, A, W, N, variant=L.VARIANT_GENERIC)
+        assert used == L.VARIANT_GEMM_TC
+        assert rel_l2(a, g) <= 6e-4
+
+
+def test_config3_q4_k_prefill_512x4096x14336():
+    """Benchmark configuration 3 at full size; the CPU checker covers the first and last 192 weight rows."""
+    from gpu_util import rel_l2, run_blocks
+
+    M, K, N = 512, 4096, 14336
+    A, W = _inputs(synth.Q4_K, M, K, N, np.float16, seed=303)
+    got, used, st = run_blocks(synth.Q4_K, A, W, N)
+    assert used == L.VARIANT_GEMM_TC and st == 0
+    rb = synth.row_bytes(synth.Q4_K, K)
+    for lo, hi in ((0, 192), (N - 192, N)):
+        ref = _ref(synth.Q4_K, A, W[lo * rb:hi * rb], M, K, hi - lo)
+        assert rel_l2(got[:, lo:hi], ref) <= TOL
+    assert np.all(np.isfinite(got))
