@@ -353,7 +353,9 @@ def test_gemm_tc_fused_epilogues(ftype, fop):
     got, used, _ = run_blocks(synth.Q4_K, A, W, N, D_np=D, fusion_type=ftype, fusion_op=fop)
     assert used == L.VARIANT_GEMM_TC
     ref = _ref(synth.Q4_K, A, W, M, K, N, D=D, fusion_type=ftype, fusion_op=fop)
-    assert np.allclose(got, ref, rtol=5e-3, atol=5e-2)
+    from gpu_util import rel_l2
+
+    assert rel_l2(got, ref) <= 2e-3  # fp16 operands feed the epilogue: same tolerance class as the unfused GEMM
 
 
 def test_gemm_tc_agrees_with_generic_on_fp16_rounded_weights():
