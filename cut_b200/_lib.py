@@ -20,7 +20,8 @@ FLAG_NO_OVERLAP = 1
 
 # every symbol include/cutb.h declares
 EXPORTS = [
-    "cutb_qmatmul_workspace_bytes", "cutb_qmatmul_select_variant", "cutb_qmatmul", "cutb_dequant",
+    "cutb_qmatmul_workspace_bytes", "cutb_qmatmul_select_variant", "cutb_qmatmul", "cutb_qmatmul_decode_noalloc",
+    "cutb_dequant",
     "cutb_transpose_q4", "cutb_version", "cutb_status_string", "cutb_last_error", "cutb_device_sm_count",
     "cutb_variant_name",
 ]
@@ -64,6 +65,8 @@ def lib() -> C.CDLL:
         l.cutb_qmatmul_select_variant.argtypes = [C.POINTER(QMatmulDesc)]
         l.cutb_qmatmul.restype = C.c_int
         l.cutb_qmatmul.argtypes = [C.POINTER(QMatmulDesc), C.c_void_p]
+        l.cutb_qmatmul_decode_noalloc.restype = C.c_int
+        l.cutb_qmatmul_decode_noalloc.argtypes = [C.POINTER(QMatmulDesc), C.c_void_p]
         l.cutb_dequant.restype = C.c_int
         l.cutb_dequant.argtypes = [C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
                                    C.c_void_p]

@@ -107,6 +107,9 @@ int select(const cutb_qmatmul_desc &d) {
 }
 
 }  // namespace
+
+int check_qmatmul_desc(const cutb_qmatmul_desc *d) { return validate(d); }
+
 }  // namespace cutb
 
 using namespace cutb;

@@ -7,6 +7,9 @@
 
 namespace cutb {
 
+// Argument checks shared by the cutb_qmatmul entry points (CUTB_OK or an error code + message).
+int check_qmatmul_desc(const cutb_qmatmul_desc *d);
+
 // Decode mat-vec over GGUF blocks (bulk-copy ring + warp MMA).
 bool qgemv_blocks_supported(const cutb_qmatmul_desc &d);
 uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d);

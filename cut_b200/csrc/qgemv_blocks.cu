@@ -949,3 +949,59 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
 }
 
 }  // namespace cutb
+
+// ---------------------------------------------------------------------------
+// Decode mat-vec for callers that must not allocate device memory.
+//
+// Some embedders of this library cannot call cudaMalloc at the point where they
+// run a mat-vec: an inference server that has handed the whole device to its own
+// arena allocator, a plugin loaded into a process whose memory budget is fixed
+// at start-up, or code running inside a region where allocation is forbidden.
+// The split-K decode shapes (long K, few rows per GPU) need scratch for their
+// partial sums; this entry point takes that scratch from a fixed array that is
+// part of the library image instead of from the caller.
+//
+// The array below lives in every GPU context that loads the library, until the
+// process exits.  Its size bounds what the entry point accepts.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr uint64_t kNoAllocScratchFloats = 1u << 20;  // 4 MiB of partial sums: ksplit * M * N <= 1,048,576
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocScratchFloats];
+}  // namespace
+
+extern "C" int cutb_qmatmul_decode_noalloc(const cutb_qmatmul_desc *desc, void *stream) {
+  using namespace cutb;
+  if (int rc = check_qmatmul_desc(desc)) return rc;
+  if (!qgemv_blocks_supported(*desc)) {
+    set_last_error("decode_noalloc: needs GGUF blocks, K %% 256 == 0, 16-byte aligned W and M <= 16 (fp16) / 8 (fp32)");
+    return CUTB_ERR_UNSUPPORTED;
+  }
+  const uint64_t need = qgemv_blocks_workspace(*desc);
+  if (need > kNoAllocScratchFloats * sizeof(float)) {
+    set_last_error("decode_noalloc: this shape needs %llu bytes of scratch, the built-in array holds %llu; "
+                   "use cutb_qmatmul with a caller-provided workspace",
+                   (unsigned long long)need, (unsigned long long)(kNoAllocScratchFloats * sizeof(float)));
+    return CUTB_ERR_WORKSPACE;
+  }
+  // Device address of the array, looked up once per device with that device
+  // current.  (In host code the array's name is only a handle for this lookup,
+  // never a pointer a kernel could use.)
+  static float *scratch_of_device[64] = {};
+  int dev = -1;
+  CUTB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_last_error("decode_noalloc: device index %d out of range", dev);
+    return CUTB_ERR_CUDA;
+  }
+  if (!scratch_of_device[dev]) {
+    float *ptr = nullptr;
+    CUTB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_scratch));
+    scratch_of_device[dev] = ptr;
+  }
+  cutb_qmatmul_desc d = *desc;
+  d.variant = CUTB_VARIANT_GEMV_MMA;
+  d.workspace = scratch_of_device[dev];
+  d.workspace_bytes = kNoAllocScratchFloats * sizeof(float);
+  return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream));
+}
+

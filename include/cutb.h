@@ -128,6 +128,23 @@ CUTB_API int cutb_qmatmul_select_variant(const cutb_qmatmul_desc *desc);
 CUTB_API int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream);
 
 /*
+ * The decode mat-vec of cutb_qmatmul (variant CUTB_VARIANT_GEMV_MMA) for callers
+ * that cannot allocate device memory -- servers that gave the whole GPU to their
+ * own arena, plugins with a memory budget fixed at start-up.  It has no
+ * counterpart in the reference.  desc->workspace is ignored: split-K partial
+ * sums go to a 4 MiB array built into the library (resident in every GPU context
+ * that loads it, until exit), so ksplit * M * N must not exceed 1,048,576
+ * floats; larger shapes are rejected with CUTB_ERR_WORKSPACE and belong to
+ * cutb_qmatmul with a caller-provided workspace.  It calls no allocating routine.
+ * The first call on each device looks up the array's device address; make that
+ * call outside any stream capture.  All calls share the one array and every
+ * call overwrites the region it uses before reading it, so nothing needs
+ * clearing between calls -- but two calls that overlap on the GPU (different
+ * streams, or different host threads) race on it: serialise them.
+ */
+CUTB_API int cutb_qmatmul_decode_noalloc(const cutb_qmatmul_desc *desc, void *stream);
+
+/*
  * Raw GGUF blocks -> fp32 [rows, cols] with row stride ldo (elements).
  * Replaces DequantOpNode's dispatch (operators/impl/dequant/DequantOp.cpp:7-61,
  * DequantQ4K.cu:6-50); Q8_0 and Q4_0 follow the loader's CPU dequantisers
