@@ -195,6 +195,74 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def secondary_measurements(dev) -> dict:
+    """Context numbers for the other benchmark configurations (not the headline value):
+    configs[0] Q8_0 4096x4096 fp32 mat-vec (GB/s, weights cycled over 32 copies) and
+    configs[2] Q4_K prefill GEMM M=512 K=4096 N=14336 (TFLOP/s = 2 M K N / time)."""
+    import torch
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    out = {}
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / iters  # us
+
+    # configs[0]
+    n, k, reps = 4096, 4096, 32
+    base = torch.from_numpy(synth.make_weights(synth.Q8_0, n, k, seed=31)).to(dev)
+    W = torch.stack([torch.roll(base, shifts=34 * 5 * r) for r in range(reps)])
+    A = torch.from_numpy(synth.make_activations(1, k, 32, np.float32)).to(dev)
+    C = torch.zeros((reps, 1, n), dtype=torch.float32, device=dev)
+    descs = [ops.make_desc(A, W[r], L.Q8_0, n, C_out=C[r]) for r in range(reps)]
+
+    def sweep():
+        for d, _, _ in descs:
+            ops.launch(d)
+
+    sweep()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        sweep()
+    us = timed(g.replay, 50) / reps
+    bytes0 = n * (k // 32) * 34 + k * 4 + n * 4
+    out["configs[0]_q8_0_4096x4096_fp32_matvec"] = {"us_per_launch": us, "GB/s": bytes0 / us / 1e3,
+                                                      "algorithmic_bytes": bytes0}
+    del W, C, descs, g
+
+    # configs[2]
+    m, k, n = 512, 4096, 14336
+    W = torch.from_numpy(synth.make_weights(synth.Q4_K, n, k, seed=33)).to(dev)
+    A = torch.from_numpy(synth.make_activations(m, k, 34, np.float16)).to(dev)
+    C = torch.empty((m, n), dtype=torch.float32, device=dev)
+    d, _, keep = ops.make_desc(A, W, L.Q4_K, n, C_out=C)
+    assert ops.select_variant(d) == L.VARIANT_GEMM_TC
+    us = timed(lambda: ops.launch(d), 20)
+    flops = 2.0 * m * k * n
+    peaks = {}
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peaks = json.load(f)
+    tf = flops / us / 1e6
+    out["configs[2]_q4_k_prefill_gemm_512x4096x14336"] = {
+        "us_per_launch": us, "TFLOP/s": tf,
+        "frac_of_measured_bf16_sustained": tf / peaks["bf16_tflops_sustained"] if "bf16_tflops_sustained" in peaks else None,
+        "kernel": "tcgen05.mma kind::f16, TMEM accumulators"}
+    return out
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -352,6 +420,11 @@ def run_ours(args) -> None:
     if int(status.item()) != 0:
         raise SystemExit(f"bench: device status word = {int(status.item())}")
 
+    # ---- the other two parts of the metric, as context (rank 0, single GPU only) ----
+    extra = {}
+    if world == 1:
+        extra = secondary_measurements(dev)
+
     cpu = None
     if rank == 0 and world == 1:
         v, cores, sample = cpu_port_throughput(args.cpu_seconds)
@@ -369,6 +442,7 @@ def run_ours(args) -> None:
                 "parallelism": "single GPU" if world == 1 else f"rows sharded over {world} GPUs, NCCL all-gather of output slices per step",
                 "graph": graph is not None,
                 "pct_of_8TBs": 100.0 * value / world / 8000.0,
+                "also_measured": extra,
             },
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",

@@ -124,24 +124,27 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One try_wait with a suspend-time hint: the hardware parks the thread until the
+// phase completes or about `hint_ns` nanoseconds pass, so a waiting warp issues
+// almost no instructions (a hot polling loop competes for issue slots with the
+// warps that do the work).
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls and returns false; the caller
-// records CUTB_ERR_TIMEOUT and drains instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 22)) {
-  for (uint32_t i = 0; i < limit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
-  }
+// Bounded wait: gives up after `limit` parked waits of up to ~16 us each (about a
+// second by default) and returns false; the caller records CUTB_ERR_TIMEOUT and
+// drains instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 16)) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_wait(bar, parity, 16384u)) return true;
   return false;
 }
 // global -> this CTA's shared memory, completion counted in bytes on `bar`.

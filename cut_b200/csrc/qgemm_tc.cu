@@ -108,16 +108,8 @@ __device__ __forceinline__ void st_chunk(uint8_t *tile, uint32_t r, uint32_t c, 
   *reinterpret_cast<uint4 *>(tile + sw128(r, c)) = v;
 }
 
-// 32-bit little-endian read of the raw weight bytes at 2-byte alignment.
-__device__ __forceinline__ uint32_t ldg32_a2(const uint8_t *p) {
-  if ((reinterpret_cast<uintptr_t>(p) & 3) == 0) return __ldg(reinterpret_cast<const uint32_t *>(p));
-  const uint16_t *q = reinterpret_cast<const uint16_t *>(p);
-  return (uint32_t)__ldg(q) | ((uint32_t)__ldg(q + 1) << 16);
-}
-
-// four nibbles (bits 0-3, 8-11, 16-19, 24-27 of x >> shift) -> two half2 of exact integers
+// four nibbles (low 4 bits of each byte of x) -> two half2 of exact integers
 __device__ __forceinline__ void nib4_to_h2(uint32_t x, __half2 &h01, __half2 &h23) {
-  // bytes b0..b3 hold the nibbles in their low 4 bits: pair (b0, b1) and (b2, b3)
   const uint32_t m = x & 0x0F0F0F0Fu;
   const uint32_t p01 = __byte_perm(m, 0x64646464u, 0x4140), p23 = __byte_perm(m, 0x64646464u, 0x4342);  // 1024 + q
   const __half2 k1024 = __float2half2_rn(1024.f);
@@ -132,69 +124,90 @@ __device__ __forceinline__ void i8x4_to_h2(uint32_t x, __half2 &h01, __half2 &h2
   h23 = __hsub2(u32_as_h2(p23), k);
 }
 
-// Dequantises the 64 weights [k0, k0 + 64) of one row into 8 chunks of 8 halves.
+// Raw bytes of the 64 weights [k0, k0 + 64) of one row, as aligned 32-bit words:
+// Q8_0 two 34-byte blocks (17 words), Q4_0 two 18-byte blocks (9 words), Q4_K the
+// 16-byte super-block header and the 32 quant bytes of the 64-weight group (12 words).
+// Loading is split from converting so that the next stage's bytes are in flight
+// while this stage is converted.
+template <int FMT> struct RawWords {
+  static constexpr int N = FMT == CUTB_Q8_0 ? 17 : (FMT == CUTB_Q4_0 ? 9 : 12);
+  uint32_t w[N];
+};
+
+template <int FMT> __device__ __forceinline__ void load_raw(const uint8_t *row, uint32_t k0, RawWords<FMT> &r) {
+  if constexpr (FMT == CUTB_Q4_K) {
+    const uint8_t *blk = row + (size_t)(k0 / 256) * 144;
+    const uint32_t gq = (k0 % 256) / 64;
+    const uint4 hd = __ldg(reinterpret_cast<const uint4 *>(blk));
+    const uint4 q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * gq));
+    const uint4 q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32 + 32 * gq));
+    r.w[0] = hd.x; r.w[1] = hd.y; r.w[2] = hd.z; r.w[3] = hd.w;
+    r.w[4] = q0.x; r.w[5] = q0.y; r.w[6] = q0.z; r.w[7] = q0.w;
+    r.w[8] = q1.x; r.w[9] = q1.y; r.w[10] = q1.z; r.w[11] = q1.w;
+  } else {
+    // a pair of 18- or 34-byte blocks starts on a 4-byte boundary (K is a multiple of 64)
+    const uint32_t *p = reinterpret_cast<const uint32_t *>(row + (size_t)(k0 / 32) * block_bytes(FMT));
+#pragma unroll
+    for (int i = 0; i < RawWords<FMT>::N; ++i) r.w[i] = __ldg(p + i);
+  }
+}
+
+// Dequantises the 64 weights held in `r` into 8 chunks of 8 halves (k order).
 // Q8_0 / Q4_0 multiply the exact integer by the fp16 block scale in fp16, as the
 // reference's tensor-core variants do (MatMulQ8CoopMatTiled.cu:71-74,
 // MatMulQ4CoopMatTiled.cu:84-87); Q4_K applies fp16(d * sc) and fp16(dmin * m),
 // the precision of the runner's affine re-encode (interface/runner/llama/llama.cpp:602-607).
-template <int FMT> __device__ __forceinline__ void dequant64(const uint8_t *row, uint32_t k0, uint4 (&out)[8]) {
+template <int FMT> __device__ __forceinline__ void convert64(const RawWords<FMT> &r, uint32_t k0, uint4 (&out)[8]) {
   __half2 h[32];
   if constexpr (FMT == CUTB_Q8_0) {
+    // words: {d0,q0,q1} {q2..q5} ... {q30,q31,d1} then block 1's 32 quants in 8 aligned words
+    const __half2 d0 = __half2half2(__ushort_as_half((unsigned short)(r.w[0] & 0xFFFFu)));
+    const __half2 d1 = __half2half2(__ushort_as_half((unsigned short)(r.w[8] >> 16)));
 #pragma unroll
-    for (int b = 0; b < 2; ++b) {
-      const uint8_t *blk = row + (size_t)(k0 / 32 + b) * 34;
-      const __half2 d = __half2half2(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t *>(blk))));
-#pragma unroll
-      for (int w = 0; w < 8; ++w) {
-        __half2 a, c;
-        i8x4_to_h2(ldg32_a2(blk + 2 + 4 * w), a, c);
-        h[b * 16 + 2 * w] = __hmul2(a, d);
-        h[b * 16 + 2 * w + 1] = __hmul2(c, d);
-      }
+    for (int w = 0; w < 8; ++w) {
+      __half2 a, c;
+      i8x4_to_h2(__funnelshift_r(r.w[w], r.w[w + 1], 16), a, c);  // quants 4w .. 4w+3 of block 0
+      h[2 * w] = __hmul2(a, d0);
+      h[2 * w + 1] = __hmul2(c, d0);
+      i8x4_to_h2(r.w[9 + w], a, c);
+      h[16 + 2 * w] = __hmul2(a, d1);
+      h[16 + 2 * w + 1] = __hmul2(c, d1);
     }
   } else if constexpr (FMT == CUTB_Q4_0) {
+    // words: {d0,b0,b1} {b2..b5} {b6..b9} {b10..b13} {b14,b15,d1} then block 1's 16 bytes in 4 aligned words
+    const __half2 d0 = __half2half2(__ushort_as_half((unsigned short)(r.w[0] & 0xFFFFu)));
+    const __half2 d1 = __half2half2(__ushort_as_half((unsigned short)(r.w[4] >> 16)));
+    const __half2 k8 = __float2half2_rn(8.f);
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
-      const uint8_t *blk = row + (size_t)(k0 / 32 + b) * 18;
-      const __half2 d = __half2half2(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t *>(blk))));
-      const __half2 k8 = __float2half2_rn(8.f);
+      const __half2 d = b ? d1 : d0;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        const uint32_t x = ldg32_a2(blk + 2 + 4 * w);
+        const uint32_t x = b ? r.w[5 + w] : __funnelshift_r(r.w[w], r.w[w + 1], 16);  // bytes 4w .. 4w+3
         __half2 a, c;
-        nib4_to_h2(x, a, c);  // elements 4w .. 4w+3
+        nib4_to_h2(x, a, c);  // elements 4w .. 4w+3 (low nibbles)
         h[b * 16 + 2 * w] = __hmul2(__hsub2(a, k8), d);
         h[b * 16 + 2 * w + 1] = __hmul2(__hsub2(c, k8), d);
-        nib4_to_h2(x >> 4, a, c);  // elements 16 + 4w ..
+        nib4_to_h2(x >> 4, a, c);  // elements 16 + 4w .. (high nibbles)
         h[b * 16 + 8 + 2 * w] = __hmul2(__hsub2(a, k8), d);
         h[b * 16 + 8 + 2 * w + 1] = __hmul2(__hsub2(c, k8), d);
       }
     }
   } else {
-    const uint8_t *blk = row + (size_t)(k0 / 256) * 144;
     const uint32_t gq = (k0 % 256) / 64;  // 64-weight group: sub-blocks 2gq (low nibbles), 2gq + 1 (high)
-    const uint4 hd = __ldg(reinterpret_cast<const uint4 *>(blk));
-    const float d = h2f_bits(hd.x & 0xFFFFu), dmin = h2f_bits(hd.x >> 16);
-    // 6-bit scale / min of the two sub-blocks (gguf_reader.cpp:668-676)
-    uint32_t sc[2], mn[2];
+    const float d = h2f_bits(r.w[0] & 0xFFFFu), dmin = h2f_bits(r.w[0] >> 16);
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const uint32_t j = 2 * gq + i;
-      const uint32_t lo_sc = (hd.y >> (8 * (j & 3))) & 0xFF, lo_mn = (hd.z >> (8 * (j & 3))) & 0xFF;
-      const uint32_t hi = (hd.w >> (8 * (j & 3))) & 0xFF;
-      sc[i] = j < 4 ? (lo_sc & 63) : ((hi & 0xF) | ((lo_sc >> 6) << 4));
-      mn[i] = j < 4 ? (lo_mn & 63) : ((hi >> 4) | ((lo_mn >> 6) << 4));
-    }
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * gq));
-    const uint4 q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32 + 32 * gq));
-    const uint32_t qs[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const __half2 ds = __float2half2_rn(d * (float)sc[i]), dm = __float2half2_rn(-(dmin * (float)mn[i]));
+      // 6-bit scale / min of sub-block j (gguf_reader.cpp:668-676)
+      const uint32_t j = 2 * gq + i, sh = 8 * (j & 3);
+      const uint32_t lo_sc = (r.w[1] >> sh) & 0xFF, lo_mn = (r.w[2] >> sh) & 0xFF, hi = (r.w[3] >> sh) & 0xFF;
+      const uint32_t sc = j < 4 ? (lo_sc & 63) : ((hi & 0xF) | ((lo_sc >> 6) << 4));
+      const uint32_t mn = j < 4 ? (lo_mn & 63) : ((hi >> 4) | ((lo_mn >> 6) << 4));
+      const __half2 ds = __float2half2_rn(d * (float)sc), dm = __float2half2_rn(-(dmin * (float)mn));
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
         __half2 a, c;
-        nib4_to_h2(qs[w] >> (4 * i), a, c);
+        nib4_to_h2(r.w[4 + w] >> (4 * i), a, c);
         h[i * 16 + 2 * w] = __hfma2(a, ds, dm);
         h[i * 16 + 2 * w + 1] = __hfma2(c, ds, dm);
       }
@@ -223,7 +236,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) qgemm_tc_kernel(const TcParams 
 
   if (tid == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
-      mbar_init(full_u + s * 8, 256);  // every loader and converter thread arrives once per stage
+      mbar_init(full_u + s * 8, 8);    // one arrival per loader / converter warp and stage
       mbar_init(empty_u + s * 8, 1);   // one tcgen05.commit per stage
     }
     mbar_init(accum_u, 1);
@@ -271,58 +284,87 @@ __global__ void __launch_bounds__(TC_THREADS, 2) qgemm_tc_kernel(const TcParams 
     }
     __syncwarp();
   } else {
-    // ---- producers: warps 1-4 stage A rows, warps 5-8 dequantise W rows -----------
+    // ---- producers: warps 1-4 stage the A tile, warps 5-8 dequantise W rows --------
+    // Every thread keeps the next stage's bytes in flight (registers) while it
+    // stores the current stage.  One lane per warp polls the "empty" barrier and
+    // one lane per warp arrives on "full", so the barriers see 8 parties, not 256.
     const bool is_a = warp <= 4;
-    const uint32_t r = is_a ? tid - 32 : tid - 160;  // row of the tile owned by this thread
+    const uint32_t pt = is_a ? tid - 32 : tid - 160;  // 0..127 within the producer group
     bool dead = false;
-    for (uint32_t ks = 0; ks < nk; ++ks) {
+    auto acquire = [&](uint32_t ks) -> bool {  // warp-uniform: is stage ks free to be written?
       const uint32_t s = ks % TC_STAGES;
-      if (ks >= TC_STAGES && !dead) {
-        if (!mbar_wait_bounded(empty_u + s * 8, ((ks / TC_STAGES) - 1) & 1u)) {
-          give_up();
-          dead = true;
-        }
+      uint32_t ok = 1;
+      if (ks >= TC_STAGES && lane == 0) ok = mbar_wait_bounded(empty_u + s * 8, ((ks / TC_STAGES) - 1) & 1u) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) {
+        if (lane == 0) give_up();
+        dead = true;
       }
-      if (dead || *reinterpret_cast<volatile uint32_t *>(abort_flag)) break;
-      const uint32_t k0 = ks * TC_BK;
-      if (is_a) {
-        uint8_t *tile = tileA + s * TC_TILE_BYTES;
-        const uint32_t m = m0 + r;
-        if (m < p.M) {
-          if (p.a_f32) {
-            const float *src = reinterpret_cast<const float *>(p.A) + (size_t)m * p.lda + k0;
+      return !dead && !*reinterpret_cast<volatile uint32_t *>(abort_flag);
+    };
+    auto release = [&](uint32_t ks) {
+      fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_u + (ks % TC_STAGES) * 8);
+    };
+    if (is_a) {
+      // thread -> 16-byte chunk (pt & 7) of rows (pt >> 3) + 16 i: eight lanes read one 128-byte row segment
+      const uint32_t c = pt & 7, rb = pt >> 3;
+      uint4 nxt[8];
+      auto load_stage = [&](uint32_t ks) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const float4 f0 = __ldg(reinterpret_cast<const float4 *>(src + 8 * c));
-              const float4 f1 = __ldg(reinterpret_cast<const float4 *>(src + 8 * c + 4));
-              st_chunk(tile, r, c,
-                       make_uint4(h2_as_u32(__floats2half2_rn(f0.x, f0.y)), h2_as_u32(__floats2half2_rn(f0.z, f0.w)),
-                                  h2_as_u32(__floats2half2_rn(f1.x, f1.y)), h2_as_u32(__floats2half2_rn(f1.z, f1.w))));
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t m = m0 + rb + 16 * i;
+          nxt[i] = make_uint4(0, 0, 0, 0);
+          if (m < p.M) {
+            const size_t idx = (size_t)m * p.lda + (size_t)ks * TC_BK + 8 * c;
+            if (p.a_f32) {
+              const float *src = reinterpret_cast<const float *>(p.A) + idx;
+              const float4 f0 = __ldg(reinterpret_cast<const float4 *>(src)), f1 = __ldg(reinterpret_cast<const float4 *>(src + 4));
+              nxt[i] = make_uint4(h2_as_u32(__floats2half2_rn(f0.x, f0.y)), h2_as_u32(__floats2half2_rn(f0.z, f0.w)),
+                                  h2_as_u32(__floats2half2_rn(f1.x, f1.y)), h2_as_u32(__floats2half2_rn(f1.z, f1.w)));
+            } else {
+              nxt[i] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.A) + idx));
             }
-          } else {
-            const __half *src = reinterpret_cast<const __half *>(p.A) + (size_t)m * p.lda + k0;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) st_chunk(tile, r, c, __ldg(reinterpret_cast<const uint4 *>(src + 8 * c)));
           }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) st_chunk(tile, r, c, make_uint4(0, 0, 0, 0));
         }
-      } else {
-        uint8_t *tile = tileB + s * TC_TILE_BYTES;
-        const uint32_t n = n0 + r;
+      };
+      load_stage(0);
+      for (uint32_t ks = 0; ks < nk; ++ks) {
         uint4 out[8];
-        if (n < p.N) {
-          dequant64<FMT>(p.W + (size_t)n * p.row_bytes, k0, out);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] = nxt[i];
+        if (ks + 1 < nk) load_stage(ks + 1);
+        if (!acquire(ks)) break;
+        uint8_t *tile = tileA + (ks % TC_STAGES) * TC_TILE_BYTES;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) st_chunk(tile, rb + 16 * i, c, out[i]);
+        release(ks);
+      }
+    } else {
+      const uint32_t r = pt, n = n0 + r;  // one weight row per thread
+      const bool live = n < p.N;
+      const uint8_t *wrow = p.W + (size_t)(live ? n : 0) * p.row_bytes;
+      RawWords<FMT> nxt;
+#pragma unroll
+      for (int i = 0; i < RawWords<FMT>::N; ++i) nxt.w[i] = 0;
+      if (live) load_raw<FMT>(wrow, 0, nxt);
+      for (uint32_t ks = 0; ks < nk; ++ks) {
+        const RawWords<FMT> cur = nxt;
+        if (live && ks + 1 < nk) load_raw<FMT>(wrow, (ks + 1) * TC_BK, nxt);
+        uint4 out[8];
+        if (live) {
+          convert64<FMT>(cur, ks * TC_BK, out);
         } else {
 #pragma unroll
           for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
         }
+        if (!acquire(ks)) break;
+        uint8_t *tile = tileB + (ks % TC_STAGES) * TC_TILE_BYTES;
 #pragma unroll
         for (int c = 0; c < 8; ++c) st_chunk(tile, r, c, out[c]);
+        release(ks);
       }
-      fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
-      mbar_arrive(full_u + s * 8);
     }
 
     // ---- epilogue: warps 1-4, one TMEM lane (= output row) per thread ---------------
@@ -332,7 +374,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) qgemm_tc_kernel(const TcParams 
       } else {
         tc_fence_after();
         const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
-        const uint32_t row = q * 32 + lane, m = m0 + row;
+        const uint32_t row = q * 32 + lane;
+        const uint32_t m = m0 + row;
 #pragma unroll 1
         for (uint32_t c0 = 0; c0 < TC_BN; c0 += 32) {
           uint32_t v[32];

@@ -646,7 +646,7 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
     }
     // stay resident until every copy issued here has landed (bounded)
     const uint32_t first = total_stages > S ? total_stages - S : 0;
-    for (uint32_t j = first; j < total_stages; ++j) (void)mbar_wait_bounded(full_u + (j % S) * 8, (j / S) & 1u, 1u << 18);
+    for (uint32_t j = first; j < total_stages; ++j) (void)mbar_wait_bounded(full_u + (j % S) * 8, (j / S) & 1u);
     return;
   }
 
