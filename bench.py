@@ -48,8 +48,8 @@ METRIC = "qgemv_hbm_gbs"
 UNIT = "GB/s"
 
 # DRAM bytes (read + write) per mat-vec launch seen by ncu for this workload
-# (profiles/qgemv_q4_0_11008x4096.md); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# (profiles/qgemv_q4_0_11008x4096_b1.md: dram__bytes_read.sum + dram__bytes_write.sum).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 25408768
 
 
 def algorithmic_bytes(n_rows: int, k: int, batch: int) -> int:
