@@ -456,7 +456,16 @@ def run_ours(args) -> None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing the communicator down: with CUDA graphs that captured a collective
+        # still alive, destroy_process_group() was seen to block forever on this stack.  Every rank
+        # has finished its work and synchronised; the process exit releases the NCCL resources.
+        del graph, g2
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:
