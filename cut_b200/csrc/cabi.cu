@@ -154,7 +154,9 @@ int cutb_qmatmul_select_variant(const cutb_qmatmul_desc *desc) {
 
 uint64_t cutb_qmatmul_workspace_bytes(const cutb_qmatmul_desc *desc) {
   if (validate(desc) != CUTB_OK) return 0;
-  if (select(*desc) == CUTB_VARIANT_GEMV_MMA) return qgemv_blocks_workspace(*desc);
+  const int v = select(*desc);
+  if (v == CUTB_VARIANT_GEMV_MMA) return qgemv_blocks_workspace(*desc);
+  if (v == CUTB_VARIANT_GEMM_TC) return qgemm_tc_workspace(*desc);
   return 0;
 }
 

@@ -20,6 +20,7 @@ int qmatmul_generic_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
 
 // Prefill GEMM over GGUF blocks on tcgen05 tensor cores.
 bool qgemm_tc_supported(const cutb_qmatmul_desc &d);
+uint64_t qgemm_tc_workspace(const cutb_qmatmul_desc &d);
 int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
 
 int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,

@@ -8,27 +8,31 @@
 // activations and dequantised weights are rounded to fp16, products are
 // accumulated in fp32.
 //
-// One CTA computes one 128 x 128 output tile with tcgen05.mma (kind::f16,
-// M = 128, N = 128, K = 16 per instruction) accumulating in tensor memory:
-//   warp 0      allocates 128 TMEM columns, then one elected lane issues the MMAs
-//               of every K stage and commits them to the stage's "empty" barrier;
-//   warps 1-4   stage the activation tile (fp16, or fp32 converted on the fly)
-//               into shared memory in the K-major 128-byte-swizzled layout the
-//               MMA reads, and afterwards run the epilogue: tcgen05.ld of the
-//               accumulator, fused unary/binary op, stores to C;
-//   warps 5-8   dequantise the weight tile: each thread owns one weight row,
-//               reads its raw block bytes for the 64-k stage, widens the quants
-//               to fp16 with half2 arithmetic (scale applied as in the
-//               reference's tensor-core variants) and stores them in the same
-//               swizzled layout.
-// A 3-stage ring (32 KB per stage) lets two CTAs share an SM, so one CTA's
-// epilogue overlaps the other's main loop.  The raster walks the M tiles of one
-// weight tile back to back, so the raw weight bytes are served by L2 after
-// their first use.
+// One CTA owns one tile of 128 weight rows and up to four 128-token blocks
+// (512 tokens) of the activations, so a weight tile is dequantised once for all
+// of them.  tcgen05.mma (kind::f16, M = 128, N = 128, K = 16 per instruction)
+// accumulates every token block in its own 128 columns of tensor memory:
+//   warp 0      allocates the TMEM columns; one elected lane issues the MMAs of
+//               every K stage (token blocks x 4 instructions) and commits them to
+//               the stage's "empty" barrier;
+//   warp 1      one lane issues the TMA tensor copies of the activation blocks
+//               (64 k x 128 tokens of fp16, 128-byte swizzle, rows past M are
+//               zero-filled by the copy engine), completion counted on the
+//               stage's "full A" barrier;
+//   warps 2-5   dequantise the weight tile: each thread owns one weight row, keeps
+//               the next stage's raw block bytes in flight in registers, widens
+//               the quants to fp16 with half2 arithmetic (scale applied as in the
+//               reference's tensor-core variants) and stores them in the K-major
+//               128-byte-swizzled layout the MMA reads; afterwards they run the
+//               epilogue: tcgen05.ld of the accumulators, fused op, stores to C.
+// fp32 activations are first rounded to fp16 into the caller's workspace by a
+// small cast kernel (the copy engine cannot convert).  With four token blocks a
+// stage is 80 KB and the ring has two stages; with fewer blocks it is deeper.
 //
 // Every wait is bounded; on expiry the CTA records CUTB_ERR_TIMEOUT in the
 // caller's status word, skips its remaining work, frees its tensor memory and
 // returns.
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -38,10 +42,9 @@ namespace cutb {
 namespace {
 
 constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
-constexpr int TC_STAGES = 3;
-constexpr int TC_THREADS = 9 * 32;
-constexpr uint32_t TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 16 KB, A and B tiles alike
-constexpr uint32_t TC_TMEM_COLS = 128;
+constexpr int TC_MAX_MB = 4;          // token blocks per CTA (4 x 128 columns = all of tensor memory)
+constexpr int TC_THREADS = 6 * 32;
+constexpr uint32_t TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 16 KB: one token block, or the weight tile, per stage
 
 struct TcParams {
   const uint8_t *W;
@@ -53,8 +56,9 @@ struct TcParams {
   const float *D;
   uint32_t ldd;
   uint32_t M, K, N;
+  uint32_t mb;      // token blocks per CTA (1..4)
+  uint32_t stages;  // ring depth
   int fusion_type, fusion_op;
-  int a_f32;
   int *status;
 };
 
@@ -88,6 +92,12 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// 2-D TMA tile copy global -> this CTA's shared memory; x = innermost (k) coordinate in elements.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -219,34 +229,34 @@ template <int FMT> __device__ __forceinline__ void convert64(const RawWords<FMT>
 }
 
 template <int FMT>
-__global__ void __launch_bounds__(TC_THREADS, 2) qgemm_tc_kernel(const TcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmapA, const TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // tiles must start on a 1024-byte boundary (the 128-byte swizzle repeats every 8 rows)
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t *tileA = smem;                                   // [TC_STAGES][16 KB]
-  uint8_t *tileB = smem + TC_STAGES * TC_TILE_BYTES;       // [TC_STAGES][16 KB]
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 2 * TC_STAGES * TC_TILE_BYTES);  // full[S], empty[S], accum
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * TC_STAGES + 1);
+  const uint32_t S = p.stages, MB = p.mb;
+  const uint32_t stage_bytes = (MB + 1) * TC_TILE_BYTES;  // MB activation blocks, then the weight tile
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * stage_bytes);  // fullA[S], fullB[S], empty[S], accum
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
   uint32_t *abort_flag = tmem_slot + 1;
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
+  const uint32_t n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * (TC_MAX_MB * TC_BM);
   const uint32_t nk = p.K / TC_BK;
-  const uint32_t full_u = smem_u32(bars), empty_u = full_u + TC_STAGES * 8, accum_u = empty_u + TC_STAGES * 8;
+  const uint32_t fulla_u = smem_u32(bars), fullb_u = fulla_u + S * 8, empty_u = fullb_u + S * 8, accum_u = empty_u + S * 8;
+  const uint32_t tmem_cols = MB == 1 ? 128u : (MB == 2 ? 256u : 512u);
 
   if (tid == 0) {
-    for (int s = 0; s < TC_STAGES; ++s) {
-      mbar_init(full_u + s * 8, 8);    // one arrival per loader / converter warp and stage
-      mbar_init(empty_u + s * 8, 1);   // one tcgen05.commit per stage
+    for (uint32_t s = 0; s < S; ++s) {
+      mbar_init(fulla_u + s * 8, 1);  // the TMA lane's arrive.expect_tx
+      mbar_init(fullb_u + s * 8, 4);  // one arrival per converter warp
+      mbar_init(empty_u + s * 8, 1);  // one tcgen05.commit per stage
     }
     mbar_init(accum_u, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
   if (warp == 0) {
-    // one warp allocates the accumulator columns and publishes the TMEM base address
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(TC_TMEM_COLS)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -259,141 +269,120 @@ __global__ void __launch_bounds__(TC_THREADS, 2) qgemm_tc_kernel(const TcParams 
     if (p.status) atomicExch(p.status, (int)CUTB_ERR_TIMEOUT);
     atomicExch(abort_flag, 1u);
   };
+  auto aborted = [&]() { return *reinterpret_cast<volatile uint32_t *>(abort_flag) != 0; };
 
   if (warp == 0) {
-    // ---- MMA issuer ------------------------------------------------------------
+    // ---- MMA issuer --------------------------------------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_f16(TC_BM, TC_BN);
       bool dead = false;
       for (uint32_t ks = 0; ks < nk && !dead; ++ks) {
-        const uint32_t s = ks % TC_STAGES;
-        if (!mbar_wait_bounded(full_u + s * 8, (ks / TC_STAGES) & 1u)) {
+        const uint32_t s = ks % S, par = (ks / S) & 1u;
+        if (!mbar_wait_bounded(fulla_u + s * 8, par) || !mbar_wait_bounded(fullb_u + s * 8, par)) {
           give_up();
           dead = true;
           break;
         }
         tc_fence_after();
-        const uint64_t adesc = umma_desc_sw128(smem_u32(tileA + s * TC_TILE_BYTES));
-        const uint64_t bdesc = umma_desc_sw128(smem_u32(tileB + s * TC_TILE_BYTES));
+        const uint32_t stage_u = smem_u32(smem + s * stage_bytes);
+        const uint64_t bdesc = umma_desc_sw128(stage_u + MB * TC_TILE_BYTES);
+        for (uint32_t mb = 0; mb < MB; ++mb) {
+          const uint64_t adesc = umma_desc_sw128(stage_u + mb * TC_TILE_BYTES);
 #pragma unroll
-        for (uint32_t k4 = 0; k4 < TC_BK / 16; ++k4)  // 16 k = 32 bytes = 2 descriptor units along the swizzled row
-          umma_f16(tmem_base, adesc + 2 * k4, bdesc + 2 * k4, idesc, (ks | k4) != 0);
+          for (uint32_t k4 = 0; k4 < TC_BK / 16; ++k4)  // 16 k = 32 bytes = 2 descriptor units along the swizzled row
+            umma_f16(tmem_base + mb * TC_BN, adesc + 2 * k4, bdesc + 2 * k4, idesc, (ks | k4) != 0);
+        }
         umma_commit(empty_u + s * 8);  // frees the stage when these MMAs have read it
       }
-      if (!dead) umma_commit(accum_u);  // accumulator complete
+      if (!dead) umma_commit(accum_u);  // accumulators complete
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---- TMA producer: the activation blocks of every stage --------------------------
+    if (lane == 0) {
+      uint32_t issued = 0;
+      for (uint32_t ks = 0; ks < nk; ++ks) {
+        const uint32_t s = ks % S;
+        if (ks >= S && !mbar_wait_bounded(empty_u + s * 8, ((ks / S) - 1) & 1u)) {
+          give_up();
+          break;
+        }
+        if (aborted()) break;
+        const uint32_t bar = fulla_u + s * 8, dst = smem_u32(smem + s * stage_bytes);
+        mbar_arrive_expect_tx(bar, MB * TC_TILE_BYTES);
+        for (uint32_t mb = 0; mb < MB; ++mb) tma_load_2d(dst + mb * TC_TILE_BYTES, &tmapA, ks * TC_BK, m0 + mb * TC_BM, bar);
+        ++issued;
+      }
+      // an aborting CTA must not retire with copies still landing in its shared memory
+      if (aborted())
+        for (uint32_t ks = issued > S ? issued - S : 0; ks < issued; ++ks) mbar_wait_bounded(fulla_u + (ks % S) * 8, (ks / S) & 1u, 1u << 10);
     }
     __syncwarp();
   } else {
-    // ---- producers: warps 1-4 stage the A tile, warps 5-8 dequantise W rows --------
-    // Every thread keeps the next stage's bytes in flight (registers) while it
-    // stores the current stage.  One lane per warp polls the "empty" barrier and
-    // one lane per warp arrives on "full", so the barriers see 8 parties, not 256.
-    const bool is_a = warp <= 4;
-    const uint32_t pt = is_a ? tid - 32 : tid - 160;  // 0..127 within the producer group
+    // ---- converters: one weight row per thread, next stage's bytes kept in flight -------
+    const uint32_t r = tid - 64, n = n0 + r;
+    const bool live = n < p.N;
+    const uint8_t *wrow = p.W + (size_t)(live ? n : 0) * p.row_bytes;
     bool dead = false;
-    auto acquire = [&](uint32_t ks) -> bool {  // warp-uniform: is stage ks free to be written?
-      const uint32_t s = ks % TC_STAGES;
-      uint32_t ok = 1;
-      if (ks >= TC_STAGES && lane == 0) ok = mbar_wait_bounded(empty_u + s * 8, ((ks / TC_STAGES) - 1) & 1u) ? 1u : 0u;
+    RawWords<FMT> nxt;
+#pragma unroll
+    for (int i = 0; i < RawWords<FMT>::N; ++i) nxt.w[i] = 0;
+    if (live) load_raw<FMT>(wrow, 0, nxt);
+    for (uint32_t ks = 0; ks < nk; ++ks) {
+      const uint32_t s = ks % S;
+      const RawWords<FMT> cur = nxt;
+      if (live && ks + 1 < nk) load_raw<FMT>(wrow, (ks + 1) * TC_BK, nxt);
+      uint4 out[8];
+      if (live) {
+        convert64<FMT>(cur, ks * TC_BK, out);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
+      }
+      uint32_t ok = 1;  // one lane per warp polls the barrier
+      if (ks >= S && lane == 0) ok = mbar_wait_bounded(empty_u + s * 8, ((ks / S) - 1) & 1u) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) {
         if (lane == 0) give_up();
         dead = true;
       }
-      return !dead && !*reinterpret_cast<volatile uint32_t *>(abort_flag);
-    };
-    auto release = [&](uint32_t ks) {
+      if (dead || aborted()) break;
+      uint8_t *tile = smem + s * stage_bytes + MB * TC_TILE_BYTES;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) st_chunk(tile, r, c, out[c]);
       fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(full_u + (ks % TC_STAGES) * 8);
-    };
-    if (is_a) {
-      // thread -> 16-byte chunk (pt & 7) of rows (pt >> 3) + 16 i: eight lanes read one 128-byte row segment
-      const uint32_t c = pt & 7, rb = pt >> 3;
-      uint4 nxt[8];
-      auto load_stage = [&](uint32_t ks) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint32_t m = m0 + rb + 16 * i;
-          nxt[i] = make_uint4(0, 0, 0, 0);
-          if (m < p.M) {
-            const size_t idx = (size_t)m * p.lda + (size_t)ks * TC_BK + 8 * c;
-            if (p.a_f32) {
-              const float *src = reinterpret_cast<const float *>(p.A) + idx;
-              const float4 f0 = __ldg(reinterpret_cast<const float4 *>(src)), f1 = __ldg(reinterpret_cast<const float4 *>(src + 4));
-              nxt[i] = make_uint4(h2_as_u32(__floats2half2_rn(f0.x, f0.y)), h2_as_u32(__floats2half2_rn(f0.z, f0.w)),
-                                  h2_as_u32(__floats2half2_rn(f1.x, f1.y)), h2_as_u32(__floats2half2_rn(f1.z, f1.w)));
-            } else {
-              nxt[i] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(p.A) + idx));
-            }
-          }
-        }
-      };
-      load_stage(0);
-      for (uint32_t ks = 0; ks < nk; ++ks) {
-        uint4 out[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) out[i] = nxt[i];
-        if (ks + 1 < nk) load_stage(ks + 1);
-        if (!acquire(ks)) break;
-        uint8_t *tile = tileA + (ks % TC_STAGES) * TC_TILE_BYTES;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) st_chunk(tile, rb + 16 * i, c, out[i]);
-        release(ks);
-      }
-    } else {
-      const uint32_t r = pt, n = n0 + r;  // one weight row per thread
-      const bool live = n < p.N;
-      const uint8_t *wrow = p.W + (size_t)(live ? n : 0) * p.row_bytes;
-      RawWords<FMT> nxt;
-#pragma unroll
-      for (int i = 0; i < RawWords<FMT>::N; ++i) nxt.w[i] = 0;
-      if (live) load_raw<FMT>(wrow, 0, nxt);
-      for (uint32_t ks = 0; ks < nk; ++ks) {
-        const RawWords<FMT> cur = nxt;
-        if (live && ks + 1 < nk) load_raw<FMT>(wrow, (ks + 1) * TC_BK, nxt);
-        uint4 out[8];
-        if (live) {
-          convert64<FMT>(cur, ks * TC_BK, out);
-        } else {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
-        }
-        if (!acquire(ks)) break;
-        uint8_t *tile = tileB + (ks % TC_STAGES) * TC_TILE_BYTES;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) st_chunk(tile, r, c, out[c]);
-        release(ks);
-      }
+      if (lane == 0) mbar_arrive(fullb_u + s * 8);
     }
 
-    // ---- epilogue: warps 1-4, one TMEM lane (= output row) per thread ---------------
-    if (is_a && !dead && !*reinterpret_cast<volatile uint32_t *>(abort_flag)) {
+    // ---- epilogue: one TMEM lane (= token row of each block) per thread --------------------
+    if (!dead && !aborted()) {
       if (!mbar_wait_bounded(accum_u, 0)) {
         give_up();
       } else {
         tc_fence_after();
         const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
-        const uint32_t row = q * 32 + lane;
-        const uint32_t m = m0 + row;
+        for (uint32_t mb = 0; mb < MB; ++mb) {
+          const uint32_t m = m0 + mb * TC_BM + q * 32 + lane;
 #pragma unroll 1
-        for (uint32_t c0 = 0; c0 < TC_BN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + ((q * 32) << 16) + c0, v);
-          if (m < p.M) {
-            float *dst = p.C + (size_t)m * p.ldc + n0 + c0;
-            const float *dsrc = p.fusion_type == CUTB_FUSION_BINARY ? p.D + (size_t)m * p.ldd + n0 + c0 : nullptr;
-            const bool vec = (n0 + c0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-            if (vec && p.fusion_type == CUTB_FUSION_NONE) {
+          for (uint32_t c0 = 0; c0 < TC_BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((q * 32) << 16) + mb * TC_BN + c0, v);
+            if (m < p.M) {
+              float *dst = p.C + (size_t)m * p.ldc + n0 + c0;
+              const float *dsrc = p.fusion_type == CUTB_FUSION_BINARY ? p.D + (size_t)m * p.ldd + n0 + c0 : nullptr;
+              const bool vec = (n0 + c0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+              if (vec && p.fusion_type == CUTB_FUSION_NONE) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                reinterpret_cast<float4 *>(dst)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-            } else {
+                for (int i = 0; i < 8; ++i)
+                  reinterpret_cast<float4 *>(dst)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                                   __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+              } else {
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (n0 + c0 + i < p.N)
-                  dst[i] = apply_epilogue(__uint_as_float(v[i]), p.fusion_type, p.fusion_op, dsrc ? dsrc[i] : 0.f);
+                for (int i = 0; i < 32; ++i)
+                  if (n0 + c0 + i < p.N)
+                    dst[i] = apply_epilogue(__uint_as_float(v[i]), p.fusion_type, p.fusion_op, dsrc ? dsrc[i] : 0.f);
+              }
             }
           }
         }
@@ -406,23 +395,69 @@ __global__ void __launch_bounds__(TC_THREADS, 2) qgemm_tc_kernel(const TcParams 
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
   }
 }
 
-constexpr size_t TC_SMEM = 1024 + 2 * TC_STAGES * TC_TILE_BYTES + (2 * TC_STAGES + 1) * 8 + 16;
+// fp32 activations -> fp16 rows of K elements (the TMA source of the GEMM)
+__global__ void cast_f32_f16_kernel(const float *__restrict__ A, uint32_t lda, __half *__restrict__ out, uint32_t M, uint32_t K) {
+  const size_t total = (size_t)M * (K / 4);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = i / (K / 4), k = (i % (K / 4)) * 4;
+    const float4 f = __ldg(reinterpret_cast<const float4 *>(A + m * lda + k));
+    *reinterpret_cast<uint2 *>(out + m * K + k) =
+        make_uint2(h2_as_u32(__floats2half2_rn(f.x, f.y)), h2_as_u32(__floats2half2_rn(f.z, f.w)));
+  }
+}
 
-template <int FMT> int tc_launch(const TcParams &p, cudaStream_t stream) {
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_tmap_a(CUtensorMap *map, const void *a_f16, uint32_t M, uint32_t K, uint64_t row_stride_bytes) {
+  static EncodeTiledFn encode = nullptr;
+  if (!encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CUTB_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess) {
+      set_last_error("qgemm: the driver does not provide cuTensorMapEncodeTiled");
+      return CUTB_ERR_CUDA;
+    }
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const cuuint64_t dims[2] = {K, M};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {TC_BK, TC_BM};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a_f16), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("qgemm: cuTensorMapEncodeTiled failed with %d (M=%u K=%u stride=%llu)", (int)r, M, K,
+                   (unsigned long long)row_stride_bytes);
+    return CUTB_ERR_CUDA;
+  }
+  return CUTB_OK;
+}
+
+size_t tc_smem_bytes(uint32_t mb, uint32_t stages) {
+  return 1024 + (size_t)stages * (mb + 1) * TC_TILE_BYTES + (3 * stages + 1) * 8 + 16;
+}
+
+template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cudaStream_t stream) {
   static int configured_device = -1;
   int dev = 0;
   CUTB_CUDA_TRY(cudaGetDevice(&dev));
   if (configured_device != dev) {
-    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+    DeviceInfo di;
+    if (int rc = get_device_info(&di)) return rc;
+    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)di.smem_optin));
     configured_device = dev;
   }
-  // M tiles fastest: the CTAs that share a weight tile run back to back
-  dim3 grid((p.M + TC_BM - 1) / TC_BM, (p.N + TC_BN - 1) / TC_BN);
-  qgemm_tc_kernel<FMT><<<grid, TC_THREADS, TC_SMEM, stream>>>(p);
+  dim3 grid((p.N + TC_BN - 1) / TC_BN, (p.M + TC_MAX_MB * TC_BM - 1) / (TC_MAX_MB * TC_BM));
+  qgemm_tc_kernel<FMT><<<grid, TC_THREADS, tc_smem_bytes(p.mb, p.stages), stream>>>(map, p);
   CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;
 }
@@ -441,7 +476,14 @@ bool qgemm_tc_supported(const cutb_qmatmul_desc &d) {
   return di.cc_major == 10;
 }
 
+uint64_t qgemm_tc_workspace(const cutb_qmatmul_desc &d) {
+  // fp32 activations are rounded to fp16 rows of K elements first
+  return d.a_dtype == CUTB_F32 ? (uint64_t)d.M * d.K * sizeof(__half) : 0;
+}
+
 int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
+  DeviceInfo di;
+  if (int rc = get_device_info(&di)) return rc;
   TcParams p;
   p.W = reinterpret_cast<const uint8_t *>(d.W);
   p.row_bytes = row_bytes(d.format, d.K);
@@ -456,12 +498,42 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.N = d.N;
   p.fusion_type = d.fusion_type;
   p.fusion_op = d.fusion_op;
-  p.a_f32 = d.a_dtype == CUTB_F32;
   p.status = d.status;
+  const uint32_t mblocks = (d.M + TC_BM - 1) / TC_BM;
+  p.mb = mblocks < TC_MAX_MB ? mblocks : TC_MAX_MB;
+  p.stages = 0;
+  for (uint32_t st = 6; st >= 2; --st)
+    if (tc_smem_bytes(p.mb, st) <= di.smem_optin) {
+      p.stages = st;
+      break;
+    }
+  if (!p.stages) {
+    set_last_error("qgemm: shared memory too small for a two-stage ring");
+    return CUTB_ERR_UNSUPPORTED;
+  }
+  const void *a16 = d.A;
+  uint64_t stride = (uint64_t)d.lda * sizeof(__half);
+  if (d.a_dtype == CUTB_F32) {
+    const uint64_t need = qgemm_tc_workspace(d);
+    if (!d.workspace || d.workspace_bytes < need || reinterpret_cast<uintptr_t>(d.workspace) % 16 != 0) {
+      set_last_error("qgemm: fp32 activations need %llu bytes of 16-byte aligned workspace, got %llu",
+                     (unsigned long long)need, (unsigned long long)d.workspace_bytes);
+      return CUTB_ERR_WORKSPACE;
+    }
+    const size_t total = (size_t)d.M * (d.K / 4);
+    const unsigned blocks = (unsigned)((total + 255) / 256 < (size_t)di.sm_count * 8 ? (total + 255) / 256 : (size_t)di.sm_count * 8);
+    cast_f32_f16_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float *>(d.A), d.lda,
+                                                    reinterpret_cast<__half *>(d.workspace), d.M, d.K);
+    CUTB_CUDA_TRY(cudaGetLastError());
+    a16 = d.workspace;
+    stride = (uint64_t)d.K * sizeof(__half);
+  }
+  CUtensorMap map;
+  if (int rc = make_tmap_a(&map, a16, d.M, d.K, stride)) return rc;
   switch (d.format) {
-    case CUTB_Q8_0: return tc_launch<CUTB_Q8_0>(p, stream);
-    case CUTB_Q4_0: return tc_launch<CUTB_Q4_0>(p, stream);
-    default: return tc_launch<CUTB_Q4_K>(p, stream);
+    case CUTB_Q8_0: return tc_launch<CUTB_Q8_0>(map, p, stream);
+    case CUTB_Q4_0: return tc_launch<CUTB_Q4_0>(map, p, stream);
+    default: return tc_launch<CUTB_Q4_K>(map, p, stream);
   }
 }
 
