@@ -147,6 +147,23 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity, 16384u)) return true;
   return false;
 }
+// Bounded polling wait without parking: for the single threads on a kernel's critical
+// path (an MMA issuer, a copy producer), where the wake-up delay of a parked wait would
+// be paid once per pipeline step.  About a second at ~30 cycles per probe.
+__device__ __forceinline__ bool mbar_spin_bounded(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 26)) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
 // global -> this CTA's shared memory, completion counted in bytes on `bar`.
 // dst, src 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {

@@ -8,32 +8,43 @@
 // activations and dequantised weights are rounded to fp16, products are
 // accumulated in fp32.
 //
-// One CTA owns one tile of 128 weight rows and up to four 128-token blocks
-// (512 tokens) of the activations, so a weight tile is dequantised once for all
-// of them.  tcgen05.mma (kind::f16, M = 128, N = 128, K = 16 per instruction)
-// accumulates every token block in its own 128 columns of tensor memory:
-//   warp 0      allocates the TMEM columns; one elected lane issues the MMAs of
-//               every K stage (token blocks x 4 instructions) and commits them to
-//               the stage's "empty" barrier;
+// One CTA owns one tile of 128 weight rows and up to 512 tokens, so a weight tile
+// is dequantised once for all of them.  The weight tile is the MMA's M operand
+// (one weight row per tensor-memory lane) and the tokens are its N operand, 256
+// at a time: tcgen05.mma kind::f16 with M = 128, N = 256, K = 16 reads 12 KB of
+// shared memory per instruction where the 128 x 128 shape reads 8 KB for half the
+// work, and shared-memory bandwidth (operand reads + tile writes) is what bounds
+// this kernel.  Each pair of 128-token blocks accumulates in its own 256 columns
+// of tensor memory.
+//   warp 0      allocates the TMEM columns; one lane issues the MMAs of every K stage
+//               and commits the stage's activation slot and weight slot to their
+//               "empty" barriers.  Its instruction stream is the kernel's critical
+//               path (a lone thread retires an instruction every ~6 cycles), so the
+//               loop keeps ring indices and descriptor words incrementally and
+//               waits by polling, not by parking;
+//   warp 2      a second issuer for the second token pair (independent accumulator);
 //   warp 1      one lane issues the TMA tensor copies of the activation blocks
 //               (64 k x 128 tokens of fp16, 128-byte swizzle, rows past M are
-//               zero-filled by the copy engine), completion counted on the
-//               stage's "full A" barrier;
-//   warps 2-5   dequantise the weight tile: each thread owns one weight row, keeps
-//               the next stage's raw block bytes in flight in registers, widens
+//               zero-filled by the copy engine), completion counted on the stage's
+//               "full" barrier;
+//   warps 4..   dequantise the weight tile in groups of four warps; group g owns the
+//               K stages g, g + G, ...; each thread owns one weight row, keeps the
+//               raw block bytes of its next stage in flight in registers, widens
 //               the quants to fp16 with half2 arithmetic (scale applied as in the
 //               reference's tensor-core variants) and stores them in the K-major
 //               128-byte-swizzled layout the MMA reads; afterwards they run the
-//               epilogue: tcgen05.ld of the accumulators, fused op, stores to C.
+//               epilogue: tcgen05.ld of the accumulators (lane = weight row, column
+//               = token), fused op, stores to C coalesced along n.
 // fp32 activations are first rounded to fp16 into the caller's workspace by a
-// small cast kernel (the copy engine cannot convert).  With four token blocks a
-// stage is 80 KB and the ring has two stages; with fewer blocks it is deeper.
+// small cast kernel (the copy engine cannot convert).  Shared memory holds a ring
+// of activation stages (three at 512 tokens) and a ring of two weight tiles.
 //
 // Every wait is bounded; on expiry the CTA records CUTB_ERR_TIMEOUT in the
 // caller's status word, skips its remaining work, frees its tensor memory and
 // returns.
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -41,23 +52,28 @@
 namespace cutb {
 namespace {
 
-constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64;
+constexpr int TC_BW = 128;            // weight rows per CTA (MMA M, one per TMEM lane)
+constexpr int TC_BT = 128;            // tokens per activation tile (rows of one TMA box)
+constexpr int TC_BK = 64;             // k per stage: one 128-byte swizzled row of fp16
 constexpr int TC_MAX_MB = 4;          // token blocks per CTA (4 x 128 columns = all of tensor memory)
-constexpr int TC_THREADS = 6 * 32;
-constexpr uint32_t TC_TILE_BYTES = TC_BM * TC_BK * 2;  // 16 KB: one token block, or the weight tile, per stage
+constexpr int TC_MAX_GROUPS = 2;      // converter groups of 128 threads; group g dequantises K stages g, g + G, ...
+constexpr int TC_CTRL_THREADS = 128;  // warps 0-3: issuer, copy producer, second issuer, spare
+constexpr int TC_MAX_THREADS = TC_CTRL_THREADS + 128 * TC_MAX_GROUPS;
+constexpr uint32_t TC_TILE_BYTES = 128 * TC_BK * 2;  // 16 KB: one token block, or the weight tile, per stage
+constexpr uint32_t TC_TILE_DESC = TC_TILE_BYTES >> 4;  // the same in descriptor address units
 
 struct TcParams {
   const uint8_t *W;
   uint64_t row_bytes;
-  const void *A;
-  uint32_t lda;
   float *C;
   uint32_t ldc;
   const float *D;
   uint32_t ldd;
   uint32_t M, K, N;
-  uint32_t mb;      // token blocks per CTA (1..4)
-  uint32_t stages;  // ring depth
+  uint32_t mb;       // token blocks per CTA (1..4)
+  uint32_t sa, nb;   // activation stages (of mb tiles each) and weight slots in shared memory
+  uint32_t groups;   // converter groups (1..nb)
+  uint32_t issuers;  // MMA issuer threads (1..2, at most one per token pair)
   int fusion_type, fusion_op;
   int *status;
 };
@@ -79,11 +95,16 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 __host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
   return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// The descriptors of all tiles differ only in the start-address field, so the issuer keeps the
+// low words and one shared high word; `accumulate` = 0 overwrites the accumulator.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint32_t adesc_lo, uint32_t bdesc_lo, uint32_t desc_hi, uint32_t idesc,
+                                         uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(adesc_lo), "r"(bdesc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -229,29 +250,34 @@ template <int FMT> __device__ __forceinline__ void convert64(const RawWords<FMT>
 }
 
 template <int FMT>
-__global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmapA, const TcParams p) {
+__global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmapA, const TcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // tiles must start on a 1024-byte boundary (the 128-byte swizzle repeats every 8 rows)
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t S = p.stages, MB = p.mb;
-  const uint32_t stage_bytes = (MB + 1) * TC_TILE_BYTES;  // MB activation blocks, then the weight tile
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S * stage_bytes);  // fullA[S], fullB[S], empty[S], accum
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+  const uint32_t SA = p.sa, NB = p.nb, MB = p.mb, NI = p.issuers;
+  const uint32_t a_stage_bytes = MB * TC_TILE_BYTES;
+  uint8_t *a_ring = smem, *b_ring = smem + SA * a_stage_bytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(b_ring + NB * TC_TILE_BYTES);  // fullA[SA] emptyA[SA] fullB[NB] emptyB[NB] accum
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * SA + 2 * NB + 1);
   uint32_t *abort_flag = tmem_slot + 1;
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * (TC_MAX_MB * TC_BM);
+  const uint32_t n0 = blockIdx.x * TC_BW, m0 = blockIdx.y * (TC_MAX_MB * TC_BT);
   const uint32_t nk = p.K / TC_BK;
-  const uint32_t fulla_u = smem_u32(bars), fullb_u = fulla_u + S * 8, empty_u = fullb_u + S * 8, accum_u = empty_u + S * 8;
+  const uint32_t fulla_u = smem_u32(bars), emptya_u = fulla_u + SA * 8, fullb_u = emptya_u + SA * 8, emptyb_u = fullb_u + NB * 8,
+                 accum_u = emptyb_u + NB * 8;
   const uint32_t tmem_cols = MB == 1 ? 128u : (MB == 2 ? 256u : 512u);
 
   if (tid == 0) {
-    for (uint32_t s = 0; s < S; ++s) {
-      mbar_init(fulla_u + s * 8, 1);  // the TMA lane's arrive.expect_tx
-      mbar_init(fullb_u + s * 8, 4);  // one arrival per converter warp
-      mbar_init(empty_u + s * 8, 1);  // one tcgen05.commit per stage
+    for (uint32_t s = 0; s < SA; ++s) {
+      mbar_init(fulla_u + s * 8, 1);    // the TMA lane's arrive.expect_tx
+      mbar_init(emptya_u + s * 8, NI);  // one tcgen05.commit per issuer and stage
     }
-    mbar_init(accum_u, 1);
+    for (uint32_t s = 0; s < NB; ++s) {
+      mbar_init(fullb_u + s * 8, 4);    // one arrival per converter warp of the owning group
+      mbar_init(emptyb_u + s * 8, NI);  // one tcgen05.commit per issuer and stage
+    }
+    mbar_init(accum_u, NI);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -271,67 +297,92 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
   };
   auto aborted = [&]() { return *reinterpret_cast<volatile uint32_t *>(abort_flag) != 0; };
 
-  if (warp == 0) {
-    // ---- MMA issuer --------------------------------------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(TC_BM, TC_BN);
+  if (warp == 0 || warp == 2) {
+    // ---- MMA issuers: issuer i owns the token pairs i, i + NI (256 tokens = 256 TMEM columns) ----
+    const uint32_t me = warp >> 1;
+    if (lane == 0 && me < NI) {
+      const uint32_t npairs = (MB + 1) >> 1;
+      // descriptor words: start address in the low word, stride / version / swizzle in the high word
+      const uint64_t proto = umma_desc_sw128(0);
+      const uint32_t desc_hi = (uint32_t)(proto >> 32), lo0 = (uint32_t)proto;
+      const uint32_t w_lo0 = lo0 + ((smem_u32(b_ring) & 0x3FFFFu) >> 4), t_lo0 = lo0 + ((smem_u32(a_ring) & 0x3FFFFu) >> 4);
+      const uint32_t idesc256 = umma_idesc_f16(TC_BW, 256), idesc128 = umma_idesc_f16(TC_BW, 128);
+      uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
       bool dead = false;
-      for (uint32_t ks = 0; ks < nk && !dead; ++ks) {
-        const uint32_t s = ks % S, par = (ks / S) & 1u;
-        if (!mbar_wait_bounded(fulla_u + s * 8, par) || !mbar_wait_bounded(fullb_u + s * 8, par)) {
+      for (uint32_t ks = 0; ks < nk; ++ks) {
+        if (!mbar_spin_bounded(fullb_u + sb * 8, pb) || !mbar_spin_bounded(fulla_u + sa * 8, pa)) {
           give_up();
           dead = true;
           break;
         }
         tc_fence_after();
-        const uint32_t stage_u = smem_u32(smem + s * stage_bytes);
-        const uint64_t bdesc = umma_desc_sw128(stage_u + MB * TC_TILE_BYTES);
-        for (uint32_t mb = 0; mb < MB; ++mb) {
-          const uint64_t adesc = umma_desc_sw128(stage_u + mb * TC_TILE_BYTES);
-#pragma unroll
-          for (uint32_t k4 = 0; k4 < TC_BK / 16; ++k4)  // 16 k = 32 bytes = 2 descriptor units along the swizzled row
-            umma_f16(tmem_base + mb * TC_BN, adesc + 2 * k4, bdesc + 2 * k4, idesc, (ks | k4) != 0);
+        const uint32_t w_lo = w_lo0 + sb * TC_TILE_DESC, t_lo = t_lo0 + sa * MB * TC_TILE_DESC;
+        const uint32_t acc = ks != 0;
+        for (uint32_t pr = me; pr < npairs; pr += NI) {
+          const uint32_t idesc = (2 * pr + 2 <= MB) ? idesc256 : idesc128;
+          const uint32_t tl = t_lo + pr * 2 * TC_TILE_DESC, d = tmem_base + pr * 256;
+          // 16 k = 32 bytes = 2 descriptor units along the swizzled row
+          umma_f16(d, w_lo, tl, desc_hi, idesc, acc);
+          umma_f16(d, w_lo + 2, tl + 2, desc_hi, idesc, 1);
+          umma_f16(d, w_lo + 4, tl + 4, desc_hi, idesc, 1);
+          umma_f16(d, w_lo + 6, tl + 6, desc_hi, idesc, 1);
         }
-        umma_commit(empty_u + s * 8);  // frees the stage when these MMAs have read it
+        umma_commit(emptya_u + sa * 8);  // frees the activation stage when these MMAs have read it
+        umma_commit(emptyb_u + sb * 8);  // and the weight slot
+        if (++sa == SA) sa = 0, pa ^= 1u;
+        if (++sb == NB) sb = 0, pb ^= 1u;
       }
-      if (!dead) umma_commit(accum_u);  // accumulators complete
+      if (!dead) umma_commit(accum_u);  // this issuer's accumulators are complete
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ---- TMA producer: the activation blocks of every stage --------------------------
+    // ---- TMA producer: the activation blocks of every stage ------------------------------
     if (lane == 0) {
+      uint32_t sa = 0, pa = 1u;  // parity of the slot's previous use (first turn: nothing to wait for)
       uint32_t issued = 0;
+      const uint32_t a_base = smem_u32(a_ring);
       for (uint32_t ks = 0; ks < nk; ++ks) {
-        const uint32_t s = ks % S;
-        if (ks >= S && !mbar_wait_bounded(empty_u + s * 8, ((ks / S) - 1) & 1u)) {
+        if (ks >= SA && !mbar_spin_bounded(emptya_u + sa * 8, pa)) {
           give_up();
           break;
         }
         if (aborted()) break;
-        const uint32_t bar = fulla_u + s * 8, dst = smem_u32(smem + s * stage_bytes);
-        mbar_arrive_expect_tx(bar, MB * TC_TILE_BYTES);
-        for (uint32_t mb = 0; mb < MB; ++mb) tma_load_2d(dst + mb * TC_TILE_BYTES, &tmapA, ks * TC_BK, m0 + mb * TC_BM, bar);
+        const uint32_t bar = fulla_u + sa * 8, dst = a_base + sa * a_stage_bytes;
+        mbar_arrive_expect_tx(bar, a_stage_bytes);
+        for (uint32_t mb = 0; mb < MB; ++mb) tma_load_2d(dst + mb * TC_TILE_BYTES, &tmapA, ks * TC_BK, m0 + mb * TC_BT, bar);
         ++issued;
+        if (++sa == SA) sa = 0, pa ^= 1u;
       }
-      // an aborting CTA must not retire with copies still landing in its shared memory
-      if (aborted())
-        for (uint32_t ks = issued > S ? issued - S : 0; ks < issued; ++ks) mbar_wait_bounded(fulla_u + (ks % S) * 8, (ks / S) & 1u, 1u << 10);
+      // an aborting CTA must not retire with copies still landing in its shared memory:
+      // wait (bounded) for the last ring turn of copies it issued
+      if (aborted()) {
+        const uint32_t pending = issued < SA ? issued : SA;
+        for (uint32_t i = 0; i < pending; ++i) {
+          if (sa == 0) sa = SA, pa ^= 1u;
+          --sa;
+          mbar_wait_bounded(fulla_u + sa * 8, pa ^ 1u, 1u << 10);
+        }
+      }
     }
     __syncwarp();
-  } else {
-    // ---- converters: one weight row per thread, next stage's bytes kept in flight -------
-    const uint32_t r = tid - 64, n = n0 + r;
+  } else if (warp >= 4) {
+    // ---- converters: one weight row per thread; group g owns K stages g, g + G, ... and keeps
+    // the raw bytes of its next stage in flight while it converts the current one.  G <= NB:
+    // a group further ahead than one ring turn would alias the parity of the slot's barrier ----
+    const uint32_t G = (blockDim.x - TC_CTRL_THREADS) >> 7;
+    const uint32_t ct = tid - TC_CTRL_THREADS, r = ct & 127u, g = ct >> 7, n = n0 + r;
     const bool live = n < p.N;
     const uint8_t *wrow = p.W + (size_t)(live ? n : 0) * p.row_bytes;
     bool dead = false;
     RawWords<FMT> nxt;
 #pragma unroll
     for (int i = 0; i < RawWords<FMT>::N; ++i) nxt.w[i] = 0;
-    if (live) load_raw<FMT>(wrow, 0, nxt);
-    for (uint32_t ks = 0; ks < nk; ++ks) {
-      const uint32_t s = ks % S;
+    if (live && g < nk) load_raw<FMT>(wrow, g * TC_BK, nxt);
+    // this group's slot sequence: start at slot g, advance by G modulo NB; `turn` counts ring turns
+    uint32_t sb = g % NB, turn = g / NB;
+    for (uint32_t ks = g; ks < nk; ks += G) {
       const RawWords<FMT> cur = nxt;
-      if (live && ks + 1 < nk) load_raw<FMT>(wrow, (ks + 1) * TC_BK, nxt);
+      if (live && ks + G < nk) load_raw<FMT>(wrow, (ks + G) * TC_BK, nxt);
       uint4 out[8];
       if (live) {
         convert64<FMT>(cur, ks * TC_BK, out);
@@ -340,50 +391,52 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qgemm_tc_kernel(const __grid_co
         for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
       }
       uint32_t ok = 1;  // one lane per warp polls the barrier
-      if (ks >= S && lane == 0) ok = mbar_wait_bounded(empty_u + s * 8, ((ks / S) - 1) & 1u) ? 1u : 0u;
+      if (turn && lane == 0) ok = mbar_spin_bounded(emptyb_u + sb * 8, (turn - 1) & 1u) ? 1u : 0u;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) {
         if (lane == 0) give_up();
         dead = true;
       }
       if (dead || aborted()) break;
-      uint8_t *tile = smem + s * stage_bytes + MB * TC_TILE_BYTES;
+      uint8_t *tile = b_ring + sb * TC_TILE_BYTES;
 #pragma unroll
       for (int c = 0; c < 8; ++c) st_chunk(tile, r, c, out[c]);
       fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
       __syncwarp();
-      if (lane == 0) mbar_arrive(fullb_u + s * 8);
+      if (lane == 0) mbar_arrive(fullb_u + sb * 8);
+      sb += G;
+      if (sb >= NB) sb -= NB, ++turn;  // G <= NB: at most one wrap
     }
 
-    // ---- epilogue: one TMEM lane (= token row of each block) per thread --------------------
+    // ---- epilogue: one TMEM lane (= weight row) per thread, 32 token columns per item; the
+    // groups share the items round-robin; a warp's stores of one token cover 32 consecutive n ----
     if (!dead && !aborted()) {
       if (!mbar_wait_bounded(accum_u, 0)) {
         give_up();
       } else {
         tc_fence_after();
         const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
-        for (uint32_t mb = 0; mb < MB; ++mb) {
-          const uint32_t m = m0 + mb * TC_BM + q * 32 + lane;
+        const uint32_t nn = n0 + q * 32 + lane;
+        const bool n_ok = nn < p.N;
 #pragma unroll 1
-          for (uint32_t c0 = 0; c0 < TC_BN; c0 += 32) {
-            uint32_t v[32];
-            tmem_ld32(tmem_base + ((q * 32) << 16) + mb * TC_BN + c0, v);
-            if (m < p.M) {
-              float *dst = p.C + (size_t)m * p.ldc + n0 + c0;
-              const float *dsrc = p.fusion_type == CUTB_FUSION_BINARY ? p.D + (size_t)m * p.ldd + n0 + c0 : nullptr;
-              const bool vec = (n0 + c0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-              if (vec && p.fusion_type == CUTB_FUSION_NONE) {
+        for (uint32_t item = g; item < MB * (TC_BT / 32); item += G) {
+          const uint32_t c0 = item * 32;  // token offset = accumulator column
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((q * 32) << 16) + c0, v);
+          const uint32_t mbase = m0 + c0;
+          if (mbase >= p.M) continue;
+          float *dst = p.C + (size_t)mbase * p.ldc + nn;
+          if (p.fusion_type == CUTB_FUSION_NONE) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  reinterpret_cast<float4 *>(dst)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                                   __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-              } else {
+            for (int i = 0; i < 32; ++i)
+              if (n_ok && mbase + i < p.M) dst[(size_t)i * p.ldc] = __uint_as_float(v[i]);
+          } else {
+            const float *dsrc = p.fusion_type == CUTB_FUSION_BINARY ? p.D + (size_t)mbase * p.ldd + nn : nullptr;
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (n0 + c0 + i < p.N)
-                    dst[i] = apply_epilogue(__uint_as_float(v[i]), p.fusion_type, p.fusion_op, dsrc ? dsrc[i] : 0.f);
-              }
-            }
+            for (int i = 0; i < 32; ++i)
+              if (n_ok && mbase + i < p.M)
+                dst[(size_t)i * p.ldc] = apply_epilogue(__uint_as_float(v[i]), p.fusion_type, p.fusion_op,
+                                                        dsrc ? dsrc[(size_t)i * p.ldd] : 0.f);
           }
         }
       }
@@ -429,7 +482,7 @@ int make_tmap_a(CUtensorMap *map, const void *a_f16, uint32_t M, uint32_t K, uin
   }
   const cuuint64_t dims[2] = {K, M};
   const cuuint64_t strides[1] = {row_stride_bytes};
-  const cuuint32_t box[2] = {TC_BK, TC_BM};
+  const cuuint32_t box[2] = {TC_BK, TC_BT};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a_f16), dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -442,8 +495,15 @@ int make_tmap_a(CUtensorMap *map, const void *a_f16, uint32_t M, uint32_t K, uin
   return CUTB_OK;
 }
 
-size_t tc_smem_bytes(uint32_t mb, uint32_t stages) {
-  return 1024 + (size_t)stages * (mb + 1) * TC_TILE_BYTES + (3 * stages + 1) * 8 + 16;
+// Tuning aids: CUTB_TC_GROUPS (converter groups) and CUTB_TC_ISSUERS (MMA issuer threads).
+uint32_t tc_env(const char *name, int lo, int hi, int dflt) {
+  const char *e = getenv(name);
+  const int n = e ? atoi(e) : dflt;
+  return (uint32_t)((n >= lo && n <= hi) ? n : dflt);
+}
+
+size_t tc_smem_bytes(uint32_t mb, uint32_t sa, uint32_t nb) {
+  return 1024 + (size_t)(sa * mb + nb) * TC_TILE_BYTES + (2 * sa + 2 * nb + 1) * 8 + 16;
 }
 
 template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cudaStream_t stream) {
@@ -456,8 +516,8 @@ template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cuda
     CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)di.smem_optin));
     configured_device = dev;
   }
-  dim3 grid((p.N + TC_BN - 1) / TC_BN, (p.M + TC_MAX_MB * TC_BM - 1) / (TC_MAX_MB * TC_BM));
-  qgemm_tc_kernel<FMT><<<grid, TC_THREADS, tc_smem_bytes(p.mb, p.stages), stream>>>(map, p);
+  dim3 grid((p.N + TC_BW - 1) / TC_BW, (p.M + TC_MAX_MB * TC_BT - 1) / (TC_MAX_MB * TC_BT));
+  qgemm_tc_kernel<FMT><<<grid, TC_CTRL_THREADS + 128 * p.groups, tc_smem_bytes(p.mb, p.sa, p.nb), stream>>>(map, p);
   CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;
 }
@@ -487,8 +547,6 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   TcParams p;
   p.W = reinterpret_cast<const uint8_t *>(d.W);
   p.row_bytes = row_bytes(d.format, d.K);
-  p.A = d.A;
-  p.lda = d.lda;
   p.C = d.C;
   p.ldc = d.ldc;
   p.D = d.D;
@@ -499,16 +557,23 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.fusion_type = d.fusion_type;
   p.fusion_op = d.fusion_op;
   p.status = d.status;
-  const uint32_t mblocks = (d.M + TC_BM - 1) / TC_BM;
+  const uint32_t mblocks = (d.M + TC_BT - 1) / TC_BT;
   p.mb = mblocks < TC_MAX_MB ? mblocks : TC_MAX_MB;
-  p.stages = 0;
-  for (uint32_t st = 6; st >= 2; --st)
-    if (tc_smem_bytes(p.mb, st) <= di.smem_optin) {
-      p.stages = st;
+  // two weight slots (one per converter group); the rest of shared memory holds activation
+  // stages in flight
+  p.nb = 2;
+  p.groups = tc_env("CUTB_TC_GROUPS", 1, TC_MAX_GROUPS, 2);
+  if (p.groups > p.nb) p.groups = p.nb;
+  p.issuers = tc_env("CUTB_TC_ISSUERS", 1, 2, 2);
+  if (p.issuers > (p.mb + 1) / 2) p.issuers = (p.mb + 1) / 2;
+  p.sa = 0;
+  for (uint32_t sa = 6; sa >= 2; --sa)
+    if (tc_smem_bytes(p.mb, sa, p.nb) <= di.smem_optin) {
+      p.sa = sa;
       break;
     }
-  if (!p.stages) {
-    set_last_error("qgemm: shared memory too small for a two-stage ring");
+  if (!p.sa) {
+    set_last_error("qgemm: shared memory too small for the tile rings");
     return CUTB_ERR_UNSUPPORTED;
   }
   const void *a16 = d.A;
