@@ -44,7 +44,6 @@
 // returns.
 #include <cuda.h>
 #include <cuda_fp16.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -155,32 +154,55 @@ __device__ __forceinline__ void i8x4_to_h2(uint32_t x, __half2 &h01, __half2 &h2
   h23 = __hsub2(u32_as_h2(p23), k);
 }
 
-// Raw bytes of the 64 weights [k0, k0 + 64) of one row, as aligned 32-bit words:
-// Q8_0 two 34-byte blocks (17 words), Q4_0 two 18-byte blocks (9 words), Q4_K the
-// 16-byte super-block header and the 32 quant bytes of the 64-weight group (12 words).
-// Loading is split from converting so that the next stage's bytes are in flight
-// while this stage is converted.
+// Raw bytes of the 64 weights [k0, k0 + 64) of one row, as 32-bit words: Q8_0 two
+// 34-byte blocks (17 words), Q4_0 two 18-byte blocks (9 words), Q4_K the 16-byte
+// super-block header and the 32 quant bytes of the 64-weight group (12 words).
 template <int FMT> struct RawWords {
   static constexpr int N = FMT == CUTB_Q8_0 ? 17 : (FMT == CUTB_Q4_0 ? 9 : 12);
   uint32_t w[N];
 };
 
-template <int FMT> __device__ __forceinline__ void load_raw(const uint8_t *row, uint32_t k0, RawWords<FMT> &r) {
+// What a converter thread keeps in flight for its next stage: 16-byte loads only.  A
+// thread per weight row means every lane of a load touches its own cache line, so the
+// cost of a stage's loads is their count; the 68 (36) bytes of a Q8_0 (Q4_0) chunk start
+// 0, 4, 8 or 12 bytes into a 16-byte line (k0 / 64 mod 4), and the aligned window of five
+// (three) lines around them costs a third of the 17 (9) word loads.  Rows are a multiple
+// of 16 bytes (K % 256 == 0) and the last chunk of a row ends on its last line, so the
+// window never leaves the row.
+template <int FMT> struct RawWindow {
+  static constexpr int NV = FMT == CUTB_Q8_0 ? 5 : 3;
+  uint4 v[NV];
+};
+
+template <int FMT> __device__ __forceinline__ void load_window(const uint8_t *row, uint32_t k0, RawWindow<FMT> &r) {
   if constexpr (FMT == CUTB_Q4_K) {
     const uint8_t *blk = row + (size_t)(k0 / 256) * 144;
     const uint32_t gq = (k0 % 256) / 64;
-    const uint4 hd = __ldg(reinterpret_cast<const uint4 *>(blk));
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * gq));
-    const uint4 q1 = __ldg(reinterpret_cast<const uint4 *>(blk + 32 + 32 * gq));
-    r.w[0] = hd.x; r.w[1] = hd.y; r.w[2] = hd.z; r.w[3] = hd.w;
-    r.w[4] = q0.x; r.w[5] = q0.y; r.w[6] = q0.z; r.w[7] = q0.w;
-    r.w[8] = q1.x; r.w[9] = q1.y; r.w[10] = q1.z; r.w[11] = q1.w;
+    r.v[0] = __ldg(reinterpret_cast<const uint4 *>(blk));
+    r.v[1] = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * gq));
+    r.v[2] = __ldg(reinterpret_cast<const uint4 *>(blk + 32 + 32 * gq));
   } else {
-    // a pair of 18- or 34-byte blocks starts on a 4-byte boundary (K is a multiple of 64)
-    const uint32_t *p = reinterpret_cast<const uint32_t *>(row + (size_t)(k0 / 32) * block_bytes(FMT));
+    const size_t off = (size_t)(k0 / 32) * block_bytes(FMT);
+    const uint4 *p = reinterpret_cast<const uint4 *>(row + (off & ~(size_t)15));
 #pragma unroll
-    for (int i = 0; i < RawWords<FMT>::N; ++i) r.w[i] = __ldg(p + i);
+    for (int i = 0; i < RawWindow<FMT>::NV; ++i) r.v[i] = __ldg(p + i);
   }
+}
+
+// The chunk's words out of its window; S = (k0 / 64) % 4 is the chunk's word offset in
+// the first line (static, so this is register renaming).
+template <int FMT, int S> __device__ __forceinline__ void window_words(const RawWindow<FMT> &win, RawWords<FMT> &r) {
+  uint32_t flat[RawWindow<FMT>::NV * 4];
+#pragma unroll
+  for (int i = 0; i < RawWindow<FMT>::NV; ++i) {
+    flat[4 * i] = win.v[i].x;
+    flat[4 * i + 1] = win.v[i].y;
+    flat[4 * i + 2] = win.v[i].z;
+    flat[4 * i + 3] = win.v[i].w;
+  }
+  constexpr int s = FMT == CUTB_Q4_K ? 0 : S;
+#pragma unroll
+  for (int i = 0; i < RawWords<FMT>::N; ++i) r.w[i] = flat[i + s];
 }
 
 // Dequantises the 64 weights held in `r` into 8 chunks of 8 halves (k order).
@@ -247,6 +269,21 @@ template <int FMT> __device__ __forceinline__ void convert64(const RawWords<FMT>
 #pragma unroll
   for (int c = 0; c < 8; ++c)
     out[c] = make_uint4(h2_as_u32(h[4 * c]), h2_as_u32(h[4 * c + 1]), h2_as_u32(h[4 * c + 2]), h2_as_u32(h[4 * c + 3]));
+}
+
+template <int FMT> __device__ __forceinline__ void convert_window(const RawWindow<FMT> &win, uint32_t k0, uint4 (&out)[8]) {
+  RawWords<FMT> r;
+  if constexpr (FMT == CUTB_Q4_K) {
+    window_words<FMT, 0>(win, r);
+  } else {
+    switch ((k0 / TC_BK) & 3u) {
+      case 0: window_words<FMT, 0>(win, r); break;
+      case 1: window_words<FMT, 1>(win, r); break;
+      case 2: window_words<FMT, 2>(win, r); break;
+      default: window_words<FMT, 3>(win, r); break;
+    }
+  }
+  convert64<FMT>(r, k0, out);
 }
 
 template <int FMT>
@@ -374,18 +411,18 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
     const bool live = n < p.N;
     const uint8_t *wrow = p.W + (size_t)(live ? n : 0) * p.row_bytes;
     bool dead = false;
-    RawWords<FMT> nxt;
+    RawWindow<FMT> nxt;
 #pragma unroll
-    for (int i = 0; i < RawWords<FMT>::N; ++i) nxt.w[i] = 0;
-    if (live && g < nk) load_raw<FMT>(wrow, g * TC_BK, nxt);
+    for (int i = 0; i < RawWindow<FMT>::NV; ++i) nxt.v[i] = make_uint4(0, 0, 0, 0);
+    if (live && g < nk) load_window<FMT>(wrow, g * TC_BK, nxt);
     // this group's slot sequence: start at slot g, advance by G modulo NB; `turn` counts ring turns
     uint32_t sb = g % NB, turn = g / NB;
     for (uint32_t ks = g; ks < nk; ks += G) {
-      const RawWords<FMT> cur = nxt;
-      if (live && ks + G < nk) load_raw<FMT>(wrow, (ks + G) * TC_BK, nxt);
+      const RawWindow<FMT> cur = nxt;
+      if (live && ks + G < nk) load_window<FMT>(wrow, (ks + G) * TC_BK, nxt);
       uint4 out[8];
       if (live) {
-        convert64<FMT>(cur, ks * TC_BK, out);
+        convert_window<FMT>(cur, ks * TC_BK, out);
       } else {
 #pragma unroll
         for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
@@ -495,13 +532,6 @@ int make_tmap_a(CUtensorMap *map, const void *a_f16, uint32_t M, uint32_t K, uin
   return CUTB_OK;
 }
 
-// Tuning aids: CUTB_TC_GROUPS (converter groups) and CUTB_TC_ISSUERS (MMA issuer threads).
-uint32_t tc_env(const char *name, int lo, int hi, int dflt) {
-  const char *e = getenv(name);
-  const int n = e ? atoi(e) : dflt;
-  return (uint32_t)((n >= lo && n <= hi) ? n : dflt);
-}
-
 size_t tc_smem_bytes(uint32_t mb, uint32_t sa, uint32_t nb) {
   return 1024 + (size_t)(sa * mb + nb) * TC_TILE_BYTES + (2 * sa + 2 * nb + 1) * 8 + 16;
 }
@@ -562,9 +592,9 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   // two weight slots (one per converter group); the rest of shared memory holds activation
   // stages in flight
   p.nb = 2;
-  p.groups = tc_env("CUTB_TC_GROUPS", 1, TC_MAX_GROUPS, 2);
+  p.groups = TC_MAX_GROUPS;
   if (p.groups > p.nb) p.groups = p.nb;
-  p.issuers = tc_env("CUTB_TC_ISSUERS", 1, 2, 2);
+  p.issuers = 2;
   if (p.issuers > (p.mb + 1) / 2) p.issuers = (p.mb + 1) / 2;
   p.sa = 0;
   for (uint32_t sa = 6; sa >= 2; --sa)
