@@ -147,6 +147,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity, 16384u)) return true;
   return false;
 }
+// Probe once, park only if the phase is still open: a parked wait costs a few hundred
+// cycles even when the barrier completed long ago, the probe a few tens.  (Polling in a
+// loop instead of parking was slower in the decode kernel: the pollers of both resident
+// CTAs take issue slots from the warps that compute.)
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_probe_first(uint32_t bar, uint32_t parity) {
+  return mbar_test(bar, parity) || mbar_wait_bounded(bar, parity);
+}
 // Bounded polling wait without parking: for the single threads on a kernel's critical
 // path (an MMA issuer, a copy producer), where the wake-up delay of a parked wait would
 // be paid once per pipeline step.  About a second at ~30 cycles per probe.

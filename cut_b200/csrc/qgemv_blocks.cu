@@ -445,10 +445,16 @@ template <bool AF32> __device__ __forceinline__ float load_act(const void *A, ui
   return __half2float(__ldg(reinterpret_cast<const __half *>(A) + idx));
 }
 
-// Balanced int8 digits of |v| <= 32639: v = 256 * hi + lo, both in [-128, 127].
-__device__ __forceinline__ void digits(int v, int &hi, int &lo) {
-  lo = ((v + 128) & 0xFF) - 128;
-  hi = (v - lo) >> 8;
+// Balanced int8 digits of |v| <= 32639: v = 256 * hi + lo, both in [-128, 127].  Eight values
+// packed four to a word: the low digit is the value's low byte as it stands (read as int8),
+// the high digit is byte 1 of value + 128.
+__device__ __forceinline__ void pack_digits(const int (&v)[8], uint32_t (&hi)[2], uint32_t (&lo)[2]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t a = (uint32_t)v[4 * h], b = (uint32_t)v[4 * h + 1], c = (uint32_t)v[4 * h + 2], d = (uint32_t)v[4 * h + 3];
+    lo[h] = __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+    hi[h] = __byte_perm(__byte_perm(a + 128u, b + 128u, 0x0051), __byte_perm(c + 128u, d + 128u, 0x0051), 0x5410);
+  }
 }
 
 constexpr float GV_QMAX = 32512.f;
@@ -474,7 +480,8 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     const uint32_t id = base + tid;
     const bool live = id < nchunks;
     const uint32_t ct = id & 3, q = id >> 2;
-    const uint32_t m = live ? q % nrows : 0, kb = live ? q / nrows : 0;
+    // (a single activation row is the common decode case: no division on its path)
+    const uint32_t m = (live && nrows > 1) ? q % nrows : 0, kb = live ? (nrows > 1 ? q / nrows : q) : 0;
     const bool even = (FMT == CUTB_Q4_K) || ((kb & 1) == 0);
     float x[8];
     float amax = 0.f;
@@ -494,16 +501,13 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     const float inv = (amax > 0.f && finite) ? GV_QMAX / amax : 0.f;
     float e = finite ? amax * (1.0f / GV_QMAX) : __int_as_float(0x7fc00000);
     int v[8], isum = 0;
-    uint32_t whi[2] = {0, 0}, wlo[2] = {0, 0};
+    uint32_t whi[2], wlo[2];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       v[i] = __float2int_rn(x[i] * inv);
       isum += v[i];
-      int hi, lo;
-      digits(v[i], hi, lo);
-      whi[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
-      wlo[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
     }
+    pack_digits(v, whi, wlo);
     const uint32_t vr = AF32 ? 2 * m : m;
     if constexpr (FMT != CUTB_Q8_0) {
       isum += __shfl_xor_sync(0xffffffffu, isum, 1);
@@ -525,18 +529,15 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     if constexpr (AF32) {
       // second 16-bit level: the residual x - x^ e, at scale e / 65024
       const float e2 = e * (1.0f / (2.f * GV_QMAX)), inv2 = inv * (2.f * GV_QMAX);
-      int isum2 = 0;
-      uint32_t rhi[2] = {0, 0}, rlo[2] = {0, 0};
+      int w[8], isum2 = 0;
+      uint32_t rhi[2], rlo[2];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float r = fmaf(-(float)v[i], e, x[i]);
-        const int w = __float2int_rn(r * inv2);
-        isum2 += w;
-        int hi, lo;
-        digits(w, hi, lo);
-        rhi[i >> 2] |= (uint32_t)(hi & 0xFF) << (8 * (i & 3));
-        rlo[i >> 2] |= (uint32_t)(lo & 0xFF) << (8 * (i & 3));
+        w[i] = __float2int_rn(r * inv2);
+        isum2 += w[i];
       }
+      pack_digits(w, rhi, rlo);
       if constexpr (FMT != CUTB_Q8_0) {
         isum2 += __shfl_xor_sync(0xffffffffu, isum2, 1);
         isum2 += __shfl_xor_sync(0xffffffffu, isum2, 2);
@@ -605,16 +606,22 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
   const uint32_t total_stages = ntiles * cpt;
 
   const uint32_t ring_u = smem_u32(ring);
-  const uint32_t full_u = smem_u32(bars), empty_u = full_u + S * 8;
+  // Q8_0: two barrier pairs per ring slot.  The K halves of a stage (8 granules, 8 warps each)
+  // are copied, consumed and handed back independently, which halves the copy-issue time
+  // inside the release -> refill -> consume loop of a slot.  The 4-bit formats keep whole
+  // rows per copy: their half rows (1152 bytes) cost more in copy efficiency than the
+  // shorter loop wins.
+  constexpr uint32_t HV = FMT == CUTB_Q8_0 ? 2u : 1u;
+  const uint32_t full_u = smem_u32(bars), empty_u = full_u + S * HV * 8;
 
   // Let the next kernel of the stream start its own prologue and weight
   // prefetch as soon as an SM has room for it (programmatic dependent launch).
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (tid == 0) {
-    for (uint32_t s = 0; s < S; ++s) {
+    for (uint32_t s = 0; s < HV * S; ++s) {
       mbar_init(full_u + s * 8, 1);
-      mbar_init(empty_u + s * 8, GV_WARPS);
+      mbar_init(empty_u + s * 8, GV_WARPS / HV);
     }
     fence_mbar_init();
   }
@@ -623,30 +630,35 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
   if (warp == GV_WARPS) {
     // ---- producer warp: whole row segments, one bulk copy per row and stage ----
     bool dead = false;
+    uint32_t tile = 0, c = 0, slot = 0, par = 1u;  // par: parity of the slot's previous use
     for (uint32_t j = 0; j < total_stages && !dead; ++j) {
-      const uint32_t tile = j / cpt, c = j - tile * cpt, slot = j % S;
-      if (j >= S) {
-        const bool ok = mbar_wait_bounded(empty_u + slot * 8, ((j / S) - 1) & 1u);
-        if (!__all_sync(0xffffffffu, ok)) {
-          dead = true;
-          if (lane == 0 && p.status) atomicExch(p.status, (int)CUTB_ERR_TIMEOUT);
-          break;
-        }
-      }
-      const uint32_t gq = gs0 + c * GV_KC;
-      const uint32_t bytes = min((uint32_t)GV_KC, gs1 - gq) * GB;
       const uint32_t row_base = r0 + tile * GV_ROWS;
       const uint32_t valid = min((uint32_t)GV_ROWS, r1 - row_base);
-      const uint32_t bar = full_u + slot * 8;
-      if (lane == 0) mbar_arrive_expect_tx(bar, valid * bytes);
-      __syncwarp();
-      if (lane < valid)
-        bulk_g2s(ring_u + slot * STAGE_BYTES + lane * RS, p.W + (uint64_t)(row_base + lane) * p.row_bytes + (uint64_t)gq * GB,
-                 bytes, bar);
+      for (uint32_t h = 0; h < HV && !dead; ++h) {
+        if (j >= S) {
+          const bool ok = mbar_wait_probe_first(empty_u + (slot * HV + h) * 8, par);
+          if (!__all_sync(0xffffffffu, ok)) {
+            dead = true;
+            if (lane == 0 && p.status) atomicExch(p.status, (int)CUTB_ERR_TIMEOUT);
+            break;
+          }
+        }
+        const uint32_t gq = gs0 + c * GV_KC + h * (GV_KC / HV);
+        const uint32_t bytes = gq < gs1 ? min((uint32_t)(GV_KC / HV), gs1 - gq) * GB : 0u;
+        const uint32_t bar = full_u + (slot * HV + h) * 8;
+        if (lane == 0) mbar_arrive_expect_tx(bar, valid * bytes);  // zero bytes: the phase completes at once
+        __syncwarp();
+        if (bytes && lane < valid)
+          bulk_g2s(ring_u + slot * STAGE_BYTES + lane * RS + h * (GV_KC / HV) * GB,
+                   p.W + (uint64_t)(row_base + lane) * p.row_bytes + (uint64_t)gq * GB, bytes, bar);
+      }
+      if (++slot == S) slot = 0, par ^= 1u;
+      if (++c == cpt) c = 0, ++tile;
     }
     // stay resident until every copy issued here has landed (bounded)
     const uint32_t first = total_stages > S ? total_stages - S : 0;
-    for (uint32_t j = first; j < total_stages; ++j) (void)mbar_wait_bounded(full_u + (j % S) * 8, (j / S) & 1u);
+    for (uint32_t j = first; j < total_stages; ++j)
+      for (uint32_t h = 0; h < HV; ++h) (void)mbar_wait_bounded(full_u + ((j % S) * HV + h) * 8, (j / S) & 1u);
     return;
   }
 
@@ -675,15 +687,16 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
   }
 
   bool dead = false;
+  uint32_t slot = 0, parity = 0;
+  const uint32_t hv = HV == 2 ? warp >> 3 : 0u;  // the K half this warp's granule belongs to
   for (uint32_t tile = 0; tile < ntiles; ++tile) {
     float tot[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
 
     for (uint32_t c = 0; c < cpt; ++c) {
-      const uint32_t j = tile * cpt + c, slot = j % S, parity = (j / S) & 1u;
       if (!dead) {
-        const bool ok = mbar_wait_bounded(full_u + slot * 8, parity);
+        const bool ok = mbar_wait_probe_first(full_u + (slot * HV + hv) * 8, parity);
         if (!__all_sync(0xffffffffu, ok)) {
           dead = true;
           if (lane == 0 && p.status) atomicExch(p.status, (int)CUTB_ERR_TIMEOUT);
@@ -708,7 +721,8 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty_u + slot * 8);
+      if (lane == 0) mbar_arrive(empty_u + (slot * HV + hv) * 8);
+      if (++slot == S) slot = 0, parity ^= 1u;
     }
 
     // meet the other warps' K slices in a fixed order (double-buffered: one barrier per tile)
@@ -787,7 +801,7 @@ size_t gv_smem_bytes(int fmt, bool diag, uint32_t stages, uint32_t nt, uint32_t 
   b += diag ? nblk * nt * 64 + 32 : nblk * ncp * 32;
   b += nblk * nv * 4 * (fmt != CUTB_Q8_0 ? 2 : 1);
   b += (size_t)2 * GV_WARPS * GV_ROWS * nv * 4;
-  b += 2 * stages * 8;
+  b += 4 * stages * 8;  // full / empty barriers of both K halves of every slot
   return b;
 }
 
