@@ -17,8 +17,8 @@ all-gather assembles the full output on every rank once per step ("weak"
 scaling: per-GPU work is fixed).
 
 Besides the device-resident number (`value`) the line carries `e2e` (same
-metric through the host-buffer call: activations copied from pinned host memory
-and results copied back every launch), `roofline` (achieved GB/s of the mat-vec
+metric through the host-buffer calls: every step uploads its activations from
+pinned host memory, runs its mat-vecs and downloads their results), `roofline` (achieved GB/s of the mat-vec
 kernel against the measured HBM copy peak), `cpu_baseline` (the CPU checker
 timed on this host) and the SM clocks sampled during the timed region.
 
@@ -268,7 +268,7 @@ def run_ours(args) -> None:
     import torch.distributed as dist
 
     from cut_b200 import _lib as L
-    from cut_b200 import ops, synth
+    from cut_b200 import ops, synth, tp
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -301,7 +301,24 @@ def run_ours(args) -> None:
         descs.append(d)
         keep.append(k)
 
+    # N > 1, fused exchange: the epilogue of every mat-vec stores its slice into every rank's full
+    # output (peer-mapped), one bounded wait kernel per step orders the stream behind all ranks.
+    # Output slots: one per replica, twice (steps that download results alternate between the halves).
+    fused = world > 1 and args.exchange == "fused"
+    grp = tp.ScatterGroup(BATCH, world * N_ROWS, slots=2 * REPLICAS, device=dev) if fused else None
+    peer_args = [grp.peers(s) for s in range(2 * REPLICAS)] if fused else None
+
+    def scatter_sweep(ds, half):
+        stream = torch.cuda.current_stream().cuda_stream
+        arrivals = 0
+        for r, d in enumerate(ds):
+            arrivals += grp.launch(d, peer_args[half * REPLICAS + r], stream)
+        grp.wait_step(arrivals, stream)
+
     def sweep():
+        if fused:
+            scatter_sweep(descs, 0)
+            return
         for d in descs:
             ops.launch(d)
         if world > 1:
@@ -315,7 +332,18 @@ def run_ours(args) -> None:
     rows = 256
     ref = O.qmatmul_blocks(synth.Q4_0, a_host.numpy().astype(np.float32), base[: rows * (K_COLS // 32) * 18], BATCH,
                            K_COLS, rows)
-    got = C_all[0, :, :rows].cpu().numpy()
+    if fused:
+        got = grp.out[0, :, rank * N_ROWS: rank * N_ROWS + rows].cpu().numpy()
+        # and the assembled output equals what the NCCL all-gather of the plain kernel's slices gives
+        for d in descs:
+            ops.launch(d)
+        dist.all_gather_into_tensor(gathered.view(-1), C_all.view(-1))
+        torch.cuda.synchronize()
+        plain = gathered.permute(1, 2, 0, 3).reshape(REPLICAS, BATCH, world * N_ROWS)
+        if not torch.equal(plain, grp.out[:REPLICAS]) or int(grp.status.item()) != 0:
+            raise SystemExit(f"bench: fused exchange differs from mat-vec + all-gather (status {int(grp.status.item())})")
+    else:
+        got = C_all[0, :, :rows].cpu().numpy()
     rel = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
     if not rel <= 1e-3 or int(status.item()) != 0:
         raise SystemExit(f"bench: kernel output disagrees with the checker (rel-L2 {rel}, status {int(status.item())})")
@@ -390,21 +418,65 @@ def run_ours(args) -> None:
     achieved = bytes_per_launch / (us_per_launch * 1e-6) / 1e9
     peak, peak_kind = measured_peak_gbs()
 
-    # ---- end to end through the host-buffer call: pinned activations in, result out, every launch ----
-    c_host = torch.empty((BATCH, N_ROWS), dtype=torch.float32).pin_memory()
-    e2e_steps = max(1, min(args.steps, 50))
+    # ---- end to end through the host-buffer calls, as the reference's backend is driven: upload
+    # the step's inputs (one activation per mat-vec, pinned host memory), the step's dispatches,
+    # download the step's results; everything inside the timed region, every step ----
+    a_host_all = torch.from_numpy(np.stack([synth.make_activations(BATCH, K_COLS, 77 + r, np.float16)
+                                             for r in range(REPLICAS)])).pin_memory()
+    A_all = torch.empty_like(a_host_all, device=dev)
+    c_host_all = torch.empty((REPLICAS, BATCH, N_ROWS), dtype=torch.float32).pin_memory()
+    e2e_descs = []
+    for r in range(REPLICAS):
+        d, _, k = ops.make_desc(A_all[r], W[r], L.Q4_0, N_ROWS, C_out=C_all[r], status=status)
+        e2e_descs.append(d)
+        keep.append(k)
+    e2e_steps = max(1, min(args.steps, 200))
 
-    def e2e_step():
-        for r, d in enumerate(descs):
-            A.copy_(a_host, non_blocking=True)
+    def e2e_body(half=0):
+        A_all.copy_(a_host_all, non_blocking=True)
+        if fused:
+            # each rank downloads its own slice of the assembled outputs; consecutive steps use
+            # different output halves, so a rank that is one step ahead never writes what another
+            # is still downloading
+            scatter_sweep(e2e_descs, half)
+            c_host_all.copy_(grp.out[half * REPLICAS:(half + 1) * REPLICAS, :, rank * N_ROWS:(rank + 1) * N_ROWS],
+                             non_blocking=True)
+            return
+        for d in e2e_descs:
             ops.launch(d)
-            c_host.copy_(C_all[r], non_blocking=True)
         if world > 1:
             dist.all_gather_into_tensor(gathered.view(-1), C_all.view(-1))
-        torch.cuda.current_stream().synchronize()
+        c_host_all.copy_(C_all, non_blocking=True)
+
+    e2e_body(0)
+    if fused:
+        e2e_body(1)
+    torch.cuda.synchronize()
+    g3 = []
+    try:
+        for half in ((0, 1) if fused else (0,)):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                e2e_body(half)
+            g3.append(g)
+        e2e_launch = [g.replay for g in g3]
+    except Exception:
+        g3, e2e_launch = [], [lambda: e2e_body(0), lambda: e2e_body(1)] if fused else [lambda: e2e_body(0)]
+    e2e_count = [0]
+
+    def e2e_step():
+        e2e_launch[e2e_count[0] % len(e2e_launch)]()
+        e2e_count[0] += 1
+        torch.cuda.current_stream().synchronize()  # the host reads c_host_all here
 
     for _ in range(3):
         e2e_step()
+    # what came back is what the device-resident path computes for the same inputs
+    chk = O.qmatmul_blocks(synth.Q4_0, a_host_all[REPLICAS - 1].numpy().astype(np.float32),
+                           np.roll(base, 18 * 7 * (REPLICAS - 1))[: rows * (K_COLS // 32) * 18], BATCH, K_COLS, rows)
+    rel = float(np.linalg.norm(c_host_all[REPLICAS - 1, :, :rows].numpy() - chk) / np.linalg.norm(chk))
+    if not rel <= 1e-3:
+        raise SystemExit(f"bench: end-to-end output disagrees with the checker (rel-L2 {rel})")
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
@@ -439,7 +511,9 @@ def run_ours(args) -> None:
                 "workload": f"configs[1]: {FMT_NAME} decode mat-vec {N_ROWS}x{K_COLS} (GGUF blocks), fp16 activation, batch {BATCH}",
                 "replicas_per_step": REPLICAS,
                 "l2": f"{REPLICAS} distinct weight tensors cycled ({REPLICAS * base.size / 1e6:.0f} MB > 126 MB L2)",
-                "parallelism": "single GPU" if world == 1 else f"rows sharded over {world} GPUs, NCCL all-gather of output slices per step",
+                "parallelism": "single GPU" if world == 1 else (
+                    f"rows sharded over {world} GPUs, slices exchanged by the mat-vec's peer-store epilogue (NVLink), one bounded wait per step"
+                    if fused else f"rows sharded over {world} GPUs, NCCL all-gather of output slices per step"),
                 "graph": graph is not None,
                 "pct_of_8TBs": 100.0 * value / world / 8000.0,
                 "also_measured": extra,
@@ -447,8 +521,9 @@ def run_ours(args) -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",
                          "us_per_launch": us_per_launch, "algorithmic_bytes_per_launch": bytes_per_launch},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": REPLICAS * BATCH * K_COLS * 2,
-                    "d2h_bytes_per_step": REPLICAS * BATCH * N_ROWS * 4, "steps": e2e_steps},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": world * a_host_all.numel() * 2,
+                    "d2h_bytes_per_step": world * c_host_all.numel() * 4, "steps": e2e_steps,
+                    "ms_per_step": 1e3 * e2e_s / e2e_steps, "graph": bool(g3)},
             "gpu_launches": launches,
             "clocks": clocks,
         }
@@ -459,7 +534,7 @@ def run_ours(args) -> None:
         # Leave without tearing the communicator down: with CUDA graphs that captured a collective
         # still alive, destroy_process_group() was seen to block forever on this stack.  Every rank
         # has finished its work and synchronised; the process exit releases the NCCL resources.
-        del graph, g2
+        del graph, g2, g3
         torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
@@ -475,6 +550,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: slices meet through the mat-vec's own peer-store epilogue, or through an NCCL all-gather")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps == 2000:

@@ -80,6 +80,12 @@ struct GvParams {
   int fusion_type, fusion_op;
   int a_f32;
   int *status;
+  // Row-sharded scatter epilogue (world > 1): instead of C, the output slice is stored into
+  // every rank's full output at column n_off, and every CTA ends by bumping every rank's
+  // arrival counter.  Peer-mapped pointers; plain stores, no multicast.
+  uint32_t world, n_off, ldc_total;
+  float *peer_C[CUTB_MAX_PEERS];
+  unsigned long long *peer_flag[CUTB_MAX_PEERS];
 };
 
 // Shared-memory loads by 32-bit shared address.  Plain loads through an
@@ -767,10 +773,23 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
           p.partial[((size_t)blockIdx.y * p.M + m) * p.N + n] = sum;
         } else {
           const float dv = (p.fusion_type == CUTB_FUSION_BINARY) ? p.D[(size_t)m * p.ldd + n] : 0.f;
-          p.C[(size_t)m * p.ldc + n] = apply_epilogue(sum, p.fusion_type, p.fusion_op, dv);
+          const float out = apply_epilogue(sum, p.fusion_type, p.fusion_op, dv);
+          if (p.world > 1) {
+            const size_t at = (size_t)m * p.ldc_total + p.n_off + n;
+            for (uint32_t q = 0; q < p.world; ++q) p.peer_C[q][at] = out;
+          } else {
+            p.C[(size_t)m * p.ldc + n] = out;
+          }
         }
       }
     }
+  }
+  if (p.world > 1) {
+    // every output of this CTA is stored: make the stores visible system-wide, then count this
+    // CTA in on every rank (release pattern: stores, fence, flag)
+    __threadfence_system();
+    asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
+    if (tid < p.world) atomicAdd_system(p.peer_flag[tid], 1ull);
   }
 }
 
@@ -784,6 +803,29 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *_
   for (uint32_t s = 0; s < ksplit; ++s) sum += partial[((size_t)s * M + m) * N + n];
   const float dv = (ftype == CUTB_FUSION_BINARY) ? D[(size_t)m * ldd + n] : 0.f;
   C[(size_t)m * ldc + n] = apply_epilogue(sum, ftype, fop, dv);
+}
+
+// Stream-ordered wait for the scatter epilogues of all ranks: one thread polls this rank's
+// arrival counter (system-scope acquire loads) until it reaches the target, for at most about a
+// second; on expiry it records CUTB_ERR_TIMEOUT and returns, so the stream and the context stay
+// usable.  Kernels after it in the stream see every rank's slice.
+__global__ void peer_wait_kernel(const unsigned long long *flag, unsigned long long expected, unsigned long long *step_counter,
+                                 int *status) {
+  // with a step counter the target is (number of waits so far) x (arrivals per step): the same
+  // launch can then be replayed from a CUDA graph
+  if (step_counter) expected *= ++*step_counter;
+  const long long t0 = clock64();
+  const long long limit = 2000000000ll;  // cycles: about a second at 2 GHz
+  for (;;) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+    if (v >= expected) return;
+    if (clock64() - t0 > limit) {
+      if (status) atomicExch(status, (int)CUTB_ERR_TIMEOUT);
+      return;
+    }
+    __nanosleep(200);
+  }
 }
 
 // ---- host side ---------------------------------------------------------------
@@ -907,7 +949,7 @@ uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d) {
   return pl.ksplit > 1 ? (uint64_t)pl.ksplit * d.M * d.N * sizeof(float) : 0;
 }
 
-int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
+int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const cutb_peer_scatter *sc, uint32_t *arrivals) {
   DeviceInfo di;
   if (int rc = get_device_info(&di)) return rc;
   GvPlan pl;
@@ -937,6 +979,23 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.fusion_op = d.fusion_op;
   p.a_f32 = af32;
   p.status = d.status;
+  p.world = 0;
+  p.n_off = p.ldc_total = 0;
+  for (int q = 0; q < CUTB_MAX_PEERS; ++q) p.peer_C[q] = nullptr, p.peer_flag[q] = nullptr;
+  if (sc) {
+    if (pl.ksplit > 1) {
+      set_last_error("qgemv scatter: this shape splits K (%u ways); the scatter epilogue needs the whole K in one CTA", pl.ksplit);
+      return CUTB_ERR_UNSUPPORTED;
+    }
+    p.world = sc->world;
+    p.n_off = sc->n_offset;
+    p.ldc_total = sc->ldc_total;
+    for (uint32_t q = 0; q < sc->world; ++q) {
+      p.peer_C[q] = sc->C_peers[q];
+      p.peer_flag[q] = reinterpret_cast<unsigned long long *>(sc->flag_peers[q]);
+    }
+    if (arrivals) *arrivals = pl.grid_x;
+  }
   if (pl.ksplit > 1) {
     const uint64_t need = (uint64_t)pl.ksplit * d.M * d.N * sizeof(float);
     if (!d.workspace || d.workspace_bytes < need) {
@@ -959,6 +1018,13 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
                                                                  d.fusion_type, d.fusion_op);
     CUTB_CUDA_TRY(cudaGetLastError());
   }
+  return CUTB_OK;
+}
+
+int peer_wait_launch(const uint64_t *flag, uint64_t expected, uint64_t *step_counter, int *status, cudaStream_t stream) {
+  peer_wait_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<const unsigned long long *>(flag), expected,
+                                        reinterpret_cast<unsigned long long *>(step_counter), status);
+  CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;
 }
 
@@ -1016,6 +1082,6 @@ extern "C" int cutb_qmatmul_decode_noalloc(const cutb_qmatmul_desc *desc, void *
   d.variant = CUTB_VARIANT_GEMV_MMA;
   d.workspace = scratch_of_device[dev];
   d.workspace_bytes = kNoAllocScratchFloats * sizeof(float);
-  return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream));
+  return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr);
 }
 

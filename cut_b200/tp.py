@@ -2,17 +2,23 @@
 
 Output rows (N) are independent, so rank r of g owns GGUF rows
 [r * N / g, (r + 1) * N / g): one contiguous byte range of the tensor, which
-never moves.  Activations are replicated; every rank computes its slice of C
-and one all-gather over NCCL (NVLink / NVSwitch) assembles the full output.
+never moves.  Activations are replicated; every rank computes its slice of C.
+The slices meet either through one NCCL all-gather (`all_gather_rows`) or inside the
+mat-vec kernel itself (`ScatterGroup`): its epilogue stores the slice into every rank's
+full output through peer-mapped pointers over NVLink and counts itself in on every rank's
+arrival counter; a one-thread wait kernel then orders the consumers behind all ranks.
 The reference has no counterpart (its only multi-device mode is a layer split
 with a host bounce, runtime/Runtime.cpp:267-284); the split follows the plan
 of keeping N / g a multiple of the kernels' 16-row tile.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
+from . import _lib as L
 from . import synth
 
 ROW_TILE = 16
@@ -52,3 +58,79 @@ def all_gather_rows(c_local: torch.Tensor, N: int, group=None) -> torch.Tensor:
     for r, (lo, hi) in enumerate(sizes):
         out[:, lo:hi] = recv[r, :, : hi - lo]
     return out
+
+
+def _share(t: torch.Tensor):
+    """CUDA IPC handle of the tensor's storage (what torch.multiprocessing sends between processes)."""
+    return t.untyped_storage()._share_cuda_()
+
+
+def _open(handle) -> torch.UntypedStorage:
+    return torch.UntypedStorage._new_shared_cuda(*handle)
+
+
+class ScatterGroup:
+    """Per-rank state of the fused exchange: `slots` full outputs [M, N] and one arrival counter,
+    each mapped into every other rank's address space (CUDA IPC; no multicast object is created).
+
+    Use: `launch(desc, peers(slot))` for every mat-vec of a step, then `wait_step(total arrivals)`
+    once; afterwards `out[slot]` holds every rank's slice.  The ranks must pass a step
+    boundary of their own (e.g. `dist.barrier()`) before a slot is written again.
+    """
+
+    def __init__(self, M: int, N: int, slots: int, device: torch.device, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if not 2 <= self.world <= L.MAX_PEERS:
+            raise ValueError(f"ScatterGroup needs 2..{L.MAX_PEERS} ranks, got {self.world}")
+        self.M, self.N, self.slots = M, N, slots
+        self.lo, self.hi = shard_rows(N, self.rank, self.world)
+        # one allocation per rank: outputs first, the counter behind them on a 256-byte boundary
+        out_bytes = (slots * M * N * 4 + 255) // 256 * 256
+        self.buf = torch.zeros(out_bytes + 256, dtype=torch.uint8, device=device)
+        self.out = self.buf[: slots * M * N * 4].view(torch.float32).view(slots, M, N)
+        self.flag = self.buf[out_bytes: out_bytes + 8].view(torch.int64)
+        torch.cuda.synchronize(device)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, _share(self.buf), group=group)
+        self._peer_storages = []
+        self.peer_base = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.peer_base.append(self.buf.data_ptr())
+                continue
+            st = _open(h)
+            self._peer_storages.append(st)
+            remote = torch.empty(0, dtype=torch.uint8, device=st.device).set_(st)
+            # a first device-to-device copy makes torch enable peer access between the two GPUs
+            probe = torch.empty(8, dtype=torch.uint8, device=device)
+            probe.copy_(remote[out_bytes: out_bytes + 8])
+            self.peer_base.append(remote.data_ptr())
+        torch.cuda.synchronize(device)
+        self._flag_off = out_bytes
+        self.steps = torch.zeros(1, dtype=torch.int64, device=device)  # waits made so far (device side)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.barrier(group=group)
+
+    def peers(self, slot: int) -> "L.PeerScatter":
+        ps = L.PeerScatter()
+        ps.world, ps.rank, ps.ldc_total, ps.n_offset = self.world, self.rank, self.N, self.lo
+        for r in range(self.world):
+            ps.C_peers[r] = self.peer_base[r] + slot * self.M * self.N * 4
+            ps.flag_peers[r] = self.peer_base[r] + self._flag_off
+        return ps
+
+    def launch(self, desc, peers, stream_ptr: int) -> int:
+        """One row-shard mat-vec whose epilogue scatters into `peers` (from `peers(slot)`); returns the
+        arrivals the launch adds to every rank's counter once all ranks have made the same launch."""
+        arrivals = C.c_uint32(0)
+        L.check(L.lib().cutb_qmatmul_scatter(C.byref(desc), C.byref(peers), C.byref(arrivals), stream_ptr))
+        return self.world * arrivals.value
+
+    def wait_step(self, arrivals_per_step: int, stream_ptr: int) -> None:
+        """Orders the stream behind the current step's launches of every rank (bounded).  Every step
+        must add the same `arrivals_per_step`; the step count lives on the device, so the launch can
+        be captured once and replayed."""
+        L.check(L.lib().cutb_peer_wait(self.flag.data_ptr(), arrivals_per_step, self.steps.data_ptr(),
+                                       self.status.data_ptr(), stream_ptr))

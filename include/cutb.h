@@ -145,6 +145,45 @@ CUTB_API int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream);
 CUTB_API int cutb_qmatmul_decode_noalloc(const cutb_qmatmul_desc *desc, void *stream);
 
 /*
+ * Row-sharded decode mat-vec over several GPUs with the exchange step fused into the
+ * kernel: rank r owns weight rows [n_offset, n_offset + desc->N) of a tensor of N_total rows,
+ * computes its slice of the output and stores it into EVERY rank's full output
+ * C_full[M, ldc_total] through peer-mapped device pointers (plain stores over NVLink; no
+ * multicast object is involved), then counts its CTAs in on every rank's arrival counter
+ * (system-scope release).  It replaces "mat-vec, then all-gather of the slices".  The
+ * reference has no counterpart (it offers a pipeline split with a host bounce only).
+ *
+ *   world        ranks (2 .. CUTB_MAX_PEERS); rank = this rank's index
+ *   C_peers[q]   rank q's full output as mapped into THIS process (own buffer at [rank])
+ *   flag_peers[q] rank q's arrival counter (one uint64, zero before the first launch, never reset)
+ *   ldc_total    row stride of the full outputs (elements); n_offset: first column of the slice
+ *
+ * desc->C is not written.  The shape must take the mat-vec variant with the whole K in one
+ * CTA (cutb_qmatmul_workspace_bytes(desc) == 0), else CUTB_ERR_UNSUPPORTED.  *arrivals
+ * receives the count this launch adds to every rank's counter; with identical shapes on
+ * every rank a counter reaches launches * world * arrivals.
+ *
+ * cutb_peer_wait enqueues a one-thread kernel that polls this rank's counter until it reaches
+ * the target or about a second has passed (then *status = CUTB_ERR_TIMEOUT; nothing hangs).
+ * With step_counter == NULL the target is `expected`; otherwise the kernel increments
+ * *step_counter (a device uint64, zero at the start) and the target is that count times
+ * `expected` (= arrivals per step), so one captured launch serves every replay of a CUDA graph.
+ * Work enqueued after it on the stream sees every rank's slice.  Before a buffer is reused for
+ * the next exchange every rank must have consumed it (an application-level step boundary, or
+ * double buffering).
+ */
+#define CUTB_MAX_PEERS 8
+typedef struct cutb_peer_scatter {
+  uint32_t world, rank;
+  uint32_t ldc_total, n_offset;
+  float *C_peers[CUTB_MAX_PEERS];
+  uint64_t *flag_peers[CUTB_MAX_PEERS];
+} cutb_peer_scatter;
+CUTB_API int cutb_qmatmul_scatter(const cutb_qmatmul_desc *desc, const cutb_peer_scatter *peers, uint32_t *arrivals,
+                                  void *stream);
+CUTB_API int cutb_peer_wait(const uint64_t *flag, uint64_t expected, uint64_t *step_counter, int *status, void *stream);
+
+/*
  * Raw GGUF blocks -> fp32 [rows, cols] with row stride ldo (elements).
  * Replaces DequantOpNode's dispatch (operators/impl/dequant/DequantOp.cpp:7-61,
  * DequantQ4K.cu:6-50); Q8_0 and Q4_0 follow the loader's CPU dequantisers

@@ -41,6 +41,7 @@ def test_descriptor_layout_matches_header():
         fields += [first] + names[1:]
     assert fields == [f[0] for f in L.QMatmulDesc._fields_]
     assert C.sizeof(L.QMatmulDesc) == 152
+    assert C.sizeof(L.PeerScatter) == 16 + 2 * 8 * L.MAX_PEERS
 
 
 def test_validation_needs_no_device():
