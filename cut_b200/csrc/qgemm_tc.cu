@@ -17,8 +17,8 @@
 // this kernel.  Each pair of 128-token blocks accumulates in its own 256 columns
 // of tensor memory.
 //   warp 0      allocates the TMEM columns; one lane issues the MMAs of every K stage
-//               and commits the stage's activation slot and weight slot to their
-//               "empty" barriers.  Its instruction stream is the kernel's critical
+//               and commits them to the stage's "consumed" barrier, which frees both
+//               the activation stage and the weight slot.  Its instruction stream is the kernel's critical
 //               path (a lone thread retires an instruction every ~6 cycles), so the
 //               loop keeps ring indices and descriptor words incrementally and
 //               waits by polling, not by parking;
@@ -294,26 +294,25 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
   const uint32_t SA = p.sa, NB = p.nb, MB = p.mb, NI = p.issuers;
   const uint32_t a_stage_bytes = MB * TC_TILE_BYTES;
   uint8_t *a_ring = smem, *b_ring = smem + SA * a_stage_bytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(b_ring + NB * TC_TILE_BYTES);  // fullA[SA] emptyA[SA] fullB[NB] emptyB[NB] accum
+  // fullA[SA] fullB[NB] consumed[NC] accum.  One "consumed" barrier per K stage in a ring of
+  // NC = SA + NB: a single tcgen05.commit per issuer and stage frees both the activation
+  // stage and the weight slot (the copy producer waits for stage ks - SA, a converter for
+  // stage ks - NB); NC > SA, NB keeps a barrier from being reused before both have seen it.
+  const uint32_t NC = SA + NB;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(b_ring + NB * TC_TILE_BYTES);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * SA + 2 * NB + 1);
   uint32_t *abort_flag = tmem_slot + 1;
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t n0 = blockIdx.x * TC_BW, m0 = blockIdx.y * (TC_MAX_MB * TC_BT);
   const uint32_t nk = p.K / TC_BK;
-  const uint32_t fulla_u = smem_u32(bars), emptya_u = fulla_u + SA * 8, fullb_u = emptya_u + SA * 8, emptyb_u = fullb_u + NB * 8,
-                 accum_u = emptyb_u + NB * 8;
+  const uint32_t fulla_u = smem_u32(bars), fullb_u = fulla_u + SA * 8, cons_u = fullb_u + NB * 8, accum_u = cons_u + NC * 8;
   const uint32_t tmem_cols = MB == 1 ? 128u : (MB == 2 ? 256u : 512u);
 
   if (tid == 0) {
-    for (uint32_t s = 0; s < SA; ++s) {
-      mbar_init(fulla_u + s * 8, 1);    // the TMA lane's arrive.expect_tx
-      mbar_init(emptya_u + s * 8, NI);  // one tcgen05.commit per issuer and stage
-    }
-    for (uint32_t s = 0; s < NB; ++s) {
-      mbar_init(fullb_u + s * 8, 4);    // one arrival per converter warp of the owning group
-      mbar_init(emptyb_u + s * 8, NI);  // one tcgen05.commit per issuer and stage
-    }
+    for (uint32_t s = 0; s < SA; ++s) mbar_init(fulla_u + s * 8, 1);  // the TMA lane's arrive.expect_tx
+    for (uint32_t s = 0; s < NB; ++s) mbar_init(fullb_u + s * 8, 4);  // one arrival per converter warp of the owning group
+    for (uint32_t s = 0; s < NC; ++s) mbar_init(cons_u + s * 8, NI);  // one tcgen05.commit per issuer and stage
     mbar_init(accum_u, NI);
     *abort_flag = 0;
     fence_mbar_init();
@@ -344,7 +343,7 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
       const uint32_t desc_hi = (uint32_t)(proto >> 32), lo0 = (uint32_t)proto;
       const uint32_t w_lo0 = lo0 + ((smem_u32(b_ring) & 0x3FFFFu) >> 4), t_lo0 = lo0 + ((smem_u32(a_ring) & 0x3FFFFu) >> 4);
       const uint32_t idesc256 = umma_idesc_f16(TC_BW, 256), idesc128 = umma_idesc_f16(TC_BW, 128);
-      uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
+      uint32_t sa = 0, pa = 0, sb = 0, pb = 0, sc = 0;
       bool dead = false;
       for (uint32_t ks = 0; ks < nk; ++ks) {
         if (!mbar_spin_bounded(fullb_u + sb * 8, pb) || !mbar_spin_bounded(fulla_u + sa * 8, pa)) {
@@ -364,10 +363,10 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
           umma_f16(d, w_lo + 4, tl + 4, desc_hi, idesc, 1);
           umma_f16(d, w_lo + 6, tl + 6, desc_hi, idesc, 1);
         }
-        umma_commit(emptya_u + sa * 8);  // frees the activation stage when these MMAs have read it
-        umma_commit(emptyb_u + sb * 8);  // and the weight slot
+        umma_commit(cons_u + sc * 8);  // the stage is consumed when these MMAs have read it
         if (++sa == SA) sa = 0, pa ^= 1u;
         if (++sb == NB) sb = 0, pb ^= 1u;
+        if (++sc == NC) sc = 0;
       }
       if (!dead) umma_commit(accum_u);  // this issuer's accumulators are complete
     }
@@ -375,13 +374,17 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
   } else if (warp == 1) {
     // ---- TMA producer: the activation blocks of every stage ------------------------------
     if (lane == 0) {
-      uint32_t sa = 0, pa = 1u;  // parity of the slot's previous use (first turn: nothing to wait for)
+      uint32_t sa = 0, pa = 1u;  // parity of the slot's previous fill (used when draining)
+      uint32_t sc = 0, pc = 0;   // consumed barrier of stage ks - SA
       uint32_t issued = 0;
       const uint32_t a_base = smem_u32(a_ring);
       for (uint32_t ks = 0; ks < nk; ++ks) {
-        if (ks >= SA && !mbar_spin_bounded(emptya_u + sa * 8, pa)) {
-          give_up();
-          break;
+        if (ks >= SA) {
+          if (!mbar_spin_bounded(cons_u + sc * 8, pc)) {
+            give_up();
+            break;
+          }
+          if (++sc == NC) sc = 0, pc ^= 1u;
         }
         if (aborted()) break;
         const uint32_t bar = fulla_u + sa * 8, dst = a_base + sa * a_stage_bytes;
@@ -404,8 +407,7 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
     __syncwarp();
   } else if (warp >= 4) {
     // ---- converters: one weight row per thread; group g owns K stages g, g + G, ... and keeps
-    // the raw bytes of its next stage in flight while it converts the current one.  G <= NB:
-    // a group further ahead than one ring turn would alias the parity of the slot's barrier ----
+    // the raw bytes of its next stage in flight while it converts the current one (G <= NB) ----
     const uint32_t G = (blockDim.x - TC_CTRL_THREADS) >> 7;
     const uint32_t ct = tid - TC_CTRL_THREADS, r = ct & 127u, g = ct >> 7, n = n0 + r;
     const bool live = n < p.N;
@@ -415,8 +417,10 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
 #pragma unroll
     for (int i = 0; i < RawWindow<FMT>::NV; ++i) nxt.v[i] = make_uint4(0, 0, 0, 0);
     if (live && g < nk) load_window<FMT>(wrow, g * TC_BK, nxt);
-    // this group's slot sequence: start at slot g, advance by G modulo NB; `turn` counts ring turns
-    uint32_t sb = g % NB, turn = g / NB;
+    // this group's slot sequence: start at slot g, advance by G modulo NB
+    uint32_t sb = g % NB;
+    uint32_t sc = 0, pc = 0;  // consumed barrier of stage ks - NB, once ks >= NB
+    bool sc_set = false;
     for (uint32_t ks = g; ks < nk; ks += G) {
       const RawWindow<FMT> cur = nxt;
       if (live && ks + G < nk) load_window<FMT>(wrow, (ks + G) * TC_BK, nxt);
@@ -428,7 +432,12 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
         for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
       }
       uint32_t ok = 1;  // one lane per warp polls the barrier
-      if (turn && lane == 0) ok = mbar_spin_bounded(emptyb_u + sb * 8, (turn - 1) & 1u) ? 1u : 0u;
+      if (ks >= NB) {
+        if (!sc_set) sc = ks - NB, sc_set = true;  // first wait: stage ks - NB < G <= NB < NC
+        if (lane == 0) ok = mbar_spin_bounded(cons_u + sc * 8, pc) ? 1u : 0u;
+        sc += G;
+        if (sc >= NC) sc -= NC, pc ^= 1u;
+      }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) {
         if (lane == 0) give_up();
@@ -442,7 +451,7 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
       __syncwarp();
       if (lane == 0) mbar_arrive(fullb_u + sb * 8);
       sb += G;
-      if (sb >= NB) sb -= NB, ++turn;  // G <= NB: at most one wrap
+      if (sb >= NB) sb -= NB;  // G <= NB: at most one wrap
     }
 
     // ---- epilogue: one TMEM lane (= weight row) per thread, 32 token columns per item; the
@@ -533,7 +542,7 @@ int make_tmap_a(CUtensorMap *map, const void *a_f16, uint32_t M, uint32_t K, uin
 }
 
 size_t tc_smem_bytes(uint32_t mb, uint32_t sa, uint32_t nb) {
-  return 1024 + (size_t)(sa * mb + nb) * TC_TILE_BYTES + (2 * sa + 2 * nb + 1) * 8 + 16;
+  return 1024 + (size_t)(sa * mb + nb) * TC_TILE_BYTES + (2 * sa + 2 * nb + 1) * 8 + 16;  // fullA, fullB, consumed[sa + nb], accum
 }
 
 template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cudaStream_t stream) {

@@ -332,7 +332,10 @@ def test_affine_q4_planes_from_q4k():
 # ---- prefill GEMM on the tcgen05 tensor cores ----
 @pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("dtype", [np.float16, np.float32])
-@pytest.mark.parametrize("M,K,N", [(17, 256, 128), (64, 1024, 136), (128, 512, 1000), (200, 768, 264), (512, 1024, 384)])
+@pytest.mark.parametrize("M,K,N", [(17, 256, 128), (64, 1024, 136), (128, 512, 1000), (200, 768, 264), (512, 1024, 384),
+                                   (300, 512, 256),   # three token blocks: one 256-token pair and one 128-token MMA
+                                   (600, 512, 130),   # two CTAs along the tokens, the second mostly zero-filled
+                                   (1100, 256, 72)])  # three CTAs along the tokens, one partial weight tile
 def test_gemm_tc_matches_checker(fmt, dtype, M, K, N):
     from gpu_util import rel_l2, run_blocks
 
