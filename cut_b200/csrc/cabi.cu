@@ -183,17 +183,24 @@ int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
   }
 }
 
-int cutb_qmatmul_scatter(const cutb_qmatmul_desc *desc, const cutb_peer_scatter *peers, uint32_t *arrivals, void *stream) {
-  if (int rc = validate(desc)) return rc;
+namespace {
+int check_peers(const cutb_peer_scatter *peers, const char *who) {
   if (!peers || peers->world < 2 || peers->world > CUTB_MAX_PEERS || peers->rank >= peers->world) {
-    set_last_error("qmatmul_scatter: world must be 2..%d and rank < world", CUTB_MAX_PEERS);
+    set_last_error("%s: world must be 2..%d and rank < world", who, CUTB_MAX_PEERS);
     return CUTB_ERR_INVALID;
   }
   for (uint32_t q = 0; q < peers->world; ++q)
     if (!peers->C_peers[q] || !peers->flag_peers[q] || reinterpret_cast<uintptr_t>(peers->flag_peers[q]) % 8 != 0) {
-      set_last_error("qmatmul_scatter: rank %u's output or counter pointer is null or misaligned", q);
+      set_last_error("%s: rank %u's output or counter pointer is null or misaligned", who, q);
       return CUTB_ERR_INVALID;
     }
+  return CUTB_OK;
+}
+}  // namespace
+
+int cutb_qmatmul_scatter(const cutb_qmatmul_desc *desc, const cutb_peer_scatter *peers, void *stream) {
+  if (int rc = validate(desc)) return rc;
+  if (int rc = check_peers(peers, "qmatmul_scatter")) return rc;
   if ((uint64_t)peers->n_offset + desc->N > peers->ldc_total) {
     set_last_error("qmatmul_scatter: slice [%u, %u) exceeds the row stride %u of the full output", peers->n_offset,
                    peers->n_offset + desc->N, peers->ldc_total);
@@ -205,15 +212,16 @@ int cutb_qmatmul_scatter(const cutb_qmatmul_desc *desc, const cutb_peer_scatter 
     set_last_error("qmatmul_scatter: needs GGUF blocks, K %% 256 == 0, 16-byte aligned W and M <= 16 (fp16) / 8 (fp32)");
     return CUTB_ERR_UNSUPPORTED;
   }
-  return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream), peers, arrivals);
+  return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream), peers);
 }
 
-int cutb_peer_wait(const uint64_t *flag, uint64_t expected, uint64_t *step_counter, int *status, void *stream) {
-  if (!flag || reinterpret_cast<uintptr_t>(flag) % 8 != 0 || reinterpret_cast<uintptr_t>(step_counter) % 8 != 0) {
-    set_last_error("peer_wait: null or misaligned counter");
+int cutb_peer_exchange(const cutb_peer_scatter *peers, uint64_t *step_counter, int *status, void *stream) {
+  if (int rc = check_peers(peers, "peer_exchange")) return rc;
+  if (!step_counter || reinterpret_cast<uintptr_t>(step_counter) % 8 != 0) {
+    set_last_error("peer_exchange: null or misaligned step counter");
     return CUTB_ERR_INVALID;
   }
-  return peer_wait_launch(flag, expected, step_counter, status, reinterpret_cast<cudaStream_t>(stream));
+  return peer_exchange_launch(*peers, step_counter, status, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,

@@ -13,11 +13,10 @@ int check_qmatmul_desc(const cutb_qmatmul_desc *d);
 // Decode mat-vec over GGUF blocks (bulk-copy ring + warp MMA).
 bool qgemv_blocks_supported(const cutb_qmatmul_desc &d);
 uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d);
-// `scatter` (optional): store the output slice into every rank's full output instead of d.C and
-// count the CTAs in on every rank's arrival counter; *arrivals = arrivals this launch adds per rank.
-int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const cutb_peer_scatter *scatter = nullptr,
-                        uint32_t *arrivals = nullptr);
-int peer_wait_launch(const uint64_t *flag, uint64_t expected, uint64_t *step_counter, int *status, cudaStream_t stream);
+// `scatter` (optional): store the output slice into every rank's full output instead of d.C.
+int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const cutb_peer_scatter *scatter = nullptr);
+// Publishes this rank's peer stores of the step and waits (bounded) for every rank's.
+int peer_exchange_launch(const cutb_peer_scatter &peers, uint64_t *step_counter, int *status, cudaStream_t stream);
 
 // Any-shape SIMT matmul over GGUF blocks or the reference's [K,N] planes.
 int qmatmul_generic_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);

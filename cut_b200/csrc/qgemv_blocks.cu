@@ -81,11 +81,10 @@ struct GvParams {
   int a_f32;
   int *status;
   // Row-sharded scatter epilogue (world > 1): instead of C, the output slice is stored into
-  // every rank's full output at column n_off, and every CTA ends by bumping every rank's
-  // arrival counter.  Peer-mapped pointers; plain stores, no multicast.
+  // every rank's full output at column n_off.  Peer-mapped pointers; plain stores, no
+  // multicast, no fence here: the step's exchange kernel publishes them.
   uint32_t world, n_off, ldc_total;
   float *peer_C[CUTB_MAX_PEERS];
-  unsigned long long *peer_flag[CUTB_MAX_PEERS];
 };
 
 // Shared-memory loads by 32-bit shared address.  Plain loads through an
@@ -784,47 +783,66 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
       }
     }
   }
-  if (p.world > 1) {
-    // every output of this CTA is stored: make the stores visible system-wide, then count this
-    // CTA in on every rank (release pattern: stores, fence, flag)
-    __threadfence_system();
-    asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
-    if (tid < p.world) atomicAdd_system(p.peer_flag[tid], 1ull);
+}
+
+// Destination of a row-sharded scatter (world > 1) as the kernels see it.
+struct ScatterArgs {
+  uint32_t world, n_off, ldc_total;
+  float *peer_C[CUTB_MAX_PEERS];
+};
+
+// Fixed-order sum of the K-split partials followed by the fused epilogue; with a scatter
+// destination the result goes to every rank's full output.
+__global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ C, const float *__restrict__ D,
+                                     uint32_t M, uint32_t N, uint32_t ldc, uint32_t ldd, uint32_t ksplit, int ftype, int fop,
+                                     const ScatterArgs sc) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < M * N) {
+    const uint32_t m = i / N, n = i % N;
+    float sum = 0.f;
+    for (uint32_t s = 0; s < ksplit; ++s) sum += partial[((size_t)s * M + m) * N + n];
+    const float dv = (ftype == CUTB_FUSION_BINARY) ? D[(size_t)m * ldd + n] : 0.f;
+    const float out = apply_epilogue(sum, ftype, fop, dv);
+    if (sc.world > 1) {
+      const size_t at = (size_t)m * sc.ldc_total + sc.n_off + n;
+      for (uint32_t q = 0; q < sc.world; ++q) sc.peer_C[q][at] = out;
+    } else {
+      C[(size_t)m * ldc + n] = out;
+    }
   }
 }
 
-// Fixed-order sum of the K-split partials followed by the fused epilogue.
-__global__ void splitk_reduce_kernel(const float *__restrict__ partial, float *__restrict__ C, const float *__restrict__ D,
-                                     uint32_t M, uint32_t N, uint32_t ldc, uint32_t ldd, uint32_t ksplit, int ftype, int fop) {
-  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= M * N) return;
-  const uint32_t m = i / N, n = i % N;
-  float sum = 0.f;
-  for (uint32_t s = 0; s < ksplit; ++s) sum += partial[((size_t)s * M + m) * N + n];
-  const float dv = (ftype == CUTB_FUSION_BINARY) ? D[(size_t)m * ldd + n] : 0.f;
-  C[(size_t)m * ldc + n] = apply_epilogue(sum, ftype, fop, dv);
-}
-
-// Stream-ordered wait for the scatter epilogues of all ranks: one thread polls this rank's
-// arrival counter (system-scope acquire loads) until it reaches the target, for at most about a
-// second; on expiry it records CUTB_ERR_TIMEOUT and returns, so the stream and the context stay
-// usable.  Kernels after it in the stream see every rank's slice.
-__global__ void peer_wait_kernel(const unsigned long long *flag, unsigned long long expected, unsigned long long *step_counter,
-                                 int *status) {
-  // with a step counter the target is (number of waits so far) x (arrivals per step): the same
-  // launch can then be replayed from a CUDA graph
-  if (step_counter) expected *= ++*step_counter;
+// The step boundary of the fused exchange, one small block per rank and step.  Everything the
+// earlier kernels of this stream stored into peer memory happened before this kernel (stream
+// order); a system-scope fence followed by one system-scope add on every rank's arrival counter
+// publishes it.  Then one thread polls this rank's own counter (system-scope acquire loads) until
+// all `world` ranks have signalled this step, for at most about a second; on expiry it records
+// CUTB_ERR_TIMEOUT and returns, so the stream and the context stay usable.  The step number lives
+// on the device (*step_counter), so the same launch can be replayed from a CUDA graph.  Kernels
+// after it in the stream see every rank's slice.
+struct ExchangeArgs {
+  uint32_t world, rank;
+  unsigned long long *flag[CUTB_MAX_PEERS];
+};
+__global__ void peer_exchange_kernel(const ExchangeArgs a, unsigned long long *step_counter, int *status) {
+  __shared__ unsigned long long step;
+  if (threadIdx.x == 0) step = ++*step_counter;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < a.world) atomicAdd_system(a.flag[threadIdx.x], 1ull);
+  if (threadIdx.x != 0) return;
+  const unsigned long long expected = step * a.world;
   const long long t0 = clock64();
   const long long limit = 2000000000ll;  // cycles: about a second at 2 GHz
   for (;;) {
     unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(a.flag[a.rank]) : "memory");
     if (v >= expected) return;
     if (clock64() - t0 > limit) {
       if (status) atomicExch(status, (int)CUTB_ERR_TIMEOUT);
       return;
     }
-    __nanosleep(200);
+    __nanosleep(100);
   }
 }
 
@@ -949,7 +967,7 @@ uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d) {
   return pl.ksplit > 1 ? (uint64_t)pl.ksplit * d.M * d.N * sizeof(float) : 0;
 }
 
-int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const cutb_peer_scatter *sc, uint32_t *arrivals) {
+int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const cutb_peer_scatter *sc) {
   DeviceInfo di;
   if (int rc = get_device_info(&di)) return rc;
   GvPlan pl;
@@ -981,20 +999,23 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
   p.status = d.status;
   p.world = 0;
   p.n_off = p.ldc_total = 0;
-  for (int q = 0; q < CUTB_MAX_PEERS; ++q) p.peer_C[q] = nullptr, p.peer_flag[q] = nullptr;
+  for (int q = 0; q < CUTB_MAX_PEERS; ++q) p.peer_C[q] = nullptr;
+  ScatterArgs sa;
+  sa.world = 0;
+  sa.n_off = sa.ldc_total = 0;
+  for (int q = 0; q < CUTB_MAX_PEERS; ++q) sa.peer_C[q] = nullptr;
+  const uint32_t reduce_blocks = (d.M * d.N + 255) / 256;
   if (sc) {
-    if (pl.ksplit > 1) {
-      set_last_error("qgemv scatter: this shape splits K (%u ways); the scatter epilogue needs the whole K in one CTA", pl.ksplit);
-      return CUTB_ERR_UNSUPPORTED;
+    sa.world = sc->world;
+    sa.n_off = sc->n_offset;
+    sa.ldc_total = sc->ldc_total;
+    for (uint32_t q = 0; q < sc->world; ++q) sa.peer_C[q] = sc->C_peers[q];
+    if (pl.ksplit == 1) {  // the mat-vec kernel scatters; with split K its reduction kernel does
+      p.world = sa.world;
+      p.n_off = sa.n_off;
+      p.ldc_total = sa.ldc_total;
+      for (uint32_t q = 0; q < sa.world; ++q) p.peer_C[q] = sa.peer_C[q];
     }
-    p.world = sc->world;
-    p.n_off = sc->n_offset;
-    p.ldc_total = sc->ldc_total;
-    for (uint32_t q = 0; q < sc->world; ++q) {
-      p.peer_C[q] = sc->C_peers[q];
-      p.peer_flag[q] = reinterpret_cast<unsigned long long *>(sc->flag_peers[q]);
-    }
-    if (arrivals) *arrivals = pl.grid_x;
   }
   if (pl.ksplit > 1) {
     const uint64_t need = (uint64_t)pl.ksplit * d.M * d.N * sizeof(float);
@@ -1013,17 +1034,20 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
   }
   if (rc != CUTB_OK) return rc;
   if (pl.ksplit > 1) {
-    const uint32_t total = d.M * d.N;
-    splitk_reduce_kernel<<<(total + 255) / 256, 256, 0, stream>>>(p.partial, d.C, d.D, d.M, d.N, d.ldc, d.ldd, pl.ksplit,
-                                                                 d.fusion_type, d.fusion_op);
+    splitk_reduce_kernel<<<reduce_blocks, 256, 0, stream>>>(p.partial, d.C, d.D, d.M, d.N, d.ldc, d.ldd, pl.ksplit, d.fusion_type,
+                                                           d.fusion_op, sa);
     CUTB_CUDA_TRY(cudaGetLastError());
   }
   return CUTB_OK;
 }
 
-int peer_wait_launch(const uint64_t *flag, uint64_t expected, uint64_t *step_counter, int *status, cudaStream_t stream) {
-  peer_wait_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<const unsigned long long *>(flag), expected,
-                                        reinterpret_cast<unsigned long long *>(step_counter), status);
+int peer_exchange_launch(const cutb_peer_scatter &peers, uint64_t *step_counter, int *status, cudaStream_t stream) {
+  ExchangeArgs a;
+  a.world = peers.world;
+  a.rank = peers.rank;
+  for (int q = 0; q < CUTB_MAX_PEERS; ++q)
+    a.flag[q] = q < (int)peers.world ? reinterpret_cast<unsigned long long *>(peers.flag_peers[q]) : nullptr;
+  peer_exchange_kernel<<<1, 32, 0, stream>>>(a, reinterpret_cast<unsigned long long *>(step_counter), status);
   CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;
 }
@@ -1082,6 +1106,6 @@ extern "C" int cutb_qmatmul_decode_noalloc(const cutb_qmatmul_desc *desc, void *
   d.variant = CUTB_VARIANT_GEMV_MMA;
   d.workspace = scratch_of_device[dev];
   d.workspace_bytes = kNoAllocScratchFloats * sizeof(float);
-  return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr);
+  return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream), nullptr);
 }
 

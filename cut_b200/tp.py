@@ -5,8 +5,9 @@ Output rows (N) are independent, so rank r of g owns GGUF rows
 never moves.  Activations are replicated; every rank computes its slice of C.
 The slices meet either through one NCCL all-gather (`all_gather_rows`) or inside the
 mat-vec kernel itself (`ScatterGroup`): its epilogue stores the slice into every rank's
-full output through peer-mapped pointers over NVLink and counts itself in on every rank's
-arrival counter; a one-thread wait kernel then orders the consumers behind all ranks.
+full output through peer-mapped pointers over NVLink; once per step a small exchange kernel
+publishes the stores (system-scope fence, one add on every rank's arrival counter) and waits,
+bounded, until every rank has done the same.
 The reference has no counterpart (its only multi-device mode is a layer split
 with a host bounce, runtime/Runtime.cpp:267-284); the split follows the plan
 of keeping N / g a multiple of the kernels' 16-row tile.
@@ -65,16 +66,22 @@ def _share(t: torch.Tensor):
     return t.untyped_storage()._share_cuda_()
 
 
-def _open(handle) -> torch.UntypedStorage:
-    return torch.UntypedStorage._new_shared_cuda(*handle)
+def _open(handle, local_device: int) -> torch.UntypedStorage:
+    """Maps a peer's allocation into THIS rank's device context.  The handle is opened with the
+    local device current (first field of the tuple), so the runtime enables peer access from the
+    local GPU to the owner lazily (cudaIpcMemLazyEnablePeerAccess) and the returned address is one
+    the local GPU's kernels may dereference.  (Opened under the owner's device index, as torch
+    does when it rebuilds a shared tensor, the mapping belongs to that device's context and a
+    local kernel faults on it unless peer access local -> owner was enabled by other means.)"""
+    return torch.UntypedStorage._new_shared_cuda(local_device, *handle[1:])
 
 
 class ScatterGroup:
     """Per-rank state of the fused exchange: `slots` full outputs [M, N] and one arrival counter,
     each mapped into every other rank's address space (CUDA IPC; no multicast object is created).
 
-    Use: `launch(desc, peers(slot))` for every mat-vec of a step, then `wait_step(total arrivals)`
-    once; afterwards `out[slot]` holds every rank's slice.  The ranks must pass a step
+    Use: `launch(desc, peers(slot))` for every mat-vec of a step, then `exchange()` once;
+    afterwards `out[slot]` holds every rank's slice.  The ranks must pass a step
     boundary of their own (e.g. `dist.barrier()`) before a slot is written again.
     """
 
@@ -100,17 +107,16 @@ class ScatterGroup:
             if r == self.rank:
                 self.peer_base.append(self.buf.data_ptr())
                 continue
-            st = _open(h)
+            if not torch.cuda.can_device_access_peer(device.index, h[0]):
+                raise RuntimeError(f"GPU {device.index} cannot access GPU {h[0]} as a peer")
+            st = _open(h, device.index)
             self._peer_storages.append(st)
-            remote = torch.empty(0, dtype=torch.uint8, device=st.device).set_(st)
-            # a first device-to-device copy makes torch enable peer access between the two GPUs
-            probe = torch.empty(8, dtype=torch.uint8, device=device)
-            probe.copy_(remote[out_bytes: out_bytes + 8])
-            self.peer_base.append(remote.data_ptr())
+            self.peer_base.append(st.data_ptr())
         torch.cuda.synchronize(device)
         self._flag_off = out_bytes
         self.steps = torch.zeros(1, dtype=torch.int64, device=device)  # waits made so far (device side)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._any_peers = self.peers(0)
         dist.barrier(group=group)
 
     def peers(self, slot: int) -> "L.PeerScatter":
@@ -121,16 +127,12 @@ class ScatterGroup:
             ps.flag_peers[r] = self.peer_base[r] + self._flag_off
         return ps
 
-    def launch(self, desc, peers, stream_ptr: int) -> int:
-        """One row-shard mat-vec whose epilogue scatters into `peers` (from `peers(slot)`); returns the
-        arrivals the launch adds to every rank's counter once all ranks have made the same launch."""
-        arrivals = C.c_uint32(0)
-        L.check(L.lib().cutb_qmatmul_scatter(C.byref(desc), C.byref(peers), C.byref(arrivals), stream_ptr))
-        return self.world * arrivals.value
+    def launch(self, desc, peers, stream_ptr: int) -> None:
+        """One row-shard mat-vec whose epilogue stores its slice into `peers` (from `peers(slot)`)."""
+        L.check(L.lib().cutb_qmatmul_scatter(C.byref(desc), C.byref(peers), stream_ptr))
 
-    def wait_step(self, arrivals_per_step: int, stream_ptr: int) -> None:
-        """Orders the stream behind the current step's launches of every rank (bounded).  Every step
-        must add the same `arrivals_per_step`; the step count lives on the device, so the launch can
-        be captured once and replayed."""
-        L.check(L.lib().cutb_peer_wait(self.flag.data_ptr(), arrivals_per_step, self.steps.data_ptr(),
-                                       self.status.data_ptr(), stream_ptr))
+    def exchange(self, stream_ptr: int) -> None:
+        """Step boundary: publishes this rank's stores of the step and orders the stream behind every
+        rank's (bounded).  The step count lives on the device, so the launch can be captured once
+        and replayed."""
+        L.check(L.lib().cutb_peer_exchange(C.byref(self._any_peers), self.steps.data_ptr(), self.status.data_ptr(), stream_ptr))

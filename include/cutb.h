@@ -149,28 +149,28 @@ CUTB_API int cutb_qmatmul_decode_noalloc(const cutb_qmatmul_desc *desc, void *st
  * kernel: rank r owns weight rows [n_offset, n_offset + desc->N) of a tensor of N_total rows,
  * computes its slice of the output and stores it into EVERY rank's full output
  * C_full[M, ldc_total] through peer-mapped device pointers (plain stores over NVLink; no
- * multicast object is involved), then counts its CTAs in on every rank's arrival counter
- * (system-scope release).  It replaces "mat-vec, then all-gather of the slices".  The
+ * multicast object is involved).  It replaces "mat-vec, then all-gather of the slices".  The
  * reference has no counterpart (it offers a pipeline split with a host bounce only).
  *
- *   world        ranks (2 .. CUTB_MAX_PEERS); rank = this rank's index
- *   C_peers[q]   rank q's full output as mapped into THIS process (own buffer at [rank])
- *   flag_peers[q] rank q's arrival counter (one uint64, zero before the first launch, never reset)
- *   ldc_total    row stride of the full outputs (elements); n_offset: first column of the slice
+ *   world         ranks (2 .. CUTB_MAX_PEERS); rank = this rank's index
+ *   C_peers[q]    rank q's full output as mapped into THIS process (own buffer at [rank])
+ *   flag_peers[q] rank q's arrival counter (one uint64, zero at the start, never reset)
+ *   ldc_total     row stride of the full outputs (elements); n_offset: first column of the slice
  *
- * desc->C is not written.  The shape must take the mat-vec variant with the whole K in one
- * CTA (cutb_qmatmul_workspace_bytes(desc) == 0), else CUTB_ERR_UNSUPPORTED.  *arrivals
- * receives the count this launch adds to every rank's counter; with identical shapes on
- * every rank a counter reaches launches * world * arrivals.
+ * cutb_qmatmul_scatter: desc->C is not written.  The shape must take the mat-vec variant
+ * (M <= 16 fp16 / 8 fp32 rows, K % 256 == 0), else CUTB_ERR_UNSUPPORTED; shapes that split K need
+ * the workspace of cutb_qmatmul_workspace_bytes(desc) as usual (their reduction kernel scatters).
+ * The stores are not yet published when it returns or when its kernel ends.
  *
- * cutb_peer_wait enqueues a one-thread kernel that polls this rank's counter until it reaches
- * the target or about a second has passed (then *status = CUTB_ERR_TIMEOUT; nothing hangs).
- * With step_counter == NULL the target is `expected`; otherwise the kernel increments
- * *step_counter (a device uint64, zero at the start) and the target is that count times
- * `expected` (= arrivals per step), so one captured launch serves every replay of a CUDA graph.
- * Work enqueued after it on the stream sees every rank's slice.  Before a buffer is reused for
- * the next exchange every rank must have consumed it (an application-level step boundary, or
- * double buffering).
+ * cutb_peer_exchange is the step boundary, called by every rank once per step after the step's
+ * scatter launches (any number of them, C_peers may differ per launch; only flag_peers, world
+ * and rank are read here): a small kernel issues a system-scope fence and adds one to every
+ * rank's counter, then polls this rank's own counter until all ranks have signalled the step or
+ * about a second has passed (then *status = CUTB_ERR_TIMEOUT; nothing hangs).  The step number is
+ * kept in *step_counter (a device uint64, zero at the start), so one captured launch serves
+ * every replay of a CUDA graph.  Work enqueued after it on the stream sees every rank's slices.
+ * Before an output buffer is scattered into again every rank must have consumed it (double
+ * buffering by step parity is enough: no rank can be more than one step ahead of another).
  */
 #define CUTB_MAX_PEERS 8
 typedef struct cutb_peer_scatter {
@@ -179,9 +179,8 @@ typedef struct cutb_peer_scatter {
   float *C_peers[CUTB_MAX_PEERS];
   uint64_t *flag_peers[CUTB_MAX_PEERS];
 } cutb_peer_scatter;
-CUTB_API int cutb_qmatmul_scatter(const cutb_qmatmul_desc *desc, const cutb_peer_scatter *peers, uint32_t *arrivals,
-                                  void *stream);
-CUTB_API int cutb_peer_wait(const uint64_t *flag, uint64_t expected, uint64_t *step_counter, int *status, void *stream);
+CUTB_API int cutb_qmatmul_scatter(const cutb_qmatmul_desc *desc, const cutb_peer_scatter *peers, void *stream);
+CUTB_API int cutb_peer_exchange(const cutb_peer_scatter *peers, uint64_t *step_counter, int *status, void *stream);
 
 /*
  * Raw GGUF blocks -> fp32 [rows, cols] with row stride ldo (elements).

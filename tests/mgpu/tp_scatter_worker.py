@@ -2,7 +2,7 @@
 
 Every rank owns an equal slice of the weight rows, runs the mat-vec whose epilogue scatters the slice
 into every rank's full output, waits on its arrival counter and checks the assembled output against
-(a) the plain single-GPU kernel on the whole matrix, bit for bit, and (b) the CPU checker.
+(a) the plain single-GPU kernel run on every slice, bit for bit, and (b) the CPU checker.
 """
 import os
 import sys
@@ -27,8 +27,11 @@ def main() -> int:
     dist.init_process_group("nccl", device_id=dev)
     stream = torch.cuda.current_stream().cuda_stream
     failures = []
-    for fmt, M, adt in ((L.Q4_0, 1, np.float16), (L.Q4_K, 2, np.float16), (L.Q8_0, 1, np.float32)):
-        K, N = 4096, 1024 * world
+    # 4096 rows per rank: whole K per CTA, the mat-vec kernel scatters; 512 rows per rank: K is
+    # split and the reduction kernel scatters
+    for fmt, M, adt, rows_per_rank in ((L.Q4_0, 1, np.float16, 4096), (L.Q4_K, 2, np.float16, 4096),
+                                       (L.Q8_0, 1, np.float32, 2048), (L.Q4_0, 1, np.float16, 512)):
+        K, N = 4096, rows_per_rank * world
         Wfull = synth.make_weights(fmt, N, K, seed=5)  # same on every rank
         A_h = synth.make_activations(M, K, 9, adt)
         lo, hi = tp.shard_rows(N, rank, world)
@@ -37,17 +40,24 @@ def main() -> int:
         A = torch.from_numpy(A_h).to(dev)
         grp = tp.ScatterGroup(M, N, slots=2, device=dev)
         c_dummy = torch.empty((M, hi - lo), dtype=torch.float32, device=dev)
-        d, _, keep = ops.make_desc(A, W_local, fmt, hi - lo, C_out=c_dummy, status=grp.status)
-        # whole matrix on this GPU through the plain entry point
-        ref_dev = ops.qmatmul(A, torch.from_numpy(Wfull).to(dev), fmt, N).cpu().numpy()
+        d, _, keep = ops.make_desc(A, W_local, fmt, hi - lo, C_out=c_dummy, status=grp.status, variant=L.VARIANT_GEMV_MMA)
+        need = ops.workspace_bytes(d)
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        if need:
+            d.workspace, d.workspace_bytes = ws.data_ptr(), need
+        # every rank's slice on this GPU through the plain entry point (same shape, hence the same
+        # launch plan and summation order as the rank that owns the slice)
+        ref_dev = np.concatenate(
+            [ops.qmatmul(A, torch.from_numpy(Wfull[a * rb: b * rb].copy()).to(dev), fmt, b - a).cpu().numpy()
+             for a, b in (tp.shard_rows(N, r, world) for r in range(world))], axis=1)
         ref_cpu = O.qmatmul_blocks(fmt, A_h.astype(np.float32), Wfull, M, K, N)
         for step in range(3):
             slot = step & 1
             grp.out[slot].zero_()
             torch.cuda.synchronize()
             dist.barrier()  # step boundary: nobody still reads or clears the slot
-            arrivals = grp.launch(d, grp.peers(slot), stream)
-            grp.wait_step(arrivals, stream)
+            grp.launch(d, grp.peers(slot), stream)
+            grp.exchange(stream)
             torch.cuda.synchronize()
             got = grp.out[slot].cpu().numpy()
             if int(grp.status.item()) != 0:
@@ -67,8 +77,11 @@ def main() -> int:
     if rank == 0:
         print("TP_SCATTER_OK" if int(flag.item()) == 0 else "TP_SCATTER_FAILED", flush=True)
     dist.barrier()
-    dist.destroy_process_group()
-    return 0 if int(flag.item()) == 0 else 1
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    # leave without tearing down the communicator and the peer mappings (interpreter shutdown
+    # with peer-mapped storages alive crashed on this stack); every rank is past the barrier
+    os._exit(0 if int(flag.item()) == 0 else 1)
 
 
 if __name__ == "__main__":
