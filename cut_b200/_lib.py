@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libcutb.so")
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT = range(6)
-Q8_0, Q4_0, Q4_K = 0, 1, 2
+Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 4, 5  # the last three: cutb_dequant only
 F32, F16 = 0, 1
 LAYOUT_GGUF_BLOCKS, LAYOUT_KN_PLANES = 0, 1
 FUSION_NONE, FUSION_UNARY, FUSION_BINARY = 0, 1, 2

@@ -226,7 +226,7 @@ int cutb_peer_exchange(const cutb_peer_scatter *peers, uint64_t *step_counter, i
 
 int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                  void *stream) {
-  if (format < CUTB_Q8_0 || format > CUTB_Q4_K) {
+  if (format < CUTB_Q8_0 || format > CUTB_BF16) {
     set_last_error("dequant: unknown format %d", format);
     return CUTB_ERR_INVALID;
   }

@@ -23,9 +23,11 @@ int cuda_fail(cudaError_t e, const char *what);
 
 // Block geometry of the three GGUF formats the path covers
 // (interface/loader/gguf/gguf_types.hpp:109-150).
-__host__ __device__ constexpr uint32_t block_elems(int fmt) { return fmt == CUTB_Q4_K ? 256u : 32u; }
+__host__ __device__ constexpr uint32_t block_elems(int fmt) {
+  return (fmt == CUTB_Q4_K || fmt == CUTB_Q5_K || fmt == CUTB_Q6_K) ? 256u : (fmt == CUTB_BF16 ? 1u : 32u);
+}
 __host__ __device__ constexpr uint32_t block_bytes(int fmt) {
-  return fmt == CUTB_Q8_0 ? 34u : (fmt == CUTB_Q4_0 ? 18u : 144u);
+  return fmt == CUTB_Q8_0 ? 34u : fmt == CUTB_Q4_0 ? 18u : fmt == CUTB_Q4_K ? 144u : fmt == CUTB_Q5_K ? 176u : fmt == CUTB_Q6_K ? 210u : 2u;
 }
 // Bytes of 256 consecutive weights of one row: the copy granule of the decode
 // kernel (a multiple of 16 bytes in all three formats).
@@ -188,15 +190,6 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
-}
-
-// ---- warp-level MMA m16n8k16, fp16 x fp16 -> fp32 ---------------------------
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }

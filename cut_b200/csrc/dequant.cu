@@ -1,8 +1,11 @@
 // Raw GGUF blocks -> fp32 [rows, ldo], bit-exact with the reference.
 //
-// Replaces DequantQ4K.cu (operators/impl/dequant/DequantQ4K.cu:6-50, helpers
-// DequantCommon.cuh:16-70) and adds the Q8_0 / Q4_0 cases the reference only
-// has on the CPU (interface/loader/gguf/gguf_reader.cpp:541-572, 826-850).
+// Replaces the reference's dequant kernels (operators/impl/dequant/DequantQ4K.cu:6-50,
+// DequantQ5K.cu, DequantQ6K.cu, DequantBF16.cu, helpers DequantCommon.cuh:16-70) and
+// adds the Q8_0 / Q4_0 cases the reference only has on the CPU
+// (interface/loader/gguf/gguf_reader.cpp:541-572, 826-850).  Every format follows the
+// loader's dequantiser operation by operation (each product and the subtract rounded on
+// their own), so the output equals its float32 bits.
 //
 // The op is write-bound (4 bytes out per 0.56-1.06 bytes in).  Each thread
 // decodes 8 consecutive weights of one block -- the block header is read once
@@ -28,10 +31,57 @@ __device__ __forceinline__ uint32_t ldg32u(const uint8_t *p) {
   return ldg8(p) | (ldg8(p + 1) << 8) | (ldg8(p + 2) << 16) | (ldg8(p + 3) << 24);
 }
 
-// 8 weights [8*oct, 8*oct+8) of the 32-weight (Q8_0, Q4_0) or 256-weight (Q4_K)
-// block at `b`.
-template <int FMT> __device__ __forceinline__ void decode8(const uint8_t *b, uint32_t oct, float (&v)[8]) {
-  if constexpr (FMT == CUTB_Q8_0) {
+// 6-bit (scale, min) of sub-block j from the 12 packed bytes of a Q4_K / Q5_K super-block
+// (gguf_reader.cpp:668-676).
+__device__ __forceinline__ void scale_min_k4(const uint8_t *sc, uint32_t j, uint32_t &s, uint32_t &m) {
+  if (j < 4) {
+    s = ldg8(sc + j) & 63;
+    m = ldg8(sc + j + 4) & 63;
+  } else {
+    s = (ldg8(sc + j + 4) & 0xF) | ((ldg8(sc + j - 4) >> 6) << 4);
+    m = (ldg8(sc + j + 4) >> 4) | ((ldg8(sc + j) >> 6) << 4);
+  }
+}
+
+// 8 weights [8*oct, 8*oct+8) of the 32-weight (Q8_0, Q4_0) or 256-weight (Q4_K, Q5_K,
+// Q6_K) block at `b`; for BF16 `b` points at the first of `valid` (<= 8) elements.
+template <int FMT> __device__ __forceinline__ void decode8(const uint8_t *b, uint32_t oct, float (&v)[8], uint32_t valid) {
+  if constexpr (FMT == CUTB_BF16) {
+    // the upper half of a float32 (gguf_reader.cpp:860-870, DequantBF16.cu:20-28)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (uint32_t)i < valid ? __uint_as_float(ldg16(b + 2 * i) << 16) : 0.f;
+  } else if constexpr (FMT == CUTB_Q5_K) {
+    // gguf_reader.cpp:726-772: group g of 64 = sub-blocks 2g (low nibbles) and 2g + 1 (high
+    // nibbles) of the group's 32 ql bytes; bit j of qh[l] is element l's fifth bit in sub-block j
+    const uint32_t j = oct >> 2, l0 = (oct & 3) * 8;
+    const uint32_t hdr = ldg32u(b);
+    const float d = h2f_bits(hdr & 0xFFFF), dmin = h2f_bits(hdr >> 16);
+    uint32_t s, m;
+    scale_min_k4(b + 4, j, s, m);
+    const float d1 = __fmul_rn(d, (float)s), dm = __fmul_rn(dmin, (float)m);
+    const uint8_t *ql = b + 48 + (j >> 1) * 32 + l0, *qh = b + 16 + l0;
+    const uint32_t sh = (j & 1) * 4;
+    const uint32_t w[2] = {ldg32u(ql), ldg32u(ql + 4)}, h[2] = {ldg32u(qh), ldg32u(qh + 4)};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t q = ((w[i >> 2] >> (8 * (i & 3) + sh)) & 0xF) + (((h[i >> 2] >> (8 * (i & 3) + j)) & 1) << 4);
+      v[i] = __fsub_rn(__fmul_rn(d1, (float)q), dm);
+    }
+  } else if constexpr (FMT == CUTB_Q6_K) {
+    // gguf_reader.cpp:774-824: half (128 elements), run r of 32, element l of the run
+    const uint32_t half = oct >> 4, r = (oct >> 2) & 3, l0 = (oct & 3) * 8;
+    const float d = h2f_bits(ldg16(b + 208));
+    const uint8_t *ql = b + 64 * half + 32 * (r & 1) + l0, *qh = b + 128 + 32 * half + l0;
+    const int sc = (int)(int8_t)ldg8(b + 192 + 8 * half + 2 * r + (l0 >> 4));
+    const float ds = __fmul_rn(d, (float)sc);
+    const uint32_t sh = (r >> 1) * 4;
+    const uint32_t w[2] = {ldg32u(ql), ldg32u(ql + 4)}, h[2] = {ldg32u(qh), ldg32u(qh + 4)};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int q = (int)(((w[i >> 2] >> (8 * (i & 3) + sh)) & 0xF) | (((h[i >> 2] >> (8 * (i & 3) + 2 * r)) & 3) << 4)) - 32;
+      v[i] = __fmul_rn(ds, (float)q);
+    }
+  } else if constexpr (FMT == CUTB_Q8_0) {
     const float d = h2f_bits(ldg16(b));
     const uint32_t w0 = ldg32u(b + 2 + 8 * oct), w1 = ldg32u(b + 6 + 8 * oct);
 #pragma unroll
@@ -53,15 +103,8 @@ template <int FMT> __device__ __forceinline__ void decode8(const uint8_t *b, uin
     const uint32_t j = oct >> 2, l0 = (oct & 3) * 8;  // sub-block, first element inside it
     const uint32_t hdr = __ldg(reinterpret_cast<const uint32_t *>(b));
     const float d = h2f_bits(hdr & 0xFFFF), dmin = h2f_bits(hdr >> 16);
-    const uint8_t *sc = b + 4;
     uint32_t s, m;
-    if (j < 4) {
-      s = ldg8(sc + j) & 63;
-      m = ldg8(sc + j + 4) & 63;
-    } else {
-      s = (ldg8(sc + j + 4) & 0xF) | ((ldg8(sc + j - 4) >> 6) << 4);
-      m = (ldg8(sc + j + 4) >> 4) | ((ldg8(sc + j) >> 6) << 4);
-    }
+    scale_min_k4(b + 4, j, s, m);
     // value = (d * sc) * q - dmin * m, each product rounded on its own
     // (gguf_reader.cpp:700-718, DequantQ4K.cu:39-46); both products are exact.
     const float d1 = __fmul_rn(d, (float)s), dm = __fmul_rn(dmin, (float)m);
@@ -87,7 +130,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
     const uint32_t k = o * 8;
     const uint8_t *b = raw + (uint64_t)r * row_bytes_ + (uint64_t)(k / BE) * BB;
     float v[8];
-    decode8<FMT>(b, (k % BE) / 8, v);
+    decode8<FMT>(b, (k % BE) / 8, v, cols - k);
     float *dst = out + (uint64_t)r * ldo + k;
     if (vec_ok && k + 8 <= cols) {
       reinterpret_cast<float4 *>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
@@ -118,10 +161,22 @@ int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint3
     set_last_error("dequant: Q4_K blocks must be 4-byte aligned");
     return CUTB_ERR_INVALID;
   }
+  if ((format == CUTB_Q5_K || format == CUTB_Q6_K) && cols % 256 != 0) {
+    set_last_error("dequant: Q5_K / Q6_K rows are whole 256-weight super-blocks, cols = %u", cols);
+    return CUTB_ERR_INVALID;
+  }
+  if (format == CUTB_BF16 && (reinterpret_cast<uintptr_t>(raw) % 2 != 0)) {
+    set_last_error("dequant: BF16 input must be 2-byte aligned");
+    return CUTB_ERR_INVALID;
+  }
+  const unsigned g = (unsigned)blocks;
   switch (format) {
-    case CUTB_Q8_0: dequant_kernel<CUTB_Q8_0><<<(unsigned)blocks, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
-    case CUTB_Q4_0: dequant_kernel<CUTB_Q4_0><<<(unsigned)blocks, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
-    default: dequant_kernel<CUTB_Q4_K><<<(unsigned)blocks, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    case CUTB_Q8_0: dequant_kernel<CUTB_Q8_0><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    case CUTB_Q4_0: dequant_kernel<CUTB_Q4_0><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    case CUTB_Q5_K: dequant_kernel<CUTB_Q5_K><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    case CUTB_Q6_K: dequant_kernel<CUTB_Q6_K><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    case CUTB_BF16: dequant_kernel<CUTB_BF16><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    default: dequant_kernel<CUTB_Q4_K><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
   }
   CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;

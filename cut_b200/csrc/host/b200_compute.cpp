@@ -64,6 +64,9 @@ int cutbFormat(uint32_t f) {
     case DequantFormat::Q8_0: return CUTB_Q8_0;
     case DequantFormat::Q4_0: return CUTB_Q4_0;
     case DequantFormat::Q4_K: return CUTB_Q4_K;
+    case DequantFormat::Q5_K: return CUTB_Q5_K;  // dequant only; the matmul entry point rejects them
+    case DequantFormat::Q6_K: return CUTB_Q6_K;
+    case DequantFormat::BF16: return CUTB_BF16;
     default: throw std::runtime_error("B200Compute: block format has no kernel");
   }
 }

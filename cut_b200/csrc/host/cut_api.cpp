@@ -412,7 +412,11 @@ size_t DequantOpNode::shaderKey() const {
 }
 
 std::optional<std::vector<uint32_t>> DequantOpNode::shader() const {
-  if (!isBlockFormat(format_)) return std::nullopt;  // BF16 / Q5_K / Q6_K: no kernel in this backend
+  switch (format_) {  // the reference's DequantFormat set plus the two 32-weight block formats
+    case DequantFormat::BF16: case DequantFormat::Q4_K: case DequantFormat::Q5_K: case DequantFormat::Q6_K:
+    case DequantFormat::Q8_0: case DequantFormat::Q4_0: break;
+    default: return std::nullopt;
+  }
   KernelDesc d;
   d.op = Dequantize;
   d.format = (uint32_t)format_;

@@ -869,8 +869,10 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
   const bool af32 = d.a_dtype == CUTB_F32;
   pl->nvr = af32 ? 2 * d.M : d.M;
   if (pl->nvr == 0 || pl->nvr > 16) return false;
-  // one or two virtual rows: the diagonal variant (nt = virtual rows); otherwise 4 virtual rows per MMA n-tile
-  pl->diag = pl->nvr <= 2;
+  // one virtual row: the diagonal variant (nt = virtual rows); otherwise 4 virtual rows per MMA n-tile
+  // measured: with two virtual rows the diagonal variant only pays for two fp16 rows of Q8_0
+  // (elsewhere its second row costs registers and spills: Q4_K 13.4 -> 10.5 us, fp32 rows 10 % faster shared-k)
+  pl->diag = pl->nvr == 1 || (pl->nvr == 2 && !af32 && d.format == CUTB_Q8_0);
   pl->nt = pl->diag ? pl->nvr : (pl->nvr <= 4 ? 1 : (pl->nvr <= 8 ? 2 : 4));
   const uint32_t ncols = 2 * pl->nvr;
   pl->ncp = ncols < pl->nt * 8 ? ncols + 1 : ncols;

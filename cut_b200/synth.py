@@ -11,6 +11,12 @@ benchmark configurations:
         element j in the low and element j + 16 in the high nibble, U[0, 15]
   Q4_K  144-byte super-blocks of 256: f16 d, f16 dmin = |N(0, 0.01)|, 12 bytes
         of packed 6-bit (scale, min) pairs ~ U[0, 63], 128 bytes of nibbles
+  Q5_K  176-byte super-blocks: the Q4_K header, 32 bytes of fifth bits, 128
+        bytes of nibbles (gguf_reader.cpp:726-772); uniform random bits
+  Q6_K  210-byte super-blocks: 128 bytes of low nibbles, 64 bytes of 2-bit high
+        parts, 16 int8 scales ~ U[-128, 127], f16 d (gguf_reader.cpp:774-824)
+  BF16  the upper halves of N(0, 1) float32 values, some replaced by
+        infinities, NaNs, zeros and subnormals
 
 fp16 conversions round to nearest even and keep subnormals (numpy's astype),
 which matters: a third of the Q8_0 scales above are fp16 subnormals.
@@ -19,10 +25,10 @@ from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_0, Q4_K = 0, 1, 2
-FMT_NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_K: "Q4_K"}
-BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_K: 144}
+Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 4, 5  # the last three: dequant operator only
+FMT_NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", BF16: "BF16"}
+BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, BF16: 1}
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_K: 144, Q5_K: 176, Q6_K: 210, BF16: 2}
 
 
 def row_bytes(fmt: int, K: int) -> int:
@@ -74,6 +80,25 @@ def make_weights(fmt: int, N: int, K: int, seed: int) -> np.ndarray:
         blocks[:, 2:4] = dmin.view(np.uint8).reshape(nb, 2)
         blocks[:, 4:16] = pack_q4k_scales(sc, m)
         blocks[:, 16:144] = (nib[:, :, 0, :] | (nib[:, :, 1, :] << 4)).reshape(nb, 128)
+    elif fmt == Q5_K:
+        d = np.abs(rng.normal(0.0, 0.01, nb)).astype(np.float32).astype(np.float16)
+        dmin = np.abs(rng.normal(0.0, 0.01, nb)).astype(np.float32).astype(np.float16)
+        blocks[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+        blocks[:, 2:4] = dmin.view(np.uint8).reshape(nb, 2)
+        blocks[:, 4:16] = pack_q4k_scales(rng.integers(0, 64, size=(nb, 8), dtype=np.uint8),
+                                          rng.integers(0, 64, size=(nb, 8), dtype=np.uint8))
+        blocks[:, 16:176] = rng.integers(0, 256, size=(nb, 160), dtype=np.uint8)
+    elif fmt == Q6_K:
+        d = np.abs(rng.normal(0.0, 0.002, nb)).astype(np.float32).astype(np.float16)
+        blocks[:, 0:208] = rng.integers(0, 256, size=(nb, 208), dtype=np.uint8)
+        blocks[:, 208:210] = d.view(np.uint8).reshape(nb, 2)
+    elif fmt == BF16:
+        x = rng.normal(0.0, 1.0, nb).astype(np.float32)
+        bits = (x.view(np.uint32) >> 16).astype(np.uint16)
+        special = np.array([0x7F80, 0xFF80, 0x7FC0, 0x0000, 0x8000, 0x0001, 0x807F, 0x7F7F], dtype=np.uint16)
+        idx = rng.integers(0, nb, size=min(nb, 64))
+        bits[idx] = special[rng.integers(0, special.size, size=idx.size)]
+        blocks[:, 0:2] = bits.view(np.uint8).reshape(nb, 2)
     else:
         raise ValueError(f"unknown format {fmt}")
     return blocks.reshape(-1)

@@ -44,8 +44,11 @@ enum {
   CUTB_ERR_TIMEOUT = 5      /* a bounded device-side wait ran out (read from the status word) */
 };
 
-/* GGUF block formats (interface/loader/gguf/gguf_types.hpp:109-150). */
-enum { CUTB_Q8_0 = 0, CUTB_Q4_0 = 1, CUTB_Q4_K = 2 };
+/* GGUF block formats (interface/loader/gguf/gguf_types.hpp:109-150).  The matmul entry points
+ * take the first three; cutb_dequant also takes the rest of the reference's DequantFormat set
+ * (operators/impl/dequant/DequantOp.h:8-13): Q5_K (176-byte super-blocks), Q6_K (210-byte
+ * super-blocks) and BF16 (2 bytes per element). */
+enum { CUTB_Q8_0 = 0, CUTB_Q4_0 = 1, CUTB_Q4_K = 2, CUTB_Q5_K = 3, CUTB_Q6_K = 4, CUTB_BF16 = 5 };
 
 /* Activation element types (core/api/include/ComputeCommon.h:107-113). */
 enum { CUTB_F32 = 0, CUTB_F16 = 1 };
@@ -184,9 +187,11 @@ CUTB_API int cutb_peer_exchange(const cutb_peer_scatter *peers, uint64_t *step_c
 
 /*
  * Raw GGUF blocks -> fp32 [rows, cols] with row stride ldo (elements).
- * Replaces DequantOpNode's dispatch (operators/impl/dequant/DequantOp.cpp:7-61,
- * DequantQ4K.cu:6-50); Q8_0 and Q4_0 follow the loader's CPU dequantisers
- * (interface/loader/gguf/gguf_reader.cpp:541-572, 826-850).  Bit-exact.
+ * Replaces DequantOpNode's dispatch (operators/impl/dequant/DequantOp.cpp:7-61;
+ * DequantQ4K.cu:6-50, DequantQ5K.cu, DequantQ6K.cu, DequantBF16.cu); Q8_0 and Q4_0
+ * follow the loader's CPU dequantisers (interface/loader/gguf/gguf_reader.cpp:541-572,
+ * 826-850).  Bit-exact with the loader's dequantisers for every format.  Q5_K and Q6_K
+ * need cols % 256 == 0, as the reference's kernels do.
  */
 CUTB_API int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows,
                  uint32_t cols, uint32_t ldo, void *stream);

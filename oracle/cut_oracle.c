@@ -201,12 +201,103 @@ ORC_API void orc_dequant_q4_k(const uint8_t *data, float *out, size_t n_elements
   }
 }
 
-/* Format codes shared with the tests (they mirror the product's C ABI values
- * but are defined independently here). */
-enum { ORC_Q8_0 = 0, ORC_Q4_0 = 1, ORC_Q4_K = 2 };
+/* interface/loader/gguf/gguf_reader.cpp:726-772 -- Q5_K: 176-byte super-blocks
+ * {f16 d, f16 dmin, 12 bytes scales, 32 bytes qh, 128 bytes ql}; four groups of
+ * 64 elements, low nibbles then high nibbles of the group's 32 ql bytes; bit
+ * 2g (2g+1) of qh[l] is the fifth bit of element l of the low (high) half;
+ * value = (d*sc)*q - (dmin*m), the products formed in float before the subtract. */
+ORC_API void orc_dequant_q5_k(const uint8_t *data, float *out, size_t n_elements) {
+  size_t n_blocks = (n_elements + 255) / 256;
+  size_t o = 0;
+  for (size_t i = 0; i < n_blocks && o < n_elements; ++i) {
+    const uint8_t *blk = data + i * 176;
+    uint16_t dbits, mbits;
+    memcpy(&dbits, blk, 2);
+    memcpy(&mbits, blk + 2, 2);
+    float d = orc_f16_to_f32(dbits);
+    float dmin = orc_f16_to_f32(mbits);
+    const uint8_t *scales = blk + 4;
+    const uint8_t *qh = blk + 16;
+    const uint8_t *ql = blk + 48;
+    for (int g = 0; g < 4 && o < n_elements; ++g) {
+      uint8_t sc1, m1, sc2, m2;
+      orc_scale_min_k4(2 * g, scales, &sc1, &m1);
+      orc_scale_min_k4(2 * g + 1, scales, &sc2, &m2);
+      float d1 = d * (float)sc1, dm1 = dmin * (float)m1;
+      float d2 = d * (float)sc2, dm2 = dmin * (float)m2;
+      uint8_t u1 = (uint8_t)(1u << (2 * g)), u2 = (uint8_t)(2u << (2 * g));
+      for (int l = 0; l < 32 && o < n_elements; ++l) {
+        float p = d1 * (float)((ql[32 * g + l] & 0xF) + ((qh[l] & u1) ? 16 : 0));
+        out[o++] = p - dm1;
+      }
+      for (int l = 0; l < 32 && o < n_elements; ++l) {
+        float p = d2 * (float)((ql[32 * g + l] >> 4) + ((qh[l] & u2) ? 16 : 0));
+        out[o++] = p - dm2;
+      }
+    }
+  }
+}
 
-ORC_API size_t orc_block_bytes(int fmt) { return fmt == ORC_Q8_0 ? 34 : fmt == ORC_Q4_0 ? 18 : 144; }
-ORC_API size_t orc_block_elems(int fmt) { return fmt == ORC_Q4_K ? 256 : 32; }
+/* interface/loader/gguf/gguf_reader.cpp:774-824 -- Q6_K: 210-byte super-blocks
+ * {128 bytes ql, 64 bytes qh, 16 int8 scales, f16 d}; two halves of 128
+ * elements, each four interleaved runs of 32: run r of element l takes its low
+ * four bits from ql[l + 32 (r & 1)] (low nibble for r < 2, high nibble else) and
+ * its two high bits from bits 2r..2r+1 of qh[l]; the 6-bit value is biased by 32;
+ * scale index = 8 half + 2 r + l / 16; value = (d * sc) * q.  Whole super-blocks
+ * only (the reference's partial-block tail is not restated). */
+ORC_API void orc_dequant_q6_k(const uint8_t *data, float *out, size_t n_elements) {
+  size_t n_blocks = n_elements / 256;
+  for (size_t i = 0; i < n_blocks; ++i) {
+    const uint8_t *blk = data + i * 210;
+    uint16_t dbits;
+    memcpy(&dbits, blk + 208, 2);
+    float d = orc_f16_to_f32(dbits);
+    for (int half = 0; half < 2; ++half) {
+      const uint8_t *ql = blk + 64 * half;
+      const uint8_t *qh = blk + 128 + 32 * half;
+      const int8_t *sc = (const int8_t *)(blk + 192 + 8 * half);
+      float *o = out + i * 256 + 128 * half;
+      for (int l = 0; l < 32; ++l) {
+        int is = l / 16;
+        for (int r = 0; r < 4; ++r) {
+          uint8_t lo = ql[l + 32 * (r & 1)];
+          int q = (int)((r < 2 ? (lo & 0xF) : (lo >> 4)) | (((qh[l] >> (2 * r)) & 3) << 4)) - 32;
+          float ds = d * (float)sc[is + 2 * r];
+          o[l + 32 * r] = ds * (float)q;
+        }
+      }
+    }
+  }
+}
+
+/* interface/loader/gguf/gguf_reader.cpp:860-870 -- BF16: the upper 16 bits of a float32. */
+ORC_API void orc_dequant_bf16(const uint8_t *data, float *out, size_t n_elements) {
+  for (size_t i = 0; i < n_elements; ++i) {
+    uint16_t b;
+    memcpy(&b, data + 2 * i, 2);
+    uint32_t w = (uint32_t)b << 16;
+    memcpy(out + i, &w, 4);
+  }
+}
+
+/* Format codes shared with the tests (they mirror the product's C ABI values
+ * but are defined independently here).  Q5_K, Q6_K and BF16 exist for the
+ * dequant operator only. */
+enum { ORC_Q8_0 = 0, ORC_Q4_0 = 1, ORC_Q4_K = 2, ORC_Q5_K = 3, ORC_Q6_K = 4, ORC_BF16 = 5 };
+
+ORC_API size_t orc_block_bytes(int fmt) {
+  switch (fmt) {
+    case ORC_Q8_0: return 34;
+    case ORC_Q4_0: return 18;
+    case ORC_Q4_K: return 144;
+    case ORC_Q5_K: return 176;
+    case ORC_Q6_K: return 210;
+    default: return 2;
+  }
+}
+ORC_API size_t orc_block_elems(int fmt) {
+  return (fmt == ORC_Q4_K || fmt == ORC_Q5_K || fmt == ORC_Q6_K) ? 256 : (fmt == ORC_BF16 ? 1 : 32);
+}
 
 ORC_API size_t orc_row_bytes(int fmt, size_t K) {
   size_t be = orc_block_elems(fmt);
@@ -218,6 +309,12 @@ ORC_API void orc_dequant(int fmt, const uint8_t *data, float *out, size_t n_elem
     orc_dequant_q8_0(data, out, n_elements);
   else if (fmt == ORC_Q4_0)
     orc_dequant_q4_0(data, out, n_elements);
+  else if (fmt == ORC_Q5_K)
+    orc_dequant_q5_k(data, out, n_elements);
+  else if (fmt == ORC_Q6_K)
+    orc_dequant_q6_k(data, out, n_elements);
+  else if (fmt == ORC_BF16)
+    orc_dequant_bf16(data, out, n_elements);
   else
     orc_dequant_q4_k(data, out, n_elements);
 }

@@ -17,9 +17,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libcutref.so")
 
-Q8_0, Q4_0, Q4_K = 0, 1, 2
-BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_K: 144}
+Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 4, 5  # the last three: dequant operator only
+BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, BF16: 1}
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_K: 144, Q5_K: 176, Q6_K: 210, BF16: 2}
 
 
 def build(force: bool = False) -> None:
@@ -223,7 +223,7 @@ def set_num_threads(n: int) -> None:
 
 
 # ------------------------------------------ the reference's own reader (_ref)
-_TYPE_NAME = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_K: "Q4_K"}
+_TYPE_NAME = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", BF16: "BF16"}
 
 
 def _with_gguf(fmt: int, raw, rows: int, cols: int, fn):

@@ -240,7 +240,8 @@ void blockNodesAndDequant() {
   DequantOpNode dq(s, raw, DequantFormat::Q4_K, N, K);
   CHECK(dq.dispatchSize().x == K && dq.dispatchSize().y == N);
   CHECK(f.rt.getTensor(dq.output()).getShape() == (std::vector<uint32_t>{N, K}));
-  CHECK(dq.shader().has_value() && !DequantOpNode(s, raw, DequantFormat::Q6_K, N, K).shader().has_value());
+  CHECK(dq.shader().has_value() && DequantOpNode(s, raw, DequantFormat::Q6_K, N, K).shader().has_value());
+  CHECK(!DequantOpNode(s, raw, static_cast<DequantFormat>(9), N, K).shader().has_value());
   TransposeQ4NibbleOpNode tq(s, s.createTensor({6, 16}, DataType::Int8), 6, 32);
   CHECK(f.rt.getTensor(tq.output()).getShape() == (std::vector<uint32_t>{32, 3}));
   struct {
@@ -271,7 +272,7 @@ void dispatcherAndOperations() {
   CHECK(f.raw->executed[3].label == "MatMulQ8Binary" && f.raw->executed[3].outputHandle == c4);
   // a node without a kernel is an error, not a silent skip
   auto raw = s.createTensor({210}, DataType::Int8);
-  CHECK_THROWS(ops.dequantize(raw, (uint32_t)DequantFormat::Q6_K, 1, 256), "no shader");
+  CHECK_THROWS(ops.dequantize(raw, 9u /* not a DequantFormat */, 1, 256), "no shader");
   (void)c3;
 }
 

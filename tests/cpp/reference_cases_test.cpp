@@ -328,7 +328,18 @@ void errorBehaviour() {
   CHECK_THROWS(rt->ops().matmul(a, b, s), "must match A cols");
   CHECK_THROWS(rt->ops().transposeQ4(b, 3, 32), "N must be even");
   auto raw = rt->createTensor({210}, DataType::Int8);
-  CHECK_THROWS(rt->ops().dequantize(raw, (uint32_t)DequantFormat::Q6_K, 1, 256), "no shader");
+  CHECK_THROWS(rt->ops().dequantize(raw, 9u /* not a DequantFormat */, 1, 256), "no shader");
+  {  // Q6_K has a kernel: one super-block of zero quants (q = -32) with scale 1 and d = 1
+    std::vector<uint8_t> blk(210, 0);
+    for (int i = 192; i < 208; ++i) blk[i] = 1;
+    blk[208] = 0x00, blk[209] = 0x3C;
+    auto q6 = rt->createTensor({210}, DataType::Int8, blk.data());
+    auto out = rt->ops().dequantize(q6, (uint32_t)DequantFormat::Q6_K, 1, 256);
+    std::vector<float> v(256), want(256);
+    rt->copyFromTensor(out, v.data(), v.size() * sizeof(float));
+    orc_dequant_rows(4, blk.data(), want.data(), 1, 256, 256);
+    for (int i = 0; i < 256; ++i) CHECK(v[i] == -32.0f && want[i] == -32.0f);
+  }
   CHECK(rt->iface().caps().backend == ComputeBackend::CUDA && rt->iface().caps().cooperativeMatrix);
   CHECK(rt->iface().bufferCount() > 0 && rt->iface().deviceTotalMemoryBytes() > (size_t)100 << 30);
 }

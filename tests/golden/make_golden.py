@@ -7,7 +7,8 @@ Run from the repository root in a container that has the reference checked out
 
 It (1) builds oracle/_ref/libcutref.so from the reference's unmodified
 gguf_reader.cpp, (2) pushes hand-crafted edge-case blocks and seeded random
-blocks of Q8_0 / Q4_0 / Q4_K through the reference's GGUFReader and stores the
+blocks of Q8_0 / Q4_0 / Q4_K (and Q5_K / Q6_K / BF16, which only the dequant
+operator takes) through the reference's GGUFReader and stores the
 raw bytes next to the float32 bit patterns and separated planes it returned,
 and (3) stores the mt19937 activation vectors of the reference's own tests.
 """
@@ -75,12 +76,50 @@ def edge_q4_k() -> np.ndarray:
     return blocks.reshape(-1)
 
 
+def edge_q5_k() -> np.ndarray:
+    pats = [(0x3C00, 0x0000), (0x3C00, 0x3C00), (0x0001, 0x03FF), (0x7BFF, 0x0400), (0xBC00, 0x2E66), (0x0000, 0x3C00)]
+    blocks = np.zeros((len(pats) * 2, 176), dtype=np.uint8)
+    for i, (d, dm) in enumerate(pats):
+        for v in range(2):
+            b = blocks[2 * i + v]
+            b[0:2] = np.array([d], dtype=np.uint16).view(np.uint8)
+            b[2:4] = np.array([dm], dtype=np.uint16).view(np.uint8)
+            sc = np.array([63, 0, 1, 32, 33, 47, 48, 63], dtype=np.uint8) if v == 0 else (np.arange(8) * 9 % 64).astype(np.uint8)
+            m = np.array([0, 63, 31, 16, 15, 62, 17, 63], dtype=np.uint8) if v == 0 else (63 - np.arange(8) * 7).astype(np.uint8)
+            b[4:16] = synth.pack_q4k_scales(sc, m)
+            b[16:48] = (np.arange(32) * (37 + 64 * v) % 256).astype(np.uint8)  # fifth bits: every mask position exercised
+            b[48:] = (np.arange(128) * (3 + v) % 256).astype(np.uint8)
+    return blocks.reshape(-1)
+
+
+def edge_q6_k() -> np.ndarray:
+    ds = [0x3C00, 0x0001, 0x03FF, 0x7BFF, 0xBC00, 0x0000, 0x2E66, 0x8400]
+    blocks = np.zeros((len(ds) * 2, 210), dtype=np.uint8)
+    for i, d in enumerate(ds):
+        for v in range(2):
+            b = blocks[2 * i + v]
+            b[0:128] = (np.arange(128) * (5 + 2 * v) % 256).astype(np.uint8)
+            b[128:192] = (np.arange(64) * (11 + 4 * v) % 256).astype(np.uint8)
+            sc = np.array([-128, 127, -1, 0, 1, 64, -64, 33, 2, -2, 100, -100, 17, -17, 127, -128], dtype=np.int8)
+            b[192:208] = (sc if v == 0 else sc[::-1]).view(np.uint8)
+            b[208:210] = np.array([d], dtype=np.uint16).view(np.uint8)
+    return blocks.reshape(-1)
+
+
+def edge_bf16() -> np.ndarray:
+    # +-0, subnormals, smallest normal, 1, largest finite, +-inf, quiet and signalling NaN payloads
+    bits = np.array([0x0000, 0x8000, 0x0001, 0x007F, 0x0080, 0x3F80, 0xBF80, 0x7F7F, 0xFF7F, 0x7F80, 0xFF80, 0x7FC0,
+                     0x7FA1, 0xFFFF, 0x4049, 0x1234], dtype=np.uint16)
+    return bits.view(np.uint8).copy()
+
+
 def main() -> None:
     O.build(force=True)
     assert O.have_ref(), "reference sources not found; cannot regenerate fixtures"
     out = {}
     for fmt, name, edge in ((synth.Q8_0, "q8_0", edge_q8_0), (synth.Q4_0, "q4_0", edge_q4_0),
-                            (synth.Q4_K, "q4_k", edge_q4_k)):
+                            (synth.Q4_K, "q4_k", edge_q4_k), (synth.Q5_K, "q5_k", edge_q5_k),
+                            (synth.Q6_K, "q6_k", edge_q6_k), (synth.BF16, "bf16", edge_bf16)):
         e = edge()
         be = synth.BLOCK_ELEMS[fmt]
         n_edge = e.size // synth.BLOCK_BYTES[fmt] * be
@@ -91,7 +130,7 @@ def main() -> None:
         out[f"{name}_rand_raw"] = r
         out[f"{name}_rand_shape"] = np.array([rows, cols], dtype=np.int64)
         out[f"{name}_rand_f32bits"] = O.ref_dequant(fmt, r, rows, cols).view(np.uint32).reshape(-1)
-        if fmt != synth.Q4_K:
+        if fmt in (synth.Q8_0, synth.Q4_0):
             vals, scales = O.ref_separate(fmt, r, rows, cols)
             out[f"{name}_rand_sep_values"] = vals.view(np.uint8)
             out[f"{name}_rand_sep_scales"] = scales

@@ -9,7 +9,8 @@ from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
 
-FMTS = [(synth.Q8_0, "q8_0"), (synth.Q4_0, "q4_0"), (synth.Q4_K, "q4_k")]
+FMTS = [(synth.Q8_0, "q8_0"), (synth.Q4_0, "q4_0"), (synth.Q4_K, "q4_k"), (synth.Q5_K, "q5_k"), (synth.Q6_K, "q6_k"),
+        (synth.BF16, "bf16")]
 
 
 @pytest.fixture(scope="module")
@@ -57,7 +58,7 @@ def test_dequant_matches_checker_bitexact(gpu, fmt, name, rows, cols):
     assert np.array_equal(np.ascontiguousarray(got).view(np.uint32), want.view(np.uint32))
 
 
-@pytest.mark.parametrize("fmt,cols", [(synth.Q8_0, 32), (synth.Q4_0, 96), (synth.Q8_0, 4064)])
+@pytest.mark.parametrize("fmt,cols", [(synth.Q8_0, 32), (synth.Q4_0, 96), (synth.Q8_0, 4064), (synth.BF16, 13), (synth.BF16, 1001)])
 def test_dequant_cols_not_multiple_of_eight_octets(gpu, fmt, cols):
     raw = synth.make_weights(fmt, 5, cols, seed=cols)
     got = _dq(gpu, fmt, raw, 5, cols)

@@ -9,9 +9,11 @@ from cut_b200 import synth
 from oracle import oracle as O
 
 FMTS = [(synth.Q8_0, "q8_0"), (synth.Q4_0, "q4_0"), (synth.Q4_K, "q4_k")]
+# formats the dequant operator takes: the three above and the rest of the reference's DequantFormat set
+DEQ_FMTS = FMTS + [(synth.Q5_K, "q5_k"), (synth.Q6_K, "q6_k"), (synth.BF16, "bf16")]
 
 
-@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("fmt,name", DEQ_FMTS)
 def test_dequant_matches_golden_edge_blocks(golden, fmt, name):
     raw = golden[f"{name}_edge_raw"]
     want = golden[f"{name}_edge_f32bits"]
@@ -19,7 +21,7 @@ def test_dequant_matches_golden_edge_blocks(golden, fmt, name):
     assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("fmt,name", DEQ_FMTS)
 def test_dequant_matches_golden_random_blocks(golden, fmt, name):
     raw = golden[f"{name}_rand_raw"]
     rows, cols = (int(x) for x in golden[f"{name}_rand_shape"])
@@ -40,7 +42,7 @@ def test_plane_separation_matches_golden(golden, fmt, name):
 
 
 @pytest.mark.skipif(not O.have_ref(), reason="reference reader not built (oracle/_ref)")
-@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("fmt,name", DEQ_FMTS)
 @pytest.mark.parametrize("rows,cols", [(1, 256), (3, 512), (16, 4096)])
 def test_dequant_matches_compiled_reference(fmt, name, rows, cols):
     raw = synth.make_weights(fmt, rows, cols, seed=rows * 131 + cols + fmt)
