@@ -34,12 +34,16 @@ __device__ __forceinline__ uint32_t ldg32u(const uint8_t *p) {
 // 6-bit (scale, min) of sub-block j from the 12 packed bytes of a Q4_K / Q5_K super-block
 // (gguf_reader.cpp:668-676).
 __device__ __forceinline__ void scale_min_k4(const uint8_t *sc, uint32_t j, uint32_t &s, uint32_t &m) {
+  // the 12 bytes as three words (bytes 0-3: low scales, 4-7: low mins, 8-11: high nibbles)
+  const uint32_t w0 = ldg32u(sc), w1 = ldg32u(sc + 4), w2 = ldg32u(sc + 8);
+  const uint32_t sh = 8 * (j & 3);
+  const uint32_t a = (w0 >> sh) & 0xFF, b = (w1 >> sh) & 0xFF, c = (w2 >> sh) & 0xFF;
   if (j < 4) {
-    s = ldg8(sc + j) & 63;
-    m = ldg8(sc + j + 4) & 63;
+    s = a & 63;
+    m = b & 63;
   } else {
-    s = (ldg8(sc + j + 4) & 0xF) | ((ldg8(sc + j - 4) >> 6) << 4);
-    m = (ldg8(sc + j + 4) >> 4) | ((ldg8(sc + j) >> 6) << 4);
+    s = (c & 0xF) | ((a >> 6) << 4);
+    m = (c >> 4) | ((b >> 6) << 4);
   }
 }
 
@@ -48,8 +52,18 @@ __device__ __forceinline__ void scale_min_k4(const uint8_t *sc, uint32_t j, uint
 template <int FMT> __device__ __forceinline__ void decode8(const uint8_t *b, uint32_t oct, float (&v)[8], uint32_t valid) {
   if constexpr (FMT == CUTB_BF16) {
     // the upper half of a float32 (gguf_reader.cpp:860-870, DequantBF16.cu:20-28)
+    if (valid >= 8 && (reinterpret_cast<uintptr_t>(b) & 15) == 0) {
+      const uint4 w = __ldg(reinterpret_cast<const uint4 *>(b));
+      const uint32_t x[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = (uint32_t)i < valid ? __uint_as_float(ldg16(b + 2 * i) << 16) : 0.f;
+      for (int i = 0; i < 4; ++i) {
+        v[2 * i] = __uint_as_float(x[i] << 16);
+        v[2 * i + 1] = __uint_as_float(x[i] & 0xFFFF0000u);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = (uint32_t)i < valid ? __uint_as_float(ldg16(b + 2 * i) << 16) : 0.f;
+    }
   } else if constexpr (FMT == CUTB_Q5_K) {
     // gguf_reader.cpp:726-772: group g of 64 = sub-blocks 2g (low nibbles) and 2g + 1 (high
     // nibbles) of the group's 32 ql bytes; bit j of qh[l] is element l's fifth bit in sub-block j
@@ -124,17 +138,19 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
                                                       uint32_t cols, uint32_t ldo, uint64_t row_bytes_, int vec_ok) {
   constexpr uint32_t BE = block_elems(FMT), BB = block_bytes(FMT);
   const uint32_t octs_per_row = (cols + 7) / 8;
-  const uint64_t total = (uint64_t)rows * octs_per_row;
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-    const uint32_t r = (uint32_t)(i / octs_per_row), o = (uint32_t)(i % octs_per_row);
+  // grid.x walks a row's groups of eight weights, grid.y the rows: no division per element
+  for (uint32_t r = blockIdx.y; r < rows; r += gridDim.y)
+  for (uint32_t o = blockIdx.x * blockDim.x + threadIdx.x; o < octs_per_row; o += gridDim.x * blockDim.x) {
     const uint32_t k = o * 8;
     const uint8_t *b = raw + (uint64_t)r * row_bytes_ + (uint64_t)(k / BE) * BB;
     float v[8];
     decode8<FMT>(b, (k % BE) / 8, v, cols - k);
     float *dst = out + (uint64_t)r * ldo + k;
     if (vec_ok && k + 8 <= cols) {
-      reinterpret_cast<float4 *>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
-      reinterpret_cast<float4 *>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+      // written once, read by another kernel much later: streaming stores keep them from
+      // displacing the raw blocks in L2
+      __stcs(reinterpret_cast<float4 *>(dst), make_float4(v[0], v[1], v[2], v[3]));
+      __stcs(reinterpret_cast<float4 *>(dst) + 1, make_float4(v[4], v[5], v[6], v[7]));
     } else {
 #pragma unroll
       for (int e = 0; e < 8; ++e)
@@ -151,9 +167,15 @@ int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint3
   if (int rc = get_device_info(&di)) return rc;
   const uint64_t total = (uint64_t)rows * ((cols + 7) / 8);
   if (total == 0) return CUTB_OK;
-  uint64_t blocks = (total + 255) / 256;
-  const uint64_t cap = (uint64_t)di.sm_count * 8;
-  if (blocks > cap) blocks = cap;
+  // about 8 CTAs per SM in all: enough along a row to cover it once, the rest along the rows
+  const uint32_t cap = (uint32_t)di.sm_count * 8;
+  uint32_t gx = ((cols + 7) / 8 + 255) / 256;
+  if (gx > cap) gx = cap;
+  uint32_t gy = cap / gx;
+  if (gy > rows) gy = rows;
+  if (gy > 65535u) gy = 65535u;
+  if (gy == 0) gy = 1;
+  const dim3 blocks(gx, gy);
   const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (ldo % 4 == 0);
   const uint8_t *r = reinterpret_cast<const uint8_t *>(raw);
   const uint64_t rb = row_bytes(format, cols);
@@ -169,7 +191,7 @@ int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint3
     set_last_error("dequant: BF16 input must be 2-byte aligned");
     return CUTB_ERR_INVALID;
   }
-  const unsigned g = (unsigned)blocks;
+  const dim3 g = blocks;
   switch (format) {
     case CUTB_Q8_0: dequant_kernel<CUTB_Q8_0><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
     case CUTB_Q4_0: dequant_kernel<CUTB_Q4_0><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
