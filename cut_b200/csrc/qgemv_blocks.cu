@@ -6,17 +6,21 @@
 // MatMulQ8GemvKPar8.cu:11-92) on the block layout its loader reads
 // (interface/loader/gguf/gguf_reader.cpp:541-572, 678-724, 826-850).
 //
-// Design (HBM-bound: every weight byte is read exactly once, and the kernel
-// spends as few instructions per byte as it can so that issue slots do not
-// become the bound):
-//  * Persistent CTAs own contiguous ranges of weight rows, walked in tiles of
-//    16 rows.  The K axis of a tile is split over the CTA's warps.
-//  * Each warp runs its own ring of shared-memory stages filled by bulk async
-//    copies (cp.async.bulk, the TMA engine's untiled form; one copy per row
-//    and stage, completion counted on an mbarrier).  A stage holds 16 rows x
-//    256 or 512 weights of raw block bytes, row stride chosen so that the
-//    fragment reads below are bank-conflict free.  A CTA's first copies are in
-//    flight before it touches the activations.
+// Design (every weight byte is read from DRAM exactly once, and the kernel spends as few
+// instructions per byte as it can so that issue slots do not become the bound):
+//  * One persistent CTA per SM owns a contiguous range of weight rows, walked in tiles of
+//    16 rows.  A producer warp fills a ring of shared-memory stages with bulk async copies
+//    (cp.async.bulk, the TMA engine's untiled form): one copy per row and stage of the whole
+//    row segment (up to 4096 weights: 2304 bytes for the 4-bit formats, 4352 for Q8_0 --
+//    large contiguous reads keep DRAM pages open), completion counted on an mbarrier.  The
+//    K axis of a stage is split over 16 consumer warps, one 256-weight granule each; row
+//    strides in shared memory are padded so that the fragment reads are bank-conflict free.
+//    Q8_0 stages have a barrier pair per K half, so that half a stage can be refilled while
+//    the other half is still being read.
+//  * The kernel is launched with programmatic stream serialization: it lets its successor
+//    start at once (griddepcontrol.launch_dependents), issues its first copies, and waits for
+//    its predecessor (griddepcontrol.wait) only before it reads the activations; the
+//    shared-memory plan keeps a CTA under half an SM so that both launches' CTAs co-reside.
 //  * The 4- and 8-bit quants feed the integer tensor-core MMA directly
 //    (m16n8k32, s8 x s8 -> s32): a nibble becomes the int8 value 16 (q - 8) with
 //    one shift and one LOP3 per four weights, int8 quants are used as they
@@ -35,9 +39,10 @@
 //    dmin*m to the staged sum of x^, with the 6-bit fields unpacked in
 //    registers.
 //  * Partial sums of a CTA's warps meet in shared memory in a fixed order
-//    (deterministic), then the fused epilogue runs and C is written.  With
-//    ksplit > 1 (long K or few rows) partial sums go to a workspace and a
-//    second small kernel adds them in a fixed order.
+//    (deterministic), then the fused epilogue runs and C is written (or, for a
+//    row-sharded launch, stored into every rank's output through peer-mapped
+//    pointers).  With ksplit > 1 (long K or few rows) partial sums go to a
+//    workspace and a second small kernel adds them in a fixed order.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel stores
 // CUTB_ERR_TIMEOUT in the caller's status word and leaves without spinning.
