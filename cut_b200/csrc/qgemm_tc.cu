@@ -73,6 +73,7 @@ struct TcParams {
   uint32_t sa, nb;   // activation stages (of mb tiles each) and weight slots in shared memory
   uint32_t groups;   // converter groups (1..nb)
   uint32_t issuers;  // MMA issuer threads (1..2, at most one per token pair)
+  uint32_t ksub;     // 64-k sub-tiles per stage (2 up to 256 tokens: the issuer's waits are paid per stage)
   int fusion_type, fusion_op;
   int *status;
 };
@@ -291,21 +292,22 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // tiles must start on a 1024-byte boundary (the 128-byte swizzle repeats every 8 rows)
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const uint32_t SA = p.sa, NB = p.nb, MB = p.mb, NI = p.issuers;
-  const uint32_t a_stage_bytes = MB * TC_TILE_BYTES;
+  const uint32_t SA = p.sa, NB = p.nb, MB = p.mb, NI = p.issuers, KS = p.ksub;
+  // a stage = KS sub-tiles of 64 k: activation tiles laid out [sub][token block], the weight slot [sub]
+  const uint32_t a_stage_bytes = MB * KS * TC_TILE_BYTES, b_slot_bytes = KS * TC_TILE_BYTES;
   uint8_t *a_ring = smem, *b_ring = smem + SA * a_stage_bytes;
   // fullA[SA] fullB[NB] consumed[NC] accum.  One "consumed" barrier per K stage in a ring of
   // NC = SA + NB: a single tcgen05.commit per issuer and stage frees both the activation
   // stage and the weight slot (the copy producer waits for stage ks - SA, a converter for
   // stage ks - NB); NC > SA, NB keeps a barrier from being reused before both have seen it.
   const uint32_t NC = SA + NB;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(b_ring + NB * TC_TILE_BYTES);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(b_ring + NB * b_slot_bytes);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * SA + 2 * NB + 1);
   uint32_t *abort_flag = tmem_slot + 1;
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t n0 = blockIdx.x * TC_BW, m0 = blockIdx.y * (TC_MAX_MB * TC_BT);
-  const uint32_t nk = p.K / TC_BK;
+  const uint32_t nk = p.K / (TC_BK * KS);  // K stages
   const uint32_t fulla_u = smem_u32(bars), fullb_u = fulla_u + SA * 8, cons_u = fullb_u + NB * 8, accum_u = cons_u + NC * 8;
   const uint32_t tmem_cols = MB == 1 ? 128u : (MB == 2 ? 256u : 512u);
 
@@ -352,16 +354,18 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
           break;
         }
         tc_fence_after();
-        const uint32_t w_lo = w_lo0 + sb * TC_TILE_DESC, t_lo = t_lo0 + sa * MB * TC_TILE_DESC;
-        const uint32_t acc = ks != 0;
-        for (uint32_t pr = me; pr < npairs; pr += NI) {
-          const uint32_t idesc = (2 * pr + 2 <= MB) ? idesc256 : idesc128;
-          const uint32_t tl = t_lo + pr * 2 * TC_TILE_DESC, d = tmem_base + pr * 256;
-          // 16 k = 32 bytes = 2 descriptor units along the swizzled row
-          umma_f16(d, w_lo, tl, desc_hi, idesc, acc);
-          umma_f16(d, w_lo + 2, tl + 2, desc_hi, idesc, 1);
-          umma_f16(d, w_lo + 4, tl + 4, desc_hi, idesc, 1);
-          umma_f16(d, w_lo + 6, tl + 6, desc_hi, idesc, 1);
+        for (uint32_t sub = 0; sub < KS; ++sub) {
+          const uint32_t w_lo = w_lo0 + (sb * KS + sub) * TC_TILE_DESC, t_lo = t_lo0 + (sa * KS + sub) * MB * TC_TILE_DESC;
+          const uint32_t acc = (ks | sub) != 0;
+          for (uint32_t pr = me; pr < npairs; pr += NI) {
+            const uint32_t idesc = (2 * pr + 2 <= MB) ? idesc256 : idesc128;
+            const uint32_t tl = t_lo + pr * 2 * TC_TILE_DESC, d = tmem_base + pr * 256;
+            // 16 k = 32 bytes = 2 descriptor units along the swizzled row
+            umma_f16(d, w_lo, tl, desc_hi, idesc, acc);
+            umma_f16(d, w_lo + 2, tl + 2, desc_hi, idesc, 1);
+            umma_f16(d, w_lo + 4, tl + 4, desc_hi, idesc, 1);
+            umma_f16(d, w_lo + 6, tl + 6, desc_hi, idesc, 1);
+          }
         }
         umma_commit(cons_u + sc * 8);  // the stage is consumed when these MMAs have read it
         if (++sa == SA) sa = 0, pa ^= 1u;
@@ -389,7 +393,9 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
         if (aborted()) break;
         const uint32_t bar = fulla_u + sa * 8, dst = a_base + sa * a_stage_bytes;
         mbar_arrive_expect_tx(bar, a_stage_bytes);
-        for (uint32_t mb = 0; mb < MB; ++mb) tma_load_2d(dst + mb * TC_TILE_BYTES, &tmapA, ks * TC_BK, m0 + mb * TC_BT, bar);
+        for (uint32_t sub = 0; sub < KS; ++sub)
+          for (uint32_t mb = 0; mb < MB; ++mb)
+            tma_load_2d(dst + (sub * MB + mb) * TC_TILE_BYTES, &tmapA, (ks * KS + sub) * TC_BK, m0 + mb * TC_BT, bar);
         ++issued;
         if (++sa == SA) sa = 0, pa ^= 1u;
       }
@@ -416,37 +422,49 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
     RawWindow<FMT> nxt;
 #pragma unroll
     for (int i = 0; i < RawWindow<FMT>::NV; ++i) nxt.v[i] = make_uint4(0, 0, 0, 0);
-    if (live && g < nk) load_window<FMT>(wrow, g * TC_BK, nxt);
+    if (live && g < nk) load_window<FMT>(wrow, g * KS * TC_BK, nxt);
     // this group's slot sequence: start at slot g, advance by G modulo NB
     uint32_t sb = g % NB;
     uint32_t sc = 0, pc = 0;  // consumed barrier of stage ks - NB, once ks >= NB
     bool sc_set = false;
-    for (uint32_t ks = g; ks < nk; ks += G) {
-      const RawWindow<FMT> cur = nxt;
-      if (live && ks + G < nk) load_window<FMT>(wrow, (ks + G) * TC_BK, nxt);
-      uint4 out[8];
-      if (live) {
-        convert_window<FMT>(cur, ks * TC_BK, out);
-      } else {
+    for (uint32_t ks = g; ks < nk && !dead; ks += G) {
+      uint8_t *slot = b_ring + sb * b_slot_bytes;
+      for (uint32_t sub = 0; sub < KS; ++sub) {
+        const uint32_t chunk = ks * KS + sub;  // 64-k chunk of the row
+        const RawWindow<FMT> cur = nxt;
+        // the chunk this thread converts next: the following sub-tile, or the first of the group's next stage
+        const uint32_t nchunk = sub + 1 < KS ? chunk + 1 : (ks + G) * KS;
+        if (live && nchunk < nk * KS) load_window<FMT>(wrow, nchunk * TC_BK, nxt);
+        uint4 out[8];
+        if (live) {
+          convert_window<FMT>(cur, chunk * TC_BK, out);
+        } else {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
-      }
-      uint32_t ok = 1;  // one lane per warp polls the barrier
-      if (ks >= NB) {
-        if (!sc_set) sc = ks - NB, sc_set = true;  // first wait: stage ks - NB < G <= NB < NC
-        if (lane == 0) ok = mbar_spin_bounded(cons_u + sc * 8, pc) ? 1u : 0u;
-        sc += G;
-        if (sc >= NC) sc -= NC, pc ^= 1u;
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) {
-        if (lane == 0) give_up();
-        dead = true;
-      }
-      if (dead || aborted()) break;
-      uint8_t *tile = b_ring + sb * TC_TILE_BYTES;
+          for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
+        }
+        if (sub == 0) {
+          uint32_t ok = 1;  // one lane per warp polls the barrier
+          if (ks >= NB) {
+            if (!sc_set) sc = ks - NB, sc_set = true;  // first wait: stage ks - NB < G <= NB < NC
+            if (lane == 0) ok = mbar_spin_bounded(cons_u + sc * 8, pc) ? 1u : 0u;
+            sc += G;
+            if (sc >= NC) sc -= NC, pc ^= 1u;
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) {
+            if (lane == 0) give_up();
+            dead = true;
+          }
+          if (dead || aborted()) {
+            dead = true;
+            break;
+          }
+        }
+        uint8_t *tile = slot + sub * TC_TILE_BYTES;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) st_chunk(tile, r, c, out[c]);
+        for (int c = 0; c < 8; ++c) st_chunk(tile, r, c, out[c]);
+      }
+      if (dead) break;
       fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
       __syncwarp();
       if (lane == 0) mbar_arrive(fullb_u + sb * 8);
@@ -541,8 +559,8 @@ int make_tmap_a(CUtensorMap *map, const void *a_f16, uint32_t M, uint32_t K, uin
   return CUTB_OK;
 }
 
-size_t tc_smem_bytes(uint32_t mb, uint32_t sa, uint32_t nb) {
-  return 1024 + (size_t)(sa * mb + nb) * TC_TILE_BYTES + (2 * sa + 2 * nb + 1) * 8 + 16;  // fullA, fullB, consumed[sa + nb], accum
+size_t tc_smem_bytes(uint32_t mb, uint32_t sa, uint32_t nb, uint32_t ksub) {
+  return 1024 + (size_t)(sa * mb + nb) * ksub * TC_TILE_BYTES + (2 * sa + 2 * nb + 1) * 8 + 16;  // fullA, fullB, consumed[sa + nb], accum
 }
 
 template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cudaStream_t stream) {
@@ -556,7 +574,7 @@ template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cuda
     configured_device = dev;
   }
   dim3 grid((p.N + TC_BW - 1) / TC_BW, (p.M + TC_MAX_MB * TC_BT - 1) / (TC_MAX_MB * TC_BT));
-  qgemm_tc_kernel<FMT><<<grid, TC_CTRL_THREADS + 128 * p.groups, tc_smem_bytes(p.mb, p.sa, p.nb), stream>>>(map, p);
+  qgemm_tc_kernel<FMT><<<grid, TC_CTRL_THREADS + 128 * p.groups, tc_smem_bytes(p.mb, p.sa, p.nb, p.ksub), stream>>>(map, p);
   CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;
 }
@@ -605,9 +623,13 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   if (p.groups > p.nb) p.groups = p.nb;
   p.issuers = 2;
   if (p.issuers > (p.mb + 1) / 2) p.issuers = (p.mb + 1) / 2;
+  // Up to 256 tokens the tensor work of a 64-k stage (256-512 cycles) is less than what the issuer
+  // thread spends on the stage's two barrier waits and four to eight MMA issues: stages of 128 k
+  // halve the waits per k, and shared memory has room for them there.
+  p.ksub = p.mb <= 2 ? 2u : 1u;
   p.sa = 0;
   for (uint32_t sa = 6; sa >= 2; --sa)
-    if (tc_smem_bytes(p.mb, sa, p.nb) <= di.smem_optin) {
+    if (tc_smem_bytes(p.mb, sa, p.nb, p.ksub) <= di.smem_optin) {
       p.sa = sa;
       break;
     }
