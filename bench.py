@@ -198,7 +198,8 @@ def run_reference(args) -> None:
 def secondary_measurements(dev) -> dict:
     """Context numbers for the other benchmark configurations (not the headline value):
     configs[0] Q8_0 4096x4096 fp32 mat-vec (GB/s, weights cycled over 32 copies) and
-    configs[2] Q4_K prefill GEMM M=512 K=4096 N=14336 (TFLOP/s = 2 M K N / time)."""
+    configs[2] Q4_K prefill GEMM M=512 K=4096 N=14336 (TFLOP/s = 2 M K N / time), and the
+    dequant operator on that weight (GB/s over raw bytes in + fp32 bytes out)."""
     import torch
 
     from cut_b200 import _lib as L
@@ -260,6 +261,20 @@ def secondary_measurements(dev) -> dict:
         "us_per_launch": us, "TFLOP/s": tf,
         "frac_of_measured_bf16_sustained": tf / peaks["bf16_tflops_sustained"] if "bf16_tflops_sustained" in peaks else None,
         "kernel": "tcgen05.mma kind::f16, TMEM accumulators"}
+    del A, C, d, keep
+
+    # the dequant operator on the same weight (write-bound: 33 MB in, 235 MB out; three output
+    # buffers cycled so that L2 cannot absorb the writes)
+    outs = [torch.empty((n, k), dtype=torch.float32, device=dev) for _ in range(3)]
+
+    def dq():
+        for o in outs:
+            ops.dequantize(W, L.Q4_K, n, k, out=o)
+
+    us = timed(dq, 10) / len(outs)
+    dq_bytes = W.numel() + n * k * 4
+    out["dequant_q4_k_14336x4096"] = {"us_per_launch": us, "GB/s": dq_bytes / us / 1e3, "algorithmic_bytes": dq_bytes,
+                                      "frac_of_measured_hbm": (dq_bytes / us / 1e3) / peaks["hbm_gbs"] if "hbm_gbs" in peaks else None}
     return out
 
 

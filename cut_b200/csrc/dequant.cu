@@ -33,9 +33,12 @@ __device__ __forceinline__ uint32_t ldg32u(const uint8_t *p) {
 
 // 6-bit (scale, min) of sub-block j from the 12 packed bytes of a Q4_K / Q5_K super-block
 // (gguf_reader.cpp:668-676).
+__device__ __forceinline__ uint32_t ldg32a(const uint8_t *p) { return __ldg(reinterpret_cast<const uint32_t *>(p)); }  // 4-byte aligned
+
 __device__ __forceinline__ void scale_min_k4(const uint8_t *sc, uint32_t j, uint32_t &s, uint32_t &m) {
-  // the 12 bytes as three words (bytes 0-3: low scales, 4-7: low mins, 8-11: high nibbles)
-  const uint32_t w0 = ldg32u(sc), w1 = ldg32u(sc + 4), w2 = ldg32u(sc + 8);
+  // the 12 bytes as three words (bytes 0-3: low scales, 4-7: low mins, 8-11: high nibbles);
+  // Q4_K / Q5_K super-blocks are 4-byte aligned (checked at launch)
+  const uint32_t w0 = ldg32a(sc), w1 = ldg32a(sc + 4), w2 = ldg32a(sc + 8);
   const uint32_t sh = 8 * (j & 3);
   const uint32_t a = (w0 >> sh) & 0xFF, b = (w1 >> sh) & 0xFF, c = (w2 >> sh) & 0xFF;
   if (j < 4) {
@@ -68,14 +71,14 @@ template <int FMT> __device__ __forceinline__ void decode8(const uint8_t *b, uin
     // gguf_reader.cpp:726-772: group g of 64 = sub-blocks 2g (low nibbles) and 2g + 1 (high
     // nibbles) of the group's 32 ql bytes; bit j of qh[l] is element l's fifth bit in sub-block j
     const uint32_t j = oct >> 2, l0 = (oct & 3) * 8;
-    const uint32_t hdr = ldg32u(b);
+    const uint32_t hdr = ldg32a(b);
     const float d = h2f_bits(hdr & 0xFFFF), dmin = h2f_bits(hdr >> 16);
     uint32_t s, m;
     scale_min_k4(b + 4, j, s, m);
     const float d1 = __fmul_rn(d, (float)s), dm = __fmul_rn(dmin, (float)m);
     const uint8_t *ql = b + 48 + (j >> 1) * 32 + l0, *qh = b + 16 + l0;
     const uint32_t sh = (j & 1) * 4;
-    const uint32_t w[2] = {ldg32u(ql), ldg32u(ql + 4)}, h[2] = {ldg32u(qh), ldg32u(qh + 4)};
+    const uint32_t w[2] = {ldg32a(ql), ldg32a(ql + 4)}, h[2] = {ldg32a(qh), ldg32a(qh + 4)};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const uint32_t q = ((w[i >> 2] >> (8 * (i & 3) + sh)) & 0xF) + (((h[i >> 2] >> (8 * (i & 3) + j)) & 1) << 4);
@@ -179,8 +182,8 @@ int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint3
   const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (ldo % 4 == 0);
   const uint8_t *r = reinterpret_cast<const uint8_t *>(raw);
   const uint64_t rb = row_bytes(format, cols);
-  if (format == CUTB_Q4_K && (reinterpret_cast<uintptr_t>(raw) % 4 != 0)) {
-    set_last_error("dequant: Q4_K blocks must be 4-byte aligned");
+  if ((format == CUTB_Q4_K || format == CUTB_Q5_K) && (reinterpret_cast<uintptr_t>(raw) % 4 != 0)) {
+    set_last_error("dequant: Q4_K / Q5_K blocks must be 4-byte aligned");
     return CUTB_ERR_INVALID;
   }
   if ((format == CUTB_Q5_K || format == CUTB_Q6_K) && cols % 256 != 0) {

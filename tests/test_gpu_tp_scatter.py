@@ -28,3 +28,38 @@ def test_scatter_epilogue_two_ranks():
            "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "mgpu", "tp_scatter_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "TP_SCATTER_OK" in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
+
+
+@pytest.mark.gpu
+def test_exchange_wait_runs_out_instead_of_hanging():
+    """Failure detection of the fused exchange on one GPU: a two-rank exchange in which the other rank
+    never signals.  The exchange kernel's wait is bounded (about a second): it must come back with
+    CUTB_ERR_TIMEOUT in the status word and leave the stream and the context usable."""
+    import ctypes as C
+    import time
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    sys.path.insert(0, ROOT)
+    from cut_b200 import _lib as L
+
+    dev = torch.device("cuda", 0)
+    out = torch.zeros(16, dtype=torch.float32, device=dev)
+    flags = torch.zeros(2 * 32, dtype=torch.int64, device=dev)  # two counters, 256 bytes apart
+    steps = torch.zeros(1, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ps = L.PeerScatter()
+    ps.world, ps.rank, ps.ldc_total, ps.n_offset = 2, 0, 16, 0
+    for r in range(2):
+        ps.C_peers[r] = out.data_ptr()
+        ps.flag_peers[r] = flags.data_ptr() + 256 * r
+    t0 = time.perf_counter()
+    L.check(L.lib().cutb_peer_exchange(C.byref(ps), steps.data_ptr(), status.data_ptr(), None))
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert int(status.item()) == L.ERR_TIMEOUT
+    assert 0.2 < waited < 10.0
+    # this rank signalled both counters once, the missing rank never did; the step was counted
+    assert flags[0].item() == 1 and flags[32].item() == 1 and steps.item() == 1
+    # the context still works
+    assert float((out + 1).sum().item()) == 16.0
