@@ -224,6 +224,65 @@ int cutb_peer_exchange(const cutb_peer_scatter *peers, uint64_t *step_counter, i
   return peer_exchange_launch(*peers, step_counter, status, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cutb_separate_blocks(int format, const void *raw, uint64_t raw_bytes, void *values, void *scales, uint64_t rows, uint64_t cols,
+                         void *stream) {
+  if (format != CUTB_Q8_0 && format != CUTB_Q4_0) {
+    set_last_error("separate_blocks: format must be Q8_0 or Q4_0");
+    return CUTB_ERR_INVALID;
+  }
+  if (rows == 0 || cols == 0) return CUTB_OK;
+  if (!raw || !values || !scales || cols % 32 != 0 || reinterpret_cast<uintptr_t>(raw) % 2 || reinterpret_cast<uintptr_t>(values) % 2 ||
+      reinterpret_cast<uintptr_t>(scales) % 2) {
+    set_last_error("separate_blocks: null or odd pointer, or cols %% 32 != 0");
+    return CUTB_ERR_INVALID;
+  }
+  if (raw_bytes < rows * (cols / 32) * block_bytes(format)) {
+    set_last_error("separate_blocks: %llu raw bytes for %llu x %llu", (unsigned long long)raw_bytes, (unsigned long long)rows,
+                   (unsigned long long)cols);
+    return CUTB_ERR_INVALID;
+  }
+  return separate_launch(format, raw, values, scales, rows, cols, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_transpose_2d(uint32_t elem_bytes, const void *in, void *out, uint32_t rows, uint32_t cols, uint64_t ldi, uint64_t ldo,
+                      void *stream) {
+  if (elem_bytes != 1 && elem_bytes != 2) {
+    set_last_error("transpose_2d: element size must be 1 or 2 bytes");
+    return CUTB_ERR_INVALID;
+  }
+  if (rows == 0 || cols == 0) return CUTB_OK;
+  if (!in || !out || ldi < cols || ldo < rows || reinterpret_cast<uintptr_t>(in) % elem_bytes || reinterpret_cast<uintptr_t>(out) % elem_bytes) {
+    set_last_error("transpose_2d: null or misaligned pointer, or a stride shorter than the row");
+    return CUTB_ERR_INVALID;
+  }
+  return transpose_launch(elem_bytes, in, out, rows, cols, ldi, ldo, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_requant_q4k_affine(const void *raw, uint64_t raw_bytes, void *packedT, void *scalesT, uint32_t N, uint32_t K, uint64_t ldp,
+                            uint64_t lds, void *stream) {
+  if (K % 256 != 0 || N % 2 != 0) {  // the reference declines these shapes too (llama.cpp:576-578)
+    set_last_error("requant_q4k_affine: needs K %% 256 == 0 and even N (K=%u N=%u)", K, N);
+    return CUTB_ERR_UNSUPPORTED;
+  }
+  if (N == 0 || K == 0) return CUTB_OK;
+  if (!raw || !packedT || !scalesT || reinterpret_cast<uintptr_t>(raw) % 4 || reinterpret_cast<uintptr_t>(scalesT) % 2 || ldp < N / 2 ||
+      lds < N || raw_bytes < (uint64_t)N * (K / 256) * 144) {
+    set_last_error("requant_q4k_affine: null or misaligned pointer, short stride or short input");
+    return CUTB_ERR_INVALID;
+  }
+  return requant_q4k_affine_launch(raw, packedT, scalesT, N, K, ldp, lds, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_quantize_rows_q8_0(const float *x, void *values, void *scales, uint64_t n, void *stream) {
+  if (n == 0) return CUTB_OK;
+  if (!x || !values || !scales || n % 32 != 0 || reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(values) % 16 ||
+      reinterpret_cast<uintptr_t>(scales) % 2) {
+    set_last_error("quantize_rows_q8_0: null or misaligned pointer, or n %% 32 != 0");
+    return CUTB_ERR_INVALID;
+  }
+  return quantize_rows_q8_0_launch(x, values, scales, n, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                  void *stream) {
   if (format < CUTB_Q8_0 || format > CUTB_BF16) {

@@ -28,6 +28,13 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
 
 int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                    cudaStream_t stream);
+// Load-time repacks (repack.cu), bit-exact with the reference's CPU loader / runner code.
+int separate_launch(int format, const void *raw, void *values, void *scales, uint64_t rows, uint64_t cols, cudaStream_t stream);
+int transpose_launch(uint32_t elem_bytes, const void *in, void *out, uint32_t R, uint32_t C, uint64_t ldi, uint64_t ldo,
+                     cudaStream_t stream);
+int requant_q4k_affine_launch(const void *raw, void *packedT, void *scalesT, uint32_t N, uint32_t K, uint64_t ldp, uint64_t lds,
+                              cudaStream_t stream);
+int quantize_rows_q8_0_launch(const float *x, void *values, void *scales, uint64_t n, cudaStream_t stream);
 int transpose_q4_launch(const void *in, void *out, uint32_t N, uint32_t K, uint32_t stride_in, uint32_t stride_out,
                         cudaStream_t stream);
 

@@ -100,3 +100,42 @@ def transpose_q4(packed: torch.Tensor, N: int, K: int) -> torch.Tensor:
     L.check(L.lib().cutb_transpose_q4(packed.data_ptr(), out.data_ptr(), N, K, packed.stride(0), out.stride(0),
                                       _stream_ptr()))
     return out
+
+
+# ---- load-time repacks on the device (bit-exact with the reference's CPU loader / runner) ----
+def separate_blocks(raw: torch.Tensor, fmt: int, rows: int, cols: int):
+    """Q8_0 / Q4_0 blocks -> (values [rows, cols] int8 or packed nibbles [rows, cols / 2] uint8, scales [rows, cols / 32]
+    as int16 bit patterns of f16), as the reference's read_tensor_q8/q4_separated return them."""
+    vals = torch.empty((rows, cols if fmt == L.Q8_0 else cols // 2), dtype=torch.int8 if fmt == L.Q8_0 else torch.uint8,
+                       device=raw.device)
+    scales = torch.empty((rows, cols // 32), dtype=torch.int16, device=raw.device)
+    L.check(L.lib().cutb_separate_blocks(fmt, raw.data_ptr(), raw.numel() * raw.element_size(), vals.data_ptr(), scales.data_ptr(),
+                                         rows, cols, _stream_ptr()))
+    return vals, scales
+
+
+def transpose_2d(x: torch.Tensor, ldo: int | None = None) -> torch.Tensor:
+    """[R, C] of 1- or 2-byte elements -> [C, ldo >= R] (padding zero-filled)."""
+    R, Cc = x.shape
+    ldo = R if ldo is None else ldo
+    out = torch.zeros((Cc, ldo), dtype=x.dtype, device=x.device)
+    L.check(L.lib().cutb_transpose_2d(x.element_size(), x.data_ptr(), out.data_ptr(), R, Cc, x.stride(0), ldo, _stream_ptr()))
+    return out
+
+
+def requant_q4k_affine(raw: torch.Tensor, N: int, K: int):
+    """Q4_K rows -> (nibbles [K, N / 2] uint8, f16 bit patterns [2 K / 32, N] int16): the runner's affine re-encode."""
+    packedT = torch.zeros((K, N // 2), dtype=torch.uint8, device=raw.device)
+    scalesT = torch.zeros((2 * (K // 32), N), dtype=torch.int16, device=raw.device)
+    L.check(L.lib().cutb_requant_q4k_affine(raw.data_ptr(), raw.numel() * raw.element_size(), packedT.data_ptr(), scalesT.data_ptr(),
+                                            N, K, N // 2, N, _stream_ptr()))
+    return packedT, scalesT
+
+
+def quantize_rows_q8_0(x: torch.Tensor):
+    """float32 values (multiple of 32) -> (int8 values, f16 scale bit patterns), the runner's Q8_0 requantiser."""
+    x = x.contiguous().view(-1)
+    vals = torch.empty(x.numel(), dtype=torch.int8, device=x.device)
+    scales = torch.empty(x.numel() // 32, dtype=torch.int16, device=x.device)
+    L.check(L.lib().cutb_quantize_rows_q8_0(x.data_ptr(), vals.data_ptr(), scales.data_ptr(), x.numel(), _stream_ptr()))
+    return vals, scales

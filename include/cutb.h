@@ -206,6 +206,32 @@ CUTB_API int cutb_transpose_q4(const void *in, void *out, uint32_t N, uint32_t K
                       uint32_t stride_out, void *stream);
 
 /* Library / device information. */
+/*
+ * Load-time repacks on the device, for callers that keep the reference's [K, N] plane layout
+ * (the block kernels above need none of them).  Each is bit-exact with the CPU code it replaces.
+ *
+ * cutb_separate_blocks: Q8_0 / Q4_0 blocks of a row-major [rows, cols] tensor -> value plane
+ *   (int8 [rows, cols], or GGML-packed nibbles [rows, cols / 2]) and f16 scale plane
+ *   [rows, cols / 32], as GGUFReader::read_tensor_q8_separated / read_tensor_q4_separated return
+ *   them (interface/loader/gguf/gguf_reader.cpp:389-501).  cols % 32 == 0.
+ * cutb_transpose_2d: out[c * ldo + r] = in[r * ldi + c] for 1- or 2-byte elements (strides in
+ *   elements): the runner's CPU transposes of the value and scale planes into the matmul's
+ *   [K, N] orientation (interface/runner/llama/llama.cpp:934-1027).
+ * cutb_requant_q4k_affine: Q4_K rows -> nibbles [K, ldp bytes] (low nibble = even n) and f16 planes
+ *   [2 K / 32, lds]: rows [0, K / 32) = half(d sc), rows [K / 32, 2 K / 32) = half(8 d sc - dmin m),
+ *   with the runner's float -> half rounding (llama.cpp:445-482, 573-619).  K % 256 == 0, N even;
+ *   padding bytes of the outputs are not written.
+ * cutb_quantize_rows_q8_0: n floats (n % 32 == 0, 16-byte aligned) -> int8 values and f16 scales,
+ *   d = amax / 127, q = lround(x / d) (llama.cpp:488-505).
+ */
+CUTB_API int cutb_separate_blocks(int format, const void *raw, uint64_t raw_bytes, void *values, void *scales, uint64_t rows,
+                                  uint64_t cols, void *stream);
+CUTB_API int cutb_transpose_2d(uint32_t elem_bytes, const void *in, void *out, uint32_t rows, uint32_t cols, uint64_t ldi,
+                               uint64_t ldo, void *stream);
+CUTB_API int cutb_requant_q4k_affine(const void *raw, uint64_t raw_bytes, void *packedT, void *scalesT, uint32_t N, uint32_t K,
+                                     uint64_t ldp, uint64_t lds, void *stream);
+CUTB_API int cutb_quantize_rows_q8_0(const float *x, void *values, void *scales, uint64_t n, void *stream);
+
 CUTB_API int cutb_version(void);
 CUTB_API const char *cutb_status_string(int status);
 CUTB_API const char *cutb_last_error(void);
