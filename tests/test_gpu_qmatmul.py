@@ -388,3 +388,45 @@ def test_config3_q4_k_prefill_512x4096x14336():
         ref = _ref(synth.Q4_K, A, W[lo * rb:hi * rb], M, K, hi - lo)
         assert rel_l2(got[:, lo:hi], ref) <= TOL
     assert np.all(np.isfinite(got))
+
+
+# ---- size-independent properties at the benchmark configurations' full sizes ----
+@pytest.mark.parametrize("fmt,M,K,N", [(synth.Q8_0, 1, 4096, 4096), (synth.Q4_0, 1, 4096, 11008), (synth.Q4_0, 8, 4096, 11008),
+                                       (synth.Q4_K, 512, 4096, 14336)])
+def test_full_size_matmul_equals_dense_matmul_over_dequant(fmt, M, K, N):
+    """Every output of the fused kernels against an independent composition on the device: the
+    (bit-exact, separately tested) dequant operator followed by a float64 dense matmul."""
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev
+
+    A, W = _inputs(fmt, M, K, N, np.float16, seed=7 * M + fmt)
+    a_d, w_d = dev(A), dev(W)
+    got = ops.qmatmul(a_d, w_d, fmt, N)
+    dense = ops.dequantize(w_d, fmt, N, K).double()
+    ref = a_d.double() @ dense.T
+    torch.cuda.synchronize()
+    rel = float(torch.linalg.norm(got.double() - ref) / torch.linalg.norm(ref))
+    assert rel <= TOL
+    assert bool(torch.isfinite(got).all())
+
+
+@pytest.mark.parametrize("fmt,M,K,N", [(synth.Q4_0, 1, 4096, 11008), (synth.Q4_K, 512, 4096, 14336)])
+def test_full_size_linearity_in_the_activations(fmt, M, K, N):
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev
+
+    x, W = _inputs(fmt, M, K, N, np.float16, seed=11 + fmt)
+    y = synth.make_activations(M, K, 99, np.float16)
+    w_d = dev(W)
+    xd, yd = dev(x), dev(y)
+    comb = (2.0 * xd.float() - 3.0 * yd.float()).half()
+    lhs = ops.qmatmul(comb, w_d, fmt, N).double()
+    # the combination was rounded to fp16: compare against the same rounded vector's decomposition
+    rhs = 2.0 * ops.qmatmul(xd, w_d, fmt, N).double() - 3.0 * ops.qmatmul(yd, w_d, fmt, N).double()
+    torch.cuda.synchronize()
+    rel = float(torch.linalg.norm(lhs - rhs) / torch.linalg.norm(rhs))
+    assert rel <= 2e-3  # two extra fp16 roundings of the combined activations on top of the kernel's own tolerance
