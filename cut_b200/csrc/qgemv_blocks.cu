@@ -59,13 +59,17 @@ constexpr int GV_WARPS = 16;                      // consumer warps; one more wa
 constexpr int GV_THREADS = (GV_WARPS + 1) * 32;
 constexpr int GV_KC = GV_WARPS;                   // granules (256 weights) per row and stage, one per consumer warp
 
-// Shared-memory row stride of a stage (bytes): GV_KC granules plus the padding
-// that keeps the 8 row groups of a warp on disjoint banks for the access
-// pattern of the format (4 consecutive words per row for Q8_0 / Q4_0, 8 for Q4_K).
-__host__ __device__ constexpr int gv_row_stride(int fmt, bool diag) {
-  return fmt == CUTB_Q8_0 ? 16 * 272 + 16               // 1092 words = 4 (mod 32)
-         : (fmt == CUTB_Q4_0 || diag) ? 16 * 144 + 16   // 580 words = 4 (mod 32); Q4_K diagonal: 16-byte loads
-                                      : 16 * 144 + 32;  // 584 words = 8 (mod 32); Q4_K: 8-byte loads
+// Shared-memory layout of a stage: the 16 rows of a tile sit in 8 pairs, tile rows 2i and 2i + 1
+// back to back (one full row segment of GV_KC granules each), pairs GV pair-stride bytes apart.
+// MMA row g reads tile row 2g and MMA row g + 8 reads tile row 2g + 1 -- in different load
+// instructions, so the two rows of a pair may share banks, while the padding of the pair stride
+// keeps the 8 pairs of one instruction on disjoint banks (4 consecutive words per row for Q8_0 /
+// Q4_0 and the Q4_K diagonal variant, 8 for Q4_K shared-k).  Two rows that are adjacent in global
+// memory thus land adjacent in shared memory: when a stage holds whole rows, one bulk copy moves
+// a pair (the copy engine takes about as long to accept a copy whatever its size).
+__host__ __device__ constexpr int gv_raw_row(int fmt) { return GV_KC * (fmt == CUTB_Q8_0 ? 272 : 144); }
+__host__ __device__ constexpr int gv_pair_stride(int fmt, bool diag) {
+  return 2 * gv_raw_row(fmt) + ((fmt == CUTB_Q4_K && !diag) ? 32 : 16);  // = 4 or 8 words (mod 32)
 }
 
 struct GvParams {
@@ -202,11 +206,11 @@ __device__ __forceinline__ void block_mmas(int (&c)[4], int (&c2)[4], const uint
 // the diagonal variant.  `rowA`: shared address of row g's granule; actp/escp/sxp:
 // per-lane shared addresses of the lane's even block (see the kernel), pass_a /
 // pass_e: byte distance to its odd block (0 for lanes whose columns are idle).
-template <int FMT, int NVR, int RS>
+template <int FMT, int NVR>
 __device__ __forceinline__ void compute_granule_diag(uint32_t rowA, const uint32_t (&actp)[NVR], uint32_t pass_a,
                                                      const uint32_t (&escp)[NVR], const uint32_t (&sxp)[NVR],
                                                      uint32_t pass_e, uint32_t t, float (&tot)[NVR][2]) {
-  const uint32_t rowB = rowA + 8 * RS;
+  const uint32_t rowB = rowA + gv_raw_row(FMT);  // the pair's second row: MMA row g + 8
   // c / c2: two independent accumulation chains of the block's four MMAs
   auto finish = [&](int nt, const int (&c)[4], const int (&c2)[4], float sA, float sB, uint32_t eoff) {
     const float e = __uint_as_float(lds_u32(escp[nt] + eoff));
@@ -335,12 +339,12 @@ __device__ __forceinline__ void compute_granule_diag(uint32_t rowA, const uint32
 // One stage of one warp: 16 rows x ngr granules of raw blocks at shared
 // address `st`.  `actb` / `escb` / `sxb` point at the staged activations,
 // scales and (Q4_K) scaled sums of the first 32-k block of the stage.
-template <int FMT, int NT, int RS>
+template <int FMT, int NT, int PS>
 __device__ __forceinline__ void compute_stage(uint32_t st, uint32_t ngr, uint32_t actb, uint32_t act_stride,
                                               const uint32_t (&aoff)[NT], uint32_t escb, uint32_t sxb, uint32_t g,
                                               uint32_t t, float (&tot)[NT][2]) {
   constexpr uint32_t NV = NT * 4;
-  const uint32_t rowA = st + g * RS, rowB = rowA + 8 * RS;
+  const uint32_t rowA = st + g * PS, rowB = rowA + gv_raw_row(FMT);  // tile rows 2g and 2g + 1
 
   // scale the exact integer block dot products and accumulate in fp32
   auto accumulate = [&](uint32_t kb, float dA, float dB, const uint32_t (&fa)[2], const uint32_t (&fb)[2]) {
@@ -583,9 +587,10 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
 
 template <int FMT, bool AF32, int NT, bool DIAG>
 __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvParams p) {
-  constexpr int RS = gv_row_stride(FMT, DIAG);
+  constexpr int PS = gv_pair_stride(FMT, DIAG);
+  constexpr uint32_t RAWROW = gv_raw_row(FMT);
   constexpr uint32_t GB = granule_bytes(FMT);
-  constexpr uint32_t STAGE_BYTES = GV_ROWS * RS;
+  constexpr uint32_t STAGE_BYTES = (GV_ROWS / 2) * PS;
   constexpr uint32_t NV = DIAG ? NT : NT * 4, NC8 = NT * 8;
   extern __shared__ __align__(128) uint8_t smem[];
 
@@ -658,9 +663,15 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
         const uint32_t bar = full_u + (slot * HV + h) * 8;
         if (lane == 0) mbar_arrive_expect_tx(bar, valid * bytes);  // zero bytes: the phase completes at once
         __syncwarp();
-        if (bytes && lane < valid)
-          bulk_g2s(ring_u + slot * STAGE_BYTES + lane * RS + h * (GV_KC / HV) * GB,
+        if (HV == 1 && bytes == RAWROW && p.row_bytes == RAWROW) {
+          // the stage holds whole rows: tile rows 2i and 2i + 1 are one contiguous range, one copy per pair
+          if (2 * lane < valid)
+            bulk_g2s(ring_u + slot * STAGE_BYTES + lane * PS, p.W + (uint64_t)(row_base + 2 * lane) * p.row_bytes,
+                     (2 * lane + 1 < valid) ? 2 * RAWROW : RAWROW, bar);
+        } else if (bytes && lane < valid) {
+          bulk_g2s(ring_u + slot * STAGE_BYTES + (lane >> 1) * PS + (lane & 1) * RAWROW + h * (GV_KC / HV) * GB,
                    p.W + (uint64_t)(row_base + lane) * p.row_bytes + (uint64_t)gq * GB, bytes, bar);
+        }
       }
       if (++slot == S) slot = 0, par ^= 1u;
       if (++c == cpt) c = 0, ++tile;
@@ -723,10 +734,10 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
             escp[nt] = esc_u + ((kb0 + 2 * t) * NT + nt) * 4;
             sxp[nt] = sx_u + ((kb0 + 2 * t) * NT + nt) * 4;
           }
-          compute_granule_diag<FMT, NT, RS>(ring_u + slot * STAGE_BYTES + warp * GB + g * RS, actp, pass_a, escp, sxp,
+          compute_granule_diag<FMT, NT>(ring_u + slot * STAGE_BYTES + warp * GB + g * PS, actp, pass_a, escp, sxp,
                                             NT * 4, t, tot);
         } else {
-          compute_stage<FMT, NT, RS>(ring_u + slot * STAGE_BYTES + warp * GB, 1, act_u + kb0 * act_stride, act_stride,
+          compute_stage<FMT, NT, PS>(ring_u + slot * STAGE_BYTES + warp * GB, 1, act_u + kb0 * act_stride, act_stride,
                                      aoff, esc_u + kb0 * NV * 4, sx_u + kb0 * NV * 4, g, t, tot);
         }
       }
@@ -748,13 +759,13 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
         b += __shfl_xor_sync(0xffffffffu, b, 2);
         if (t == 0) {
           float *r = rbuf + ((size_t)warp * GV_ROWS) * NV + nt;
-          r[g * NV] = a;
-          r[(g + 8) * NV] = b;
+          r[(2 * g) * NV] = a;      // MMA row g = tile row 2g
+          r[(2 * g + 1) * NV] = b;  // MMA row g + 8 = tile row 2g + 1
         }
       } else {
         float *r = rbuf + ((size_t)warp * GV_ROWS) * NV + nt * 4 + t;
-        r[g * NV] = tot[nt][0];
-        r[(g + 8) * NV] = tot[nt][1];
+        r[(2 * g) * NV] = tot[nt][0];
+        r[(2 * g + 1) * NV] = tot[nt][1];
       }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
@@ -862,7 +873,7 @@ struct GvPlan {
 size_t gv_smem_bytes(int fmt, bool diag, uint32_t stages, uint32_t nt, uint32_t ncp, uint32_t gran_per_split) {
   const size_t nblk = (size_t)gran_per_split * 8;
   const size_t nv = diag ? nt : nt * 4;
-  size_t b = (size_t)stages * GV_ROWS * gv_row_stride(fmt, diag);
+  size_t b = (size_t)stages * (GV_ROWS / 2) * gv_pair_stride(fmt, diag);
   b += diag ? nblk * nt * 64 + 32 : nblk * ncp * 32;
   b += nblk * nv * 4 * (fmt != CUTB_Q8_0 ? 2 : 1);
   b += (size_t)2 * GV_WARPS * GV_ROWS * nv * 4;
