@@ -283,6 +283,38 @@ int cutb_quantize_rows_q8_0(const float *x, void *values, void *scales, uint64_t
   return quantize_rows_q8_0_launch(x, values, scales, n, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cutb_rmsnorm(int dtype, const void *x, const void *weight, void *y, uint32_t rows, uint32_t dim, uint64_t ldx, float eps,
+                 void *stream) {
+  if (dtype != CUTB_F32 && dtype != CUTB_F16) {
+    set_last_error("rmsnorm: dtype must be fp32 or fp16");
+    return CUTB_ERR_INVALID;
+  }
+  if (rows == 0 || dim == 0) return CUTB_OK;
+  if (!x || !weight || !y || ldx < dim) {
+    set_last_error("rmsnorm: null pointer or row stride shorter than the row");
+    return CUTB_ERR_INVALID;
+  }
+  return rmsnorm_launch(dtype, x, weight, y, rows, dim, ldx, eps, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_embedding(const uint32_t *indices, const float *table, float *out, uint64_t n, uint32_t dim, uint32_t vocab, int *status,
+                   void *stream) {
+  if (n == 0 || dim == 0) return CUTB_OK;
+  if (!indices || !table || !out || reinterpret_cast<uintptr_t>(table) % 16 || reinterpret_cast<uintptr_t>(out) % 16) {
+    set_last_error("embedding: null pointer, or table / output not 16-byte aligned");
+    return CUTB_ERR_INVALID;
+  }
+  return embedding_launch(indices, table, out, n, dim, vocab, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_argreduce(int is_max, const float *values, float *out, uint32_t n, void *stream) {
+  if (!out || (n && !values)) {
+    set_last_error("argreduce: null pointer");
+    return CUTB_ERR_INVALID;
+  }
+  return argreduce_launch(is_max, values, out, n, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                  void *stream) {
   if (format < CUTB_Q8_0 || format > CUTB_BF16) {

@@ -28,6 +28,13 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
 
 int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                    cudaStream_t stream);
+// Layer operators next to the matmul (layer_ops.cu).
+int rmsnorm_launch(int dtype, const void *x, const void *weight, void *y, uint32_t rows, uint32_t dim, uint64_t ldx, float eps,
+                   cudaStream_t stream);
+int embedding_launch(const uint32_t *indices, const float *table, float *out, uint64_t n, uint32_t dim, uint32_t vocab, int *status,
+                     cudaStream_t stream);
+int argreduce_launch(int is_max, const float *v, float *out, uint32_t n, cudaStream_t stream);
+
 // Load-time repacks (repack.cu), bit-exact with the reference's CPU loader / runner code.
 int separate_launch(int format, const void *raw, void *values, void *scales, uint64_t rows, uint64_t cols, cudaStream_t stream);
 int transpose_launch(uint32_t elem_bytes, const void *in, void *out, uint32_t R, uint32_t C, uint64_t ldi, uint64_t ldo,

@@ -139,3 +139,32 @@ def quantize_rows_q8_0(x: torch.Tensor):
     scales = torch.empty(x.numel() // 32, dtype=torch.int16, device=x.device)
     L.check(L.lib().cutb_quantize_rows_q8_0(x.data_ptr(), vals.data_ptr(), scales.data_ptr(), x.numel(), _stream_ptr()))
     return vals, scales
+
+
+# ---- layer operators next to the matmul ----
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """y = x * rsqrt(mean(x^2) + eps) * weight over the last dimension (fp32 or fp16, 1-D or 2-D)."""
+    x2 = x if x.dim() == 2 else x.view(1, -1)
+    if x2.stride(1) != 1 or weight.dtype != x.dtype:
+        raise RuntimeError("rmsnorm: contiguous rows and a weight of the input's dtype")
+    y = torch.empty_like(x2)
+    dt = L.F16 if x.dtype == torch.float16 else L.F32
+    L.check(L.lib().cutb_rmsnorm(dt, x2.data_ptr(), weight.data_ptr(), y.data_ptr(), x2.shape[0], x2.shape[1], x2.stride(0), eps,
+                                 _stream_ptr()))
+    return y.view_as(x)
+
+
+def embedding(indices: torch.Tensor, table: torch.Tensor, dim: int | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """table [vocab, pad4(dim)] float32, indices int32 -> [n, pad4(dim)]."""
+    dim = table.shape[1] if dim is None else dim
+    out = torch.empty((indices.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    L.check(L.lib().cutb_embedding(indices.data_ptr(), table.data_ptr(), out.data_ptr(), indices.numel(), dim, table.shape[0],
+                                   status.data_ptr() if status is not None else None, _stream_ptr()))
+    return out
+
+
+def argreduce(values: torch.Tensor, is_max: bool = True) -> torch.Tensor:
+    """Index of the maximum / minimum as a one-element float tensor (the reference's output type and tie rule)."""
+    out = torch.empty(1, dtype=torch.float32, device=values.device)
+    L.check(L.lib().cutb_argreduce(1 if is_max else 0, values.data_ptr(), out.data_ptr(), values.numel(), _stream_ptr()))
+    return out

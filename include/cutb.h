@@ -232,6 +232,28 @@ CUTB_API int cutb_requant_q4k_affine(const void *raw, uint64_t raw_bytes, void *
                                      uint64_t ldp, uint64_t lds, void *stream);
 CUTB_API int cutb_quantize_rows_q8_0(const float *x, void *values, void *scales, uint64_t n, void *stream);
 
+/*
+ * The operators on either side of the matmul in a decoder layer (first steps past the matmul
+ * path; per token they move a few KB to a few hundred KB against the gigabytes of weights).
+ *
+ * cutb_rmsnorm: y[r, i] = x[r, i] * rsqrt(mean_i(x[r, i]^2) + eps) * weight[i] for `rows` rows of
+ *   `dim` elements, row stride ldx elements, fp32 or fp16 (a_dtype codes), fp32 accumulation
+ *   (RMSNormOpNode: operators/impl/rmsnorm/RMSNormOp.cpp:7-76, RMSNorm.cu:6-37; the reference
+ *   pads the row stride to 4).
+ * cutb_embedding: out[i, :] = table[indices[i], :], rows of pad4(dim) floats, 16-byte aligned
+ *   (operators/impl/memory/Embedding.cu:18-35).  An index >= vocab writes zeros and sets *status
+ *   to CUTB_ERR_INVALID instead of reading outside the table (the reference does not check).
+ * cutb_argreduce: index of the maximum (is_max) or minimum of n floats, written as a float to
+ *   out[0], with the reference's tie rule (the outcome of its 256-thread strided scan and
+ *   shared-memory tree): among equal extremes the smallest bit-reversed (i mod 256) wins, then
+ *   the smallest i (operators/impl/reduce/ReduceArg.cu:27-59).
+ */
+CUTB_API int cutb_rmsnorm(int dtype, const void *x, const void *weight, void *y, uint32_t rows, uint32_t dim, uint64_t ldx,
+                          float eps, void *stream);
+CUTB_API int cutb_embedding(const uint32_t *indices, const float *table, float *out, uint64_t n, uint32_t dim, uint32_t vocab,
+                            int *status, void *stream);
+CUTB_API int cutb_argreduce(int is_max, const float *values, float *out, uint32_t n, void *stream);
+
 CUTB_API int cutb_version(void);
 CUTB_API const char *cutb_status_string(int status);
 CUTB_API const char *cutb_last_error(void);

@@ -680,3 +680,54 @@ ORC_API void orc_set_num_threads(int n) {
   (void)n;
 #endif
 }
+
+/* ------------------------------------------------------------------------- */
+/* First steps past the matmul path: the producer / consumers of its operands  */
+/* in a decoder layer.                                                        */
+/* ------------------------------------------------------------------------- */
+
+/* operators/impl/rmsnorm/RMSNorm.cu:6-37 -- y = x * rsqrt(mean(x^2) + eps) * weight per row of
+ * `dim` floats (row stride ldx); the sum of squares is accumulated in double here, so the
+ * checker is the more exact side of a tolerance comparison. */
+ORC_API void orc_rmsnorm(const float *x, const float *weight, float *y, size_t rows, size_t dim, size_t ldx, float eps) {
+  for (size_t r = 0; r < rows; ++r) {
+    const float *xr = x + r * ldx;
+    double ss = 0.0;
+    for (size_t i = 0; i < dim; ++i) ss += (double)xr[i] * (double)xr[i];
+    double scale = 1.0 / sqrt(ss / (double)dim + (double)eps);
+    for (size_t i = 0; i < dim; ++i) y[r * ldx + i] = (float)((double)xr[i] * scale * (double)weight[i]);
+  }
+}
+
+/* operators/impl/memory/Embedding.cu:18-35 -- out[i, :] = table[indices[i], :], rows padded to 4 floats. */
+ORC_API void orc_embedding(const uint32_t *indices, const float *table, float *out, size_t n, size_t dim) {
+  size_t ld = (dim + 3) & ~(size_t)3;
+  for (size_t i = 0; i < n; ++i) memcpy(out + i * ld, table + (size_t)indices[i] * ld, ld * sizeof(float));
+}
+
+/* operators/impl/reduce/ReduceArg.cu:27-59 -- arg-max / arg-min with the reference's tie rule:
+ * 256 threads scan i = t, t + 256, ... keeping the FIRST strictly better value, then a
+ * shared-memory tree (strides 128 .. 1) keeps the lower position on ties; both steps are replayed
+ * here literally.  (Among equal extremes that prefers the smallest bit-reversed i % 256, then the
+ * smallest i.)  The result is returned as a float. */
+ORC_API float orc_argreduce(const float *v, size_t n, int is_max) {
+  float best[256];
+  uint32_t idx[256];
+  for (int t = 0; t < 256; ++t) {
+    best[t] = is_max ? -3.402823466e+38f : 3.402823466e+38f;
+    idx[t] = 0;
+    for (size_t i = (size_t)t; i < n; i += 256)
+      if (is_max ? v[i] > best[t] : v[i] < best[t]) {
+        best[t] = v[i];
+        idx[t] = (uint32_t)i;
+      }
+  }
+  for (int stride = 128; stride > 0; stride >>= 1)
+    for (int t = 0; t < stride; ++t)
+      if (is_max ? best[t + stride] > best[t] : best[t + stride] < best[t]) {
+        best[t] = best[t + stride];
+        idx[t] = idx[t + stride];
+      }
+  return (float)idx[0];
+}
+

@@ -50,6 +50,7 @@ def lib() -> C.CDLL:
         _lib.orc_epilogue.restype = C.c_float
         _lib.orc_epilogue.argtypes = [C.c_float, C.c_int, C.c_int, C.c_float]
         _lib.orc_requant_q4k_affine.restype = C.c_int
+        _lib.orc_argreduce.restype = C.c_float
         _lib.orc_num_threads.restype = C.c_int
     return _lib
 
@@ -288,3 +289,28 @@ def ref_separate(fmt: int, raw, rows: int, cols: int):
         return vals, scales
 
     return _with_gguf(fmt, raw, rows, cols, run)
+
+
+# ------------------------------------------------------ layer ops next to the matmul
+def rmsnorm(x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    rows, dim = (1, x.shape[0]) if x.ndim == 1 else x.shape
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    y = np.empty_like(x)
+    lib().orc_rmsnorm(_p(x), _p(w), _p(y), C.c_size_t(rows), C.c_size_t(dim), C.c_size_t(dim), C.c_float(eps))
+    return y
+
+
+def embedding(indices: np.ndarray, table: np.ndarray) -> np.ndarray:
+    """table [vocab, pad4(dim)] float32 -> [n, pad4(dim)]."""
+    idx = np.ascontiguousarray(indices, dtype=np.uint32)
+    t = np.ascontiguousarray(table, dtype=np.float32)
+    out = np.empty((idx.size, t.shape[1]), dtype=np.float32)
+    lib().orc_embedding(_p(idx), _p(t), _p(out), C.c_size_t(idx.size), C.c_size_t(t.shape[1]))
+    return out
+
+
+def argreduce(v: np.ndarray, is_max: bool = True) -> float:
+    v = np.ascontiguousarray(v, dtype=np.float32).reshape(-1)
+    return float(lib().orc_argreduce(_p(v), C.c_size_t(v.size), C.c_int(1 if is_max else 0)))
+

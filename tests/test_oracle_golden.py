@@ -192,3 +192,27 @@ def test_epilogue_ops():
     assert O.epilogue(2.0, 2, 0, 5.0) == 7.0  # residual add
     assert O.epilogue(2.0, 2, 2, 5.0) == 10.0
     assert O.epilogue(2.0, 0, 0, 5.0) == 2.0
+
+
+def test_argreduce_replay_equals_the_bit_reversal_rule():
+    """The checker replays the reference's 256-thread scan and shared-memory tree literally
+    (ReduceArg.cu:27-59); in closed form that prefers, among equal extremes, the smallest
+    bit-reversed (i mod 256), then the smallest i."""
+    rng = np.random.default_rng(3)
+    brev = lambda t: int(f"{t:08b}"[::-1], 2)
+    for _ in range(30):
+        n = int(rng.integers(1, 3000))
+        v = rng.integers(-2, 3, n).astype(np.float32)
+        for is_max in (True, False):
+            ext = v.max() if is_max else v.min()
+            cands = np.flatnonzero(v == ext)
+            want = min(cands, key=lambda i: (brev(int(i) % 256), int(i)))
+            assert O.argreduce(v, is_max) == float(want)
+
+
+def test_rmsnorm_and_embedding_checker():
+    x = np.arange(1, 9, dtype=np.float32)
+    y = O.rmsnorm(x, np.full(8, 2.0, np.float32), 0.0)
+    assert np.allclose(y, 2.0 * x / np.sqrt(np.mean(x ** 2)), rtol=1e-6)
+    table = np.arange(40, dtype=np.float32).reshape(5, 8)
+    assert np.array_equal(O.embedding(np.array([4, 0, 4], np.uint32), table), table[[4, 0, 4]])
