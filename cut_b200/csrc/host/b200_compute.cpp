@@ -189,6 +189,7 @@ public:
     if (!desc) throw std::runtime_error("B200Compute: not a kernel descriptor");
     switch (desc->op) {
       case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case TransposeQ4: break;
+      case RMSNorm: case Embedding: case ReduceArgmax: case ReduceArgmin: break;
       default: throw std::runtime_error("B200Compute: no kernel for operator " + std::to_string(desc->op));
     }
     if (desc->op == Dequantize || desc->op == MatMulQBlocks) (void)cutbFormat(desc->format);
@@ -371,6 +372,25 @@ private:
         } pc = pushConstants<PC>(d);
         const DeviceBuffer &in = buf(d, 0), &out = buf(d, 1);
         cutbCheck(cutb_transpose_q4(in.data, out.data, pc.N, pc.K, pc.strideInHalf, pc.strideOutHalf, stream_), "TransposeQ4");
+      } else if (k.op == RMSNorm) {
+        struct PC {
+          uint32_t dim, alignedDim;
+          float eps;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &x = buf(d, 0), &w = buf(d, 1), &y = buf(d, 2);
+        cutbCheck(cutb_rmsnorm(k.dtypeA == (uint32_t)DataType::Float16 ? CUTB_F16 : CUTB_F32, x.data, w.data, y.data, d.size.y,
+                               pc.dim, pc.alignedDim, pc.eps, stream_), "RMSNorm");
+      } else if (k.op == Embedding) {
+        struct PC {
+          uint32_t numIndices, embDim;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &idx = buf(d, 0), &table = buf(d, 1), &out = buf(d, 2);
+        cutbCheck(cutb_embedding((const uint32_t *)idx.data, (const float *)table.data, (float *)out.data, pc.numIndices,
+                                 pc.embDim, table.getShape()[0], status_, stream_), "Embedding");
+      } else if (k.op == ReduceArgmax || k.op == ReduceArgmin) {
+        const uint32_t n = pushConstants<uint32_t>(d);
+        cutbCheck(cutb_argreduce(k.op == ReduceArgmax, (const float *)buf(d, 0).data, (float *)buf(d, 1).data, n, stream_),
+                  "ReduceArg");
       } else {
         throw std::runtime_error("B200Compute: no kernel for dispatch " + d.label);
       }

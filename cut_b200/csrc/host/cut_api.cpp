@@ -463,6 +463,124 @@ std::vector<uint8_t> TransposeQ4NibbleOpNode::pushConstants() const {
 }
 
 // ---------------------------------------------------------------------------
+// RMSNormOpNode / EmbeddingOpNode / GlobalReduceOpNode: the layer operators next to the matmul
+// ---------------------------------------------------------------------------
+RMSNormOpNode::RMSNormOpNode(TensorStore &store, const Tensor &x, const Tensor &weight, float eps,
+                             std::optional<uint32_t> spec)
+    : OpNode(RMSNorm, store, spec), eps_(eps) {
+  const auto &bx = store.getTensor(x);
+  const auto &bw = store.getTensor(weight);
+  const auto &sx = bx.getShape();
+  const auto &sw = bw.getShape();
+  dtype_ = bx.getDtype();
+  if (sx.empty() || sx.size() > 2 || sw.size() != 1) throw std::runtime_error("RMSNorm requires 1D or 2D input, 1D weight");
+  batchSize_ = sx.size() == 2 ? sx[0] : 1;
+  dim_ = sx.back();
+  if (sw[0] != dim_) throw std::runtime_error("RMSNorm: weight dimension must match input");
+  if (bw.getDtype() != dtype_) throw std::runtime_error("RMSNorm: weight must have same dtype as input");
+  alignedDim_ = (dim_ + 3) & ~3u;
+  inputs_ = {x, weight};
+  output_ = store.createTensorEmpty(outputShape(), dtype_);
+}
+
+std::vector<uint32_t> RMSNormOpNode::outputShape() const {
+  if (batchSize_ > 1) return {batchSize_, dim_};
+  return {dim_};
+}
+
+std::optional<std::vector<uint32_t>> RMSNormOpNode::shader() const {
+  if (dtype_ != DataType::Float32 && dtype_ != DataType::Float16) return std::nullopt;
+  KernelDesc d;
+  d.op = RMSNorm;
+  d.dtypeA = d.dtypeB = (uint32_t)dtype_;
+  return d.encode();
+}
+
+std::vector<uint8_t> RMSNormOpNode::pushConstants() const {
+  struct {
+    uint32_t dim, alignedDim;
+    float eps;
+  } pc{dim_, alignedDim_, eps_};
+  return toBytes(pc);
+}
+
+EmbeddingOpNode::EmbeddingOpNode(TensorStore &store, const Tensor &indices, const Tensor &weight,
+                                 const Tensor &preallocOutput, std::optional<uint32_t> spec)
+    : OpNode(Embedding, store, spec) {
+  const auto &bi = store.getTensor(indices);
+  const auto &bw = store.getTensor(weight);
+  dtype_ = bw.getDtype();
+  if (bw.getShape().size() != 2)
+    throw std::runtime_error("embedding: weight must be 2D [num_embeddings, embedding_dim]");
+  embDim_ = bw.getShape()[1];
+  for (uint32_t d : bi.getShape()) numIndices_ *= d;
+  outShape_ = bi.getShape();
+  outShape_.push_back(embDim_);
+  inputs_ = {indices, weight};
+  output_ = preallocOutput ? preallocOutput : store.createTensorEmpty(outShape_, dtype_);
+}
+
+std::optional<std::vector<uint32_t>> EmbeddingOpNode::shader() const {
+  if (dtype_ != DataType::Float32) return std::nullopt;  // the table kernel gathers fp32 rows
+  KernelDesc d;
+  d.op = Embedding;
+  d.dtypeA = d.dtypeB = (uint32_t)dtype_;
+  return d.encode();
+}
+
+ThreadSize EmbeddingOpNode::dispatchSize() const {
+  const uint32_t vec4PerRow = ((embDim_ + 3) & ~3u) / 4;
+  return {(numIndices_ * vec4PerRow + 255) / 256 * 256, 1, 1};
+}
+
+std::vector<uint8_t> EmbeddingOpNode::pushConstants() const {
+  struct {
+    uint32_t numIndices, embDim;
+  } pc{numIndices_, embDim_};
+  return toBytes(pc);
+}
+
+GlobalReduceOpNode::GlobalReduceOpNode(OperatorEnum op, TensorStore &store, const Tensor &a, std::optional<uint32_t> spec)
+    : OpNode(op, store, spec) {
+  const auto &b = store.getTensor(a);
+  dtype_ = b.getDtype();
+  numElements_ = 1;
+  for (uint32_t d : b.getShape()) numElements_ *= d;
+  actualInner_ = b.innerDimSize();
+  alignedInner_ = b.innerDimPadded();
+  inputs_ = {a};
+  output_ = store.createTensorEmpty({1}, dtype_);
+}
+
+std::optional<std::vector<uint32_t>> GlobalReduceOpNode::shader() const {
+  if ((op_ != ReduceArgmax && op_ != ReduceArgmin) || dtype_ != DataType::Float32) return std::nullopt;
+  KernelDesc d;
+  d.op = op_;
+  d.dtypeA = d.dtypeB = (uint32_t)dtype_;
+  return d.encode();
+}
+
+std::vector<uint8_t> GlobalReduceOpNode::pushConstants() const {
+  if (op_ == ReduceArgmax || op_ == ReduceArgmin) return toBytes(static_cast<uint32_t>(numElements_));
+  struct {
+    uint32_t numElements, actualInner, alignedInner;
+  } pc{static_cast<uint32_t>(numElements_), actualInner_, alignedInner_};
+  return toBytes(pc);
+}
+
+std::string GlobalReduceOpNode::displayName() const {
+  switch (op_) {
+    case ReduceArgmax: return "ReduceArgmax";
+    case ReduceArgmin: return "ReduceArgmin";
+    case ReduceSum: return "ReduceSum";
+    case ReduceMean: return "ReduceMean";
+    case ReduceMin: return "ReduceMin";
+    case ReduceMax: return "ReduceMax";
+    default: return "Reduce";
+  }
+}
+
+// ---------------------------------------------------------------------------
 // VariantSelector (runtime/VariantSelector.cpp:242-428) with a small JSON reader
 // ---------------------------------------------------------------------------
 namespace {
@@ -730,6 +848,19 @@ Tensor Operations::transposeQ4(const Tensor &packedInput, uint32_t N, uint32_t K
 
 Tensor Operations::dequantize(const Tensor &rawData, uint32_t format, uint32_t rows, uint32_t cols) {
   return dispatch(std::make_unique<DequantOpNode>(*store_, rawData, static_cast<DequantFormat>(format), rows, cols));
+}
+
+Tensor Operations::rmsNorm(const Tensor &x, const Tensor &weight, float eps, std::optional<uint32_t> spec) {
+  return dispatch(std::make_unique<RMSNormOpNode>(*store_, x, weight, eps, spec));
+}
+
+Tensor Operations::embedding(const Tensor &indices, const Tensor &weight, const Tensor &preallocOutput,
+                             std::optional<uint32_t> spec) {
+  return dispatch(std::make_unique<EmbeddingOpNode>(*store_, indices, weight, preallocOutput, spec));
+}
+
+Tensor Operations::reduce(OperatorEnum op, const Tensor &a, std::optional<uint32_t> spec) {
+  return dispatch(std::make_unique<GlobalReduceOpNode>(op, *store_, a, spec));
 }
 
 Runtime::Runtime(std::unique_ptr<ComputeInterface> iface)

@@ -67,6 +67,8 @@ enum OperatorEnum : uint32_t {
   UnaryLog = 109, UnaryTanh = 121, UnaryFloor = 122, UnaryCeil = 123, UnaryRound = 124, UnaryRelu = 130,
   UnarySigmoid = 131, UnaryGelu = 132, UnarySilu = 133, UnarySoftplus = 134, UnaryRelu6 = 137, UnaryMish = 141,
   UnaryHardswish = 142, UnaryHardsigmoid = 143, UnaryRsqrt = 148,
+  ReduceSum = 208, ReduceMean = 209, ReduceMin = 210, ReduceMax = 211, ReduceArgmax = 214, ReduceArgmin = 215,
+  RMSNorm = 312, Embedding = 320,
   MatMulQ8 = 371, MatMulQ4 = 374,
   MatMulQBlocks = 375,  // new: weights as raw GGUF blocks
   Dequantize = 390, TransposeQ4 = 401,
@@ -375,6 +377,64 @@ private:
   uint32_t N_, K_, strideInHalf_, strideOutHalf_;
 };
 
+/// Row-wise RMS normalisation with a weight vector (operators/impl/rmsnorm/RMSNormOp.cpp:7-76):
+/// x is [dim] or [batch, dim], weight [dim] of the same dtype; one 256-thread group per row.
+class RMSNormOpNode : public OpNode {
+public:
+  RMSNormOpNode(TensorStore &store, const Tensor &x, const Tensor &weight, float eps = 1e-5f,
+                std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return dtype_; }
+  size_t shaderKey() const override { return static_cast<size_t>(op_) | (static_cast<size_t>(dtype_) << 16); }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override;
+  ThreadSize dispatchSize() const override { return {256, batchSize_, 1}; }
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "RMSNorm"; }
+
+private:
+  DataType dtype_ = DataType::Float32;
+  uint32_t batchSize_ = 1, dim_ = 0, alignedDim_ = 0;
+  float eps_;
+};
+
+/// Row gather out[i, :] = weight[indices[i], :] (operators/impl/memory/MemoryOp.cpp:68-125).
+class EmbeddingOpNode : public OpNode {
+public:
+  EmbeddingOpNode(TensorStore &store, const Tensor &indices, const Tensor &weight, const Tensor &preallocOutput = {},
+                  std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return dtype_; }
+  size_t shaderKey() const override { return static_cast<size_t>(op_) | (static_cast<size_t>(dtype_) << 16); }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return outShape_; }
+  ThreadSize dispatchSize() const override;
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "Embedding"; }
+
+private:
+  DataType dtype_ = DataType::Float32;
+  uint32_t embDim_ = 0, numIndices_ = 1;
+  std::vector<uint32_t> outShape_;
+};
+
+/// Whole-tensor reduction to one element (operators/impl/reduce/ReduceOp.cpp:29-91).  Only the two
+/// index reductions the sampler uses have a kernel here; the others construct but have no shader.
+class GlobalReduceOpNode : public OpNode {
+public:
+  GlobalReduceOpNode(OperatorEnum op, TensorStore &store, const Tensor &a, std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return dtype_; }
+  size_t shaderKey() const override { return static_cast<size_t>(op_) | (static_cast<size_t>(dtype_) << 16); }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return {1}; }
+  ThreadSize dispatchSize() const override { return {256, 1, 1}; }
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override;
+
+private:
+  DataType dtype_ = DataType::Float32;
+  size_t numElements_ = 0;
+  uint32_t actualInner_ = 0, alignedInner_ = 0;
+};
+
 // ---- VariantSelector: tuning_data.json rules (runtime/VariantSelector.cpp:242-428) ----------
 class VariantSelector {
 public:
@@ -418,7 +478,7 @@ private:
   Tensor getOrCreateShader(const OpNode &node);
 };
 
-// ---- Operations (the five methods of the path) and a minimal Runtime ---------------------
+// ---- Operations (the methods of the path and of its neighbours in a layer) and a minimal Runtime ---------------------
 class Operations {
 public:
   Operations(TensorStore *store, Dispatcher *dispatcher) : store_(store), dispatcher_(dispatcher) {}
@@ -436,6 +496,11 @@ public:
                             uint32_t N, const Tensor &d, std::optional<uint32_t> spec = {});
   Tensor transposeQ4(const Tensor &packedInput, uint32_t N, uint32_t K);
   Tensor dequantize(const Tensor &rawData, uint32_t format, uint32_t rows, uint32_t cols);
+  Tensor rmsNorm(const Tensor &x, const Tensor &weight, float eps = 1e-5f, std::optional<uint32_t> spec = {});
+  Tensor embedding(const Tensor &indices, const Tensor &weight, const Tensor &preallocOutput = {},
+                   std::optional<uint32_t> spec = {});
+  /// Whole-tensor reduction (the reference's per-dimension form is outside this path).
+  Tensor reduce(OperatorEnum op, const Tensor &a, std::optional<uint32_t> spec = {});
   void barrier() { dispatcher_->encodeBarrier(); }
 
 private:

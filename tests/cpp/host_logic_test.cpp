@@ -310,7 +310,66 @@ void variantSelectorRules() {
 
 }  // namespace
 
+// RMSNormOpNode / EmbeddingOpNode / GlobalReduceOpNode: validation, geometry and recorded dispatches
+void layerOperatorNodes() {
+  Fixture f;
+  TensorStore &s = f.rt.store();
+  auto x1 = s.createTensor({10}, DataType::Float32), x2 = s.createTensor({3, 10}, DataType::Float32);
+  auto w = s.createTensor({10}, DataType::Float32), wh = s.createTensor({10}, DataType::Float16);
+  RMSNormOpNode n1(s, x1, w), n2(s, x2, w, 1e-6f);
+  CHECK(n1.outputShape() == (std::vector<uint32_t>{10}) && n2.outputShape() == (std::vector<uint32_t>{3, 10}));
+  CHECK(n2.dispatchSize().x == 256 && n2.dispatchSize().y == 3 && n1.dispatchSize().y == 1);
+  struct {
+    uint32_t dim, alignedDim;
+    float eps;
+  } pc;
+  auto b = n2.bindings();
+  CHECK(b.size() == 4 && b[2].handle == n2.output() && b[3].bytes.size() == sizeof(pc));
+  std::memcpy(&pc, b[3].bytes.data(), sizeof(pc));
+  CHECK(pc.dim == 10 && pc.alignedDim == 12 && pc.eps == 1e-6f);
+  CHECK(n1.op() == RMSNorm && n1.displayName() == "RMSNorm" && n1.shader().has_value());
+  CHECK_THROWS(RMSNormOpNode(s, s.createTensor({1, 3, 10}, DataType::Float32), w), "1D or 2D input, 1D weight");
+  CHECK_THROWS(RMSNormOpNode(s, x1, x2), "1D or 2D input, 1D weight");
+  CHECK_THROWS(RMSNormOpNode(s, x1, s.createTensor({12}, DataType::Float32)), "weight dimension must match");
+  CHECK_THROWS(RMSNormOpNode(s, x1, wh), "same dtype");
+  CHECK(RMSNormOpNode(s, s.createTensor({10}, DataType::Float16), wh).shaderKey() != n1.shaderKey());
+
+  auto table = s.createTensor({50, 6}, DataType::Float32), idx = s.createTensor({2, 5}, DataType::UInt32);
+  EmbeddingOpNode e(s, idx, table);
+  CHECK(e.outputShape() == (std::vector<uint32_t>{2, 5, 6}) && e.outputDtype() == DataType::Float32);
+  CHECK(e.dispatchSize().x == 256 && e.dispatchSize().y == 1);  // 10 rows x 2 vec4 -> one group of 256
+  uint32_t epc[2];
+  std::memcpy(epc, e.bindings().back().bytes.data(), sizeof(epc));
+  CHECK(epc[0] == 10 && epc[1] == 6);
+  auto pre = s.createTensor({2, 5, 6}, DataType::Float32);
+  CHECK(EmbeddingOpNode(s, idx, table, pre).output() == pre);
+  CHECK_THROWS(EmbeddingOpNode(s, idx, w), "weight must be 2D");
+  CHECK(!EmbeddingOpNode(s, idx, s.createTensor({50, 6}, DataType::Float16)).shader().has_value());
+
+  GlobalReduceOpNode am(ReduceArgmax, s, s.createTensor({1, 1000}, DataType::Float32));
+  CHECK(am.outputShape() == (std::vector<uint32_t>{1}) && am.dispatchSize().x == 256 && am.displayName() == "ReduceArgmax");
+  uint32_t n = 0;
+  CHECK(am.bindings().back().bytes.size() == 4);
+  std::memcpy(&n, am.bindings().back().bytes.data(), 4);
+  CHECK(n == 1000);
+  CHECK(GlobalReduceOpNode(ReduceSum, s, x2).bindings().back().bytes.size() == 12);
+  CHECK(am.shaderKey() != GlobalReduceOpNode(ReduceArgmin, s, x1).shaderKey());
+
+  const size_t before = f.raw->modules;
+  auto y = f.rt.ops().rmsNorm(x2, w);
+  f.rt.ops().rmsNorm(x2, w);  // same kernel: one module
+  auto emb = f.rt.ops().embedding(idx, table);
+  auto arg = f.rt.ops().reduce(ReduceArgmin, x1);
+  CHECK(f.raw->modules == before + 3);
+  CHECK(f.rt.getTensor(y).getShape() == (std::vector<uint32_t>{3, 10}) && f.rt.getTensor(arg).getShape() == (std::vector<uint32_t>{1}));
+  CHECK(f.rt.getTensor(emb).getShape() == (std::vector<uint32_t>{2, 5, 6}));
+  CHECK_THROWS(f.rt.ops().reduce(ReduceSum, x1), "no shader");
+  f.rt.flush();
+  CHECK(f.raw->executed.size() == 4 && f.raw->executed[2].label == "Embedding" && f.raw->executed[3].label == "ReduceArgmin");
+}
+
 int main() {
+  RUN(layerOperatorNodes);
   RUN(bufferGeometry);
   RUN(quantFormatDetectionAndVariants);
   RUN(shapeErrors);

@@ -18,6 +18,8 @@ void orc_qmatmul_blocks(int fmt, const float *A, const uint8_t *W, float *C, con
 void orc_dequant_rows(int fmt, const uint8_t *data, float *out, size_t rows, size_t cols, size_t ldo);
 uint16_t orc_f32_to_f16_trunc(float v);
 uint16_t orc_f32_to_f16_runner(float v);
+void orc_rmsnorm(const float *x, const float *weight, float *y, size_t rows, size_t dim, size_t ldx, float eps);
+float orc_argreduce(const float *v, size_t n, int is_max);
 }
 
 namespace {
@@ -344,6 +346,96 @@ void errorBehaviour() {
   CHECK(rt->iface().bufferCount() > 0 && rt->iface().deviceTotalMemoryBytes() > (size_t)100 << 30);
 }
 
+// RMSNorm through Operations::rmsNorm (cases of OpCoverageTests.cpp:146-178 and
+// RuntimeTests.cpp:3182-3209: 1-D known values, weighted rows, 13 x 5120 against fp64)
+void rmsNormCases() {
+  auto run = [&](uint32_t rows, uint32_t dim, const std::vector<float> &x, const std::vector<float> &w, bool oneD, float rel, float abs) {
+    auto a = oneD ? rt->createTensor({dim}, DataType::Float32, x.data()) : rt->createTensor({rows, dim}, DataType::Float32, x.data());
+    auto wt = rt->createTensor({dim}, DataType::Float32, w.data());
+    auto out = rt->ops().rmsNorm(a, wt, 1e-5f);
+    std::vector<float> got(rows * dim), want(rows * dim);
+    rt->copyFromTensor(out, got.data(), got.size() * sizeof(float));
+    orc_rmsnorm(x.data(), w.data(), want.data(), rows, dim, dim, 1e-5f);
+    int bad = 0;
+    for (uint32_t r = 0; r < rows; ++r) {
+      double ss = 0;
+      for (uint32_t i = 0; i < dim; ++i) ss += (double)x[r * dim + i] * x[r * dim + i];
+      const double sc = 1.0 / std::sqrt(ss / dim + 1e-5);
+      for (uint32_t i = 0; i < dim; ++i) {
+        const double e = x[r * dim + i] * sc * w[i];
+        if (!(std::abs(got[r * dim + i] - e) <= std::abs(e) * rel + abs)) ++bad;
+        if (!(std::abs(want[r * dim + i] - e) <= std::abs(e) * rel + abs)) ++bad;
+      }
+    }
+    CHECK(bad == 0);
+  };
+  run(1, 4, {1.f, 2.f, 3.f, 4.f}, {1.f, 1.f, 1.f, 1.f}, true, 0.f, 1e-4f);
+  run(2, 4, {1.f, 2.f, 3.f, 4.f, 2.f, 4.f, 6.f, 8.f}, {0.5f, 1.0f, 1.5f, 2.0f}, false, 0.f, 1e-4f);
+  const uint32_t N = 13, dim = 5120;
+  std::mt19937 gen(7);
+  std::uniform_real_distribution<float> dist(-1.0f, 1.0f);
+  std::vector<float> hidden(N * dim), weight(dim);
+  for (auto &v : hidden) v = dist(gen);
+  for (auto &v : weight) v = dist(gen) * 0.1f + 1.0f;
+  run(N, dim, hidden, weight, false, 1e-3f, 1e-4f);
+  run(3, 10, std::vector<float>(hidden.begin(), hidden.begin() + 30), std::vector<float>(weight.begin(), weight.begin() + 10), false,
+      1e-3f, 1e-4f);  // dim % 4 != 0: padded row stride
+}
+
+// Whole-tensor argmax / argmin (RuntimeTests.cpp:1207-1262) plus the tie rule of the reference's tree
+void argReduceCases() {
+  auto run = [&](OperatorEnum op, const std::vector<float> &v) {
+    auto in = rt->createTensor({(uint32_t)v.size()}, DataType::Float32, v.data());
+    auto out = rt->ops().reduce(op, in);
+    float got = -1.f;
+    rt->copyFromTensor(out, &got, sizeof(float));
+    const float want = orc_argreduce(v.data(), v.size(), op == ReduceArgmax);
+    CHECK(got == want);
+    return (int)got;
+  };
+  CHECK(run(ReduceArgmax, {1.f, 5.f, 3.f, 9.f, 2.f, 7.f, 4.f, 6.f}) == 3);
+  CHECK(run(ReduceArgmin, {5.f, 3.f, 1.f, 9.f, 2.f, 7.f, 4.f, 6.f}) == 2);
+  std::mt19937 gen(42);
+  std::uniform_real_distribution<float> dist(-100.f, 100.f);
+  std::vector<float> big(1024);
+  for (auto &v : big) v = dist(gen);
+  int expect = 0;
+  for (int i = 1; i < 1024; ++i)
+    if (big[i] > big[expect]) expect = i;
+  CHECK(run(ReduceArgmax, big) == expect);
+  std::vector<float> ties(600, 0.f);
+  ties[1] = ties[2] = ties[258] = 1.f;  // lanes 1, 2, 2: bit-reversed lane 2 (64) beats lane 1 (128), then the smaller index
+  CHECK(run(ReduceArgmax, ties) == 2);
+}
+
+// Embedding gather through Operations::embedding (rows of a [vocab, dim] fp32 table)
+void embeddingCases() {
+  const uint32_t vocab = 37, dim = 10;
+  std::vector<float> table(vocab * dim);
+  for (size_t i = 0; i < table.size(); ++i) table[i] = (float)i * 0.25f;
+  std::vector<uint32_t> idx = {36, 0, 5, 5, 17};
+  auto tT = rt->createTensor({vocab, dim}, DataType::Float32, table.data());
+  auto tI = rt->createTensor({(uint32_t)idx.size()}, DataType::UInt32, idx.data());
+  auto out = rt->ops().embedding(tI, tT);
+  CHECK(rt->getTensor(out).getShape() == (std::vector<uint32_t>{5, dim}));
+  std::vector<float> got(idx.size() * dim);
+  rt->copyFromTensor(out, got.data(), got.size() * sizeof(float));
+  int bad = 0;
+  for (size_t i = 0; i < idx.size(); ++i)
+    for (uint32_t j = 0; j < dim; ++j)
+      if (got[i * dim + j] != table[idx[i] * dim + j]) ++bad;
+  CHECK(bad == 0);
+  idx[1] = vocab;  // outside the table: zeros and an error when the batch is waited for
+  auto tBad = rt->createTensor({(uint32_t)idx.size()}, DataType::UInt32, idx.data());
+  auto outBad = rt->ops().embedding(tBad, tT);
+  CHECK_THROWS(rt->flush(), "kernel reported");
+  rt->copyFromTensor(outBad, got.data(), got.size() * sizeof(float));
+  bad = 0;
+  for (uint32_t j = 0; j < dim; ++j)
+    if (got[dim + j] != 0.f || got[j] != table[36 * dim + j]) ++bad;
+  CHECK(bad == 0);
+}
+
 }  // namespace
 
 int main() {
@@ -363,6 +455,9 @@ int main() {
     RUN(blocksEntryPoint);
     RUN(reusableCommandBuffer);
     RUN(errorBehaviour);
+    RUN(rmsNormCases);
+    RUN(argReduceCases);
+    RUN(embeddingCases);
   } catch (const std::exception &e) {
     std::printf("FAIL: unexpected exception: %s\n", e.what());
     return 2;
