@@ -195,6 +195,51 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = True) -> dict:
+    """configs[3]: Llama-style decoder (hidden 4096, 32 query / 8 KV heads of 128, FFN 14336, vocab 32000, Q4_K
+    projections, fp16 KV cache of 2048 rows), batch-1 greedy decode of `steps` tokens from position 512.  The
+    prompt phase is not run (no batched prefill attention yet): cache rows 0..511 hold synthetic fp16 values
+    ~N(0, 1), so every decode step attends over the 512 + t rows the configuration prescribes.  Layer 0's
+    weights are generated, the other layers are row rotations of them at their own addresses (4 GB in all)."""
+    import torch
+
+    from cut_b200.llama_decode import LlamaConfig, LlamaDecoder, synthetic_weights
+
+    cfg = LlamaConfig(n_layers=n_layers)
+    dec = LlamaDecoder(cfg, synthetic_weights(cfg, seed=41, distinct_layers=False), dev)
+    gen = torch.Generator(device=dev).manual_seed(42)
+    for l in range(cfg.n_layers):
+        dec.k_cache[l][:512].copy_(torch.randn((512, cfg.kv_dim), generator=gen, device=dev))
+        dec.v_cache[l][:512].copy_(torch.randn((512, cfg.kv_dim), generator=gen, device=dev))
+    logits = dec.step(5, 512)
+    finite = bool(torch.isfinite(logits).all())
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        dec.set_position(5, 512)
+        dec.capture()
+        dec.replay(3)
+        dec.set_position(5, 512)
+        torch.cuda.synchronize()
+        a.record()
+        dec.replay(steps)
+        b.record()
+    else:  # eager: one launch per call, for a profiler's launch list
+        tok = 5
+        torch.cuda.synchronize()
+        a.record()
+        for t in range(steps):
+            dec.step(tok, 512 + t)
+        b.record()
+    torch.cuda.synchronize()
+    dec.check_status()
+    ms = a.elapsed_time(b)
+    wb = dec.weight_bytes_per_token()
+    return {"tok/s": steps * 1e3 / ms, "ms_per_token": ms / steps, "tokens": steps, "layers": cfg.n_layers,
+            "weight_bytes_per_token": wb, "weight_GB/s": wb * steps / ms / 1e6, "kernel_launches_per_token": dec.launches_per_step,
+            "logits_finite": finite, "graph": graph, "kv_cache": "fp16, rows 0..511 synthetic, decode at 512..",
+            "activations": "fp32, staged at 16 bits per 32-k block"}
+
+
 def secondary_measurements(dev) -> dict:
     """Context numbers for the other benchmark configurations (not the headline value):
     configs[0] Q8_0 4096x4096 fp32 mat-vec (GB/s, weights cycled over 32 copies) and
@@ -275,6 +320,9 @@ def secondary_measurements(dev) -> dict:
     dq_bytes = W.numel() + n * k * 4
     out["dequant_q4_k_14336x4096"] = {"us_per_launch": us, "GB/s": dq_bytes / us / 1e3, "algorithmic_bytes": dq_bytes,
                                       "frac_of_measured_hbm": (dq_bytes / us / 1e3) / peaks["hbm_gbs"] if "hbm_gbs" in peaks else None}
+    del outs, W
+    torch.cuda.empty_cache()
+    out["configs[3]_llama_q4_k_decode_batch1"] = decode_measurement(dev)
     return out
 
 
@@ -591,9 +639,23 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="budget of the CPU baseline leg")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="run only the configs[3] decoder measurement on one GPU and print it (not the contract line)")
+    ap.add_argument("--decode-layers", type=int, default=32)
+    ap.add_argument("--decode-steps", type=int, default=256)
+    ap.add_argument("--decode-eager", action="store_true", help="with --decode-only: no CUDA graph (one launch per kernel)")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
                     help="N > 1: slices meet through the mat-vec's own peer-store epilogue, or through an NCCL all-gather")
     args = ap.parse_args()
+    if args.decode_only:
+        import torch
+
+        if not torch.cuda.is_available():
+            raise SystemExit("bench: --decode-only needs a CUDA device (there is no CPU path)")
+        torch.cuda.set_device(0)
+        print(json.dumps({"configs[3]_llama_q4_k_decode_batch1": decode_measurement(
+            torch.device("cuda:0"), args.decode_layers, args.decode_steps, graph=not args.decode_eager)}), flush=True)
+        return
     if args.impl == "reference":
         if args.steps == 2000:
             args.steps, args.warmup = 20, 3

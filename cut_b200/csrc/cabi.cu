@@ -315,6 +315,54 @@ int cutb_argreduce(int is_max, const float *values, float *out, uint32_t n, void
   return argreduce_launch(is_max, values, out, n, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cutb_rope_kv_write(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params, const float *cos_table,
+                       const float *sin_table, void *k_cache, void *v_cache, float *q_out, uint32_t q_dim, uint32_t kv_dim,
+                       uint32_t head_dim, uint64_t ld, uint32_t max_seq, int *status, void *stream) {
+  if (kv_dtype != CUTB_F32 && kv_dtype != CUTB_F16) {
+    set_last_error("rope_kv_write: cache dtype must be fp32 or fp16");
+    return CUTB_ERR_INVALID;
+  }
+  if (!q || !k || !v || !params || !cos_table || !sin_table || !k_cache || !v_cache || !q_out) {
+    set_last_error("rope_kv_write: null pointer");
+    return CUTB_ERR_INVALID;
+  }
+  if (head_dim == 0 || head_dim % 2 || q_dim % head_dim || kv_dim % head_dim || ld < kv_dim || max_seq == 0) {
+    set_last_error("rope_kv_write: head_dim must be even and divide q_dim and kv_dim; ld >= kv_dim; max_seq > 0");
+    return CUTB_ERR_INVALID;
+  }
+  return rope_kv_write_launch(kv_dtype, q, k, v, params, cos_table, sin_table, k_cache, v_cache, q_out, q_dim, kv_dim, head_dim, ld,
+                              max_seq, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+uint64_t cutb_attention_workspace_bytes(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_seq) {
+  return attention_workspace_bytes(n_heads, n_kv_heads, head_dim, max_seq);
+}
+
+int cutb_attention_decode(int kv_dtype, const float *q, const void *k_cache, const void *v_cache, const uint32_t *params, float *out,
+                          uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint64_t ld, uint32_t max_seq, float scale,
+                          void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+  if (kv_dtype != CUTB_F32 && kv_dtype != CUTB_F16) {
+    set_last_error("attention: cache dtype must be fp32 or fp16");
+    return CUTB_ERR_INVALID;
+  }
+  if (!q || !k_cache || !v_cache || !params || !out || !workspace) {
+    set_last_error("attention: null pointer");
+    return CUTB_ERR_INVALID;
+  }
+  if (n_heads == 0 || n_kv_heads == 0 || n_heads % n_kv_heads || n_heads / n_kv_heads > 8 || head_dim == 0 || head_dim > 128 ||
+      ld < (uint64_t)n_kv_heads * head_dim || max_seq == 0) {
+    set_last_error("attention: need n_heads = n_kv_heads * (1..8), head_dim in 1..128, ld >= n_kv_heads * head_dim, max_seq > 0");
+    return CUTB_ERR_INVALID;
+  }
+  if (reinterpret_cast<uintptr_t>(workspace) % 16 || workspace_bytes < attention_workspace_bytes(n_heads, n_kv_heads, head_dim, max_seq)) {
+    set_last_error("attention: workspace must be 16-byte aligned and hold %llu bytes",
+                   (unsigned long long)attention_workspace_bytes(n_heads, n_kv_heads, head_dim, max_seq));
+    return CUTB_ERR_INVALID;
+  }
+  return attention_decode_launch(kv_dtype, q, k_cache, v_cache, params, out, n_heads, n_kv_heads, head_dim, ld, max_seq, scale,
+                                 workspace, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                  void *stream) {
   if (format < CUTB_Q8_0 || format > CUTB_BF16) {

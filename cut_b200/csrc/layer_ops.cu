@@ -9,15 +9,44 @@
 namespace cutb {
 namespace {
 
-// One CTA per row: 16-byte loads, the sum of squares in fp32 through a warp-shuffle tree and one
-// shared-memory step, y = x * rsqrt(mean + eps) * w.  The row stays in registers between the two
-// passes when it fits (up to 8 floats per thread x 256 threads x 4 = 8192 columns); longer rows
-// are read twice (the second read hits L2).
+// fp32 rows of up to 8192 columns whose length and stride are multiples of 4: one CTA of up to
+// 1024 threads per row, every thread loads its (at most two) 16-byte pieces of the row and of the
+// weight at once, so the whole operator is one memory round trip, a shuffle tree and two barriers;
+// the row never leaves registers.
+__global__ void __launch_bounds__(1024) rmsnorm_row_kernel(const float4 *__restrict__ x, const float4 *__restrict__ w,
+                                                           float4 *__restrict__ y, uint32_t dim4, uint64_t ldx4, float inv_dim,
+                                                           float eps) {
+  __shared__ float warp_part[32];
+  pdl_enter();
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const uint64_t row = blockIdx.x;
+  const uint32_t i0 = tid, i1 = tid + blockDim.x;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 a0 = i0 < dim4 ? __ldg(x + row * ldx4 + i0) : zero, a1 = i1 < dim4 ? __ldg(x + row * ldx4 + i1) : zero;
+  const float4 w0 = i0 < dim4 ? __ldg(w + i0) : zero, w1 = i1 < dim4 ? __ldg(w + i1) : zero;
+  float ss = fmaf(a0.x, a0.x, fmaf(a0.y, a0.y, fmaf(a0.z, a0.z, a0.w * a0.w)));
+  ss += fmaf(a1.x, a1.x, fmaf(a1.y, a1.y, fmaf(a1.z, a1.z, a1.w * a1.w)));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if (lane == 0) warp_part[warp] = ss;
+  __syncthreads();
+  float t = lane < nwarps ? warp_part[lane] : 0.f;  // every warp adds the partials in the same order
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+  const float scale = rsqrtf(t * inv_dim + eps);
+  if (i0 < dim4) y[row * ldx4 + i0] = make_float4(a0.x * scale * w0.x, a0.y * scale * w0.y, a0.z * scale * w0.z, a0.w * scale * w0.w);
+  if (i1 < dim4) y[row * ldx4 + i1] = make_float4(a1.x * scale * w1.x, a1.y * scale * w1.y, a1.z * scale * w1.z, a1.w * scale * w1.w);
+}
+
+// Any other row: one CTA of 256 threads per row, the sum of squares in fp32 through a
+// warp-shuffle tree and one shared-memory step, y = x * rsqrt(mean + eps) * w; the row is read
+// twice (the second read hits L2).
 template <bool HALF>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const void *__restrict__ x_, const void *__restrict__ w_, void *__restrict__ y_,
                                                       uint32_t dim, uint64_t ldx, float eps) {
   __shared__ float warp_part[8];
   __shared__ float total;
+  pdl_enter();
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint64_t row = blockIdx.x;
   auto ldx_at = [&](uint32_t i) -> float {
@@ -58,6 +87,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const void *__restrict__ x
 __global__ void __launch_bounds__(256) embedding_kernel(const uint32_t *__restrict__ indices, const uint4 *__restrict__ table,
                                                         uint4 *__restrict__ out, uint64_t n, uint32_t ld4, uint32_t vocab,
                                                         int *status) {
+  pdl_enter();
   const uint64_t total = n * ld4;
   for (uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (uint64_t)gridDim.x * blockDim.x) {
     const uint64_t i = g / ld4;
@@ -91,10 +121,12 @@ template <bool MAX> __device__ __forceinline__ bool arg_better(const ArgKey &a, 
 template <bool MAX>
 __global__ void __launch_bounds__(1024) argreduce_kernel(const float *__restrict__ v, float *__restrict__ out, uint32_t n) {
   __shared__ ArgKey part[32];
+  pdl_enter();
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // the reference starts every thread at (worst value, index 0) and replaces it only by strictly
   // better values: an input that never beats the start value yields index 0
   ArgKey best{MAX ? -3.402823466e+38f : 3.402823466e+38f, 0xFFFFFFFFu};
+#pragma unroll 8
   for (uint32_t i = tid; i < n; i += 1024) {
     const ArgKey c{__ldg(v + i), i};
     const bool strictly = MAX ? c.v > best.v : c.v < best.v;
@@ -131,11 +163,18 @@ __global__ void __launch_bounds__(1024) argreduce_kernel(const float *__restrict
 int rmsnorm_launch(int dtype, const void *x, const void *weight, void *y, uint32_t rows, uint32_t dim, uint64_t ldx, float eps,
                    cudaStream_t stream) {
   if (rows == 0 || dim == 0) return CUTB_OK;
-  if (dtype == CUTB_F16)
-    rmsnorm_kernel<true><<<rows, 256, 0, stream>>>(x, weight, y, dim, ldx, eps);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  if (dtype == CUTB_F32 && aligned && dim % 4 == 0 && ldx % 4 == 0 && dim <= 8192) {
+    const uint32_t dim4 = dim / 4;
+    uint32_t threads = ((dim4 + 1) / 2 + 31) / 32 * 32;  // two pieces per thread, whole warps
+    if (threads < 128) threads = (dim4 + 31) / 32 * 32 < 128 ? (dim4 + 31) / 32 * 32 : 128;
+    CUTB_CUDA_TRY(launch_pdl(rmsnorm_row_kernel, dim3(rows), dim3(threads), 0, stream, reinterpret_cast<const float4 *>(x),
+                             reinterpret_cast<const float4 *>(weight), reinterpret_cast<float4 *>(y), dim4, ldx / 4, 1.0f / (float)dim,
+                             eps));
+  } else if (dtype == CUTB_F16)
+    CUTB_CUDA_TRY(launch_pdl(rmsnorm_kernel<true>, dim3(rows), dim3(256), 0, stream, x, weight, y, dim, ldx, eps));
   else
-    rmsnorm_kernel<false><<<rows, 256, 0, stream>>>(x, weight, y, dim, ldx, eps);
-  CUTB_CUDA_TRY(cudaGetLastError());
+    CUTB_CUDA_TRY(launch_pdl(rmsnorm_kernel<false>, dim3(rows), dim3(256), 0, stream, x, weight, y, dim, ldx, eps));
   return CUTB_OK;
 }
 
@@ -148,18 +187,16 @@ int embedding_launch(const uint32_t *indices, const float *table, float *out, ui
   if (total == 0) return CUTB_OK;
   uint64_t blocks = (total + 255) / 256;
   if (blocks > (uint64_t)di.sm_count * 16) blocks = (uint64_t)di.sm_count * 16;
-  embedding_kernel<<<(unsigned)blocks, 256, 0, stream>>>(indices, reinterpret_cast<const uint4 *>(table), reinterpret_cast<uint4 *>(out),
-                                                         n, ld4, vocab, status);
-  CUTB_CUDA_TRY(cudaGetLastError());
+  CUTB_CUDA_TRY(launch_pdl(embedding_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, indices, reinterpret_cast<const uint4 *>(table),
+                           reinterpret_cast<uint4 *>(out), n, ld4, vocab, status));
   return CUTB_OK;
 }
 
 int argreduce_launch(int is_max, const float *v, float *out, uint32_t n, cudaStream_t stream) {
   if (is_max)
-    argreduce_kernel<true><<<1, 1024, 0, stream>>>(v, out, n);
+    CUTB_CUDA_TRY(launch_pdl(argreduce_kernel<true>, dim3(1), dim3(1024), 0, stream, v, out, n));
   else
-    argreduce_kernel<false><<<1, 1024, 0, stream>>>(v, out, n);
-  CUTB_CUDA_TRY(cudaGetLastError());
+    CUTB_CUDA_TRY(launch_pdl(argreduce_kernel<false>, dim3(1), dim3(1024), 0, stream, v, out, n));
   return CUTB_OK;
 }
 

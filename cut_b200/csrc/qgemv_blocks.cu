@@ -57,6 +57,9 @@ constexpr int GV_ROWS = 16;
 
 constexpr int GV_WARPS = 16;                      // consumer warps; one more warp issues the copies
 constexpr int GV_THREADS = (GV_WARPS + 1) * 32;
+// how the activations are read and staged
+constexpr int GV_A_HALF = 0, GV_A_F32_TWO = 1, GV_A_F32_ONE = 2;
+
 constexpr int GV_KC = GV_WARPS;                   // granules (256 weights) per row and stage, one per consumer warp
 
 // Shared-memory layout of a stage: the 16 rows of a tile sit in 8 pairs, tile rows 2i and 2i + 1
@@ -481,12 +484,14 @@ constexpr float GV_QMAX = 32512.f;
 //
 // Diagonal variant (DIAG): act is [blk][vrow][digit][MMA i][8 bytes] followed by
 // 32 zero bytes, esc / sx are [blk][NT] (NT = number of virtual rows).
-template <int FMT, bool AF32, int NT, bool DIAG, int THREADS>
+template <int FMT, int AMODE, int NT, bool DIAG, int THREADS>
 __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *act, float *esc, float *sx, uint32_t k0,
                                                   uint32_t nblk, uint32_t ncp, uint32_t tid) {
   constexpr uint32_t NV = DIAG ? NT : NT * 4;
   const uint32_t nrows = p.M;
-  const uint32_t nvr = AF32 ? 2 * nrows : nrows;
+  constexpr bool AF32 = AMODE != GV_A_HALF;      // fp32 loads
+  constexpr bool TWO = AMODE == GV_A_F32_TWO;     // two 16-bit levels per fp32 value
+  const uint32_t nvr = TWO ? 2 * nrows : nrows;
   const uint32_t nchunks = nblk * nrows * 4;
   const float wscale = (FMT == CUTB_Q4_0) ? 0.0625f : 1.0f;  // Q4_0 nibbles enter the MMA as 16 q
   const float sxscale = (FMT == CUTB_Q4_0) ? 8.0f : 1.0f;    // Q4_0: the -8 offset of every weight
@@ -522,7 +527,7 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
       isum += v[i];
     }
     pack_digits(v, whi, wlo);
-    const uint32_t vr = AF32 ? 2 * m : m;
+    const uint32_t vr = TWO ? 2 * m : m;
     if constexpr (FMT != CUTB_Q8_0) {
       isum += __shfl_xor_sync(0xffffffffu, isum, 1);
       isum += __shfl_xor_sync(0xffffffffu, isum, 2);
@@ -540,7 +545,7 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
         if constexpr (FMT != CUTB_Q8_0) sx[kb * NV + vr] = sxscale * e * (float)isum;
       }
     }
-    if constexpr (AF32) {
+    if constexpr (TWO) {
       // second 16-bit level: the residual x - x^ e, at scale e / 65024
       const float e2 = e * (1.0f / (2.f * GV_QMAX)), inv2 = inv * (2.f * GV_QMAX);
       int w[8], isum2 = 0;
@@ -585,7 +590,7 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     }
 }
 
-template <int FMT, bool AF32, int NT, bool DIAG>
+template <int FMT, int AMODE, int NT, bool DIAG>
 __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvParams p) {
   constexpr int PS = gv_pair_stride(FMT, DIAG);
   constexpr uint32_t RAWROW = gv_raw_row(FMT);
@@ -595,7 +600,8 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
   extern __shared__ __align__(128) uint8_t smem[];
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const uint32_t nvr = AF32 ? 2 * p.M : p.M;  // virtual activation rows (two per fp32 row)
+  constexpr bool TWO = AMODE == GV_A_F32_TWO;
+  const uint32_t nvr = TWO ? 2 * p.M : p.M;  // virtual activation rows (two per fp32 row staged at two levels)
   const uint32_t ncols = 2 * nvr;
   const uint32_t ncp = (ncols < NC8) ? ncols + 1 : ncols;
   const uint32_t nblk_alloc = p.gran_per_split * 8;
@@ -687,7 +693,7 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
   // Everything above only read the (constant) weights.  The activations, D and
   // C may belong to the previous kernel of the stream: wait for it to finish.
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  stage_activations<FMT, AF32, NT, DIAG, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid);
+  stage_activations<FMT, AMODE, NT, DIAG, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid);
   asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
 
   const uint32_t act_u = smem_u32(act), act_stride = ncp * 32, esc_u = smem_u32(esc), sx_u = smem_u32(sx);
@@ -774,7 +780,7 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
       const uint32_t row = o % GV_ROWS, m = o / GV_ROWS, n = row_base + row;
       if (n < r1) {
         float sum = 0.f;
-        if constexpr (AF32) {
+        if constexpr (TWO) {
 #pragma unroll
           for (int w = 0; w < GV_WARPS; ++w) {
             const float2 hl = *reinterpret_cast<const float2 *>(rbuf + ((size_t)w * GV_ROWS + row) * NV + 2 * m);
@@ -864,6 +870,11 @@ __global__ void peer_exchange_kernel(const ExchangeArgs a, unsigned long long *s
 
 // ---- host side ---------------------------------------------------------------
 
+int gv_amode(const cutb_qmatmul_desc &d) {
+  if (d.a_dtype != CUTB_F32) return GV_A_HALF;
+  return (d.flags & CUTB_FLAG_ACT_16BIT) ? GV_A_F32_ONE : GV_A_F32_TWO;
+}
+
 struct GvPlan {
   uint32_t nt, nvr, ncp, grid_x, ksplit, gran_per_split, stages;
   bool diag, overlap;
@@ -882,7 +893,7 @@ size_t gv_smem_bytes(int fmt, bool diag, uint32_t stages, uint32_t nt, uint32_t 
 }
 
 bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
-  const bool af32 = d.a_dtype == CUTB_F32;
+  const bool af32 = gv_amode(d) == GV_A_F32_TWO;  // two virtual rows per activation row
   pl->nvr = af32 ? 2 * d.M : d.M;
   if (pl->nvr == 0 || pl->nvr > 16) return false;
   // one virtual row: the diagonal variant (nt = virtual rows); otherwise 4 virtual rows per MMA n-tile
@@ -921,7 +932,7 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
   return false;
 }
 
-template <int FMT, bool AF32, int NT, bool DIAG>
+template <int FMT, int AMODE, int NT, bool DIAG>
 int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   static int configured_device = -1;
   int dev = 0;
@@ -929,7 +940,7 @@ int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   if (configured_device != dev) {
     DeviceInfo di;
     if (int rc = get_device_info(&di)) return rc;
-    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AF32, NT, DIAG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AMODE, NT, DIAG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)di.smem_optin));
     configured_device = dev;
   }
@@ -943,23 +954,27 @@ int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pl.overlap ? 1 : 0;
-  CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, qgemv_blocks_kernel<FMT, AF32, NT, DIAG>, p));
+  CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, qgemv_blocks_kernel<FMT, AMODE, NT, DIAG>, p));
   return CUTB_OK;
 }
 
-template <int FMT, bool AF32>
+template <int FMT, int AMODE>
 int gv_launch_nt(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
-  if (pl.diag) return pl.nt == 1 ? gv_launch_inst<FMT, AF32, 1, true>(p, pl, stream) : gv_launch_inst<FMT, AF32, 2, true>(p, pl, stream);
+  if (pl.diag) return pl.nt == 1 ? gv_launch_inst<FMT, AMODE, 1, true>(p, pl, stream) : gv_launch_inst<FMT, AMODE, 2, true>(p, pl, stream);
   switch (pl.nt) {
-    case 1: return gv_launch_inst<FMT, AF32, 1, false>(p, pl, stream);
-    case 2: return gv_launch_inst<FMT, AF32, 2, false>(p, pl, stream);
-    default: return gv_launch_inst<FMT, AF32, 4, false>(p, pl, stream);
+    case 1: return gv_launch_inst<FMT, AMODE, 1, false>(p, pl, stream);
+    case 2: return gv_launch_inst<FMT, AMODE, 2, false>(p, pl, stream);
+    default: return gv_launch_inst<FMT, AMODE, 4, false>(p, pl, stream);
   }
 }
 
 template <int FMT>
-int gv_launch_a(const GvParams &p, const GvPlan &pl, bool af32, cudaStream_t stream) {
-  return af32 ? gv_launch_nt<FMT, true>(p, pl, stream) : gv_launch_nt<FMT, false>(p, pl, stream);
+int gv_launch_a(const GvParams &p, const GvPlan &pl, int amode, cudaStream_t stream) {
+  switch (amode) {
+    case GV_A_HALF: return gv_launch_nt<FMT, GV_A_HALF>(p, pl, stream);
+    case GV_A_F32_ONE: return gv_launch_nt<FMT, GV_A_F32_ONE>(p, pl, stream);
+    default: return gv_launch_nt<FMT, GV_A_F32_TWO>(p, pl, stream);
+  }
 }
 
 }  // namespace
@@ -967,7 +982,7 @@ int gv_launch_a(const GvParams &p, const GvPlan &pl, bool af32, cudaStream_t str
 bool qgemv_blocks_supported(const cutb_qmatmul_desc &d) {
   if (d.layout != CUTB_LAYOUT_GGUF_BLOCKS) return false;
   if (d.K == 0 || d.K % 256 != 0 || d.N == 0 || d.M == 0) return false;
-  const uint32_t nvr = d.a_dtype == CUTB_F32 ? 2 * d.M : d.M;
+  const uint32_t nvr = gv_amode(d) == GV_A_F32_TWO ? 2 * d.M : d.M;
   if (nvr > 16) return false;
   if (reinterpret_cast<uintptr_t>(d.W) % 16 != 0) return false;
   return true;
@@ -993,7 +1008,7 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
     set_last_error("qgemv: no shared-memory plan for M=%u K=%u N=%u", d.M, d.K, d.N);
     return CUTB_ERR_UNSUPPORTED;
   }
-  const bool af32 = d.a_dtype == CUTB_F32;
+  const int amode = gv_amode(d);
   pl.overlap = !(d.flags & CUTB_FLAG_NO_OVERLAP);
   GvParams p;
   p.W = reinterpret_cast<const uint8_t *>(d.W);
@@ -1013,7 +1028,7 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
   p.stages = pl.stages;
   p.fusion_type = d.fusion_type;
   p.fusion_op = d.fusion_op;
-  p.a_f32 = af32;
+  p.a_f32 = amode != GV_A_HALF;
   p.status = d.status;
   p.world = 0;
   p.n_off = p.ldc_total = 0;
@@ -1046,9 +1061,9 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
   }
   int rc;
   switch (d.format) {
-    case CUTB_Q8_0: rc = gv_launch_a<CUTB_Q8_0>(p, pl, af32, stream); break;
-    case CUTB_Q4_0: rc = gv_launch_a<CUTB_Q4_0>(p, pl, af32, stream); break;
-    default: rc = gv_launch_a<CUTB_Q4_K>(p, pl, af32, stream); break;
+    case CUTB_Q8_0: rc = gv_launch_a<CUTB_Q8_0>(p, pl, amode, stream); break;
+    case CUTB_Q4_0: rc = gv_launch_a<CUTB_Q4_0>(p, pl, amode, stream); break;
+    default: rc = gv_launch_a<CUTB_Q4_K>(p, pl, amode, stream); break;
   }
   if (rc != CUTB_OK) return rc;
   if (pl.ksplit > 1) {

@@ -1,0 +1,222 @@
+"""One-token decode step of a Llama-style decoder over raw GGUF-block weights, on the C ABI.
+
+The per-token dispatch sequence of the reference's runner (interface/runner/llama/llama.cpp:
+runLayer 2045-2084, forward 2090-2166): embedding gather, then per layer RMSNorm -> fused QKV
+mat-vec -> fused RoPE + KV-cache write -> grouped-query attention -> output projection with the
+residual add fused -> RMSNorm -> gate mat-vec with SiLU fused -> up mat-vec with the multiply
+fused -> down projection with the residual add fused; final RMSNorm, LM head, arg-max.  Position
+and token live in device buffers ({pos, seqLen} as in the reference's runtimeParams), the whole
+step is recorded once into a CUDA graph and replayed per token; the arg-max feeds the next
+token on the device, so a decode loop makes no host round trip.
+
+torch supplies device memory, the stream and the graph capture; every kernel of the step is this
+package's.  Weights are raw GGUF blocks ([N rows][K / block] of Q8_0, Q4_0 or Q4_K), Q/K/V
+concatenated along N, exactly as a GGUF file stores them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib as L
+from . import ops, synth
+
+UNARY_SILU, BINARY_ADD, BINARY_MUL = 133, 0, 2  # OperatorEnum codes (operators/runtime/ComputeOpsShared.h)
+
+
+@dataclass
+class LlamaConfig:
+    n_layers: int = 32
+    hidden: int = 4096
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 32000
+    eps: float = 1e-5
+    rope_theta: float = 10000.0
+    max_seq: int = 2048
+    fmt: int = L.Q4_K
+    kv_dtype: torch.dtype = torch.float16
+
+    @property
+    def q_dim(self) -> int:
+        return self.n_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.n_kv_heads * self.head_dim
+
+
+def rope_tables(cfg: LlamaConfig):
+    """cos / sin [max_seq, head_dim / 2] in float32 arithmetic (llama.cpp:1652-1666)."""
+    half = cfg.head_dim // 2
+    freq = (np.float32(1.0) / np.power(np.float32(cfg.rope_theta), (2 * np.arange(half, dtype=np.float32)) / np.float32(cfg.head_dim)))
+    ang = np.arange(cfg.max_seq, dtype=np.float32)[:, None] * freq.astype(np.float32)[None, :]
+    return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+
+def synthetic_weights(cfg: LlamaConfig, seed: int = 0, distinct_layers: bool = True) -> dict:
+    """Random-init weights as host arrays: block tensors from the synthetic generators of the
+    benchmark configurations, norms near 1, an fp32 embedding table ~N(0, 0.02).  With
+    distinct_layers False, layer 0 is generated and the others are row rotations of it (different
+    matrices at different addresses for a fraction of the generation time)."""
+    rng = np.random.default_rng(seed)
+    shapes = {"wqkv": (cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden), "wo": (cfg.hidden, cfg.q_dim), "wgate": (cfg.ffn, cfg.hidden),
+              "wup": (cfg.ffn, cfg.hidden), "wdown": (cfg.hidden, cfg.ffn)}
+    layers = []
+    for l in range(cfg.n_layers):
+        if l == 0 or distinct_layers:
+            lw = {k: synth.make_weights(cfg.fmt, n, kk, seed=seed * 1000 + l * 10 + i) for i, (k, (n, kk)) in enumerate(shapes.items())}
+        else:
+            lw = {}
+            for k, (n, kk) in shapes.items():
+                rb = synth.row_bytes(cfg.fmt, kk)
+                lw[k] = np.roll(layers[0][k].reshape(n, rb), 16 * l, axis=0).reshape(-1)
+        lw["attn_norm"] = (1.0 + 0.1 * rng.standard_normal(cfg.hidden)).astype(np.float32)
+        lw["ffn_norm"] = (1.0 + 0.1 * rng.standard_normal(cfg.hidden)).astype(np.float32)
+        layers.append(lw)
+    return {"layers": layers, "final_norm": (1.0 + 0.1 * rng.standard_normal(cfg.hidden)).astype(np.float32),
+            "lm_head": synth.make_weights(cfg.fmt, cfg.vocab, cfg.hidden, seed=seed * 1000 + 999),
+            "embedding": (0.02 * rng.standard_normal((cfg.vocab, cfg.hidden))).astype(np.float32)}
+
+
+class LlamaDecoder:
+    """Device state of one model and the recorded decode step.
+
+    `step(token, pos)` runs one token eagerly; `capture()` records the step once and `replay(n)`
+    runs n further tokens from the device-resident {token, pos}, greedy (arg-max feeds back)."""
+
+    def __init__(self, cfg: LlamaConfig, weights: dict, device: torch.device | str = "cuda", act_16bit: bool = True,
+                 overlap: bool = False):
+        if not torch.cuda.is_available():
+            raise RuntimeError("LlamaDecoder needs a CUDA device: there is no CPU path")
+        if cfg.hidden % 4 or cfg.n_heads % cfg.n_kv_heads:
+            raise ValueError("hidden must be a multiple of 4 and n_heads a multiple of n_kv_heads")
+        self.cfg, self.dev = cfg, torch.device(device)
+        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(self.dev)
+        self.layers = [{k: up(v) for k, v in lw.items()} for lw in weights["layers"]]
+        self.final_norm, self.lm_head, self.table = up(weights["final_norm"]), up(weights["lm_head"]), up(weights["embedding"])
+        cos_t, sin_t = rope_tables(cfg)
+        self.cos_t, self.sin_t = up(cos_t), up(sin_t)
+        ld = (cfg.kv_dim + 3) // 4 * 4
+        self.k_cache = [torch.zeros((cfg.max_seq, ld), dtype=cfg.kv_dtype, device=self.dev) for _ in range(cfg.n_layers)]
+        self.v_cache = [torch.zeros((cfg.max_seq, ld), dtype=cfg.kv_dtype, device=self.dev) for _ in range(cfg.n_layers)]
+        f32 = lambda n: torch.zeros(n, dtype=torch.float32, device=self.dev)
+        self.params = torch.zeros(2, dtype=torch.int32, device=self.dev)  # {pos, seqLen}
+        self.token = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.x = [f32(cfg.hidden), f32(cfg.hidden)]
+        self.h, self.qkv, self.q_roped, self.attn = f32(cfg.hidden), f32(cfg.q_dim + 2 * cfg.kv_dim), f32(cfg.q_dim), f32(cfg.q_dim)
+        self.gate, self.act, self.logits, self.next_tok = f32(cfg.ffn), f32(cfg.ffn), f32(cfg.vocab), f32(1)
+        self.attn_ws = ops.attention_workspace(cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.max_seq, self.dev)
+        # fp32 activations staged at one 16-bit level per 32-k block: fp16-grade error, fp32 range
+        self.act_flags = L.FLAG_ACT_16BIT if act_16bit else 0
+        # overlap: let a mat-vec that follows a mat-vec (up after gate, down after up) prefetch under its predecessor's
+        # tail.  Off by default: a chain of equal mat-vecs gains ~1.4 us per launch from it, the mixed step lost 7 %.
+        self.overlap = overlap
+        self._keep, self._descs, self.launches_per_step = [], [], 0
+        self._plan()
+        self.graph = None
+
+    # -- the recorded sequence: a list of closures over prepared descriptors --------------------
+    def _matvec(self, A, W, N, out, fusion_type=L.FUSION_NONE, fusion_op=0, D=None, after_matvec=False):
+        d, _, keep = ops.make_desc(A, W, self.cfg.fmt, N, C_out=out.view(1, -1), D=D.view(1, -1) if D is not None else None,
+                                   fusion_type=fusion_type, fusion_op=fusion_op, status=self.status,
+                                   flags=self.act_flags | (0 if (after_matvec and self.overlap) else L.FLAG_NO_OVERLAP))
+        need = ops.workspace_bytes(d)
+        if need:  # split-K shapes: scratch owned by this descriptor, sized before capture
+            ws = torch.empty(need, dtype=torch.uint8, device=self.dev)
+            d.workspace, d.workspace_bytes = ws.data_ptr(), need
+            keep = keep + (ws,)
+        self._keep.append(keep)
+        self._descs.append(d)
+        return lambda d=d: L.check(L.lib().cutb_qmatmul(C.byref(d), ops._stream_ptr()))
+
+    def _plan(self):
+        cfg, lib = self.cfg, L.lib()
+        seq = []
+        st = self.status.data_ptr()
+        kvd = L.F16 if cfg.kv_dtype == torch.float16 else L.F32
+
+        def rms(x, w, y):
+            return lambda: L.check(lib.cutb_rmsnorm(L.F32, x.data_ptr(), w.data_ptr(), y.data_ptr(), 1, cfg.hidden, cfg.hidden, cfg.eps,
+                                                    ops._stream_ptr()))
+
+        seq.append(lambda: L.check(lib.cutb_embedding(self.token.data_ptr(), self.table.data_ptr(), self.x[0].data_ptr(), 1, cfg.hidden,
+                                                      cfg.vocab, st, ops._stream_ptr())))
+        q, k, v = self.qkv[: cfg.q_dim], self.qkv[cfg.q_dim: cfg.q_dim + cfg.kv_dim], self.qkv[cfg.q_dim + cfg.kv_dim:]
+        scale = 1.0 / float(np.sqrt(np.float32(cfg.head_dim)))
+        for l, lw in enumerate(self.layers):
+            kc, vc = self.k_cache[l], self.v_cache[l]
+            seq.append(rms(self.x[0], lw["attn_norm"], self.h))
+            seq.append(self._matvec(self.h, lw["wqkv"], cfg.q_dim + 2 * cfg.kv_dim, self.qkv))
+            seq.append(lambda kc=kc, vc=vc: L.check(lib.cutb_rope_kv_write(
+                kvd, q.data_ptr(), k.data_ptr(), v.data_ptr(), self.params.data_ptr(), self.cos_t.data_ptr(), self.sin_t.data_ptr(),
+                kc.data_ptr(), vc.data_ptr(), self.q_roped.data_ptr(), cfg.q_dim, cfg.kv_dim, cfg.head_dim, kc.stride(0), cfg.max_seq, st,
+                ops._stream_ptr())))
+            seq.append(lambda kc=kc, vc=vc: L.check(lib.cutb_attention_decode(
+                kvd, self.q_roped.data_ptr(), kc.data_ptr(), vc.data_ptr(), self.params.data_ptr(), self.attn.data_ptr(), cfg.n_heads,
+                cfg.n_kv_heads, cfg.head_dim, kc.stride(0), cfg.max_seq, scale, self.attn_ws.data_ptr(), self.attn_ws.numel(), st,
+                ops._stream_ptr())))
+            seq.append(self._matvec(self.attn, lw["wo"], cfg.hidden, self.x[1], L.FUSION_BINARY, BINARY_ADD, self.x[0]))
+            seq.append(rms(self.x[1], lw["ffn_norm"], self.h))
+            seq.append(self._matvec(self.h, lw["wgate"], cfg.ffn, self.gate, L.FUSION_UNARY, UNARY_SILU))
+            seq.append(self._matvec(self.h, lw["wup"], cfg.ffn, self.act, L.FUSION_BINARY, BINARY_MUL, self.gate, after_matvec=True))
+            seq.append(self._matvec(self.act, lw["wdown"], cfg.hidden, self.x[0], L.FUSION_BINARY, BINARY_ADD, self.x[1], after_matvec=True))
+        seq.append(rms(self.x[0], self.final_norm, self.h))
+        seq.append(self._matvec(self.h, self.lm_head, cfg.vocab, self.logits))
+        seq.append(lambda: L.check(lib.cutb_argreduce(1, self.logits.data_ptr(), self.next_tok.data_ptr(), cfg.vocab, ops._stream_ptr())))
+        self._seq = seq
+        # split-K mat-vecs launch a second (reduction) kernel
+        self.launches_per_step = len(seq) + sum(1 for d in self._descs if d.workspace_bytes)
+
+    def weight_bytes_per_token(self) -> int:
+        """Bytes of block weights one token streams (every projection once, plus the LM head)."""
+        return sum(t.numel() for lw in self.layers for k, t in lw.items() if k.startswith("w")) + self.lm_head.numel()
+
+    def set_position(self, token: int, pos: int) -> None:
+        self.token.fill_(token)
+        self.params.copy_(torch.tensor([pos, pos + 1], dtype=torch.int32))
+
+    def _run(self) -> None:
+        for f in self._seq:
+            f()
+
+    def _advance(self) -> None:
+        # plumbing between tokens: the greedy pick becomes the next token, the position moves on
+        self.token.copy_(self.next_tok.to(torch.int32))
+        self.params.add_(1)
+
+    def step(self, token: int, pos: int) -> torch.Tensor:
+        """One token eagerly; returns the logits (device tensor, overwritten by the next step)."""
+        self.set_position(token, pos)
+        self._run()
+        return self.logits
+
+    def capture(self) -> None:
+        """Records step + advance into one CUDA graph (call after at least one eager step)."""
+        torch.cuda.synchronize(self.dev)
+        saved = (self.token.clone(), self.params.clone())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._run()
+            self._advance()
+        self.token.copy_(saved[0])
+        self.params.copy_(saved[1])
+        self.graph = g
+
+    def replay(self, n: int) -> None:
+        if self.graph is None:
+            raise RuntimeError("capture() first")
+        for _ in range(n):
+            self.graph.replay()
+
+    def check_status(self) -> None:
+        st = int(self.status.item())
+        if st:
+            raise L.CutbError(st, "a kernel of the decode step reported an error (position past the cache, token past the "
+                                  "vocabulary, or an expired bounded wait)")

@@ -168,3 +168,48 @@ def argreduce(values: torch.Tensor, is_max: bool = True) -> torch.Tensor:
     out = torch.empty(1, dtype=torch.float32, device=values.device)
     L.check(L.lib().cutb_argreduce(1 if is_max else 0, values.data_ptr(), out.data_ptr(), values.numel(), _stream_ptr()))
     return out
+
+
+# ---- decode-step attention ----
+def _kv_dtype(cache: torch.Tensor) -> int:
+    if cache.dtype == torch.float16:
+        return L.F16
+    if cache.dtype == torch.float32:
+        return L.F32
+    raise RuntimeError("KV cache must be float32 or float16")
+
+
+def rope_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, params: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor,
+                  k_cache: torch.Tensor, v_cache: torch.Tensor, head_dim: int, q_out: torch.Tensor | None = None,
+                  status: torch.Tensor | None = None) -> torch.Tensor:
+    """Half-split RoPE of q and k at params[0]; roped k and v go to row params[0] of the caches
+    ([max_seq, ld]); returns the roped q.  params: int32/uint32 device tensor {pos, seqLen}."""
+    if q_out is None:
+        q_out = torch.empty_like(q)
+    L.check(L.lib().cutb_rope_kv_write(_kv_dtype(k_cache), q.data_ptr(), k.data_ptr(), v.data_ptr(), params.data_ptr(),
+                                       cos_t.data_ptr(), sin_t.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q_out.data_ptr(),
+                                       q.numel(), k.numel(), head_dim, k_cache.stride(0), k_cache.shape[0],
+                                       status.data_ptr() if status is not None else None, _stream_ptr()))
+    return q_out
+
+
+def attention_workspace(n_heads: int, n_kv_heads: int, head_dim: int, max_seq: int, device) -> torch.Tensor:
+    """Zeroed scratch for attention_decode (its first 256 bytes are arrival counters that every launch leaves zero)."""
+    n = int(L.lib().cutb_attention_workspace_bytes(n_heads, n_kv_heads, head_dim, max_seq))
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, params: torch.Tensor, n_heads: int,
+                     n_kv_heads: int, head_dim: int, workspace: torch.Tensor, out: torch.Tensor | None = None,
+                     scale: float | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """Grouped-query attention of one roped query [n_heads * head_dim] over rows [0, params[1]) of the caches."""
+    if out is None:
+        out = torch.empty(n_heads * head_dim, dtype=torch.float32, device=q.device)
+    if scale is None:
+        scale = 1.0 / float(head_dim) ** 0.5
+    L.check(L.lib().cutb_attention_decode(_kv_dtype(k_cache), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), params.data_ptr(),
+                                          out.data_ptr(), n_heads, n_kv_heads, head_dim, k_cache.stride(0), k_cache.shape[0],
+                                          scale, workspace.data_ptr(), workspace.numel(),
+                                          status.data_ptr() if status is not None else None, _stream_ptr()))
+    return out
+

@@ -83,8 +83,15 @@ enum {
  *     previous kernel of the stream is still finishing, and it waits for that
  *     kernel to complete before it reads A or D or writes C.  This is only
  *     correct if the previous kernel does not write W (weights are constants of
- *     the model).  Set this flag to launch with plain stream ordering instead. */
-enum { CUTB_FLAG_NO_OVERLAP = 1 };
+ *     the model).  Set this flag to launch with plain stream ordering instead.
+ *   CUTB_FLAG_ACT_16BIT: the decode mat-vec stages activations as 16-bit integers with one fp32
+ *     scale per 32-k block.  fp32 activations are normally staged at two such levels (32 bits,
+ *     fp32-accurate results); with this flag they are staged at one, which halves the tensor-core
+ *     work and selects the fastest kernel shape for a single row.  The result then carries the
+ *     error fp16 activations would (relative error of a dot product about 3e-5) but keeps the
+ *     fp32 range, so large activations cannot overflow.  Ignored for fp16 activations and by the
+ *     other variants. */
+enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2 };
 
 /*
  * C[M, N] = epilogue(A[M, K] * dequant(W)), fp32 accumulate, fp32 output.
@@ -253,6 +260,34 @@ CUTB_API int cutb_rmsnorm(int dtype, const void *x, const void *weight, void *y,
 CUTB_API int cutb_embedding(const uint32_t *indices, const float *table, float *out, uint64_t n, uint32_t dim, uint32_t vocab,
                             int *status, void *stream);
 CUTB_API int cutb_argreduce(int is_max, const float *values, float *out, uint32_t n, void *stream);
+
+/*
+ * Decode-step attention for one token.  `params` is the reference's two-word device buffer
+ * {pos, seqLen} (interface/runner/llama/llama.cpp:2087-2094), read by the kernels, so a recorded
+ * step replays for every token.  Caches are [max_seq][ld] elements (ld >= n_kv_heads * head_dim,
+ * the reference pads it to 4), kv_dtype CUTB_F32 or CUTB_F16; head_dim even and <= 128.
+ *
+ * cutb_rope_kv_write: half-split rotary embedding of q[q_dim] and k[kv_dim] with the tables
+ *   cos/sin[max_seq][head_dim / 2] at row pos; writes q_out[q_dim], the roped k into
+ *   k_cache[pos] and v into v_cache[pos] (FusedRoPEKVWriteOpNode's dispatch,
+ *   operators/impl/attention/FusedRoPEKVWrite.cu:13-75).  pos >= max_seq writes nothing and sets
+ *   *status to CUTB_ERR_INVALID (the reference does not check).
+ * cutb_attention_decode: out[h] = softmax(scale * q[h] . K[0..seqLen)) . V[0..seqLen) per query
+ *   head, head h reading KV head h / (n_heads / n_kv_heads) (AttentionOpNode's dispatch,
+ *   operators/impl/attention/Attention.cu:31-108).  n_heads / n_kv_heads <= 8, max_seq <= 32768.
+ *   seqLen > max_seq is clamped and reported through *status.  `workspace` holds
+ *   cutb_attention_workspace_bytes() bytes; its first 256 bytes must be zero before the first
+ *   call and are left zero by every call (launches sharing a workspace must not overlap).
+ */
+CUTB_API int cutb_rope_kv_write(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params,
+                                const float *cos_table, const float *sin_table, void *k_cache, void *v_cache, float *q_out,
+                                uint32_t q_dim, uint32_t kv_dim, uint32_t head_dim, uint64_t ld, uint32_t max_seq, int *status,
+                                void *stream);
+CUTB_API uint64_t cutb_attention_workspace_bytes(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_seq);
+CUTB_API int cutb_attention_decode(int kv_dtype, const float *q, const void *k_cache, const void *v_cache, const uint32_t *params,
+                                   float *out, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint64_t ld,
+                                   uint32_t max_seq, float scale, void *workspace, uint64_t workspace_bytes, int *status,
+                                   void *stream);
 
 CUTB_API int cutb_version(void);
 CUTB_API const char *cutb_status_string(int status);

@@ -731,3 +731,95 @@ ORC_API float orc_argreduce(const float *v, size_t n, int is_max) {
   return (float)idx[0];
 }
 
+/* IEEE round-to-nearest-even float -> half (the conversion the device's __float2half performs
+ * when the reference's fp16 cache variants store a value, AttentionCommon.cuh:18-20). */
+ORC_API uint16_t orc_f32_to_f16_rne(float v) {
+  uint32_t u;
+  memcpy(&u, &v, sizeof(u));
+  uint32_t sign = (u >> 16) & 0x8000u, mag = u & 0x7FFFFFFFu;
+  if (mag >= 0x7F800000u) return (uint16_t)(sign | (mag > 0x7F800000u ? 0x7E00u : 0x7C00u));
+  if (mag >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u); /* rounds to >= 65520: infinity */
+  if (mag < 0x33000001u) return (uint16_t)sign;              /* <= 2^-25: zero (a tie goes to even) */
+  int32_t e = (int32_t)(mag >> 23) - 127;
+  uint32_t m = (mag & 0x7FFFFFu) | 0x800000u;
+  uint32_t shift = e < -14 ? (uint32_t)(13 + (-14 - e)) : 13u; /* subnormal halves drop more bits */
+  uint32_t kept = m >> shift, rem = m & ((1u << shift) - 1u), halfway = 1u << (shift - 1);
+  if (rem > halfway || (rem == halfway && (kept & 1u))) ++kept;
+  if (e < -14) return (uint16_t)(sign | kept); /* a carry into bit 10 is the smallest normal */
+  return (uint16_t)(sign | ((((uint32_t)(e + 15)) << 10) + (kept - 0x400u)));
+}
+
+/* operators/impl/attention/FusedRoPEKVWrite.cu:13-75 -- half-split rotary embedding of q and k
+ * at position pos (tables [max_seq][head_dim / 2]), roped k and v written to row pos of the
+ * caches (row stride ld; kv_half: caches hold halves, stored round-to-nearest-even).  Plain
+ * float products and sums in the kernel's order. */
+ORC_API void orc_rope_kv_write(int kv_half, const float *q, const float *k, const float *v, uint32_t pos, const float *cos_t,
+                               const float *sin_t, void *k_cache, void *v_cache, float *q_out, size_t q_dim, size_t kv_dim,
+                               size_t head_dim, size_t ld) {
+  size_t half = head_dim / 2;
+  const float *c = cos_t + (size_t)pos * half, *s = sin_t + (size_t)pos * half;
+  for (size_t pass = 0; pass < 2; ++pass) {
+    const float *x = pass ? k : q;
+    size_t n = pass ? kv_dim : q_dim;
+    for (size_t i = 0; i < n; ++i) {
+      size_t in_head = i % head_dim;
+      volatile float a, b; /* keep the two products rounded separately */
+      float r;
+      if (in_head < half) {
+        a = x[i] * c[in_head];
+        b = x[i + half] * s[in_head];
+        r = a - b;
+      } else {
+        a = x[i - half] * s[in_head - half];
+        b = x[i] * c[in_head - half];
+        r = a + b;
+      }
+      if (!pass) q_out[i] = r;
+      else if (kv_half) ((uint16_t *)k_cache)[(size_t)pos * ld + i] = orc_f32_to_f16_rne(r);
+      else ((float *)k_cache)[(size_t)pos * ld + i] = r;
+    }
+  }
+  for (size_t i = 0; i < kv_dim; ++i) {
+    if (kv_half) ((uint16_t *)v_cache)[(size_t)pos * ld + i] = orc_f32_to_f16_rne(v[i]);
+    else ((float *)v_cache)[(size_t)pos * ld + i] = v[i];
+  }
+}
+
+/* operators/impl/attention/Attention.cu:31-108 (and the CPU helper of the reference's own test,
+ * tests/runtime/RuntimeTests.cpp:5946-5991) -- per query head: scores = (q . K[t]) * scale over
+ * the first seq_len cache rows, softmax, weighted sum of V; head h reads KV head
+ * h / (n_heads / n_kv_heads).  Accumulated in double, so the checker is the more exact side. */
+ORC_API void orc_attention(int kv_half, const float *q, const void *k_cache, const void *v_cache, size_t seq_len, float *out,
+                           size_t n_heads, size_t n_kv_heads, size_t head_dim, size_t ld, float scale) {
+  size_t n_rep = n_heads / n_kv_heads;
+  double *score = (double *)malloc((seq_len ? seq_len : 1) * sizeof(double));
+  for (size_t h = 0; h < n_heads; ++h) {
+    size_t kvh = h / n_rep;
+    double mx = -1e30, sum = 0.0;
+    for (size_t t = 0; t < seq_len; ++t) {
+      double dot = 0.0;
+      for (size_t d = 0; d < head_dim; ++d) {
+        size_t at = t * ld + kvh * head_dim + d;
+        double kv = kv_half ? (double)orc_f16_to_f32(((const uint16_t *)k_cache)[at]) : (double)((const float *)k_cache)[at];
+        dot += (double)q[h * head_dim + d] * kv;
+      }
+      score[t] = dot * (double)scale;
+      if (score[t] > mx) mx = score[t];
+    }
+    for (size_t t = 0; t < seq_len; ++t) {
+      score[t] = exp(score[t] - mx);
+      sum += score[t];
+    }
+    for (size_t d = 0; d < head_dim; ++d) {
+      double acc = 0.0;
+      for (size_t t = 0; t < seq_len; ++t) {
+        size_t at = t * ld + kvh * head_dim + d;
+        double vv = kv_half ? (double)orc_f16_to_f32(((const uint16_t *)v_cache)[at]) : (double)((const float *)v_cache)[at];
+        acc += score[t] * vv;
+      }
+      out[h * head_dim + d] = seq_len ? (float)(acc / sum) : 0.0f;
+    }
+  }
+  free(score);
+}
+

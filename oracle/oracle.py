@@ -50,6 +50,8 @@ def lib() -> C.CDLL:
         _lib.orc_epilogue.restype = C.c_float
         _lib.orc_epilogue.argtypes = [C.c_float, C.c_int, C.c_int, C.c_float]
         _lib.orc_requant_q4k_affine.restype = C.c_int
+        _lib.orc_f32_to_f16_rne.restype = C.c_uint16
+        _lib.orc_f32_to_f16_rne.argtypes = [C.c_float]
         _lib.orc_argreduce.restype = C.c_float
         _lib.orc_num_threads.restype = C.c_int
     return _lib
@@ -313,4 +315,35 @@ def embedding(indices: np.ndarray, table: np.ndarray) -> np.ndarray:
 def argreduce(v: np.ndarray, is_max: bool = True) -> float:
     v = np.ascontiguousarray(v, dtype=np.float32).reshape(-1)
     return float(lib().orc_argreduce(_p(v), C.c_size_t(v.size), C.c_int(1 if is_max else 0)))
+
+
+def f32_to_f16_rne(x: float) -> int:
+    return int(lib().orc_f32_to_f16_rne(C.c_float(x)))
+
+
+def rope_kv_write(q, k, v, pos: int, cos_t, sin_t, k_cache: np.ndarray, v_cache: np.ndarray, head_dim: int) -> np.ndarray:
+    """Writes row `pos` of the caches ([max_seq, ld], float32 or float16) in place; returns roped q."""
+    q, k, v = (np.ascontiguousarray(a, dtype=np.float32) for a in (q, k, v))
+    cos_t, sin_t = (np.ascontiguousarray(a, dtype=np.float32) for a in (cos_t, sin_t))
+    assert k_cache.dtype == v_cache.dtype and k_cache.dtype in (np.float32, np.float16)
+    assert k_cache.flags.c_contiguous and v_cache.flags.c_contiguous
+    out = np.empty_like(q)
+    lib().orc_rope_kv_write(C.c_int(int(k_cache.dtype == np.float16)), _p(q), _p(k), _p(v), C.c_uint32(pos), _p(cos_t), _p(sin_t),
+                            _p(k_cache), _p(v_cache), _p(out), C.c_size_t(q.size), C.c_size_t(k.size), C.c_size_t(head_dim),
+                            C.c_size_t(k_cache.shape[1]))
+    return out
+
+
+def attention(q, k_cache: np.ndarray, v_cache: np.ndarray, seq_len: int, n_heads: int, n_kv_heads: int, head_dim: int,
+              scale: float | None = None) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    assert k_cache.dtype == v_cache.dtype and k_cache.dtype in (np.float32, np.float16)
+    k_cache, v_cache = np.ascontiguousarray(k_cache), np.ascontiguousarray(v_cache)
+    out = np.empty(n_heads * head_dim, dtype=np.float32)
+    if scale is None:
+        scale = 1.0 / float(np.sqrt(np.float32(head_dim)))
+    lib().orc_attention(C.c_int(int(k_cache.dtype == np.float16)), _p(q), _p(k_cache), _p(v_cache), C.c_size_t(seq_len), _p(out),
+                        C.c_size_t(n_heads), C.c_size_t(n_kv_heads), C.c_size_t(head_dim), C.c_size_t(k_cache.shape[1]),
+                        C.c_float(scale))
+    return out
 

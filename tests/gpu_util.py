@@ -18,14 +18,14 @@ def rel_l2(got: np.ndarray, ref: np.ndarray) -> float:
     return float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30))
 
 
-def run_blocks(fmt, A_np, W_np, N, *, variant=L.VARIANT_AUTO, D_np=None, fusion_type=0, fusion_op=0, with_status=True):
+def run_blocks(fmt, A_np, W_np, N, *, variant=L.VARIANT_AUTO, D_np=None, fusion_type=0, fusion_op=0, with_status=True, flags=0):
     """C-ABI quantized matmul over GGUF blocks on numpy inputs; returns (C, variant used, status word)."""
     A = dev(A_np)
     W = dev(W_np)
     D = dev(D_np) if D_np is not None else None
     status = torch.zeros(1, dtype=torch.int32, device="cuda") if with_status else None
     d, C_out, keep = ops.make_desc(A, W, fmt, N, D=D, fusion_type=fusion_type, fusion_op=fusion_op, variant=variant,
-                                   status=status)
+                                   status=status, flags=flags)
     used = ops.select_variant(d)
     need = ops.workspace_bytes(d)
     ws = None

@@ -1,0 +1,121 @@
+"""The recorded decode step of a Llama-style decoder against a float64 composition of the CPU
+checker's pieces (dequantised weights, RMSNorm, RoPE + fp16 cache write, attention), on small
+geometries: logits within rel-L2 1e-3 per step with forced tokens, then greedy decoding through the
+captured graph equal to the eager path token for token."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+BLOCK = {0: (34, 32), 1: (18, 32), 2: (144, 256)}  # format -> (block bytes, weights per block)
+
+
+def _soften(raw: np.ndarray, fmt: int) -> np.ndarray:
+    """Divides the fp16 super-block scales of Q4_K by 16 (exponent arithmetic on normal halves): the
+    benchmark's Q4_K distribution gives weights of magnitude ~2, which makes the softmax one-hot
+    and a tolerance comparison ill-conditioned; the 32-weight formats are small already."""
+    shift = 4 if fmt == 2 else 0
+    if shift == 0:
+        return raw
+    bb, _ = BLOCK[fmt]
+    blocks = raw.reshape(-1, bb).copy()
+    for off in ((0, 2) if fmt == 2 else (0,)):
+        h = blocks[:, off:off + 2].copy().view(np.uint16).reshape(-1)
+        e = (h >> 10) & 0x1F
+        h = np.where(e > shift, h - (shift << 10), 0).astype(np.uint16)
+        blocks[:, off:off + 2] = h.view(np.uint8).reshape(-1, 2)
+    return blocks.reshape(-1)
+
+
+class Reference:
+    def __init__(self, cfg, w):
+        self.cfg = cfg
+        deq = lambda raw, n, k: O.dequant_rows(cfg.fmt, raw, n, k).astype(np.float64)
+        qkv_n = cfg.q_dim + 2 * cfg.kv_dim
+        self.layers = [dict(wqkv=deq(l["wqkv"], qkv_n, cfg.hidden), wo=deq(l["wo"], cfg.hidden, cfg.q_dim),
+                            wgate=deq(l["wgate"], cfg.ffn, cfg.hidden), wup=deq(l["wup"], cfg.ffn, cfg.hidden),
+                            wdown=deq(l["wdown"], cfg.hidden, cfg.ffn), attn_norm=l["attn_norm"], ffn_norm=l["ffn_norm"])
+                       for l in w["layers"]]
+        self.final_norm, self.lm = w["final_norm"], deq(w["lm_head"], cfg.vocab, cfg.hidden)
+        self.table = w["embedding"]
+        from cut_b200.llama_decode import rope_tables
+
+        self.cos_t, self.sin_t = rope_tables(cfg)
+        self.kc = [np.zeros((cfg.max_seq, cfg.kv_dim), np.float16) for _ in range(cfg.n_layers)]
+        self.vc = [np.zeros((cfg.max_seq, cfg.kv_dim), np.float16) for _ in range(cfg.n_layers)]
+
+    def step(self, token, pos):
+        cfg = self.cfg
+        x = self.table[token].astype(np.float64)
+        norm = lambda v, wt: O.rmsnorm(v.astype(np.float32), wt, cfg.eps).astype(np.float64)
+        for l, lw in enumerate(self.layers):
+            qkv = (lw["wqkv"] @ norm(x, lw["attn_norm"])).astype(np.float32)
+            q, k, v = qkv[:cfg.q_dim], qkv[cfg.q_dim:cfg.q_dim + cfg.kv_dim], qkv[cfg.q_dim + cfg.kv_dim:]
+            qr = O.rope_kv_write(q, k, v, pos, self.cos_t, self.sin_t, self.kc[l], self.vc[l], cfg.head_dim)
+            a = O.attention(qr, self.kc[l], self.vc[l], pos + 1, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim).astype(np.float64)
+            x = x + lw["wo"] @ a
+            h = norm(x, lw["ffn_norm"])
+            g = lw["wgate"] @ h
+            x = x + lw["wdown"] @ ((g / (1.0 + np.exp(-g))) * (lw["wup"] @ h))
+        return self.lm @ norm(x, self.final_norm)
+
+
+@pytest.mark.parametrize("fmt", [2, 0, 1])
+def test_decode_steps_match_composed_checker(fmt):
+    import torch
+
+    from cut_b200.llama_decode import LlamaConfig, LlamaDecoder, synthetic_weights
+
+    cfg = LlamaConfig(n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=512, max_seq=32, fmt=fmt)
+    w = synthetic_weights(cfg, seed=fmt + 1)
+    for lw in w["layers"]:
+        for k in ("wqkv", "wo", "wgate", "wup", "wdown"):
+            lw[k] = _soften(lw[k], fmt)
+    w["lm_head"] = _soften(w["lm_head"], fmt)
+    w["embedding"] = (w["embedding"] * 50).astype(np.float32)
+    dec, ref = LlamaDecoder(cfg, w), Reference(cfg, w)
+    tokens = [3, 500, 17, 17, 0, 301, 42]
+    for pos, tok in enumerate(tokens):
+        got = dec.step(tok, pos).cpu().numpy().astype(np.float64)
+        want = ref.step(tok, pos)
+        rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+        assert np.isfinite(got).all() and rel <= 1e-3, (pos, rel)
+    dec.check_status()
+    # the caches hold what the checker's hold (fp16, one rounding of nearly equal fp32 values)
+    for l in range(cfg.n_layers):
+        kc = dec.k_cache[l][: len(tokens), : cfg.kv_dim].float().cpu().numpy()
+        assert np.allclose(kc, ref.kc[l][: len(tokens)].astype(np.float32), rtol=2e-3, atol=2e-3)
+
+    # greedy continuation: eager steps against the captured graph, token for token
+    pos0 = len(tokens)
+    eager, tok = [], 7
+    for i in range(6):
+        logits = dec.step(tok, pos0 + i)
+        tok = int(torch.argmax(logits).item())
+        assert tok == int(dec.next_tok.item())
+        eager.append(tok)
+    dec.set_position(7, pos0)
+    dec.capture()
+    got = []
+    for i in range(6):
+        dec.replay(1)
+        got.append(int(dec.token.item()))
+    assert got == eager
+    assert int(dec.params[0].item()) == pos0 + 6
+    dec.check_status()
+    assert dec.launches_per_step >= 3 + 9 * cfg.n_layers + 1
+
+
+def test_position_past_the_cache_is_reported():
+    from cut_b200 import _lib as L
+    from cut_b200.llama_decode import LlamaConfig, LlamaDecoder, synthetic_weights
+
+    cfg = LlamaConfig(n_layers=1, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=256, vocab=64, max_seq=4, fmt=0)
+    dec = LlamaDecoder(cfg, synthetic_weights(cfg))
+    dec.step(1, 3)
+    dec.check_status()
+    dec.step(1, 4)
+    with pytest.raises(L.CutbError):
+        dec.check_status()

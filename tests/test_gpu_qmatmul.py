@@ -48,6 +48,24 @@ def test_gemv_mma_matches_checker(fmt, dtype, M, K, N):
 
 
 @pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 1024), (1, 14336, 512), (2, 1024, 264), (8, 512, 40), (16, 1024, 264)])
+def test_fp32_activations_staged_at_16_bits(fmt, M, K, N):
+    """CUTB_FLAG_ACT_16BIT: fp32 activations at one 16-bit level per block (up to 16 rows instead of 8),
+    values far outside the fp16 range included: the block scale is fp32."""
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(fmt, M, K, N, np.float32, seed=M + K + fmt)
+    A = (A * np.float32(3.0e5)).astype(np.float32)  # > 65504: fp16 activations would overflow
+    got, used, st = run_blocks(fmt, A, W, N, flags=L.FLAG_ACT_16BIT)
+    assert used == L.VARIANT_GEMV_MMA and st == 0
+    ref = _ref(fmt, A, W, M, K, N)
+    assert rel_l2(got, ref) <= TOL
+    two, _, _ = run_blocks(fmt, A, W, N) if M <= 8 else (None, None, None)
+    if two is not None:  # the default two-level staging is the more exact of the two
+        assert rel_l2(two, ref) <= rel_l2(got, ref) + 1e-7
+
+
+@pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("dtype,M", [(np.float16, 9), (np.float16, 16), (np.float32, 5), (np.float32, 8)])
 def test_gemv_mma_wide_batches(fmt, dtype, M):
     from gpu_util import rel_l2, run_blocks
