@@ -18,6 +18,7 @@ FUSION_NONE, FUSION_UNARY, FUSION_BINARY = 0, 1, 2
 VARIANT_AUTO, VARIANT_GENERIC, VARIANT_GEMV_MMA, VARIANT_GEMM_TC = -1, 0, 1, 2
 FLAG_NO_OVERLAP = 1
 FLAG_ACT_16BIT = 2
+FLAG_A_RMSNORM = 4
 
 # every symbol include/cutb.h declares
 EXPORTS = [
@@ -44,6 +45,7 @@ class QMatmulDesc(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
         ("status", C.c_void_p),
         ("flags", C.c_uint32),
+        ("a_norm_weight", C.c_void_p), ("a_norm_eps", C.c_float),
     ]
 
 

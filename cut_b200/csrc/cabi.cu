@@ -164,6 +164,16 @@ int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
   if (int rc = validate(desc)) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int v = select(*desc);
+  if (desc->flags & CUTB_FLAG_A_RMSNORM) {
+    if (!desc->a_norm_weight) {
+      set_last_error("qmatmul: CUTB_FLAG_A_RMSNORM without a_norm_weight");
+      return CUTB_ERR_INVALID;
+    }
+    if (v != CUTB_VARIANT_GEMV_MMA) {
+      set_last_error("qmatmul: the fused RMSNorm exists in the decode mat-vec only (variant %s was selected)", cutb_variant_name(v));
+      return CUTB_ERR_UNSUPPORTED;
+    }
+  }
   switch (v) {
     case CUTB_VARIANT_GEMV_MMA:
       if (!qgemv_blocks_supported(*desc)) {

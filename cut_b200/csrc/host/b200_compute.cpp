@@ -96,6 +96,7 @@ public:
   ~B200Compute() override {
     cudaStreamSynchronize(stream_);
     if (workspace_) cudaFree(workspace_);
+    if (attnWs_) cudaFree(attnWs_);
     cudaFree(status_);
     cudaStreamDestroy(stream_);
   }
@@ -189,7 +190,10 @@ public:
     if (!desc) throw std::runtime_error("B200Compute: not a kernel descriptor");
     switch (desc->op) {
       case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case TransposeQ4: break;
-      case RMSNorm: case Embedding: case ReduceArgmax: case ReduceArgmin: break;
+      case RMSNorm: case Embedding: case ReduceArgmax: case ReduceArgmin: case Attention: break;
+      case CacheWrite:
+        if (desc->variant != FusedRoPEKVWriteOpNode::kVariant) throw std::runtime_error("B200Compute: no kernel for this CacheWrite operator");
+        break;
       default: throw std::runtime_error("B200Compute: no kernel for operator " + std::to_string(desc->op));
     }
     if (desc->op == Dequantize || desc->op == MatMulQBlocks) (void)cutbFormat(desc->format);
@@ -226,6 +230,14 @@ protected:
         need = w > need ? w : need;
       }
     ensureWorkspace(need);
+    size_t attnNeed = 0;
+    for (const auto &d : cb->dispatches)
+      if (!d.isBarrier && descOf(d).op == Attention) {
+        const AttnPC pc = pushConstants<AttnPC>(d);
+        const size_t w = cutb_attention_workspace_bytes(pc.nHeads, pc.nKvHeads, pc.headDim, buf(d, 1).getShape()[0]);
+        attnNeed = w > attnNeed ? w : attnNeed;
+      }
+    ensureAttnWorkspace(attnNeed);
     if (reusable) {
       // warm launch outside capture (first-use kernel attributes), then capture the same list
       launchAll(*cb, descs);
@@ -279,6 +291,21 @@ private:
     cudaCheck(cudaMalloc(&workspace_, need), "cudaMalloc(workspace)");
     workspaceBytes_ = need;
   }
+
+  void ensureAttnWorkspace(size_t need) {
+    if (need <= attnWsBytes_) return;
+    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    if (attnWs_) cudaFree(attnWs_);
+    attnWs_ = nullptr;
+    cudaCheck(cudaMalloc(&attnWs_, need), "cudaMalloc(attention workspace)");
+    cudaCheck(cudaMemset(attnWs_, 0, need), "cudaMemset(attention workspace)");
+    attnWsBytes_ = need;
+  }
+
+  struct AttnPC {
+    uint32_t nHeads, nKvHeads, headDim, kvDim, alignedKvDim, nRep;
+    float scale;
+  };
 
   static const KernelDesc &descOf(const ComputeDispatch &d) {
     auto *m = d.shader.as<ShaderModule>();
@@ -387,6 +414,23 @@ private:
         const DeviceBuffer &idx = buf(d, 0), &table = buf(d, 1), &out = buf(d, 2);
         cutbCheck(cutb_embedding((const uint32_t *)idx.data, (const float *)table.data, (float *)out.data, pc.numIndices,
                                  pc.embDim, table.getShape()[0], status_, stream_), "Embedding");
+      } else if (k.op == CacheWrite) {  // fused RoPE + KV-cache write
+        struct PC {
+          uint32_t qDim, kvDim, headDim, halfDim, alignedKvDim;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &kc = buf(d, 6);
+        cutbCheck(cutb_rope_kv_write(k.dtypeA == (uint32_t)DataType::Float16 ? CUTB_F16 : CUTB_F32, (const float *)buf(d, 0).data,
+                                     (const float *)buf(d, 1).data, (const float *)buf(d, 2).data, (const uint32_t *)buf(d, 3).data,
+                                     (const float *)buf(d, 4).data, (const float *)buf(d, 5).data, kc.data, buf(d, 7).data,
+                                     (float *)buf(d, 8).data, pc.qDim, pc.kvDim, pc.headDim, pc.alignedKvDim, kc.getShape()[0],
+                                     status_, stream_), "FusedRoPEKVWrite");
+      } else if (k.op == Attention) {
+        const AttnPC pc = pushConstants<AttnPC>(d);
+        const DeviceBuffer &kc = buf(d, 1);
+        cutbCheck(cutb_attention_decode(k.dtypeA == (uint32_t)DataType::Float16 ? CUTB_F16 : CUTB_F32, (const float *)buf(d, 0).data,
+                                        kc.data, buf(d, 2).data, (const uint32_t *)buf(d, 3).data, (float *)buf(d, 4).data, pc.nHeads,
+                                        pc.nKvHeads, pc.headDim, pc.alignedKvDim, kc.getShape()[0], pc.scale, attnWs_, attnWsBytes_,
+                                        status_, stream_), "Attention");
       } else if (k.op == ReduceArgmax || k.op == ReduceArgmin) {
         const uint32_t n = pushConstants<uint32_t>(d);
         cutbCheck(cutb_argreduce(k.op == ReduceArgmax, (const float *)buf(d, 0).data, (float *)buf(d, 1).data, n, stream_),
@@ -401,6 +445,8 @@ private:
   cudaStream_t stream_ = nullptr;
   void *workspace_ = nullptr;
   size_t workspaceBytes_ = 0;
+  void *attnWs_ = nullptr;  // attention scratch; its arrival counters start at zero and every launch leaves them zero
+  size_t attnWsBytes_ = 0;
   int *status_ = nullptr;
   size_t nextId_ = 0, activeBytes_ = 0, bufferCount_ = 0, totalMem_ = 0;
   uint32_t smemOptin_ = 0;

@@ -4,6 +4,8 @@
 // behind ComputeInterface (b200_compute.cpp) and, below that, the C ABI.
 #include "cut_api.h"
 
+#include <cmath>
+
 #include <cstdio>
 #include <cstdlib>
 #include <fstream>
@@ -580,6 +582,76 @@ std::string GlobalReduceOpNode::displayName() const {
   }
 }
 
+AttentionOpNode::AttentionOpNode(TensorStore &store, const Tensor &q, const Tensor &kCache, const Tensor &vCache,
+                                 const Tensor &runtimeParams, uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim,
+                                 const Tensor &preallocOutput, std::optional<uint32_t> spec)
+    : OpNode(Attention, store, spec), nHeads_(nHeads), nKvHeads_(nKvHeads), headDim_(headDim) {
+  if (nHeads == 0 || nKvHeads == 0 || headDim == 0 || nHeads % nKvHeads != 0)
+    throw std::runtime_error("attention: nHeads must be a positive multiple of nKvHeads and headDim positive");
+  dtype_ = store.getTensor(kCache).getDtype();
+  if (store.getTensor(vCache).getDtype() != dtype_) throw std::runtime_error("attention: K and V caches must share a dtype");
+  kvDim_ = nKvHeads * headDim;
+  alignedKvDim_ = (kvDim_ + 3) & ~3u;
+  nRep_ = nHeads / nKvHeads;
+  scale_ = 1.0f / std::sqrt(static_cast<float>(headDim));
+  inputs_ = {q, kCache, vCache, runtimeParams};
+  output_ = preallocOutput ? preallocOutput : store.createTensorEmpty({nHeads * headDim}, DataType::Float32);
+}
+
+std::optional<std::vector<uint32_t>> AttentionOpNode::shader() const {
+  if (dtype_ != DataType::Float32 && dtype_ != DataType::Float16) return std::nullopt;
+  if (headDim_ > 128 || nRep_ > 8) return std::nullopt;  // the kernels' limits (the reference's shared query holds 128 floats)
+  KernelDesc d;
+  d.op = Attention;
+  d.dtypeA = d.dtypeB = (uint32_t)dtype_;
+  return d.encode();
+}
+
+std::vector<uint8_t> AttentionOpNode::pushConstants() const {
+  struct {
+    uint32_t nHeads, nKvHeads, headDim, kvDim, alignedKvDim, nRep;
+    float scale;
+  } pc{nHeads_, nKvHeads_, headDim_, kvDim_, alignedKvDim_, nRep_, scale_};
+  return toBytes(pc);
+}
+
+FusedRoPEKVWriteOpNode::FusedRoPEKVWriteOpNode(TensorStore &store, const Tensor &q, const Tensor &k, const Tensor &v,
+                                               const Tensor &runtimeParams, const Tensor &cosTable, const Tensor &sinTable,
+                                               const Tensor &kCache, const Tensor &vCache, uint32_t headDim,
+                                               std::optional<uint32_t> spec)
+    : OpNode(CacheWrite, store, spec), headDim_(headDim) {
+  const auto &sq = store.getTensor(q).getShape();
+  const auto &sk = store.getTensor(k).getShape();
+  if (sq.empty() || sk.empty() || store.getTensor(v).getShape() != sk)
+    throw std::runtime_error("fusedRoPEKVWrite: q, k and v must be vectors, k and v of one length");
+  qDim_ = sq[0];
+  kvDim_ = sk[0];
+  if (headDim == 0 || headDim % 2 != 0 || qDim_ % headDim != 0 || kvDim_ % headDim != 0)
+    throw std::runtime_error("fusedRoPEKVWrite: headDim must be even and divide the q and k lengths");
+  cacheDtype_ = store.getTensor(kCache).getDtype();
+  if (store.getTensor(vCache).getDtype() != cacheDtype_) throw std::runtime_error("fusedRoPEKVWrite: K and V caches must share a dtype");
+  halfDim_ = headDim / 2;
+  alignedKvDim_ = (kvDim_ + 3) & ~3u;
+  inputs_ = {q, k, v, runtimeParams, cosTable, sinTable, kCache, vCache};
+  output_ = store.createTensorEmpty({qDim_}, DataType::Float32);
+}
+
+std::optional<std::vector<uint32_t>> FusedRoPEKVWriteOpNode::shader() const {
+  if (cacheDtype_ != DataType::Float32 && cacheDtype_ != DataType::Float16) return std::nullopt;
+  KernelDesc d;
+  d.op = CacheWrite;
+  d.variant = kVariant;
+  d.dtypeA = d.dtypeB = (uint32_t)cacheDtype_;
+  return d.encode();
+}
+
+std::vector<uint8_t> FusedRoPEKVWriteOpNode::pushConstants() const {
+  struct {
+    uint32_t qDim, kvDim, headDim, halfDim, alignedKvDim;
+  } pc{qDim_, kvDim_, headDim_, halfDim_, alignedKvDim_};
+  return toBytes(pc);
+}
+
 // ---------------------------------------------------------------------------
 // VariantSelector (runtime/VariantSelector.cpp:242-428) with a small JSON reader
 // ---------------------------------------------------------------------------
@@ -861,6 +933,17 @@ Tensor Operations::embedding(const Tensor &indices, const Tensor &weight, const 
 
 Tensor Operations::reduce(OperatorEnum op, const Tensor &a, std::optional<uint32_t> spec) {
   return dispatch(std::make_unique<GlobalReduceOpNode>(op, *store_, a, spec));
+}
+
+Tensor Operations::attention(const Tensor &q, const Tensor &kCache, const Tensor &vCache, const Tensor &runtimeParams,
+                             uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, const Tensor &preallocOutput) {
+  return dispatch(std::make_unique<AttentionOpNode>(*store_, q, kCache, vCache, runtimeParams, nHeads, nKvHeads, headDim, preallocOutput));
+}
+
+Tensor Operations::fusedRoPEKVWrite(const Tensor &q, const Tensor &k, const Tensor &v, const Tensor &runtimeParams,
+                                    const Tensor &cosTable, const Tensor &sinTable, const Tensor &kCache, const Tensor &vCache,
+                                    uint32_t headDim) {
+  return dispatch(std::make_unique<FusedRoPEKVWriteOpNode>(*store_, q, k, v, runtimeParams, cosTable, sinTable, kCache, vCache, headDim));
 }
 
 Runtime::Runtime(std::unique_ptr<ComputeInterface> iface)

@@ -69,6 +69,7 @@ enum OperatorEnum : uint32_t {
   UnaryHardswish = 142, UnaryHardsigmoid = 143, UnaryRsqrt = 148,
   ReduceSum = 208, ReduceMean = 209, ReduceMin = 210, ReduceMax = 211, ReduceArgmax = 214, ReduceArgmin = 215,
   RMSNorm = 312, Embedding = 320,
+  CacheWrite = 360, Attention = 361,
   MatMulQ8 = 371, MatMulQ4 = 374,
   MatMulQBlocks = 375,  // new: weights as raw GGUF blocks
   Dequantize = 390, TransposeQ4 = 401,
@@ -435,6 +436,52 @@ private:
   uint32_t actualInner_ = 0, alignedInner_ = 0;
 };
 
+/// Decode attention of one roped query over the populated KV cache with grouped-query heads
+/// (operators/impl/attention/AttentionOp.cpp:57-122).  runtimeParams is the device buffer
+/// {pos, seqLen}; the cache dtype (Float32 or Float16) selects the kernel, q and the output stay fp32.
+class AttentionOpNode : public OpNode {
+public:
+  AttentionOpNode(TensorStore &store, const Tensor &q, const Tensor &kCache, const Tensor &vCache, const Tensor &runtimeParams,
+                  uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, const Tensor &preallocOutput = {},
+                  std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return DataType::Float32; }
+  size_t shaderKey() const override { return static_cast<size_t>(op_) | ((static_cast<size_t>(dtype_) & 0xF) << 56); }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return {nHeads_ * headDim_}; }
+  ThreadSize dispatchSize() const override { return {nHeads_ * 256, 1, 1}; }
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "Attention"; }
+
+private:
+  DataType dtype_ = DataType::Float32;
+  uint32_t nHeads_, nKvHeads_, headDim_, kvDim_, alignedKvDim_, nRep_;
+  float scale_;
+};
+
+/// Half-split RoPE of q and k at runtimeParams[0] fused with the write of the roped k and of v
+/// into row pos of the caches; the output is the roped q
+/// (operators/impl/attention/AttentionOp.cpp:553-612).
+class FusedRoPEKVWriteOpNode : public OpNode {
+public:
+  static constexpr uint32_t kVariant = 1;  ///< KernelDesc::variant of this user of the CacheWrite op code
+  FusedRoPEKVWriteOpNode(TensorStore &store, const Tensor &q, const Tensor &k, const Tensor &v, const Tensor &runtimeParams,
+                         const Tensor &cosTable, const Tensor &sinTable, const Tensor &kCache, const Tensor &vCache,
+                         uint32_t headDim, std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return DataType::Float32; }
+  size_t shaderKey() const override {
+    return static_cast<size_t>(op_) | (size_t{1} << 34) | ((static_cast<size_t>(cacheDtype_) & 0xF) << 56);
+  }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return {qDim_}; }
+  ThreadSize dispatchSize() const override { return {(qDim_ + 2 * kvDim_ + 255) / 256 * 256, 1, 1}; }
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "FusedRoPEKVWrite"; }
+
+private:
+  DataType cacheDtype_ = DataType::Float32;
+  uint32_t qDim_, kvDim_, headDim_, halfDim_, alignedKvDim_;
+};
+
 // ---- VariantSelector: tuning_data.json rules (runtime/VariantSelector.cpp:242-428) ----------
 class VariantSelector {
 public:
@@ -501,6 +548,10 @@ public:
                    std::optional<uint32_t> spec = {});
   /// Whole-tensor reduction (the reference's per-dimension form is outside this path).
   Tensor reduce(OperatorEnum op, const Tensor &a, std::optional<uint32_t> spec = {});
+  Tensor attention(const Tensor &q, const Tensor &kCache, const Tensor &vCache, const Tensor &runtimeParams, uint32_t nHeads,
+                   uint32_t nKvHeads, uint32_t headDim, const Tensor &preallocOutput = {});
+  Tensor fusedRoPEKVWrite(const Tensor &q, const Tensor &k, const Tensor &v, const Tensor &runtimeParams, const Tensor &cosTable,
+                          const Tensor &sinTable, const Tensor &kCache, const Tensor &vCache, uint32_t headDim);
   void barrier() { dispatcher_->encodeBarrier(); }
 
 private:

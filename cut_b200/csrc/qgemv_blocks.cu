@@ -91,6 +91,8 @@ struct GvParams {
   uint32_t stages;
   int fusion_type, fusion_op;
   int a_f32;
+  const float *norm_w;  // fused RMSNorm of the activation rows (nullptr: none)
+  float norm_eps;
   int *status;
   // Row-sharded scatter epilogue (world > 1): instead of C, the output slice is stored into
   // every rank's full output at column n_off.  Peer-mapped pointers; plain stores, no
@@ -486,7 +488,7 @@ constexpr float GV_QMAX = 32512.f;
 // 32 zero bytes, esc / sx are [blk][NT] (NT = number of virtual rows).
 template <int FMT, int AMODE, int NT, bool DIAG, int THREADS>
 __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *act, float *esc, float *sx, uint32_t k0,
-                                                  uint32_t nblk, uint32_t ncp, uint32_t tid) {
+                                                  uint32_t nblk, uint32_t ncp, uint32_t tid, const float *nscale) {
   constexpr uint32_t NV = DIAG ? NT : NT * 4;
   const uint32_t nrows = p.M;
   constexpr bool AF32 = AMODE != GV_A_HALF;      // fp32 loads
@@ -505,9 +507,12 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     float x[8];
     float amax = 0.f;
     const uint64_t rowbase = (uint64_t)m * p.lda + k0 + kb * 32;
+    const float rs = (nscale && live) ? nscale[m] : 1.f;
 #pragma unroll
     for (uint32_t i = 0; i < 8; ++i) {
-      x[i] = live ? load_act<AF32>(p.A, rowbase + (DIAG ? diag_elem<FMT>(even, ct, i) : frag_elem<FMT>(even, ct, i))) : 0.f;
+      const uint32_t el = DIAG ? diag_elem<FMT>(even, ct, i) : frag_elem<FMT>(even, ct, i);
+      x[i] = live ? load_act<AF32>(p.A, rowbase + el) : 0.f;
+      if (nscale && live) x[i] = x[i] * rs * __ldg(p.norm_w + k0 + kb * 32 + el);  // RMSNorm fused into the staging
       amax = fmaxf(amax, fabsf(x[i]));
     }
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -693,7 +698,41 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
   // Everything above only read the (constant) weights.  The activations, D and
   // C may belong to the previous kernel of the stream: wait for it to finish.
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  stage_activations<FMT, AMODE, NT, DIAG, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid);
+  const float *nscale = nullptr;
+  if (p.norm_w) {
+    // fused RMSNorm: every CTA needs the scale of the whole row, whatever K slice it stages; the
+    // reduction buffers are idle until the first tile
+    constexpr bool AF32N = AMODE != GV_A_HALF;
+    for (uint32_t m = 0; m < p.M; ++m) {
+      float ss = 0.f;
+      // K is a multiple of 256: two elements per thread and pass, four passes' loads in flight
+      for (uint32_t k = 2 * tid; k < p.K; k += 8 * GV_WARPS * 32) {
+        float v[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+          const uint32_t kk = k + u * 2 * GV_WARPS * 32;
+          const bool in = kk < p.K;
+          v[2 * u] = in ? load_act<AF32N>(p.A, (uint64_t)m * p.lda + kk) : 0.f;
+          v[2 * u + 1] = in ? load_act<AF32N>(p.A, (uint64_t)m * p.lda + kk + 1) : 0.f;
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 8; ++u) ss = fmaf(v[u], v[u], ss);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) red[warp * 16 + m] = ss;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
+    if (tid < p.M) {
+      float ss = 0.f;
+#pragma unroll
+      for (int w = 0; w < GV_WARPS; ++w) ss += red[w * 16 + tid];
+      red[GV_WARPS * 16 + tid] = rsqrtf(ss / (float)p.K + p.norm_eps);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
+    nscale = red + GV_WARPS * 16;
+  }
+  stage_activations<FMT, AMODE, NT, DIAG, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid, nscale);
   asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
 
   const uint32_t act_u = smem_u32(act), act_stride = ncp * 32, esc_u = smem_u32(esc), sx_u = smem_u32(sx);
@@ -1029,6 +1068,8 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
   p.fusion_type = d.fusion_type;
   p.fusion_op = d.fusion_op;
   p.a_f32 = amode != GV_A_HALF;
+  p.norm_w = (d.flags & CUTB_FLAG_A_RMSNORM) ? d.a_norm_weight : nullptr;
+  p.norm_eps = d.a_norm_eps;
   p.status = d.status;
   p.world = 0;
   p.n_off = p.ldc_total = 0;

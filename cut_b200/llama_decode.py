@@ -91,7 +91,7 @@ class LlamaDecoder:
     runs n further tokens from the device-resident {token, pos}, greedy (arg-max feeds back)."""
 
     def __init__(self, cfg: LlamaConfig, weights: dict, device: torch.device | str = "cuda", act_16bit: bool = True,
-                 overlap: bool = False):
+                 overlap: bool = False, fuse_norm: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("LlamaDecoder needs a CUDA device: there is no CPU path")
         if cfg.hidden % 4 or cfg.n_heads % cfg.n_kv_heads:
@@ -118,15 +118,21 @@ class LlamaDecoder:
         # overlap: let a mat-vec that follows a mat-vec (up after gate, down after up) prefetch under its predecessor's
         # tail.  Off by default: a chain of equal mat-vecs gains ~1.4 us per launch from it, the mixed step lost 7 %.
         self.overlap = overlap
+        # fuse_norm: the RMSNorms run inside the projections that consume them (no launch, no round trip of h)
+        self.fuse_norm = fuse_norm
         self._keep, self._descs, self.launches_per_step = [], [], 0
         self._plan()
         self.graph = None
 
     # -- the recorded sequence: a list of closures over prepared descriptors --------------------
-    def _matvec(self, A, W, N, out, fusion_type=L.FUSION_NONE, fusion_op=0, D=None, after_matvec=False):
+    def _matvec(self, A, W, N, out, fusion_type=L.FUSION_NONE, fusion_op=0, D=None, after_matvec=False, norm=None):
         d, _, keep = ops.make_desc(A, W, self.cfg.fmt, N, C_out=out.view(1, -1), D=D.view(1, -1) if D is not None else None,
                                    fusion_type=fusion_type, fusion_op=fusion_op, status=self.status,
                                    flags=self.act_flags | (0 if (after_matvec and self.overlap) else L.FLAG_NO_OVERLAP))
+        if norm is not None:  # the RMSNorm in front of this projection, applied while the mat-vec stages its activations
+            d.flags |= L.FLAG_A_RMSNORM
+            d.a_norm_weight, d.a_norm_eps = norm.data_ptr(), self.cfg.eps
+            keep = keep + (norm,)
         need = ops.workspace_bytes(d)
         if need:  # split-K shapes: scratch owned by this descriptor, sized before capture
             ws = torch.empty(need, dtype=torch.uint8, device=self.dev)
@@ -139,6 +145,7 @@ class LlamaDecoder:
     def _plan(self):
         cfg, lib = self.cfg, L.lib()
         seq = []
+        fuse = self.fuse_norm
         st = self.status.data_ptr()
         kvd = L.F16 if cfg.kv_dtype == torch.float16 else L.F32
 
@@ -152,8 +159,11 @@ class LlamaDecoder:
         scale = 1.0 / float(np.sqrt(np.float32(cfg.head_dim)))
         for l, lw in enumerate(self.layers):
             kc, vc = self.k_cache[l], self.v_cache[l]
-            seq.append(rms(self.x[0], lw["attn_norm"], self.h))
-            seq.append(self._matvec(self.h, lw["wqkv"], cfg.q_dim + 2 * cfg.kv_dim, self.qkv))
+            if fuse:
+                seq.append(self._matvec(self.x[0], lw["wqkv"], cfg.q_dim + 2 * cfg.kv_dim, self.qkv, norm=lw["attn_norm"]))
+            else:
+                seq.append(rms(self.x[0], lw["attn_norm"], self.h))
+                seq.append(self._matvec(self.h, lw["wqkv"], cfg.q_dim + 2 * cfg.kv_dim, self.qkv))
             seq.append(lambda kc=kc, vc=vc: L.check(lib.cutb_rope_kv_write(
                 kvd, q.data_ptr(), k.data_ptr(), v.data_ptr(), self.params.data_ptr(), self.cos_t.data_ptr(), self.sin_t.data_ptr(),
                 kc.data_ptr(), vc.data_ptr(), self.q_roped.data_ptr(), cfg.q_dim, cfg.kv_dim, cfg.head_dim, kc.stride(0), cfg.max_seq, st,
@@ -163,12 +173,18 @@ class LlamaDecoder:
                 cfg.n_kv_heads, cfg.head_dim, kc.stride(0), cfg.max_seq, scale, self.attn_ws.data_ptr(), self.attn_ws.numel(), st,
                 ops._stream_ptr())))
             seq.append(self._matvec(self.attn, lw["wo"], cfg.hidden, self.x[1], L.FUSION_BINARY, BINARY_ADD, self.x[0]))
-            seq.append(rms(self.x[1], lw["ffn_norm"], self.h))
-            seq.append(self._matvec(self.h, lw["wgate"], cfg.ffn, self.gate, L.FUSION_UNARY, UNARY_SILU))
-            seq.append(self._matvec(self.h, lw["wup"], cfg.ffn, self.act, L.FUSION_BINARY, BINARY_MUL, self.gate, after_matvec=True))
+            ffn_in, ffn_norm = (self.x[1], lw["ffn_norm"]) if fuse else (self.h, None)
+            if not fuse:
+                seq.append(rms(self.x[1], lw["ffn_norm"], self.h))
+            seq.append(self._matvec(ffn_in, lw["wgate"], cfg.ffn, self.gate, L.FUSION_UNARY, UNARY_SILU, norm=ffn_norm))
+            seq.append(self._matvec(ffn_in, lw["wup"], cfg.ffn, self.act, L.FUSION_BINARY, BINARY_MUL, self.gate, after_matvec=True,
+                                    norm=ffn_norm))
             seq.append(self._matvec(self.act, lw["wdown"], cfg.hidden, self.x[0], L.FUSION_BINARY, BINARY_ADD, self.x[1], after_matvec=True))
-        seq.append(rms(self.x[0], self.final_norm, self.h))
-        seq.append(self._matvec(self.h, self.lm_head, cfg.vocab, self.logits))
+        if fuse:
+            seq.append(self._matvec(self.x[0], self.lm_head, cfg.vocab, self.logits, norm=self.final_norm))
+        else:
+            seq.append(rms(self.x[0], self.final_norm, self.h))
+            seq.append(self._matvec(self.h, self.lm_head, cfg.vocab, self.logits))
         seq.append(lambda: L.check(lib.cutb_argreduce(1, self.logits.data_ptr(), self.next_tok.data_ptr(), cfg.vocab, ops._stream_ptr())))
         self._seq = seq
         # split-K mat-vecs launch a second (reduction) kernel

@@ -90,8 +90,13 @@ enum {
  *     work and selects the fastest kernel shape for a single row.  The result then carries the
  *     error fp16 activations would (relative error of a dot product about 3e-5) but keeps the
  *     fp32 range, so large activations cannot overflow.  Ignored for fp16 activations and by the
- *     other variants. */
-enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2 };
+ *     other variants.
+ *   CUTB_FLAG_A_RMSNORM: the decode mat-vec normalises its activation rows while it stages them:
+ *     A'[m, k] = A[m, k] * rsqrt(mean_k(A[m, k]^2) + a_norm_eps) * a_norm_weight[k], i.e. the
+ *     RMSNorm that precedes every projection of a decoder layer (RMSNormOpNode,
+ *     operators/impl/rmsnorm/RMSNormOp.cpp:7-76) without its own launch and round trip.  Only the
+ *     CUTB_VARIANT_GEMV_MMA kernel implements it; other shapes return CUTB_ERR_UNSUPPORTED. */
+enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2, CUTB_FLAG_A_RMSNORM = 4 };
 
 /*
  * C[M, N] = epilogue(A[M, K] * dequant(W)), fp32 accumulate, fp32 output.
@@ -124,6 +129,8 @@ typedef struct cutb_qmatmul_desc {
   uint64_t workspace_bytes;
   int32_t *status;     /* optional device int: kernels store CUTB_ERR_TIMEOUT here if a bounded wait gives up */
   uint32_t flags;      /* CUTB_FLAG_* */
+  const float *a_norm_weight; /* CUTB_FLAG_A_RMSNORM: device, [K] fp32 */
+  float a_norm_eps;           /* CUTB_FLAG_A_RMSNORM */
 } cutb_qmatmul_desc;
 
 /* Scratch bytes cutb_qmatmul needs for this descriptor (0 for most shapes;

@@ -368,7 +368,55 @@ void layerOperatorNodes() {
   CHECK(f.raw->executed.size() == 4 && f.raw->executed[2].label == "Embedding" && f.raw->executed[3].label == "ReduceArgmin");
 }
 
+// AttentionOpNode / FusedRoPEKVWriteOpNode: geometry, push constants, keys, validation
+void attentionNodes() {
+  Fixture f;
+  TensorStore &s = f.rt.store();
+  const uint32_t nH = 8, nKv = 2, hd = 16, maxSeq = 32;
+  auto q = s.createTensor({nH * hd}, DataType::Float32), k = s.createTensor({nKv * hd}, DataType::Float32);
+  auto v = s.createTensor({nKv * hd}, DataType::Float32), params = s.createTensor({2}, DataType::UInt32);
+  auto cosT = s.createTensor({maxSeq * hd / 2}, DataType::Float32), sinT = s.createTensor({maxSeq * hd / 2}, DataType::Float32);
+  auto kc = s.createTensor({maxSeq, nKv * hd}, DataType::Float16), vc = s.createTensor({maxSeq, nKv * hd}, DataType::Float16);
+  auto kc32 = s.createTensor({maxSeq, nKv * hd}, DataType::Float32), vc32 = s.createTensor({maxSeq, nKv * hd}, DataType::Float32);
+  AttentionOpNode a(s, q, kc, vc, params, nH, nKv, hd);
+  CHECK(a.op() == Attention && a.outputShape() == (std::vector<uint32_t>{nH * hd}) && a.outputDtype() == DataType::Float32);
+  CHECK(a.dispatchSize().x == nH * 256 && a.displayName() == "Attention");
+  struct {
+    uint32_t nHeads, nKvHeads, headDim, kvDim, alignedKvDim, nRep;
+    float scale;
+  } pc;
+  auto b = a.bindings();
+  CHECK(b.size() == 6 && b[4].handle == a.output() && b[5].bytes.size() == sizeof(pc));
+  std::memcpy(&pc, b[5].bytes.data(), sizeof(pc));
+  CHECK(pc.nHeads == nH && pc.nKvHeads == nKv && pc.headDim == hd && pc.kvDim == 32 && pc.alignedKvDim == 32 && pc.nRep == 4);
+  CHECK(pc.scale == 0.25f);
+  CHECK(a.shaderKey() != AttentionOpNode(s, q, kc32, vc32, params, nH, nKv, hd).shaderKey());
+  auto pre = s.createTensor({nH * hd}, DataType::Float32);
+  CHECK(AttentionOpNode(s, q, kc, vc, params, nH, nKv, hd, pre).output() == pre);
+  CHECK_THROWS(AttentionOpNode(s, q, kc, vc, params, nH, 3, hd), "multiple of nKvHeads");
+  CHECK_THROWS(AttentionOpNode(s, q, kc, vc32, params, nH, nKv, hd), "share a dtype");
+  CHECK(!AttentionOpNode(s, q, kc, vc, params, 18, 2, hd).shader().has_value());  // nine query heads per KV head
+
+  FusedRoPEKVWriteOpNode r(s, q, k, v, params, cosT, sinT, kc, vc, hd);
+  CHECK(r.op() == CacheWrite && r.outputShape() == (std::vector<uint32_t>{nH * hd}) && r.displayName() == "FusedRoPEKVWrite");
+  CHECK(r.dispatchSize().x == 256 && r.bindings().size() == 10);  // 128 + 2 * 32 elements -> one group
+  uint32_t rpc[5];
+  std::memcpy(rpc, r.bindings().back().bytes.data(), sizeof(rpc));
+  CHECK(rpc[0] == nH * hd && rpc[1] == nKv * hd && rpc[2] == hd && rpc[3] == hd / 2 && rpc[4] == 32);
+  auto kd = KernelDesc::decode(*r.shader());
+  CHECK(kd && kd->op == CacheWrite && kd->variant == FusedRoPEKVWriteOpNode::kVariant && kd->dtypeA == (uint32_t)DataType::Float16);
+  CHECK(r.shaderKey() != FusedRoPEKVWriteOpNode(s, q, k, v, params, cosT, sinT, kc32, vc32, hd).shaderKey());
+  CHECK_THROWS(FusedRoPEKVWriteOpNode(s, q, k, v, params, cosT, sinT, kc, vc, 6), "headDim must be even and divide");
+  CHECK_THROWS(FusedRoPEKVWriteOpNode(s, q, k, q, params, cosT, sinT, kc, vc, hd), "k and v of one length");
+  auto qr = f.rt.ops().fusedRoPEKVWrite(q, k, v, params, cosT, sinT, kc, vc, hd);
+  auto out = f.rt.ops().attention(qr, kc, vc, params, nH, nKv, hd);
+  f.rt.flush();
+  CHECK(f.raw->executed.size() == 2 && f.raw->executed[0].label == "FusedRoPEKVWrite" && f.raw->executed[1].label == "Attention");
+  CHECK(f.rt.getTensor(out).getShape() == (std::vector<uint32_t>{nH * hd}));
+}
+
 int main() {
+  RUN(attentionNodes);
   RUN(layerOperatorNodes);
   RUN(bufferGeometry);
   RUN(quantFormatDetectionAndVariants);

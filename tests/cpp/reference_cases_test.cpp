@@ -20,6 +20,10 @@ uint16_t orc_f32_to_f16_trunc(float v);
 uint16_t orc_f32_to_f16_runner(float v);
 void orc_rmsnorm(const float *x, const float *weight, float *y, size_t rows, size_t dim, size_t ldx, float eps);
 float orc_argreduce(const float *v, size_t n, int is_max);
+void orc_rope_kv_write(int kv_half, const float *q, const float *k, const float *v, uint32_t pos, const float *cos_t, const float *sin_t,
+                       void *k_cache, void *v_cache, float *q_out, size_t q_dim, size_t kv_dim, size_t head_dim, size_t ld);
+void orc_attention(int kv_half, const float *q, const void *k_cache, const void *v_cache, size_t seq_len, float *out, size_t n_heads,
+                   size_t n_kv_heads, size_t head_dim, size_t ld, float scale);
 }
 
 namespace {
@@ -436,6 +440,78 @@ void embeddingCases() {
   CHECK(bad == 0);
 }
 
+// Attention through Operations::attention: the reference's two geometries (RuntimeTests.cpp:5996-6066,
+// uniform [0.1, 10) data, its 1e-3 / 1e-2 absolute tolerances) against the CPU checker
+void attentionCases() {
+  auto run = [&](uint32_t nH, uint32_t nKv, uint32_t hd, uint32_t seq, uint32_t maxSeq, float tol) {
+    const uint32_t dim = nH * hd, kvDim = nKv * hd;
+    auto q = generateTestData(dim, 42), kData = generateTestData(maxSeq * kvDim, 100), vData = generateTestData(maxSeq * kvDim, 200);
+    auto tq = rt->createTensor({dim}, DataType::Float32, q.data());
+    auto tk = rt->createTensor({maxSeq, kvDim}, DataType::Float32, kData.data());
+    auto tv = rt->createTensor({maxSeq, kvDim}, DataType::Float32, vData.data());
+    uint32_t params[2] = {seq - 1, seq};
+    auto tp = rt->createTensor({2}, DataType::UInt32, params);
+    auto out = rt->ops().attention(tq, tk, tv, tp, nH, nKv, hd);
+    std::vector<float> got(dim), want(dim);
+    rt->copyFromTensor(out, got.data(), dim * sizeof(float));
+    orc_attention(0, q.data(), kData.data(), vData.data(), seq, want.data(), nH, nKv, hd, kvDim, 1.0f / std::sqrt((float)hd));
+    int bad = 0;
+    for (uint32_t i = 0; i < dim; ++i)
+      if (!(std::abs(got[i] - want[i]) <= tol)) ++bad;
+    CHECK(bad == 0);
+  };
+  run(1, 1, 4, 3, 8, 1e-3f);
+  run(4, 2, 8, 4, 16, 1e-2f);
+  run(32, 8, 128, 300, 512, 1e-3f);  // the decoder's geometry: the cluster kernel
+}
+
+// Per-token chain fusedRoPEKVWrite -> attention over growing positions (the sequence of
+// RuntimeTests.cpp:2231-2262, fp32 caches) against the checker's chain
+void ropeCacheAttentionChain() {
+  const uint32_t nH = 4, nKv = 2, hd = 16, maxSeq = 16, N = 6, qdim = nH * hd, kvdim = nKv * hd, half = hd / 2;
+  std::mt19937 gen(123);
+  std::uniform_real_distribution<float> dist(-1.f, 1.f);
+  std::vector<float> cosT(maxSeq * half), sinT(maxSeq * half);
+  for (uint32_t p = 0; p < maxSeq; ++p)
+    for (uint32_t i = 0; i < half; ++i) {
+      const float theta = float(p) / std::pow(10000.0f, 2.0f * i / hd);
+      cosT[p * half + i] = std::cos(theta);
+      sinT[p * half + i] = std::sin(theta);
+    }
+  auto tCos = rt->createTensor({maxSeq * half}, DataType::Float32, cosT.data());
+  auto tSin = rt->createTensor({maxSeq * half}, DataType::Float32, sinT.data());
+  std::vector<float> zeros(maxSeq * kvdim, 0.f), kRef(zeros), vRef(zeros);
+  auto tK = rt->createTensor({maxSeq, kvdim}, DataType::Float32, zeros.data());
+  auto tV = rt->createTensor({maxSeq, kvdim}, DataType::Float32, zeros.data());
+  int bad = 0;
+  for (uint32_t i = 0; i < N; ++i) {
+    std::vector<float> q(qdim), k(kvdim), v(kvdim), qr(qdim), want(qdim), got(qdim), gotQ(qdim);
+    for (auto &x : q) x = dist(gen);
+    for (auto &x : k) x = dist(gen);
+    for (auto &x : v) x = dist(gen);
+    uint32_t params[2] = {i, i + 1};
+    auto tp = rt->createTensor({2}, DataType::UInt32, params);
+    auto tq = rt->createTensor({qdim}, DataType::Float32, q.data());
+    auto tk = rt->createTensor({kvdim}, DataType::Float32, k.data());
+    auto tv = rt->createTensor({kvdim}, DataType::Float32, v.data());
+    auto roped = rt->ops().fusedRoPEKVWrite(tq, tk, tv, tp, tCos, tSin, tK, tV, hd);
+    rt->ops().barrier();
+    auto attn = rt->ops().attention(roped, tK, tV, tp, nH, nKv, hd);
+    rt->copyFromTensor(attn, got.data(), qdim * sizeof(float));
+    rt->copyFromTensor(roped, gotQ.data(), qdim * sizeof(float));
+    orc_rope_kv_write(0, q.data(), k.data(), v.data(), i, cosT.data(), sinT.data(), kRef.data(), vRef.data(), qr.data(), qdim, kvdim, hd,
+                      kvdim);
+    orc_attention(0, qr.data(), kRef.data(), vRef.data(), i + 1, want.data(), nH, nKv, hd, kvdim, 1.0f / std::sqrt((float)hd));
+    if (std::memcmp(gotQ.data(), qr.data(), qdim * sizeof(float)) != 0) ++bad;  // the rotation is bit-exact
+    for (uint32_t j = 0; j < qdim; ++j)
+      if (!(std::abs(got[j] - want[j]) <= std::abs(want[j]) * 1e-3f + 1e-4f)) ++bad;
+  }
+  CHECK(bad == 0);
+  std::vector<float> kGot(maxSeq * kvdim);
+  rt->copyFromTensor(tK, kGot.data(), kGot.size() * sizeof(float));
+  CHECK(std::memcmp(kGot.data(), kRef.data(), kGot.size() * sizeof(float)) == 0);
+}
+
 }  // namespace
 
 int main() {
@@ -458,6 +534,8 @@ int main() {
     RUN(rmsNormCases);
     RUN(argReduceCases);
     RUN(embeddingCases);
+    RUN(attentionCases);
+    RUN(ropeCacheAttentionChain);
   } catch (const std::exception &e) {
     std::printf("FAIL: unexpected exception: %s\n", e.what());
     return 2;

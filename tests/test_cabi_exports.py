@@ -40,7 +40,7 @@ def test_descriptor_layout_matches_header():
         first = names[0].split()[-1].lstrip("*")
         fields += [first] + names[1:]
     assert fields == [f[0] for f in L.QMatmulDesc._fields_]
-    assert C.sizeof(L.QMatmulDesc) == 152
+    assert C.sizeof(L.QMatmulDesc) == 168
     assert C.sizeof(L.PeerScatter) == 16 + 2 * 8 * L.MAX_PEERS
 
 

@@ -66,6 +66,55 @@ def test_fp32_activations_staged_at_16_bits(fmt, M, K, N):
 
 
 @pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("dtype,flags", [(np.float32, 0), (np.float32, L.FLAG_ACT_16BIT), (np.float16, 0)])
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 1024), (3, 1024, 264), (1, 14336, 96), (8, 512, 40)])
+def test_fused_rmsnorm_of_the_activations(fmt, dtype, flags, M, K, N):
+    """CUTB_FLAG_A_RMSNORM: C = (RMSNorm(A) * weight) . dequant(W)^T in one launch, against the checker's
+    RMSNorm followed by its matmul (split-K shapes included: every CTA reduces the whole row)."""
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev, rel_l2
+
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M * 7 + K + fmt)
+    A = (A.astype(np.float32) * 3.0 + 0.5).astype(dtype)
+    nw = np.random.default_rng(K).normal(1.0, 0.2, K).astype(np.float32)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    d, C_out, keep = ops.make_desc(dev(A), dev(W), fmt, N, status=status, flags=flags | L.FLAG_A_RMSNORM)
+    nwd = dev(nw)
+    d.a_norm_weight, d.a_norm_eps = nwd.data_ptr(), 1e-5
+    assert ops.select_variant(d) == L.VARIANT_GEMV_MMA
+    need = ops.workspace_bytes(d)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+    d.workspace, d.workspace_bytes = ws.data_ptr(), need
+    ops.launch(d)
+    torch.cuda.synchronize()
+    normed = O.rmsnorm(A.astype(np.float32), nw, 1e-5)
+    assert int(status.item()) == 0
+    assert rel_l2(C_out.cpu().numpy(), _ref(fmt, normed, W, M, K, N)) <= TOL
+
+
+def test_fused_rmsnorm_needs_the_decode_kernel_and_a_weight():
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev
+
+    A, W = _inputs(synth.Q8_0, 64, 512, 128, np.float16, seed=1)  # 64 rows: the prefill GEMM would be chosen
+    d, _, keep = ops.make_desc(dev(A), dev(W), synth.Q8_0, 128, flags=L.FLAG_A_RMSNORM)
+    nw = torch.ones(512, device="cuda")
+    d.a_norm_weight, d.a_norm_eps = nw.data_ptr(), 1e-5
+    with pytest.raises(L.CutbError) as e:
+        ops.launch(d)
+    assert e.value.status == 2
+    A1, _ = _inputs(synth.Q8_0, 1, 512, 128, np.float16, seed=1)
+    d, _, keep = ops.make_desc(dev(A1), dev(W), synth.Q8_0, 128, flags=L.FLAG_A_RMSNORM)
+    with pytest.raises(L.CutbError) as e:
+        ops.launch(d)
+    assert e.value.status == 1
+
+
+@pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("dtype,M", [(np.float16, 9), (np.float16, 16), (np.float32, 5), (np.float32, 8)])
 def test_gemv_mma_wide_batches(fmt, dtype, M):
     from gpu_util import rel_l2, run_blocks
