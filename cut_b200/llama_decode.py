@@ -128,7 +128,7 @@ class LlamaDecoder:
     def _matvec(self, A, W, N, out, fusion_type=L.FUSION_NONE, fusion_op=0, D=None, after_matvec=False, norm=None):
         d, _, keep = ops.make_desc(A, W, self.cfg.fmt, N, C_out=out.view(1, -1), D=D.view(1, -1) if D is not None else None,
                                    fusion_type=fusion_type, fusion_op=fusion_op, status=self.status,
-                                   flags=self.act_flags | (0 if (after_matvec and self.overlap) else L.FLAG_NO_OVERLAP))
+                                   flags=self.act_flags | (0 if (after_matvec and self._overlaps(after_matvec)) else L.FLAG_NO_OVERLAP))
         if norm is not None:  # the RMSNorm in front of this projection, applied while the mat-vec stages its activations
             d.flags |= L.FLAG_A_RMSNORM
             d.a_norm_weight, d.a_norm_eps = norm.data_ptr(), self.cfg.eps
@@ -141,6 +141,9 @@ class LlamaDecoder:
         self._keep.append(keep)
         self._descs.append(d)
         return lambda d=d: L.check(L.lib().cutb_qmatmul(C.byref(d), ops._stream_ptr()))
+
+    def _overlaps(self, name) -> bool:
+        return bool(self.overlap) if isinstance(self.overlap, bool) else name in self.overlap
 
     def _plan(self):
         cfg, lib = self.cfg, L.lib()
@@ -177,9 +180,9 @@ class LlamaDecoder:
             if not fuse:
                 seq.append(rms(self.x[1], lw["ffn_norm"], self.h))
             seq.append(self._matvec(ffn_in, lw["wgate"], cfg.ffn, self.gate, L.FUSION_UNARY, UNARY_SILU, norm=ffn_norm))
-            seq.append(self._matvec(ffn_in, lw["wup"], cfg.ffn, self.act, L.FUSION_BINARY, BINARY_MUL, self.gate, after_matvec=True,
+            seq.append(self._matvec(ffn_in, lw["wup"], cfg.ffn, self.act, L.FUSION_BINARY, BINARY_MUL, self.gate, after_matvec="up",
                                     norm=ffn_norm))
-            seq.append(self._matvec(self.act, lw["wdown"], cfg.hidden, self.x[0], L.FUSION_BINARY, BINARY_ADD, self.x[1], after_matvec=True))
+            seq.append(self._matvec(self.act, lw["wdown"], cfg.hidden, self.x[0], L.FUSION_BINARY, BINARY_ADD, self.x[1], after_matvec="down"))
         if fuse:
             seq.append(self._matvec(self.x[0], self.lm_head, cfg.vocab, self.logits, norm=self.final_norm))
         else:
