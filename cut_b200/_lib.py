@@ -19,6 +19,7 @@ VARIANT_AUTO, VARIANT_GENERIC, VARIANT_GEMV_MMA, VARIANT_GEMM_TC = -1, 0, 1, 2
 FLAG_NO_OVERLAP = 1
 FLAG_ACT_16BIT = 2
 FLAG_A_RMSNORM = 4
+FLAG_GLU_PAIRS = 8
 
 # every symbol include/cutb.h declares
 EXPORTS = [

@@ -33,7 +33,12 @@ int validate(const cutb_qmatmul_desc *d) {
     set_last_error("qmatmul: null A, W or C");
     return CUTB_ERR_INVALID;
   }
-  if (d->lda < d->K || d->ldc < d->N) {
+  const bool glu = (d->flags & CUTB_FLAG_GLU_PAIRS) != 0;
+  if (glu && (d->N % 2 != 0 || d->fusion_type != CUTB_FUSION_UNARY)) {
+    set_last_error("qmatmul: CUTB_FLAG_GLU_PAIRS needs an even N and a unary fusion (the gate's activation)");
+    return CUTB_ERR_INVALID;
+  }
+  if (d->lda < d->K || d->ldc < (glu ? d->N / 2 : d->N)) {
     set_last_error("qmatmul: lda (%u) < K (%u) or ldc (%u) < N (%u)", d->lda, d->K, d->ldc, d->N);
     return CUTB_ERR_INVALID;
   }
@@ -164,6 +169,10 @@ int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
   if (int rc = validate(desc)) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int v = select(*desc);
+  if ((desc->flags & CUTB_FLAG_GLU_PAIRS) && (v != CUTB_VARIANT_GEMV_MMA || qgemv_blocks_workspace(*desc) != 0)) {
+    set_last_error("qmatmul: paired gate/up rows exist in the decode mat-vec only, for shapes that do not split K");
+    return CUTB_ERR_UNSUPPORTED;
+  }
   if (desc->flags & CUTB_FLAG_A_RMSNORM) {
     if (!desc->a_norm_weight) {
       set_last_error("qmatmul: CUTB_FLAG_A_RMSNORM without a_norm_weight");

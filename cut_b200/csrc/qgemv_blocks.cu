@@ -91,6 +91,7 @@ struct GvParams {
   uint32_t stages;
   int fusion_type, fusion_op;
   int a_f32;
+  int glu;              // rows in (gate, up) pairs: C[m, i] = unary(acc[2i]) * acc[2i + 1]
   const float *norm_w;  // fused RMSNorm of the activation rows (nullptr: none)
   float norm_eps;
   int *status;
@@ -621,8 +622,9 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
 
   // rows of this CTA and granules (256 weights) of this K split; a stage holds
   // 16 rows x up to GV_KC granules, one granule per consumer warp
-  const uint32_t r0 = (uint32_t)((uint64_t)blockIdx.x * p.N / gridDim.x);
-  const uint32_t r1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * p.N / gridDim.x);
+  const uint32_t unit = p.glu ? 2u : 1u;  // paired rows stay in one CTA (and, ranges being even, in one tile)
+  const uint32_t r0 = (uint32_t)((uint64_t)blockIdx.x * (p.N / unit) / gridDim.x) * unit;
+  const uint32_t r1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * (p.N / unit) / gridDim.x) * unit;
   const uint32_t G = p.K >> 8;
   const uint32_t gs0 = blockIdx.y * p.gran_per_split;
   const uint32_t gs1 = min(G, gs0 + p.gran_per_split);
@@ -815,20 +817,32 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
     }
     asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
     const uint32_t row_base = r0 + tile * GV_ROWS;
+    auto row_sum = [&](uint32_t row, uint32_t m) -> float {
+      float sum = 0.f;
+      if constexpr (TWO) {
+#pragma unroll
+        for (int w = 0; w < GV_WARPS; ++w) {
+          const float2 hl = *reinterpret_cast<const float2 *>(rbuf + ((size_t)w * GV_ROWS + row) * NV + 2 * m);
+          sum += hl.x + hl.y;
+        }
+      } else {
+#pragma unroll
+        for (int w = 0; w < GV_WARPS; ++w) sum += rbuf[((size_t)w * GV_ROWS + row) * NV + m];
+      }
+      return sum;
+    };
+    if (p.glu) {  // (gate, up) row pairs: one output per pair
+      for (uint32_t o = tid; o < (GV_ROWS / 2) * p.M; o += GV_WARPS * 32) {
+        const uint32_t pr = o % (GV_ROWS / 2), m = o / (GV_ROWS / 2), n = row_base + 2 * pr;
+        if (n < r1)
+          p.C[(size_t)m * p.ldc + (n >> 1)] = apply_epilogue(row_sum(2 * pr, m), CUTB_FUSION_UNARY, p.fusion_op, 0.f) * row_sum(2 * pr + 1, m);
+      }
+      continue;
+    }
     for (uint32_t o = tid; o < GV_ROWS * p.M; o += GV_WARPS * 32) {
       const uint32_t row = o % GV_ROWS, m = o / GV_ROWS, n = row_base + row;
       if (n < r1) {
-        float sum = 0.f;
-        if constexpr (TWO) {
-#pragma unroll
-          for (int w = 0; w < GV_WARPS; ++w) {
-            const float2 hl = *reinterpret_cast<const float2 *>(rbuf + ((size_t)w * GV_ROWS + row) * NV + 2 * m);
-            sum += hl.x + hl.y;
-          }
-        } else {
-#pragma unroll
-          for (int w = 0; w < GV_WARPS; ++w) sum += rbuf[((size_t)w * GV_ROWS + row) * NV + m];
-        }
+        const float sum = row_sum(row, m);
         if (p.ksplit > 1) {
           p.partial[((size_t)blockIdx.y * p.M + m) * p.N + n] = sum;
         } else {
@@ -1070,6 +1084,7 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
   p.a_f32 = amode != GV_A_HALF;
   p.norm_w = (d.flags & CUTB_FLAG_A_RMSNORM) ? d.a_norm_weight : nullptr;
   p.norm_eps = d.a_norm_eps;
+  p.glu = (d.flags & CUTB_FLAG_GLU_PAIRS) ? 1 : 0;
   p.status = d.status;
   p.world = 0;
   p.n_off = p.ldc_total = 0;

@@ -95,8 +95,14 @@ enum {
  *     A'[m, k] = A[m, k] * rsqrt(mean_k(A[m, k]^2) + a_norm_eps) * a_norm_weight[k], i.e. the
  *     RMSNorm that precedes every projection of a decoder layer (RMSNormOpNode,
  *     operators/impl/rmsnorm/RMSNormOp.cpp:7-76) without its own launch and round trip.  Only the
- *     CUTB_VARIANT_GEMV_MMA kernel implements it; other shapes return CUTB_ERR_UNSUPPORTED. */
-enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2, CUTB_FLAG_A_RMSNORM = 4 };
+ *     CUTB_VARIANT_GEMV_MMA kernel implements it; other shapes return CUTB_ERR_UNSUPPORTED.
+ *   CUTB_FLAG_GLU_PAIRS: gated projection in one launch.  W holds N rows in pairs -- row 2i of the
+ *     gate matrix, row 2i + 1 of the up matrix -- and the output has N / 2 columns:
+ *     C[m, i] = unary(fusion_op)(acc[m, 2i]) * acc[m, 2i + 1] (fusion_type CUTB_FUSION_UNARY; with
+ *     SiLU this is the SwiGLU feed-forward the runner builds from matmulUnary + a multiply,
+ *     interface/runner/llama/llama.cpp:2455-2470).  ldc >= N / 2.  Decode mat-vec only, shapes that
+ *     do not split K; anything else returns CUTB_ERR_UNSUPPORTED. */
+enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2, CUTB_FLAG_A_RMSNORM = 4, CUTB_FLAG_GLU_PAIRS = 8 };
 
 /*
  * C[M, N] = epilogue(A[M, K] * dequant(W)), fp32 accumulate, fp32 output.

@@ -94,6 +94,55 @@ def test_fused_rmsnorm_of_the_activations(fmt, dtype, flags, M, K, N):
     assert rel_l2(C_out.cpu().numpy(), _ref(fmt, normed, W, M, K, N)) <= TOL
 
 
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("M,K,N2", [(1, 4096, 2048), (1, 512, 1200), (3, 1024, 1189), (1, 256, 14336)])
+def test_paired_gate_up_rows(fmt, M, K, N2):
+    """CUTB_FLAG_GLU_PAIRS: rows (2i, 2i + 1) = (gate_i, up_i), C[m, i] = silu(gate . a) * (up . a), against the
+    checker's two matmuls and its SiLU."""
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev, rel_l2
+
+    A, Wg = _inputs(fmt, M, K, N2, np.float32, seed=K + N2 + fmt)
+    Wu = synth.make_weights(fmt, N2, K, seed=K + N2 + fmt + 77)
+    rb = synth.row_bytes(fmt, K)
+    W = np.stack([Wg.reshape(N2, rb), Wu.reshape(N2, rb)], axis=1).reshape(-1)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    C_out = torch.zeros((M, N2), dtype=torch.float32, device="cuda")
+    d, _, keep = ops.make_desc(dev(A), dev(W), fmt, 2 * N2, C_out=C_out, fusion_type=1, fusion_op=133, status=status,
+                               flags=L.FLAG_GLU_PAIRS)
+    assert ops.workspace_bytes(d) == 0
+    ops.launch(d)
+    torch.cuda.synchronize()
+    g = _ref(fmt, A, Wg, M, K, N2, fusion_type=1, fusion_op=133).astype(np.float64)
+    u = _ref(fmt, A, Wu, M, K, N2).astype(np.float64)
+    assert int(status.item()) == 0
+    assert rel_l2(C_out.cpu().numpy(), (g * u).astype(np.float32)) <= TOL
+
+
+def test_paired_rows_are_refused_where_no_kernel_has_them():
+    from cut_b200 import ops
+    from gpu_util import dev
+
+    A, W = _inputs(synth.Q8_0, 64, 512, 128, np.float16, seed=1)  # prefill shape
+    d, _, keep = ops.make_desc(dev(A), dev(W), synth.Q8_0, 128, fusion_type=1, fusion_op=133, flags=L.FLAG_GLU_PAIRS)
+    with pytest.raises(L.CutbError) as e:
+        ops.launch(d)
+    assert e.value.status == 2
+    A1, W1 = _inputs(synth.Q8_0, 1, 512, 128, np.float16, seed=1)
+    d, _, keep = ops.make_desc(dev(A1), dev(W1), synth.Q8_0, 128, flags=L.FLAG_GLU_PAIRS)  # no unary fusion
+    with pytest.raises(L.CutbError) as e:
+        ops.launch(d)
+    assert e.value.status == 1
+    A2, W2 = _inputs(synth.Q8_0, 1, 4096, 128, np.float16, seed=2)  # few rows, long K: the plan splits K
+    d, _, keep = ops.make_desc(dev(A2), dev(W2), synth.Q8_0, 128, fusion_type=1, fusion_op=133, flags=L.FLAG_GLU_PAIRS)
+    assert ops.workspace_bytes(d) > 0
+    with pytest.raises(L.CutbError) as e:
+        ops.launch(d)
+    assert e.value.status == 2
+
+
 def test_fused_rmsnorm_needs_the_decode_kernel_and_a_weight():
     import torch
 
