@@ -123,7 +123,9 @@ class LlamaDecoder:
         # fp32 activations staged at one 16-bit level per 32-k block: fp16-grade error, fp32 range
         self.act_flags = L.FLAG_ACT_16BIT if act_16bit else 0
         # overlap: which mat-vecs that directly follow a mat-vec may prefetch under their predecessor's tail (True: all).
-        # Measured on the 32-layer step: qkv (after down), gate and up each gain, together +3.6 %; down loses 9 %.
+        # Measured on the 32-layer step: qkv (after down), gate and up each gain, together +3.6 %; down loses 9 %, and the
+        # output projection started under the attention kernel (which holds 64 SMs) loses 15 %: its 148 persistent
+        # CTAs double up on the free SMs.
         self.overlap = overlap
         # fuse_norm: the RMSNorms run inside the projections that consume them (no launch, no round trip of h)
         self.fuse_norm = fuse_norm
