@@ -114,6 +114,8 @@ struct AttnParams {
   int *status;
   uint32_t nHeads, nKvHeads, headDim, ld, nRep, max_seq, splits;
   uint32_t chunk_cap;  // cluster path: rows a block's shared-memory tiles hold
+  // fused RoPE + cache write (cluster path; k_new == nullptr: plain attention): q is the unrotated query
+  const float *k_new, *v_new, *cosT, *sinT;
   float scale;
 };
 
@@ -387,6 +389,18 @@ __global__ void __launch_bounds__(CL_THREADS) attention_decode_cluster_kernel(co
   const uint32_t chunk = (seqLen + S - 1) / S;  // <= chunk_cap
   const uint32_t t0 = min(split * chunk, seqLen), t1 = min(t0 + chunk, seqLen), cnt = t1 - t0;
   const uint32_t row_bytes = HD * (uint32_t)sizeof(KV), RS = row_bytes + 16;  // padded: rows start on different banks
+  // fused mode: this token's K / V row is rotated here, put into the slice that owns its position and
+  // written to the cache by the first slice; the copies below never touch that row
+  const bool fused = p.k_new != nullptr;
+  uint32_t pos = 0xFFFFFFFFu;
+  if (fused) {
+    pos = __ldg(p.params);
+    if (pos >= p.max_seq) {  // never write outside the cache: record it, rotate nothing
+      if (p.status && tid == 0 && kvH == 0 && split == 0) atomicExch(p.status, (int)CUTB_ERR_INVALID);
+      pos = 0xFFFFFFFFu;
+    }
+  }
+  const bool own = pos >= t0 && pos < t1;
   uint8_t *ktile = tiles, *vtile = tiles + (size_t)p.chunk_cap * RS;
   float *red = reinterpret_cast<float *>(tiles + (size_t)2 * p.chunk_cap * RS);  // [G][NREP][HD]
   {
@@ -396,6 +410,7 @@ __global__ void __launch_bounds__(CL_THREADS) attention_decode_cluster_kernel(co
     const uint64_t gstride = (uint64_t)p.ld * sizeof(KV);
     for (uint32_t id = tid; id < total; id += CL_THREADS) {
       const uint32_t r = id / ppr, c = id % ppr;
+      if (own && r == pos - t0) continue;
       const uint32_t kd = (uint32_t)__cvta_generic_to_shared(ktile + (size_t)r * RS + c * 16);
       const uint32_t vd = (uint32_t)__cvta_generic_to_shared(vtile + (size_t)r * RS + c * 16);
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kd), "l"(kg + r * gstride + c * 16) : "memory");
@@ -403,7 +418,33 @@ __global__ void __launch_bounds__(CL_THREADS) attention_decode_cluster_kernel(co
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
-  for (uint32_t i = tid; i < nRep * HD; i += CL_THREADS) qs[i] = __ldg(p.q + (uint64_t)kvH * nRep * HD + i);
+  if (pos != 0xFFFFFFFFu) {
+    const uint32_t half = HD / 2;
+    const float *cs = p.cosT + (uint64_t)pos * half, *sn = p.sinT + (uint64_t)pos * half;
+    // half-split rotation with separately rounded products, as the stand-alone kernel computes it
+    auto rotate = [&](const float *x, uint32_t i) -> float {
+      const uint32_t in_head = i % HD;
+      if (in_head < half) return __fsub_rn(__fmul_rn(__ldg(x + i), __ldg(cs + in_head)), __fmul_rn(__ldg(x + i + half), __ldg(sn + in_head)));
+      return __fadd_rn(__fmul_rn(__ldg(x + i - half), __ldg(sn + in_head - half)), __fmul_rn(__ldg(x + i), __ldg(cs + in_head - half)));
+    };
+    for (uint32_t i = tid; i < nRep * HD; i += CL_THREADS) qs[i] = rotate(p.q + (uint64_t)kvH * nRep * HD, i);
+    if (own || split == 0) {
+      for (uint32_t e = tid; e < HD; e += CL_THREADS) {
+        const float kr = rotate(p.k_new + (uint64_t)kvH * HD, e), vv = __ldg(p.v_new + (uint64_t)kvH * HD + e);
+        if (own) {
+          kv_store(reinterpret_cast<KV *>(ktile + (size_t)(pos - t0) * RS) + e, kr);
+          kv_store(reinterpret_cast<KV *>(vtile + (size_t)(pos - t0) * RS) + e, vv);
+        }
+        if (split == 0) {
+          const uint64_t at = (uint64_t)pos * p.ld + (uint64_t)kvH * HD + e;
+          kv_store(reinterpret_cast<KV *>(const_cast<void *>(p.kC)) + at, kr);
+          kv_store(reinterpret_cast<KV *>(const_cast<void *>(p.vC)) + at, vv);
+        }
+      }
+    }
+  } else {
+    for (uint32_t i = tid; i < nRep * HD; i += CL_THREADS) qs[i] = __ldg(p.q + (uint64_t)kvH * nRep * HD + i);
+  }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 
@@ -576,17 +617,23 @@ int rope_kv_write_launch(int kv_dtype, const float *q, const float *k, const flo
 }
 
 // Workspace: 256 bytes of arrival counters (zero before the first launch; every launch leaves
-// them zero), then the slices' partial sums, maxima and exp-sums.
+// them zero), then the slices' partial sums, maxima and exp-sums, then one rotated query (used
+// when a fused request runs as two launches).
 uint64_t attention_workspace_bytes(uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint32_t max_seq) {
   if (nKvHeads == 0 || max_seq == 0) return 0;
   const uint64_t S = attn_splits(nKvHeads, max_seq);
-  return 256 + (uint64_t)nHeads * S * (headDim + 2) * sizeof(float);
+  return 256 + (uint64_t)nHeads * S * (headDim + 2) * sizeof(float) + (uint64_t)nHeads * headDim * sizeof(float);
 }
 
-int attention_decode_launch(int kv_dtype, const float *q, const void *kC, const void *vC, const uint32_t *params, float *out,
-                            uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale,
-                            void *workspace, int *status, cudaStream_t stream) {
+namespace {
+// Plain attention (k_new == nullptr) or RoPE + cache write + attention in one launch where the cluster kernel applies;
+// elsewhere the fused request runs as the stand-alone rotation kernel followed by the general attention kernel.
+int attention_launch_any(int kv_dtype, const float *q, const float *k_new, const float *v_new, const float *cosT, const float *sinT,
+                         void *kC, void *vC, const uint32_t *params, float *out, uint32_t nHeads, uint32_t nKvHeads,
+                         uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale, void *workspace, int *status,
+                         cudaStream_t stream) {
   AttnParams p{};
+  p.k_new = k_new, p.v_new = v_new, p.cosT = cosT, p.sinT = sinT;
   p.q = q, p.kC = kC, p.vC = vC, p.params = params, p.out = out, p.status = status;
   p.nHeads = nHeads, p.nKvHeads = nKvHeads, p.headDim = headDim, p.ld = (uint32_t)ld, p.nRep = nHeads / nKvHeads;
   p.max_seq = max_seq, p.scale = scale;
@@ -621,6 +668,14 @@ int attention_decode_launch(int kv_dtype, const float *q, const void *kC, const 
       }
     }
   }
+  if (k_new) {  // not fusable here: rotate into the scratch behind the partial sums, then attend
+    float *q_roped = p.part_l + (uint64_t)nHeads * p.splits;
+    if (int rc = rope_kv_write_launch(kv_dtype, q, k_new, v_new, params, cosT, sinT, kC, vC, q_roped, nHeads * headDim,
+                                      nKvHeads * headDim, headDim, ld, max_seq, status, stream))
+      return rc;
+    p.q = q_roped;
+    p.k_new = p.v_new = p.cosT = p.sinT = nullptr;
+  }
   const dim3 grid(nKvHeads, p.splits);
   if (kv_dtype == CUTB_F16) {
     if (vec) CUTB_CUDA_TRY(launch_pdl(attention_decode_kernel<__half, true>, grid, dim3(AT_THREADS), 0, stream, p));
@@ -630,6 +685,22 @@ int attention_decode_launch(int kv_dtype, const float *q, const void *kC, const 
     else CUTB_CUDA_TRY(launch_pdl(attention_decode_kernel<float, false>, grid, dim3(AT_THREADS), 0, stream, p));
   }
   return CUTB_OK;
+}
+}  // namespace
+
+int attention_decode_launch(int kv_dtype, const float *q, const void *kC, const void *vC, const uint32_t *params, float *out,
+                            uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale,
+                            void *workspace, int *status, cudaStream_t stream) {
+  return attention_launch_any(kv_dtype, q, nullptr, nullptr, nullptr, nullptr, const_cast<void *>(kC), const_cast<void *>(vC), params,
+                              out, nHeads, nKvHeads, headDim, ld, max_seq, scale, workspace, status, stream);
+}
+
+int rope_attention_decode_launch(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params,
+                                 const float *cosT, const float *sinT, void *kC, void *vC, float *out, uint32_t nHeads,
+                                 uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale, void *workspace,
+                                 int *status, cudaStream_t stream) {
+  return attention_launch_any(kv_dtype, q, k, v, cosT, sinT, kC, vC, params, out, nHeads, nKvHeads, headDim, ld, max_seq, scale,
+                              workspace, status, stream);
 }
 
 }  // namespace cutb

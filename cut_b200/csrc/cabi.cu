@@ -382,6 +382,32 @@ int cutb_attention_decode(int kv_dtype, const float *q, const void *k_cache, con
                                  workspace, status, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cutb_rope_attention_decode(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params,
+                               const float *cos_table, const float *sin_table, void *k_cache, void *v_cache, float *out,
+                               uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint64_t ld, uint32_t max_seq, float scale,
+                               void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+  if (kv_dtype != CUTB_F32 && kv_dtype != CUTB_F16) {
+    set_last_error("rope_attention: cache dtype must be fp32 or fp16");
+    return CUTB_ERR_INVALID;
+  }
+  if (!q || !k || !v || !params || !cos_table || !sin_table || !k_cache || !v_cache || !out || !workspace) {
+    set_last_error("rope_attention: null pointer");
+    return CUTB_ERR_INVALID;
+  }
+  if (n_heads == 0 || n_kv_heads == 0 || n_heads % n_kv_heads || n_heads / n_kv_heads > 8 || head_dim == 0 || head_dim > 128 ||
+      head_dim % 2 || ld < (uint64_t)n_kv_heads * head_dim || max_seq == 0) {
+    set_last_error("rope_attention: need n_heads = n_kv_heads * (1..8), even head_dim <= 128, ld >= n_kv_heads * head_dim, max_seq > 0");
+    return CUTB_ERR_INVALID;
+  }
+  if (reinterpret_cast<uintptr_t>(workspace) % 16 || workspace_bytes < attention_workspace_bytes(n_heads, n_kv_heads, head_dim, max_seq)) {
+    set_last_error("rope_attention: workspace must be 16-byte aligned and hold %llu bytes",
+                   (unsigned long long)attention_workspace_bytes(n_heads, n_kv_heads, head_dim, max_seq));
+    return CUTB_ERR_INVALID;
+  }
+  return rope_attention_decode_launch(kv_dtype, q, k, v, params, cos_table, sin_table, k_cache, v_cache, out, n_heads, n_kv_heads,
+                                      head_dim, ld, max_seq, scale, workspace, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                  void *stream) {
   if (format < CUTB_Q8_0 || format > CUTB_BF16) {

@@ -38,6 +38,10 @@ int argreduce_launch(int is_max, const float *v, float *out, uint32_t n, cudaStr
 int rope_kv_write_launch(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params, const float *cosT,
                          const float *sinT, void *kC, void *vC, float *qOut, uint32_t qDim, uint32_t kvDim, uint32_t headDim,
                          uint64_t ld, uint32_t max_seq, int *status, cudaStream_t stream);
+int rope_attention_decode_launch(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params,
+                                 const float *cosT, const float *sinT, void *kC, void *vC, float *out, uint32_t nHeads,
+                                 uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale, void *workspace,
+                                 int *status, cudaStream_t stream);
 uint64_t attention_workspace_bytes(uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint32_t max_seq);
 int attention_decode_launch(int kv_dtype, const float *q, const void *kC, const void *vC, const uint32_t *params, float *out,
                             uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale,

@@ -91,7 +91,8 @@ class LlamaDecoder:
     runs n further tokens from the device-resident {token, pos}, greedy (arg-max feeds back)."""
 
     def __init__(self, cfg: LlamaConfig, weights: dict, device: torch.device | str = "cuda", act_16bit: bool = True,
-                 overlap=("qkv", "gate", "up"), fuse_norm: bool = True, glu_pairs: bool = True):
+                 overlap=("qkv", "gate", "up"), fuse_norm: bool = True, glu_pairs: bool = True,
+                 fuse_rope: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("LlamaDecoder needs a CUDA device: there is no CPU path")
         if cfg.hidden % 4 or cfg.n_heads % cfg.n_kv_heads:
@@ -129,6 +130,8 @@ class LlamaDecoder:
         self.overlap = overlap
         # fuse_norm: the RMSNorms run inside the projections that consume them (no launch, no round trip of h)
         self.fuse_norm = fuse_norm
+        # fuse_rope: RoPE + KV-cache write inside the attention launch
+        self.fuse_rope = fuse_rope
         self._keep, self._descs, self.launches_per_step = [], [], 0
         self._plan()
         self.graph = None
@@ -180,14 +183,20 @@ class LlamaDecoder:
             else:
                 seq.append(rms(self.x[0], lw["attn_norm"], self.h))
                 seq.append(self._matvec(self.h, lw["wqkv"], cfg.q_dim + 2 * cfg.kv_dim, self.qkv))
-            seq.append(lambda kc=kc, vc=vc: L.check(lib.cutb_rope_kv_write(
-                kvd, q.data_ptr(), k.data_ptr(), v.data_ptr(), self.params.data_ptr(), self.cos_t.data_ptr(), self.sin_t.data_ptr(),
-                kc.data_ptr(), vc.data_ptr(), self.q_roped.data_ptr(), cfg.q_dim, cfg.kv_dim, cfg.head_dim, kc.stride(0), cfg.max_seq, st,
-                ops._stream_ptr())))
-            seq.append(lambda kc=kc, vc=vc: L.check(lib.cutb_attention_decode(
-                kvd, self.q_roped.data_ptr(), kc.data_ptr(), vc.data_ptr(), self.params.data_ptr(), self.attn.data_ptr(), cfg.n_heads,
-                cfg.n_kv_heads, cfg.head_dim, kc.stride(0), cfg.max_seq, scale, self.attn_ws.data_ptr(), self.attn_ws.numel(), st,
-                ops._stream_ptr())))
+            if self.fuse_rope:
+                seq.append(lambda kc=kc, vc=vc: L.check(lib.cutb_rope_attention_decode(
+                    kvd, q.data_ptr(), k.data_ptr(), v.data_ptr(), self.params.data_ptr(), self.cos_t.data_ptr(), self.sin_t.data_ptr(),
+                    kc.data_ptr(), vc.data_ptr(), self.attn.data_ptr(), cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, kc.stride(0),
+                    cfg.max_seq, scale, self.attn_ws.data_ptr(), self.attn_ws.numel(), st, ops._stream_ptr())))
+            else:
+                seq.append(lambda kc=kc, vc=vc: L.check(lib.cutb_rope_kv_write(
+                    kvd, q.data_ptr(), k.data_ptr(), v.data_ptr(), self.params.data_ptr(), self.cos_t.data_ptr(), self.sin_t.data_ptr(),
+                    kc.data_ptr(), vc.data_ptr(), self.q_roped.data_ptr(), cfg.q_dim, cfg.kv_dim, cfg.head_dim, kc.stride(0), cfg.max_seq, st,
+                    ops._stream_ptr())))
+                seq.append(lambda kc=kc, vc=vc: L.check(lib.cutb_attention_decode(
+                    kvd, self.q_roped.data_ptr(), kc.data_ptr(), vc.data_ptr(), self.params.data_ptr(), self.attn.data_ptr(), cfg.n_heads,
+                    cfg.n_kv_heads, cfg.head_dim, kc.stride(0), cfg.max_seq, scale, self.attn_ws.data_ptr(), self.attn_ws.numel(), st,
+                    ops._stream_ptr())))
             seq.append(self._matvec(self.attn, lw["wo"], cfg.hidden, self.x[1], L.FUSION_BINARY, BINARY_ADD, self.x[0]))
             ffn_in, ffn_norm = (self.x[1], lw["ffn_norm"]) if fuse else (self.h, None)
             if not fuse:

@@ -213,3 +213,20 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                                           status.data_ptr() if status is not None else None, _stream_ptr()))
     return out
 
+
+def rope_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, params: torch.Tensor, cos_t: torch.Tensor,
+                          sin_t: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, n_heads: int, n_kv_heads: int,
+                          head_dim: int, workspace: torch.Tensor, out: torch.Tensor | None = None, scale: float | None = None,
+                          status: torch.Tensor | None = None) -> torch.Tensor:
+    """rope_kv_write + attention_decode in one call (one launch where the cluster kernel applies)."""
+    if out is None:
+        out = torch.empty(n_heads * head_dim, dtype=torch.float32, device=q.device)
+    if scale is None:
+        scale = 1.0 / float(head_dim) ** 0.5
+    L.check(L.lib().cutb_rope_attention_decode(_kv_dtype(k_cache), q.data_ptr(), k.data_ptr(), v.data_ptr(), params.data_ptr(),
+                                               cos_t.data_ptr(), sin_t.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                               out.data_ptr(), n_heads, n_kv_heads, head_dim, k_cache.stride(0), k_cache.shape[0],
+                                               scale, workspace.data_ptr(), workspace.numel(),
+                                               status.data_ptr() if status is not None else None, _stream_ptr()))
+    return out
+

@@ -291,12 +291,22 @@ CUTB_API int cutb_argreduce(int is_max, const float *values, float *out, uint32_
  *   seqLen > max_seq is clamped and reported through *status.  `workspace` holds
  *   cutb_attention_workspace_bytes() bytes; its first 256 bytes must be zero before the first
  *   call and are left zero by every call (launches sharing a workspace must not overlap).
+ * cutb_rope_attention_decode: cutb_rope_kv_write followed by cutb_attention_decode as ONE launch
+ *   where the cluster kernel applies (head_dim % 32 == 0, 1 / 2 / 4 / 8 query heads per KV head,
+ *   slices that fit in shared memory): every slice rotates its own copy of q, the slice that owns
+ *   row pos takes the rotated k and v straight into its tile and the first slice stores them to
+ *   the caches.  Other shapes run the two kernels back to back.  Same results as the two calls
+ *   (cache rows bit-exact); the rotated q is not returned.  q, k, v must not alias the caches.
  */
 CUTB_API int cutb_rope_kv_write(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params,
                                 const float *cos_table, const float *sin_table, void *k_cache, void *v_cache, float *q_out,
                                 uint32_t q_dim, uint32_t kv_dim, uint32_t head_dim, uint64_t ld, uint32_t max_seq, int *status,
                                 void *stream);
 CUTB_API uint64_t cutb_attention_workspace_bytes(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_seq);
+CUTB_API int cutb_rope_attention_decode(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params,
+                                        const float *cos_table, const float *sin_table, void *k_cache, void *v_cache, float *out,
+                                        uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint64_t ld, uint32_t max_seq,
+                                        float scale, void *workspace, uint64_t workspace_bytes, int *status, void *stream);
 CUTB_API int cutb_attention_decode(int kv_dtype, const float *q, const void *k_cache, const void *v_cache, const uint32_t *params,
                                    float *out, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint64_t ld,
                                    uint32_t max_seq, float scale, void *workspace, uint64_t workspace_bytes, int *status,

@@ -122,6 +122,45 @@ def test_attention_decode_matches_checker(gpu, kv, n_heads, n_kv, hd, max_seq, s
     assert not ws[:256].cpu().numpy().any()
 
 
+@pytest.mark.parametrize("kv", [np.float32, np.float16])
+@pytest.mark.parametrize("n_heads,n_kv,hd,max_seq,positions", [
+    (32, 8, 128, 2048, [0, 1, 255, 256, 511, 2047]),  # cluster kernel; rows at slice boundaries (fp32 caches: two launches)
+    (8, 8, 64, 64, [0, 7, 8, 63]),                     # cluster kernel, one query head per KV head
+    (6, 2, 64, 100, [0, 50, 99]),                      # three heads per KV head: rotation kernel + general attention
+    (4, 2, 8, 16, [0, 3, 15]),                         # tiny head_dim: scalar general kernel
+])
+def test_rope_attention_decode_equals_the_two_calls(gpu, kv, n_heads, n_kv, hd, max_seq, positions):
+    import torch
+
+    rng = np.random.default_rng(hd + max_seq)
+    ld = (n_kv * hd + 3) // 4 * 4
+    cos_t, sin_t = rope_tables(max_seq, hd)
+    kc = rng.normal(0, 1, (max_seq, ld)).astype(kv)
+    vc = rng.normal(0, 1, (max_seq, ld)).astype(kv)
+    dkc, dvc = _dev(kc), _dev(vc)
+    kc_ref, vc_ref = kc.copy(), vc.copy()
+    ws = gpu.attention_workspace(n_heads, n_kv, hd, max_seq, "cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bits = np.uint16 if kv == np.float16 else np.uint32
+    for pos in positions:
+        q = rng.normal(0, 1, n_heads * hd).astype(np.float32)
+        k = rng.normal(0, 1, n_kv * hd).astype(np.float32)
+        v = rng.normal(0, 1, n_kv * hd).astype(np.float32)
+        q_ref = O.rope_kv_write(q, k, v, pos, cos_t, sin_t, kc_ref, vc_ref, hd)
+        want = O.attention(q_ref, kc_ref, vc_ref, pos + 1, n_heads, n_kv, hd)
+        got = gpu.rope_attention_decode(_dev(q), _dev(k), _dev(v), _dev(np.array([pos, pos + 1], np.int32)), _dev(cos_t), _dev(sin_t),
+                                        dkc, dvc, n_heads, n_kv, hd, ws, status=status).cpu().numpy()
+        assert np.all(np.abs(got - want) <= 1e-5 + 1e-4 * np.abs(want)), (pos, float(np.max(np.abs(got - want))))
+        assert np.array_equal(dkc.cpu().numpy().view(bits), kc_ref.view(bits))  # row pos written bit-exactly, nothing else touched
+        assert np.array_equal(dvc.cpu().numpy().view(bits), vc_ref.view(bits))
+    assert int(status.item()) == 0
+    # a position past the cache: reported, nothing written
+    before = dkc.clone()
+    gpu.rope_attention_decode(_dev(q), _dev(k), _dev(v), _dev(np.array([max_seq, max_seq], np.int32)), _dev(cos_t), _dev(sin_t), dkc, dvc,
+                              n_heads, n_kv, hd, ws, status=status)
+    assert int(status.item()) == 1 and torch.equal(before, dkc)
+
+
 def test_attention_empty_cache_and_clamped_length(gpu):
     import torch
 

@@ -62,9 +62,9 @@ class Reference:
         return self.lm @ norm(x, self.final_norm)
 
 
-@pytest.mark.parametrize("fuse_norm,glu", [(True, True), (True, False), (False, False), (False, True)])
+@pytest.mark.parametrize("fuse_norm,glu,fuse_rope", [(True, True, True), (True, False, True), (False, False, False), (False, True, False)])
 @pytest.mark.parametrize("fmt", [2, 0, 1])
-def test_decode_steps_match_composed_checker(fmt, fuse_norm, glu):
+def test_decode_steps_match_composed_checker(fmt, fuse_norm, glu, fuse_rope):
     import torch
 
     from cut_b200.llama_decode import LlamaConfig, LlamaDecoder, synthetic_weights
@@ -76,7 +76,7 @@ def test_decode_steps_match_composed_checker(fmt, fuse_norm, glu):
             lw[k] = _soften(lw[k], fmt)
     w["lm_head"] = _soften(w["lm_head"], fmt)
     w["embedding"] = (w["embedding"] * 50).astype(np.float32)
-    dec, ref = LlamaDecoder(cfg, w, fuse_norm=fuse_norm, glu_pairs=glu), Reference(cfg, w)
+    dec, ref = LlamaDecoder(cfg, w, fuse_norm=fuse_norm, glu_pairs=glu, fuse_rope=fuse_rope), Reference(cfg, w)
     tokens = [3, 500, 17, 17, 0, 301, 42]
     for pos, tok in enumerate(tokens):
         got = dec.step(tok, pos).cpu().numpy().astype(np.float64)
@@ -106,7 +106,7 @@ def test_decode_steps_match_composed_checker(fmt, fuse_norm, glu):
     assert got == eager
     assert int(dec.params[0].item()) == pos0 + 6
     dec.check_status()
-    assert dec.launches_per_step >= 3 + (0 if fuse_norm else 1) + ((7 if fuse_norm else 9) - (1 if glu else 0)) * cfg.n_layers
+    assert dec.launches_per_step >= 3 + (0 if fuse_norm else 1) + ((7 if fuse_norm else 9) - (1 if glu else 0) - (1 if fuse_rope else 0)) * cfg.n_layers
 
 
 def test_position_past_the_cache_is_reported():
