@@ -195,36 +195,47 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
-def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = True) -> dict:
+def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = True, synthetic_cache: bool = False) -> dict:
     """configs[3]: Llama-style decoder (hidden 4096, 32 query / 8 KV heads of 128, FFN 14336, vocab 32000, Q4_K
-    projections, fp16 KV cache of 2048 rows), batch-1 greedy decode of `steps` tokens from position 512.  The
-    prompt phase is not run (no batched prefill attention yet): cache rows 0..511 hold synthetic fp16 values
-    ~N(0, 1), so every decode step attends over the 512 + t rows the configuration prescribes.  Layer 0's
-    weights are generated, the other layers are row rotations of them at their own addresses (4 GB in all)."""
+    projections, fp16 KV cache of 2048 rows): a prompt of 512 random token ids, then batch-1 greedy decode of
+    `steps` tokens.  The prompt is fed through the decode step token by token (there is no batched prefill
+    attention yet; its time is reported separately and is not part of tok/s), so every decode step attends over
+    the 512 + t rows the model itself wrote.  Layer 0's weights are generated, the other layers are row
+    rotations of them at their own addresses (4 GB in all)."""
     import torch
 
     from cut_b200.llama_decode import LlamaConfig, LlamaDecoder, synthetic_weights
 
     cfg = LlamaConfig(n_layers=n_layers)
     dec = LlamaDecoder(cfg, synthetic_weights(cfg, seed=41, distinct_layers=False), dev)
-    gen = torch.Generator(device=dev).manual_seed(42)
-    for l in range(cfg.n_layers):
-        dec.k_cache[l][:512].copy_(torch.randn((512, cfg.kv_dim), generator=gen, device=dev))
-        dec.v_cache[l][:512].copy_(torch.randn((512, cfg.kv_dim), generator=gen, device=dev))
-    logits = dec.step(5, 512)
+    prompt = np.random.default_rng(42).integers(0, cfg.vocab, 512)
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    if synthetic_cache:  # profiling aid: no prompt run, cache rows 0..511 ~N(0, 1), one step at position 512
+        gen = torch.Generator(device=dev).manual_seed(42)
+        for l in range(cfg.n_layers):
+            dec.k_cache[l][:512].copy_(torch.randn((512, cfg.kv_dim), generator=gen, device=dev))
+            dec.v_cache[l][:512].copy_(torch.randn((512, cfg.kv_dim), generator=gen, device=dev))
+        logits = dec.step(int(prompt[-1]), 512)
+    else:
+        logits = dec.prompt(prompt)
+    p1.record()
+    torch.cuda.synchronize()
+    prompt_ms = p0.elapsed_time(p1)
     finite = bool(torch.isfinite(logits).all())
+    first = int(torch.argmax(logits).item())
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if graph:
-        dec.set_position(5, 512)
+        dec.set_position(first, 512)
         dec.capture()
         dec.replay(3)
-        dec.set_position(5, 512)
+        dec.set_position(first, 512)
         torch.cuda.synchronize()
         a.record()
         dec.replay(steps)
         b.record()
     else:  # eager: one launch per call, for a profiler's launch list
-        tok = 5
+        tok = first
         torch.cuda.synchronize()
         a.record()
         for t in range(steps):
@@ -236,7 +247,9 @@ def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = 
     wb = dec.weight_bytes_per_token()
     return {"tok/s": steps * 1e3 / ms, "ms_per_token": ms / steps, "tokens": steps, "layers": cfg.n_layers,
             "weight_bytes_per_token": wb, "weight_GB/s": wb * steps / ms / 1e6, "kernel_launches_per_token": dec.launches_per_step,
-            "logits_finite": finite, "graph": graph, "kv_cache": "fp16, rows 0..511 synthetic, decode at 512..",
+            "logits_finite": finite, "graph": graph,
+            "kv_cache": "fp16; rows 0..511 synthetic" if synthetic_cache else
+            "fp16; rows 0..511 written by the 512-token prompt run through the decode step", "prompt_ms_eager": prompt_ms,
             "activations": "fp32, staged at 16 bits per 32-k block"}
 
 
@@ -644,6 +657,8 @@ def main() -> None:
     ap.add_argument("--decode-layers", type=int, default=32)
     ap.add_argument("--decode-steps", type=int, default=256)
     ap.add_argument("--decode-eager", action="store_true", help="with --decode-only: no CUDA graph (one launch per kernel)")
+    ap.add_argument("--decode-synthetic-cache", action="store_true",
+                    help="with --decode-only: skip the prompt, fill cache rows 0..511 with synthetic values (profiling aid)")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
                     help="N > 1: slices meet through the mat-vec's own peer-store epilogue, or through an NCCL all-gather")
     args = ap.parse_args()
@@ -654,7 +669,8 @@ def main() -> None:
             raise SystemExit("bench: --decode-only needs a CUDA device (there is no CPU path)")
         torch.cuda.set_device(0)
         print(json.dumps({"configs[3]_llama_q4_k_decode_batch1": decode_measurement(
-            torch.device("cuda:0"), args.decode_layers, args.decode_steps, graph=not args.decode_eager)}), flush=True)
+            torch.device("cuda:0"), args.decode_layers, args.decode_steps, graph=not args.decode_eager,
+            synthetic_cache=args.decode_synthetic_cache)}), flush=True)
         return
     if args.impl == "reference":
         if args.steps == 2000:

@@ -243,6 +243,15 @@ class LlamaDecoder:
         self._run()
         return self.logits
 
+    def prompt(self, tokens, start: int = 0) -> torch.Tensor:
+        """Feeds a prompt through the decode step, one token per step (positions start, start + 1, ...), so the
+        KV cache holds what the model computes for it; returns the last step's logits.  (There is no batched
+        prefill attention yet: this is the sequential way to the same cache contents.)"""
+        logits = self.logits
+        for i, t in enumerate(tokens):
+            logits = self.step(int(t), start + i)
+        return logits
+
     def capture(self) -> None:
         """Records step + advance into one CUDA graph (call after at least one eager step)."""
         torch.cuda.synchronize(self.dev)
