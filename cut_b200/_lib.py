@@ -27,6 +27,7 @@ EXPORTS = [
     "cutb_qmatmul_scatter", "cutb_peer_exchange",
     "cutb_rmsnorm", "cutb_embedding", "cutb_argreduce",
     "cutb_rope_kv_write", "cutb_attention_workspace_bytes", "cutb_attention_decode", "cutb_rope_attention_decode",
+    "cutb_batched_kv_write", "cutb_batched_attention", "cutb_glu_pairs",
     "cutb_dequant", "cutb_separate_blocks", "cutb_transpose_2d", "cutb_requant_q4k_affine", "cutb_quantize_rows_q8_0",
     "cutb_transpose_q4", "cutb_version", "cutb_status_string", "cutb_last_error", "cutb_device_sm_count",
     "cutb_variant_name",
@@ -108,6 +109,14 @@ def lib() -> C.CDLL:
         l.cutb_rope_attention_decode.restype = C.c_int
         l.cutb_rope_attention_decode.argtypes = [C.c_int] + [C.c_void_p] * 9 + [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint32,
                                                                                 C.c_float, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p]
+        l.cutb_batched_kv_write.restype = C.c_int
+        l.cutb_batched_kv_write.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32] + [C.c_void_p] * 5 + [
+            C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint32, C.c_void_p, C.c_void_p]
+        l.cutb_batched_attention.restype = C.c_int
+        l.cutb_batched_attention.argtypes = [C.c_int, C.c_void_p, C.c_uint32] + [C.c_void_p] * 6 + [
+            C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint32, C.c_float, C.c_void_p, C.c_void_p]
+        l.cutb_glu_pairs.restype = C.c_int
+        l.cutb_glu_pairs.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, C.c_int, C.c_void_p]
         l.cutb_separate_blocks.restype = C.c_int
         l.cutb_separate_blocks.argtypes = [C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p]
         l.cutb_transpose_2d.restype = C.c_int

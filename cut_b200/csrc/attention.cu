@@ -102,6 +102,32 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(const float *__restr
   }
 }
 
+// Prefill: roped k and v of a batch of tokens into their cache rows (BatchedKVCacheWrite.cu:33-62).
+// One block per token; k_in / v_in rows may be columns of a wider matrix (row strides in elements).
+template <typename KV>
+__global__ void __launch_bounds__(256) batched_kv_write_kernel(const float *__restrict__ kIn, const float *__restrict__ vIn,
+                                                               uint32_t kStride, uint32_t vStride, const uint32_t *__restrict__ positions,
+                                                               const float *__restrict__ cosT, const float *__restrict__ sinT,
+                                                               KV *__restrict__ kC, KV *__restrict__ vC, uint32_t kvDim, uint32_t headDim,
+                                                               uint32_t ld, uint32_t max_seq, int *status) {
+  pdl_enter();
+  const uint32_t token = blockIdx.x, pos = __ldg(positions + token);
+  if (pos >= max_seq) {
+    if (status && threadIdx.x == 0) atomicExch(status, (int)CUTB_ERR_INVALID);
+    return;
+  }
+  const uint32_t half = headDim / 2;
+  const float *k = kIn + (uint64_t)token * kStride, *v = vIn + (uint64_t)token * vStride;
+  const float *cs = cosT + (uint64_t)pos * half, *sn = sinT + (uint64_t)pos * half;
+  for (uint32_t i = threadIdx.x; i < kvDim; i += blockDim.x) {
+    const uint32_t in_head = i % headDim;
+    const float kr = in_head < half ? __fsub_rn(__fmul_rn(__ldg(k + i), __ldg(cs + in_head)), __fmul_rn(__ldg(k + i + half), __ldg(sn + in_head)))
+                                    : __fadd_rn(__fmul_rn(__ldg(k + i - half), __ldg(sn + in_head - half)), __fmul_rn(__ldg(k + i), __ldg(cs + in_head - half)));
+    kv_store(kC + (uint64_t)pos * ld + i, kr);
+    kv_store(vC + (uint64_t)pos * ld + i, __ldg(v + i));
+  }
+}
+
 struct AttnParams {
   const float *q;
   const void *kC, *vC;
@@ -116,6 +142,10 @@ struct AttnParams {
   uint32_t chunk_cap;  // cluster path: rows a block's shared-memory tiles hold
   // fused RoPE + cache write (cluster path; k_new == nullptr: plain attention): q is the unrotated query
   const float *k_new, *v_new, *cosT, *sinT;
+  // batched (prefill) mode of the general kernel: one block per (KV head, token); token i attends rows [0, positions[i]]
+  // with its query rotated here; q and out advance by their strides per token
+  const uint32_t *positions;
+  uint32_t q_stride, out_stride;
   float scale;
 };
 
@@ -133,18 +163,32 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t kvH = blockIdx.x, split = blockIdx.y, S = p.splits;
   const uint32_t nRep = p.nRep, HD = p.headDim;
+  const bool batched = p.positions != nullptr;
+  const uint32_t token = batched ? blockIdx.z : 0u;
   pdl_enter();
-  uint32_t seqLen = __ldg(p.params + 1);
-  if (seqLen > p.max_seq) {  // never read outside the cache
+  uint32_t seqLen = batched ? __ldg(p.positions + token) + 1u : __ldg(p.params + 1);
+  const uint32_t seq_cap = batched ? min(p.max_seq, (uint32_t)AT_MAX_CHUNK) : p.max_seq;  // a batched block owns its whole range
+  if (seqLen > seq_cap) {  // never read outside the cache (or past what one block holds)
     if (p.status && tid == 0 && kvH == 0 && split == 0) atomicExch(p.status, (int)CUTB_ERR_INVALID);
-    seqLen = p.max_seq;
+    seqLen = seq_cap;
   }
   const uint32_t chunk = (seqLen + S - 1) / S;  // <= AT_MAX_CHUNK by the launcher's choice of S
   const uint32_t t0 = min(split * chunk, seqLen), t1 = min(t0 + chunk, seqLen), cnt = t1 - t0;
   const KV *kC = reinterpret_cast<const KV *>(p.kC) + (uint64_t)kvH * HD;
   const KV *vC = reinterpret_cast<const KV *>(p.vC) + (uint64_t)kvH * HD;
 
-  for (uint32_t i = tid; i < nRep * HD; i += AT_THREADS) qs[i] = __ldg(p.q + (uint64_t)kvH * nRep * HD + i);
+  if (batched) {  // rotate this token's query heads at its own position (half-split, separately rounded products)
+    const uint32_t half = HD / 2, pos = seqLen - 1;
+    const float *x = p.q + (uint64_t)token * p.q_stride + (uint64_t)kvH * nRep * HD;
+    const float *cs = p.cosT + (uint64_t)pos * half, *sn = p.sinT + (uint64_t)pos * half;
+    for (uint32_t i = tid; i < nRep * HD; i += AT_THREADS) {
+      const uint32_t in_head = i % HD;
+      qs[i] = in_head < half ? __fsub_rn(__fmul_rn(__ldg(x + i), __ldg(cs + in_head)), __fmul_rn(__ldg(x + i + half), __ldg(sn + in_head)))
+                             : __fadd_rn(__fmul_rn(__ldg(x + i - half), __ldg(sn + in_head - half)), __fmul_rn(__ldg(x + i), __ldg(cs + in_head - half)));
+    }
+  } else {
+    for (uint32_t i = tid; i < nRep * HD; i += AT_THREADS) qs[i] = __ldg(p.q + (uint64_t)kvH * nRep * HD + i);
+  }
   __syncthreads();
 
   // scores: eight lanes per position, four positions per warp and pass; the loads of up to four
@@ -293,6 +337,15 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
         }
     }
     __syncthreads();
+    if (S == 1) {  // one slice: it is the result (an empty range gives zeros, as the reference's sum does)
+      for (uint32_t idx = tid; idx < nRep * HD; idx += AT_THREADS) {
+        const uint32_t r = idx / HD, d = idx % HD;
+        float s = 0.f;
+        for (uint32_t g = 0; g < G; ++g) s += red[(g * nRep + r) * HD + d];
+        p.out[(uint64_t)token * p.out_stride + (uint64_t)(kvH * nRep + r) * HD + d] = head_l[r] > 0.f ? s / head_l[r] : 0.f;
+      }
+      return;
+    }
     for (uint32_t idx = tid; idx < nRep * HD; idx += AT_THREADS) {
       const uint32_t r = idx / HD, d = idx % HD;
       float s = 0.f;
@@ -701,6 +754,43 @@ int rope_attention_decode_launch(int kv_dtype, const float *q, const float *k, c
                                  int *status, cudaStream_t stream) {
   return attention_launch_any(kv_dtype, q, k, v, cosT, sinT, kC, vC, params, out, nHeads, nKvHeads, headDim, ld, max_seq, scale,
                               workspace, status, stream);
+}
+
+int batched_kv_write_launch(int kv_dtype, const float *k_in, const float *v_in, uint32_t k_stride, uint32_t v_stride,
+                            const uint32_t *positions, const float *cosT, const float *sinT, void *kC, void *vC, uint32_t n_tokens,
+                            uint32_t kvDim, uint32_t headDim, uint64_t ld, uint32_t max_seq, int *status, cudaStream_t stream) {
+  if (n_tokens == 0) return CUTB_OK;
+  if (kv_dtype == CUTB_F16)
+    CUTB_CUDA_TRY(launch_pdl(batched_kv_write_kernel<__half>, dim3(n_tokens), dim3(256), 0, stream, k_in, v_in, k_stride, v_stride, positions,
+                             cosT, sinT, (__half *)kC, (__half *)vC, kvDim, headDim, (uint32_t)ld, max_seq, status));
+  else
+    CUTB_CUDA_TRY(launch_pdl(batched_kv_write_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, k_in, v_in, k_stride, v_stride, positions,
+                             cosT, sinT, (float *)kC, (float *)vC, kvDim, headDim, (uint32_t)ld, max_seq, status));
+  return CUTB_OK;
+}
+
+int batched_attention_launch(int kv_dtype, const float *q_in, uint32_t q_stride, const void *kC, const void *vC,
+                             const uint32_t *positions, const float *cosT, const float *sinT, float *out, uint32_t out_stride,
+                             uint32_t n_tokens, uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq,
+                             float scale, int *status, cudaStream_t stream) {
+  if (n_tokens == 0) return CUTB_OK;
+  AttnParams p{};
+  p.q = q_in, p.kC = kC, p.vC = vC, p.out = out, p.status = status, p.positions = positions, p.cosT = cosT, p.sinT = sinT;
+  p.q_stride = q_stride, p.out_stride = out_stride;
+  p.nHeads = nHeads, p.nKvHeads = nKvHeads, p.headDim = headDim, p.ld = (uint32_t)ld, p.nRep = nHeads / nKvHeads;
+  p.max_seq = max_seq, p.scale = scale, p.splits = 1;
+  const uint32_t esz = kv_dtype == CUTB_F16 ? 2 : 4;
+  const bool vec = headDim % 32 == 0 && (ld * esz) % 16 == 0 && reinterpret_cast<uintptr_t>(kC) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(vC) % 16 == 0;
+  const dim3 grid(nKvHeads, 1, n_tokens);
+  if (kv_dtype == CUTB_F16) {
+    if (vec) CUTB_CUDA_TRY(launch_pdl(attention_decode_kernel<__half, true>, grid, dim3(AT_THREADS), 0, stream, p));
+    else CUTB_CUDA_TRY(launch_pdl(attention_decode_kernel<__half, false>, grid, dim3(AT_THREADS), 0, stream, p));
+  } else {
+    if (vec) CUTB_CUDA_TRY(launch_pdl(attention_decode_kernel<float, true>, grid, dim3(AT_THREADS), 0, stream, p));
+    else CUTB_CUDA_TRY(launch_pdl(attention_decode_kernel<float, false>, grid, dim3(AT_THREADS), 0, stream, p));
+  }
+  return CUTB_OK;
 }
 
 }  // namespace cutb

@@ -458,4 +458,46 @@ int cutb_transpose_q4(const void *in, void *out, uint32_t N, uint32_t K, uint32_
   return transpose_q4_launch(in, out, N, K, stride_in, stride_out, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cutb_batched_kv_write(int kv_dtype, const float *k_in, const float *v_in, uint32_t k_stride, uint32_t v_stride,
+                          const uint32_t *positions, const float *cos_table, const float *sin_table, void *k_cache, void *v_cache,
+                          uint32_t n_tokens, uint32_t kv_dim, uint32_t head_dim, uint64_t ld, uint32_t max_seq, int *status, void *stream) {
+  if ((kv_dtype != CUTB_F32 && kv_dtype != CUTB_F16) || !k_in || !v_in || !positions || !cos_table || !sin_table || !k_cache || !v_cache) {
+    set_last_error("batched_kv_write: null pointer or cache dtype not fp32 / fp16");
+    return CUTB_ERR_INVALID;
+  }
+  if (head_dim == 0 || head_dim % 2 || kv_dim % head_dim || ld < kv_dim || k_stride < kv_dim || v_stride < kv_dim || max_seq == 0) {
+    set_last_error("batched_kv_write: head_dim must be even and divide kv_dim; ld, k_stride, v_stride >= kv_dim; max_seq > 0");
+    return CUTB_ERR_INVALID;
+  }
+  return batched_kv_write_launch(kv_dtype, k_in, v_in, k_stride, v_stride, positions, cos_table, sin_table, k_cache, v_cache, n_tokens,
+                                 kv_dim, head_dim, ld, max_seq, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_batched_attention(int kv_dtype, const float *q_in, uint32_t q_stride, const void *k_cache, const void *v_cache,
+                           const uint32_t *positions, const float *cos_table, const float *sin_table, float *out, uint32_t out_stride,
+                           uint32_t n_tokens, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint64_t ld, uint32_t max_seq,
+                           float scale, int *status, void *stream) {
+  if ((kv_dtype != CUTB_F32 && kv_dtype != CUTB_F16) || !q_in || !k_cache || !v_cache || !positions || !cos_table || !sin_table || !out) {
+    set_last_error("batched_attention: null pointer or cache dtype not fp32 / fp16");
+    return CUTB_ERR_INVALID;
+  }
+  if (n_heads == 0 || n_kv_heads == 0 || n_heads % n_kv_heads || n_heads / n_kv_heads > 8 || head_dim == 0 || head_dim > 128 ||
+      head_dim % 2 || ld < (uint64_t)n_kv_heads * head_dim || q_stride < n_heads * head_dim || out_stride < n_heads * head_dim ||
+      max_seq == 0) {
+    set_last_error("batched_attention: need n_heads = n_kv_heads * (1..8), even head_dim <= 128, strides >= n_heads * head_dim");
+    return CUTB_ERR_INVALID;
+  }
+  return batched_attention_launch(kv_dtype, q_in, q_stride, k_cache, v_cache, positions, cos_table, sin_table, out, out_stride, n_tokens,
+                                  n_heads, n_kv_heads, head_dim, ld, max_seq, scale, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_glu_pairs(const float *in, float *out, uint32_t rows, uint32_t cols_out, uint64_t ldi, uint64_t ldo, int unary_op, void *stream) {
+  if (rows == 0 || cols_out == 0) return CUTB_OK;
+  if (!in || !out || ldi % 2 || ldi < 2ull * cols_out || ldo < cols_out || reinterpret_cast<uintptr_t>(in) % 8) {
+    set_last_error("glu_pairs: null pointer, odd or short ldi, short ldo, or input not 8-byte aligned");
+    return CUTB_ERR_INVALID;
+  }
+  return glu_pairs_launch(in, out, rows, cols_out, ldi, ldo, unary_op, reinterpret_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

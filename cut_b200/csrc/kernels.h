@@ -42,6 +42,15 @@ int rope_attention_decode_launch(int kv_dtype, const float *q, const float *k, c
                                  const float *cosT, const float *sinT, void *kC, void *vC, float *out, uint32_t nHeads,
                                  uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale, void *workspace,
                                  int *status, cudaStream_t stream);
+int batched_kv_write_launch(int kv_dtype, const float *k_in, const float *v_in, uint32_t k_stride, uint32_t v_stride,
+                            const uint32_t *positions, const float *cosT, const float *sinT, void *kC, void *vC, uint32_t n_tokens,
+                            uint32_t kvDim, uint32_t headDim, uint64_t ld, uint32_t max_seq, int *status, cudaStream_t stream);
+int batched_attention_launch(int kv_dtype, const float *q_in, uint32_t q_stride, const void *kC, const void *vC,
+                             const uint32_t *positions, const float *cosT, const float *sinT, float *out, uint32_t out_stride,
+                             uint32_t n_tokens, uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq,
+                             float scale, int *status, cudaStream_t stream);
+int glu_pairs_launch(const float *in, float *out, uint32_t rows, uint32_t cols_out, uint64_t ldi, uint64_t ldo, int unary_op,
+                     cudaStream_t stream);
 uint64_t attention_workspace_bytes(uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint32_t max_seq);
 int attention_decode_launch(int kv_dtype, const float *q, const void *kC, const void *vC, const uint32_t *params, float *out,
                             uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale,

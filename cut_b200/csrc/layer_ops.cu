@@ -158,7 +158,31 @@ __global__ void __launch_bounds__(1024) argreduce_kernel(const float *__restrict
   }
 }
 
+// out[r, i] = unary(in[r, 2i]) * in[r, 2i + 1]: the gated feed-forward's activation over a prefill GEMM whose
+// weight rows are stored in (gate, up) pairs (the decode mat-vec does this in its epilogue).
+__global__ void __launch_bounds__(256) glu_pairs_kernel(const float2 *__restrict__ in, float *__restrict__ out, uint32_t rows,
+                                                        uint32_t cols_out, uint64_t ldi2, uint64_t ldo, int op) {
+  pdl_enter();
+  const uint64_t total = (uint64_t)rows * cols_out;
+  for (uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; g < total; g += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t r = g / cols_out, c = g % cols_out;
+    const float2 gu = __ldg(in + r * ldi2 + c);
+    out[r * ldo + c] = apply_epilogue(gu.x, CUTB_FUSION_UNARY, op, 0.f) * gu.y;
+  }
+}
+
 }  // namespace
+
+int glu_pairs_launch(const float *in, float *out, uint32_t rows, uint32_t cols_out, uint64_t ldi, uint64_t ldo, int unary_op,
+                     cudaStream_t stream) {
+  const uint64_t total = (uint64_t)rows * cols_out;
+  if (total == 0) return CUTB_OK;
+  uint64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  CUTB_CUDA_TRY(launch_pdl(glu_pairs_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, reinterpret_cast<const float2 *>(in), out, rows,
+                           cols_out, ldi / 2, ldo, unary_op));
+  return CUTB_OK;
+}
 
 int rmsnorm_launch(int dtype, const void *x, const void *weight, void *y, uint32_t rows, uint32_t dim, uint64_t ldx, float eps,
                    cudaStream_t stream) {

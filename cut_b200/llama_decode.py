@@ -59,7 +59,23 @@ def rope_tables(cfg: LlamaConfig):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
-def synthetic_weights(cfg: LlamaConfig, seed: int = 0, distinct_layers: bool = True) -> dict:
+def soften_scales(raw: np.ndarray, fmt: int, shift: int = 4) -> np.ndarray:
+    """Divides the fp16 super-block scales (d, dmin) of Q4_K blocks by 2^shift (exponent arithmetic on normal halves; smaller
+    ones become zero).  The benchmark's Q4_K distribution gives weights of magnitude ~2, hence activations far beyond what
+    a trained model produces (and beyond fp16, which the prefill GEMM rounds its activations to); the 32-weight formats'
+    distributions are small already and are returned unchanged."""
+    if fmt != L.Q4_K or shift == 0:
+        return raw
+    blocks = raw.reshape(-1, 144).copy()
+    for off in (0, 2):
+        h = blocks[:, off:off + 2].copy().view(np.uint16).reshape(-1)
+        e = (h >> 10) & 0x1F
+        h = np.where(e > shift, h - (shift << 10), 0).astype(np.uint16)
+        blocks[:, off:off + 2] = h.view(np.uint8).reshape(-1, 2)
+    return blocks.reshape(-1)
+
+
+def synthetic_weights(cfg: LlamaConfig, seed: int = 0, distinct_layers: bool = True, scale_shift: int = 0) -> dict:
     """Random-init weights as host arrays: block tensors from the synthetic generators of the
     benchmark configurations, norms near 1, an fp32 embedding table ~N(0, 0.02).  With
     distinct_layers False, layer 0 is generated and the others are row rotations of it (different
@@ -70,7 +86,8 @@ def synthetic_weights(cfg: LlamaConfig, seed: int = 0, distinct_layers: bool = T
     layers = []
     for l in range(cfg.n_layers):
         if l == 0 or distinct_layers:
-            lw = {k: synth.make_weights(cfg.fmt, n, kk, seed=seed * 1000 + l * 10 + i) for i, (k, (n, kk)) in enumerate(shapes.items())}
+            lw = {k: soften_scales(synth.make_weights(cfg.fmt, n, kk, seed=seed * 1000 + l * 10 + i), cfg.fmt, scale_shift)
+                  for i, (k, (n, kk)) in enumerate(shapes.items())}
         else:
             lw = {}
             for k, (n, kk) in shapes.items():
@@ -80,7 +97,7 @@ def synthetic_weights(cfg: LlamaConfig, seed: int = 0, distinct_layers: bool = T
         lw["ffn_norm"] = (1.0 + 0.1 * rng.standard_normal(cfg.hidden)).astype(np.float32)
         layers.append(lw)
     return {"layers": layers, "final_norm": (1.0 + 0.1 * rng.standard_normal(cfg.hidden)).astype(np.float32),
-            "lm_head": synth.make_weights(cfg.fmt, cfg.vocab, cfg.hidden, seed=seed * 1000 + 999),
+            "lm_head": soften_scales(synth.make_weights(cfg.fmt, cfg.vocab, cfg.hidden, seed=seed * 1000 + 999), cfg.fmt, scale_shift),
             "embedding": (0.02 * rng.standard_normal((cfg.vocab, cfg.hidden))).astype(np.float32)}
 
 
@@ -251,6 +268,43 @@ class LlamaDecoder:
         for i, t in enumerate(tokens):
             logits = self.step(int(t), start + i)
         return logits
+
+    def prefill(self, tokens, start: int = 0) -> torch.Tensor:
+        """The prompt as one batch (interface/runner/llama/llama.cpp prefillBatched): every projection is one matmul over
+        all T tokens (the tensor-core GEMM from 17 tokens up), K / V rows go to the cache through the batched RoPE
+        write and every token attends over the rows up to its own.  start + T <= 512 (one attention block holds a
+        token's whole range).  Leaves the cache as T decode steps would (up to rounding) and returns the last
+        token's logits; the greedy pick is in next_tok."""
+        cfg, dev = self.cfg, self.dev
+        T = len(tokens)
+        if T == 0 or start + T > min(cfg.max_seq, 512):
+            raise ValueError("prefill: 1 .. 512 - start tokens per call")
+        tok = torch.as_tensor(np.asarray(tokens, dtype=np.int32)).to(dev)
+        pos = torch.arange(start, start + T, dtype=torch.int32, device=dev)
+        q_dim, kv_dim = cfg.q_dim, cfg.kv_dim
+        mm = lambda A, W, N, **kw: ops.qmatmul(A, W, cfg.fmt, N, status=self.status, flags=self.act_flags | L.FLAG_NO_OVERLAP, **kw)
+        x = ops.embedding(tok, self.table, status=self.status)
+        for l, lw in enumerate(self.layers):
+            h = ops.rmsnorm(x, lw["attn_norm"], cfg.eps)
+            qkv = mm(h, lw["wqkv"], q_dim + 2 * kv_dim)
+            ops.batched_kv_write(qkv[:, q_dim: q_dim + kv_dim], qkv[:, q_dim + kv_dim:], pos, self.cos_t, self.sin_t, self.k_cache[l],
+                                 self.v_cache[l], cfg.head_dim, status=self.status)
+            att = ops.batched_attention(qkv[:, :q_dim], self.k_cache[l], self.v_cache[l], pos, self.cos_t, self.sin_t, cfg.n_heads,
+                                        cfg.n_kv_heads, cfg.head_dim, status=self.status)
+            x = mm(att, lw["wo"], cfg.hidden, D=x, fusion_type=L.FUSION_BINARY, fusion_op=BINARY_ADD)
+            h = ops.rmsnorm(x, lw["ffn_norm"], cfg.eps)
+            if self.glu:
+                act = ops.glu_pairs(mm(h, lw["wgu"], 2 * cfg.ffn), UNARY_SILU)
+            else:
+                gate = mm(h, lw["wgate"], cfg.ffn, fusion_type=L.FUSION_UNARY, fusion_op=UNARY_SILU)
+                act = mm(h, lw["wup"], cfg.ffn, D=gate, fusion_type=L.FUSION_BINARY, fusion_op=BINARY_MUL)
+            x = mm(act, lw["wdown"], cfg.hidden, D=x, fusion_type=L.FUSION_BINARY, fusion_op=BINARY_ADD)
+        self.x[0].copy_(x[T - 1])
+        for f in self._seq[-2 if self.fuse_norm else -3:]:  # final norm, LM head, arg-max of the decode step
+            f()
+        self.token.copy_(self.next_tok.to(torch.int32))  # decoding continues at position start + T with the greedy pick
+        self.params.copy_(torch.tensor([start + T, start + T + 1], dtype=torch.int32))
+        return self.logits
 
     def capture(self) -> None:
         """Records step + advance into one CUDA graph (call after at least one eager step)."""

@@ -230,3 +230,38 @@ def rope_attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, par
                                                status.data_ptr() if status is not None else None, _stream_ptr()))
     return out
 
+
+# ---- prefill (a batch of prompt tokens) ----
+def batched_kv_write(k_in: torch.Tensor, v_in: torch.Tensor, positions: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor,
+                     k_cache: torch.Tensor, v_cache: torch.Tensor, head_dim: int, status: torch.Tensor | None = None) -> None:
+    """k_cache[positions[i]] = RoPE(k_in[i]), v_cache[positions[i]] = v_in[i]; k_in / v_in are [T, kv_dim] views (any row stride)."""
+    L.check(L.lib().cutb_batched_kv_write(_kv_dtype(k_cache), k_in.data_ptr(), v_in.data_ptr(), k_in.stride(0), v_in.stride(0),
+                                          positions.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), k_cache.data_ptr(),
+                                          v_cache.data_ptr(), k_in.shape[0], k_in.shape[1], head_dim, k_cache.stride(0),
+                                          k_cache.shape[0], status.data_ptr() if status is not None else None, _stream_ptr()))
+
+
+def batched_attention(q_in: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor, cos_t: torch.Tensor,
+                      sin_t: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, out: torch.Tensor | None = None,
+                      scale: float | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+    """out[i] = attention of RoPE(q_in[i]) over cache rows [0, positions[i]]; q_in is a [T, n_heads * head_dim] view."""
+    T = q_in.shape[0]
+    if out is None:
+        out = torch.empty((T, n_heads * head_dim), dtype=torch.float32, device=q_in.device)
+    if scale is None:
+        scale = 1.0 / float(head_dim) ** 0.5
+    L.check(L.lib().cutb_batched_attention(_kv_dtype(k_cache), q_in.data_ptr(), q_in.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+                                           positions.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), out.data_ptr(), out.stride(0), T,
+                                           n_heads, n_kv_heads, head_dim, k_cache.stride(0), k_cache.shape[0], scale,
+                                           status.data_ptr() if status is not None else None, _stream_ptr()))
+    return out
+
+
+def glu_pairs(x: torch.Tensor, unary_op: int = 133, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r, i] = unary(x[r, 2i]) * x[r, 2i + 1] (SiLU by default)."""
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty((rows, cols // 2), dtype=torch.float32, device=x.device)
+    L.check(L.lib().cutb_glu_pairs(x.data_ptr(), out.data_ptr(), rows, cols // 2, x.stride(0), out.stride(0), unary_op, _stream_ptr()))
+    return out
+

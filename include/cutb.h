@@ -303,6 +303,27 @@ CUTB_API int cutb_rope_kv_write(int kv_dtype, const float *q, const float *k, co
                                 uint32_t q_dim, uint32_t kv_dim, uint32_t head_dim, uint64_t ld, uint32_t max_seq, int *status,
                                 void *stream);
 CUTB_API uint64_t cutb_attention_workspace_bytes(uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint32_t max_seq);
+/*
+ * Prefill (a batch of prompt tokens) over the same caches.  positions[i] is token i's cache row.
+ * cutb_batched_kv_write: k_cache[positions[i]] = RoPE(k_in[i]), v_cache[positions[i]] = v_in[i]; rows of
+ *   k_in / v_in are k_stride / v_stride elements apart, so they may be columns of a fused QKV matrix
+ *   (BatchedKVCacheWriteOpNode's dispatch, operators/impl/attention/BatchedKVCacheWrite.cu:33-62).
+ * cutb_batched_attention: out[i] = attention of RoPE(q_in[i]) over cache rows [0, positions[i]], one block
+ *   per (KV head, token) (operators/impl/attention/BatchedAttentionReadCache.cu).  positions[i] < 512:
+ *   one block holds a token's whole range; longer prompts go in chunks.  Call after the cache write.
+ * cutb_glu_pairs: out[r, i] = unary(op)(in[r, 2i]) * in[r, 2i + 1] (ldi even, 8-byte aligned `in`): the
+ *   gated activation over a prefill GEMM whose weight rows are stored in (gate, up) pairs.
+ */
+CUTB_API int cutb_batched_kv_write(int kv_dtype, const float *k_in, const float *v_in, uint32_t k_stride, uint32_t v_stride,
+                                   const uint32_t *positions, const float *cos_table, const float *sin_table, void *k_cache,
+                                   void *v_cache, uint32_t n_tokens, uint32_t kv_dim, uint32_t head_dim, uint64_t ld, uint32_t max_seq,
+                                   int *status, void *stream);
+CUTB_API int cutb_batched_attention(int kv_dtype, const float *q_in, uint32_t q_stride, const void *k_cache, const void *v_cache,
+                                    const uint32_t *positions, const float *cos_table, const float *sin_table, float *out,
+                                    uint32_t out_stride, uint32_t n_tokens, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
+                                    uint64_t ld, uint32_t max_seq, float scale, int *status, void *stream);
+CUTB_API int cutb_glu_pairs(const float *in, float *out, uint32_t rows, uint32_t cols_out, uint64_t ldi, uint64_t ldo, int unary_op,
+                            void *stream);
 CUTB_API int cutb_rope_attention_decode(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params,
                                         const float *cos_table, const float *sin_table, void *k_cache, void *v_cache, float *out,
                                         uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim, uint64_t ld, uint32_t max_seq,

@@ -161,6 +161,57 @@ def test_rope_attention_decode_equals_the_two_calls(gpu, kv, n_heads, n_kv, hd, 
     assert int(status.item()) == 1 and torch.equal(before, dkc)
 
 
+@pytest.mark.parametrize("kv", [np.float32, np.float16])
+@pytest.mark.parametrize("n_heads,n_kv,hd,max_seq,T,start", [(32, 8, 128, 600, 512, 0), (4, 2, 8, 16, 5, 3), (6, 3, 66, 64, 20, 7)])
+def test_batched_prefill_operators_match_checker(gpu, kv, n_heads, n_kv, hd, max_seq, T, start):
+    """cutb_batched_kv_write (bit-exact cache rows, inputs as columns of one fused QKV matrix) and
+    cutb_batched_attention (every token over the rows up to its own) against the checker run token by token."""
+    import torch
+
+    rng = np.random.default_rng(T + hd)
+    q_dim, kv_dim = n_heads * hd, n_kv * hd
+    ld = (kv_dim + 3) // 4 * 4
+    cos_t, sin_t = rope_tables(max_seq, hd)
+    qkv = rng.normal(0, 1, (T, q_dim + 2 * kv_dim)).astype(np.float32)
+    kc = rng.normal(0, 1, (max_seq, ld)).astype(kv)
+    vc = rng.normal(0, 1, (max_seq, ld)).astype(kv)
+    kc_ref, vc_ref = kc.copy(), vc.copy()
+    want = np.zeros((T, q_dim), np.float32)
+    sel = np.arange(T) if T <= 24 else np.array([0, 1, 100, 255, 256, 511])  # the float64 checker is slow on long ranges
+    q_ref = {}
+    for i in range(T):
+        q_ref[i] = O.rope_kv_write(qkv[i, :q_dim], qkv[i, q_dim:q_dim + kv_dim], qkv[i, q_dim + kv_dim:], start + i, cos_t, sin_t,
+                                   kc_ref, vc_ref, hd)
+    for i in sel:
+        want[i] = O.attention(q_ref[int(i)], kc_ref, vc_ref, start + int(i) + 1, n_heads, n_kv, hd)
+    dq, dkc, dvc = _dev(qkv), _dev(kc), _dev(vc)
+    pos = _dev(np.arange(start, start + T, dtype=np.int32))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gpu.batched_kv_write(dq[:, q_dim:q_dim + kv_dim], dq[:, q_dim + kv_dim:], pos, _dev(cos_t), _dev(sin_t), dkc, dvc, hd, status=status)
+    bits = np.uint16 if kv == np.float16 else np.uint32
+    assert np.array_equal(dkc.cpu().numpy().view(bits), kc_ref.view(bits))
+    assert np.array_equal(dvc.cpu().numpy().view(bits), vc_ref.view(bits))
+    got = gpu.batched_attention(dq[:, :q_dim], dkc, dvc, pos, _dev(cos_t), _dev(sin_t), n_heads, n_kv, hd, status=status).cpu().numpy()
+    assert int(status.item()) == 0
+    assert np.all(np.abs(got[sel] - want[sel]) <= 1e-5 + 1e-4 * np.abs(want[sel]))
+
+
+def test_batched_attention_range_limit_and_glu_pairs(gpu):
+    import torch
+
+    n_heads, n_kv, hd, max_seq = 2, 1, 32, 1024
+    cos_t, sin_t = rope_tables(max_seq, hd)
+    kc = torch.zeros((max_seq, hd), device="cuda")
+    q = torch.zeros((1, n_heads * hd), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gpu.batched_attention(q, kc, kc, _dev(np.array([600], np.int32)), _dev(cos_t), _dev(sin_t), n_heads, n_kv, hd, status=status)
+    assert int(status.item()) == 1  # a token past row 511: one block cannot hold its range, reported
+    x = np.random.default_rng(0).normal(0, 2, (7, 20)).astype(np.float32)
+    got = gpu.glu_pairs(_dev(x)).cpu().numpy()
+    want = np.array([[O.epilogue(float(x[r, 2 * i]), 1, 133) * np.float32(x[r, 2 * i + 1]) for i in range(10)] for r in range(7)], np.float32)
+    assert np.allclose(got, want, rtol=1e-6, atol=1e-7)
+
+
 def test_attention_empty_cache_and_clamped_length(gpu):
     import torch
 

@@ -109,6 +109,39 @@ def test_decode_steps_match_composed_checker(fmt, fuse_norm, glu, fuse_rope):
     assert dec.launches_per_step >= 3 + (0 if fuse_norm else 1) + ((7 if fuse_norm else 9) - (1 if glu else 0) - (1 if fuse_rope else 0)) * cfg.n_layers
 
 
+@pytest.mark.parametrize("fmt,T", [(2, 6), (2, 40), (0, 40), (1, 23)])
+@pytest.mark.parametrize("glu", [True, False])
+def test_batched_prefill_matches_the_token_by_token_checker(fmt, T, glu):
+    """The prompt as one batch (GEMM projections from 17 tokens up, batched RoPE cache write, one attention block per
+    KV head and token) against the float64 composition run token by token: caches, last token's logits and the
+    next decode step within 3e-3 rel-L2 (the prefill GEMM rounds activations to fp16)."""
+    from cut_b200.llama_decode import LlamaConfig, LlamaDecoder, synthetic_weights
+
+    cfg = LlamaConfig(n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=512, max_seq=64, fmt=fmt)
+    w = synthetic_weights(cfg, seed=fmt + 11, scale_shift=4)
+    w["embedding"] = (w["embedding"] * 50).astype(np.float32)
+    dec, ref = LlamaDecoder(cfg, w, glu_pairs=glu), Reference(cfg, w)
+    tokens = np.random.default_rng(T).integers(0, cfg.vocab, T)
+    for pos, tok in enumerate(tokens):
+        want = ref.step(int(tok), pos)
+    got = dec.prefill(tokens).cpu().numpy().astype(np.float64)
+    dec.check_status()
+    rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+    assert np.isfinite(got).all() and rel <= 3e-3, rel
+    for l in range(cfg.n_layers):
+        kc = dec.k_cache[l][:T, : cfg.kv_dim].float().cpu().numpy()
+        vc = dec.v_cache[l][:T, : cfg.kv_dim].float().cpu().numpy()
+        for got_c, want_c in ((kc, ref.kc[l][:T].astype(np.float32)), (vc, ref.vc[l][:T].astype(np.float32))):
+            assert np.linalg.norm(got_c - want_c) / np.linalg.norm(want_c) <= 3e-3
+        assert not dec.k_cache[l][T:].any()
+    assert int(dec.params[0].item()) == T and int(dec.token.item()) == int(np.argmax(got))
+    nxt = int(dec.token.item())
+    got2 = dec.step(nxt, T).cpu().numpy().astype(np.float64)
+    want2 = ref.step(nxt, T)
+    assert np.linalg.norm(got2 - want2) / np.linalg.norm(want2) <= 3e-3
+    dec.check_status()
+
+
 def test_position_past_the_cache_is_reported():
     from cut_b200 import _lib as L
     from cut_b200.llama_decode import LlamaConfig, LlamaDecoder, synthetic_weights
