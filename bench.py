@@ -207,8 +207,9 @@ def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = 
     from cut_b200.llama_decode import LlamaConfig, LlamaDecoder, synthetic_weights
 
     cfg = LlamaConfig(n_layers=n_layers)
-    # super-block scales divided by 16: activations of a trained model's size (the prefill GEMM rounds them to fp16)
-    dec = LlamaDecoder(cfg, synthetic_weights(cfg, seed=41, distinct_layers=False, scale_shift=4), dev)
+    # super-block scales divided by 128: the configuration's Q4_K distribution has a positive mean (~2), every
+    # projection then sums coherently and SiLU(gate) * up leaves fp16, the operand type of the prefill GEMM
+    dec = LlamaDecoder(cfg, synthetic_weights(cfg, seed=41, distinct_layers=False, scale_shift=7), dev)
     prompt = np.random.default_rng(42).integers(0, cfg.vocab, 512)
     p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     p0.record()

@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
   uint32_t *abort_flag = tmem_slot + 1;
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t n0 = blockIdx.x * TC_BW, m0 = blockIdx.y * (TC_MAX_MB * TC_BT);
+  const uint32_t n0 = blockIdx.x * TC_BW, m0 = blockIdx.y * (p.mb * TC_BT);
   const uint32_t nk = p.K / (TC_BK * KS);  // K stages
   const uint32_t fulla_u = smem_u32(bars), fullb_u = fulla_u + SA * 8, cons_u = fullb_u + NB * 8, accum_u = cons_u + NC * 8;
   const uint32_t tmem_cols = MB == 1 ? 128u : (MB == 2 ? 256u : 512u);
@@ -573,7 +573,7 @@ template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cuda
     CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)di.smem_optin));
     configured_device = dev;
   }
-  dim3 grid((p.N + TC_BW - 1) / TC_BW, (p.M + TC_MAX_MB * TC_BT - 1) / (TC_MAX_MB * TC_BT));
+  dim3 grid((p.N + TC_BW - 1) / TC_BW, (p.M + p.mb * TC_BT - 1) / (p.mb * TC_BT));
   qgemm_tc_kernel<FMT><<<grid, TC_CTRL_THREADS + 128 * p.groups, tc_smem_bytes(p.mb, p.sa, p.nb, p.ksub), stream>>>(map, p);
   CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;
@@ -616,6 +616,13 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.status = d.status;
   const uint32_t mblocks = (d.M + TC_BT - 1) / TC_BT;
   p.mb = mblocks < TC_MAX_MB ? mblocks : TC_MAX_MB;
+  // Few weight rows (a 4096-row projection is 32 column tiles): fewer tokens per CTA until the grid covers at
+  // least half of the SMs.  Each weight tile is then dequantised once per token group, which costs far less than
+  // leaving three quarters of the SMs idle.
+  {
+    const uint32_t ctiles = (d.N + TC_BW - 1) / TC_BW;
+    while (p.mb > 1 && ctiles * ((mblocks + p.mb - 1) / p.mb) * 2 <= (uint32_t)di.sm_count) p.mb = (p.mb + 1) / 2;
+  }
   // two weight slots (one per converter group); the rest of shared memory holds activation
   // stages in flight
   p.nb = 2;
