@@ -192,7 +192,7 @@ public:
       case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case TransposeQ4: break;
       case RMSNorm: case Embedding: case ReduceArgmax: case ReduceArgmin: case Attention: break;
       case CacheWrite:
-        if (desc->variant != FusedRoPEKVWriteOpNode::kVariant) throw std::runtime_error("B200Compute: no kernel for this CacheWrite operator");
+        if (desc->variant != FusedRoPEKVWriteOpNode::kVariant && desc->variant != BatchedKVCacheWriteOpNode::kVariant) throw std::runtime_error("B200Compute: no kernel for this CacheWrite operator");
         break;
       default: throw std::runtime_error("B200Compute: no kernel for operator " + std::to_string(desc->op));
     }
@@ -232,7 +232,7 @@ protected:
     ensureWorkspace(need);
     size_t attnNeed = 0;
     for (const auto &d : cb->dispatches)
-      if (!d.isBarrier && descOf(d).op == Attention) {
+      if (!d.isBarrier && descOf(d).op == Attention && descOf(d).variant == 0) {
         const AttnPC pc = pushConstants<AttnPC>(d);
         const size_t w = cutb_attention_workspace_bytes(pc.nHeads, pc.nKvHeads, pc.headDim, buf(d, 1).getShape()[0]);
         attnNeed = w > attnNeed ? w : attnNeed;
@@ -414,6 +414,28 @@ private:
         const DeviceBuffer &idx = buf(d, 0), &table = buf(d, 1), &out = buf(d, 2);
         cutbCheck(cutb_embedding((const uint32_t *)idx.data, (const float *)table.data, (float *)out.data, pc.numIndices,
                                  pc.embDim, table.getShape()[0], status_, stream_), "Embedding");
+      } else if (k.op == CacheWrite && k.variant == BatchedKVCacheWriteOpNode::kVariant) {
+        struct PC {
+          uint32_t batchSize, kvDim, alignedKvDim, headDim, halfDim, kStride, vStride, kOffset, vOffset;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &kc = buf(d, 2);
+        cutbCheck(cutb_batched_kv_write(k.dtypeA == (uint32_t)DataType::Float16 ? CUTB_F16 : CUTB_F32,
+                                        (const float *)buf(d, 0).data + pc.kOffset, (const float *)buf(d, 1).data + pc.vOffset, pc.kStride,
+                                        pc.vStride, (const uint32_t *)buf(d, 4).data, (const float *)buf(d, 5).data,
+                                        (const float *)buf(d, 6).data, kc.data, buf(d, 3).data, pc.batchSize, pc.kvDim, pc.headDim,
+                                        pc.alignedKvDim, kc.getShape()[0], status_, stream_), "BatchedKVCacheWrite");
+      } else if (k.op == Attention && k.variant == BatchedAttentionReadCacheOpNode::kVariant) {
+        struct PC {
+          uint32_t batchSize, nHeads, nKvHeads, headDim, alignedKvDim, nRep;
+          float scale;
+          uint32_t halfDim, qStride, qOffset;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &kc = buf(d, 1), &out = buf(d, 6);
+        cutbCheck(cutb_batched_attention(k.dtypeA == (uint32_t)DataType::Float16 ? CUTB_F16 : CUTB_F32,
+                                         (const float *)buf(d, 0).data + pc.qOffset, pc.qStride, kc.data, buf(d, 2).data,
+                                         (const uint32_t *)buf(d, 3).data, (const float *)buf(d, 4).data, (const float *)buf(d, 5).data,
+                                         (float *)out.data, out.innerDimPadded(), pc.batchSize, pc.nHeads, pc.nKvHeads, pc.headDim,
+                                         pc.alignedKvDim, kc.getShape()[0], pc.scale, status_, stream_), "BatchedAttentionReadCache");
       } else if (k.op == CacheWrite) {  // fused RoPE + KV-cache write
         struct PC {
           uint32_t qDim, kvDim, headDim, halfDim, alignedKvDim;

@@ -652,6 +652,77 @@ std::vector<uint8_t> FusedRoPEKVWriteOpNode::pushConstants() const {
   return toBytes(pc);
 }
 
+BatchedKVCacheWriteOpNode::BatchedKVCacheWriteOpNode(TensorStore &store, const Tensor &k, const Tensor &v, const Tensor &kCache,
+                                                     const Tensor &vCache, const Tensor &positions, const Tensor &cosTable,
+                                                     const Tensor &sinTable, uint32_t batchSize, uint32_t nKvHeads, uint32_t headDim,
+                                                     uint32_t kStride, uint32_t vStride, uint32_t kOffset, uint32_t vOffset,
+                                                     std::optional<uint32_t> spec)
+    : OpNode(CacheWrite, store, spec), batchSize_(batchSize), headDim_(headDim), kStride_(kStride), vStride_(vStride),
+      kOffset_(kOffset), vOffset_(vOffset) {
+  if (headDim == 0 || headDim % 2 != 0 || nKvHeads == 0) throw std::runtime_error("batchedKVCacheWrite: headDim must be even, nKvHeads positive");
+  kvDim_ = nKvHeads * headDim;
+  if (kStride < kOffset + kvDim_ || vStride < vOffset + kvDim_)
+    throw std::runtime_error("batchedKVCacheWrite: a row stride is shorter than offset + kvDim");
+  alignedKvDim_ = (kvDim_ + 3) & ~3u;
+  cacheDtype_ = store.getTensor(kCache).getDtype();
+  if (store.getTensor(vCache).getDtype() != cacheDtype_) throw std::runtime_error("batchedKVCacheWrite: K and V caches must share a dtype");
+  inputs_ = {k, v, kCache, vCache, positions, cosTable, sinTable};
+  output_ = kCache;
+}
+
+std::optional<std::vector<uint32_t>> BatchedKVCacheWriteOpNode::shader() const {
+  if (cacheDtype_ != DataType::Float32 && cacheDtype_ != DataType::Float16) return std::nullopt;
+  KernelDesc d;
+  d.op = CacheWrite;
+  d.variant = kVariant;
+  d.dtypeA = d.dtypeB = (uint32_t)cacheDtype_;
+  return d.encode();
+}
+
+std::vector<uint8_t> BatchedKVCacheWriteOpNode::pushConstants() const {
+  struct {
+    uint32_t batchSize, kvDim, alignedKvDim, headDim, halfDim, kStride, vStride, kOffset, vOffset;
+  } pc{batchSize_, kvDim_, alignedKvDim_, headDim_, headDim_ / 2, kStride_, vStride_, kOffset_, vOffset_};
+  return toBytes(pc);
+}
+
+BatchedAttentionReadCacheOpNode::BatchedAttentionReadCacheOpNode(TensorStore &store, const Tensor &q, const Tensor &kCache,
+                                                                 const Tensor &vCache, const Tensor &positions, const Tensor &cosTable,
+                                                                 const Tensor &sinTable, uint32_t batchSize, uint32_t nHeads,
+                                                                 uint32_t nKvHeads, uint32_t headDim, uint32_t qStride, uint32_t qOffset,
+                                                                 const Tensor &preallocOutput, std::optional<uint32_t> spec)
+    : OpNode(Attention, store, spec), batchSize_(batchSize), nHeads_(nHeads), nKvHeads_(nKvHeads), headDim_(headDim), qStride_(qStride),
+      qOffset_(qOffset) {
+  if (nHeads == 0 || nKvHeads == 0 || headDim == 0 || headDim % 2 != 0 || nHeads % nKvHeads != 0)
+    throw std::runtime_error("batchedAttentionReadCache: nHeads must be a positive multiple of nKvHeads and headDim even");
+  if (qStride < qOffset + nHeads * headDim) throw std::runtime_error("batchedAttentionReadCache: qStride is shorter than qOffset + nHeads * headDim");
+  dtype_ = store.getTensor(kCache).getDtype();
+  alignedKvDim_ = (nKvHeads * headDim + 3) & ~3u;
+  nRep_ = nHeads / nKvHeads;
+  scale_ = 1.0f / std::sqrt(static_cast<float>(headDim));
+  inputs_ = {q, kCache, vCache, positions, cosTable, sinTable};
+  output_ = preallocOutput ? preallocOutput : store.createTensorEmpty({batchSize, nHeads * headDim}, DataType::Float32);
+}
+
+std::optional<std::vector<uint32_t>> BatchedAttentionReadCacheOpNode::shader() const {
+  if (dtype_ != DataType::Float32 && dtype_ != DataType::Float16) return std::nullopt;
+  if (headDim_ > 128 || nRep_ > 8) return std::nullopt;
+  KernelDesc d;
+  d.op = Attention;
+  d.variant = kVariant;
+  d.dtypeA = d.dtypeB = (uint32_t)dtype_;
+  return d.encode();
+}
+
+std::vector<uint8_t> BatchedAttentionReadCacheOpNode::pushConstants() const {
+  struct {
+    uint32_t batchSize, nHeads, nKvHeads, headDim, alignedKvDim, nRep;
+    float scale;
+    uint32_t halfDim, qStride, qOffset;
+  } pc{batchSize_, nHeads_, nKvHeads_, headDim_, alignedKvDim_, nRep_, scale_, headDim_ / 2, qStride_, qOffset_};
+  return toBytes(pc);
+}
+
 // ---------------------------------------------------------------------------
 // VariantSelector (runtime/VariantSelector.cpp:242-428) with a small JSON reader
 // ---------------------------------------------------------------------------
@@ -938,6 +1009,22 @@ Tensor Operations::reduce(OperatorEnum op, const Tensor &a, std::optional<uint32
 Tensor Operations::attention(const Tensor &q, const Tensor &kCache, const Tensor &vCache, const Tensor &runtimeParams,
                              uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, const Tensor &preallocOutput) {
   return dispatch(std::make_unique<AttentionOpNode>(*store_, q, kCache, vCache, runtimeParams, nHeads, nKvHeads, headDim, preallocOutput));
+}
+
+void Operations::batchedKVCacheWrite(const Tensor &k, const Tensor &v, const Tensor &kCache, const Tensor &vCache,
+                                     const Tensor &positions, const Tensor &cosTable, const Tensor &sinTable, uint32_t batchSize,
+                                     uint32_t nKvHeads, uint32_t headDim, uint32_t kStride, uint32_t vStride, uint32_t kOffset,
+                                     uint32_t vOffset) {
+  dispatch(std::make_unique<BatchedKVCacheWriteOpNode>(*store_, k, v, kCache, vCache, positions, cosTable, sinTable, batchSize, nKvHeads,
+                                                       headDim, kStride, vStride, kOffset, vOffset));
+}
+
+Tensor Operations::batchedAttentionReadCache(const Tensor &q, const Tensor &kCache, const Tensor &vCache, const Tensor &positions,
+                                             const Tensor &cosTable, const Tensor &sinTable, uint32_t batchSize, uint32_t nHeads,
+                                             uint32_t nKvHeads, uint32_t headDim, uint32_t qStride, uint32_t qOffset,
+                                             const Tensor &preallocOutput) {
+  return dispatch(std::make_unique<BatchedAttentionReadCacheOpNode>(*store_, q, kCache, vCache, positions, cosTable, sinTable, batchSize,
+                                                                   nHeads, nKvHeads, headDim, qStride, qOffset, preallocOutput));
 }
 
 Tensor Operations::fusedRoPEKVWrite(const Tensor &q, const Tensor &k, const Tensor &v, const Tensor &runtimeParams,

@@ -482,6 +482,56 @@ private:
   uint32_t qDim_, kvDim_, headDim_, halfDim_, alignedKvDim_;
 };
 
+/// Prefill: roped k and v of a batch of tokens into the cache rows positions[i]; k and v may be columns
+/// (offset, row stride) of a wider matrix.  The node's output is the K cache itself
+/// (operators/impl/attention/AttentionOp.cpp:295-372).
+class BatchedKVCacheWriteOpNode : public OpNode {
+public:
+  static constexpr uint32_t kVariant = 2;
+  BatchedKVCacheWriteOpNode(TensorStore &store, const Tensor &k, const Tensor &v, const Tensor &kCache, const Tensor &vCache,
+                            const Tensor &positions, const Tensor &cosTable, const Tensor &sinTable, uint32_t batchSize,
+                            uint32_t nKvHeads, uint32_t headDim, uint32_t kStride, uint32_t vStride, uint32_t kOffset,
+                            uint32_t vOffset, std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return cacheDtype_; }
+  size_t shaderKey() const override {
+    return static_cast<size_t>(op_) | (size_t{1} << 33) | ((static_cast<size_t>(cacheDtype_) & 0xF) << 56);
+  }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return store_->getTensor(output_).getShape(); }
+  ThreadSize dispatchSize() const override { return {256, batchSize_, 1}; }
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "BatchedKVCacheWrite"; }
+
+private:
+  DataType cacheDtype_ = DataType::Float32;
+  uint32_t batchSize_, kvDim_, alignedKvDim_, headDim_, kStride_, vStride_, kOffset_, vOffset_;
+};
+
+/// Prefill attention over the populated cache: token i's query (rotated by the kernel) attends rows
+/// [0, positions[i]] (operators/impl/attention/AttentionOp.cpp:374-450).
+class BatchedAttentionReadCacheOpNode : public OpNode {
+public:
+  static constexpr uint32_t kVariant = 2;
+  BatchedAttentionReadCacheOpNode(TensorStore &store, const Tensor &q, const Tensor &kCache, const Tensor &vCache,
+                                  const Tensor &positions, const Tensor &cosTable, const Tensor &sinTable, uint32_t batchSize,
+                                  uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint32_t qStride, uint32_t qOffset,
+                                  const Tensor &preallocOutput = {}, std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return DataType::Float32; }
+  size_t shaderKey() const override {
+    return static_cast<size_t>(op_) | (size_t{1} << 33) | ((static_cast<size_t>(dtype_) & 0xF) << 56);
+  }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return {batchSize_, nHeads_ * headDim_}; }
+  ThreadSize dispatchSize() const override { return {nHeads_ * 256, batchSize_, 1}; }
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "BatchedAttentionReadCache"; }
+
+private:
+  DataType dtype_ = DataType::Float32;
+  uint32_t batchSize_, nHeads_, nKvHeads_, headDim_, alignedKvDim_, nRep_, qStride_, qOffset_;
+  float scale_;
+};
+
 // ---- VariantSelector: tuning_data.json rules (runtime/VariantSelector.cpp:242-428) ----------
 class VariantSelector {
 public:
@@ -550,6 +600,13 @@ public:
   Tensor reduce(OperatorEnum op, const Tensor &a, std::optional<uint32_t> spec = {});
   Tensor attention(const Tensor &q, const Tensor &kCache, const Tensor &vCache, const Tensor &runtimeParams, uint32_t nHeads,
                    uint32_t nKvHeads, uint32_t headDim, const Tensor &preallocOutput = {});
+  void batchedKVCacheWrite(const Tensor &k, const Tensor &v, const Tensor &kCache, const Tensor &vCache, const Tensor &positions,
+                           const Tensor &cosTable, const Tensor &sinTable, uint32_t batchSize, uint32_t nKvHeads, uint32_t headDim,
+                           uint32_t kStride, uint32_t vStride, uint32_t kOffset, uint32_t vOffset);
+  Tensor batchedAttentionReadCache(const Tensor &q, const Tensor &kCache, const Tensor &vCache, const Tensor &positions,
+                                   const Tensor &cosTable, const Tensor &sinTable, uint32_t batchSize, uint32_t nHeads,
+                                   uint32_t nKvHeads, uint32_t headDim, uint32_t qStride, uint32_t qOffset,
+                                   const Tensor &preallocOutput = {});
   Tensor fusedRoPEKVWrite(const Tensor &q, const Tensor &k, const Tensor &v, const Tensor &runtimeParams, const Tensor &cosTable,
                           const Tensor &sinTable, const Tensor &kCache, const Tensor &vCache, uint32_t headDim);
   void barrier() { dispatcher_->encodeBarrier(); }

@@ -408,6 +408,20 @@ void attentionNodes() {
   CHECK(r.shaderKey() != FusedRoPEKVWriteOpNode(s, q, k, v, params, cosT, sinT, kc32, vc32, hd).shaderKey());
   CHECK_THROWS(FusedRoPEKVWriteOpNode(s, q, k, v, params, cosT, sinT, kc, vc, 6), "headDim must be even and divide");
   CHECK_THROWS(FusedRoPEKVWriteOpNode(s, q, k, q, params, cosT, sinT, kc, vc, hd), "k and v of one length");
+  // prefill nodes: q / k / v as columns of one [T, 192] matrix
+  const uint32_t T = 5, width = nH * hd + 2 * nKv * hd;
+  auto qkv = s.createTensor({T, width}, DataType::Float32), posT = s.createTensor({T}, DataType::UInt32);
+  BatchedKVCacheWriteOpNode bw(s, qkv, qkv, kc, vc, posT, cosT, sinT, T, nKv, hd, width, width, nH * hd, nH * hd + nKv * hd);
+  CHECK(bw.op() == CacheWrite && bw.output() == kc && bw.dispatchSize().x == 256 && bw.dispatchSize().y == T);
+  uint32_t bpc[9];
+  std::memcpy(bpc, bw.bindings().back().bytes.data(), sizeof(bpc));
+  CHECK(bpc[0] == T && bpc[1] == 32 && bpc[2] == 32 && bpc[3] == hd && bpc[4] == hd / 2 && bpc[5] == width && bpc[7] == nH * hd);
+  CHECK(bw.shaderKey() != r.shaderKey() && KernelDesc::decode(*bw.shader())->variant == BatchedKVCacheWriteOpNode::kVariant);
+  CHECK_THROWS(BatchedKVCacheWriteOpNode(s, qkv, qkv, kc, vc, posT, cosT, sinT, T, nKv, hd, 100, width, nH * hd, 0), "row stride is shorter");
+  BatchedAttentionReadCacheOpNode ba(s, qkv, kc, vc, posT, cosT, sinT, T, nH, nKv, hd, width, 0);
+  CHECK(ba.op() == Attention && ba.outputShape() == (std::vector<uint32_t>{T, nH * hd}) && ba.dispatchSize().y == T);
+  CHECK(ba.shaderKey() != a.shaderKey() && ba.bindings().size() == 8 && ba.bindings().back().bytes.size() == 40);
+  CHECK_THROWS(BatchedAttentionReadCacheOpNode(s, qkv, kc, vc, posT, cosT, sinT, T, nH, nKv, hd, 64, 0), "qStride is shorter");
   auto qr = f.rt.ops().fusedRoPEKVWrite(q, k, v, params, cosT, sinT, kc, vc, hd);
   auto out = f.rt.ops().attention(qr, kc, vc, params, nH, nKv, hd);
   f.rt.flush();

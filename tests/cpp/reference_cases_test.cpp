@@ -512,6 +512,57 @@ void ropeCacheAttentionChain() {
   CHECK(std::memcmp(kGot.data(), kRef.data(), kGot.size() * sizeof(float)) == 0);
 }
 
+// Batched path (batchedKVCacheWrite + batchedAttentionReadCache over a fused QKV matrix) against the per-token
+// chain, row by row, with the reference's tolerance (RuntimeTests.cpp:2215-2300)
+void batchedAgainstPerToken() {
+  const uint32_t nH = 4, nKv = 2, hd = 16, maxSeq = 32, N = 9, qdim = nH * hd, kvdim = nKv * hd, half = hd / 2;
+  const uint32_t width = qdim + 2 * kvdim;
+  std::mt19937 gen(123);
+  std::uniform_real_distribution<float> dist(-1.f, 1.f);
+  std::vector<float> qkv(N * width);
+  for (auto &x : qkv) x = dist(gen);
+  std::vector<float> cosT(maxSeq * half), sinT(maxSeq * half);
+  for (uint32_t p = 0; p < maxSeq; ++p)
+    for (uint32_t i = 0; i < half; ++i) {
+      const float theta = float(p) / std::pow(10000.0f, 2.0f * i / hd);
+      cosT[p * half + i] = std::cos(theta);
+      sinT[p * half + i] = std::sin(theta);
+    }
+  auto tCos = rt->createTensor({maxSeq * half}, DataType::Float32, cosT.data());
+  auto tSin = rt->createTensor({maxSeq * half}, DataType::Float32, sinT.data());
+  std::vector<float> zeros(maxSeq * kvdim, 0.f), ref(N * qdim), got(N * qdim);
+  {  // per token
+    auto tK = rt->createTensor({maxSeq, kvdim}, DataType::Float32, zeros.data());
+    auto tV = rt->createTensor({maxSeq, kvdim}, DataType::Float32, zeros.data());
+    for (uint32_t i = 0; i < N; ++i) {
+      uint32_t params[2] = {i, i + 1};
+      auto tp = rt->createTensor({2}, DataType::UInt32, params);
+      auto tq = rt->createTensor({qdim}, DataType::Float32, &qkv[i * width]);
+      auto tk = rt->createTensor({kvdim}, DataType::Float32, &qkv[i * width + qdim]);
+      auto tv = rt->createTensor({kvdim}, DataType::Float32, &qkv[i * width + qdim + kvdim]);
+      auto roped = rt->ops().fusedRoPEKVWrite(tq, tk, tv, tp, tCos, tSin, tK, tV, hd);
+      auto attn = rt->ops().attention(roped, tK, tV, tp, nH, nKv, hd);
+      rt->copyFromTensor(attn, &ref[i * qdim], qdim * sizeof(float));
+    }
+  }
+  {  // batched, q / k / v as columns of one matrix
+    auto tK = rt->createTensor({maxSeq, kvdim}, DataType::Float32, zeros.data());
+    auto tV = rt->createTensor({maxSeq, kvdim}, DataType::Float32, zeros.data());
+    std::vector<uint32_t> positions(N);
+    for (uint32_t i = 0; i < N; ++i) positions[i] = i;
+    auto tPos = rt->createTensor({N}, DataType::UInt32, positions.data());
+    auto tQkv = rt->createTensor({N, width}, DataType::Float32, qkv.data());
+    rt->ops().batchedKVCacheWrite(tQkv, tQkv, tK, tV, tPos, tCos, tSin, N, nKv, hd, width, width, qdim, qdim + kvdim);
+    auto attn = rt->ops().batchedAttentionReadCache(tQkv, tK, tV, tPos, tCos, tSin, N, nH, nKv, hd, width, 0);
+    CHECK(rt->getTensor(attn).getShape() == (std::vector<uint32_t>{N, qdim}));
+    rt->copyFromTensor(attn, got.data(), got.size() * sizeof(float));
+  }
+  int bad = 0;
+  for (size_t j = 0; j < ref.size(); ++j)
+    if (!(std::abs(got[j] - ref[j]) <= std::abs(ref[j]) * 1e-3f + 1e-4f)) ++bad;
+  CHECK(bad == 0);
+}
+
 }  // namespace
 
 int main() {
@@ -536,6 +587,7 @@ int main() {
     RUN(embeddingCases);
     RUN(attentionCases);
     RUN(ropeCacheAttentionChain);
+    RUN(batchedAgainstPerToken);
   } catch (const std::exception &e) {
     std::printf("FAIL: unexpected exception: %s\n", e.what());
     return 2;
