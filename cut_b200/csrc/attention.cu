@@ -146,6 +146,7 @@ struct AttnParams {
   // with its query rotated here; q and out advance by their strides per token
   const uint32_t *positions;
   uint32_t q_stride, out_stride;
+  uint32_t tq, n_tokens;  // batched mode: consecutive tokens served by one block (they share every K / V row it reads)
   float scale;
 };
 
@@ -162,29 +163,51 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
 
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t kvH = blockIdx.x, split = blockIdx.y, S = p.splits;
-  const uint32_t nRep = p.nRep, HD = p.headDim;
+  const uint32_t HD = p.headDim;
   const bool batched = p.positions != nullptr;
-  const uint32_t token = batched ? blockIdx.z : 0u;
+  // Batched mode: a block serves TQ consecutive tokens.  Their query heads are "virtual heads" of the KV head
+  // (token-major), each with its own populated length; below, nRep counts virtual heads.
+  const uint32_t realRep = p.nRep, TQ = batched ? p.tq : 1u, nRep = realRep * TQ;
+  const uint32_t token0 = batched ? blockIdx.z * TQ : 0u;
+  __shared__ uint32_t vseq[AT_MAX_REP];  // rows [0, vseq) attended by each virtual head
   pdl_enter();
-  uint32_t seqLen = batched ? __ldg(p.positions + token) + 1u : __ldg(p.params + 1);
   const uint32_t seq_cap = batched ? min(p.max_seq, (uint32_t)AT_MAX_CHUNK) : p.max_seq;  // a batched block owns its whole range
-  if (seqLen > seq_cap) {  // never read outside the cache (or past what one block holds)
-    if (p.status && tid == 0 && kvH == 0 && split == 0) atomicExch(p.status, (int)CUTB_ERR_INVALID);
-    seqLen = seq_cap;
+  uint32_t seqLen = 0;
+  if (batched) {
+    for (uint32_t tq = 0; tq < TQ; ++tq) {
+      uint32_t sl = token0 + tq < p.n_tokens ? __ldg(p.positions + token0 + tq) + 1u : 0u;
+      if (sl > seq_cap) {  // never read outside the cache (or past what one block holds)
+        if (p.status && tid == 0 && kvH == 0) atomicExch(p.status, (int)CUTB_ERR_INVALID);
+        sl = seq_cap;
+      }
+      if (tid < realRep) vseq[tq * realRep + tid] = sl;
+      seqLen = max(seqLen, sl);
+    }
+  } else {
+    seqLen = __ldg(p.params + 1);
+    if (seqLen > seq_cap) {
+      if (p.status && tid == 0 && kvH == 0 && split == 0) atomicExch(p.status, (int)CUTB_ERR_INVALID);
+      seqLen = seq_cap;
+    }
   }
   const uint32_t chunk = (seqLen + S - 1) / S;  // <= AT_MAX_CHUNK by the launcher's choice of S
   const uint32_t t0 = min(split * chunk, seqLen), t1 = min(t0 + chunk, seqLen), cnt = t1 - t0;
   const KV *kC = reinterpret_cast<const KV *>(p.kC) + (uint64_t)kvH * HD;
   const KV *vC = reinterpret_cast<const KV *>(p.vC) + (uint64_t)kvH * HD;
 
-  if (batched) {  // rotate this token's query heads at its own position (half-split, separately rounded products)
-    const uint32_t half = HD / 2, pos = seqLen - 1;
-    const float *x = p.q + (uint64_t)token * p.q_stride + (uint64_t)kvH * nRep * HD;
-    const float *cs = p.cosT + (uint64_t)pos * half, *sn = p.sinT + (uint64_t)pos * half;
+  if (batched) {  // rotate every token's query heads at its own position (half-split, separately rounded products)
+    const uint32_t half = HD / 2;
     for (uint32_t i = tid; i < nRep * HD; i += AT_THREADS) {
-      const uint32_t in_head = i % HD;
-      qs[i] = in_head < half ? __fsub_rn(__fmul_rn(__ldg(x + i), __ldg(cs + in_head)), __fmul_rn(__ldg(x + i + half), __ldg(sn + in_head)))
-                             : __fadd_rn(__fmul_rn(__ldg(x + i - half), __ldg(sn + in_head - half)), __fmul_rn(__ldg(x + i), __ldg(cs + in_head - half)));
+      const uint32_t vr = i / HD, in_head = i % HD, tq = vr / realRep, r = vr % realRep, tk = token0 + tq;
+      float val = 0.f;
+      if (tk < p.n_tokens) {
+        const uint32_t pos = min(__ldg(p.positions + tk), seq_cap - 1);
+        const float *x = p.q + (uint64_t)tk * p.q_stride + (uint64_t)(kvH * realRep + r) * HD + in_head;
+        const float *cs = p.cosT + (uint64_t)pos * half, *sn = p.sinT + (uint64_t)pos * half;
+        val = in_head < half ? __fsub_rn(__fmul_rn(__ldg(x), __ldg(cs + in_head)), __fmul_rn(__ldg(x + half), __ldg(sn + in_head)))
+                             : __fadd_rn(__fmul_rn(__ldg(x - half), __ldg(sn + in_head - half)), __fmul_rn(__ldg(x), __ldg(cs + in_head - half)));
+      }
+      qs[i] = val;
     }
   } else {
     for (uint32_t i = tid; i < nRep * HD; i += AT_THREADS) qs[i] = __ldg(p.q + (uint64_t)kvH * nRep * HD + i);
@@ -273,16 +296,18 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
 
   // slice softmax: warp r owns query head r of the group
   for (uint32_t r = warp; r < nRep; r += AT_WARPS) {
+    const uint32_t cr = batched ? min(vseq[r], cnt) : cnt;  // a token of the tile sees the rows up to its own only
     float m = AT_NEG;
-    for (uint32_t i = lane; i < cnt; i += 32) m = fmaxf(m, sc[r * AT_MAX_CHUNK + i]);
+    for (uint32_t i = lane; i < cr; i += 32) m = fmaxf(m, sc[r * AT_MAX_CHUNK + i]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float l = 0.f;
-    for (uint32_t i = lane; i < cnt; i += 32) {
+    for (uint32_t i = lane; i < cr; i += 32) {
       const float e = expf(sc[r * AT_MAX_CHUNK + i] - m);
       sc[r * AT_MAX_CHUNK + i] = e;
       l += e;
     }
+    for (uint32_t i = cr + lane; i < cnt; i += 32) sc[r * AT_MAX_CHUNK + i] = 0.f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
     if (lane == 0) head_m[r] = m, head_l[r] = l;
@@ -342,7 +367,9 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
         const uint32_t r = idx / HD, d = idx % HD;
         float s = 0.f;
         for (uint32_t g = 0; g < G; ++g) s += red[(g * nRep + r) * HD + d];
-        p.out[(uint64_t)token * p.out_stride + (uint64_t)(kvH * nRep + r) * HD + d] = head_l[r] > 0.f ? s / head_l[r] : 0.f;
+        const uint32_t tk = token0 + r / realRep;
+        if (!batched || tk < p.n_tokens)
+          p.out[(uint64_t)tk * p.out_stride + (uint64_t)(kvH * realRep + r % realRep) * HD + d] = head_l[r] > 0.f ? s / head_l[r] : 0.f;
       }
       return;
     }
@@ -779,10 +806,13 @@ int batched_attention_launch(int kv_dtype, const float *q_in, uint32_t q_stride,
   p.q_stride = q_stride, p.out_stride = out_stride;
   p.nHeads = nHeads, p.nKvHeads = nKvHeads, p.headDim = headDim, p.ld = (uint32_t)ld, p.nRep = nHeads / nKvHeads;
   p.max_seq = max_seq, p.scale = scale, p.splits = 1;
+  p.n_tokens = n_tokens;
+  p.tq = (uint32_t)AT_MAX_REP / p.nRep;  // as many tokens per block as the kernel has query-head slots
+  if (p.tq < 1) p.tq = 1;
   const uint32_t esz = kv_dtype == CUTB_F16 ? 2 : 4;
   const bool vec = headDim % 32 == 0 && (ld * esz) % 16 == 0 && reinterpret_cast<uintptr_t>(kC) % 16 == 0 &&
                    reinterpret_cast<uintptr_t>(vC) % 16 == 0;
-  const dim3 grid(nKvHeads, 1, n_tokens);
+  const dim3 grid(nKvHeads, 1, (n_tokens + p.tq - 1) / p.tq);
   if (kv_dtype == CUTB_F16) {
     if (vec) CUTB_CUDA_TRY(launch_pdl(attention_decode_kernel<__half, true>, grid, dim3(AT_THREADS), 0, stream, p));
     else CUTB_CUDA_TRY(launch_pdl(attention_decode_kernel<__half, false>, grid, dim3(AT_THREADS), 0, stream, p));
