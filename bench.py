@@ -603,6 +603,21 @@ def run_ours(args) -> None:
     extra = {}
     if world == 1:
         extra = secondary_measurements(dev)
+    else:
+        # decode tok/s at N GPUs: the decoder does not shard (its per-layer exchanges would cost more than the
+        # mat-vecs they connect), so every GPU decodes its own batch-1 sequence; time = the slowest rank's
+        barrier()
+        dm = decode_measurement(dev)
+        t = torch.tensor([dm["ms_per_token"] * dm["tokens"], dm["prefill_ms"]], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ok = torch.tensor([1 if dm["logits_finite"] else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        extra = {"configs[3]_llama_q4_k_decode_replicas": {
+            "mode": "independent replicas: one batch-1 sequence per GPU, no exchange; time = max over ranks",
+            "tok/s": world * dm["tokens"] * 1e3 / float(t[0].item()), "tok/s_rank0": dm["tok/s"], "tokens_per_gpu": dm["tokens"],
+            "prefill_tok/s": world * 512e3 / float(t[1].item()), "logits_finite": bool(ok.item()),
+            "kernel_launches_per_token": dm["kernel_launches_per_token"]}}
+        barrier()
 
     cpu = None
     if rank == 0 and world == 1:
