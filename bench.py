@@ -607,16 +607,24 @@ def run_ours(args) -> None:
         # decode tok/s at N GPUs: the decoder does not shard (its per-layer exchanges would cost more than the
         # mat-vecs they connect), so every GPU decodes its own batch-1 sequence; time = the slowest rank's
         barrier()
-        dm = decode_measurement(dev)
-        t = torch.tensor([dm["ms_per_token"] * dm["tokens"], dm["prefill_ms"]], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ok = torch.tensor([1 if dm["logits_finite"] else 0], dtype=torch.int32, device=dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        extra = {"configs[3]_llama_q4_k_decode_replicas": {
-            "mode": "independent replicas: one batch-1 sequence per GPU, no exchange; time = max over ranks",
-            "tok/s": world * dm["tokens"] * 1e3 / float(t[0].item()), "tok/s_rank0": dm["tok/s"], "tokens_per_gpu": dm["tokens"],
-            "prefill_tok/s": world * 512e3 / float(t[1].item()), "logits_finite": bool(ok.item()),
-            "kernel_launches_per_token": dm["kernel_launches_per_token"]}}
+        err = None
+        try:
+            dm = decode_measurement(dev)
+            local = [dm["ms_per_token"] * dm["tokens"], dm["prefill_ms"], -1.0 if dm["logits_finite"] else 0.0, -1.0]
+        except Exception as e:  # a rank that fails still joins the reductions below, so nobody waits for it
+            err, dm = f"{type(e).__name__}: {e}", None
+            local = [float("inf"), float("inf"), 0.0, 0.0]
+        t = torch.tensor(local, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # times: slowest rank; flags are stored negated, so MAX is "any rank failed"
+        all_ok, all_finite = float(t[3].item()) < 0, float(t[2].item()) < 0
+        if all_ok and dm is not None:
+            extra = {"configs[3]_llama_q4_k_decode_replicas": {
+                "mode": "independent replicas: one batch-1 sequence per GPU, no exchange; time = max over ranks",
+                "tok/s": world * dm["tokens"] * 1e3 / float(t[0].item()), "tok/s_rank0": dm["tok/s"], "tokens_per_gpu": dm["tokens"],
+                "prefill_tok/s": world * 512e3 / float(t[1].item()), "logits_finite": all_finite,
+                "kernel_launches_per_token": dm["kernel_launches_per_token"]}}
+        else:
+            extra = {"configs[3]_llama_q4_k_decode_replicas": {"error": err or "another rank failed"}}
         barrier()
 
     cpu = None
