@@ -3,8 +3,12 @@
 // embedding row gather (operators/impl/memory/Embedding.cu:18-35) and arg-max / arg-min with the
 // reference's tie rule (operators/impl/reduce/ReduceArg.cu:27-59).  All three are bandwidth-
 // trivial next to the weight stream (a few KB to a few hundred KB per token).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "kernels.h"
+
+namespace cg = cooperative_groups;
 
 namespace cutb {
 namespace {
@@ -107,7 +111,8 @@ __global__ void __launch_bounds__(256) embedding_kernel(const uint32_t *__restri
 // tree (strides 128, 64, ..., 1, the lower position kept on ties) ends up preferring the thread
 // whose index read from the least significant bit upwards is smaller: the winner has the smallest
 // bit-reversed (i mod 256), then the smallest i.  The key (value, bitrev8(i mod 256), i) is a
-// total order, so any reduction shape gives the same winner: one CTA of 1024 threads.
+// total order, so any reduction shape gives the same winner: one CTA of 1024 threads, or for long inputs
+// (a vocabulary of logits) a cluster of eight whose block winners meet through distributed shared memory.
 struct ArgKey {
   float v;
   uint32_t i;
@@ -121,13 +126,15 @@ template <bool MAX> __device__ __forceinline__ bool arg_better(const ArgKey &a, 
 template <bool MAX>
 __global__ void __launch_bounds__(1024) argreduce_kernel(const float *__restrict__ v, float *__restrict__ out, uint32_t n) {
   __shared__ ArgKey part[32];
+  __shared__ ArgKey block_best;
   pdl_enter();
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // the reference starts every thread at (worst value, index 0) and replaces it only by strictly
   // better values: an input that never beats the start value yields index 0
   ArgKey best{MAX ? -3.402823466e+38f : 3.402823466e+38f, 0xFFFFFFFFu};
-#pragma unroll 8
-  for (uint32_t i = tid; i < n; i += 1024) {
+  const uint32_t step = gridDim.x * 1024;
+#pragma unroll 4
+  for (uint32_t i = blockIdx.x * 1024 + tid; i < n; i += step) {
     const ArgKey c{__ldg(v + i), i};
     const bool strictly = MAX ? c.v > best.v : c.v < best.v;
     if (strictly || (c.v == best.v && best.i != 0xFFFFFFFFu && arg_better<MAX>(c, best))) best = c;
@@ -154,7 +161,20 @@ __global__ void __launch_bounds__(1024) argreduce_kernel(const float *__restrict
       o.i = __shfl_down_sync(0xffffffffu, best.i, off);
       merge(o);
     }
-    if (lane == 0) out[0] = best.i == 0xFFFFFFFFu ? 0.0f : (float)best.i;
+    if (lane == 0) {
+      if (gridDim.x == 1) out[0] = best.i == 0xFFFFFFFFu ? 0.0f : (float)best.i;
+      else block_best = best;
+    }
+  }
+  if (gridDim.x > 1) {  // launched as one cluster: block 0 collects the block winners
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (blockIdx.x == 0 && tid == 0) {
+      best = block_best;
+      for (uint32_t r = 1; r < gridDim.x; ++r) merge(*cluster.map_shared_rank(&block_best, r));
+      out[0] = best.i == 0xFFFFFFFFu ? 0.0f : (float)best.i;
+    }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
   }
 }
 
@@ -217,6 +237,26 @@ int embedding_launch(const uint32_t *indices, const float *table, float *out, ui
 }
 
 int argreduce_launch(int is_max, const float *v, float *out, uint32_t n, cudaStream_t stream) {
+  if (n >= 8192) {  // eight blocks as one cluster
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(8);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 8;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    if (is_max)
+      CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, argreduce_kernel<true>, v, out, n));
+    else
+      CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, argreduce_kernel<false>, v, out, n));
+    return CUTB_OK;
+  }
   if (is_max)
     CUTB_CUDA_TRY(launch_pdl(argreduce_kernel<true>, dim3(1), dim3(1024), 0, stream, v, out, n));
   else

@@ -93,6 +93,10 @@ def test_argreduce_ties_follow_the_reference_tree(gpu, is_max):
         v = rng.integers(-3, 4, n).astype(np.float32)  # many ties
         got = float(gpu.argreduce(_dev(v), is_max).cpu().numpy()[0])
         assert got == O.argreduce(v, is_max), (trial, n)
+    for n in (8192, 32000, 40001):  # long inputs: eight blocks as one cluster
+        v = rng.integers(-3, 4, n).astype(np.float32)
+        got = float(gpu.argreduce(_dev(v), is_max).cpu().numpy()[0])
+        assert got == O.argreduce(v, is_max), n
     # the classic trap: the lowest index does not win
     v = np.zeros(1000, np.float32)
     v[1] = v[128] = 5.0 if is_max else -5.0
