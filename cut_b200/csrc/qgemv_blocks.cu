@@ -46,6 +46,8 @@
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel stores
 // CUTB_ERR_TIMEOUT in the caller's status word and leaves without spinning.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -496,6 +498,8 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
   constexpr bool TWO = AMODE == GV_A_F32_TWO;     // two 16-bit levels per fp32 value
   const uint32_t nvr = TWO ? 2 * nrows : nrows;
   const uint32_t nchunks = nblk * nrows * 4;
+  // rows whose element pairs can be read with one load each (the pair's first element is even)
+  const bool pairs = (reinterpret_cast<uintptr_t>(p.A) % (AF32 ? 8 : 4) == 0) && (p.lda % 2 == 0);
   const float wscale = (FMT == CUTB_Q4_0) ? 0.0625f : 1.0f;  // Q4_0 nibbles enter the MMA as 16 q
   const float sxscale = (FMT == CUTB_Q4_0) ? 8.0f : 1.0f;    // Q4_0: the -8 offset of every weight
   for (uint32_t base = 0; base < nchunks; base += THREADS) {  // uniform trip count: shuffles inside
@@ -509,11 +513,47 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     float amax = 0.f;
     const uint64_t rowbase = (uint64_t)m * p.lda + k0 + kb * 32;
     const float rs = (nscale && live) ? nscale[m] : 1.f;
+    // the eight elements of a chunk are four pairs (el, el + 1) with el even: one load per pair when
+    // the row is aligned for it.  All loads of a chunk are issued before any is used (idle threads
+    // read the row's first elements and discard them).
+    const uint64_t rb = live ? rowbase : 0;
+    if (pairs) {
+      if constexpr (AF32) {
+        float2 v[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+          const uint32_t el = DIAG ? diag_elem<FMT>(even, ct, 2 * i) : frag_elem<FMT>(even, ct, 2 * i);
+          v[i] = __ldg(reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(p.A) + rb + el));
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) x[2 * i] = v[i].x, x[2 * i + 1] = v[i].y;
+      } else {
+        __half2 v[4];
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+          const uint32_t el = DIAG ? diag_elem<FMT>(even, ct, 2 * i) : frag_elem<FMT>(even, ct, 2 * i);
+          v[i] = __ldg(reinterpret_cast<const __half2 *>(reinterpret_cast<const __half *>(p.A) + rb + el));
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(v[i]);
+          x[2 * i] = f.x, x[2 * i + 1] = f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (uint32_t i = 0; i < 8; ++i) {
+        const uint32_t el = DIAG ? diag_elem<FMT>(even, ct, i) : frag_elem<FMT>(even, ct, i);
+        x[i] = load_act<AF32>(p.A, rb + el);
+      }
+    }
 #pragma unroll
     for (uint32_t i = 0; i < 8; ++i) {
-      const uint32_t el = DIAG ? diag_elem<FMT>(even, ct, i) : frag_elem<FMT>(even, ct, i);
-      x[i] = live ? load_act<AF32>(p.A, rowbase + el) : 0.f;
-      if (nscale && live) x[i] = x[i] * rs * __ldg(p.norm_w + k0 + kb * 32 + el);  // RMSNorm fused into the staging
+      if (!live) x[i] = 0.f;
+      if (nscale && live) {  // RMSNorm fused into the staging
+        const uint32_t el = DIAG ? diag_elem<FMT>(even, ct, i) : frag_elem<FMT>(even, ct, i);
+        x[i] = x[i] * rs * __ldg(p.norm_w + k0 + kb * 32 + el);
+      }
       amax = fmaxf(amax, fabsf(x[i]));
     }
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -763,8 +803,8 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
     for (int nt = 0; nt < NT; ++nt) tot[nt][0] = tot[nt][1] = 0.f;
 
     for (uint32_t c = 0; c < cpt; ++c) {
-      if (!dead) {
-        const bool ok = mbar_wait_probe_first(full_u + (slot * HV + hv) * 8, parity);
+      if (!dead && !mbar_test(full_u + (slot * HV + hv) * 8, parity)) {  // the vote only on the slow path
+        const bool ok = mbar_wait_bounded(full_u + (slot * HV + hv) * 8, parity);
         if (!__all_sync(0xffffffffu, ok)) {
           dead = true;
           if (lane == 0 && p.status) atomicExch(p.status, (int)CUTB_ERR_TIMEOUT);
@@ -789,7 +829,10 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty_u + (slot * HV + hv) * 8);
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(
+                       empty_u + (slot * HV + hv) * 8),
+                   "r"(lane)
+                   : "memory");
       if (++slot == S) slot = 0, parity ^= 1u;
     }
 
@@ -968,10 +1011,12 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
   // cannot hold two stages, take the deepest ring that fits one CTA per SM.
   // K is split further only when even two stages do not fit.
   const size_t half = (di.smem_per_sm > 2048 ? di.smem_per_sm / 2 - 1024 : limit / 2);
+  uint32_t max_stages = 4;
+  if (const char *e = getenv("CUTB_GV_STAGES")) max_stages = (uint32_t)atoi(e) < 2 ? 2u : (uint32_t)atoi(e);  // tuning override
   for (uint32_t ks = want; ks <= G; ++ks) {
     const uint32_t gps = (G + ks - 1) / ks;
-    const bool pair = gv_smem_bytes(d.format, pl->diag, 2, pl->nt, pl->ncp, gps) <= half;
-    for (uint32_t st = pair ? 2 : 4; st >= 2; --st) {
+    const bool pair = !(d.flags & CUTB_FLAG_NO_OVERLAP) && gv_smem_bytes(d.format, pl->diag, 2, pl->nt, pl->ncp, gps) <= half;
+    for (uint32_t st = pair ? 2 : max_stages; st >= 2; --st) {
       const size_t sm = gv_smem_bytes(d.format, pl->diag, st, pl->nt, pl->ncp, gps);
       if (sm <= limit) {
         pl->gran_per_split = gps;
