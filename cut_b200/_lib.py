@@ -10,7 +10,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libcutb.so")
 
-OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT = range(6)
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT, ERR_RANGE = range(7)
 Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 4, 5  # the last three: cutb_dequant only
 F32, F16 = 0, 1
 LAYOUT_GGUF_BLOCKS, LAYOUT_KN_PLANES = 0, 1
@@ -25,6 +25,7 @@ FLAG_GLU_PAIRS = 8
 EXPORTS = [
     "cutb_qmatmul_workspace_bytes", "cutb_qmatmul_select_variant", "cutb_qmatmul", "cutb_qmatmul_decode_noalloc",
     "cutb_qmatmul_scatter", "cutb_peer_exchange",
+    "cutb_peer_buffer_alloc", "cutb_peer_buffer_open", "cutb_peer_buffer_close", "cutb_peer_buffer_free",
     "cutb_rmsnorm", "cutb_embedding", "cutb_argreduce",
     "cutb_rope_kv_write", "cutb_attention_workspace_bytes", "cutb_attention_decode", "cutb_rope_attention_decode",
     "cutb_batched_kv_write", "cutb_batched_attention", "cutb_glu_pairs",
@@ -89,6 +90,14 @@ def lib() -> C.CDLL:
         l.cutb_qmatmul_scatter.argtypes = [C.POINTER(QMatmulDesc), C.POINTER(PeerScatter), C.c_void_p]
         l.cutb_peer_exchange.restype = C.c_int
         l.cutb_peer_exchange.argtypes = [C.POINTER(PeerScatter), C.c_void_p, C.c_void_p, C.c_void_p]
+        l.cutb_peer_buffer_alloc.restype = C.c_int
+        l.cutb_peer_buffer_alloc.argtypes = [C.c_uint64, C.POINTER(C.c_void_p), C.c_char_p]
+        l.cutb_peer_buffer_open.restype = C.c_int
+        l.cutb_peer_buffer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+        l.cutb_peer_buffer_close.restype = C.c_int
+        l.cutb_peer_buffer_close.argtypes = [C.c_void_p]
+        l.cutb_peer_buffer_free.restype = C.c_int
+        l.cutb_peer_buffer_free.argtypes = [C.c_void_p]
         l.cutb_dequant.restype = C.c_int
         l.cutb_dequant.argtypes = [C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
                                    C.c_void_p]

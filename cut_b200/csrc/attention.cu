@@ -645,13 +645,13 @@ constexpr size_t AT_CLUSTER_SMEM = 200 * 1024;  // dynamic shared memory the clu
 
 template <typename KV, int NREP>
 int cluster_launch(const AttnParams &p, uint32_t S, size_t dyn, cudaStream_t stream) {
-  static int configured_device = -1;
+  static bool configured[64] = {};  // per device: the attribute is set once on each
   int dev = 0;
   CUTB_CUDA_TRY(cudaGetDevice(&dev));
-  if (configured_device != dev) {
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     CUTB_CUDA_TRY(cudaFuncSetAttribute(attention_decode_cluster_kernel<KV, NREP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)AT_CLUSTER_SMEM));
-    configured_device = dev;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.nKvHeads, S);
@@ -671,8 +671,24 @@ int cluster_launch(const AttnParams &p, uint32_t S, size_t dyn, cudaStream_t str
   return CUTB_OK;
 }
 
+// SM count of the current device; 148 (a B200) only when no device can be queried, so that sizes can
+// be computed ahead of time on a host without one.
+uint32_t sm_count_or_default() {
+  DeviceInfo di;
+  return (get_device_info(&di) == CUTB_OK && di.sm_count > 0) ? (uint32_t)di.sm_count : 148u;
+}
+
+// The kernels index cache rows with 32-bit strides.
+int check_ld(uint64_t ld, const char *who) {
+  if (ld > 0xFFFFFFFFull) {
+    set_last_error("%s: row stride %llu does not fit 32 bits", who, (unsigned long long)ld);
+    return CUTB_ERR_INVALID;
+  }
+  return CUTB_OK;
+}
+
 uint32_t attn_splits(uint32_t nKvHeads, uint32_t max_seq) {
-  uint32_t s = 148u / nKvHeads;
+  uint32_t s = sm_count_or_default() / nKvHeads;
   if (s < 1) s = 1;
   if (s > (uint32_t)AT_MAX_SPLITS) s = AT_MAX_SPLITS;
   if (s > max_seq) s = max_seq;
@@ -685,6 +701,7 @@ uint32_t attn_splits(uint32_t nKvHeads, uint32_t max_seq) {
 int rope_kv_write_launch(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params, const float *cosT,
                          const float *sinT, void *kC, void *vC, float *qOut, uint32_t qDim, uint32_t kvDim, uint32_t headDim,
                          uint64_t ld, uint32_t max_seq, int *status, cudaStream_t stream) {
+  if (int rc = check_ld(ld, "rope_kv_write_launch")) return rc;
   const uint32_t total = qDim + 2 * kvDim;
   const dim3 grid((total + 255) / 256);
   if (kv_dtype == CUTB_F16)
@@ -771,6 +788,7 @@ int attention_launch_any(int kv_dtype, const float *q, const float *k_new, const
 int attention_decode_launch(int kv_dtype, const float *q, const void *kC, const void *vC, const uint32_t *params, float *out,
                             uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale,
                             void *workspace, int *status, cudaStream_t stream) {
+  if (int rc = check_ld(ld, "attention_decode_launch")) return rc;
   return attention_launch_any(kv_dtype, q, nullptr, nullptr, nullptr, nullptr, const_cast<void *>(kC), const_cast<void *>(vC), params,
                               out, nHeads, nKvHeads, headDim, ld, max_seq, scale, workspace, status, stream);
 }
@@ -779,6 +797,7 @@ int rope_attention_decode_launch(int kv_dtype, const float *q, const float *k, c
                                  const float *cosT, const float *sinT, void *kC, void *vC, float *out, uint32_t nHeads,
                                  uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale, void *workspace,
                                  int *status, cudaStream_t stream) {
+  if (int rc = check_ld(ld, "rope_attention_decode_launch")) return rc;
   return attention_launch_any(kv_dtype, q, k, v, cosT, sinT, kC, vC, params, out, nHeads, nKvHeads, headDim, ld, max_seq, scale,
                               workspace, status, stream);
 }
@@ -786,6 +805,7 @@ int rope_attention_decode_launch(int kv_dtype, const float *q, const float *k, c
 int batched_kv_write_launch(int kv_dtype, const float *k_in, const float *v_in, uint32_t k_stride, uint32_t v_stride,
                             const uint32_t *positions, const float *cosT, const float *sinT, void *kC, void *vC, uint32_t n_tokens,
                             uint32_t kvDim, uint32_t headDim, uint64_t ld, uint32_t max_seq, int *status, cudaStream_t stream) {
+  if (int rc = check_ld(ld, "batched_kv_write_launch")) return rc;
   if (n_tokens == 0) return CUTB_OK;
   if (kv_dtype == CUTB_F16)
     CUTB_CUDA_TRY(launch_pdl(batched_kv_write_kernel<__half>, dim3(n_tokens), dim3(256), 0, stream, k_in, v_in, k_stride, v_stride, positions,
@@ -800,6 +820,7 @@ int batched_attention_launch(int kv_dtype, const float *q_in, uint32_t q_stride,
                              const uint32_t *positions, const float *cosT, const float *sinT, float *out, uint32_t out_stride,
                              uint32_t n_tokens, uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq,
                              float scale, int *status, cudaStream_t stream) {
+  if (int rc = check_ld(ld, "batched_attention_launch")) return rc;
   if (n_tokens == 0) return CUTB_OK;
   AttnParams p{};
   p.q = q_in, p.kC = kC, p.vC = vC, p.out = out, p.status = status, p.positions = positions, p.cosT = cosT, p.sinT = sinT;

@@ -1,5 +1,7 @@
 // extern "C" entry points of libcutb.so: argument validation, variant choice,
 // launch.  No allocation, no synchronisation, no CPU fallback.
+#include <string.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -131,6 +133,7 @@ const char *cutb_status_string(int status) {
     case CUTB_ERR_CUDA: return "CUDA error";
     case CUTB_ERR_WORKSPACE: return "workspace missing or too small";
     case CUTB_ERR_TIMEOUT: return "device-side wait timed out";
+    case CUTB_ERR_RANGE: return "activation outside the fp16 operand range";
     default: return "unknown status";
   }
 }
@@ -232,6 +235,52 @@ int cutb_qmatmul_scatter(const cutb_qmatmul_desc *desc, const cutb_peer_scatter 
     return CUTB_ERR_UNSUPPORTED;
   }
   return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream), peers);
+}
+
+int cutb_peer_buffer_alloc(uint64_t bytes, void **ptr, uint8_t handle[CUTB_PEER_HANDLE_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == CUTB_PEER_HANDLE_BYTES, "handle size");
+  if (!ptr || !handle || bytes == 0) {
+    set_last_error("peer_buffer_alloc: null argument or zero size");
+    return CUTB_ERR_INVALID;
+  }
+  void *p = nullptr;
+  CUTB_CUDA_TRY(cudaMalloc(&p, bytes));
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "cudaIpcGetMemHandle");
+  }
+  memcpy(handle, &h, sizeof(h));
+  *ptr = p;
+  return CUTB_OK;
+}
+
+int cutb_peer_buffer_open(const uint8_t handle[CUTB_PEER_HANDLE_BYTES], void **ptr) {
+  if (!ptr || !handle) {
+    set_last_error("peer_buffer_open: null argument");
+    return CUTB_ERR_INVALID;
+  }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void *p = nullptr;
+  CUTB_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = p;
+  return CUTB_OK;
+}
+
+int cutb_peer_buffer_close(void *ptr) {
+  if (!ptr) return CUTB_OK;
+  CUTB_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return CUTB_OK;
+}
+
+int cutb_peer_buffer_free(void *ptr) {
+  if (!ptr) return CUTB_OK;
+  CUTB_CUDA_TRY(cudaFree(ptr));
+  return CUTB_OK;
 }
 
 int cutb_peer_exchange(const cutb_peer_scatter *peers, uint64_t *step_counter, int *status, void *stream) {

@@ -49,12 +49,28 @@ struct ShaderModule : ComputeHandle::Slot {
   KernelDesc desc;
 };
 
+// A block of device scratch.  Command buffers share the current block; a recorded CUDA graph has the
+// block's address baked into its kernel arguments, so the block lives as long as any command buffer
+// that was built on it (a bigger request allocates a new block instead of replacing this one).
+struct Scratch {
+  explicit Scratch(size_t n, bool zero) : bytes(n) {
+    cudaCheck(cudaMalloc(&ptr, n), "cudaMalloc(scratch)");
+    if (zero) cudaCheck(cudaMemset(ptr, 0, n), "cudaMemset(scratch)");
+  }
+  ~Scratch() { cudaFree(ptr); }  // cudaFree waits for work that still uses the block
+  Scratch(const Scratch &) = delete;
+  Scratch &operator=(const Scratch &) = delete;
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+
 struct CommandBufferObj : ComputeHandle::Slot {
   ~CommandBufferObj() override {
     if (exec) cudaGraphExecDestroy(exec);
     if (graph) cudaGraphDestroy(graph);
   }
   std::vector<ComputeDispatch> dispatches;  // keeps every bound buffer alive until the work is done
+  std::shared_ptr<Scratch> workspace, attnWs;  // the scratch blocks its launches (and its graph) point into
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
 };
@@ -95,8 +111,8 @@ public:
   }
   ~B200Compute() override {
     cudaStreamSynchronize(stream_);
-    if (workspace_) cudaFree(workspace_);
-    if (attnWs_) cudaFree(attnWs_);
+    workspace_.reset();
+    attnWs_.reset();
     cudaFree(status_);
     cudaStreamDestroy(stream_);
   }
@@ -238,6 +254,8 @@ protected:
         attnNeed = w > attnNeed ? w : attnNeed;
       }
     ensureAttnWorkspace(attnNeed);
+    cb->workspace = workspace_;
+    cb->attnWs = attnWs_;
     if (reusable) {
       // warm launch outside capture (first-use kernel attributes), then capture the same list
       launchAll(*cb, descs);
@@ -283,24 +301,23 @@ private:
     cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
   }
 
+  // Scratch only grows, and never in place: command buffers recorded earlier keep the block they
+  // were built on (their graphs replay with its address), new work gets a new, larger block.
   void ensureWorkspace(size_t need) {
-    if (need <= workspaceBytes_) return;
-    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
-    if (workspace_) cudaFree(workspace_);
-    workspace_ = nullptr;
-    cudaCheck(cudaMalloc(&workspace_, need), "cudaMalloc(workspace)");
-    workspaceBytes_ = need;
+    if (workspace_ && need <= workspace_->bytes) return;
+    if (need == 0) return;
+    workspace_ = std::make_shared<Scratch>(need, false);
   }
 
   void ensureAttnWorkspace(size_t need) {
-    if (need <= attnWsBytes_) return;
-    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
-    if (attnWs_) cudaFree(attnWs_);
-    attnWs_ = nullptr;
-    cudaCheck(cudaMalloc(&attnWs_, need), "cudaMalloc(attention workspace)");
-    cudaCheck(cudaMemset(attnWs_, 0, need), "cudaMemset(attention workspace)");
-    attnWsBytes_ = need;
+    if (attnWs_ && need <= attnWs_->bytes) return;
+    if (need == 0) return;
+    attnWs_ = std::make_shared<Scratch>(need, true);  // its arrival counters start at zero
   }
+  void *wsPtr() const { return workspace_ ? workspace_->ptr : nullptr; }
+  size_t wsBytes() const { return workspace_ ? workspace_->bytes : 0; }
+  void *attnPtr() const { return attnWs_ ? attnWs_->ptr : nullptr; }
+  size_t attnBytes() const { return attnWs_ ? attnWs_->bytes : 0; }
 
   struct AttnPC {
     uint32_t nHeads, nKvHeads, headDim, kvDim, alignedKvDim, nRep;
@@ -370,8 +387,8 @@ private:
     q.fusion_op = (int32_t)k.fusionOp;
     // plane-layout variant indices all map onto the one plane kernel; block variants are the C ABI's own
     q.variant = blocks ? (int32_t)k.variant : CUTB_VARIANT_GENERIC;
-    q.workspace = workspace_;
-    q.workspace_bytes = workspaceBytes_;
+    q.workspace = wsPtr();
+    q.workspace_bytes = wsBytes();
     q.status = status_;
     q.flags = 0;
     return q;
@@ -383,8 +400,8 @@ private:
       if (d.isBarrier) continue;  // one in-order stream: dispatches are already ordered
       const KernelDesc &k = descOf(d);
       if (isMatmul(d)) {
-        descs[i].workspace = workspace_;
-        descs[i].workspace_bytes = workspaceBytes_;
+        descs[i].workspace = wsPtr();
+        descs[i].workspace_bytes = wsBytes();
         cutbCheck(cutb_qmatmul(&descs[i], stream_), d.label.c_str());
       } else if (k.op == Dequantize) {
         struct PC {
@@ -451,7 +468,7 @@ private:
         const DeviceBuffer &kc = buf(d, 1);
         cutbCheck(cutb_attention_decode(k.dtypeA == (uint32_t)DataType::Float16 ? CUTB_F16 : CUTB_F32, (const float *)buf(d, 0).data,
                                         kc.data, buf(d, 2).data, (const uint32_t *)buf(d, 3).data, (float *)buf(d, 4).data, pc.nHeads,
-                                        pc.nKvHeads, pc.headDim, pc.alignedKvDim, kc.getShape()[0], pc.scale, attnWs_, attnWsBytes_,
+                                        pc.nKvHeads, pc.headDim, pc.alignedKvDim, kc.getShape()[0], pc.scale, attnPtr(), attnBytes(),
                                         status_, stream_), "Attention");
       } else if (k.op == ReduceArgmax || k.op == ReduceArgmin) {
         const uint32_t n = pushConstants<uint32_t>(d);
@@ -465,10 +482,8 @@ private:
 
   int device_;
   cudaStream_t stream_ = nullptr;
-  void *workspace_ = nullptr;
-  size_t workspaceBytes_ = 0;
-  void *attnWs_ = nullptr;  // attention scratch; its arrival counters start at zero and every launch leaves them zero
-  size_t attnWsBytes_ = 0;
+  std::shared_ptr<Scratch> workspace_;  // split-K partial sums / cast activations of the matmuls
+  std::shared_ptr<Scratch> attnWs_;     // attention scratch; its arrival counters start at zero and every launch leaves them zero
   int *status_ = nullptr;
   size_t nextId_ = 0, activeBytes_ = 0, bufferCount_ = 0, totalMem_ = 0;
   uint32_t smemOptin_ = 0;

@@ -198,7 +198,9 @@ int glu_pairs_launch(const float *in, float *out, uint32_t rows, uint32_t cols_o
   const uint64_t total = (uint64_t)rows * cols_out;
   if (total == 0) return CUTB_OK;
   uint64_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  DeviceInfo di;
+  const uint64_t sms = (get_device_info(&di) == CUTB_OK && di.sm_count > 0) ? (uint64_t)di.sm_count : 148u;
+  if (blocks > sms * 16) blocks = sms * 16;
   CUTB_CUDA_TRY(launch_pdl(glu_pairs_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, reinterpret_cast<const float2 *>(in), out, rows,
                            cols_out, ldi / 2, ldo, unary_op));
   return CUTB_OK;

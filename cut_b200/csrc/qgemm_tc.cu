@@ -516,15 +516,21 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
   }
 }
 
-// fp32 activations -> fp16 rows of K elements (the TMA source of the GEMM)
-__global__ void cast_f32_f16_kernel(const float *__restrict__ A, uint32_t lda, __half *__restrict__ out, uint32_t M, uint32_t K) {
+// fp32 activations -> fp16 rows of K elements (the TMA source of the GEMM).  A finite value beyond the
+// fp16 range (it rounds to infinity) is reported through the caller's status word.
+__global__ void cast_f32_f16_kernel(const float *__restrict__ A, uint32_t lda, __half *__restrict__ out, uint32_t M, uint32_t K,
+                                    int *status) {
   const size_t total = (size_t)M * (K / 4);
+  bool over = false;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t m = i / (K / 4), k = (i % (K / 4)) * 4;
     const float4 f = __ldg(reinterpret_cast<const float4 *>(A + m * lda + k));
+    const float big = fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w)));  // NaN operands drop out of fmaxf
+    over |= big > 65504.0f && big < __int_as_float(0x7f800000);
     *reinterpret_cast<uint2 *>(out + m * K + k) =
         make_uint2(h2_as_u32(__floats2half2_rn(f.x, f.y)), h2_as_u32(__floats2half2_rn(f.z, f.w)));
   }
+  if (status && __any_sync(0xffffffffu, over) && (threadIdx.x & 31) == 0) atomicExch(status, (int)CUTB_ERR_RANGE);
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
@@ -564,14 +570,14 @@ size_t tc_smem_bytes(uint32_t mb, uint32_t sa, uint32_t nb, uint32_t ksub) {
 }
 
 template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cudaStream_t stream) {
-  static int configured_device = -1;
+  static bool configured[64] = {};  // per device: the attribute is set once on each
   int dev = 0;
   CUTB_CUDA_TRY(cudaGetDevice(&dev));
-  if (configured_device != dev) {
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     DeviceInfo di;
     if (int rc = get_device_info(&di)) return rc;
     CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)di.smem_optin));
-    configured_device = dev;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid((p.N + TC_BW - 1) / TC_BW, (p.M + p.mb * TC_BT - 1) / (p.mb * TC_BT));
   qgemm_tc_kernel<FMT><<<grid, TC_CTRL_THREADS + 128 * p.groups, tc_smem_bytes(p.mb, p.sa, p.nb, p.ksub), stream>>>(map, p);
@@ -656,7 +662,7 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
     const size_t total = (size_t)d.M * (d.K / 4);
     const unsigned blocks = (unsigned)((total + 255) / 256 < (size_t)di.sm_count * 8 ? (total + 255) / 256 : (size_t)di.sm_count * 8);
     cast_f32_f16_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float *>(d.A), d.lda,
-                                                    reinterpret_cast<__half *>(d.workspace), d.M, d.K);
+                                                    reinterpret_cast<__half *>(d.workspace), d.M, d.K, d.status);
     CUTB_CUDA_TRY(cudaGetLastError());
     a16 = d.workspace;
     stride = (uint64_t)d.K * sizeof(__half);

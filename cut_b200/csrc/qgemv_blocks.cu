@@ -1032,15 +1032,15 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
 
 template <int FMT, int AMODE, int NT, bool DIAG>
 int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
-  static int configured_device = -1;
+  static bool configured[64] = {};  // per device: the attribute is set once on each
   int dev = 0;
   CUTB_CUDA_TRY(cudaGetDevice(&dev));
-  if (configured_device != dev) {
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     DeviceInfo di;
     if (int rc = get_device_info(&di)) return rc;
     CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AMODE, NT, DIAG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)di.smem_optin));
-    configured_device = dev;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(pl.grid_x, pl.ksplit);
@@ -1105,6 +1105,23 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
   if (!gv_plan(d, di, &pl)) {
     set_last_error("qgemv: no shared-memory plan for M=%u K=%u N=%u", d.M, d.K, d.N);
     return CUTB_ERR_UNSUPPORTED;
+  }
+  // Flag combinations this kernel cannot run, checked here so that every entry point that reaches the
+  // mat-vec (cutb_qmatmul, cutb_qmatmul_scatter, cutb_qmatmul_decode_noalloc) refuses them before a launch.
+  if (d.flags & CUTB_FLAG_GLU_PAIRS) {
+    if (pl.ksplit > 1 || sc) {
+      set_last_error("qgemv: paired gate/up rows need a launch that neither splits K (this shape splits it %u ways) nor scatters to peers",
+                     pl.ksplit);
+      return CUTB_ERR_UNSUPPORTED;
+    }
+    if (d.N % 2 != 0) {
+      set_last_error("qgemv: paired gate/up rows need an even N, got %u", d.N);
+      return CUTB_ERR_INVALID;
+    }
+  }
+  if ((d.flags & CUTB_FLAG_A_RMSNORM) && !d.a_norm_weight) {
+    set_last_error("qgemv: CUTB_FLAG_A_RMSNORM without a_norm_weight");
+    return CUTB_ERR_INVALID;
   }
   const int amode = gv_amode(d);
   pl.overlap = !(d.flags & CUTB_FLAG_NO_OVERLAP);

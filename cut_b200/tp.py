@@ -61,28 +61,25 @@ def all_gather_rows(c_local: torch.Tensor, N: int, group=None) -> torch.Tensor:
     return out
 
 
-def _share(t: torch.Tensor):
-    """CUDA IPC handle of the tensor's storage (what torch.multiprocessing sends between processes)."""
-    return t.untyped_storage()._share_cuda_()
+PEER_HANDLE_BYTES = 64
 
 
-def _open(handle, local_device: int) -> torch.UntypedStorage:
-    """Maps a peer's allocation into THIS rank's device context.  The handle is opened with the
-    local device current (first field of the tuple), so the runtime enables peer access from the
-    local GPU to the owner lazily (cudaIpcMemLazyEnablePeerAccess) and the returned address is one
-    the local GPU's kernels may dereference.  (Opened under the owner's device index, as torch
-    does when it rebuilds a shared tensor, the mapping belongs to that device's context and a
-    local kernel faults on it unless peer access local -> owner was enabled by other means.)"""
-    return torch.UntypedStorage._new_shared_cuda(local_device, *handle[1:])
+class _RawCuda:
+    """A raw device allocation presented through __cuda_array_interface__, so that torch can view it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
 
 
 class ScatterGroup:
-    """Per-rank state of the fused exchange: `slots` full outputs [M, N] and one arrival counter,
-    each mapped into every other rank's address space (CUDA IPC; no multicast object is created).
+    """Per-rank state of the fused exchange: `slots` full outputs [M, N] and one arrival counter in
+    one device buffer that every other rank maps into its address space (cutb_peer_buffer_*: CUDA
+    IPC, opened with the local device current; no multicast object is created).
 
     Use: `launch(desc, peers(slot))` for every mat-vec of a step, then `exchange()` once;
     afterwards `out[slot]` holds every rank's slice.  The ranks must pass a step
     boundary of their own (e.g. `dist.barrier()`) before a slot is written again.
+    `close()` unmaps the peers' buffers and frees the own one (collective: every rank calls it).
     """
 
     def __init__(self, M: int, N: int, slots: int, device: torch.device, group=None):
@@ -92,32 +89,57 @@ class ScatterGroup:
         if not 2 <= self.world <= L.MAX_PEERS:
             raise ValueError(f"ScatterGroup needs 2..{L.MAX_PEERS} ranks, got {self.world}")
         self.M, self.N, self.slots = M, N, slots
+        self.device = device
         self.lo, self.hi = shard_rows(N, self.rank, self.world)
         # one allocation per rank: outputs first, the counter behind them on a 256-byte boundary
         out_bytes = (slots * M * N * 4 + 255) // 256 * 256
-        self.buf = torch.zeros(out_bytes + 256, dtype=torch.uint8, device=device)
+        self._bytes = out_bytes + 256
+        lib = L.lib()
+        own = C.c_void_p()
+        handle = C.create_string_buffer(PEER_HANDLE_BYTES)
+        with torch.cuda.device(device):
+            L.check(lib.cutb_peer_buffer_alloc(self._bytes, C.byref(own), handle))
+        self._own = own.value
+        self.buf = torch.as_tensor(_RawCuda(self._own, self._bytes), device=device)
         self.out = self.buf[: slots * M * N * 4].view(torch.float32).view(slots, M, N)
         self.flag = self.buf[out_bytes: out_bytes + 8].view(torch.int64)
-        torch.cuda.synchronize(device)
         handles = [None] * self.world
-        dist.all_gather_object(handles, _share(self.buf), group=group)
-        self._peer_storages = []
+        dist.all_gather_object(handles, (device.index, handle.raw), group=group)
+        self._opened = []
         self.peer_base = []
-        for r, h in enumerate(handles):
+        for r, (owner_dev, raw) in enumerate(handles):
             if r == self.rank:
-                self.peer_base.append(self.buf.data_ptr())
+                self.peer_base.append(self._own)
                 continue
-            if not torch.cuda.can_device_access_peer(device.index, h[0]):
-                raise RuntimeError(f"GPU {device.index} cannot access GPU {h[0]} as a peer")
-            st = _open(h, device.index)
-            self._peer_storages.append(st)
-            self.peer_base.append(st.data_ptr())
+            if not torch.cuda.can_device_access_peer(device.index, owner_dev):
+                raise RuntimeError(f"GPU {device.index} cannot access GPU {owner_dev} as a peer")
+            p = C.c_void_p()
+            with torch.cuda.device(device):
+                L.check(lib.cutb_peer_buffer_open(raw, C.byref(p)))
+            self._opened.append(p.value)
+            self.peer_base.append(p.value)
         torch.cuda.synchronize(device)
         self._flag_off = out_bytes
         self.steps = torch.zeros(1, dtype=torch.int64, device=device)  # waits made so far (device side)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._any_peers = self.peers(0)
         dist.barrier(group=group)
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers, then (after every rank has done so) frees the own buffer."""
+        if self._own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        lib = L.lib()
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                L.check(lib.cutb_peer_buffer_close(p))
+        self._opened = []
+        dist.barrier(group=self.group)  # nobody maps this rank's buffer any more
+        self.out = self.flag = self.buf = None
+        with torch.cuda.device(self.device):
+            L.check(lib.cutb_peer_buffer_free(self._own))
+        self._own = None
 
     def peers(self, slot: int) -> "L.PeerScatter":
         ps = L.PeerScatter()

@@ -41,7 +41,8 @@ enum {
   CUTB_ERR_UNSUPPORTED = 2, /* valid request no kernel covers */
   CUTB_ERR_CUDA = 3,        /* a CUDA runtime call failed (no device, launch error) */
   CUTB_ERR_WORKSPACE = 4,   /* workspace missing or smaller than cutb_qmatmul_workspace_bytes() */
-  CUTB_ERR_TIMEOUT = 5      /* a bounded device-side wait ran out (read from the status word) */
+  CUTB_ERR_TIMEOUT = 5,     /* a bounded device-side wait ran out (read from the status word) */
+  CUTB_ERR_RANGE = 6        /* an fp32 activation exceeded the fp16 operand range of the tensor-core GEMM (status word) */
 };
 
 /* GGUF block formats (interface/loader/gguf/gguf_types.hpp:109-150).  The matmul entry points
@@ -74,7 +75,8 @@ enum {
   CUTB_VARIANT_AUTO = -1,
   CUTB_VARIANT_GENERIC = 0, /* any shape, SIMT, exact fp32 dequant + FMA */
   CUTB_VARIANT_GEMV_MMA = 1, /* decode: bulk-copy ring + int8 warp MMA, M <= 16 (fp16 A) / 8 (fp32 A) */
-  CUTB_VARIANT_GEMM_TC = 2  /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory */
+  CUTB_VARIANT_GEMM_TC = 2  /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory; its operands are fp16
+                               (see the operand-range note at cutb_qmatmul_desc) */
 };
 
 /* Descriptor flags.
@@ -110,6 +112,16 @@ enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2, CUTB_FLAG_A_RMSNORM = 
  * D, C) + push constants {M, K, N, strideA, strideB, strideC, scaleStride}
  * (operators/impl/matmul/MatMulOp.cpp:507-575, MatMulQ4Common.cuh:22-30).
  * Strides are in elements (bytes for W planes), as in the reference.
+ *
+ * Operand range.  The generic and the decode variants dequantise exactly and take fp32
+ * activations at full range.  CUTB_VARIANT_GEMM_TC (what CUTB_VARIANT_AUTO picks above 8 fp32 /
+ * 16 fp16 activation rows over GGUF blocks) feeds the tensor cores fp16 operands, as the
+ * reference's tensor-core variants do (MatMulQ4CoopMatTiled.cu:37-75): fp32 activations are
+ * rounded to fp16 first, and a dequantised weight d * q (d * sc * q - dmin * m for Q4_K) is
+ * rounded to fp16 too.  |A| above 65504 therefore becomes infinity, and the launch records
+ * CUTB_ERR_RANGE in *status (the output then holds inf / NaN where such a value took part);
+ * weight products below 6e-8 flush to zero.  Callers whose activations can exceed the fp16
+ * range select CUTB_VARIANT_GENERIC, or scale A down and C up.  Accumulation and C are fp32.
  */
 typedef struct cutb_qmatmul_desc {
   int32_t format;      /* CUTB_Q8_0 / CUTB_Q4_0 / CUTB_Q4_K */
@@ -133,7 +145,8 @@ typedef struct cutb_qmatmul_desc {
   int32_t variant;     /* CUTB_VARIANT_* */
   void *workspace;     /* device scratch, >= cutb_qmatmul_workspace_bytes(desc), 256-byte aligned; may be NULL if that is 0 */
   uint64_t workspace_bytes;
-  int32_t *status;     /* optional device int: kernels store CUTB_ERR_TIMEOUT here if a bounded wait gives up */
+  int32_t *status;     /* optional device int: kernels store CUTB_ERR_TIMEOUT here if a bounded wait gives up,
+                          CUTB_ERR_RANGE if an activation left the tensor-core GEMM's fp16 operand range */
   uint32_t flags;      /* CUTB_FLAG_* */
   const float *a_norm_weight; /* CUTB_FLAG_A_RMSNORM: device, [K] fp32 */
   float a_norm_eps;           /* CUTB_FLAG_A_RMSNORM */
@@ -204,6 +217,28 @@ typedef struct cutb_peer_scatter {
 } cutb_peer_scatter;
 CUTB_API int cutb_qmatmul_scatter(const cutb_qmatmul_desc *desc, const cutb_peer_scatter *peers, void *stream);
 CUTB_API int cutb_peer_exchange(const cutb_peer_scatter *peers, uint64_t *step_counter, int *status, void *stream);
+
+/*
+ * Peer buffers of the fused exchange.  Every rank (one process per GPU) allocates ONE buffer for
+ * its full outputs and its arrival counter, exports a handle, sends the 64 handle bytes to the
+ * other ranks by any host channel, and opens theirs; the returned pointers are what
+ * cutb_peer_scatter's C_peers / flag_peers are built from.  (CUDA IPC underneath: no multicast
+ * object; the reference has no counterpart.)
+ *
+ *   cutb_peer_buffer_alloc   device memory on the current device, zero-filled, 256-byte aligned;
+ *                            `handle` receives the 64 bytes to send
+ *   cutb_peer_buffer_open    maps another rank's buffer into this process with the CURRENT device
+ *                            as the accessing device (peer access is enabled by the runtime); a
+ *                            handle exported by this same process is refused (use the pointer)
+ *   cutb_peer_buffer_close   unmaps an opened buffer; cutb_peer_buffer_free frees an own buffer.
+ *                            Close every mapping of a buffer before its owner frees it.
+ * These calls allocate and synchronise: set-up and tear-down only, never inside a stream capture.
+ */
+#define CUTB_PEER_HANDLE_BYTES 64
+CUTB_API int cutb_peer_buffer_alloc(uint64_t bytes, void **ptr, uint8_t handle[CUTB_PEER_HANDLE_BYTES]);
+CUTB_API int cutb_peer_buffer_open(const uint8_t handle[CUTB_PEER_HANDLE_BYTES], void **ptr);
+CUTB_API int cutb_peer_buffer_close(void *ptr);
+CUTB_API int cutb_peer_buffer_free(void *ptr);
 
 /*
  * Raw GGUF blocks -> fp32 [rows, cols] with row stride ldo (elements).

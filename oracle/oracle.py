@@ -16,6 +16,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libcutref.so")
+_REF_RUNNER_PATH = os.path.join(_HERE, "_ref", "libcutref_runner.so")
 
 Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 4, 5  # the last three: dequant operator only
 BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, BF16: 1}
@@ -28,7 +29,10 @@ def build(force: bool = False) -> None:
         os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "cut_oracle.c"))
     ):
         subprocess.run(["make", "-C", _HERE, "_build/liboracle.so"], check=True, capture_output=True)
-    subprocess.run(["make", "-C", _HERE, "ref"], check=True, capture_output=True)
+    # the reference helpers are rebuilt only where a checkout of the reference is named (REF_ROOT in the
+    # environment, else the place this build keeps it); elsewhere the prebuilt files are used as they are
+    ref_root = os.environ.get("REF_ROOT") or ("/root/reference" if os.path.isdir("/root/reference") else "")
+    subprocess.run(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root}"], check=True, capture_output=True)
 
 
 _lib = None
@@ -59,6 +63,49 @@ def lib() -> C.CDLL:
 
 def have_ref() -> bool:
     return os.path.exists(_REF_PATH)
+
+
+def have_ref_runner() -> bool:
+    return os.path.exists(_REF_RUNNER_PATH)
+
+
+_ref_runner = None
+
+
+def ref_runner() -> C.CDLL:
+    """The reference runner's own re-encoders (interface/runner/llama/llama.cpp:445-619), compiled from
+    its unmodified source: what the restatements in cut_oracle.c are pinned against."""
+    global _ref_runner
+    if _ref_runner is None:
+        _ref_runner = C.CDLL(_REF_RUNNER_PATH)
+        _ref_runner.cutref_runner_f32_to_f16.restype = C.c_uint16
+        _ref_runner.cutref_runner_f32_to_f16.argtypes = [C.c_float]
+        _ref_runner.cutref_runner_f16_to_f32.restype = C.c_float
+        _ref_runner.cutref_runner_f16_to_f32.argtypes = [C.c_uint16]
+        _ref_runner.cutref_runner_requant_q4k_affine.restype = C.c_int
+    return _ref_runner
+
+
+def ref_runner_quantize_rows_q8_0(x: np.ndarray):
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    values = np.empty(x.size, dtype=np.int8)
+    scales = np.empty(x.size // 32, dtype=np.uint16)
+    ref_runner().cutref_runner_quantize_rows_q8_0(_p(x), C.c_size_t(x.size), _p(values), _p(scales))
+    return values, scales
+
+
+def ref_runner_requant_q4k_affine(raw, N: int, K: int):
+    raw = _u8(raw)
+    packedT = np.empty((K, N // 2), dtype=np.uint8)
+    scalesT = np.empty((2 * (K // 32), N), dtype=np.uint16)
+    ps, ss = C.c_size_t(0), C.c_size_t(0)
+    rc = ref_runner().cutref_runner_requant_q4k_affine(_p(raw), C.c_size_t(raw.size), C.c_uint32(N), C.c_uint32(K), _p(packedT),
+                                                       C.c_size_t(packedT.size), _p(scalesT), C.c_size_t(scalesT.size),
+                                                       C.byref(ps), C.byref(ss))
+    if rc != 1:
+        raise ValueError(f"the reference declined the shape or the buffers were too small (rc {rc})")
+    assert ps.value == packedT.size and ss.value == scalesT.size
+    return packedT, scalesT
 
 
 def ref() -> C.CDLL:

@@ -327,6 +327,49 @@ void reusableCommandBuffer() {
   CHECK_THROWS(rt->iface().resubmit(ComputeHandle()), "not a reusable");
 }
 
+// A recorded command buffer keeps the scratch it was built on: record a split-K mat-vec (its partial
+// sums live in the backend's workspace), then run work that needs a much larger workspace (an fp32
+// prefill: the GEMM's fp16 copy of A), then replay the first command buffer and compare.
+void reusableSurvivesWorkspaceGrowth() {
+  const uint32_t K = 8192, N = 256;  // long K, few rows: the mat-vec splits K
+  std::vector<uint8_t> raw((size_t)N * (K / 32) * 18);
+  std::mt19937 gen(11);
+  for (auto &b : raw) b = (uint8_t)gen();
+  for (size_t blk = 0; blk < raw.size() / 18; ++blk) { uint16_t d = 0x2000; std::memcpy(&raw[blk * 18], &d, 2); }
+  std::vector<float> A(K);
+  for (uint32_t k = 0; k < K; ++k) A[k] = (float)((int)(gen() % 17) - 8) / 8.0f;
+  auto tA = rt->createTensor({K}, DataType::Float32, A.data());
+  auto tW = rt->createTensor({(uint32_t)raw.size()}, DataType::Int8, raw.data());
+  auto tC = rt->ops().matmulBlocks(tA, tW, DequantFormat::Q4_0, N);
+  ComputeHandle cb = rt->iface().submitReusable();
+  rt->iface().wait(cb);
+  std::vector<float> out1(N), out2(N), want(N);
+  rt->copyFromTensor(tC, out1.data(), N * sizeof(float));
+  orc_qmatmul_blocks(1, A.data(), raw.data(), want.data(), nullptr, 1, K, N, N, 0, 0, 0);
+  double num = 0, den = 0;
+  for (uint32_t n = 0; n < N; ++n) num += (out1[n] - want[n]) * (double)(out1[n] - want[n]), den += want[n] * (double)want[n];
+  CHECK(std::sqrt(num / den) <= 1e-3);
+  {  // 64 fp32 rows x K = 4096: the tensor-core GEMM asks for 2 * M * K bytes, far more than the mat-vec's partial sums
+    const uint32_t M2 = 64, K2 = 4096, N2 = 128;
+    std::vector<uint8_t> raw2((size_t)N2 * (K2 / 32) * 18);
+    for (auto &b : raw2) b = (uint8_t)gen();
+    for (size_t blk = 0; blk < raw2.size() / 18; ++blk) { uint16_t d = 0x2000; std::memcpy(&raw2[blk * 18], &d, 2); }
+    std::vector<float> A2((size_t)M2 * K2, 0.25f);
+    auto tA2 = rt->createTensor({M2, K2}, DataType::Float32, A2.data());
+    auto tW2 = rt->createTensor({(uint32_t)raw2.size()}, DataType::Int8, raw2.data());
+    auto tC2 = rt->ops().matmulBlocks(tA2, tW2, DequantFormat::Q4_0, N2);
+    ComputeHandle h = rt->iface().submit();
+    rt->iface().wait(h);
+  }
+  std::fill(out2.begin(), out2.end(), -1.0f);
+  rt->iface().resubmit(cb);
+  rt->iface().wait(cb);
+  rt->copyFromTensor(tC, out2.data(), N * sizeof(float));
+  int bad = 0;
+  for (uint32_t n = 0; n < N; ++n) bad += (out1[n] != out2[n]);
+  CHECK(bad == 0);
+}
+
 void errorBehaviour() {
   auto a = rt->createTensor({64}, DataType::Float32);
   auto b = rt->createTensor({32, 16}, DataType::Int8);
@@ -581,6 +624,7 @@ int main() {
     RUN(transposeQ4NibbleBitExact);
     RUN(blocksEntryPoint);
     RUN(reusableCommandBuffer);
+    RUN(reusableSurvivesWorkspaceGrowth);
     RUN(errorBehaviour);
     RUN(rmsNormCases);
     RUN(argReduceCases);

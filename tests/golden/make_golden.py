@@ -10,7 +10,11 @@ gguf_reader.cpp, (2) pushes hand-crafted edge-case blocks and seeded random
 blocks of Q8_0 / Q4_0 / Q4_K (and Q5_K / Q6_K / BF16, which only the dequant
 operator takes) through the reference's GGUFReader and stores the
 raw bytes next to the float32 bit patterns and separated planes it returned,
-and (3) stores the mt19937 activation vectors of the reference's own tests.
+(3) stores the mt19937 activation vectors of the reference's own tests, and
+(4) builds oracle/_ref/libcutref_runner.so (the reference runner's translation
+unit, reached through oracle/ref_runner_shim.cpp) and stores what its file-static
+re-encoders return: float -> half conversions of edge values, Q8_0 quantisation of
+seeded rows, and the affine re-encode of Q4_K tensors.
 """
 from __future__ import annotations
 
@@ -134,6 +138,34 @@ def main() -> None:
             vals, scales = O.ref_separate(fmt, r, rows, cols)
             out[f"{name}_rand_sep_values"] = vals.view(np.uint8)
             out[f"{name}_rand_sep_scales"] = scales
+
+    # (4) the runner's re-encoders (interface/runner/llama/llama.cpp:445-619), run from the reference's own source
+    assert O.have_ref_runner(), "the runner shim was not built; cannot regenerate its fixtures"
+    rr = O.ref_runner()
+    edge_f32 = np.array([0.0, -0.0, 1.0, -1.0, 65504.0, 65519.9, 65520.0, 1e5, -1e5, 6.1035156e-05, 6.0975552e-05, 5.9604645e-08,
+                         2.9802322e-08, 2.9802326e-08, 1e-8, 0.1, 0.33333334, 1.0009766, 1.0004883, 1.0014648, 2047.5, 2048.5,
+                         np.inf, -np.inf, 3.1415927, 1e-5, 7.5e-5, 0.00012207031], dtype=np.float32)
+    rng = np.random.default_rng(4242)
+    rand_f32 = np.concatenate([edge_f32, (rng.standard_normal(2000) * np.exp(rng.uniform(-18, 11, 2000))).astype(np.float32)])
+    out["runner_f32_in"] = rand_f32
+    out["runner_f32_to_f16"] = np.array([rr.cutref_runner_f32_to_f16(float(v)) for v in rand_f32], dtype=np.uint16)
+    halves = np.concatenate([np.array(EDGE_D + [0x7C00, 0xFC00, 0x7E00], dtype=np.uint16), rng.integers(0, 65536, 1000).astype(np.uint16)])
+    out["runner_f16_in"] = halves
+    out["runner_f16_to_f32_bits"] = np.array([rr.cutref_runner_f16_to_f32(int(h)) for h in halves], dtype=np.float32).view(np.uint32)
+    x = (rng.standard_normal(64 * 32) * np.repeat(np.exp(rng.uniform(-12, 6, 64)), 32)).astype(np.float32)
+    x[:32] = 0.0                       # an all-zero block: d = 0, id = 0
+    x[32:64] = np.linspace(-1, 1, 32)  # ties of lroundf at +-0.5 steps of d
+    x[64:96] = 127.0
+    qv, qs = O.ref_runner_quantize_rows_q8_0(x)
+    out["runner_q8_in"], out["runner_q8_values"], out["runner_q8_scales"] = x, qv.view(np.uint8), qs
+    for tag, (n, k, seed) in {"a": (8, 512, 77), "b": (34, 256, 78)}.items():
+        rawk = synth.make_weights(synth.Q4_K, n, k, seed=seed)
+        if tag == "b":  # the edge-case super-blocks of the dequant fixtures in front (subnormal d / dmin, 6-bit extremes)
+            e = edge_q4_k()
+            rawk[: e.size] = e
+        pt, st = O.ref_runner_requant_q4k_affine(rawk, n, k)
+        out[f"runner_requant_{tag}_raw"], out[f"runner_requant_{tag}_shape"] = rawk, np.array([n, k], dtype=np.int64)
+        out[f"runner_requant_{tag}_packed"], out[f"runner_requant_{tag}_scales"] = pt, st
 
     exe = os.path.join("/tmp", "gen_testdata")
     subprocess.run(["g++", "-O2", "-std=c++17", "-o", exe, os.path.join(HERE, "gen_testdata.cpp")], check=True)

@@ -63,3 +63,39 @@ def test_exchange_wait_runs_out_instead_of_hanging():
     assert flags[0].item() == 1 and flags[32].item() == 1 and steps.item() == 1
     # the context still works
     assert float((out + 1).sum().item()) == 16.0
+
+
+@pytest.mark.gpu
+def test_scatter_refuses_paired_rows_before_launching():
+    """cutb_qmatmul_scatter shares the mat-vec's flag guards: paired gate/up rows cannot be scattered
+    (the slice would go to desc->C and the peers would get nothing), so the call is refused and
+    nothing is launched.  One GPU is enough: the refusal comes before any peer pointer is used."""
+    import ctypes as C
+
+    import numpy as np
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    sys.path.insert(0, ROOT)
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    dev = torch.device("cuda", 0)
+    K, N = 4096, 256
+    A = torch.from_numpy(synth.make_activations(1, K, 3, np.float16)).to(dev)
+    W = torch.from_numpy(synth.make_weights(synth.Q4_0, N, K, seed=4)).to(dev)
+    out = torch.full((1, 2 * N), 5.0, dtype=torch.float32, device=dev)
+    flags = torch.zeros(64, dtype=torch.int64, device=dev)
+    c_dummy = torch.zeros((1, N), dtype=torch.float32, device=dev)
+    d, _, keep = ops.make_desc(A, W, synth.Q4_0, N, C_out=c_dummy, variant=L.VARIANT_GEMV_MMA)
+    d.flags = L.FLAG_GLU_PAIRS
+    d.fusion_type, d.fusion_op = L.FUSION_UNARY, 133
+    ps = L.PeerScatter()
+    ps.world, ps.rank, ps.ldc_total, ps.n_offset = 2, 0, 2 * N, 0
+    for r in range(2):
+        ps.C_peers[r] = out.data_ptr()
+        ps.flag_peers[r] = flags.data_ptr() + 256 * r
+    rc = L.lib().cutb_qmatmul_scatter(C.byref(d), C.byref(ps), None)
+    assert rc == L.ERR_UNSUPPORTED and b"paired gate/up" in L.lib().cutb_last_error()
+    torch.cuda.synchronize()
+    assert bool((out == 5.0).all()) and bool((c_dummy == 0).all())

@@ -216,3 +216,51 @@ def test_rmsnorm_and_embedding_checker():
     assert np.allclose(y, 2.0 * x / np.sqrt(np.mean(x ** 2)), rtol=1e-6)
     table = np.arange(40, dtype=np.float32).reshape(5, 8)
     assert np.array_equal(O.embedding(np.array([4, 0, 4], np.uint32), table), table[[4, 0, 4]])
+
+
+# ---- the runner's weight re-encoders (interface/runner/llama/llama.cpp:445-619): the restatements are pinned
+# ---- against fixtures that the reference's own functions produced, and against those functions when present
+def test_runner_half_conversions_match_golden(golden):
+    got = np.array([O.f32_to_f16_runner(float(v)) for v in golden["runner_f32_in"]], dtype=np.uint16)
+    assert np.array_equal(got, golden["runner_f32_to_f16"])
+    back = O.f16_to_f32(golden["runner_f16_in"]).view(np.uint32)
+    want = golden["runner_f16_to_f32_bits"]
+    nan = (want & 0x7FFFFFFF) > 0x7F800000  # NaN payloads are not part of the contract
+    assert np.array_equal(back[~nan], want[~nan]) and np.all((back[nan] & 0x7FFFFFFF) > 0x7F800000)
+
+
+def test_runner_q8_0_quantisation_matches_golden(golden):
+    vals, scales = O.quantize_rows_q8_0(golden["runner_q8_in"])
+    assert np.array_equal(vals.view(np.uint8), golden["runner_q8_values"])
+    assert np.array_equal(scales, golden["runner_q8_scales"])
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_runner_q4k_affine_reencode_matches_golden(golden, tag):
+    n, k = (int(v) for v in golden[f"runner_requant_{tag}_shape"])
+    packed, scales = O.requant_q4k_affine(golden[f"runner_requant_{tag}_raw"], n, k)
+    assert np.array_equal(packed, golden[f"runner_requant_{tag}_packed"])
+    assert np.array_equal(scales, golden[f"runner_requant_{tag}_scales"])
+
+
+@pytest.mark.skipif(not O.have_ref_runner(), reason="the reference runner helper was not built here")
+def test_runner_restatements_match_compiled_reference():
+    rr = O.ref_runner()
+    rng = np.random.default_rng(99)
+    xs = (rng.standard_normal(20000) * np.exp(rng.uniform(-20, 12, 20000))).astype(np.float32)
+    assert all(O.f32_to_f16_runner(float(v)) == rr.cutref_runner_f32_to_f16(float(v)) for v in xs)
+    hs = np.arange(0, 65536, 7, dtype=np.uint16)
+    mine = O.f16_to_f32(hs).view(np.uint32)
+    ref = np.array([rr.cutref_runner_f16_to_f32(int(h)) for h in hs], dtype=np.float32).view(np.uint32)
+    nan = (ref & 0x7FFFFFFF) > 0x7F800000
+    assert np.array_equal(mine[~nan], ref[~nan])
+    x = (rng.standard_normal(512 * 32) * np.repeat(np.exp(rng.uniform(-14, 8, 512)), 32)).astype(np.float32)
+    v0, s0 = O.quantize_rows_q8_0(x)
+    v1, s1 = O.ref_runner_quantize_rows_q8_0(x)
+    assert np.array_equal(v0, v1) and np.array_equal(s0, s1)
+    from cut_b200 import synth
+
+    raw = synth.make_weights(synth.Q4_K, 64, 1024, seed=5)
+    p0, q0 = O.requant_q4k_affine(raw, 64, 1024)
+    p1, q1 = O.ref_runner_requant_q4k_affine(raw, 64, 1024)
+    assert np.array_equal(p0, p1) and np.array_equal(q0, q1)

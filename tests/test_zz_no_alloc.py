@@ -77,9 +77,9 @@ def test_noalloc_rejects_what_it_cannot_hold():
     d, keep = _desc(A, W, synth.Q4_0, N, out)
     from cut_b200 import ops
 
-    if ops.workspace_bytes(d) > 4 << 20:
-        assert lib.cutb_qmatmul_decode_noalloc(C.byref(d), stream) == L.ERR_WORKSPACE
-        assert b"built-in array" in lib.cutb_last_error()
+    assert ops.workspace_bytes(d) > 4 << 20  # the precondition of this case: the shape needs more than the array holds
+    assert lib.cutb_qmatmul_decode_noalloc(C.byref(d), stream) == L.ERR_WORKSPACE
+    assert b"built-in array" in lib.cutb_last_error()
     # prefill-sized batches are not decode mat-vecs
     A2 = dev(synth.make_activations(64, 256, 1, np.float16))
     W2 = dev(synth.make_weights(synth.Q4_0, 16, 256, seed=2))
@@ -87,3 +87,29 @@ def test_noalloc_rejects_what_it_cannot_hold():
     d2, keep2 = _desc(A2, W2, synth.Q4_0, 16, out2)
     assert lib.cutb_qmatmul_decode_noalloc(C.byref(d2), stream) == L.ERR_UNSUPPORTED
     assert lib.cutb_qmatmul_decode_noalloc(None, stream) == L.ERR_INVALID
+
+
+def test_noalloc_rejects_flag_combinations_the_kernel_cannot_run():
+    """The flag guards of cutb_qmatmul hold for this entry point too: paired gate/up rows on a shape that
+    splits K, and a fused RMSNorm without its weight, are refused before anything is launched."""
+    import torch
+
+    from cut_b200 import ops
+
+    lib = L.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    M, K, N = 1, 28672, 1024  # splits K
+    A = torch.zeros((M, K), dtype=torch.float16, device="cuda")
+    W = torch.zeros(N * synth.row_bytes(synth.Q4_0, K), dtype=torch.uint8, device="cuda")
+    out = torch.full((M, N), 7.0, dtype=torch.float32, device="cuda")
+    d, keep = _desc(A, W, synth.Q4_0, N, out)
+    assert ops.workspace_bytes(d) > 0
+    d.flags = L.FLAG_GLU_PAIRS
+    d.fusion_type, d.fusion_op = L.FUSION_UNARY, 133
+    assert lib.cutb_qmatmul_decode_noalloc(C.byref(d), stream) == L.ERR_UNSUPPORTED
+    assert b"paired gate/up" in lib.cutb_last_error()
+    d.flags = L.FLAG_A_RMSNORM  # a_norm_weight stays null
+    d.fusion_type, d.fusion_op = 0, 0
+    assert lib.cutb_qmatmul_decode_noalloc(C.byref(d), stream) == L.ERR_INVALID
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all())  # nothing ran
