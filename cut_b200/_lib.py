@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libcutb.so")
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT, ERR_RANGE = range(7)
-Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 4, 5  # the last three: cutb_dequant only
+Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16, Q4_1, Q5_0 = 0, 1, 2, 3, 4, 5, 6, 7  # from Q5_K on: cutb_dequant only
 F32, F16 = 0, 1
 LAYOUT_GGUF_BLOCKS, LAYOUT_KN_PLANES = 0, 1
 FUSION_NONE, FUSION_UNARY, FUSION_BINARY = 0, 1, 2
@@ -26,7 +26,7 @@ EXPORTS = [
     "cutb_qmatmul_workspace_bytes", "cutb_qmatmul_select_variant", "cutb_qmatmul", "cutb_qmatmul_decode_noalloc",
     "cutb_qmatmul_scatter", "cutb_peer_exchange",
     "cutb_peer_buffer_alloc", "cutb_peer_buffer_open", "cutb_peer_buffer_close", "cutb_peer_buffer_free",
-    "cutb_rmsnorm", "cutb_embedding", "cutb_argreduce",
+    "cutb_rmsnorm", "cutb_embedding", "cutb_embedding_col", "cutb_embedding_blocks", "cutb_argreduce",
     "cutb_rope_kv_write", "cutb_attention_workspace_bytes", "cutb_attention_decode", "cutb_rope_attention_decode",
     "cutb_batched_kv_write", "cutb_batched_attention", "cutb_glu_pairs",
     "cutb_dequant", "cutb_separate_blocks", "cutb_transpose_2d", "cutb_requant_q4k_affine", "cutb_quantize_rows_q8_0",
@@ -105,6 +105,12 @@ def lib() -> C.CDLL:
         l.cutb_rmsnorm.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64, C.c_float, C.c_void_p]
         l.cutb_embedding.restype = C.c_int
         l.cutb_embedding.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+        l.cutb_embedding_col.restype = C.c_int
+        l.cutb_embedding_col.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                         C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+        l.cutb_embedding_blocks.restype = C.c_int
+        l.cutb_embedding_blocks.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                            C.c_void_p, C.c_void_p]
         l.cutb_argreduce.restype = C.c_int
         l.cutb_argreduce.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]
         l.cutb_rope_kv_write.restype = C.c_int

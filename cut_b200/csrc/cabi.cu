@@ -375,6 +375,41 @@ int cutb_embedding(const uint32_t *indices, const float *table, float *out, uint
   return embedding_launch(indices, table, out, n, dim, vocab, status, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cutb_embedding_col(int format, const uint32_t *indices, const void *matrix, const void *scales, float *out, uint32_t n,
+                       uint32_t dim, uint32_t vocab, uint32_t vocab_stride, uint32_t scale_stride, uint32_t out_stride, int *status,
+                       void *stream) {
+  if (n == 0 || dim == 0) return CUTB_OK;
+  if (format != 0 && format != 1) {
+    set_last_error("embedding_col: format must be 0 (fp16 matrix) or 1 (int8 values + fp16 scales)");
+    return CUTB_ERR_INVALID;
+  }
+  if (!indices || !matrix || !out || (format == 1 && !scales)) {
+    set_last_error("embedding_col: null pointer");
+    return CUTB_ERR_INVALID;
+  }
+  if (vocab_stride < vocab || out_stride < dim || (format == 1 && scale_stride < vocab) ||
+      (format == 0 && reinterpret_cast<uintptr_t>(matrix) % 2) || (format == 1 && reinterpret_cast<uintptr_t>(scales) % 2)) {
+    set_last_error("embedding_col: a stride is shorter than its row, or an fp16 pointer is misaligned");
+    return CUTB_ERR_INVALID;
+  }
+  return embedding_col_launch(format, indices, matrix, scales, out, n, dim, vocab, vocab_stride, scale_stride, out_stride, status,
+                              reinterpret_cast<cudaStream_t>(stream));
+}
+
+int cutb_embedding_blocks(int format, const uint32_t *indices, const void *raw, float *out, uint32_t n, uint32_t rows, uint32_t cols,
+                          uint32_t ldo, int *status, void *stream) {
+  if (n == 0 || cols == 0) return CUTB_OK;
+  if (format < CUTB_Q8_0 || format > CUTB_Q5_0) {
+    set_last_error("embedding_blocks: unknown block format %d", format);
+    return CUTB_ERR_INVALID;
+  }
+  if (!indices || !raw || !out || ldo < cols || cols % block_elems(format) != 0) {
+    set_last_error("embedding_blocks: null pointer, ldo < cols, or cols not a whole number of blocks");
+    return CUTB_ERR_INVALID;
+  }
+  return dequant_gather_launch(format, indices, raw, out, n, rows, cols, ldo, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int cutb_argreduce(int is_max, const float *values, float *out, uint32_t n, void *stream) {
   if (!out || (n && !values)) {
     set_last_error("argreduce: null pointer");
@@ -459,7 +494,7 @@ int cutb_rope_attention_decode(int kv_dtype, const float *q, const float *k, con
 
 int cutb_dequant(int format, const void *raw, uint64_t raw_bytes, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                  void *stream) {
-  if (format < CUTB_Q8_0 || format > CUTB_BF16) {
+  if (format < CUTB_Q8_0 || format > CUTB_Q5_0) {
     set_last_error("dequant: unknown format %d", format);
     return CUTB_ERR_INVALID;
   }

@@ -27,7 +27,8 @@ __host__ __device__ constexpr uint32_t block_elems(int fmt) {
   return (fmt == CUTB_Q4_K || fmt == CUTB_Q5_K || fmt == CUTB_Q6_K) ? 256u : (fmt == CUTB_BF16 ? 1u : 32u);
 }
 __host__ __device__ constexpr uint32_t block_bytes(int fmt) {
-  return fmt == CUTB_Q8_0 ? 34u : fmt == CUTB_Q4_0 ? 18u : fmt == CUTB_Q4_K ? 144u : fmt == CUTB_Q5_K ? 176u : fmt == CUTB_Q6_K ? 210u : 2u;
+  return fmt == CUTB_Q8_0 ? 34u : fmt == CUTB_Q4_0 ? 18u : fmt == CUTB_Q4_K ? 144u : fmt == CUTB_Q5_K ? 176u : fmt == CUTB_Q6_K ? 210u
+         : fmt == CUTB_Q4_1 ? 20u : fmt == CUTB_Q5_0 ? 22u : 2u;
 }
 // Bytes of 256 consecutive weights of one row: the copy granule of the decode
 // kernel (a multiple of 16 bytes in all three formats).

@@ -2,8 +2,8 @@
 //
 // Replaces the reference's dequant kernels (operators/impl/dequant/DequantQ4K.cu:6-50,
 // DequantQ5K.cu, DequantQ6K.cu, DequantBF16.cu, helpers DequantCommon.cuh:16-70) and
-// adds the Q8_0 / Q4_0 cases the reference only has on the CPU
-// (interface/loader/gguf/gguf_reader.cpp:541-572, 826-850).  Every format follows the
+// adds the Q8_0 / Q4_0 / Q4_1 / Q5_0 cases the reference only has on the CPU
+// (interface/loader/gguf/gguf_reader.cpp:541-660, 826-850).  Every format follows the
 // loader's dequantiser operation by operation (each product and the subtract rounded on
 // their own), so the output equals its float32 bits.
 //
@@ -106,6 +106,29 @@ template <int FMT> __device__ __forceinline__ void decode8(const uint8_t *b, uin
       v[i] = (float)(int8_t)((w0 >> (8 * i)) & 0xFF) * d;
       v[4 + i] = (float)(int8_t)((w1 >> (8 * i)) & 0xFF) * d;
     }
+  } else if constexpr (FMT == CUTB_Q4_1) {
+    // gguf_reader.cpp:574-611: value = float(nibble) * d + m, the product and the sum rounded on their own
+    const float d = h2f_bits(ldg16(b)), m = h2f_bits(ldg16(b + 2));
+    const uint32_t sh = (oct >> 1) * 4;
+    const uint32_t w0 = ldg32u(b + 4 + 8 * (oct & 1)), w1 = ldg32u(b + 8 + 8 * (oct & 1));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[i] = __fadd_rn(__fmul_rn((float)((w0 >> (8 * i + sh)) & 0xF), d), m);
+      v[4 + i] = __fadd_rn(__fmul_rn((float)((w1 >> (8 * i + sh)) & 0xF), d), m);
+    }
+  } else if constexpr (FMT == CUTB_Q5_0) {
+    // gguf_reader.cpp:613-660: nibbles as Q4_0, bit e of qh is element e's fifth bit; value = float(q5 - 16) * d
+    const float d = h2f_bits(ldg16(b));
+    const uint32_t qh = ldg16(b + 2) | (ldg16(b + 4) << 16);
+    const uint32_t sh = (oct >> 1) * 4, e0 = 8 * oct;
+    const uint32_t w0 = ldg32u(b + 6 + 8 * (oct & 1)), w1 = ldg32u(b + 10 + 8 * (oct & 1));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int q0 = (int)(((w0 >> (8 * i + sh)) & 0xF) | (((qh >> (e0 + i)) & 1u) << 4)) - 16;
+      const int q1 = (int)(((w1 >> (8 * i + sh)) & 0xF) | (((qh >> (e0 + 4 + i)) & 1u) << 4)) - 16;
+      v[i] = (float)q0 * d;
+      v[4 + i] = (float)q1 * d;
+    }
   } else if constexpr (FMT == CUTB_Q4_0) {
     const float d = h2f_bits(ldg16(b));
     // elements 8*oct.. live in bytes (8*oct & 15).. ; low nibbles for oct < 2, high for oct >= 2
@@ -162,7 +185,71 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t *__restrict_
   }
 }
 
+// Row gather with dequantisation: out[i, :] = dequant(row indices[i]) -- the embedding lookup when the
+// (tied) table is kept as raw GGUF blocks, one row per token.  A row index >= rows writes zeros and
+// reports through *status.
+template <int FMT>
+__global__ void __launch_bounds__(256) dequant_gather_kernel(const uint32_t *__restrict__ indices, const uint8_t *__restrict__ raw,
+                                                             float *__restrict__ out, uint32_t n, uint32_t rows, uint32_t cols,
+                                                             uint32_t ldo, uint64_t row_bytes_, int vec_ok, int *status) {
+  constexpr uint32_t BE = block_elems(FMT), BB = block_bytes(FMT);
+  const uint32_t octs_per_row = (cols + 7) / 8;
+  for (uint32_t i = blockIdx.y; i < n; i += gridDim.y) {
+    const uint32_t r = __ldg(indices + i);
+    if (r >= rows && threadIdx.x == 0 && blockIdx.x == 0 && status) atomicExch(status, (int)CUTB_ERR_INVALID);
+    for (uint32_t o = blockIdx.x * blockDim.x + threadIdx.x; o < octs_per_row; o += gridDim.x * blockDim.x) {
+      const uint32_t k = o * 8;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (r < rows) decode8<FMT>(raw + (uint64_t)r * row_bytes_ + (uint64_t)(k / BE) * BB, (k % BE) / 8, v, cols - k);
+      float *dst = out + (uint64_t)i * ldo + k;
+      if (vec_ok && k + 8 <= cols) {
+        *reinterpret_cast<float4 *>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        *(reinterpret_cast<float4 *>(dst) + 1) = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (k + e < cols) dst[e] = v[e];
+      }
+    }
+  }
+}
+
 }  // namespace
+
+int dequant_gather_launch(int format, const uint32_t *indices, const void *raw, float *out, uint32_t n, uint32_t rows, uint32_t cols,
+                          uint32_t ldo, int *status, cudaStream_t stream) {
+  if (n == 0 || cols == 0) return CUTB_OK;
+  if ((format == CUTB_Q4_K || format == CUTB_Q5_K) && (reinterpret_cast<uintptr_t>(raw) % 4 != 0)) {
+    set_last_error("embedding_blocks: Q4_K / Q5_K blocks must be 4-byte aligned");
+    return CUTB_ERR_INVALID;
+  }
+  if ((format == CUTB_Q4_K || format == CUTB_Q5_K || format == CUTB_Q6_K) && cols % 256 != 0) {
+    set_last_error("embedding_blocks: K-quant rows are whole 256-weight super-blocks, cols = %u", cols);
+    return CUTB_ERR_INVALID;
+  }
+  if (format == CUTB_BF16 && (reinterpret_cast<uintptr_t>(raw) % 2 != 0)) {
+    set_last_error("embedding_blocks: BF16 input must be 2-byte aligned");
+    return CUTB_ERR_INVALID;
+  }
+  uint32_t gx = ((cols + 7) / 8 + 255) / 256;
+  if (gx > 64) gx = 64;
+  const dim3 g(gx, n < 65535u ? n : 65535u);
+  const int vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (ldo % 4 == 0);
+  const uint8_t *r = reinterpret_cast<const uint8_t *>(raw);
+  const uint64_t rb = row_bytes(format, cols);
+  switch (format) {
+    case CUTB_Q8_0: dequant_gather_kernel<CUTB_Q8_0><<<g, 256, 0, stream>>>(indices, r, out, n, rows, cols, ldo, rb, vec_ok, status); break;
+    case CUTB_Q4_0: dequant_gather_kernel<CUTB_Q4_0><<<g, 256, 0, stream>>>(indices, r, out, n, rows, cols, ldo, rb, vec_ok, status); break;
+    case CUTB_Q5_K: dequant_gather_kernel<CUTB_Q5_K><<<g, 256, 0, stream>>>(indices, r, out, n, rows, cols, ldo, rb, vec_ok, status); break;
+    case CUTB_Q6_K: dequant_gather_kernel<CUTB_Q6_K><<<g, 256, 0, stream>>>(indices, r, out, n, rows, cols, ldo, rb, vec_ok, status); break;
+    case CUTB_BF16: dequant_gather_kernel<CUTB_BF16><<<g, 256, 0, stream>>>(indices, r, out, n, rows, cols, ldo, rb, vec_ok, status); break;
+    case CUTB_Q4_1: dequant_gather_kernel<CUTB_Q4_1><<<g, 256, 0, stream>>>(indices, r, out, n, rows, cols, ldo, rb, vec_ok, status); break;
+    case CUTB_Q5_0: dequant_gather_kernel<CUTB_Q5_0><<<g, 256, 0, stream>>>(indices, r, out, n, rows, cols, ldo, rb, vec_ok, status); break;
+    default: dequant_gather_kernel<CUTB_Q4_K><<<g, 256, 0, stream>>>(indices, r, out, n, rows, cols, ldo, rb, vec_ok, status); break;
+  }
+  CUTB_CUDA_TRY(cudaGetLastError());
+  return CUTB_OK;
+}
 
 int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                    cudaStream_t stream) {
@@ -201,6 +288,8 @@ int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint3
     case CUTB_Q5_K: dequant_kernel<CUTB_Q5_K><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
     case CUTB_Q6_K: dequant_kernel<CUTB_Q6_K><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
     case CUTB_BF16: dequant_kernel<CUTB_BF16><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    case CUTB_Q4_1: dequant_kernel<CUTB_Q4_1><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
+    case CUTB_Q5_0: dequant_kernel<CUTB_Q5_0><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
     default: dequant_kernel<CUTB_Q4_K><<<g, 256, 0, stream>>>(r, out, rows, cols, ldo, rb, vec_ok); break;
   }
   CUTB_CUDA_TRY(cudaGetLastError());

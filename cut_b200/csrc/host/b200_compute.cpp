@@ -83,6 +83,8 @@ int cutbFormat(uint32_t f) {
     case DequantFormat::Q5_K: return CUTB_Q5_K;  // dequant only; the matmul entry point rejects them
     case DequantFormat::Q6_K: return CUTB_Q6_K;
     case DequantFormat::BF16: return CUTB_BF16;
+    case DequantFormat::Q4_1: return CUTB_Q4_1;
+    case DequantFormat::Q5_0: return CUTB_Q5_0;
     default: throw std::runtime_error("B200Compute: block format has no kernel");
   }
 }
@@ -206,7 +208,7 @@ public:
     if (!desc) throw std::runtime_error("B200Compute: not a kernel descriptor");
     switch (desc->op) {
       case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case TransposeQ4: break;
-      case RMSNorm: case Embedding: case ReduceArgmax: case ReduceArgmin: case Attention: break;
+      case RMSNorm: case Embedding: case EmbeddingCol: case ReduceArgmax: case ReduceArgmin: case Attention: break;
       case CacheWrite:
         if (desc->variant != FusedRoPEKVWriteOpNode::kVariant && desc->variant != BatchedKVCacheWriteOpNode::kVariant) throw std::runtime_error("B200Compute: no kernel for this CacheWrite operator");
         break;
@@ -431,6 +433,14 @@ private:
         const DeviceBuffer &idx = buf(d, 0), &table = buf(d, 1), &out = buf(d, 2);
         cutbCheck(cutb_embedding((const uint32_t *)idx.data, (const float *)table.data, (float *)out.data, pc.numIndices,
                                  pc.embDim, table.getShape()[0], status_, stream_), "Embedding");
+      } else if (k.op == EmbeddingCol) {
+        struct PC {
+          uint32_t numIndices, embDim, vocabStride, scaleStride, outStride;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &idx = buf(d, 0), &mat = buf(d, 1), &sc = buf(d, 2), &out = buf(d, 3);
+        cutbCheck(cutb_embedding_col((int)k.fusionType, (const uint32_t *)idx.data, mat.data, sc.data, (float *)out.data, pc.numIndices,
+                                     pc.embDim, mat.getShape()[1], pc.vocabStride, pc.scaleStride, pc.outStride, status_, stream_),
+                  "EmbeddingCol");
       } else if (k.op == CacheWrite && k.variant == BatchedKVCacheWriteOpNode::kVariant) {
         struct PC {
           uint32_t batchSize, kvDim, alignedKvDim, headDim, halfDim, kStride, vStride, kOffset, vOffset;

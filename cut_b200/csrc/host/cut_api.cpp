@@ -414,9 +414,9 @@ size_t DequantOpNode::shaderKey() const {
 }
 
 std::optional<std::vector<uint32_t>> DequantOpNode::shader() const {
-  switch (format_) {  // the reference's DequantFormat set plus the two 32-weight block formats
+  switch (format_) {  // the reference's DequantFormat set plus the 32-weight block formats
     case DequantFormat::BF16: case DequantFormat::Q4_K: case DequantFormat::Q5_K: case DequantFormat::Q6_K:
-    case DequantFormat::Q8_0: case DequantFormat::Q4_0: break;
+    case DequantFormat::Q8_0: case DequantFormat::Q4_0: case DequantFormat::Q4_1: case DequantFormat::Q5_0: break;
     default: return std::nullopt;
   }
   KernelDesc d;
@@ -539,6 +539,48 @@ std::vector<uint8_t> EmbeddingOpNode::pushConstants() const {
   struct {
     uint32_t numIndices, embDim;
   } pc{numIndices_, embDim_};
+  return toBytes(pc);
+}
+
+EmbeddingColOpNode::EmbeddingColOpNode(TensorStore &store, const Tensor &indices, const Tensor &matrix, const Tensor &scales,
+                                       const Tensor &preallocOutput, std::optional<uint32_t> spec)
+    : OpNode(EmbeddingCol, store, spec) {
+  const auto &bi = store.getTensor(indices);
+  const auto &bm = store.getTensor(matrix);
+  const auto &bs = store.getTensor(scales);
+  if (bm.getShape().size() != 2) throw std::runtime_error("embeddingCol: matrix must be 2D [dim, vocab]");
+  embDim_ = bm.getShape()[0];
+  vocabStride_ = (bm.getShape()[1] + 3) & ~3u;
+  scaleStride_ = bs.getShape().size() == 2 ? ((bs.getShape()[1] + 3) & ~3u) : vocabStride_;
+  outStride_ = (embDim_ + 3) & ~3u;
+  for (uint32_t d : bi.getShape()) numIndices_ *= d;
+  format_ = bm.getDtype() == DataType::Int8 ? 1 : 0;
+  if (bm.getDtype() != DataType::Float16 && bm.getDtype() != DataType::Int8)
+    throw std::runtime_error("embeddingCol: matrix must be Float16 or Int8");
+  outShape_ = bi.getShape();
+  outShape_.push_back(embDim_);
+  inputs_ = {indices, matrix, scales};
+  output_ = preallocOutput ? preallocOutput : store.createTensorEmpty(outShape_, DataType::Float32);
+}
+
+std::optional<std::vector<uint32_t>> EmbeddingColOpNode::shader() const {
+  KernelDesc d;
+  d.op = EmbeddingCol;
+  d.dtypeA = (uint32_t)DataType::UInt32;
+  d.dtypeB = (uint32_t)DataType::Float32;
+  d.fusionType = format_;  // specialisation constant 1, as in the reference: 0 = fp16 matrix, 1 = int8 + fp16 scales
+  return d.encode();
+}
+
+ThreadSize EmbeddingColOpNode::dispatchSize() const {
+  const uint32_t total = numIndices_ * embDim_;
+  return {(total + 255) / 256 * 256, 1, 1};
+}
+
+std::vector<uint8_t> EmbeddingColOpNode::pushConstants() const {
+  struct {
+    uint32_t numIndices, embDim, vocabStride, scaleStride, outStride;
+  } pc{numIndices_, embDim_, vocabStride_, scaleStride_, outStride_};
   return toBytes(pc);
 }
 
@@ -1000,6 +1042,11 @@ Tensor Operations::rmsNorm(const Tensor &x, const Tensor &weight, float eps, std
 Tensor Operations::embedding(const Tensor &indices, const Tensor &weight, const Tensor &preallocOutput,
                              std::optional<uint32_t> spec) {
   return dispatch(std::make_unique<EmbeddingOpNode>(*store_, indices, weight, preallocOutput, spec));
+}
+
+Tensor Operations::embeddingCol(const Tensor &indices, const Tensor &matrix, const Tensor &scales, const Tensor &preallocOutput,
+                                std::optional<uint32_t> spec) {
+  return dispatch(std::make_unique<EmbeddingColOpNode>(*store_, indices, matrix, scales, preallocOutput, spec));
 }
 
 Tensor Operations::reduce(OperatorEnum op, const Tensor &a, std::optional<uint32_t> spec) {

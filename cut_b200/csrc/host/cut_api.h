@@ -68,7 +68,7 @@ enum OperatorEnum : uint32_t {
   UnarySigmoid = 131, UnaryGelu = 132, UnarySilu = 133, UnarySoftplus = 134, UnaryRelu6 = 137, UnaryMish = 141,
   UnaryHardswish = 142, UnaryHardsigmoid = 143, UnaryRsqrt = 148,
   ReduceSum = 208, ReduceMean = 209, ReduceMin = 210, ReduceMax = 211, ReduceArgmax = 214, ReduceArgmin = 215,
-  RMSNorm = 312, Embedding = 320,
+  RMSNorm = 312, Embedding = 320, EmbeddingCol = 321,
   CacheWrite = 360, Attention = 361,
   MatMulQ8 = 371, MatMulQ4 = 374,
   MatMulQBlocks = 375,  // new: weights as raw GGUF blocks
@@ -304,8 +304,8 @@ protected:
 enum class QuantFormat { None, Q8, Q4, Blocks };
 enum class MatMulFusion { None, Unary, Binary };
 /// Formats of DequantOpNode; the reference's values (operators/impl/dequant/DequantOp.h:8-13)
-/// plus the two 32-weight block formats it only dequantises on the CPU.
-enum class DequantFormat : uint32_t { BF16 = 0, Q4_K = 1, Q5_K = 2, Q6_K = 3, Q8_0 = 16, Q4_0 = 17 };
+/// plus the 32-weight block formats it only dequantises on the CPU (gguf_reader.cpp:541-660, 826-850).
+enum class DequantFormat : uint32_t { BF16 = 0, Q4_K = 1, Q5_K = 2, Q6_K = 3, Q8_0 = 16, Q4_0 = 17, Q4_1 = 18, Q5_0 = 19 };
 
 class MatMulOpNode : public OpNode {
 public:
@@ -414,6 +414,25 @@ public:
 private:
   DataType dtype_ = DataType::Float32;
   uint32_t embDim_ = 0, numIndices_ = 1;
+  std::vector<uint32_t> outShape_;
+};
+
+/// Column gather out[i, d] = matrix[d, indices[i]] from a [dim, vocab] matrix in the matmul's orientation:
+/// the embedding read out of a tied LM head, fp16 or int8 + fp16 scales (operators/impl/memory/MemoryOp.cpp:127-202).
+class EmbeddingColOpNode : public OpNode {
+public:
+  EmbeddingColOpNode(TensorStore &store, const Tensor &indices, const Tensor &matrix, const Tensor &scales,
+                     const Tensor &preallocOutput = {}, std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return DataType::Float32; }
+  size_t shaderKey() const override { return static_cast<size_t>(op_) | (static_cast<size_t>(format_) << 16); }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return outShape_; }
+  ThreadSize dispatchSize() const override;
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "EmbeddingCol"; }
+
+private:
+  uint32_t embDim_ = 0, numIndices_ = 1, vocabStride_ = 0, scaleStride_ = 0, outStride_ = 0, format_ = 0;
   std::vector<uint32_t> outShape_;
 };
 
@@ -596,6 +615,9 @@ public:
   Tensor rmsNorm(const Tensor &x, const Tensor &weight, float eps = 1e-5f, std::optional<uint32_t> spec = {});
   Tensor embedding(const Tensor &indices, const Tensor &weight, const Tensor &preallocOutput = {},
                    std::optional<uint32_t> spec = {});
+  /// Embedding gathered from a [dim, vocab] head (runtime/Operations.cpp:1044-1052).
+  Tensor embeddingCol(const Tensor &indices, const Tensor &matrix, const Tensor &scales, const Tensor &preallocOutput = {},
+                      std::optional<uint32_t> spec = {});
   /// Whole-tensor reduction (the reference's per-dimension form is outside this path).
   Tensor reduce(OperatorEnum op, const Tensor &a, std::optional<uint32_t> spec = {});
   Tensor attention(const Tensor &q, const Tensor &kCache, const Tensor &vCache, const Tensor &runtimeParams, uint32_t nHeads,

@@ -33,6 +33,11 @@ int rmsnorm_launch(int dtype, const void *x, const void *weight, void *y, uint32
                    cudaStream_t stream);
 int embedding_launch(const uint32_t *indices, const float *table, float *out, uint64_t n, uint32_t dim, uint32_t vocab, int *status,
                      cudaStream_t stream);
+int embedding_col_launch(int format, const uint32_t *indices, const void *matrix, const void *scales, float *out, uint32_t n,
+                         uint32_t dim, uint32_t vocab, uint32_t vocab_stride, uint32_t scale_stride, uint32_t out_stride, int *status,
+                         cudaStream_t stream);
+int dequant_gather_launch(int format, const uint32_t *indices, const void *raw, float *out, uint32_t n, uint32_t rows, uint32_t cols,
+                          uint32_t ldo, int *status, cudaStream_t stream);
 int argreduce_launch(int is_max, const float *v, float *out, uint32_t n, cudaStream_t stream);
 // Decode-step attention (attention.cu).
 int rope_kv_write_launch(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params, const float *cosT,

@@ -106,6 +106,32 @@ __global__ void __launch_bounds__(256) embedding_kernel(const uint32_t *__restri
   }
 }
 
+// Column gather from a [dim, vocab] matrix: out[i, d] = M[d, indices[i]] -- the embedding read out of a
+// tied LM head that is stored in the matmul's [K, N] orientation (operators/impl/memory/EmbeddingCol.cu:16-44).
+// format 0: fp16 matrix; format 1: int8 values with one fp16 scale per 32 rows and column
+// (scales [dim / 32, vocab]).  An index >= vocab writes zeros and reports through *status.
+__global__ void __launch_bounds__(256) embedding_col_kernel(const uint32_t *__restrict__ indices, const void *__restrict__ matrix,
+                                                            const __half *__restrict__ scales, float *__restrict__ out, uint32_t n,
+                                                            uint32_t dim, uint32_t vocab, uint32_t vocab_stride, uint32_t scale_stride,
+                                                            uint32_t out_stride, int format, int *status) {
+  pdl_enter();
+  const uint64_t total = (uint64_t)n * dim;
+  for (uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; gid < total; gid += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t i = (uint32_t)(gid / dim), d = (uint32_t)(gid % dim);
+    const uint32_t tkn = __ldg(indices + i);
+    float v = 0.f;
+    if (tkn >= vocab) {
+      if (status) atomicExch(status, (int)CUTB_ERR_INVALID);
+    } else if (format == 0) {
+      v = __half2float(__ldg(reinterpret_cast<const __half *>(matrix) + (uint64_t)d * vocab_stride + tkn));
+    } else {
+      const int b = (int)__ldg(reinterpret_cast<const int8_t *>(matrix) + (uint64_t)d * vocab_stride + tkn);
+      v = (float)b * __half2float(__ldg(scales + (uint64_t)(d >> 5) * scale_stride + tkn));
+    }
+    out[(uint64_t)i * out_stride + d] = v;
+  }
+}
+
 // Arg-max / arg-min with the reference's order: a value wins if it is strictly better.  Among
 // equal values its 256-thread strided scan keeps each thread's first hit, and its shared-memory
 // tree (strides 128, 64, ..., 1, the lower position kept on ties) ends up preferring the thread
@@ -235,6 +261,21 @@ int embedding_launch(const uint32_t *indices, const float *table, float *out, ui
   if (blocks > (uint64_t)di.sm_count * 16) blocks = (uint64_t)di.sm_count * 16;
   CUTB_CUDA_TRY(launch_pdl(embedding_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, indices, reinterpret_cast<const uint4 *>(table),
                            reinterpret_cast<uint4 *>(out), n, ld4, vocab, status));
+  return CUTB_OK;
+}
+
+int embedding_col_launch(int format, const uint32_t *indices, const void *matrix, const void *scales, float *out, uint32_t n,
+                         uint32_t dim, uint32_t vocab, uint32_t vocab_stride, uint32_t scale_stride, uint32_t out_stride, int *status,
+                         cudaStream_t stream) {
+  DeviceInfo di;
+  if (int rc = get_device_info(&di)) return rc;
+  const uint64_t total = (uint64_t)n * dim;
+  if (total == 0) return CUTB_OK;
+  uint64_t blocks = (total + 255) / 256;
+  if (blocks > (uint64_t)di.sm_count * 16) blocks = (uint64_t)di.sm_count * 16;
+  CUTB_CUDA_TRY(launch_pdl(embedding_col_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, indices, matrix,
+                           reinterpret_cast<const __half *>(scales), out, n, dim, vocab, vocab_stride, scale_stride, out_stride, format,
+                           status));
   return CUTB_OK;
 }
 

@@ -163,6 +163,30 @@ def embedding(indices: torch.Tensor, table: torch.Tensor, dim: int | None = None
     return out
 
 
+def embedding_col(indices: torch.Tensor, matrix: torch.Tensor, scales: torch.Tensor | None = None, vocab: int | None = None,
+                  status: torch.Tensor | None = None) -> torch.Tensor:
+    """out[i, d] = M[d, indices[i]] for M [dim, vocab_stride] in float16, or int8 with float16 scales [dim / 32, scale_stride]."""
+    dim, vstride = matrix.shape
+    vocab = vstride if vocab is None else vocab
+    fmt = 0 if matrix.dtype == torch.float16 else 1
+    ld = (dim + 3) // 4 * 4
+    out = torch.zeros((indices.numel(), ld), dtype=torch.float32, device=matrix.device)
+    L.check(L.lib().cutb_embedding_col(fmt, indices.data_ptr(), matrix.data_ptr(), scales.data_ptr() if scales is not None else None,
+                                       out.data_ptr(), indices.numel(), dim, vocab, vstride,
+                                       scales.shape[1] if scales is not None else vstride, ld,
+                                       status.data_ptr() if status is not None else None, _stream_ptr()))
+    return out
+
+
+def embedding_blocks(indices: torch.Tensor, raw: torch.Tensor, fmt: int, rows: int, cols: int,
+                     status: torch.Tensor | None = None) -> torch.Tensor:
+    """out[i, :] = dequant(row indices[i]) of a table kept as raw GGUF blocks (rows x cols weights)."""
+    out = torch.empty((indices.numel(), cols), dtype=torch.float32, device=raw.device)
+    L.check(L.lib().cutb_embedding_blocks(fmt, indices.data_ptr(), raw.data_ptr(), out.data_ptr(), indices.numel(), rows, cols, cols,
+                                          status.data_ptr() if status is not None else None, _stream_ptr()))
+    return out
+
+
 def argreduce(values: torch.Tensor, is_max: bool = True) -> torch.Tensor:
     """Index of the maximum / minimum as a one-element float tensor (the reference's output type and tie rule)."""
     out = torch.empty(1, dtype=torch.float32, device=values.device)

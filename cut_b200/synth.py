@@ -15,6 +15,8 @@ benchmark configurations:
         bytes of nibbles (gguf_reader.cpp:726-772); uniform random bits
   Q6_K  210-byte super-blocks: 128 bytes of low nibbles, 64 bytes of 2-bit high
         parts, 16 int8 scales ~ U[-128, 127], f16 d (gguf_reader.cpp:774-824)
+  Q4_1  20-byte blocks: f16 scale, f16 minimum, 16 bytes of nibbles; Q5_0  22-byte blocks: f16
+        scale, 32 fifth bits, 16 bytes of nibbles (the loader's remaining 32-weight formats)
   BF16  the upper halves of N(0, 1) float32 values, some replaced by
         infinities, NaNs, zeros and subnormals
 
@@ -25,10 +27,10 @@ from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 4, 5  # the last three: dequant operator only
-FMT_NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", BF16: "BF16"}
-BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, BF16: 1}
-BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_K: 144, Q5_K: 176, Q6_K: 210, BF16: 2}
+Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16, Q4_1, Q5_0 = 0, 1, 2, 3, 4, 5, 6, 7  # from Q5_K on: dequant operator only
+FMT_NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", BF16: "BF16", Q4_1: "Q4_1", Q5_0: "Q5_0"}
+BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, BF16: 1, Q4_1: 32, Q5_0: 32}
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_K: 144, Q5_K: 176, Q6_K: 210, BF16: 2, Q4_1: 20, Q5_0: 22}
 
 
 def row_bytes(fmt: int, K: int) -> int:
@@ -92,6 +94,17 @@ def make_weights(fmt: int, N: int, K: int, seed: int) -> np.ndarray:
         d = np.abs(rng.normal(0.0, 0.002, nb)).astype(np.float32).astype(np.float16)
         blocks[:, 0:208] = rng.integers(0, 256, size=(nb, 208), dtype=np.uint8)
         blocks[:, 208:210] = d.view(np.uint8).reshape(nb, 2)
+    elif fmt == Q4_1:
+        d = (np.abs(rng.normal(0.0, 0.02, nb)) / 8.0).astype(np.float32).astype(np.float16)
+        m = rng.normal(0.0, 0.02, nb).astype(np.float32).astype(np.float16)
+        nib = rng.integers(0, 16, size=(nb, 32), dtype=np.uint8)
+        blocks[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+        blocks[:, 2:4] = m.view(np.uint8).reshape(nb, 2)
+        blocks[:, 4:20] = nib[:, 0:16] | (nib[:, 16:32] << 4)
+    elif fmt == Q5_0:
+        d = (np.abs(rng.normal(0.0, 0.02, nb)) / 16.0).astype(np.float32).astype(np.float16)
+        blocks[:, 0:2] = d.view(np.uint8).reshape(nb, 2)
+        blocks[:, 2:22] = rng.integers(0, 256, size=(nb, 20), dtype=np.uint8)
     elif fmt == BF16:
         x = rng.normal(0.0, 1.0, nb).astype(np.float32)
         bits = (x.view(np.uint32) >> 16).astype(np.uint16)

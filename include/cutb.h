@@ -49,7 +49,7 @@ enum {
  * take the first three; cutb_dequant also takes the rest of the reference's DequantFormat set
  * (operators/impl/dequant/DequantOp.h:8-13): Q5_K (176-byte super-blocks), Q6_K (210-byte
  * super-blocks) and BF16 (2 bytes per element). */
-enum { CUTB_Q8_0 = 0, CUTB_Q4_0 = 1, CUTB_Q4_K = 2, CUTB_Q5_K = 3, CUTB_Q6_K = 4, CUTB_BF16 = 5 };
+enum { CUTB_Q8_0 = 0, CUTB_Q4_0 = 1, CUTB_Q4_K = 2, CUTB_Q5_K = 3, CUTB_Q6_K = 4, CUTB_BF16 = 5, CUTB_Q4_1 = 6, CUTB_Q5_0 = 7 };
 
 /* Activation element types (core/api/include/ComputeCommon.h:107-113). */
 enum { CUTB_F32 = 0, CUTB_F16 = 1 };
@@ -298,6 +298,15 @@ CUTB_API int cutb_quantize_rows_q8_0(const float *x, void *values, void *scales,
  * cutb_embedding: out[i, :] = table[indices[i], :], rows of pad4(dim) floats, 16-byte aligned
  *   (operators/impl/memory/Embedding.cu:18-35).  An index >= vocab writes zeros and sets *status
  *   to CUTB_ERR_INVALID instead of reading outside the table (the reference does not check).
+ * cutb_embedding_col: out[i, d] = M[d, indices[i]] for a matrix kept in the matmul's [dim, vocab]
+ *   orientation -- the embedding read out of a tied LM head (EmbeddingColOpNode:
+ *   operators/impl/memory/MemoryOp.cpp:127-202, EmbeddingCol.cu:16-44).  format 0: fp16 matrix;
+ *   format 1: int8 values with fp16 scales [dim / 32, vocab] (value * scale).  Strides in elements.
+ *   An index >= vocab writes zeros and sets *status to CUTB_ERR_INVALID (the reference does not check).
+ * cutb_embedding_blocks: the same lookup when the table is kept as raw GGUF blocks, one row of
+ *   `cols` weights per token: out[i, :] = dequant(row indices[i]), bit-exact with cutb_dequant
+ *   (every format of cutb_dequant).  It has no counterpart in the reference, whose runner either
+ *   dequantises the whole table or gathers columns from the head (llama.cpp:1029-1060, 1425-1438).
  * cutb_argreduce: index of the maximum (is_max) or minimum of n floats, written as a float to
  *   out[0], with the reference's tie rule (the outcome of its 256-thread strided scan and
  *   shared-memory tree): among equal extremes the smallest bit-reversed (i mod 256) wins, then
@@ -307,6 +316,11 @@ CUTB_API int cutb_rmsnorm(int dtype, const void *x, const void *weight, void *y,
                           float eps, void *stream);
 CUTB_API int cutb_embedding(const uint32_t *indices, const float *table, float *out, uint64_t n, uint32_t dim, uint32_t vocab,
                             int *status, void *stream);
+CUTB_API int cutb_embedding_col(int format, const uint32_t *indices, const void *matrix, const void *scales, float *out, uint32_t n,
+                                uint32_t dim, uint32_t vocab, uint32_t vocab_stride, uint32_t scale_stride, uint32_t out_stride,
+                                int *status, void *stream);
+CUTB_API int cutb_embedding_blocks(int format, const uint32_t *indices, const void *raw, float *out, uint32_t n, uint32_t rows,
+                                   uint32_t cols, uint32_t ldo, int *status, void *stream);
 CUTB_API int cutb_argreduce(int is_max, const float *values, float *out, uint32_t n, void *stream);
 
 /*

@@ -6,11 +6,14 @@
  * test-suite, the smoke check and the benchmark's CPU-baseline leg use it.
  *
  * Every function restates one piece of the reference (trviv/cut) and names the
- * reference file:line it follows.  Parity of this restatement is pinned two
+ * reference file:line it follows.  Parity of this restatement is pinned three
  * ways: against the reference's own in-code known-answer tests
- * (tests/harness/OpRegistry.h, tests/runtime/*.cpp) and against the
+ * (tests/harness/OpRegistry.h, tests/runtime/*.cpp), against the
  * reference's gguf_reader.cpp compiled unmodified (oracle/Makefile ->
- * oracle/_ref/libcutref.so).
+ * oracle/_ref/libcutref.so), and -- for the runner's weight re-encoders, which
+ * the reference keeps file-static and does not test -- against those very
+ * functions, reached by compiling its runner translation unit
+ * (oracle/ref_runner_shim.cpp -> oracle/_ref/libcutref_runner.so).
  *
  * Plain C99, no dependencies beyond libm.  Optional OpenMP (-fopenmp) only
  * parallelises the outer row loops of the matmul helpers; results do not
@@ -283,7 +286,51 @@ ORC_API void orc_dequant_bf16(const uint8_t *data, float *out, size_t n_elements
 /* Format codes shared with the tests (they mirror the product's C ABI values
  * but are defined independently here).  Q5_K, Q6_K and BF16 exist for the
  * dequant operator only. */
-enum { ORC_Q8_0 = 0, ORC_Q4_0 = 1, ORC_Q4_K = 2, ORC_Q5_K = 3, ORC_Q6_K = 4, ORC_BF16 = 5 };
+/* interface/loader/gguf/gguf_reader.cpp:574-611 -- Q4_1: 20-byte blocks of {f16 d, f16 m, 16 bytes};
+ * byte j holds element j (low nibble) and element j + 16 (high nibble); value = float(nibble) * d + m
+ * (the product and the sum each rounded: the reference's CPU build does not contract). */
+ORC_API void orc_dequant_q4_1(const uint8_t *data, float *out, size_t n_elements) {
+  size_t n_blocks = (n_elements + 31) / 32;
+  for (size_t i = 0; i < n_blocks; ++i) {
+    const uint8_t *blk = data + i * 20;
+    uint16_t dbits, mbits;
+    memcpy(&dbits, blk, 2);
+    memcpy(&mbits, blk + 2, 2);
+    float d = orc_f16_to_f32(dbits), m = orc_f16_to_f32(mbits);
+    size_t base = i * 32;
+    for (size_t j = 0; j < 16; ++j) {
+      uint8_t byte = blk[4 + j];
+      int x0 = byte & 0x0F, x1 = (byte >> 4) & 0x0F;
+      if (base + j < n_elements) out[base + j] = (float)x0 * d + m;
+      if (base + j + 16 < n_elements) out[base + j + 16] = (float)x1 * d + m;
+    }
+  }
+}
+
+/* interface/loader/gguf/gguf_reader.cpp:613-660 -- Q5_0: 22-byte blocks of {f16 d, u32 qh, 16 bytes};
+ * nibbles as in Q4_0, bit j of qh is the fifth bit of element j, bit j + 16 that of element j + 16;
+ * value = float(q5 - 16) * d. */
+ORC_API void orc_dequant_q5_0(const uint8_t *data, float *out, size_t n_elements) {
+  size_t n_blocks = (n_elements + 31) / 32;
+  for (size_t i = 0; i < n_blocks; ++i) {
+    const uint8_t *blk = data + i * 22;
+    uint16_t dbits;
+    uint32_t qh;
+    memcpy(&dbits, blk, 2);
+    memcpy(&qh, blk + 2, 4);
+    float d = orc_f16_to_f32(dbits);
+    size_t base = i * 32;
+    for (size_t j = 0; j < 16; ++j) {
+      uint8_t byte = blk[6 + j];
+      int lo = (byte & 0x0F) | (int)(((qh >> j) & 1u) << 4);
+      int hi = ((byte >> 4) & 0x0F) | (int)(((qh >> (j + 16)) & 1u) << 4);
+      if (base + j < n_elements) out[base + j] = (float)(lo - 16) * d;
+      if (base + j + 16 < n_elements) out[base + j + 16] = (float)(hi - 16) * d;
+    }
+  }
+}
+
+enum { ORC_Q8_0 = 0, ORC_Q4_0 = 1, ORC_Q4_K = 2, ORC_Q5_K = 3, ORC_Q6_K = 4, ORC_BF16 = 5, ORC_Q4_1 = 6, ORC_Q5_0 = 7 };
 
 ORC_API size_t orc_block_bytes(int fmt) {
   switch (fmt) {
@@ -292,6 +339,8 @@ ORC_API size_t orc_block_bytes(int fmt) {
     case ORC_Q4_K: return 144;
     case ORC_Q5_K: return 176;
     case ORC_Q6_K: return 210;
+    case ORC_Q4_1: return 20;
+    case ORC_Q5_0: return 22;
     default: return 2;
   }
 }
@@ -315,6 +364,10 @@ ORC_API void orc_dequant(int fmt, const uint8_t *data, float *out, size_t n_elem
     orc_dequant_q6_k(data, out, n_elements);
   else if (fmt == ORC_BF16)
     orc_dequant_bf16(data, out, n_elements);
+  else if (fmt == ORC_Q4_1)
+    orc_dequant_q4_1(data, out, n_elements);
+  else if (fmt == ORC_Q5_0)
+    orc_dequant_q5_0(data, out, n_elements);
   else
     orc_dequant_q4_k(data, out, n_elements);
 }
@@ -703,6 +756,23 @@ ORC_API void orc_rmsnorm(const float *x, const float *weight, float *y, size_t r
 ORC_API void orc_embedding(const uint32_t *indices, const float *table, float *out, size_t n, size_t dim) {
   size_t ld = (dim + 3) & ~(size_t)3;
   for (size_t i = 0; i < n; ++i) memcpy(out + i * ld, table + (size_t)indices[i] * ld, ld * sizeof(float));
+}
+
+/* operators/impl/memory/EmbeddingCol.cu:16-44 -- column gather out[i, d] = M[d, indices[i]] from a
+ * [dim, vocab] matrix: format 0 fp16 (raw bits), format 1 int8 values times the fp16 scale of the
+ * 32-row group, scales [dim / 32, scale_stride]. */
+ORC_API void orc_embedding_col(int format, const uint32_t *indices, const void *matrix, const uint16_t *scales, float *out,
+                               size_t n, size_t dim, size_t vocab_stride, size_t scale_stride, size_t out_stride) {
+  for (size_t i = 0; i < n; ++i)
+    for (size_t d = 0; d < dim; ++d) {
+      size_t idx = d * vocab_stride + indices[i];
+      float v;
+      if (format == 0)
+        v = orc_f16_to_f32(((const uint16_t *)matrix)[idx]);
+      else
+        v = (float)((const int8_t *)matrix)[idx] * orc_f16_to_f32(scales[(d >> 5) * scale_stride + indices[i]]);
+      out[i * out_stride + d] = v;
+    }
 }
 
 /* operators/impl/reduce/ReduceArg.cu:27-59 -- arg-max / arg-min with the reference's tie rule:

@@ -12,7 +12,7 @@ import struct
 
 import numpy as np
 
-GGML_TYPE = {"F32": 0, "F16": 1, "Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30}
+GGML_TYPE = {"F32": 0, "F16": 1, "Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30}
 
 
 def write_gguf(path: str, tensors: list[tuple[str, str, tuple[int, int], np.ndarray]]) -> None:

@@ -18,9 +18,9 @@ _LIB_PATH = os.path.join(_HERE, "_build", "liboracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libcutref.so")
 _REF_RUNNER_PATH = os.path.join(_HERE, "_ref", "libcutref_runner.so")
 
-Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16 = 0, 1, 2, 3, 4, 5  # the last three: dequant operator only
-BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, BF16: 1}
-BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_K: 144, Q5_K: 176, Q6_K: 210, BF16: 2}
+Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16, Q4_1, Q5_0 = 0, 1, 2, 3, 4, 5, 6, 7  # from Q5_K on: dequant operator only
+BLOCK_ELEMS = {Q8_0: 32, Q4_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, BF16: 1, Q4_1: 32, Q5_0: 32}
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_K: 144, Q5_K: 176, Q6_K: 210, BF16: 2, Q4_1: 20, Q5_0: 22}
 
 
 def build(force: bool = False) -> None:
@@ -273,7 +273,7 @@ def set_num_threads(n: int) -> None:
 
 
 # ------------------------------------------ the reference's own reader (_ref)
-_TYPE_NAME = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", BF16: "BF16"}
+_TYPE_NAME = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K", BF16: "BF16", Q4_1: "Q4_1", Q5_0: "Q5_0"}
 
 
 def _with_gguf(fmt: int, raw, rows: int, cols: int, fn):
@@ -356,6 +356,20 @@ def embedding(indices: np.ndarray, table: np.ndarray) -> np.ndarray:
     t = np.ascontiguousarray(table, dtype=np.float32)
     out = np.empty((idx.size, t.shape[1]), dtype=np.float32)
     lib().orc_embedding(_p(idx), _p(t), _p(out), C.c_size_t(idx.size), C.c_size_t(t.shape[1]))
+    return out
+
+
+def embedding_col(indices: np.ndarray, matrix: np.ndarray, scales: np.ndarray | None = None) -> np.ndarray:
+    """matrix [dim, vocab_stride] as float16 bits (uint16) or int8 (+ scales [dim / 32, scale_stride] float16 bits)."""
+    idx = np.ascontiguousarray(indices, dtype=np.uint32)
+    dim, vstride = matrix.shape
+    fmt = 1 if matrix.dtype == np.int8 else 0
+    m = np.ascontiguousarray(matrix)
+    sc = np.ascontiguousarray(scales, dtype=np.uint16) if scales is not None else np.zeros((1, 1), dtype=np.uint16)
+    ld = (dim + 3) // 4 * 4
+    out = np.zeros((idx.size, ld), dtype=np.float32)
+    lib().orc_embedding_col(C.c_int(fmt), _p(idx), _p(m), _p(sc), _p(out), C.c_size_t(idx.size), C.c_size_t(dim), C.c_size_t(vstride),
+                            C.c_size_t(sc.shape[1]), C.c_size_t(ld))
     return out
 
 

@@ -345,6 +345,24 @@ void layerOperatorNodes() {
   CHECK(EmbeddingOpNode(s, idx, table, pre).output() == pre);
   CHECK_THROWS(EmbeddingOpNode(s, idx, w), "weight must be 2D");
   CHECK(!EmbeddingOpNode(s, idx, s.createTensor({50, 6}, DataType::Float16)).shader().has_value());
+  {  // EmbeddingColOpNode (operators/impl/memory/MemoryOp.cpp:127-202): geometry, format detection, messages
+    auto head16 = s.createTensor({6, 50}, DataType::Float16);
+    auto head8 = s.createTensor({64, 50}, DataType::Int8);
+    auto sc8 = s.createTensor({2, 50}, DataType::Float16);
+    EmbeddingColOpNode c0(s, idx, head16, head16);
+    CHECK(c0.outputShape().back() == 6 && c0.outputDtype() == DataType::Float32);
+    struct PC { uint32_t numIndices, embDim, vocabStride, scaleStride, outStride; } pc;
+    auto bytes = c0.pushConstants();
+    CHECK(bytes.size() == sizeof(pc));
+    std::memcpy(&pc, bytes.data(), sizeof(pc));
+    CHECK(pc.embDim == 6 && pc.vocabStride == 52 && pc.scaleStride == 52 && pc.outStride == 8);
+    CHECK(KernelDesc::decode(*c0.shader())->fusionType == 0);
+    EmbeddingColOpNode c1(s, idx, head8, sc8);
+    CHECK(KernelDesc::decode(*c1.shader())->fusionType == 1 && KernelDesc::decode(*c1.shader())->op == EmbeddingCol);
+    CHECK(c1.dispatchSize().x == (pc.numIndices * 64 + 255) / 256 * 256);
+    CHECK_THROWS(EmbeddingColOpNode(s, idx, w, w), "matrix must be 2D");
+    CHECK_THROWS(EmbeddingColOpNode(s, idx, s.createTensor({6, 50}, DataType::Float32), sc8), "Float16 or Int8");
+  }
 
   GlobalReduceOpNode am(ReduceArgmax, s, s.createTensor({1, 1000}, DataType::Float32));
   CHECK(am.outputShape() == (std::vector<uint32_t>{1}) && am.dispatchSize().x == 256 && am.displayName() == "ReduceArgmax");

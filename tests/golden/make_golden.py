@@ -110,6 +110,32 @@ def edge_q6_k() -> np.ndarray:
     return blocks.reshape(-1)
 
 
+def edge_q4_1() -> np.ndarray:
+    mins = [0x0000, 0x8000, 0x0001, 0x3C00, 0xBC00, 0x7BFF, 0xFBFF, 0x2E66, 0x83FF, 0x0400, 0x1234, 0xB266]
+    blocks = np.zeros((len(EDGE_D) * 2, 20), dtype=np.uint8)
+    for i, d in enumerate(EDGE_D):
+        for v in range(2):
+            b = blocks[2 * i + v]
+            b[0:2] = np.array([d], dtype=np.uint16).view(np.uint8)
+            b[2:4] = np.array([mins[(i + 5 * v) % len(mins)]], dtype=np.uint16).view(np.uint8)
+            nib = (np.arange(32) % 16) if v == 0 else np.array([0, 15, 8, 7] * 8)
+            b[4:] = (nib[:16] | (nib[16:] << 4)).astype(np.uint8)
+    return blocks.reshape(-1)
+
+
+def edge_q5_0() -> np.ndarray:
+    blocks = np.zeros((len(EDGE_D) * 2, 22), dtype=np.uint8)
+    for i, d in enumerate(EDGE_D):
+        for v in range(2):
+            b = blocks[2 * i + v]
+            b[0:2] = np.array([d], dtype=np.uint16).view(np.uint8)
+            qh = 0xA5C3F00F if v == 0 else (0xFFFFFFFF if i % 2 else 0x00000001 << (i % 32))
+            b[2:6] = np.array([qh], dtype=np.uint32).view(np.uint8)
+            nib = (np.arange(32) % 16) if v == 0 else np.array([0, 15, 8, 7] * 8)
+            b[6:] = (nib[:16] | (nib[16:] << 4)).astype(np.uint8)
+    return blocks.reshape(-1)
+
+
 def edge_bf16() -> np.ndarray:
     # +-0, subnormals, smallest normal, 1, largest finite, +-inf, quiet and signalling NaN payloads
     bits = np.array([0x0000, 0x8000, 0x0001, 0x007F, 0x0080, 0x3F80, 0xBF80, 0x7F7F, 0xFF7F, 0x7F80, 0xFF80, 0x7FC0,
@@ -123,7 +149,8 @@ def main() -> None:
     out = {}
     for fmt, name, edge in ((synth.Q8_0, "q8_0", edge_q8_0), (synth.Q4_0, "q4_0", edge_q4_0),
                             (synth.Q4_K, "q4_k", edge_q4_k), (synth.Q5_K, "q5_k", edge_q5_k),
-                            (synth.Q6_K, "q6_k", edge_q6_k), (synth.BF16, "bf16", edge_bf16)):
+                            (synth.Q6_K, "q6_k", edge_q6_k), (synth.BF16, "bf16", edge_bf16),
+                            (synth.Q4_1, "q4_1", edge_q4_1), (synth.Q5_0, "q5_0", edge_q5_0)):
         e = edge()
         be = synth.BLOCK_ELEMS[fmt]
         n_edge = e.size // synth.BLOCK_BYTES[fmt] * be

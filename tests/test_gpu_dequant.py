@@ -10,7 +10,7 @@ from oracle import oracle as O
 pytestmark = pytest.mark.gpu
 
 FMTS = [(synth.Q8_0, "q8_0"), (synth.Q4_0, "q4_0"), (synth.Q4_K, "q4_k"), (synth.Q5_K, "q5_k"), (synth.Q6_K, "q6_k"),
-        (synth.BF16, "bf16")]
+        (synth.BF16, "bf16"), (synth.Q4_1, "q4_1"), (synth.Q5_0, "q5_0")]
 
 
 @pytest.fixture(scope="module")

@@ -3,6 +3,8 @@ rounding of the CPU checker, embedding gather and arg-reduce exact, ties include
 import numpy as np
 import pytest
 
+from cut_b200 import _lib as L
+from cut_b200 import synth
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -106,3 +108,61 @@ def test_argreduce_ties_follow_the_reference_tree(gpu, is_max):
 def test_argreduce_of_nothing_better_than_the_start_value(gpu):
     v = np.full(100, -3.402823466e+38, np.float32)
     assert float(gpu.argreduce(_dev(v), True).cpu().numpy()[0]) == O.argreduce(v, True) == 0.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("quantized", [False, True])
+def test_embedding_col_matches_checker(quantized):
+    """Column gather from a [dim, vocab] head (the reference's EmbeddingCol.cu): fp16 matrix, and int8 values
+    with one fp16 scale per 32 rows and column; bit-exact against the checker, strides padded to 4."""
+    import torch
+
+    from cut_b200 import ops
+    from oracle import oracle as O
+
+    rng = np.random.default_rng(12)
+    dim, vocab = 96, 37
+    vstride = (vocab + 3) // 4 * 4
+    idx = np.array([0, 36, 5, 5, 17], dtype=np.uint32)
+    if quantized:
+        m = np.zeros((dim, vstride), dtype=np.int8)
+        m[:, :vocab] = rng.integers(-128, 128, size=(dim, vocab), dtype=np.int16).astype(np.int8)
+        sc = np.zeros((dim // 32, vstride), dtype=np.float16)
+        sc[:, :vocab] = np.abs(rng.normal(0, 0.02, size=(dim // 32, vocab))).astype(np.float16)
+        want = O.embedding_col(idx, m, sc.view(np.uint16))
+        got = ops.embedding_col(torch.from_numpy(idx.astype(np.int32)).cuda(), torch.from_numpy(m).cuda(),
+                                torch.from_numpy(sc).cuda(), vocab=vocab)
+    else:
+        m = np.zeros((dim, vstride), dtype=np.float16)
+        m[:, :vocab] = rng.normal(0, 1, size=(dim, vocab)).astype(np.float16)
+        want = O.embedding_col(idx, m.view(np.uint16))
+        got = ops.embedding_col(torch.from_numpy(idx.astype(np.int32)).cuda(), torch.from_numpy(m).cuda(), vocab=vocab)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    # an index past the vocabulary is reported and written as zeros, never read
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bad = torch.tensor([3, vocab], dtype=torch.int32, device="cuda")
+    mt = torch.from_numpy(m).cuda()
+    out = ops.embedding_col(bad, mt, torch.from_numpy(sc).cuda() if quantized else None, vocab=vocab, status=status)
+    assert int(status.item()) == L.ERR_INVALID and bool((out[1] == 0).all())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_0, synth.Q4_K, synth.Q6_K, synth.Q5_0])
+def test_embedding_blocks_equals_dequantised_rows(fmt):
+    """Row gather from a table kept as raw GGUF blocks: every gathered row has the float32 bits of the checker's
+    dequantised row."""
+    import torch
+
+    from cut_b200 import ops
+    from oracle import oracle as O
+
+    rows, cols = 50, 512
+    raw = synth.make_weights(fmt, rows, cols, seed=60 + fmt)
+    table = O.dequant_rows(fmt, raw, rows, cols)
+    idx = np.array([49, 0, 7, 7, 31], dtype=np.int32)
+    got = ops.embedding_blocks(torch.from_numpy(idx).cuda(), torch.from_numpy(raw).cuda(), fmt, rows, cols)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), table[idx].view(np.uint32))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.embedding_blocks(torch.tensor([rows], dtype=torch.int32, device="cuda"), torch.from_numpy(raw).cuda(), fmt, rows, cols,
+                               status=status)
+    assert int(status.item()) == L.ERR_INVALID and bool((out == 0).all())
