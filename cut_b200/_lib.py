@@ -29,7 +29,7 @@ EXPORTS = [
     "cutb_rmsnorm", "cutb_embedding", "cutb_embedding_col", "cutb_embedding_blocks", "cutb_argreduce",
     "cutb_rope_kv_write", "cutb_attention_workspace_bytes", "cutb_attention_decode", "cutb_rope_attention_decode",
     "cutb_batched_kv_write", "cutb_batched_attention", "cutb_glu_pairs",
-    "cutb_dequant", "cutb_separate_blocks", "cutb_transpose_2d", "cutb_requant_q4k_affine", "cutb_quantize_rows_q8_0",
+    "cutb_dequant", "cutb_separate_blocks", "cutb_transpose_2d", "cutb_requant_q4k_affine", "cutb_quantize_rows_q8_0", "cutb_requant_q8_0_blocks",
     "cutb_transpose_q4", "cutb_version", "cutb_status_string", "cutb_last_error", "cutb_device_sm_count",
     "cutb_variant_name",
 ]
@@ -111,6 +111,8 @@ def lib() -> C.CDLL:
         l.cutb_embedding_blocks.restype = C.c_int
         l.cutb_embedding_blocks.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                             C.c_void_p, C.c_void_p]
+        l.cutb_requant_q8_0_blocks.restype = C.c_int
+        l.cutb_requant_q8_0_blocks.argtypes = [C.c_int, C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p]
         l.cutb_argreduce.restype = C.c_int
         l.cutb_argreduce.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]
         l.cutb_rope_kv_write.restype = C.c_int

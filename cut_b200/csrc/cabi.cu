@@ -351,6 +351,25 @@ int cutb_quantize_rows_q8_0(const float *x, void *values, void *scales, uint64_t
   return quantize_rows_q8_0_launch(x, values, scales, n, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cutb_requant_q8_0_blocks(int format, const void *raw, uint64_t raw_bytes, void *out, uint64_t rows, uint32_t cols, void *stream) {
+  if (rows == 0 || cols == 0) return CUTB_OK;
+  if (format < CUTB_Q8_0 || format > CUTB_Q5_0) {
+    set_last_error("requant_q8_0_blocks: unknown block format %d", format);
+    return CUTB_ERR_INVALID;
+  }
+  const uint32_t be = block_elems(format);
+  if (!raw || !out || cols % 32 != 0 || cols % be != 0 || reinterpret_cast<uintptr_t>(out) % 2 != 0) {
+    set_last_error("requant_q8_0_blocks: null pointer, misaligned output, or cols (%u) not a whole number of blocks", cols);
+    return CUTB_ERR_INVALID;
+  }
+  if (raw_bytes < rows * row_bytes(format, cols)) {
+    set_last_error("requant_q8_0_blocks: %llu raw bytes given, %llu needed", (unsigned long long)raw_bytes,
+                   (unsigned long long)(rows * row_bytes(format, cols)));
+    return CUTB_ERR_INVALID;
+  }
+  return requant_q8_0_blocks_launch(format, raw, out, rows, cols, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int cutb_rmsnorm(int dtype, const void *x, const void *weight, void *y, uint32_t rows, uint32_t dim, uint64_t ldx, float eps,
                  void *stream) {
   if (dtype != CUTB_F32 && dtype != CUTB_F16) {

@@ -193,6 +193,34 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                : "memory");
 }
 
+// llama.cpp:445-482: float -> half with the dropped bits rounded half UP, subnormals encoded,
+// overflow to infinity (NaN is not special-cased there and becomes infinity too).
+__device__ __forceinline__ uint16_t f32_to_f16_runner(float v) {
+  const uint32_t u = __float_as_uint(v);
+  const uint32_t sign = (u >> 16) & 0x8000u;
+  int32_t e = (int32_t)((u >> 23) & 0xffu) - 127 + 15;
+  const uint32_t mantissa = u & 0x7fffffu;
+  if (e <= 0) {
+    const uint32_t shift = (uint32_t)(14 - e);
+    if (shift > 24) return (uint16_t)sign;
+    const uint32_t significand = 0x800000u | mantissa;
+    uint32_t half = significand >> shift;
+    if ((significand >> (shift - 1)) & 1u) ++half;
+    return (uint16_t)(sign | half);
+  }
+  if (e >= 31) return (uint16_t)(sign | 0x7c00u);
+  uint32_t m = mantissa >> 13;
+  if (mantissa & 0x1000u) {
+    ++m;
+    if (m == 0x400u) {
+      m = 0;
+      ++e;
+      if (e >= 31) return (uint16_t)(sign | 0x7c00u);
+    }
+  }
+  return (uint16_t)(sign | ((uint32_t)e << 10) | m);
+}
+
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 

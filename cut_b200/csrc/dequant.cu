@@ -214,7 +214,73 @@ __global__ void __launch_bounds__(256) dequant_gather_kernel(const uint32_t *__r
   }
 }
 
+// Any dequantisable block format -> Q8_0 GGUF blocks, on the device: the runner's load-time requantisation
+// of the formats its matmul does not take (interface/runner/llama/llama.cpp:750-767 with quantizeRowsQ8_0,
+// :488-505), fused with the dequantisation.  One thread per group of 32 weights: exact dequantised values
+// (as cutb_dequant), d = amax / 127 stored through the runner's float -> half, q = lround(x * (1 / d)).
+template <int FMT>
+__global__ void __launch_bounds__(256) requant_q8_0_blocks_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ out,
+                                                                  uint64_t rows, uint32_t cols, uint64_t row_bytes_) {
+  constexpr uint32_t BE = block_elems(FMT), BB = block_bytes(FMT);
+  const uint64_t groups_per_row = cols / 32, total = rows * groups_per_row;
+  for (uint64_t gidx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; gidx < total; gidx += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t r = gidx / groups_per_row;
+    const uint32_t k = (uint32_t)(gidx % groups_per_row) * 32;
+    const uint8_t *b = raw + r * row_bytes_ + (uint64_t)(k / BE) * BB;
+    float v[32];
+#pragma unroll
+    for (int o = 0; o < 4; ++o) {
+      float t8[8];
+      decode8<FMT>(FMT == CUTB_BF16 ? raw + r * row_bytes_ + (uint64_t)(k + 8 * o) * 2 : b, (k % BE) / 8 + o, t8, 8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[8 * o + e] = t8[e];
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    uint16_t *o16 = reinterpret_cast<uint16_t *>(out + gidx * 34);  // 34-byte blocks: 2-byte aligned
+    o16[0] = f32_to_f16_runner(d);
+#pragma unroll
+    for (int w = 0; w < 16; ++w) {
+      // lroundf: nearest, halves away from zero; the product is rounded to float first, as on the CPU
+      const int q0 = (int)(int8_t)lroundf(__fmul_rn(v[2 * w], id)), q1 = (int)(int8_t)lroundf(__fmul_rn(v[2 * w + 1], id));
+      o16[1 + w] = (uint16_t)(((uint32_t)q0 & 0xFFu) | (((uint32_t)q1 & 0xFFu) << 8));
+    }
+  }
+}
+
 }  // namespace
+
+int requant_q8_0_blocks_launch(int format, const void *raw, void *out, uint64_t rows, uint32_t cols, cudaStream_t stream) {
+  DeviceInfo di;
+  if (int rc = get_device_info(&di)) return rc;
+  const uint64_t total = rows * (cols / 32);
+  if (total == 0) return CUTB_OK;
+  if ((format == CUTB_Q4_K || format == CUTB_Q5_K) && (reinterpret_cast<uintptr_t>(raw) % 4 != 0)) {
+    set_last_error("requant_q8_0_blocks: Q4_K / Q5_K blocks must be 4-byte aligned");
+    return CUTB_ERR_INVALID;
+  }
+  uint64_t blocks = (total + 255) / 256;
+  if (blocks > (uint64_t)di.sm_count * 16) blocks = (uint64_t)di.sm_count * 16;
+  const unsigned g = (unsigned)blocks;
+  const uint8_t *r = reinterpret_cast<const uint8_t *>(raw);
+  uint8_t *o = reinterpret_cast<uint8_t *>(out);
+  const uint64_t rb = row_bytes(format, cols);
+  switch (format) {
+    case CUTB_Q8_0: requant_q8_0_blocks_kernel<CUTB_Q8_0><<<g, 256, 0, stream>>>(r, o, rows, cols, rb); break;
+    case CUTB_Q4_0: requant_q8_0_blocks_kernel<CUTB_Q4_0><<<g, 256, 0, stream>>>(r, o, rows, cols, rb); break;
+    case CUTB_Q5_K: requant_q8_0_blocks_kernel<CUTB_Q5_K><<<g, 256, 0, stream>>>(r, o, rows, cols, rb); break;
+    case CUTB_Q6_K: requant_q8_0_blocks_kernel<CUTB_Q6_K><<<g, 256, 0, stream>>>(r, o, rows, cols, rb); break;
+    case CUTB_BF16: requant_q8_0_blocks_kernel<CUTB_BF16><<<g, 256, 0, stream>>>(r, o, rows, cols, rb); break;
+    case CUTB_Q4_1: requant_q8_0_blocks_kernel<CUTB_Q4_1><<<g, 256, 0, stream>>>(r, o, rows, cols, rb); break;
+    case CUTB_Q5_0: requant_q8_0_blocks_kernel<CUTB_Q5_0><<<g, 256, 0, stream>>>(r, o, rows, cols, rb); break;
+    default: requant_q8_0_blocks_kernel<CUTB_Q4_K><<<g, 256, 0, stream>>>(r, o, rows, cols, rb); break;
+  }
+  CUTB_CUDA_TRY(cudaGetLastError());
+  return CUTB_OK;
+}
 
 int dequant_gather_launch(int format, const uint32_t *indices, const void *raw, float *out, uint32_t n, uint32_t rows, uint32_t cols,
                           uint32_t ldo, int *status, cudaStream_t stream) {

@@ -36,6 +36,7 @@ int embedding_launch(const uint32_t *indices, const float *table, float *out, ui
 int embedding_col_launch(int format, const uint32_t *indices, const void *matrix, const void *scales, float *out, uint32_t n,
                          uint32_t dim, uint32_t vocab, uint32_t vocab_stride, uint32_t scale_stride, uint32_t out_stride, int *status,
                          cudaStream_t stream);
+int requant_q8_0_blocks_launch(int format, const void *raw, void *out, uint64_t rows, uint32_t cols, cudaStream_t stream);
 int dequant_gather_launch(int format, const uint32_t *indices, const void *raw, float *out, uint32_t n, uint32_t rows, uint32_t cols,
                           uint32_t ldo, int *status, cudaStream_t stream);
 int argreduce_launch(int is_max, const float *v, float *out, uint32_t n, cudaStream_t stream);

@@ -16,34 +16,6 @@
 namespace cutb {
 namespace {
 
-// llama.cpp:445-482: float -> half with the dropped bits rounded half UP, subnormals encoded,
-// overflow to infinity (NaN is not special-cased there and becomes infinity too).
-__device__ __forceinline__ uint16_t f32_to_f16_runner(float v) {
-  const uint32_t u = __float_as_uint(v);
-  const uint32_t sign = (u >> 16) & 0x8000u;
-  int32_t e = (int32_t)((u >> 23) & 0xffu) - 127 + 15;
-  const uint32_t mantissa = u & 0x7fffffu;
-  if (e <= 0) {
-    const uint32_t shift = (uint32_t)(14 - e);
-    if (shift > 24) return (uint16_t)sign;
-    const uint32_t significand = 0x800000u | mantissa;
-    uint32_t half = significand >> shift;
-    if ((significand >> (shift - 1)) & 1u) ++half;
-    return (uint16_t)(sign | half);
-  }
-  if (e >= 31) return (uint16_t)(sign | 0x7c00u);
-  uint32_t m = mantissa >> 13;
-  if (mantissa & 0x1000u) {
-    ++m;
-    if (m == 0x400u) {
-      m = 0;
-      ++e;
-      if (e >= 31) return (uint16_t)(sign | 0x7c00u);
-    }
-  }
-  return (uint16_t)(sign | ((uint32_t)e << 10) | m);
-}
-
 __device__ __forceinline__ uint32_t ld8(const uint8_t *p) { return __ldg(p); }
 __device__ __forceinline__ uint32_t ld16(const uint8_t *p) { return ld8(p) | (ld8(p + 1) << 8); }
 

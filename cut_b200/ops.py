@@ -187,6 +187,14 @@ def embedding_blocks(indices: torch.Tensor, raw: torch.Tensor, fmt: int, rows: i
     return out
 
 
+def requant_q8_0_blocks(raw: torch.Tensor, fmt: int, rows: int, cols: int) -> torch.Tensor:
+    """Raw blocks of any dequantisable format -> Q8_0 GGUF blocks (uint8, rows * cols / 32 * 34 bytes)."""
+    out = torch.empty(rows * (cols // 32) * 34, dtype=torch.uint8, device=raw.device)
+    L.check(L.lib().cutb_requant_q8_0_blocks(fmt, raw.data_ptr(), raw.numel() * raw.element_size(), out.data_ptr(), rows, cols,
+                                             _stream_ptr()))
+    return out
+
+
 def argreduce(values: torch.Tensor, is_max: bool = True) -> torch.Tensor:
     """Index of the maximum / minimum as a one-element float tensor (the reference's output type and tie rule)."""
     out = torch.empty(1, dtype=torch.float32, device=values.device)

@@ -278,6 +278,11 @@ CUTB_API int cutb_transpose_q4(const void *in, void *out, uint32_t N, uint32_t K
  *   padding bytes of the outputs are not written.
  * cutb_quantize_rows_q8_0: n floats (n % 32 == 0, 16-byte aligned) -> int8 values and f16 scales,
  *   d = amax / 127, q = lround(x / d) (llama.cpp:488-505).
+ * cutb_requant_q8_0_blocks: any format cutb_dequant takes -> Q8_0 GGUF blocks (34 bytes per 32
+ *   weights, rows x cols / 32 of them), the exact dequantised values re-quantised as
+ *   cutb_quantize_rows_q8_0 does.  This is the runner's load-time treatment of the formats its
+ *   matmul does not take (Q4_1, Q5_0, Q5_K, Q6_K: llama.cpp:750-767, 934-1027), done on the device and
+ *   straight into the block layout cutb_qmatmul reads; `out` 2-byte aligned, cols % 32 == 0.
  */
 CUTB_API int cutb_separate_blocks(int format, const void *raw, uint64_t raw_bytes, void *values, void *scales, uint64_t rows,
                                   uint64_t cols, void *stream);
@@ -286,6 +291,8 @@ CUTB_API int cutb_transpose_2d(uint32_t elem_bytes, const void *in, void *out, u
 CUTB_API int cutb_requant_q4k_affine(const void *raw, uint64_t raw_bytes, void *packedT, void *scalesT, uint32_t N, uint32_t K,
                                      uint64_t ldp, uint64_t lds, void *stream);
 CUTB_API int cutb_quantize_rows_q8_0(const float *x, void *values, void *scales, uint64_t n, void *stream);
+CUTB_API int cutb_requant_q8_0_blocks(int format, const void *raw, uint64_t raw_bytes, void *out, uint64_t rows, uint32_t cols,
+                                      void *stream);
 
 /*
  * The operators on either side of the matmul in a decoder layer (first steps past the matmul

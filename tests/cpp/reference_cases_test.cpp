@@ -345,7 +345,7 @@ void reusableSurvivesWorkspaceGrowth() {
   rt->iface().wait(cb);
   std::vector<float> out1(N), out2(N), want(N);
   rt->copyFromTensor(tC, out1.data(), N * sizeof(float));
-  orc_qmatmul_blocks(1, A.data(), raw.data(), want.data(), nullptr, 1, K, N, N, 0, 0, 0);
+  orc_qmatmul_blocks(1, A.data(), raw.data(), want.data(), nullptr, 1, K, N, K, N, 0, 0, 0, 0);
   double num = 0, den = 0;
   for (uint32_t n = 0; n < N; ++n) num += (out1[n] - want[n]) * (double)(out1[n] - want[n]), den += want[n] * (double)want[n];
   CHECK(std::sqrt(num / den) <= 1e-3);

@@ -104,3 +104,30 @@ def test_quantize_rows_q8_0_bitexact(gpu, n):
     wv, ws = O.quantize_rows_q8_0(x)
     assert np.array_equal(vals.cpu().numpy(), wv)
     assert np.array_equal(scales.cpu().numpy().view(np.uint16), ws)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", [synth.Q6_K, synth.Q5_K, synth.Q4_1, synth.Q5_0, synth.Q4_K])
+def test_requant_to_q8_0_blocks_is_the_runners_requantisation(fmt):
+    """The runner turns the formats its matmul does not take into Q8_0 at load time: dequantise (exact), then
+    quantizeRowsQ8_0 (interface/runner/llama/llama.cpp:488-505, 750-767).  The device does both in one kernel and
+    writes GGUF Q8_0 blocks: byte-exact against the checker's composition, and the mat-vec over those blocks
+    agrees with the dense product over the original weights to the accuracy of an 8-bit re-encode."""
+    import torch
+
+    from cut_b200 import ops
+    from oracle import oracle as O
+
+    rows, cols = 24, 1024
+    raw = synth.make_weights(fmt, rows, cols, seed=70 + fmt)
+    w = O.dequant_rows(fmt, raw, rows, cols)
+    vals, scales = O.quantize_rows_q8_0(w.reshape(-1))
+    want = np.zeros((rows * cols // 32, 34), dtype=np.uint8)
+    want[:, 0:2] = scales.view(np.uint8).reshape(-1, 2)
+    want[:, 2:] = vals.view(np.uint8).reshape(-1, 32)
+    got = ops.requant_q8_0_blocks(torch.from_numpy(raw).cuda(), fmt, rows, cols)
+    assert np.array_equal(got.cpu().numpy(), want.reshape(-1))
+    a = synth.make_activations(1, cols, 3, np.float32)
+    out = ops.qmatmul(torch.from_numpy(a).cuda(), got, synth.Q8_0, rows).cpu().numpy()
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    assert np.linalg.norm(out - ref) / np.linalg.norm(ref) < 1e-2
