@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 HOST_LIB = os.path.join(HERE, "libcut_host.so")
-HOST_SOURCES = ["cut_api.cpp", "b200_compute.cpp"]
+HOST_SOURCES = ["cut_api.cpp", "b200_compute.cpp", "gguf_upload.cpp"]
 
 
 def _cuda_home() -> str:
@@ -74,7 +74,8 @@ def build_host(force: bool = False) -> str:
     build(force=force)
     hdir = os.path.join(CSRC, "host")
     srcs = [os.path.join(hdir, f) for f in HOST_SOURCES]
-    deps = srcs + [os.path.join(hdir, "cut_api.h"), os.path.join(CSRC, "..", "..", "include", "cutb.h"), LIB]
+    deps = srcs + [os.path.join(hdir, "cut_api.h"), os.path.join(hdir, "gguf_upload.h"),
+                   os.path.join(CSRC, "..", "..", "include", "cutb.h"), LIB]
     if force or _stale(HOST_LIB, deps):
         cuda = _cuda_home()
         cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", HOST_LIB, *srcs, f"-I{cuda}/include",

@@ -207,7 +207,7 @@ public:
     auto desc = KernelDesc::decode(words);
     if (!desc) throw std::runtime_error("B200Compute: not a kernel descriptor");
     switch (desc->op) {
-      case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case TransposeQ4: break;
+      case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case RequantQ8Blocks: case TransposeQ4: break;
       case RMSNorm: case Embedding: case EmbeddingCol: case ReduceArgmax: case ReduceArgmin: case Attention: break;
       case CacheWrite:
         if (desc->variant != FusedRoPEKVWriteOpNode::kVariant && desc->variant != BatchedKVCacheWriteOpNode::kVariant) throw std::runtime_error("B200Compute: no kernel for this CacheWrite operator");
@@ -412,6 +412,13 @@ private:
         const DeviceBuffer &raw = buf(d, 0), &out = buf(d, 1);
         cutbCheck(cutb_dequant(cutbFormat(k.format), raw.data, raw.size(), (float *)out.data, pc.rows, pc.cols,
                                pc.outputStride, stream_), "Dequantize");
+      } else if (k.op == RequantQ8Blocks) {
+        struct PC {
+          uint32_t rows, cols;
+        } pc = pushConstants<PC>(d);
+        const DeviceBuffer &raw = buf(d, 0), &out = buf(d, 1);
+        cutbCheck(cutb_requant_q8_0_blocks(cutbFormat(k.format), raw.data, raw.size(), out.data, pc.rows, pc.cols, stream_),
+                  "RequantQ8Blocks");
       } else if (k.op == TransposeQ4) {
         struct PC {
           uint32_t N, K, strideInHalf, strideOutHalf;

@@ -409,6 +409,37 @@ DequantOpNode::DequantOpNode(TensorStore &store, const Tensor &rawData, DequantF
   output_ = store.createTensorEmpty({rows_, cols_}, DataType::Float32);
 }
 
+RequantQ8BlocksOpNode::RequantQ8BlocksOpNode(TensorStore &store, const Tensor &rawData, DequantFormat format, uint32_t rows,
+                                             uint32_t cols, std::optional<uint32_t> spec)
+    : OpNode(RequantQ8Blocks, store, spec), format_(format), rows_(rows), cols_(cols) {
+  const auto &raw = store.getTensor(rawData);
+  if (raw.getDtype() != DataType::Int8 || raw.getShape().size() != 1)
+    throw std::runtime_error("requantQ8Blocks: raw data must be a 1D Int8 tensor");
+  if (cols % 32 != 0) throw std::runtime_error("requantQ8Blocks: cols must be a multiple of 32");
+  inputs_ = {rawData};
+  output_ = store.createTensorEmpty(outputShape(), DataType::Int8);
+}
+
+std::optional<std::vector<uint32_t>> RequantQ8BlocksOpNode::shader() const {
+  switch (format_) {
+    case DequantFormat::BF16: case DequantFormat::Q4_K: case DequantFormat::Q5_K: case DequantFormat::Q6_K:
+    case DequantFormat::Q8_0: case DequantFormat::Q4_0: case DequantFormat::Q4_1: case DequantFormat::Q5_0: break;
+    default: return std::nullopt;
+  }
+  KernelDesc d;
+  d.op = RequantQ8Blocks;
+  d.format = (uint32_t)format_;
+  d.dtypeA = d.dtypeB = (uint32_t)DataType::Int8;
+  return d.encode();
+}
+
+std::vector<uint8_t> RequantQ8BlocksOpNode::pushConstants() const {
+  struct {
+    uint32_t rows, cols;
+  } pc{rows_, cols_};
+  return toBytes(pc);
+}
+
 size_t DequantOpNode::shaderKey() const {
   return static_cast<size_t>(op_) | ((static_cast<size_t>(format_) & 0x1F) << 16);
 }
@@ -1033,6 +1064,10 @@ Tensor Operations::transposeQ4(const Tensor &packedInput, uint32_t N, uint32_t K
 
 Tensor Operations::dequantize(const Tensor &rawData, uint32_t format, uint32_t rows, uint32_t cols) {
   return dispatch(std::make_unique<DequantOpNode>(*store_, rawData, static_cast<DequantFormat>(format), rows, cols));
+}
+
+Tensor Operations::requantQ8Blocks(const Tensor &rawData, DequantFormat format, uint32_t rows, uint32_t cols) {
+  return dispatch(std::make_unique<RequantQ8BlocksOpNode>(*store_, rawData, format, rows, cols));
 }
 
 Tensor Operations::rmsNorm(const Tensor &x, const Tensor &weight, float eps, std::optional<uint32_t> spec) {

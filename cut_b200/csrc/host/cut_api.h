@@ -72,7 +72,9 @@ enum OperatorEnum : uint32_t {
   CacheWrite = 360, Attention = 361,
   MatMulQ8 = 371, MatMulQ4 = 374,
   MatMulQBlocks = 375,  // new: weights as raw GGUF blocks
-  Dequantize = 390, TransposeQ4 = 401,
+  Dequantize = 390,
+  RequantQ8Blocks = 391,  // new: any block format -> Q8_0 GGUF blocks on the device
+  TransposeQ4 = 401,
 };
 
 // ---- handles and buffers -------------------------------------------------------
@@ -362,6 +364,25 @@ private:
   uint32_t rows_, cols_, outputStride_;
 };
 
+/// Raw blocks of any DequantFormat -> Q8_0 GGUF blocks [rows * cols / 32 * 34 bytes], what the runner does on the
+/// CPU for the formats its matmul does not take (interface/runner/llama/llama.cpp:488-505, 750-767).
+class RequantQ8BlocksOpNode : public OpNode {
+public:
+  RequantQ8BlocksOpNode(TensorStore &store, const Tensor &rawData, DequantFormat format, uint32_t rows, uint32_t cols,
+                        std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return DataType::Int8; }
+  size_t shaderKey() const override { return static_cast<size_t>(op_) | ((static_cast<size_t>(format_) & 0x1F) << 16); }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return {rows_ * (cols_ / 32) * 34}; }
+  ThreadSize dispatchSize() const override { return {cols_ / 32, rows_, 1}; }
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "RequantQ8Blocks"; }
+
+private:
+  DequantFormat format_;
+  uint32_t rows_, cols_;
+};
+
 class TransposeQ4NibbleOpNode : public OpNode {
 public:
   TransposeQ4NibbleOpNode(TensorStore &store, const Tensor &packedInput, uint32_t N, uint32_t K,
@@ -612,6 +633,8 @@ public:
                             uint32_t N, const Tensor &d, std::optional<uint32_t> spec = {});
   Tensor transposeQ4(const Tensor &packedInput, uint32_t N, uint32_t K);
   Tensor dequantize(const Tensor &rawData, uint32_t format, uint32_t rows, uint32_t cols);
+  /// Raw blocks of `format` -> Q8_0 GGUF blocks (a 1-D Int8 tensor matmulBlocks takes with DequantFormat::Q8_0).
+  Tensor requantQ8Blocks(const Tensor &rawData, DequantFormat format, uint32_t rows, uint32_t cols);
   Tensor rmsNorm(const Tensor &x, const Tensor &weight, float eps = 1e-5f, std::optional<uint32_t> spec = {});
   Tensor embedding(const Tensor &indices, const Tensor &weight, const Tensor &preallocOutput = {},
                    std::optional<uint32_t> spec = {});

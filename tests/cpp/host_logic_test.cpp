@@ -7,6 +7,8 @@
 
 #include "check.h"
 #include "cut_api.h"
+#include "gguf_upload.h"
+#include "gguf_writer.h"
 
 using namespace cut;
 
@@ -447,6 +449,66 @@ void attentionNodes() {
   CHECK(f.rt.getTensor(out).getShape() == (std::vector<uint32_t>{nH * hd}));
 }
 
+// GGUF header parsing (interface/loader/gguf/gguf_reader.cpp:15-58, 268-291): a file written here with every scalar
+// metadata type, strings, arrays (skipped), a non-default alignment and three tensors.
+void ggufFileParsing() {
+  GGUFWriter w;
+  w.put<uint32_t>(0x46554747u);
+  w.put<uint32_t>(3);
+  w.put<uint64_t>(3);   // tensors
+  w.put<uint64_t>(9);   // metadata pairs
+  w.str("general.alignment"); w.put<uint32_t>(4); w.put<uint32_t>(64);
+  w.str("general.name"); w.put<uint32_t>(8); w.str("tiny");
+  w.str("llama.block_count"); w.put<uint32_t>(4); w.put<uint32_t>(2);
+  w.str("llama.rope.freq_base"); w.put<uint32_t>(6); w.put<float>(10000.0f);
+  w.str("some.i8"); w.put<uint32_t>(1); w.put<int8_t>(-3);
+  w.str("some.bool"); w.put<uint32_t>(7); w.put<uint8_t>(1);
+  w.str("some.u64"); w.put<uint32_t>(10); w.put<uint64_t>(1ull << 40);
+  w.str("tokens"); w.put<uint32_t>(9); w.put<uint32_t>(8); w.put<uint64_t>(3); w.str("a"); w.str("bc"); w.str("");  // array of strings
+  w.str("scores"); w.put<uint32_t>(9); w.put<uint32_t>(6); w.put<uint64_t>(4); for (int i = 0; i < 4; ++i) w.put<float>(1.5f * i);
+  // tensor directory: name, n_dims, dims (inner first), type, offset
+  w.str("blk.0.attn_q.weight"); w.put<uint32_t>(2); w.put<uint64_t>(64); w.put<uint64_t>(3); w.put<uint32_t>(2); w.put<uint64_t>(0);     // Q4_0: 3 x 2 blocks = 108 B
+  w.str("blk.0.ffn_down.weight"); w.put<uint32_t>(2); w.put<uint64_t>(256); w.put<uint64_t>(2); w.put<uint32_t>(14); w.put<uint64_t>(128);  // Q6_K: 2 x 210 B
+  w.str("output_norm.weight"); w.put<uint32_t>(1); w.put<uint64_t>(8); w.put<uint32_t>(0); w.put<uint64_t>(576);                        // F32: 32 B
+  const size_t dataStart = (w.b.size() + 63) / 64 * 64;
+  w.b.resize(dataStart + 576 + 32);
+  for (size_t i = dataStart; i < w.b.size(); ++i) w.b[i] = (uint8_t)(i * 7 + 1);
+  const std::string path = "/tmp/cutb_host_logic_test.gguf";
+  FILE *f = fopen(path.c_str(), "wb");
+  CHECK(f != nullptr);
+  fwrite(w.b.data(), 1, w.b.size(), f);
+  fclose(f);
+
+  GGUFFile g(path);
+  CHECK(g.version() == 3 && g.alignment() == 64 && g.dataOffset() == dataStart && g.tensors().size() == 3);
+  CHECK(*g.metaString("general.name") == "tiny" && *g.metaNumber("llama.block_count") == 2.0);
+  CHECK(*g.metaNumber("llama.rope.freq_base") == 10000.0 && *g.metaNumber("some.i8") == -3.0 && *g.metaNumber("some.bool") == 1.0);
+  CHECK(*g.metaNumber("some.u64") == (double)(1ull << 40) && !g.metaNumber("tokens") && !g.metaString("scores"));
+  const auto &q = g.info("blk.0.attn_q.weight");
+  CHECK(q.dims == (std::vector<uint64_t>{64, 3}) && q.type == 2 && q.bytes() == 108 && q.elements() == 192);
+  CHECK(g.info("blk.0.ffn_down.weight").bytes() == 420 && g.info("output_norm.weight").bytes() == 32);
+  const auto raw = g.readRaw("blk.0.ffn_down.weight");
+  CHECK(raw.size() == 420 && raw[0] == (uint8_t)((dataStart + 128) * 7 + 1) && raw[419] == (uint8_t)((dataStart + 128 + 419) * 7 + 1));
+  CHECK(g.has("output_norm.weight") && !g.has("nope"));
+  CHECK_THROWS(g.info("nope"), "Tensor not found");
+  CHECK(ggmlBlockGeometry(12)->second == 144 && !ggmlBlockGeometry(10) && *ggmlDequantFormat(6) == DequantFormat::Q5_0);
+  // malformed files are refused
+  {
+    std::vector<uint8_t> bad = w.b;
+    bad[0] = 'X';
+    FILE *fb = fopen("/tmp/cutb_host_logic_bad.gguf", "wb");
+    fwrite(bad.data(), 1, bad.size(), fb);
+    fclose(fb);
+    CHECK_THROWS(GGUFFile("/tmp/cutb_host_logic_bad.gguf"), "invalid magic");
+    fb = fopen("/tmp/cutb_host_logic_bad.gguf", "wb");
+    fwrite(w.b.data(), 1, dataStart + 100, fb);  // the second tensor would lie past the end
+    fclose(fb);
+    CHECK_THROWS(GGUFFile("/tmp/cutb_host_logic_bad.gguf"), "past the end");
+    remove("/tmp/cutb_host_logic_bad.gguf");
+  }
+  remove(path.c_str());
+}
+
 int main() {
   RUN(attentionNodes);
   RUN(layerOperatorNodes);
@@ -457,5 +519,6 @@ int main() {
   RUN(blockNodesAndDequant);
   RUN(dispatcherAndOperations);
   RUN(variantSelectorRules);
+  RUN(ggufFileParsing);
   return finish();
 }

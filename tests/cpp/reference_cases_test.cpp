@@ -8,6 +8,8 @@
 
 #include "check.h"
 #include "cut_api.h"
+#include "gguf_upload.h"
+#include "gguf_writer.h"
 
 using namespace cut;
 
@@ -370,6 +372,118 @@ void reusableSurvivesWorkspaceGrowth() {
   CHECK(bad == 0);
 }
 
+// GGUF file -> device weights without the CPU detour (interface/runner/llama/llama.cpp:831-866, 934-1027): raw blocks
+// are uploaded as they lie in the file; fused QKV is a concatenation of rows, gate / up become alternating rows for the
+// paired mat-vec, a Q6_K tensor is re-encoded to Q8_0 blocks on the device.  Every product is checked against the CPU
+// checker run on the bytes of the file.
+void ggufUploadAndMatmul() {
+  const uint32_t K = 512;
+  std::mt19937 gen(21);
+  auto blocks = [&](uint32_t rows, uint32_t blockBytes, uint32_t blockElems, uint32_t dOff, uint16_t dBits) {
+    std::vector<uint8_t> raw((size_t)rows * (K / blockElems) * blockBytes);
+    for (auto &b : raw) b = (uint8_t)gen();
+    for (size_t blk = 0; blk < raw.size() / blockBytes; ++blk) std::memcpy(&raw[blk * blockBytes + dOff], &dBits, 2);
+    return raw;
+  };
+  auto q = blocks(32, 18, 32, 0, 0x2000), k = blocks(16, 18, 32, 0, 0x2000), v = blocks(16, 18, 32, 0, 0x2000);
+  auto gate = blocks(48, 144, 256, 0, 0x1C00), up = blocks(48, 144, 256, 0, 0x1C00);
+  for (auto *t : {&gate, &up})
+    for (size_t blk = 0; blk < t->size() / 144; ++blk) { uint16_t m = 0x1800; std::memcpy(&(*t)[blk * 144 + 2], &m, 2); }
+  auto down = blocks(24, 210, 256, 208, 0x1400);
+  std::vector<float> norm(K);
+  for (auto &x : norm) x = 0.5f + (float)(gen() % 100) / 100.0f;
+  GGUFWriter w;
+  w.header(7, 0);
+  uint64_t off = 0;
+  auto place = [&](size_t bytes) { const uint64_t o = off; off = (off + bytes + 31) / 32 * 32; return o; };
+  const uint64_t oq = place(q.size()), ok_ = place(k.size()), ov = place(v.size()), og = place(gate.size()), ou = place(up.size()),
+                 od = place(down.size()), on = place(norm.size() * 4);
+  w.tensor2d("q", K, 32, 2, oq); w.tensor2d("k", K, 16, 2, ok_); w.tensor2d("v", K, 16, 2, ov);
+  w.tensor2d("gate", K, 48, 12, og); w.tensor2d("up", K, 48, 12, ou); w.tensor2d("down", K, 24, 14, od);
+  w.str("norm"); w.put<uint32_t>(1); w.put<uint64_t>(K); w.put<uint32_t>(0); w.put<uint64_t>(on);
+  const size_t dataStart = (w.b.size() + 31) / 32 * 32;
+  w.b.resize(dataStart + off);
+  auto fill = [&](uint64_t o, const void *src, size_t n) { std::memcpy(w.b.data() + dataStart + o, src, n); };
+  fill(oq, q.data(), q.size()); fill(ok_, k.data(), k.size()); fill(ov, v.data(), v.size()); fill(og, gate.data(), gate.size());
+  fill(ou, up.data(), up.size()); fill(od, down.data(), down.size()); fill(on, norm.data(), norm.size() * 4);
+  const std::string path = "/tmp/cutb_reference_cases.gguf";
+  CHECK(w.save(path));
+
+  GGUFFile file(path);
+  GGUFUploader upl(*rt, file);
+  std::vector<float> A(K);
+  for (auto &x : A) x = (float)((int)(gen() % 33) - 16) / 16.0f;
+  auto tA = rt->createTensor({K}, DataType::Float32, A.data());
+  auto relL2 = [](const std::vector<float> &got, const std::vector<float> &want) {
+    double num = 0, den = 0;
+    for (size_t i = 0; i < want.size(); ++i) num += (got[i] - want[i]) * (double)(got[i] - want[i]), den += want[i] * (double)want[i];
+    return std::sqrt(num / den);
+  };
+  {  // fused QKV: 64 rows of Q4_0, byte-identical to q | k | v
+    BlockWeight qkv = upl.uploadFused({"q", "k", "v"});
+    CHECK(qkv.N == 64 && qkv.K == K && qkv.format == DequantFormat::Q4_0 && !qkv.requantized);
+    std::vector<uint8_t> all(q);
+    all.insert(all.end(), k.begin(), k.end());
+    all.insert(all.end(), v.begin(), v.end());
+    std::vector<uint8_t> dev(all.size());
+    rt->copyFromTensor(qkv.raw, dev.data(), dev.size());
+    CHECK(dev == all);
+    auto tC = rt->ops().matmulBlocks(tA, qkv.raw, qkv.format, qkv.N);
+    std::vector<float> got(64), want(64);
+    rt->copyFromTensor(tC, got.data(), got.size() * sizeof(float));
+    orc_qmatmul_blocks(1, A.data(), all.data(), want.data(), nullptr, 1, K, 64, K, 64, 0, 0, 0, 0);
+    CHECK(relL2(got, want) <= 1e-3);
+  }
+  {  // gate / up as alternating rows
+    BlockWeight gu = upl.uploadPaired("gate", "up");
+    CHECK(gu.N == 96 && gu.format == DequantFormat::Q4_K);
+    std::vector<uint8_t> dev((size_t)96 * 2 * 144);
+    rt->copyFromTensor(gu.raw, dev.data(), dev.size());
+    int bad = 0;
+    for (uint32_t i = 0; i < 48; ++i) {
+      bad += std::memcmp(&dev[(size_t)(2 * i) * 288], &gate[(size_t)i * 288], 288) != 0;
+      bad += std::memcmp(&dev[(size_t)(2 * i + 1) * 288], &up[(size_t)i * 288], 288) != 0;
+    }
+    CHECK(bad == 0);
+    CHECK_THROWS(upl.uploadPaired("gate", "down"), "paired rows need");
+  }
+  {  // Q6_K: re-encoded to Q8_0 blocks on the device, the product agrees with the dense product over the exact weights
+    BlockWeight d = upl.upload("down");
+    CHECK(d.requantized && d.format == DequantFormat::Q8_0 && d.N == 24);
+    auto tC = rt->ops().matmulBlocks(tA, d.raw, d.format, d.N);
+    std::vector<float> got(24), want(24), wf((size_t)24 * K);
+    rt->copyFromTensor(tC, got.data(), got.size() * sizeof(float));
+    orc_dequant_rows(4, down.data(), wf.data(), 24, K, K);
+    for (uint32_t n = 0; n < 24; ++n) {
+      double acc = 0;
+      for (uint32_t kk = 0; kk < K; ++kk) acc += (double)A[kk] * wf[(size_t)n * K + kk];
+      want[n] = (float)acc;
+    }
+    CHECK(relL2(got, want) <= 1e-2);  // an 8-bit re-encode of 6-bit weights
+    // and the fp32 form of the same tensor is the checker's dequantisation, bit for bit
+    auto tF = upl.uploadF32("down");
+    std::vector<float> devf((size_t)24 * K);
+    rt->copyFromTensor(tF, devf.data(), devf.size() * sizeof(float));
+    CHECK(std::memcmp(devf.data(), wf.data(), devf.size() * sizeof(float)) == 0);
+  }
+  {  // mixed formats fuse through Q8_0
+    BlockWeight m = upl.uploadFused({"k", "down"});
+    CHECK(m.requantized && m.format == DequantFormat::Q8_0 && m.N == 40);
+    auto tC = rt->ops().matmulBlocks(tA, m.raw, m.format, m.N);
+    std::vector<float> got(40);
+    rt->copyFromTensor(tC, got.data(), got.size() * sizeof(float));
+    std::vector<float> wantK(16);
+    orc_qmatmul_blocks(1, A.data(), k.data(), wantK.data(), nullptr, 1, K, 16, K, 16, 0, 0, 0, 0);
+    std::vector<float> head(got.begin(), got.begin() + 16);
+    CHECK(relL2(head, wantK) <= 1e-2);
+  }
+  auto tN = upl.uploadF32("norm");
+  std::vector<float> nf(K);
+  rt->copyFromTensor(tN, nf.data(), nf.size() * sizeof(float));
+  CHECK(nf == norm);
+  remove(path.c_str());
+}
+
 void errorBehaviour() {
   auto a = rt->createTensor({64}, DataType::Float32);
   auto b = rt->createTensor({32, 16}, DataType::Int8);
@@ -625,6 +739,7 @@ int main() {
     RUN(blocksEntryPoint);
     RUN(reusableCommandBuffer);
     RUN(reusableSurvivesWorkspaceGrowth);
+    RUN(ggufUploadAndMatmul);
     RUN(errorBehaviour);
     RUN(rmsNormCases);
     RUN(argReduceCases);

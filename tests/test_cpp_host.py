@@ -14,7 +14,7 @@ OUT = os.path.join(ROOT, "tests", "cpp", "build")
 
 def _compile(args, exe):
     os.makedirs(OUT, exist_ok=True)
-    r = subprocess.run(["g++", "-O1", "-std=c++17", f"-I{HOST}", "-o", exe, *args], capture_output=True, text=True)
+    r = subprocess.run(["g++", "-O1", "-std=c++17", f"-I{HOST}", f"-I{CPP}", "-o", exe, *args], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
 
 
@@ -26,7 +26,7 @@ def _run(exe):
 
 def test_host_logic_cpu():
     exe = os.path.join(OUT, "host_logic_test")
-    _compile([os.path.join(CPP, "host_logic_test.cpp"), os.path.join(HOST, "cut_api.cpp")], exe)
+    _compile([os.path.join(CPP, "host_logic_test.cpp"), os.path.join(HOST, "cut_api.cpp"), os.path.join(HOST, "gguf_upload.cpp")], exe)
     _run(exe)
 
 
