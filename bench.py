@@ -46,9 +46,11 @@ N_ROWS, K_COLS, BATCH = 11008, 4096, 1
 REPLICAS = 32
 METRIC = "qgemv_hbm_gbs"
 UNIT = "GB/s"
+WORKLOAD = f"configs[1]: {FMT_NAME} decode mat-vec {N_ROWS}x{K_COLS} (GGUF blocks), fp16 activation, batch {BATCH}"
 
-# DRAM bytes (read + write) per mat-vec launch seen by ncu for this workload
-# (profiles/qgemv_q4_0_11008x4096_b1.md: dram__bytes_read.sum + dram__bytes_write.sum).
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one mat-vec launch of this workload, from an ncu
+# capture of this kernel (a profiler cannot run inside the timed region, so the figure is carried here and the
+# line says where it comes from).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 25408768
 
 
@@ -153,7 +155,7 @@ def run_reference(args) -> None:
     from cut_b200 import synth
     from oracle import oracle as O
 
-    sample_rows = 2752  # a quarter of the 11008 rows per step keeps K steps within minutes
+    sample_rows = N_ROWS  # one step = one whole mat-vec of the workload (about 0.15 s on this path)
     w = synth.make_weights(synth.Q4_0, sample_rows, K_COLS, seed=9100)
     a = synth.make_activations(BATCH, K_COLS, 77, np.float16).astype(np.float32)
     use_ref = O.have_ref()
@@ -179,15 +181,14 @@ def run_reference(args) -> None:
     bytes_per_step = algorithmic_bytes(sample_rows, K_COLS, BATCH)
     val = args.steps * bytes_per_step / dt / 1e9
     kind = "reference" if use_ref else "port"
-    sample = (f"{args.steps} steps of {sample_rows}x{K_COLS} {FMT_NAME} rows (1/4 of the workload): "
+    sample = (f"{args.steps} steps of one {sample_rows}x{K_COLS} {FMT_NAME} mat-vec (the whole workload tensor): "
               + ("dequantised by the reference's gguf_reader.cpp (1 thread), " if use_ref else "dequantised by the C port, ")
               + "contracted by the restated scalar loop of its test harness (all threads)")
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"configs[1]: {FMT_NAME} decode mat-vec {N_ROWS}x{K_COLS}, fp16 activation, batch {BATCH}",
-                   "host": "cpu"},
+        "config": {"workload": WORKLOAD, "host": "cpu"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": O.num_threads(), "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -259,6 +260,118 @@ def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = 
             "activations": "fp32, staged at 16 bits per 32-k block"}
 
 
+def chain_us(dev, fmt: int, n: int, k: int, m: int, act_dtype, flags: int = 0, total_mb: float = 600.0, seed: int = 51) -> dict:
+    """Device time of one quantized matmul over GGUF blocks inside a CUDA-graph chain of launches that cycle
+    through enough distinct weight tensors (>= total_mb, so L2 cannot serve them); returns us per launch, the
+    algorithmic GB/s (weights + activations + output once each) and the variant that ran."""
+    import torch
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    rb = synth.row_bytes(fmt, k)
+    reps = max(2, min(64, int(total_mb * 1e6 // (n * rb)) + 1))
+    base = torch.from_numpy(synth.make_weights(fmt, n, k, seed=seed)).to(dev)
+    W = torch.empty((reps, base.numel()), dtype=torch.uint8, device=dev)
+    for r in range(reps):
+        W[r] = torch.roll(base, shifts=synth.BLOCK_BYTES[fmt] * 7 * r)
+    A = torch.from_numpy(synth.make_activations(m, k, seed + 1, act_dtype)).to(dev)
+    C = torch.zeros((reps, m, n), dtype=torch.float32, device=dev)
+    descs, keep = [], []
+    for r in range(reps):
+        d, _, kp = ops.make_desc(A, W[r], fmt, n, C_out=C[r], flags=flags)
+        need = ops.workspace_bytes(d)
+        if need:
+            ws = torch.empty(need, dtype=torch.uint8, device=dev)
+            d.workspace, d.workspace_bytes = ws.data_ptr(), need
+            kp = kp + (ws,)
+        descs.append(d)
+        keep.append(kp)
+    variant = ops.select_variant(descs[0])
+
+    def sweep():
+        for d in descs:
+            ops.launch(d)
+
+    sweep()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        sweep()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    iters = max(3, int(2000 // reps))
+    for _ in range(3):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b) * 1e3 / (iters * reps))
+    nbytes = n * rb + m * k * A.element_size() + m * n * 4
+    del g, W, C
+    return {"us_per_launch": best, "GB/s": nbytes / best / 1e3, "algorithmic_bytes": nbytes, "weight_copies": reps,
+            "variant": L.lib().cutb_variant_name(variant).decode()}
+
+
+def planes_chain_us(dev, n: int, k: int) -> dict:
+    """Q4_0 mat-vec over the reference's runtime layout ([K, N / 2] nibbles with even n in the low nibble, fp16 scales
+    [K / 32, N]: what its loader's plane separation, its Q4 transpose and its scale transpose produce), batch 1,
+    weights cycled over distinct copies, in a CUDA graph."""
+    import torch
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    reps = 24
+    raw = torch.from_numpy(synth.make_weights(synth.Q4_0, n, k, seed=71)).to(dev)
+    vals, scales = ops.separate_blocks(raw, L.Q4_0, n, k)      # [N, K / 2] GGML nibbles, [N, K / 32] f16 bits
+    packed = ops.transpose_q4(vals, n, k)                      # [K, pad4(N / 2)]
+    scalesT = ops.transpose_2d(scales, ldo=(n + 3) // 4 * 4)   # [K / 32, pad4(N)]
+    P = torch.stack([torch.roll(packed, shifts=13 * r, dims=1) for r in range(reps)])
+    S = torch.stack([scalesT for _ in range(reps)])
+    A = torch.from_numpy(synth.make_activations(1, k, 72, np.float32)).to(dev)
+    C = torch.zeros((reps, 1, n), dtype=torch.float32, device=dev)
+    descs = [ops.make_desc(A, P[r], L.Q4_0, n, layout=L.LAYOUT_KN_PLANES, scales=S[r], ldb=packed.stride(0), lds=scalesT.stride(0),
+                           C_out=C[r]) for r in range(reps)]
+
+    def sweep():
+        for d, _, _ in descs:
+            ops.launch(d)
+
+    sweep()
+    torch.cuda.synchronize()
+    # the plane kernel against the block kernel on the same weights (replica 0 is not rotated)
+    ref = ops.qmatmul(A, raw, L.Q4_0, n)
+    rel = float(torch.linalg.norm(C[0] - ref) / torch.linalg.norm(ref))
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        sweep()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = 30
+    a.record()
+    for _ in range(iters):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1e3 / (iters * reps)
+    nbytes = k * (n // 2) + (k // 32) * n * 2 + k * 4 + n * 4
+    variant = L.lib().cutb_variant_name(ops.select_variant(descs[0][0])).decode()
+    return {"us_per_launch": us, "GB/s": nbytes / us / 1e3, "algorithmic_bytes": nbytes, "variant": variant,
+            "rel_l2_vs_block_kernel": rel, "weight_copies": reps}
+
+
+def projection_shapes_70b():
+    """configs[4]: the projections of a 70B-shape decoder layer as (name, N rows, K) of Q4_0 weights."""
+    return [("attn_q/o 8192x8192", 8192, 8192), ("ffn_gate/up 28672x8192", 28672, 8192), ("ffn_down 8192x28672", 8192, 28672)]
+
+
 def secondary_measurements(dev) -> dict:
     """Context numbers for the other benchmark configurations (not the headline value):
     configs[0] Q8_0 4096x4096 fp32 mat-vec (GB/s, weights cycled over 32 copies) and
@@ -323,7 +436,9 @@ def secondary_measurements(dev) -> dict:
     tf = flops / us / 1e6
     out["configs[2]_q4_k_prefill_gemm_512x4096x14336"] = {
         "us_per_launch": us, "TFLOP/s": tf,
+        "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"] if "bf16_tflops" in peaks else None,
         "frac_of_measured_bf16_sustained": tf / peaks["bf16_tflops_sustained"] if "bf16_tflops_sustained" in peaks else None,
+        "peak_note": "timed alone for 20 launches, so the burst figure is the roofline; the sustained one is for context",
         "kernel": "tcgen05.mma kind::f16, TMEM accumulators"}
     del A, C, d, keep
 
@@ -341,7 +456,189 @@ def secondary_measurements(dev) -> dict:
                                       "frac_of_measured_hbm": (dq_bytes / us / 1e3) / peaks["hbm_gbs"] if "hbm_gbs" in peaks else None}
     del outs, W
     torch.cuda.empty_cache()
+
+    hbm = peaks.get("hbm_gbs")
+    # configs[1] at batch 8 (same weight bytes, eight activation rows)
+    b8 = chain_us(dev, synth.Q4_0, N_ROWS, K_COLS, 8, np.float16)
+    b8["frac_of_measured_hbm"] = b8["GB/s"] / hbm if hbm else None
+    out["configs[1]_q4_0_11008x4096_batch8"] = b8
+    # the layout the reference's unchanged loader and runner hand over: [K, N] planes (nibbles [K, N / 2] after its
+    # Q4 transpose, fp16 scales [K / 32, N]), batch 1, against the block layout above
+    out["configs[1]_q4_0_kn_planes_batch1"] = planes_chain_us(dev, N_ROWS, K_COLS)
+    if hbm:
+        out["configs[1]_q4_0_kn_planes_batch1"]["frac_of_measured_hbm"] = out["configs[1]_q4_0_kn_planes_batch1"]["GB/s"] / hbm
+    # configs[4] on one GPU: the whole 70B-shape projections (the N > 1 runs shard these same tensors)
+    proj = {}
+    for name, n, k in projection_shapes_70b():
+        for m in (1, 8, 32):
+            r = chain_us(dev, synth.Q4_0, n, k, m, np.float16, total_mb=400.0)
+            r["frac_of_measured_hbm"] = r["GB/s"] / hbm if hbm else None
+            proj[f"{name} batch {m}"] = r
+    out["configs[4]_70b_q4_0_projections_1gpu"] = proj
+    torch.cuda.empty_cache()
     out["configs[3]_llama_q4_k_decode_batch1"] = decode_measurement(dev)
+    return out
+
+
+def e2e_host_boundary(device: int, base_weights: np.ndarray, a_host_all, steps: int):
+    """The same step through the C++ operator API the reference's runner calls (Operations::matmulBlocks recorded
+    once into a reusable command buffer; per step ComputeInterface::copyDataToBuffer of every activation from
+    pinned host memory, resubmit, wait, copyDataFromBuffer of every result), driven through libcut_host.so's C
+    entry.  Returns (seconds, h2d bytes per step, d2h bytes per step, results [REPLICAS, BATCH, N])."""
+    import ctypes as C
+
+    import torch
+
+    from cut_b200 import build as B
+
+    lib = C.CDLL(B.build_host())
+    f = lib.cut_host_e2e_matvec_blocks
+    f.restype = C.c_int
+    f.argtypes = [C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p,
+                  C.c_int, C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_double), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
+                  C.c_char_p, C.c_size_t]
+    c_host = torch.empty((REPLICAS, BATCH, N_ROWS), dtype=torch.float32).pin_memory()
+    secs, h2d, d2h = C.c_double(0), C.c_uint64(0), C.c_uint64(0)
+    err = C.create_string_buffer(512)
+    w = np.ascontiguousarray(base_weights)
+    rc = f(device, 17, N_ROWS, K_COLS, BATCH, REPLICAS, w.ctypes.data, w.size, 18 * 7, a_host_all.data_ptr(), 1, c_host.data_ptr(), 3,
+           steps, C.byref(secs), C.byref(h2d), C.byref(d2h), err, len(err))
+    if rc != 0:
+        raise SystemExit(f"bench: the C++ operator API failed: {err.value.decode()}")
+    return secs.value, h2d.value, d2h.value, c_host
+
+
+def tp_projection_measurements(dev, rank: int, world: int) -> dict:
+    """configs[4] at N > 1: the 70B-shape Q4_0 projections as FIXED tensors row-sharded over the ranks (strong
+    scaling: rank r owns rows [r N / g, (r + 1) N / g) of every tensor, activations replicated), with ONE exchange
+    per projection, as a decoder needs it (every projection's output feeds the next).  Three ways per shape and batch:
+    the local mat-vecs alone, the fused exchange (scatter epilogue + one bounded exchange kernel per projection) and
+    an NCCL all-gather per projection.  Batch 32 runs the tensor-core GEMM, which has no scatter epilogue: NCCL only.
+    Two output slots alternate: the exchange of projection t + 1 is passed only once every rank has launched it, i.e.
+    has consumed projection t's output, so slot t & 1 is free again at t + 2 (a decoder's own data dependence).
+    Times are device times of a CUDA-graph chain over distinct weight copies, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth, tp
+
+    out = {}
+    stream_of = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+
+    def max_over_ranks(v: float) -> float:
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, reps: int) -> float:
+        """us per projection of `fn` (one pass over `reps` projections), replayed from a CUDA graph."""
+        fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        iters = max(3, 600 // reps)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = max_over_ranks(a.elapsed_time(b) * 1e3 / (iters * reps))
+        del g
+        return us
+
+    for name, n, k in projection_shapes_70b():
+        lo, hi = tp.shard_rows(n, rank, world)
+        rows = hi - lo
+        rb = synth.row_bytes(synth.Q4_0, k)
+        reps = max(2, min(48, int(300e6 // (rows * rb)) + 1))
+        base = torch.from_numpy(synth.make_weights(synth.Q4_0, rows, k, seed=400 + rank)).to(dev)
+        W = torch.empty((reps, base.numel()), dtype=torch.uint8, device=dev)
+        for r in range(reps):
+            W[r] = torch.roll(base, shifts=18 * 7 * r)
+        for m in (1, 8, 32):
+            A = torch.from_numpy(synth.make_activations(m, k, 401, np.float16)).to(dev)
+            c_local = torch.zeros((m, rows), dtype=torch.float32, device=dev)
+            gathered = torch.zeros((world, m, rows), dtype=torch.float32, device=dev)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            descs, keep, ws = [], [], None
+            for r in range(reps):
+                d, _, kp = ops.make_desc(A, W[r], L.Q4_0, rows, C_out=c_local, status=status)
+                need = ops.workspace_bytes(d)
+                if need:
+                    # one scratch block for all copies: the launches are ordered on one stream
+                    ws = ws if ws is not None else torch.empty(need, dtype=torch.uint8, device=dev)
+                    d.workspace, d.workspace_bytes = ws.data_ptr(), need
+                descs.append(d)
+                keep.append(kp)
+            variant = ops.select_variant(descs[0])
+            equal_shards = all(tp.shard_rows(n, q, world)[1] - tp.shard_rows(n, q, world)[0] == rows for q in range(world))
+
+            def local_only():
+                for d in descs:
+                    ops.launch(d)
+
+            def with_nccl():
+                for d in descs:
+                    ops.launch(d)
+                    dist.all_gather_into_tensor(gathered.view(-1), c_local.view(-1))
+
+            shard_bytes = rows * rb + m * k * 2 + m * rows * 4
+            full_bytes = n * rb + m * k * 2 + m * n * 4
+            res = {"variant": L.lib().cutb_variant_name(variant).decode(), "rows_per_rank": rows, "weight_copies": reps}
+            us = timed(local_only, reps)
+            res["no_exchange"] = {"us_per_projection": us, "GB/s_per_gpu": shard_bytes / us / 1e3, "GB/s_aggregate": world * shard_bytes / us / 1e3}
+            if equal_shards:
+                us = timed(with_nccl, reps)
+                res["nccl_all_gather_per_projection"] = {"us_per_projection": us, "GB/s_per_gpu": shard_bytes / us / 1e3,
+                                                         "GB/s_aggregate": full_bytes / us / 1e3}
+            if variant == L.VARIANT_GEMV_MMA:
+                grp = tp.ScatterGroup(m, n, slots=2, device=dev)
+                sdescs = []
+                for r in range(reps):
+                    d, _, kp = ops.make_desc(A, W[r], L.Q4_0, rows, C_out=c_local, status=grp.status, variant=L.VARIANT_GEMV_MMA)
+                    if descs[r].workspace:
+                        d.workspace, d.workspace_bytes = descs[r].workspace, descs[r].workspace_bytes
+                    sdescs.append(d)
+                    keep.append(kp)
+                peers = [grp.peers(0), grp.peers(1)]
+
+                def with_fused():
+                    st = stream_of()
+                    for r, d in enumerate(sdescs):
+                        grp.launch(d, peers[r & 1], st)
+                        grp.exchange(st)
+
+                # parity before timing: the assembled output of the last projection of a pass equals, bit for bit,
+                # what mat-vec + all-gather of that projection gives (split-K shapes included)
+                with_fused()
+                ops.launch(descs[reps - 1])
+                dist.all_gather_into_tensor(gathered.view(-1), c_local.view(-1))
+                torch.cuda.synchronize()
+                ok = True
+                if equal_shards:
+                    plain = gathered.permute(1, 0, 2).reshape(m, n)
+                    ok = bool(torch.equal(plain, grp.out[(reps - 1) & 1])) and int(grp.status.item()) == 0
+                flag = torch.tensor([0 if ok else 1], dtype=torch.int32, device=dev)
+                dist.all_reduce(flag)
+                res["fused_equals_matvec_plus_all_gather_bit_for_bit"] = int(flag.item()) == 0
+                if int(flag.item()) == 0:
+                    us = timed(with_fused, reps)
+                    res["fused_exchange_per_projection"] = {"us_per_projection": us, "GB/s_per_gpu": shard_bytes / us / 1e3,
+                                                            "GB/s_aggregate": full_bytes / us / 1e3}
+                dist.barrier()
+                grp.close()
+            out[f"{name} batch {m}"] = res
+            del descs, keep, gathered, c_local
+        del W, base
+        torch.cuda.empty_cache()
     return out
 
 
@@ -595,6 +892,23 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e_value = world * e2e_steps * REPLICAS * bytes_per_launch / e2e_s / 1e9
+    e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": world * a_host_all.numel() * 2,
+           "d2h_bytes_per_step": world * c_host_all.numel() * 4, "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps,
+           "graph": bool(g3), "path": "C ABI (cutb_qmatmul) with torch copies: one upload of the step's activations, the step's "
+           "mat-vecs, one download of the results, replayed as one CUDA graph"}
+    e2e_extra = {}
+    if world == 1:
+        # N = 1: the headline end-to-end number goes through the boundary the reference's runner calls (the C++ operator
+        # API); the C-ABI figure above stays beside it as context
+        hs, h2d, d2h, c_hb = e2e_host_boundary(local_rank, base, a_host_all, e2e_steps)
+        rel = float(np.linalg.norm(c_hb[REPLICAS - 1, :, :rows].numpy() - chk) / np.linalg.norm(chk))
+        if not rel <= 1e-3:
+            raise SystemExit(f"bench: the C++ operator API's output disagrees with dense matmul over dequant (rel-L2 {rel})")
+        e2e_extra = {"e2e_c_abi_graph": e2e}
+        e2e = {"value": e2e_steps * REPLICAS * bytes_per_launch / hs / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": 1e3 * hs / e2e_steps,
+               "path": "C++ operator API (Operations::matmulBlocks -> Dispatcher -> B200Compute): per step copyDataToBuffer of "
+               "every activation, resubmit of the recorded command buffer, wait, copyDataFromBuffer of every result"}
 
     if int(status.item()) != 0:
         raise SystemExit(f"bench: device status word = {int(status.item())}")
@@ -617,6 +931,10 @@ def run_ours(args) -> None:
         t = torch.tensor(local, dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)  # times: slowest rank; flags are stored negated, so MAX is "any rank failed"
         all_ok, all_finite = float(t[3].item()) < 0, float(t[2].item()) < 0
+        try:
+            extra_tp = {"configs[4]_70b_q4_0_projections_row_sharded": tp_projection_measurements(dev, rank, world)}
+        except Exception as e:  # noqa: BLE001  (every rank raises or none: the steps inside are collective)
+            extra_tp = {"configs[4]_70b_q4_0_projections_row_sharded": {"error": f"{type(e).__name__}: {e}"}}
         if all_ok and dm is not None:
             extra = {"configs[3]_llama_q4_k_decode_replicas": {
                 "mode": "independent replicas: one batch-1 sequence per GPU, no exchange; time = max over ranks",
@@ -625,6 +943,7 @@ def run_ours(args) -> None:
                 "kernel_launches_per_token": dm["kernel_launches_per_token"]}}
         else:
             extra = {"configs[3]_llama_q4_k_decode_replicas": {"error": err or "another rank failed"}}
+        extra.update(extra_tp)
         barrier()
 
     cpu = None
@@ -638,7 +957,7 @@ def run_ours(args) -> None:
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {
-                "workload": f"configs[1]: {FMT_NAME} decode mat-vec {N_ROWS}x{K_COLS} (GGUF blocks), fp16 activation, batch {BATCH}",
+                "workload": WORKLOAD,
                 "replicas_per_step": REPLICAS,
                 "l2": f"{REPLICAS} distinct weight tensors cycled ({REPLICAS * base.size / 1e6:.0f} MB > 126 MB L2)",
                 "parallelism": "single GPU" if world == 1 else (
@@ -647,14 +966,13 @@ def run_ours(args) -> None:
                 "graph": graph is not None,
                 **({"exchange_note": exchange_note} if exchange_note else {}),
                 "pct_of_8TBs": 100.0 * value / world / 8000.0,
-                "also_measured": extra,
+                "also_measured": {**extra, **e2e_extra},
             },
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": f"of {peak_kind}",
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_source": "ncu capture of this kernel and workload (per launch)",
+                         "peak_kind": f"of {peak_kind}",
                          "us_per_launch": us_per_launch, "algorithmic_bytes_per_launch": bytes_per_launch},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": world * a_host_all.numel() * 2,
-                    "d2h_bytes_per_step": world * c_host_all.numel() * 4, "steps": e2e_steps,
-                    "ms_per_step": 1e3 * e2e_s / e2e_steps, "graph": bool(g3)},
+            "e2e": e2e,
             "gpu_launches": launches,
             "clocks": clocks,
         }
@@ -667,6 +985,8 @@ def run_ours(args) -> None:
         # has finished its work and synchronised; the process exit releases the NCCL resources.
         del graph, g2, g3
         torch.cuda.synchronize()
+        if grp is not None:
+            grp.close()  # unmap the peers' buffers while every rank is still alive
         dist.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()

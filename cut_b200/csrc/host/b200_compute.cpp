@@ -14,6 +14,8 @@
 // Errors surface as std::runtime_error, like the reference's logErr.
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cstring>
 #include <string>
 
 #include "../../../include/cutb.h"
@@ -106,6 +108,7 @@ public:
     cudaCheck(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate");
     cudaCheck(cudaMalloc(&status_, sizeof(int)), "cudaMalloc(status)");
     cudaCheck(cudaMemsetAsync(status_, 0, sizeof(int), stream_), "cudaMemset(status)");
+    cudaCheck(cudaHostAlloc((void **)&stage_, kStageBytes, cudaHostAllocDefault), "cudaHostAlloc(staging)");
     caps_.backend = ComputeBackend::CUDA;
     caps_.cooperativeMatrix = true;  // tensor-core variants exist
     caps_.integerDotProduct = true;
@@ -116,6 +119,7 @@ public:
     workspace_.reset();
     attnWs_.reset();
     cudaFree(status_);
+    cudaFreeHost(stage_);
     cudaStreamDestroy(stream_);
   }
 
@@ -131,8 +135,9 @@ public:
     activeBytes_ += buf->size();
     ++bufferCount_;
     ComputeHandle h(buf);
+    if (!host || buf->size() != buf->calculateActualSize())
+      cudaCheck(cudaMemsetAsync(buf->data, 0, bytes, stream_), "cudaMemsetAsync");  // padding reads as zero
     if (host) upload(*buf, host);
-    else cudaCheck(cudaMemsetAsync(buf->data, 0, bytes, stream_), "cudaMemsetAsync");
     return h;
   }
 
@@ -178,9 +183,7 @@ public:
     }
     if (b->innerDimSize() != b->innerDimPadded()) throw std::runtime_error("copyDataToBuffer: partial copy into a padded buffer");
     if (destOffset + copySize > b->size()) throw std::runtime_error("copyDataToBuffer: out of range");
-    cudaCheck(cudaMemcpyAsync((uint8_t *)b->data + destOffset, (const uint8_t *)host + srcOffset, copySize,
-                              cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
-    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    uploadBytes((uint8_t *)b->data + destOffset, (const uint8_t *)host + srcOffset, copySize);
   }
 
   void copyDataFromBuffer(const ComputeHandle &src, void *host, size_t copySize, size_t srcOffset, size_t destOffset, bool,
@@ -189,6 +192,17 @@ public:
     if (!b) throw std::runtime_error("copyDataFromBuffer: not a buffer");
     if (b->innerDimSize() == b->innerDimPadded() || b->getShape().size() <= 1) {
       if (srcOffset + copySize > b->size()) throw std::runtime_error("copyDataFromBuffer: out of range");
+      if (copySize <= kStageBytes) {
+        // through the pinned block: a device-to-host copy into pageable memory is staged by the driver with an
+        // extra round trip per call
+        cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");  // staged uploads have left the block
+        stageUsed_ = 0;
+        cudaCheck(cudaMemcpyAsync(stage_, (const uint8_t *)b->data + srcOffset, copySize, cudaMemcpyDeviceToHost, stream_),
+                  "cudaMemcpyAsync(D2H)");
+        cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+        std::memcpy((uint8_t *)host + destOffset, stage_, copySize);
+        return;
+      }
       cudaCheck(cudaMemcpyAsync((uint8_t *)host + destOffset, (const uint8_t *)b->data + srcOffset, copySize,
                                 cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync(D2H)");
       cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
@@ -296,11 +310,34 @@ protected:
   }
 
 private:
+  // Host bytes -> device, in stream order.  Small transfers (a decode step's activations, token ids, positions) are
+  // copied into a pinned block and sent from there without waiting: the caller's memory is free again when the call
+  // returns, the device sees the data before any later work of the stream, and the step pays one wait (its
+  // download) instead of one per tensor.  The block is reused from the start once the stream has drained.
+  void uploadBytes(void *dev, const void *host, size_t bytes) {
+    if (bytes <= kStageBytes / 4) {
+      const size_t need = (bytes + 255) & ~size_t(255);
+      if (stageUsed_ + need > kStageBytes) {
+        cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+        stageUsed_ = 0;
+      }
+      std::memcpy(stage_ + stageUsed_, host, bytes);
+      cudaCheck(cudaMemcpyAsync(dev, stage_ + stageUsed_, bytes, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
+      stageUsed_ += need;
+      return;
+    }
+    cudaCheck(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
+    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+  }
+
   void upload(DeviceBuffer &b, const void *host) {
+    if (b.innerDimSize() == b.innerDimPadded() || b.getShape().size() <= 1) {
+      uploadBytes(b.data, host, std::min(b.size(), b.calculateActualSize()));
+      return;
+    }
     std::vector<uint8_t> bounce(b.size(), 0);
     copyActualToAligned(host, bounce.data(), b);
-    cudaCheck(cudaMemcpyAsync(b.data, bounce.data(), b.size(), cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
-    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+    uploadBytes(b.data, bounce.data(), b.size());
   }
 
   // Scratch only grows, and never in place: command buffers recorded earlier keep the block they
@@ -499,6 +536,9 @@ private:
 
   int device_;
   cudaStream_t stream_ = nullptr;
+  static constexpr size_t kStageBytes = 4u << 20;
+  uint8_t *stage_ = nullptr;  // pinned
+  size_t stageUsed_ = 0;
   std::shared_ptr<Scratch> workspace_;  // split-K partial sums / cast activations of the matmuls
   std::shared_ptr<Scratch> attnWs_;     // attention scratch; its arrival counters start at zero and every launch leaves them zero
   int *status_ = nullptr;

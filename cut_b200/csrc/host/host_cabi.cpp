@@ -1,0 +1,64 @@
+// C entry points over the C++ operator API, for callers that cannot link C++ (the benchmark's
+// end-to-end leg drives the boundary the reference's runner would call through this).
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+#include <exception>
+#include <vector>
+
+#include "cut_api.h"
+
+using namespace cut;
+
+// One decode step per `replicas` weight tensors, as the reference's runner drives its backend
+// (interface/runner/llama/llama.cpp:2045-2166, core/backends/cuda/CudaCommandBuffer.cpp:261-307): the mat-vecs are
+// recorded once through Operations::matmulBlocks and kept as a reusable command buffer; every step uploads its
+// activations from host memory (ComputeInterface::copyDataToBuffer), resubmits the command buffer, waits, and
+// reads every result back (copyDataFromBuffer).  The weights are model state: uploaded once, before the clock starts.
+//
+//   format        DequantFormat code of the blocks (16 = Q8_0, 17 = Q4_0, 1 = Q4_K)
+//   w_host        one weight tensor of N rows of blocks along K; replica r is its bytes rotated by r * roll_bytes
+//   a_host        [replicas][batch][K] activations, fp16 when a_is_half else fp32
+//   c_host        [replicas][batch][N] fp32 results of the last step
+//   seconds       wall time of the `steps` timed steps
+// Returns 0, or -1 with a message in err.
+extern "C" __attribute__((visibility("default"))) int cut_host_e2e_matvec_blocks(
+    int device, uint32_t format, uint32_t N, uint32_t K, uint32_t batch, uint32_t replicas, const uint8_t *w_host, uint64_t w_bytes,
+    uint64_t roll_bytes, const void *a_host, int a_is_half, float *c_host, uint32_t warmup, uint32_t steps, double *seconds,
+    uint64_t *h2d_bytes_per_step, uint64_t *d2h_bytes_per_step, char *err, size_t err_cap) {
+  try {
+    Runtime rt(device);
+    const DataType adt = a_is_half ? DataType::Float16 : DataType::Float32;
+    const size_t a_bytes = (size_t)batch * K * (a_is_half ? 2 : 4), c_bytes = (size_t)batch * N * sizeof(float);
+    std::vector<Tensor> tA(replicas), tW(replicas), tC(replicas);
+    std::vector<uint8_t> rolled(w_bytes);
+    for (uint32_t r = 0; r < replicas; ++r) {
+      const uint64_t sh = w_bytes ? (roll_bytes * r) % w_bytes : 0;
+      std::memcpy(rolled.data() + sh, w_host, w_bytes - sh);
+      std::memcpy(rolled.data(), w_host + (w_bytes - sh), sh);
+      tW[r] = rt.createTensor({(uint32_t)w_bytes}, DataType::Int8, rolled.data());
+      tA[r] = batch == 1 ? rt.createTensor({K}, adt, (const uint8_t *)a_host + r * a_bytes)
+                         : rt.createTensor({batch, K}, adt, (const uint8_t *)a_host + r * a_bytes);
+    }
+    for (uint32_t r = 0; r < replicas; ++r) tC[r] = rt.ops().matmulBlocks(tA[r], tW[r], static_cast<DequantFormat>(format), N);
+    ComputeHandle cb = rt.iface().submitReusable();
+    rt.iface().wait(cb);
+    auto step = [&]() {
+      for (uint32_t r = 0; r < replicas; ++r) rt.copyToTensor(tA[r], (const uint8_t *)a_host + r * a_bytes, a_bytes);
+      rt.iface().resubmit(cb);
+      rt.iface().wait(cb);
+      for (uint32_t r = 0; r < replicas; ++r) rt.copyFromTensor(tC[r], (uint8_t *)c_host + r * c_bytes, c_bytes);
+    };
+    for (uint32_t i = 0; i < warmup; ++i) step();
+    const auto t0 = std::chrono::steady_clock::now();
+    for (uint32_t i = 0; i < steps; ++i) step();
+    const auto t1 = std::chrono::steady_clock::now();
+    if (seconds) *seconds = std::chrono::duration<double>(t1 - t0).count();
+    if (h2d_bytes_per_step) *h2d_bytes_per_step = (uint64_t)replicas * a_bytes;
+    if (d2h_bytes_per_step) *d2h_bytes_per_step = (uint64_t)replicas * c_bytes;
+    return 0;
+  } catch (const std::exception &e) {
+    if (err && err_cap) snprintf(err, err_cap, "%s", e.what());
+    return -1;
+  }
+}
