@@ -337,6 +337,10 @@ def planes_chain_us(dev, n: int, k: int) -> dict:
     C = torch.zeros((reps, 1, n), dtype=torch.float32, device=dev)
     descs = [ops.make_desc(A, P[r], L.Q4_0, n, layout=L.LAYOUT_KN_PLANES, scales=S[r], ldb=packed.stride(0), lds=scalesT.stride(0),
                            C_out=C[r]) for r in range(reps)]
+    need = ops.workspace_bytes(descs[0][0])
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)  # K-split partial sums; launches are stream-ordered
+    for d, _, _ in descs:
+        d.workspace, d.workspace_bytes = ws.data_ptr(), need
 
     def sweep():
         for d, _, _ in descs:

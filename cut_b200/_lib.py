@@ -15,11 +15,12 @@ Q8_0, Q4_0, Q4_K, Q5_K, Q6_K, BF16, Q4_1, Q5_0 = 0, 1, 2, 3, 4, 5, 6, 7  # from 
 F32, F16 = 0, 1
 LAYOUT_GGUF_BLOCKS, LAYOUT_KN_PLANES = 0, 1
 FUSION_NONE, FUSION_UNARY, FUSION_BINARY = 0, 1, 2
-VARIANT_AUTO, VARIANT_GENERIC, VARIANT_GEMV_MMA, VARIANT_GEMM_TC = -1, 0, 1, 2
+VARIANT_AUTO, VARIANT_GENERIC, VARIANT_GEMV_MMA, VARIANT_GEMM_TC, VARIANT_GEMV_PLANES = -1, 0, 1, 2, 3
 FLAG_NO_OVERLAP = 1
 FLAG_ACT_16BIT = 2
 FLAG_A_RMSNORM = 4
 FLAG_GLU_PAIRS = 8
+FLAG_STAGE_PER_CTA = 16
 
 # every symbol include/cutb.h declares
 EXPORTS = [

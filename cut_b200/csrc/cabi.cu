@@ -94,7 +94,7 @@ int validate(const cutb_qmatmul_desc *d) {
       return CUTB_ERR_INVALID;
     }
   }
-  if (d->variant < CUTB_VARIANT_AUTO || d->variant > CUTB_VARIANT_GEMM_TC) {
+  if (d->variant < CUTB_VARIANT_AUTO || d->variant > CUTB_VARIANT_GEMV_PLANES) {
     set_last_error("qmatmul: unknown variant %d", d->variant);
     return CUTB_ERR_INVALID;
   }
@@ -109,6 +109,8 @@ int select(const cutb_qmatmul_desc &d) {
   if (d.layout == CUTB_LAYOUT_GGUF_BLOCKS) {
     if (qgemv_blocks_supported(d)) return CUTB_VARIANT_GEMV_MMA;
     if (qgemm_tc_supported(d)) return CUTB_VARIANT_GEMM_TC;
+  } else if (qgemv_planes_supported(d)) {
+    return CUTB_VARIANT_GEMV_PLANES;
   }
   return CUTB_VARIANT_GENERIC;
 }
@@ -145,6 +147,7 @@ const char *cutb_variant_name(int variant) {
     case CUTB_VARIANT_GENERIC: return "QMatMulGeneric";
     case CUTB_VARIANT_GEMV_MMA: return "QGemvBulkMma";
     case CUTB_VARIANT_GEMM_TC: return "QGemmTcgen05";
+    case CUTB_VARIANT_GEMV_PLANES: return "QGemvPlanes";
     default: return "Unknown";
   }
 }
@@ -165,6 +168,7 @@ uint64_t cutb_qmatmul_workspace_bytes(const cutb_qmatmul_desc *desc) {
   const int v = select(*desc);
   if (v == CUTB_VARIANT_GEMV_MMA) return qgemv_blocks_workspace(*desc);
   if (v == CUTB_VARIANT_GEMM_TC) return qgemm_tc_workspace(*desc);
+  if (v == CUTB_VARIANT_GEMV_PLANES) return qgemv_planes_workspace(*desc);
   return 0;
 }
 
@@ -172,7 +176,7 @@ int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
   if (int rc = validate(desc)) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int v = select(*desc);
-  if ((desc->flags & CUTB_FLAG_GLU_PAIRS) && (v != CUTB_VARIANT_GEMV_MMA || qgemv_blocks_workspace(*desc) != 0)) {
+  if ((desc->flags & CUTB_FLAG_GLU_PAIRS) && v != CUTB_VARIANT_GEMV_MMA) {  // (the mat-vec launcher refuses shapes that split K)
     set_last_error("qmatmul: paired gate/up rows exist in the decode mat-vec only, for shapes that do not split K");
     return CUTB_ERR_UNSUPPORTED;
   }
@@ -200,6 +204,12 @@ int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
         return CUTB_ERR_UNSUPPORTED;
       }
       return qgemm_tc_launch(*desc, s);
+    case CUTB_VARIANT_GEMV_PLANES:
+      if (!qgemv_planes_supported(*desc)) {
+        set_last_error("qmatmul: variant %s needs the [K, N] plane layout (Q8 or Q4), M <= 4 and strides padded to 4", cutb_variant_name(v));
+        return CUTB_ERR_UNSUPPORTED;
+      }
+      return qgemv_planes_launch(*desc, s);
     default:
       return qmatmul_generic_launch(*desc, s);
   }

@@ -424,8 +424,10 @@ private:
     q.ldd = pc.strideC;
     q.fusion_type = (int32_t)k.fusionType;
     q.fusion_op = (int32_t)k.fusionOp;
-    // plane-layout variant indices all map onto the one plane kernel; block variants are the C ABI's own
-    q.variant = blocks ? (int32_t)k.variant : CUTB_VARIANT_GENERIC;
+    // plane-layout variant indices (the reference's Tiled / GemvKPar8 / CoopMat ... tables) all map onto the library's
+    // own choice for that layout: the coalesced mat-vec up to four rows, the any-shape kernel beyond; block
+    // variants are the C ABI's own
+    q.variant = blocks ? (int32_t)k.variant : CUTB_VARIANT_AUTO;
     q.workspace = wsPtr();
     q.workspace_bytes = wsBytes();
     q.status = status_;

@@ -21,6 +21,11 @@ int peer_exchange_launch(const cutb_peer_scatter &peers, uint64_t *step_counter,
 // Any-shape SIMT matmul over GGUF blocks or the reference's [K,N] planes.
 int qmatmul_generic_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
 
+// Decode mat-vec over the reference's [K,N] planes (qgemv_planes.cu).
+bool qgemv_planes_supported(const cutb_qmatmul_desc &d);
+uint64_t qgemv_planes_workspace(const cutb_qmatmul_desc &d);
+int qgemv_planes_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
+
 // Prefill GEMM over GGUF blocks on tcgen05 tensor cores.
 bool qgemm_tc_supported(const cutb_qmatmul_desc &d);
 uint64_t qgemm_tc_workspace(const cutb_qmatmul_desc &d);

@@ -97,6 +97,10 @@ struct GvParams {
   const float *norm_w;  // fused RMSNorm of the activation rows (nullptr: none)
   float norm_eps;
   int *status;
+  // Activations staged once for all CTAs by stage_acts_kernel (nullptr: every CTA stages its own):
+  // one blob per K split in the shared-memory layout [act | esc | sx], staged_bytes each.
+  uint8_t *staged;
+  uint32_t staged_bytes;
   // Row-sharded scatter epilogue (world > 1): instead of C, the output slice is stored into
   // every rank's full output at column n_off.  Peer-mapped pointers; plain stores, no
   // multicast, no fence here: the step's exchange kernel publishes them.
@@ -636,8 +640,74 @@ __device__ __forceinline__ void stage_activations(const GvParams &p, uint8_t *ac
     }
 }
 
-template <int FMT, int AMODE, int NT, bool DIAG>
-__global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvParams p) {
+// 1 / rms of every activation row (fused RMSNorm), by GV_WARPS * 32 threads synchronising on named
+// barrier 1: red[GV_WARPS * 16 + m] holds row m's scale on return.  `red` needs GV_WARPS * 16 + 16 floats.
+template <bool AF32N>
+__device__ __forceinline__ void rms_scales(const GvParams &p, float *red, uint32_t tid) {
+  const uint32_t warp = tid >> 5, lane = tid & 31;
+  for (uint32_t m = 0; m < p.M; ++m) {
+    float ss = 0.f;
+    // K is a multiple of 256: two elements per thread and pass, four passes' loads in flight
+    for (uint32_t k = 2 * tid; k < p.K; k += 8 * GV_WARPS * 32) {
+      float v[8];
+#pragma unroll
+      for (uint32_t u = 0; u < 4; ++u) {
+        const uint32_t kk = k + u * 2 * GV_WARPS * 32;
+        const bool in = kk < p.K;
+        v[2 * u] = in ? load_act<AF32N>(p.A, (uint64_t)m * p.lda + kk) : 0.f;
+        v[2 * u + 1] = in ? load_act<AF32N>(p.A, (uint64_t)m * p.lda + kk + 1) : 0.f;
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < 8; ++u) ss = fmaf(v[u], v[u], ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) red[warp * 16 + m] = ss;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
+  if (tid < p.M) {
+    float ss = 0.f;
+#pragma unroll
+    for (int w = 0; w < GV_WARPS; ++w) ss += red[w * 16 + tid];
+    red[GV_WARPS * 16 + tid] = rsqrtf(ss / (float)p.K + p.norm_eps);
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
+}
+
+// Stages the activations of one launch once, for all its CTAs: block (x, y) stages a run of 32-k blocks
+// of K split y into that split's blob, in exactly the layout (and with exactly the arithmetic) a mat-vec
+// CTA would build in its own shared memory.  Used from three virtual rows up, where every CTA repeating
+// the staging costs more than the mat-vec itself.
+template <int FMT, int AMODE, int NT>
+__global__ void __launch_bounds__(GV_WARPS * 32) stage_acts_kernel(const GvParams p, uint32_t ncp, uint32_t blocks_per_cta) {
+  __shared__ float red[GV_WARPS * 16 + 16];
+  constexpr uint32_t NV = NT * 4;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations may come from the kernel before
+  const uint32_t tid = threadIdx.x;
+  const uint32_t G = p.K >> 8;
+  const uint32_t gs0 = blockIdx.y * p.gran_per_split;
+  const uint32_t gs1 = min(G, gs0 + p.gran_per_split);
+  const uint32_t nblk = (gs1 - gs0) * 8, nblk_alloc = p.gran_per_split * 8;
+  const uint32_t b0 = blockIdx.x * blocks_per_cta;  // even: block parity decides the fragment order
+  const float *nscale = nullptr;
+  if (p.norm_w) {
+    rms_scales<AMODE != GV_A_HALF>(p, red, tid);
+    nscale = red + GV_WARPS * 16;
+  }
+  if (b0 >= nblk) return;
+  const uint32_t nb = min(blocks_per_cta, nblk - b0);
+  uint8_t *base = p.staged + (size_t)blockIdx.y * p.staged_bytes;
+  float *esc0 = reinterpret_cast<float *>(base + (size_t)nblk_alloc * ncp * 32);
+  float *sx0 = esc0 + (size_t)nblk_alloc * NV;
+  stage_activations<FMT, AMODE, NT, false, GV_WARPS * 32>(p, base + (size_t)b0 * ncp * 32, esc0 + (size_t)b0 * NV, sx0 + (size_t)b0 * NV,
+                                                          gs0 * 256 + b0 * 32, nb, ncp, tid, nscale);
+}
+
+// MINB: CTAs per SM the register budget is kept under -- 2 where this launch's CTA and the next launch's share an
+// SM, 1 for the plans whose shared memory fills the SM anyway (then up to 120 registers instead of 56).
+template <int FMT, int AMODE, int NT, bool DIAG, int MINB>
+__global__ void __launch_bounds__(GV_THREADS, MINB) qgemv_blocks_kernel(const GvParams p) {
   constexpr int PS = gv_pair_stride(FMT, DIAG);
   constexpr uint32_t RAWROW = gv_raw_row(FMT);
   constexpr uint32_t GB = granule_bytes(FMT);
@@ -691,6 +761,7 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
       mbar_init(full_u + s * 8, 1);
       mbar_init(empty_u + s * 8, GV_WARPS / HV);
     }
+    mbar_init(full_u + 4 * S * 8, 1);  // arrival of the pre-staged activations
     fence_mbar_init();
   }
   __syncthreads();
@@ -740,41 +811,35 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
   // Everything above only read the (constant) weights.  The activations, D and
   // C may belong to the previous kernel of the stream: wait for it to finish.
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const float *nscale = nullptr;
-  if (p.norm_w) {
-    // fused RMSNorm: every CTA needs the scale of the whole row, whatever K slice it stages; the
-    // reduction buffers are idle until the first tile
-    constexpr bool AF32N = AMODE != GV_A_HALF;
-    for (uint32_t m = 0; m < p.M; ++m) {
-      float ss = 0.f;
-      // K is a multiple of 256: two elements per thread and pass, four passes' loads in flight
-      for (uint32_t k = 2 * tid; k < p.K; k += 8 * GV_WARPS * 32) {
-        float v[8];
-#pragma unroll
-        for (uint32_t u = 0; u < 4; ++u) {
-          const uint32_t kk = k + u * 2 * GV_WARPS * 32;
-          const bool in = kk < p.K;
-          v[2 * u] = in ? load_act<AF32N>(p.A, (uint64_t)m * p.lda + kk) : 0.f;
-          v[2 * u + 1] = in ? load_act<AF32N>(p.A, (uint64_t)m * p.lda + kk + 1) : 0.f;
-        }
-#pragma unroll
-        for (uint32_t u = 0; u < 8; ++u) ss = fmaf(v[u], v[u], ss);
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) red[warp * 16 + m] = ss;
+  bool dead = false;
+  bool fetched = false;
+  if constexpr (!DIAG) fetched = p.staged != nullptr;
+  if (fetched) {
+    // the launch before this one staged the activations of every K split once; fetch this split's
+    // (the same bytes this CTA would have produced) with bulk copies
+    const uint32_t abar = full_u + 4 * S * 8;
+    if (warp == 0) {
+      if (lane == 0) mbar_arrive_expect_tx(abar, p.staged_bytes);
+      __syncwarp();
+      const uint8_t *src = p.staged + (size_t)blockIdx.y * p.staged_bytes;
+      for (uint32_t off = lane * 8192u; off < p.staged_bytes; off += 32u * 8192u)
+        bulk_g2s(smem_u32(act) + off, src + off, min(8192u, p.staged_bytes - off), abar);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
-    if (tid < p.M) {
-      float ss = 0.f;
-#pragma unroll
-      for (int w = 0; w < GV_WARPS; ++w) ss += red[w * 16 + tid];
-      red[GV_WARPS * 16 + tid] = rsqrtf(ss / (float)p.K + p.norm_eps);
+    const bool ok = mbar_wait_probe_first(abar, 0);
+    if (!__all_sync(0xffffffffu, ok)) {
+      dead = true;
+      if (lane == 0 && p.status) atomicExch(p.status, (int)CUTB_ERR_TIMEOUT);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
-    nscale = red + GV_WARPS * 16;
+  } else {
+    const float *nscale = nullptr;
+    if (p.norm_w) {
+      // fused RMSNorm: every CTA needs the scale of the whole row, whatever K slice it stages; the
+      // reduction buffers are idle until the first tile
+      rms_scales<AMODE != GV_A_HALF>(p, red, tid);
+      nscale = red + GV_WARPS * 16;
+    }
+    stage_activations<FMT, AMODE, NT, DIAG, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid, nscale);
   }
-  stage_activations<FMT, AMODE, NT, DIAG, GV_WARPS * 32>(p, act, esc, sx, gs0 * 256, ng * 8, ncp, tid, nscale);
   asm volatile("bar.sync 1, %0;" ::"n"(GV_WARPS * 32) : "memory");
 
   const uint32_t act_u = smem_u32(act), act_stride = ncp * 32, esc_u = smem_u32(esc), sx_u = smem_u32(sx);
@@ -794,7 +859,6 @@ __global__ void __launch_bounds__(GV_THREADS, 2) qgemv_blocks_kernel(const GvPar
     }
   }
 
-  bool dead = false;
   uint32_t slot = 0, parity = 0;
   const uint32_t hv = HV == 2 ? warp >> 3 : 0u;  // the K half this warp's granule belongs to
   for (uint32_t tile = 0; tile < ntiles; ++tile) {
@@ -973,8 +1037,12 @@ int gv_amode(const cutb_qmatmul_desc &d) {
 
 struct GvPlan {
   uint32_t nt, nvr, ncp, grid_x, ksplit, gran_per_split, stages;
-  bool diag, overlap;
+  bool diag, overlap, pair;
   size_t smem;
+  // activations staged once per launch by stage_acts_kernel (otherwise by every CTA)
+  bool prestage;
+  uint32_t staged_bytes;    // one K split's blob
+  uint64_t partial_bytes;   // split-K partial sums, rounded up to 256: the blobs follow them in the workspace
 };
 
 size_t gv_smem_bytes(int fmt, bool diag, uint32_t stages, uint32_t nt, uint32_t ncp, uint32_t gran_per_split) {
@@ -984,7 +1052,7 @@ size_t gv_smem_bytes(int fmt, bool diag, uint32_t stages, uint32_t nt, uint32_t 
   b += diag ? nblk * nt * 64 + 32 : nblk * ncp * 32;
   b += nblk * nv * 4 * (fmt != CUTB_Q8_0 ? 2 : 1);
   b += (size_t)2 * GV_WARPS * GV_ROWS * nv * 4;
-  b += 4 * stages * 8;  // full / empty barriers of both K halves of every slot
+  b += 4 * stages * 8 + 8;  // full / empty barriers of both K halves of every slot; arrival of pre-staged activations
   return b;
 }
 
@@ -1023,6 +1091,20 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
         pl->ksplit = (G + gps - 1) / gps;
         pl->stages = st;
         pl->smem = sm;
+        pl->pair = pair;
+        // A split forced by shared memory (many activation rows, long K) must not push the launch into a
+        // second wave: CTAs this large sit one to an SM, so give every CTA more rows instead.
+        if (!pair && (uint64_t)pl->grid_x * pl->ksplit > (uint32_t)di.sm_count) {
+          const uint32_t gx = (uint32_t)di.sm_count / pl->ksplit;
+          pl->grid_x = gx ? gx : 1;
+        }
+        const uint32_t nv = pl->diag ? pl->nt : pl->nt * 4;
+        // From three virtual rows up the staging, repeated by every CTA, outweighs the mat-vec (measured:
+        // 11008 x 4096 Q4_0, batch 8: 17.6 us, of which about 10 us staging): stage once, in a launch of its own.
+        pl->prestage = !pl->diag && pl->nvr >= 3 && !(d.flags & CUTB_FLAG_STAGE_PER_CTA);
+        if (const char *e = getenv("CUTB_GV_PRESTAGE")) pl->prestage = pl->prestage && atoi(e) != 0;  // tuning override
+        pl->staged_bytes = gps * 8 * (pl->ncp * 32 + nv * 4 * (d.format != CUTB_Q8_0 ? 2 : 1));
+        pl->partial_bytes = pl->ksplit > 1 ? ((uint64_t)pl->ksplit * d.M * d.N * sizeof(float) + 255) / 256 * 256 : 0;
         return true;
       }
     }
@@ -1030,7 +1112,29 @@ bool gv_plan(const cutb_qmatmul_desc &d, const DeviceInfo &di, GvPlan *pl) {
   return false;
 }
 
-template <int FMT, int AMODE, int NT, bool DIAG>
+uint64_t gv_workspace_need(const GvPlan &pl) {
+  return pl.partial_bytes + (pl.prestage ? (uint64_t)pl.ksplit * pl.staged_bytes : 0);
+}
+
+template <int FMT, int AMODE, int NT>
+int gv_launch_prestage(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
+  // one pass of the staging loop per CTA: 512 threads = 512 chunks of (block, row, lane) = 128 / M blocks, even
+  uint32_t per = (GV_WARPS * 32 / 4) / p.M;
+  per = per < 2 ? 2 : per & ~1u;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((pl.gran_per_split * 8 + per - 1) / per, pl.ksplit);
+  cfg.blockDim = dim3(GV_WARPS * 32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pl.overlap ? 1 : 0;
+  CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, stage_acts_kernel<FMT, AMODE, NT>, p, pl.ncp, per));
+  return CUTB_OK;
+}
+
+template <int FMT, int AMODE, int NT, bool DIAG, int MINB>
 int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   static bool configured[64] = {};  // per device: the attribute is set once on each
   int dev = 0;
@@ -1038,9 +1142,13 @@ int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   if (dev < 0 || dev >= 64 || !configured[dev]) {
     DeviceInfo di;
     if (int rc = get_device_info(&di)) return rc;
-    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AMODE, NT, DIAG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemv_blocks_kernel<FMT, AMODE, NT, DIAG, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)di.smem_optin));
     if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  if constexpr (!DIAG) {
+    if (pl.prestage)
+      if (int rc = gv_launch_prestage<FMT, AMODE, NT>(p, pl, stream)) return rc;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(pl.grid_x, pl.ksplit);
@@ -1052,17 +1160,20 @@ int gv_launch_inst(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pl.overlap ? 1 : 0;
-  CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, qgemv_blocks_kernel<FMT, AMODE, NT, DIAG>, p));
+  CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, qgemv_blocks_kernel<FMT, AMODE, NT, DIAG, MINB>, p));
   return CUTB_OK;
 }
 
 template <int FMT, int AMODE>
 int gv_launch_nt(const GvParams &p, const GvPlan &pl, cudaStream_t stream) {
-  if (pl.diag) return pl.nt == 1 ? gv_launch_inst<FMT, AMODE, 1, true>(p, pl, stream) : gv_launch_inst<FMT, AMODE, 2, true>(p, pl, stream);
+  if (pl.diag) return pl.nt == 1 ? gv_launch_inst<FMT, AMODE, 1, true, 2>(p, pl, stream) : gv_launch_inst<FMT, AMODE, 2, true, 2>(p, pl, stream);
+  // measured: the 56-register build is the faster one for 4 and 8 virtual rows even where shared memory leaves room
+  // for one CTA only (11008 x 4096 Q4_0, batch 8: 12.2 us against 13.7 with 96 registers); 16 rows gain from the
+  // larger budget (34.9 -> 28.2 us): no spills, four independent MMA chains per block
   switch (pl.nt) {
-    case 1: return gv_launch_inst<FMT, AMODE, 1, false>(p, pl, stream);
-    case 2: return gv_launch_inst<FMT, AMODE, 2, false>(p, pl, stream);
-    default: return gv_launch_inst<FMT, AMODE, 4, false>(p, pl, stream);
+    case 1: return gv_launch_inst<FMT, AMODE, 1, false, 2>(p, pl, stream);
+    case 2: return gv_launch_inst<FMT, AMODE, 2, false, 2>(p, pl, stream);
+    default: return gv_launch_inst<FMT, AMODE, 4, false, 1>(p, pl, stream);  // 16 virtual rows never leave room for a second CTA
   }
 }
 
@@ -1095,7 +1206,7 @@ uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d) {
   }
   GvPlan pl;
   if (!qgemv_blocks_supported(d) || !gv_plan(d, di, &pl)) return 0;
-  return pl.ksplit > 1 ? (uint64_t)pl.ksplit * d.M * d.N * sizeof(float) : 0;
+  return gv_workspace_need(pl);
 }
 
 int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const cutb_peer_scatter *sc) {
@@ -1168,14 +1279,24 @@ int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const c
       for (uint32_t q = 0; q < sa.world; ++q) p.peer_C[q] = sa.peer_C[q];
     }
   }
-  if (pl.ksplit > 1) {
-    const uint64_t need = (uint64_t)pl.ksplit * d.M * d.N * sizeof(float);
+  p.staged = nullptr;
+  p.staged_bytes = 0;
+  if (const uint64_t need = gv_workspace_need(pl)) {
     if (!d.workspace || d.workspace_bytes < need) {
-      set_last_error("qgemv: split-K needs %llu workspace bytes, got %llu", (unsigned long long)need,
-                     (unsigned long long)d.workspace_bytes);
+      set_last_error("qgemv: this shape needs %llu workspace bytes (split-K partial sums %llu, staged activations %llu), got %llu",
+                     (unsigned long long)need, (unsigned long long)pl.partial_bytes,
+                     (unsigned long long)(need - pl.partial_bytes), (unsigned long long)d.workspace_bytes);
       return CUTB_ERR_WORKSPACE;
     }
-    p.partial = reinterpret_cast<float *>(d.workspace);
+    if (reinterpret_cast<uintptr_t>(d.workspace) % 16 != 0) {
+      set_last_error("qgemv: the workspace must be 16-byte aligned");
+      return CUTB_ERR_INVALID;
+    }
+    if (pl.ksplit > 1) p.partial = reinterpret_cast<float *>(d.workspace);
+    if (pl.prestage) {
+      p.staged = reinterpret_cast<uint8_t *>(d.workspace) + pl.partial_bytes;
+      p.staged_bytes = pl.staged_bytes;
+    }
   }
   int rc;
   switch (d.format) {
@@ -1231,7 +1352,13 @@ extern "C" int cutb_qmatmul_decode_noalloc(const cutb_qmatmul_desc *desc, void *
     set_last_error("decode_noalloc: needs GGUF blocks, K %% 256 == 0, 16-byte aligned W and M <= 16 (fp16) / 8 (fp32)");
     return CUTB_ERR_UNSUPPORTED;
   }
-  const uint64_t need = qgemv_blocks_workspace(*desc);
+  cutb_qmatmul_desc d = *desc;
+  d.variant = CUTB_VARIANT_GEMV_MMA;
+  uint64_t need = qgemv_blocks_workspace(d);
+  if (need > kNoAllocScratchFloats * sizeof(float) && !(d.flags & CUTB_FLAG_STAGE_PER_CTA)) {
+    d.flags |= CUTB_FLAG_STAGE_PER_CTA;  // leaves the scratch to the partial sums
+    need = qgemv_blocks_workspace(d);
+  }
   if (need > kNoAllocScratchFloats * sizeof(float)) {
     set_last_error("decode_noalloc: this shape needs %llu bytes of scratch, the built-in array holds %llu; "
                    "use cutb_qmatmul with a caller-provided workspace",
@@ -1253,8 +1380,6 @@ extern "C" int cutb_qmatmul_decode_noalloc(const cutb_qmatmul_desc *desc, void *
     CUTB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_noalloc_scratch));
     scratch_of_device[dev] = ptr;
   }
-  cutb_qmatmul_desc d = *desc;
-  d.variant = CUTB_VARIANT_GEMV_MMA;
   d.workspace = scratch_of_device[dev];
   d.workspace_bytes = kNoAllocScratchFloats * sizeof(float);
   return qgemv_blocks_launch(d, reinterpret_cast<cudaStream_t>(stream), nullptr);

@@ -75,8 +75,10 @@ enum {
   CUTB_VARIANT_AUTO = -1,
   CUTB_VARIANT_GENERIC = 0, /* any shape, SIMT, exact fp32 dequant + FMA */
   CUTB_VARIANT_GEMV_MMA = 1, /* decode: bulk-copy ring + int8 warp MMA, M <= 16 (fp16 A) / 8 (fp32 A) */
-  CUTB_VARIANT_GEMM_TC = 2  /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory; its operands are fp16
+  CUTB_VARIANT_GEMM_TC = 2, /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory; its operands are fp16
                                (see the operand-range note at cutb_qmatmul_desc) */
+  CUTB_VARIANT_GEMV_PLANES = 3 /* decode over CUTB_LAYOUT_KN_PLANES (the reference's run-time layout), M <= 4: coalesced
+                                  column groups, K split over warps and blocks */
 };
 
 /* Descriptor flags.
@@ -103,8 +105,14 @@ enum {
  *     C[m, i] = unary(fusion_op)(acc[m, 2i]) * acc[m, 2i + 1] (fusion_type CUTB_FUSION_UNARY; with
  *     SiLU this is the SwiGLU feed-forward the runner builds from matmulUnary + a multiply,
  *     interface/runner/llama/llama.cpp:2455-2470).  ldc >= N / 2.  Decode mat-vec only, shapes that
- *     do not split K; anything else returns CUTB_ERR_UNSUPPORTED. */
-enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2, CUTB_FLAG_A_RMSNORM = 4, CUTB_FLAG_GLU_PAIRS = 8 };
+ *     do not split K; anything else returns CUTB_ERR_UNSUPPORTED.
+ *   CUTB_FLAG_STAGE_PER_CTA: from three activation rows up the decode mat-vec quantises its
+ *     activations once per call, in a small launch of its own, into the workspace
+ *     (cutb_qmatmul_workspace_bytes counts the room), and every block copies the result.  With this
+ *     flag every block stages the activations itself, as it does for one or two rows: no staging
+ *     scratch, slower for more than two rows.  The results are the same bit for bit. */
+enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2, CUTB_FLAG_A_RMSNORM = 4, CUTB_FLAG_GLU_PAIRS = 8,
+       CUTB_FLAG_STAGE_PER_CTA = 16 };
 
 /*
  * C[M, N] = epilogue(A[M, K] * dequant(W)), fp32 accumulate, fp32 output.

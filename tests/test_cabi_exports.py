@@ -84,8 +84,20 @@ def test_select_variant_and_workspace_plan_without_device():
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 1, 4096, 4096, L.F32))) == L.VARIANT_GEMV_MMA
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 9, 4096, 4096, L.F32))) != L.VARIANT_GEMV_MMA
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 1, 96, 8))) == L.VARIANT_GENERIC
-    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 1, 64, 4, L.F32, L.LAYOUT_KN_PLANES))) == L.VARIANT_GENERIC
+    # the reference's [K, N] planes: the coalesced mat-vec up to four rows, strides padded to 4; else the any-shape kernel
+    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 1, 64, 4, L.F32, L.LAYOUT_KN_PLANES))) == L.VARIANT_GEMV_PLANES
+    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 4, 4096, 11008, L.F32, L.LAYOUT_KN_PLANES))) == L.VARIANT_GEMV_PLANES
+    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 5, 64, 4, L.F32, L.LAYOUT_KN_PLANES))) == L.VARIANT_GENERIC
+    assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 1, 64, 6, L.F32, L.LAYOUT_KN_PLANES))) == L.VARIANT_GENERIC  # ldb = 6
+    assert lib.cutb_qmatmul_workspace_bytes(C.byref(desc(L.Q8_0, 1, 4096, 4096, L.F32, L.LAYOUT_KN_PLANES))) > 0  # K split over blocks
+    assert lib.cutb_variant_name(L.VARIANT_GEMV_PLANES) == b"QGemvPlanes"
     assert lib.cutb_qmatmul_workspace_bytes(C.byref(desc(L.Q4_0, 1, 4096, 11008))) == 0
     # few rows, long K: split over K, partial sums staged in the workspace
-    ws = lib.cutb_qmatmul_workspace_bytes(C.byref(desc(L.Q4_0, 8, 28672, 1024)))
+    d = desc(L.Q4_0, 8, 28672, 1024)
+    d.flags = L.FLAG_STAGE_PER_CTA
+    ws = lib.cutb_qmatmul_workspace_bytes(C.byref(d))
     assert ws > 0 and ws % (8 * 1024 * 4) == 0
+    # three rows and more: the activations are quantised once per call into the workspace as well
+    d.flags = 0
+    assert lib.cutb_qmatmul_workspace_bytes(C.byref(d)) > ws
+    assert lib.cutb_qmatmul_workspace_bytes(C.byref(desc(L.Q4_0, 2, 4096, 11008))) == 0

@@ -112,7 +112,10 @@ def test_paired_gate_up_rows(fmt, M, K, N2):
     C_out = torch.zeros((M, N2), dtype=torch.float32, device="cuda")
     d, _, keep = ops.make_desc(dev(A), dev(W), fmt, 2 * N2, C_out=C_out, fusion_type=1, fusion_op=133, status=status,
                                flags=L.FLAG_GLU_PAIRS)
-    assert ops.workspace_bytes(d) == 0
+    need = ops.workspace_bytes(d)  # no split-K partial sums with paired rows; staged activations from three rows up
+    assert (need == 0) == (M < 3)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    d.workspace, d.workspace_bytes = ws.data_ptr(), need
     ops.launch(d)
     torch.cuda.synchronize()
     g = _ref(fmt, A, Wg, M, K, N2, fusion_type=1, fusion_op=133).astype(np.float64)
@@ -230,6 +233,45 @@ def test_q4_k_decode_14336x4096_fp16(B):
 
 
 @pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("dtype,flags", [(np.float16, 0), (np.float32, 0), (np.float32, L.FLAG_ACT_16BIT), (np.float16, L.FLAG_A_RMSNORM)])
+@pytest.mark.parametrize("M,K,N", [(3, 1024, 264), (4, 4096, 2368), (8, 4096, 1000), (16, 2048, 520), (8, 28672, 1024), (5, 8192, 96)])
+def test_activations_staged_once_equal_per_block_staging(fmt, dtype, flags, M, K, N):
+    """From three activation rows up the decode mat-vec quantises the activations once per call, in a
+    launch of its own, into the workspace; with CUTB_FLAG_STAGE_PER_CTA every block does it itself.  The
+    two must agree bit for bit (same arithmetic, same layout), on shapes that split K as well, and the
+    shared staging must be what cutb_qmatmul_workspace_bytes asks room for."""
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev, rel_l2
+
+    if dtype == np.float32 and not (flags & L.FLAG_ACT_16BIT) and M > 8:
+        pytest.skip("fp32 rows staged at two levels: at most 8 rows in the decode kernel")
+    A, W = _inputs(fmt, M, K, N, dtype, seed=900 + M + fmt)
+    Ad, Wd = dev(A), dev(W)
+    nw = dev(np.random.default_rng(5).uniform(0.5, 1.5, K).astype(np.float32)) if flags & L.FLAG_A_RMSNORM else None
+    outs, needs = [], []
+    for extra in (0, L.FLAG_STAGE_PER_CTA):
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        d, C_out, keep = ops.make_desc(Ad, Wd, fmt, N, variant=L.VARIANT_GEMV_MMA, status=status, flags=flags | extra)
+        if nw is not None:
+            d.a_norm_weight, d.a_norm_eps = nw.data_ptr(), 1e-5
+        need = ops.workspace_bytes(d)
+        needs.append(need)
+        ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+        d.workspace, d.workspace_bytes = ws.data_ptr(), need
+        ops.launch(d)
+        ops.launch(d)  # back to back: the second call restages into the same scratch behind the first
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        outs.append(C_out.cpu().numpy())
+    assert needs[0] > needs[1]  # the staged activations take workspace
+    assert np.array_equal(outs[0], outs[1])
+    if not flags & L.FLAG_A_RMSNORM:
+        assert rel_l2(outs[0], _ref(fmt, A, W, M, K, N)) <= TOL
+
+
+@pytest.mark.parametrize("fmt", FMTS)
 def test_long_k_and_few_rows_use_split_k(fmt):
     """70B-shape slices: K = 28672 with N/8 rows per GPU -> K is split across CTAs
     and summed in a fixed order from the workspace."""
@@ -279,6 +321,79 @@ def test_fused_epilogues(variant, ftype, fop):
     got, _, _ = run_blocks(synth.Q4_0, A, W, N, variant=variant, D_np=D, fusion_type=ftype, fusion_op=fop)
     ref = _ref(synth.Q4_0, A, W, M, K, N, D=D, fusion_type=ftype, fusion_op=fop)
     assert np.allclose(got, ref, rtol=2e-3, atol=2e-4)
+
+
+UNARY_OPS = [100, 101, 102, 103, 104, 106, 109, 121, 122, 123, 124, 130, 131, 132, 133, 134, 137, 141, 142, 143, 148]
+BINARY_OPS = [0, 1, 2, 3, 4, 5, 6, 13, 14]
+
+
+@pytest.mark.parametrize("variant,M", [(L.VARIANT_GEMV_MMA, 1), (L.VARIANT_GEMV_MMA, 5), (L.VARIANT_GENERIC, 3), (L.VARIANT_GEMM_TC, 40)])
+@pytest.mark.parametrize("ftype,fop", [(1, op) for op in UNARY_OPS] + [(2, op) for op in BINARY_OPS])
+def test_every_fused_epilogue_op(variant, M, ftype, fop):
+    """All 21 unary and 9 binary epilogue operations of the reference (MatMulQ4Common.cuh:63-114) in the decode
+    mat-vec (diagonal and shared-k variants), the any-shape kernel and the tensor-core GEMM, against the
+    checker's epilogue applied to the checker's matmul.  The kernels' accumulators differ from the checker's in
+    the last bits, and several operations are steep or discontinuous (1/x, log, floor, mod, pow), so an output
+    passes when it is close to the checker's, or lies within the range the checker's operation takes over
+    accumulator +- 2e-3 (relative to max(1, |acc|); 4e-3 for the GEMM, whose weights are rounded to fp16).  NaNs must agree, except within that distance of the edge of an operation's domain
+    (sqrt, log, rsqrt of an accumulator next to zero)."""
+    from gpu_util import run_blocks
+
+    K, N = 512, 256
+    A, W = _inputs(synth.Q8_0, M, K, N, np.float16, seed=300 + fop + 7 * ftype)
+    # accumulators of a few units (a power-of-two rescale, exact in fp16): exp and pow stay finite, few sit next to zero
+    spread = float(np.std(_ref(synth.Q8_0, A, W, M, K, N)))
+    A = (A.astype(np.float32) * np.float32(2.0 ** round(np.log2(1.5 / spread)))).astype(np.float16)
+    D = (synth.make_activations(M, N, 301 + fop) * 0.5 + 0.25).astype(np.float32) if ftype == 2 else None
+    got, used, st = run_blocks(synth.Q8_0, A, W, N, variant=variant, D_np=D, fusion_type=ftype, fusion_op=fop)
+    assert used == variant and st == 0
+    acc = _ref(synth.Q8_0, A, W, M, K, N).astype(np.float32)
+    # (the tensor-core GEMM rounds its weights to fp16: a wider band)
+    delta = (4e-3 if variant == L.VARIANT_GEMM_TC else 2e-3) * np.maximum(1.0, np.abs(acc))
+
+    def apply(x):
+        out = np.empty_like(x)
+        for i in np.ndindex(x.shape):
+            out[i] = O.epilogue(float(x[i]), ftype, fop, float(D[i]) if D is not None else 0.0)
+        return out
+
+    with np.errstate(all="ignore"):
+        r0 = apply(acc)
+        # the operation over the band around the accumulator (kinks and jumps inside it included)
+        band = np.stack([apply((acc + t * delta).astype(np.float32)) for t in np.linspace(-1.0, 1.0, 17)])
+        lo, hi = np.nanmin(np.where(np.isnan(band), np.inf, band), axis=0), np.nanmax(np.where(np.isnan(band), -np.inf, band), axis=0)
+        tol = 1e-4 + 2e-3 * np.abs(r0)
+        tol = np.where(np.isfinite(tol), tol, 1e-4)
+        near = np.abs(got - r0) <= tol
+        step = np.where(np.isfinite(hi - lo), (hi - lo) / 16.0, 0.0)  # what the operation moves between two samples of the band
+        between = (got >= lo - tol - step) & (got <= hi + tol + step)
+        edge = np.isnan(band).any(axis=0) & ~np.isnan(band).all(axis=0)  # the band crosses the edge of the operation's domain
+        both_nan = np.isnan(got) & np.isnan(r0)
+        same_inf = np.isinf(got) & (got == r0)
+    bad = ~(near | between | both_nan | same_inf | edge)
+    assert not bad.any(), (int(bad.sum()), got[bad][:4], r0[bad][:4], acc[bad][:4])
+    assert edge.mean() < 0.05
+
+
+def test_gemm_tc_reports_fp32_activations_beyond_the_fp16_range():
+    """The tensor-core GEMM's operand type is fp16: an fp32 activation beyond 65504 would become infinity.  The
+    cast kernel reports it through the status word (CUTB_ERR_RANGE) instead of letting it pass silently; the
+    same activations are fine for the decode mat-vec (block floating point at fp32 range) and for the any-shape
+    kernel."""
+    from gpu_util import rel_l2, run_blocks
+
+    M, K, N = 40, 512, 256
+    A, W = _inputs(synth.Q8_0, M, K, N, np.float32, seed=808)
+    A[7, 100] = 1.0e5
+    _, used, st = run_blocks(synth.Q8_0, A, W, N, variant=L.VARIANT_GEMM_TC)
+    assert used == L.VARIANT_GEMM_TC and st == L.ERR_RANGE
+    got, _, st = run_blocks(synth.Q8_0, A, W, N, variant=L.VARIANT_GENERIC)
+    assert st == 0 and rel_l2(got, _ref(synth.Q8_0, A, W, M, K, N)) <= TOL
+    got, used, st = run_blocks(synth.Q8_0, A[:8], W, N)
+    assert used == L.VARIANT_GEMV_MMA and st == 0 and rel_l2(got, _ref(synth.Q8_0, A[:8], W, 8, K, N)) <= TOL
+    A[7, 100] = 6.0e4  # inside the range: no report
+    _, _, st = run_blocks(synth.Q8_0, A, W, N, variant=L.VARIANT_GEMM_TC)
+    assert st == 0
 
 
 def test_large_activation_magnitudes_fp32():
@@ -341,6 +456,47 @@ def _run_planes(q4, A, B, S, M, K, N, *, affine=False, D=None, ftype=0, fop=0, d
                       fusion_type=ftype, fusion_op=fop)
     torch.cuda.synchronize()
     return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("q4,affine", [(False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (1, 4096, 11008), (2, 2048, 1001), (3, 1024, 264), (4, 512, 38), (1, 96, 8),
+                                   (1, 14336, 512)])
+def test_plane_layout_matvec_matches_checker_and_anyshape_kernel(q4, affine, dtype, M, K, N):
+    """The coalesced mat-vec over the reference's [K, N] planes (one to four rows; K split over warps and,
+    for narrow matrices, over blocks with partial sums in the workspace) against the checker's element
+    semantics (MatMulQ4Common.cuh:126-153, MatMulQ8Common.cuh:127-200) and against the any-shape kernel on
+    the same operands; odd N, strides padded to 4, a K that is not a multiple of 256, the affine mins."""
+    import torch
+
+    from cut_b200 import ops
+    from gpu_util import dev, rel_l2
+
+    if q4 and N % 2:
+        N += 1  # nibble pairs
+    rng = np.random.default_rng(K + N + M)
+    ldb, lds = R.pad4(N // 2 if q4 else N), R.pad4(N)
+    B = rng.integers(0, 256, size=(K, ldb), dtype=np.uint8)
+    nsb = K // 32 * (2 if affine else 1)
+    S = np.zeros((nsb, lds), np.float16)
+    S[: K // 32] = rng.uniform(0.002, 0.02, size=(K // 32, lds)).astype(np.float16)
+    if affine:
+        S[K // 32:] = rng.uniform(-0.05, 0.05, size=(K // 32, lds)).astype(np.float16)
+    A = synth.make_activations(M, K, 5 + M, dtype)
+    D = synth.make_activations(M, N, 6 + M)
+    want = O.qmatmul_planes(q4, affine, A.astype(np.float32), B, S.view(np.uint16), M, K, N, lda=K, ldb=ldb, lds=lds, acc64=True,
+                            D=D, fusion_type=2, fusion_op=0)
+    outs = {}
+    for variant in (L.VARIANT_GEMV_PLANES, L.VARIANT_GENERIC):
+        out = ops.qmatmul(dev(A), dev(B), L.Q4_0 if q4 else L.Q8_0, N, layout=L.LAYOUT_KN_PLANES, scales=dev(S.view(np.uint16)),
+                          affine=affine, ldb=ldb, lds=lds, D=dev(D), fusion_type=2, fusion_op=0, variant=variant)
+        torch.cuda.synchronize()
+        outs[variant] = out.cpu().numpy()
+    assert rel_l2(outs[L.VARIANT_GEMV_PLANES], want) <= 1e-5
+    assert rel_l2(outs[L.VARIANT_GEMV_PLANES], outs[L.VARIANT_GENERIC]) <= 1e-5
+    again = ops.qmatmul(dev(A), dev(B), L.Q4_0 if q4 else L.Q8_0, N, layout=L.LAYOUT_KN_PLANES, scales=dev(S.view(np.uint16)),
+                        affine=affine, ldb=ldb, lds=lds, D=dev(D), fusion_type=2, fusion_op=0)
+    assert np.array_equal(again.cpu().numpy(), outs[L.VARIANT_GEMV_PLANES])  # the default choice, and deterministic
 
 
 def test_reference_q8_simple_and_withscales():
