@@ -1008,6 +1008,11 @@ struct ExchangeArgs {
 };
 __global__ void peer_exchange_kernel(const ExchangeArgs a, unsigned long long *step_counter, int *status) {
   __shared__ unsigned long long step;
+  // Launched with programmatic stream serialization: the mat-vec behind this kernel may start its weight prefetch
+  // now (it waits for this kernel's completion before it touches activations or outputs); this kernel itself waits
+  // for the kernels before it -- whose peer stores it publishes -- to complete and flush.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) step = ++*step_counter;
   __threadfence_system();
   __syncthreads();
@@ -1319,8 +1324,16 @@ int peer_exchange_launch(const cutb_peer_scatter &peers, uint64_t *step_counter,
   a.rank = peers.rank;
   for (int q = 0; q < CUTB_MAX_PEERS; ++q)
     a.flag[q] = q < (int)peers.world ? reinterpret_cast<unsigned long long *>(peers.flag_peers[q]) : nullptr;
-  peer_exchange_kernel<<<1, 32, 0, stream>>>(a, reinterpret_cast<unsigned long long *>(step_counter), status);
-  CUTB_CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUTB_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_exchange_kernel, a, reinterpret_cast<unsigned long long *>(step_counter), status));
   return CUTB_OK;
 }
 
