@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 HOST_LIB = os.path.join(HERE, "libcut_host.so")
-HOST_SOURCES = ["cut_api.cpp", "b200_compute.cpp", "gguf_upload.cpp", "host_cabi.cpp"]
+HOST_SOURCES = ["cut_api.cpp", "b200_compute.cpp", "gguf_upload.cpp", "llama_runner.cpp", "host_cabi.cpp"]
 
 
 def _cuda_home() -> str:

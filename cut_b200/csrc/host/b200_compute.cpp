@@ -395,9 +395,21 @@ private:
     const KernelDesc &k = descOf(d);
     struct PC {
       uint32_t M, K, N, strideA, strideB, strideC, scaleStride;
-    } pc = pushConstants<PC>(d);
-    cutb_qmatmul_desc q{};
+    } pc;
+    struct PCN {  // with the fused RMSNorm: one more word
+      uint32_t M, K, N, strideA, strideB, strideC, scaleStride;
+      float normEps;
+    };
     const bool blocks = k.op == MatMulQBlocks;
+    float normEps = 0.f;
+    if (blocks && (k.flags & kBlockFlagRmsNorm)) {
+      const PCN n = pushConstants<PCN>(d);
+      std::memcpy(&pc, &n, sizeof(pc));
+      normEps = n.normEps;
+    } else {
+      pc = pushConstants<PC>(d);
+    }
+    cutb_qmatmul_desc q{};
     const DeviceBuffer &A = buf(d, 0), &W = buf(d, 1);
     size_t i = 2;
     q.layout = blocks ? CUTB_LAYOUT_GGUF_BLOCKS : CUTB_LAYOUT_KN_PLANES;
@@ -417,11 +429,21 @@ private:
       q.ldb = pc.strideB;
       q.lds = pc.scaleStride;
     }
-    const DeviceBuffer &D = buf(d, i++), &C = buf(d, i++);
+    // bindings behind the weights: D (binary fusion) or a stand-in, [the RMSNorm weight], C
+    const bool binary = k.fusionType == (uint32_t)MatMulFusion::Binary;
+    const DeviceBuffer *D = nullptr, *NW = nullptr;
+    if (binary) D = &buf(d, i++);
+    if (blocks && (k.flags & kBlockFlagRmsNorm)) NW = &buf(d, i++);
+    if (!binary) D = &buf(d, i++);
+    const DeviceBuffer &C = buf(d, i++);
     q.C = (float *)C.data;
     q.ldc = pc.strideC;
-    q.D = (const float *)D.data;
-    q.ldd = pc.strideC;
+    q.D = (const float *)D->data;
+    q.ldd = (pc.N + 3) & ~3u;
+    if (NW) {
+      q.a_norm_weight = (const float *)NW->data;
+      q.a_norm_eps = normEps;
+    }
     q.fusion_type = (int32_t)k.fusionType;
     q.fusion_op = (int32_t)k.fusionOp;
     // plane-layout variant indices (the reference's Tiled / GemvKPar8 / CoopMat ... tables) all map onto the library's
@@ -431,7 +453,7 @@ private:
     q.workspace = wsPtr();
     q.workspace_bytes = wsBytes();
     q.status = status_;
-    q.flags = 0;
+    q.flags = blocks ? k.flags : 0;  // kBlockFlag* are the C ABI's CUTB_FLAG_* bit for bit
     return q;
   }
 

@@ -103,14 +103,17 @@ void ComputeInterface::wait(const ComputeHandle &cb) { waitFor(cb); }
 // Kernel descriptors
 // ---------------------------------------------------------------------------
 std::vector<uint32_t> KernelDesc::encode() const {
-  return {kMagic, op, variant, dtypeA, dtypeB, fusionType, fusionOp, affine, format};
+  std::vector<uint32_t> w = {kMagic, op, variant, dtypeA, dtypeB, fusionType, fusionOp, affine, format};
+  if (flags) w.push_back(flags);
+  return w;
 }
 
 std::optional<KernelDesc> KernelDesc::decode(const std::vector<uint32_t> &w) {
-  if (w.size() != 9 || w[0] != kMagic) return std::nullopt;
+  if ((w.size() != 9 && w.size() != 10) || w[0] != kMagic) return std::nullopt;
   KernelDesc d;
   d.op = w[1]; d.variant = w[2]; d.dtypeA = w[3]; d.dtypeB = w[4];
   d.fusionType = w[5]; d.fusionOp = w[6]; d.affine = w[7]; d.format = w[8];
+  d.flags = w.size() == 10 ? w[9] : 0u;
   return d;
 }
 
@@ -315,11 +318,36 @@ void MatMulOpNode::setFusion(MatMulFusion fusion, OperatorEnum fusionOp, const T
   // (the reference falls back for float cooperative-matrix variants only, MatMulOp.cpp:400-417)
 }
 
+void MatMulOpNode::setBlockOptions(const MatMulBlockOptions &opt) {
+  if (format_ != QuantFormat::Blocks) throw std::runtime_error("matmul: block options need the raw-block constructor");
+  if (opt.flags & ~(kBlockFlagNoOverlap | kBlockFlagAct16 | kBlockFlagRmsNorm | kBlockFlagGluPairs))
+    throw std::runtime_error("matmul: unknown block option bits");
+  if (opt.flags & (kBlockFlagRmsNorm | kBlockFlagGluPairs)) {
+    // only the decode mat-vec has these (variant 1: K % 256 == 0, at most 16 virtual activation rows)
+    if (*spec_ != 1) throw std::runtime_error("matmul: fused RMSNorm / paired rows exist in the decode mat-vec only");
+  }
+  if (opt.flags & kBlockFlagGluPairs) {
+    if (fusion_ != MatMulFusion::Unary) throw std::runtime_error("matmul: paired gate/up rows need a unary fusion");
+    if (N_ % 2) throw std::runtime_error("matmul: paired gate/up rows need an even N");
+  }
+  if (opt.flags & kBlockFlagRmsNorm) {
+    if (!opt.normWeight) throw std::runtime_error("matmul: fused RMSNorm needs its weight");
+    const auto &w = store_->getTensor(opt.normWeight);
+    if (w.getDtype() != DataType::Float32 || w.getShape().size() != 1 || w.getShape()[0] != K_)
+      throw std::runtime_error("matmul: the RMSNorm weight must be Float32 [K]");
+    inputs_.push_back(opt.normWeight);  // binds after D
+    normEps_ = opt.normEps;
+  }
+  blockFlags_ = opt.flags;
+  if (opt.flags & kBlockFlagGluPairs) output_ = store_->createTensorEmpty(outputShape(), outputDtype());
+}
+
 size_t MatMulOpNode::shaderKey() const {
   size_t key = static_cast<size_t>(op_);
   key |= (static_cast<size_t>(dtypeA_) & 0xF) << 16;
   key |= (static_cast<size_t>(dtypeB_) & 0xF) << 20;
   if (format_ == QuantFormat::Blocks) key |= (static_cast<size_t>(blockFormat_) & 0x1F) << 24;
+  key |= (static_cast<size_t>(blockFlags_) & 0xF) << 29;
   key |= (static_cast<size_t>(q4Affine_ ? 1 : 0)) << 35;
   key |= (static_cast<size_t>(fusion_) & 0xF) << 36;
   if (fusion_ != MatMulFusion::None) key |= (static_cast<size_t>(fusionOp_) & 0xFF) << 40;
@@ -346,6 +374,7 @@ std::optional<std::vector<uint32_t>> MatMulOpNode::shader() const {
   d.fusionType = (uint32_t)fusion_;
   d.fusionOp = fusion_ != MatMulFusion::None ? (uint32_t)fusionOp_ : 0u;
   d.affine = q4Affine_ ? 1u : 0u;
+  d.flags = blockFlags_;
   return d.encode();
 }
 
@@ -364,10 +393,18 @@ std::vector<uint8_t> MatMulOpNode::pushConstants() const {
   uint32_t strideB = (N_ + 3) & ~3u;
   if (format_ == QuantFormat::Q4) strideB = (N_ / 2 + 3) & ~3u;
   if (format_ == QuantFormat::Blocks) strideB = (K_ / blockElems(blockFormat_)) * blockBytes(blockFormat_);
-  const uint32_t strideC = (N_ + 3) & ~3u, scaleStride = (N_ + 3) & ~3u;
+  const uint32_t nOut = (blockFlags_ & kBlockFlagGluPairs) ? N_ / 2 : N_;
+  const uint32_t strideC = (nOut + 3) & ~3u, scaleStride = (N_ + 3) & ~3u;
   struct {
     uint32_t M, K, N, strideA, strideB, strideC, scaleStride;
   } pc{M_, K_, N_, strideA, strideB, strideC, scaleStride};
+  if (blockFlags_ & kBlockFlagRmsNorm) {  // one more word: the epsilon
+    struct {
+      uint32_t M, K, N, strideA, strideB, strideC, scaleStride;
+      float normEps;
+    } pcn{M_, K_, N_, strideA, strideB, strideC, scaleStride, normEps_};
+    return toBytes(pcn);
+  }
   return toBytes(pc);
 }
 
@@ -1055,6 +1092,14 @@ Tensor Operations::matmulBlocksBinary(OperatorEnum binaryOp, const Tensor &a, co
                                       uint32_t N, const Tensor &d, std::optional<uint32_t> spec) {
   auto node = std::make_unique<MatMulOpNode>(*store_, a, raw, f, N, spec);
   node->setFusion(MatMulFusion::Binary, binaryOp, d);
+  return dispatch(std::move(node));
+}
+
+Tensor Operations::matmulBlocksFused(const Tensor &a, const Tensor &raw, DequantFormat f, uint32_t N, const MatMulBlockOptions &opt,
+                                     MatMulFusion fusion, OperatorEnum fusionOp, const Tensor &d) {
+  auto node = std::make_unique<MatMulOpNode>(*store_, a, raw, f, N, std::nullopt);
+  if (fusion != MatMulFusion::None) node->setFusion(fusion, fusionOp, d);
+  node->setBlockOptions(opt);
   return dispatch(std::move(node));
 }
 

@@ -162,6 +162,7 @@ struct KernelDesc {
   uint32_t fusionType = 0, fusionOp = 0;  ///< specialisation constants 1 and 2
   uint32_t affine = 0;    ///< specialisation constant 3
   uint32_t format = 0;    ///< block format (Blocks / Dequantize)
+  uint32_t flags = 0;     ///< MatMulQBlocks: kBlockFlag* bits (a tenth word, present only when non-zero)
   std::vector<uint32_t> encode() const;
   static std::optional<KernelDesc> decode(const std::vector<uint32_t> &words);
 };
@@ -309,6 +310,18 @@ enum class MatMulFusion { None, Unary, Binary };
 /// plus the 32-weight block formats it only dequantises on the CPU (gguf_reader.cpp:541-660, 826-850).
 enum class DequantFormat : uint32_t { BF16 = 0, Q4_K = 1, Q5_K = 2, Q6_K = 3, Q8_0 = 16, Q4_0 = 17, Q4_1 = 18, Q5_0 = 19 };
 
+/// Extras of the block-layout decode mat-vec that a runner's per-token step uses (bit values = the C ABI's
+/// CUTB_FLAG_*): kBlockFlagNoOverlap -- the launch does not prefetch under its predecessor; kBlockFlagAct16 -- fp32
+/// activations staged at one 16-bit level per 32-k block; kBlockFlagRmsNorm -- the RMSNorm in front of the
+/// projection applied while the activations are staged (needs normWeight); kBlockFlagGluPairs -- rows stored as
+/// (gate_i, up_i) pairs, C[m, i] = unary(acc[2i]) * acc[2i + 1] (needs a unary fusion; output [M, N / 2]).
+enum : uint32_t { kBlockFlagNoOverlap = 1, kBlockFlagAct16 = 2, kBlockFlagRmsNorm = 4, kBlockFlagGluPairs = 8 };
+struct MatMulBlockOptions {
+  uint32_t flags = 0;
+  Tensor normWeight;       ///< Float32 [K], with kBlockFlagRmsNorm
+  float normEps = 1e-5f;
+};
+
 class MatMulOpNode : public OpNode {
 public:
   /// Quantized matmul over the reference's plane layout; detects Q8 / Q4 / affine Q4 from the
@@ -322,10 +335,15 @@ public:
   MatMulFusion fusion() const { return fusion_; }
   bool affine() const { return q4Affine_; }
   void setFusion(MatMulFusion fusion, OperatorEnum fusionOp = {}, const Tensor &d = {});
+  /// Block layout only, after setFusion(); throws std::runtime_error on combinations no kernel has.
+  void setBlockOptions(const MatMulBlockOptions &opt);
+  uint32_t blockFlags() const { return blockFlags_; }
   DataType outputDtype() const override { return DataType::Float32; }
   size_t shaderKey() const override;
   std::optional<std::vector<uint32_t>> shader() const override;
-  std::vector<uint32_t> outputShape() const override { return {M_, N_}; }
+  std::vector<uint32_t> outputShape() const override {
+    return {M_, (blockFlags_ & kBlockFlagGluPairs) ? N_ / 2 : N_};
+  }
   ThreadSize dispatchSize() const override;
   std::vector<uint8_t> pushConstants() const override;
   std::vector<ComputeBinding> bindings() const override;
@@ -345,6 +363,8 @@ private:
   bool autoSpec_ = false, q4Affine_ = false;
   uint32_t fusionFallbackSpec_ = 0;
   DequantFormat blockFormat_ = DequantFormat::Q4_K;
+  uint32_t blockFlags_ = 0;
+  float normEps_ = 0.f;
 };
 
 class DequantOpNode : public OpNode {
@@ -631,6 +651,11 @@ public:
                            uint32_t N, std::optional<uint32_t> spec = {});
   Tensor matmulBlocksBinary(OperatorEnum binaryOp, const Tensor &a, const Tensor &rawBlocks, DequantFormat format,
                             uint32_t N, const Tensor &d, std::optional<uint32_t> spec = {});
+  /// The block-layout matmul with a runner's extras (fused RMSNorm of A, paired gate / up rows, staging and
+  /// overlap flags); `fusion` / `fusionOp` / `d` as in matmulBlocksUnary / matmulBlocksBinary.
+  Tensor matmulBlocksFused(const Tensor &a, const Tensor &rawBlocks, DequantFormat format, uint32_t N,
+                           const MatMulBlockOptions &opt, MatMulFusion fusion = MatMulFusion::None, OperatorEnum fusionOp = {},
+                           const Tensor &d = {});
   Tensor transposeQ4(const Tensor &packedInput, uint32_t N, uint32_t K);
   Tensor dequantize(const Tensor &rawData, uint32_t format, uint32_t rows, uint32_t cols);
   /// Raw blocks of `format` -> Q8_0 GGUF blocks (a 1-D Int8 tensor matmulBlocks takes with DequantFormat::Q8_0).

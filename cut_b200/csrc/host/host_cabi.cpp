@@ -6,7 +6,11 @@
 #include <exception>
 #include <vector>
 
+#include <stdexcept>
+
 #include "cut_api.h"
+#include "gguf_upload.h"
+#include "llama_runner.h"
 
 using namespace cut;
 
@@ -56,6 +60,59 @@ extern "C" __attribute__((visibility("default"))) int cut_host_e2e_matvec_blocks
     if (seconds) *seconds = std::chrono::duration<double>(t1 - t0).count();
     if (h2d_bytes_per_step) *h2d_bytes_per_step = (uint64_t)replicas * a_bytes;
     if (d2h_bytes_per_step) *d2h_bytes_per_step = (uint64_t)replicas * c_bytes;
+    return 0;
+  } catch (const std::exception &e) {
+    if (err && err_cap) snprintf(err, err_cap, "%s", e.what());
+    return -1;
+  }
+}
+
+// Greedy decoding of a llama-style GGUF model through LlamaRunner (llama_runner.h): the prompt is fed one token
+// per step (positions 0, 1, ...), then `n_generate` tokens are generated from the arg-max of each step.
+//
+//   option_bits   1 fused RMSNorms, 2 paired gate / up rows, 4 activations staged at 16 bits, 8 fp16 KV cache
+//   tokens_out    [n_prompt + n_generate] the arg-max after every step (tokens_out[i] is what follows step i)
+//   logits_out    null, or [n_prompt + n_generate][vocab] the logits of every step
+//   seconds       wall time of the generation steps only (the prompt steps are warm-up)
+// Returns 0, or -1 with a message in err.
+extern "C" __attribute__((visibility("default"))) int cut_host_llama_generate(
+    int device, const char *gguf_path, uint32_t max_seq, uint32_t option_bits, const uint32_t *prompt, uint32_t n_prompt,
+    uint32_t n_generate, uint32_t *tokens_out, float *logits_out, uint32_t *vocab_out, double *seconds, uint64_t *weight_bytes_per_token,
+    uint32_t *dispatches_per_token, char *err, size_t err_cap) {
+  try {
+    if (!gguf_path || !prompt || n_prompt == 0 || !tokens_out) throw std::runtime_error("llama_generate: null argument or empty prompt");
+    Runtime rt(device);
+    GGUFFile file(gguf_path);
+    LlamaRunnerOptions opt;
+    opt.maxSeq = max_seq;
+    opt.fuseNorm = (option_bits & 1u) != 0;
+    opt.gluPairs = (option_bits & 2u) != 0;
+    opt.act16 = (option_bits & 4u) != 0;
+    opt.kvHalf = (option_bits & 8u) != 0;
+    LlamaRunner runner(rt, file, opt);
+    const uint32_t vocab = runner.config().vocab;
+    if (vocab_out) *vocab_out = vocab;
+    if (weight_bytes_per_token) *weight_bytes_per_token = runner.weightBytesPerToken();
+    if (dispatches_per_token) *dispatches_per_token = (uint32_t)runner.dispatchesPerToken();
+    uint32_t pos = 0, next = 0;
+    auto keep = [&](uint32_t step) {
+      tokens_out[step] = next;
+      if (logits_out) {
+        const std::vector<float> l = runner.logits();
+        std::memcpy(logits_out + (size_t)step * vocab, l.data(), (size_t)vocab * sizeof(float));
+      }
+    };
+    for (uint32_t i = 0; i < n_prompt; ++i, ++pos) {
+      next = runner.forward(prompt[i], pos);
+      keep(i);
+    }
+    const auto t0 = std::chrono::steady_clock::now();
+    for (uint32_t i = 0; i < n_generate; ++i, ++pos) {
+      next = runner.forward(next, pos);
+      keep(n_prompt + i);
+    }
+    const auto t1 = std::chrono::steady_clock::now();
+    if (seconds) *seconds = std::chrono::duration<double>(t1 - t0).count();
     return 0;
   } catch (const std::exception &e) {
     if (err && err_cap) snprintf(err, err_cap, "%s", e.what());

@@ -329,3 +329,72 @@ class LlamaDecoder:
         if st:
             raise L.CutbError(st, "a kernel of the decode step reported an error (position past the cache, token past the "
                                   "vocabulary, or an expired bounded wait)")
+
+
+# ---- the same model as a GGUF file, and the C++ runner over it ------------------------------------------------------
+_GGML_NAME = {L.Q8_0: "Q8_0", L.Q4_0: "Q4_0", L.Q4_K: "Q4_K"}
+
+
+def write_model_gguf(path: str, cfg: LlamaConfig, weights: dict) -> None:
+    """Writes `weights` (the dict of synthetic_weights) as a llama-architecture GGUF v3 file with the tensor names and
+    metadata keys the reference's runner reads (interface/runner/llama/llama.cpp:1084-1118, 831-866): Q / K / V as
+    three tensors (rows of the fused matrix), norms and the embedding table F32, block weights as raw blocks."""
+    from .gguf_write import write_gguf
+
+    t = _GGML_NAME[cfg.fmt]
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32).view(np.uint8).reshape(-1)
+    tensors = [("token_embd.weight", "F32", (cfg.vocab, cfg.hidden), f32(weights["embedding"])),
+               ("output_norm.weight", "F32", (cfg.hidden,), f32(weights["final_norm"])),
+               ("output.weight", t, (cfg.vocab, cfg.hidden), weights["lm_head"])]
+    rb = synth.row_bytes(cfg.fmt, cfg.hidden)
+    for l, lw in enumerate(weights["layers"]):
+        b = f"blk.{l}."
+        qkv = lw["wqkv"].reshape(cfg.q_dim + 2 * cfg.kv_dim, rb)
+        tensors += [(b + "attn_norm.weight", "F32", (cfg.hidden,), f32(lw["attn_norm"])),
+                    (b + "attn_q.weight", t, (cfg.q_dim, cfg.hidden), qkv[: cfg.q_dim].reshape(-1)),
+                    (b + "attn_k.weight", t, (cfg.kv_dim, cfg.hidden), qkv[cfg.q_dim: cfg.q_dim + cfg.kv_dim].reshape(-1)),
+                    (b + "attn_v.weight", t, (cfg.kv_dim, cfg.hidden), qkv[cfg.q_dim + cfg.kv_dim:].reshape(-1)),
+                    (b + "attn_output.weight", t, (cfg.hidden, cfg.q_dim), lw["wo"]),
+                    (b + "ffn_norm.weight", "F32", (cfg.hidden,), f32(lw["ffn_norm"])),
+                    (b + "ffn_gate.weight", t, (cfg.ffn, cfg.hidden), lw["wgate"]),
+                    (b + "ffn_up.weight", t, (cfg.ffn, cfg.hidden), lw["wup"]),
+                    (b + "ffn_down.weight", t, (cfg.hidden, cfg.ffn), lw["wdown"])]
+    meta = {"general.architecture": "llama", "llama.embedding_length": cfg.hidden, "llama.block_count": cfg.n_layers,
+            "llama.attention.head_count": cfg.n_heads, "llama.attention.head_count_kv": cfg.n_kv_heads,
+            "llama.attention.key_length": cfg.head_dim, "llama.feed_forward_length": cfg.ffn, "llama.context_length": cfg.max_seq,
+            "llama.rope.freq_base": float(cfg.rope_theta), "llama.attention.layer_norm_rms_epsilon": float(cfg.eps)}
+    write_gguf(path, meta, tensors)
+
+
+def run_cpp_runner(path: str, prompt, n_generate: int, *, device: int = 0, max_seq: int = 512, fuse_norm: bool = True,
+                   glu_pairs: bool = True, act_16bit: bool = True, kv_half: bool = True, want_logits: bool = False) -> dict:
+    """Greedy decoding through the C++ LlamaRunner of libcut_host.so (Runtime -> GGUFFile -> GGUFUploader -> the recorded
+    per-token command buffer): the prompt token by token, then n_generate tokens.  Returns the arg-max after every step,
+    optionally every step's logits, the seconds spent on the generation steps and the runner's own counts."""
+    from . import build
+
+    lib = C.CDLL(build.build_host())
+    fn = lib.cut_host_llama_generate
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_int, C.c_char_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
+                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]
+    prompt = np.ascontiguousarray(prompt, dtype=np.uint32)
+    steps = len(prompt) + n_generate
+    toks = np.zeros(steps, dtype=np.uint32)
+    vocab, disp = C.c_uint32(0), C.c_uint32(0)
+    secs, wbytes = C.c_double(0.0), C.c_uint64(0)
+    err = C.create_string_buffer(512)
+    bits = (1 if fuse_norm else 0) | (2 if glu_pairs else 0) | (4 if act_16bit else 0) | (8 if kv_half else 0)
+    logits = None
+    if want_logits:
+        # the vocabulary is in the file: token_embd's outer dimension; a first call without logits reports it
+        if fn(device, path.encode(), max_seq, bits, prompt.ctypes.data, 1, 0, toks.ctypes.data, None, C.byref(vocab), None, None, None,
+              err, len(err)) != 0:
+            raise RuntimeError(f"cut_host_llama_generate: {err.value.decode()}")
+        logits = np.zeros((steps, vocab.value), dtype=np.float32)
+    rc = fn(device, path.encode(), max_seq, bits, prompt.ctypes.data, len(prompt), n_generate, toks.ctypes.data,
+            logits.ctypes.data if logits is not None else None, C.byref(vocab), C.byref(secs), C.byref(wbytes), C.byref(disp), err, len(err))
+    if rc != 0:
+        raise RuntimeError(f"cut_host_llama_generate: {err.value.decode()}")
+    return {"tokens": toks, "logits": logits, "seconds": secs.value, "weight_bytes_per_token": wbytes.value,
+            "dispatches_per_token": disp.value, "vocab": vocab.value}

@@ -153,3 +153,39 @@ def test_position_past_the_cache_is_reported():
     dec.step(1, 4)
     with pytest.raises(L.CutbError):
         dec.check_status()
+
+
+@pytest.mark.parametrize("fuse_norm,glu", [(True, True), (False, False), (True, False)])
+@pytest.mark.parametrize("fmt", [2, 0, 1])
+def test_cpp_runner_over_a_gguf_file_matches_composed_checker(tmp_path, fmt, fuse_norm, glu):
+    """The per-token step as the C++ host records it (LlamaRunner: GGUF header -> device upload with fused QKV and
+    paired gate / up rows -> one reusable command buffer over the operator API, replayed per token): every step's
+    logits against the float64 composition of the checker's pieces, its arg-max against the logits it returns,
+    and greedy generation consistent with them."""
+    from cut_b200.llama_decode import LlamaConfig, run_cpp_runner, synthetic_weights, write_model_gguf
+
+    cfg = LlamaConfig(n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=512, max_seq=32, fmt=fmt)
+    w = synthetic_weights(cfg, seed=fmt + 11)
+    for lw in w["layers"]:
+        for k in ("wqkv", "wo", "wgate", "wup", "wdown"):
+            lw[k] = _soften(lw[k], fmt)
+    w["lm_head"] = _soften(w["lm_head"], fmt)
+    w["embedding"] = (w["embedding"] * 50).astype(np.float32)
+    path = str(tmp_path / "model.gguf")
+    write_model_gguf(path, cfg, w)
+    prompt, n_gen = [3, 500, 17, 17, 0, 301, 42], 5
+    out = run_cpp_runner(path, prompt, n_gen, max_seq=cfg.max_seq, fuse_norm=fuse_norm, glu_pairs=glu, want_logits=True)
+    assert out["vocab"] == cfg.vocab and out["logits"].shape == (len(prompt) + n_gen, cfg.vocab)
+    # separate RMSNorm launches when not fused; gate and up as two launches when not paired; RoPE and attention are two
+    per_layer = 6 + (0 if fuse_norm else 2) + (0 if glu else 1)
+    assert out["dispatches_per_token"] >= 3 + (0 if fuse_norm else 1) + per_layer * cfg.n_layers
+    ref = Reference(cfg, w)
+    feed = list(prompt)
+    for step in range(len(prompt) + n_gen):
+        want = ref.step(feed[step], step)
+        got = out["logits"][step].astype(np.float64)
+        rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+        assert np.isfinite(got).all() and rel <= 1e-3, (step, rel)
+        assert int(out["tokens"][step]) == int(np.argmax(out["logits"][step]))
+        if step + 1 >= len(prompt):
+            feed.append(int(out["tokens"][step]))  # generation continues with the runner's own greedy pick
