@@ -196,7 +196,8 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
-def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = True, synthetic_cache: bool = False) -> dict:
+def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = True, synthetic_cache: bool = False,
+                       weights: dict | None = None) -> dict:
     """configs[3]: Llama-style decoder (hidden 4096, 32 query / 8 KV heads of 128, FFN 14336, vocab 32000, Q4_K
     projections, fp16 KV cache of 2048 rows): a prompt of 512 random token ids, then batch-1 greedy decode of
     `steps` tokens.  The prompt runs as one batch (tensor-core GEMM projections, batched RoPE cache write, one
@@ -210,7 +211,7 @@ def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = 
     cfg = LlamaConfig(n_layers=n_layers)
     # super-block scales divided by 128: the configuration's Q4_K distribution has a positive mean (~2), every
     # projection then sums coherently and SiLU(gate) * up leaves fp16, the operand type of the prefill GEMM
-    dec = LlamaDecoder(cfg, synthetic_weights(cfg, seed=41, distinct_layers=False, scale_shift=7), dev)
+    dec = LlamaDecoder(cfg, weights if weights is not None else synthetic_weights(cfg, seed=41, distinct_layers=False, scale_shift=7), dev)
     prompt = np.random.default_rng(42).integers(0, cfg.vocab, 512)
     p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     p0.record()
@@ -258,6 +259,28 @@ def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = 
             "fp16; rows 0..511 written by the batched prefill of the 512-token prompt",
             "prefill_ms": prompt_ms, "prefill_tok/s": 512e3 / prompt_ms,
             "activations": "fp32, staged at 16 bits per 32-k block"}
+
+
+def cpp_runner_measurement(device_index: int, cfg, weights: dict, steps: int = 128) -> dict:
+    """configs[3] through the C++ host: the same synthetic model written as a GGUF file, loaded by GGUFFile / GGUFUploader
+    (fused QKV, paired gate / up rows), the per-token step recorded by LlamaRunner over the operator API into one
+    reusable command buffer and replayed per token.  Per token the host writes {pos, seqLen} and the token id, resubmits,
+    waits and reads the arg-max back, as the reference's runner does (interface/runner/llama/llama.cpp:2090-2166), so
+    tok/s here includes that round trip.  A 16-token prompt is fed token by token, then `steps` greedy tokens are timed."""
+    import tempfile
+
+    from cut_b200.llama_decode import run_cpp_runner, write_model_gguf
+
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "model.gguf")
+        write_model_gguf(path, cfg, weights)
+        prompt = np.random.default_rng(42).integers(0, cfg.vocab, 16)
+        r = run_cpp_runner(path, prompt, steps, device=device_index, max_seq=cfg.max_seq)
+    return {"tok/s": steps / r["seconds"], "ms_per_token": 1e3 * r["seconds"] / steps, "tokens": steps,
+            "dispatches_per_token": r["dispatches_per_token"], "weight_bytes_per_token": r["weight_bytes_per_token"],
+            "weight_GB/s": r["weight_bytes_per_token"] * steps / r["seconds"] / 1e9,
+            "host_round_trip_per_token": True, "context": "positions 16..%d" % (16 + steps - 1),
+            "path": "GGUF file -> GGUFUploader -> LlamaRunner (Operations, reusable command buffer) in libcut_host.so"}
 
 
 def chain_us(dev, fmt: int, n: int, k: int, m: int, act_dtype, flags: int = 0, total_mb: float = 600.0, seed: int = 51) -> dict:
@@ -480,7 +503,17 @@ def secondary_measurements(dev) -> dict:
             proj[f"{name} batch {m}"] = r
     out["configs[4]_70b_q4_0_projections_1gpu"] = proj
     torch.cuda.empty_cache()
-    out["configs[3]_llama_q4_k_decode_batch1"] = decode_measurement(dev)
+    from cut_b200.llama_decode import LlamaConfig, synthetic_weights
+
+    cfg4 = LlamaConfig()
+    w4 = synthetic_weights(cfg4, seed=41, distinct_layers=False, scale_shift=7)
+    out["configs[3]_llama_q4_k_decode_batch1"] = decode_measurement(dev, weights=w4)
+    torch.cuda.empty_cache()
+    try:
+        out["configs[3]_llama_q4_k_decode_cpp_runner"] = cpp_runner_measurement(dev.index or 0, cfg4, w4)
+    except Exception as e:  # noqa: BLE001  (context, never the headline)
+        out["configs[3]_llama_q4_k_decode_cpp_runner"] = {"error": f"{type(e).__name__}: {e}"}
+    del w4
     return out
 
 
