@@ -372,6 +372,62 @@ void reusableSurvivesWorkspaceGrowth() {
   CHECK(bad == 0);
 }
 
+// Results of a reusable command buffer are copied to pinned host memory behind every replay; reading them must
+// always give what the device buffer holds: the new result after every replay with new inputs, and the buffer's own
+// contents again once something else has written it.
+void resultCopiesFollowReplaysAndWrites() {
+  const uint32_t K = 512, N = 96;
+  std::vector<uint8_t> raw((size_t)N * (K / 32) * 34);
+  std::mt19937 gen(23);
+  for (auto &b : raw) b = (uint8_t)gen();
+  for (size_t blk = 0; blk < raw.size() / 34; ++blk) { uint16_t d = 0x2400; std::memcpy(&raw[blk * 34], &d, 2); }
+  std::vector<float> A1(K), A2(K), want(N), got(N);
+  for (uint32_t k = 0; k < K; ++k) A1[k] = (float)((int)(gen() % 17) - 8) / 8.0f, A2[k] = (float)((int)(gen() % 13) - 6) / 4.0f;
+  auto tA = rt->createTensor({K}, DataType::Float32, A1.data());
+  auto tW = rt->createTensor({(uint32_t)raw.size()}, DataType::Int8, raw.data());
+  auto tC = rt->ops().matmulBlocks(tA, tW, DequantFormat::Q8_0, N);
+  // a second operator consumes tC: tC is then no result of the command buffer (read back the slow way), tR is
+  std::vector<float> ones(N, 1.0f), gotR(N);
+  auto tOnes = rt->createTensor({N}, DataType::Float32, ones.data());
+  auto tR = rt->ops().rmsNorm(tC, tOnes, 1e-6f);
+  ComputeHandle cb = rt->iface().submitReusable();
+  rt->iface().wait(cb);
+  auto relErr = [&](const std::vector<float> &a) {
+    orc_qmatmul_blocks(0, a.data(), raw.data(), want.data(), nullptr, 1, K, N, K, N, 0, 0, 0, 0);
+    double num = 0, den = 0;
+    for (uint32_t n = 0; n < N; ++n) num += (got[n] - want[n]) * (double)(got[n] - want[n]), den += want[n] * (double)want[n];
+    return std::sqrt(num / den);
+  };
+  for (int round = 0; round < 4; ++round) {
+    const std::vector<float> &a = (round & 1) ? A2 : A1;
+    rt->copyToTensor(tA, a.data(), K * sizeof(float));
+    rt->iface().resubmit(cb);
+    rt->iface().wait(cb);
+    rt->copyFromTensor(tC, got.data(), N * sizeof(float));
+    CHECK(relErr(a) <= 1e-3);
+    rt->copyFromTensor(tR, gotR.data(), N * sizeof(float));
+    double ss = 0;
+    for (uint32_t n = 0; n < N; ++n) ss += got[n] * (double)got[n];
+    const double inv = 1.0 / std::sqrt(ss / N + 1e-6);
+    double worst = 0;
+    for (uint32_t n = 0; n < N; ++n) worst = std::max(worst, std::fabs(gotR[n] - got[n] * inv));
+    CHECK(worst <= 1e-4 * (1.0 + std::sqrt(ss / N) * inv));
+  }
+  // something else writes the result buffer: the next read returns the buffer, not the stale copy
+  std::vector<float> sevens(N, 7.0f);
+  rt->copyToTensor(tR, sevens.data(), N * sizeof(float));
+  rt->copyFromTensor(tR, gotR.data(), N * sizeof(float));
+  int bad = 0;
+  for (uint32_t n = 0; n < N; ++n) bad += (gotR[n] != 7.0f);
+  CHECK(bad == 0);
+  // and a replay refreshes it again
+  rt->copyToTensor(tA, A1.data(), K * sizeof(float));
+  rt->iface().resubmit(cb);
+  rt->iface().wait(cb);
+  rt->copyFromTensor(tC, got.data(), N * sizeof(float));
+  CHECK(relErr(A1) <= 1e-3);
+}
+
 // GGUF file -> device weights without the CPU detour (interface/runner/llama/llama.cpp:831-866, 934-1027): raw blocks
 // are uploaded as they lie in the file; fused QKV is a concatenation of rows, gate / up become alternating rows for the
 // paired mat-vec, a Q6_K tensor is re-encoded to Q8_0 blocks on the device.  Every product is checked against the CPU
@@ -739,6 +795,7 @@ int main() {
     RUN(blocksEntryPoint);
     RUN(reusableCommandBuffer);
     RUN(reusableSurvivesWorkspaceGrowth);
+    RUN(resultCopiesFollowReplaysAndWrites);
     RUN(ggufUploadAndMatmul);
     RUN(errorBehaviour);
     RUN(rmsNormCases);
