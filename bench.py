@@ -945,7 +945,9 @@ def run_ours(args) -> None:
         e2e = {"value": e2e_steps * REPLICAS * bytes_per_launch / hs / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "steps": e2e_steps, "ms_per_step": 1e3 * hs / e2e_steps,
                "path": "C++ operator API (Operations::matmulBlocks -> Dispatcher -> B200Compute): per step copyDataToBuffer of "
-               "every activation, resubmit of the recorded command buffer, wait, copyDataFromBuffer of every result"}
+               "every activation, resubmit of the recorded command buffer, wait, copyDataFromBuffer of every result; inside the "
+               "backend the uploads go out as one transfer plus one scatter launch and the results come back as one gather launch "
+               "plus one transfer behind the replay"}
 
     if int(status.item()) != 0:
         raise SystemExit(f"bench: device status word = {int(status.item())}")

@@ -25,7 +25,7 @@ FLAG_STAGE_PER_CTA = 16
 # every symbol include/cutb.h declares
 EXPORTS = [
     "cutb_qmatmul_workspace_bytes", "cutb_qmatmul_select_variant", "cutb_qmatmul", "cutb_qmatmul_decode_noalloc",
-    "cutb_qmatmul_scatter", "cutb_peer_exchange",
+    "cutb_qmatmul_scatter", "cutb_peer_exchange", "cutb_copy_batch",
     "cutb_peer_buffer_alloc", "cutb_peer_buffer_open", "cutb_peer_buffer_close", "cutb_peer_buffer_free",
     "cutb_rmsnorm", "cutb_embedding", "cutb_embedding_col", "cutb_embedding_blocks", "cutb_argreduce",
     "cutb_rope_kv_write", "cutb_attention_workspace_bytes", "cutb_attention_decode", "cutb_rope_attention_decode",
@@ -89,6 +89,8 @@ def lib() -> C.CDLL:
         l.cutb_qmatmul_decode_noalloc.argtypes = [C.POINTER(QMatmulDesc), C.c_void_p]
         l.cutb_qmatmul_scatter.restype = C.c_int
         l.cutb_qmatmul_scatter.argtypes = [C.POINTER(QMatmulDesc), C.POINTER(PeerScatter), C.c_void_p]
+        l.cutb_copy_batch.restype = C.c_int
+        l.cutb_copy_batch.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p]
         l.cutb_peer_exchange.restype = C.c_int
         l.cutb_peer_exchange.argtypes = [C.POINTER(PeerScatter), C.c_void_p, C.c_void_p, C.c_void_p]
         l.cutb_peer_buffer_alloc.restype = C.c_int

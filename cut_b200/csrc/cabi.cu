@@ -604,6 +604,19 @@ int cutb_batched_attention(int kv_dtype, const float *q_in, uint32_t q_stride, c
                                   n_heads, n_kv_heads, head_dim, ld, max_seq, scale, status, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int cutb_copy_batch(const cutb_copy_range *table, uint32_t n, uint64_t max_bytes, void *stream) {
+  if (n == 0) return CUTB_OK;
+  if (!table || n > 65535) {
+    set_last_error("copy_batch: null table or more than 65535 ranges");
+    return CUTB_ERR_INVALID;
+  }
+  // (the ranges themselves are read on the device: their alignment is the caller's contract)
+  uint64_t blocks = (max_bytes / 16 + 2047) / 2048;  // about eight vectors per thread
+  if (blocks < 1) blocks = 1;
+  if (blocks > 64) blocks = 64;
+  return copy_batch_launch(table, n, (uint32_t)blocks, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int cutb_glu_pairs(const float *in, float *out, uint32_t rows, uint32_t cols_out, uint64_t ldi, uint64_t ldo, int unary_op, void *stream) {
   if (rows == 0 || cols_out == 0) return CUTB_OK;
   if (!in || !out || ldi % 2 || ldi < 2ull * cols_out || ldo < cols_out || reinterpret_cast<uintptr_t>(in) % 8) {

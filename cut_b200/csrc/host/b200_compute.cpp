@@ -69,6 +69,7 @@ struct Scratch {
 
 struct CommandBufferObj : ComputeHandle::Slot {
   ~CommandBufferObj() override {
+    if (gatherHost) cudaFreeHost(gatherHost);
     if (exec) cudaGraphExecDestroy(exec);
     if (graph) cudaGraphDestroy(graph);
   }
@@ -85,6 +86,11 @@ struct CommandBufferObj : ComputeHandle::Slot {
   };
   std::unordered_map<const void *, Shadow> shadows;  // keyed by the buffer object
   uint64_t shadowEpoch = 0;                         // the backend epoch at which the pinned copies were requested
+  // with more than one result: {result -> its place in the backend's device block}, read by one gather launch
+  // (host-mapped pinned memory), followed by a single download of the block
+  cutb_copy_range *gatherHost = nullptr, *gatherDev = nullptr;
+  uint32_t gatherCount = 0;
+  size_t gatherBytes = 0, gatherMax = 0;
 };
 
 int cutbFormat(uint32_t f) {
@@ -120,6 +126,10 @@ public:
     cudaCheck(cudaMemsetAsync(status_, 0, sizeof(int), stream_), "cudaMemset(status)");
     cudaCheck(cudaHostAlloc((void **)&stage_, kStageBytes, cudaHostAllocDefault), "cudaHostAlloc(staging)");
     cudaCheck(cudaHostAlloc((void **)&shadowStage_, kShadowBytes + 256, cudaHostAllocDefault), "cudaHostAlloc(results)");
+    cudaCheck(cudaMalloc((void **)&devStage_, kStageBytes), "cudaMalloc(upload block)");
+    cudaCheck(cudaMalloc((void **)&devResults_, kShadowBytes), "cudaMalloc(result block)");
+    cudaCheck(cudaHostAlloc((void **)&tableHost_, kTableEntries * sizeof(cutb_copy_range), cudaHostAllocMapped), "cudaHostAlloc(table)");
+    cudaCheck(cudaHostGetDevicePointer((void **)&tableDev_, tableHost_, 0), "cudaHostGetDevicePointer");
     caps_.backend = ComputeBackend::CUDA;
     caps_.cooperativeMatrix = true;  // tensor-core variants exist
     caps_.integerDotProduct = true;
@@ -129,6 +139,10 @@ public:
     cudaStreamSynchronize(stream_);
     lastReplayed_ = nullptr;
     lastReplayedHandle_.reset();
+    pendingUploads_.clear();
+    cudaFree(devStage_);
+    cudaFree(devResults_);
+    cudaFreeHost(tableHost_);
     workspace_.reset();
     attnWs_.reset();
     cudaFree(status_);
@@ -151,7 +165,7 @@ public:
     ComputeHandle h(buf);
     if (!host || buf->size() != buf->calculateActualSize())
       cudaCheck(cudaMemsetAsync(buf->data, 0, bytes, stream_), "cudaMemsetAsync");  // padding reads as zero
-    if (host) upload(*buf, host);
+    if (host) upload(h, *buf, host);
     return h;
   }
 
@@ -193,18 +207,19 @@ public:
     if (!b) throw std::runtime_error("copyDataToBuffer: not a buffer");
     if (lastReplayed_ && lastReplayed_->shadows.count(b)) ++epoch_;  // a result buffer is overwritten: its pinned copy is stale
     if (srcOffset == 0 && destOffset == 0 && copySize == b->calculateActualSize()) {
-      upload(*b, host);
+      upload(dest, *b, host);
       return;
     }
     if (b->innerDimSize() != b->innerDimPadded()) throw std::runtime_error("copyDataToBuffer: partial copy into a padded buffer");
     if (destOffset + copySize > b->size()) throw std::runtime_error("copyDataToBuffer: out of range");
-    uploadBytes((uint8_t *)b->data + destOffset, (const uint8_t *)host + srcOffset, copySize);
+    uploadBytes(dest, (uint8_t *)b->data + destOffset, (const uint8_t *)host + srcOffset, copySize);
   }
 
   void copyDataFromBuffer(const ComputeHandle &src, void *host, size_t copySize, size_t srcOffset, size_t destOffset, bool,
                           bool) override {
     auto *b = src.as<DeviceBuffer>();
     if (!b) throw std::runtime_error("copyDataFromBuffer: not a buffer");
+    flushUploads();
     if (lastReplayed_ && lastReplayed_->shadowEpoch == epoch_) {
       auto it = lastReplayed_->shadows.find(b);
       if (it != lastReplayed_->shadows.end() && srcOffset + copySize <= it->second.bytes) {
@@ -267,7 +282,10 @@ public:
   size_t activeBufferMemoryBytes() const override { return activeBytes_; }
   uint32_t maxSharedMemoryPerBlock() const override { return smemOptin_; }
   size_t deviceTotalMemoryBytes() const override { return totalMem_; }
-  void flushTransfers() override { cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize"); }
+  void flushTransfers() override {
+    flushUploads();
+    cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+  }
 
 protected:
   ComputeHandle executeDispatches(std::vector<ComputeDispatch> &&dispatches, bool reusable) override {
@@ -275,6 +293,7 @@ protected:
     cb->id = ++nextId_;
     cb->dispatches = std::move(dispatches);
     cudaCheck(cudaSetDevice(device_), "cudaSetDevice");
+    flushUploads();
     // scratch is sized before anything is launched or captured
     size_t need = 0;
     std::vector<cutb_qmatmul_desc> descs(cb->dispatches.size());
@@ -324,6 +343,16 @@ protected:
         cb->shadows[ob] = CommandBufferObj::Shadow{ob->data, ob->size(), off};
         off += need;
       }
+      if (cb->shadows.size() > 1) {
+        cudaCheck(cudaHostAlloc((void **)&cb->gatherHost, cb->shadows.size() * sizeof(cutb_copy_range), cudaHostAllocMapped),
+                  "cudaHostAlloc(gather table)");
+        cudaCheck(cudaHostGetDevicePointer((void **)&cb->gatherDev, cb->gatherHost, 0), "cudaHostGetDevicePointer");
+        for (const auto &kv : cb->shadows) {
+          cb->gatherHost[cb->gatherCount++] = cutb_copy_range{kv.second.dev, devResults_ + kv.second.off, kv.second.bytes};
+          cb->gatherMax = std::max(cb->gatherMax, kv.second.bytes);
+        }
+        cb->gatherBytes = off;
+      }
       // warm launch outside capture (first-use kernel attributes), then capture the same list
       launchAll(*cb, descs);
       cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
@@ -347,11 +376,17 @@ protected:
   void replay(const ComputeHandle &h) override {
     auto *cb = h.as<CommandBufferObj>();
     if (!cb || !cb->exec) throw std::runtime_error("resubmit: not a reusable command buffer");
+    flushUploads();
     cudaCheck(cudaGraphLaunch(cb->exec, stream_), "cudaGraphLaunch");
     ++epoch_;
-    for (const auto &kv : cb->shadows)
-      cudaCheck(cudaMemcpyAsync(shadowStage_ + kv.second.off, kv.second.dev, kv.second.bytes, cudaMemcpyDeviceToHost, stream_),
-                "cudaMemcpyAsync(results)");
+    if (cb->gatherCount > 1) {  // one gather launch into the device block, one download of the block
+      cutbCheck(cutb_copy_batch(cb->gatherDev, cb->gatherCount, cb->gatherMax, stream_), "result gather");
+      cudaCheck(cudaMemcpyAsync(shadowStage_, devResults_, cb->gatherBytes, cudaMemcpyDeviceToHost, stream_), "cudaMemcpyAsync(results)");
+    } else {
+      for (const auto &kv : cb->shadows)
+        cudaCheck(cudaMemcpyAsync(shadowStage_ + kv.second.off, kv.second.dev, kv.second.bytes, cudaMemcpyDeviceToHost, stream_),
+                  "cudaMemcpyAsync(results)");
+    }
     cudaCheck(cudaMemcpyAsync(shadowStage_ + kShadowBytes, status_, sizeof(int), cudaMemcpyDeviceToHost, stream_),
               "cudaMemcpyAsync(status)");
     statusShadowed_ = true;
@@ -361,6 +396,7 @@ protected:
   }
 
   void waitFor(const ComputeHandle &) override {
+    flushUploads();
     cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
     int st = 0;
     if (statusShadowed_) std::memcpy(&st, shadowStage_ + kShadowBytes, sizeof(int));  // copied behind the replay
@@ -373,34 +409,66 @@ protected:
   }
 
 private:
-  // Host bytes -> device, in stream order.  Small transfers (a decode step's activations, token ids, positions) are
-  // copied into a pinned block and sent from there without waiting: the caller's memory is free again when the call
-  // returns, the device sees the data before any later work of the stream, and the step pays one wait (its
-  // download) instead of one per tensor.  The block is reused from the start once the stream has drained.
-  void uploadBytes(void *dev, const void *host, size_t bytes) {
-    if (bytes <= kStageBytes / 4) {
+  // Host bytes -> device.  Small transfers (a decode step's activations, token ids, positions) are copied into a
+  // pinned block at once -- the caller's memory is free again when the call returns -- and sent LATER, together:
+  // everything that is pending when the stream is next used (a submit or replay, a download, a flush) goes out as
+  // ONE host-to-device copy of the pinned range into a device block, followed by one launch that moves every piece
+  // to its tensor.  A step that uploads 32 activations pays one transfer, not 32.  The pinned block is reused from
+  // the start once it is full and the stream has drained.  (`keep` holds the destination alive until then.)
+  void uploadBytes(const ComputeHandle &keep, void *dev, const void *host, size_t bytes) {
+    if (bytes <= kStageBytes / 4 && reinterpret_cast<uintptr_t>(dev) % 16 == 0) {
       const size_t need = (bytes + 255) & ~size_t(255);
       if (stageUsed_ + need > kStageBytes) {
+        flushUploads();
         cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
         stageUsed_ = 0;
       }
       std::memcpy(stage_ + stageUsed_, host, bytes);
-      cudaCheck(cudaMemcpyAsync(dev, stage_ + stageUsed_, bytes, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
+      pendingUploads_.push_back(Pending{keep, dev, stageUsed_, bytes});
       stageUsed_ += need;
       return;
     }
+    flushUploads();  // keep the order of writes to one buffer
     cudaCheck(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
     cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
   }
 
-  void upload(DeviceBuffer &b, const void *host) {
+  // Sends what uploadBytes() has collected; called before anything else is put on the stream.
+  void flushUploads() {
+    if (pendingUploads_.empty()) return;
+    if (pendingUploads_.size() <= 2) {  // (one or two pieces: a copy each is cheaper than a copy and a launch)
+      for (const Pending &u : pendingUploads_)
+        cudaCheck(cudaMemcpyAsync(u.dev, stage_ + u.off, u.bytes, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
+    } else {
+      const size_t first = pendingUploads_.front().off;
+      const size_t last = pendingUploads_.back().off + ((pendingUploads_.back().bytes + 255) & ~size_t(255));
+      cudaCheck(cudaMemcpyAsync(devStage_ + first, stage_ + first, last - first, cudaMemcpyHostToDevice, stream_), "cudaMemcpyAsync(H2D)");
+      const size_t n = pendingUploads_.size();
+      if (n > kTableEntries) throw std::runtime_error("B200Compute: too many pending uploads");
+      if (tableUsed_ + n > kTableEntries) {  // the table is read by launches that may still be queued
+        cudaCheck(cudaStreamSynchronize(stream_), "cudaStreamSynchronize");
+        tableUsed_ = 0;
+      }
+      uint64_t maxBytes = 0;
+      for (size_t i = 0; i < n; ++i) {
+        const Pending &u = pendingUploads_[i];
+        tableHost_[tableUsed_ + i] = cutb_copy_range{devStage_ + u.off, u.dev, u.bytes};
+        maxBytes = std::max<uint64_t>(maxBytes, u.bytes);
+      }
+      cutbCheck(cutb_copy_batch(tableDev_ + tableUsed_, (uint32_t)n, maxBytes, stream_), "upload scatter");
+      tableUsed_ += n;
+    }
+    pendingUploads_.clear();
+  }
+
+  void upload(const ComputeHandle &keep, DeviceBuffer &b, const void *host) {
     if (b.innerDimSize() == b.innerDimPadded() || b.getShape().size() <= 1) {
-      uploadBytes(b.data, host, std::min(b.size(), b.calculateActualSize()));
+      uploadBytes(keep, b.data, host, std::min(b.size(), b.calculateActualSize()));
       return;
     }
     std::vector<uint8_t> bounce(b.size(), 0);
     copyActualToAligned(host, bounce.data(), b);
-    uploadBytes(b.data, bounce.data(), b.size());
+    uploadBytes(keep, b.data, bounce.data(), b.size());
   }
 
   // Scratch only grows, and never in place: command buffers recorded earlier keep the block they
@@ -626,6 +694,16 @@ private:
   static constexpr size_t kStageBytes = 4u << 20;
   uint8_t *stage_ = nullptr;  // pinned
   size_t stageUsed_ = 0;
+  struct Pending {
+    ComputeHandle keep;
+    void *dev;
+    size_t off, bytes;
+  };
+  std::vector<Pending> pendingUploads_;
+  uint8_t *devStage_ = nullptr, *devResults_ = nullptr;  // device blocks behind the pinned ones
+  static constexpr size_t kTableEntries = 4096;
+  cutb_copy_range *tableHost_ = nullptr, *tableDev_ = nullptr;  // host-mapped: ranges of the batched copies
+  size_t tableUsed_ = 0;
   static constexpr size_t kShadowBytes = 4u << 20;
   uint8_t *shadowStage_ = nullptr;  // pinned: results of the last replayed command buffer, then the status word
   uint64_t epoch_ = 0;               // bumped by everything that can change a device buffer

@@ -44,6 +44,7 @@ int embedding_col_launch(int format, const uint32_t *indices, const void *matrix
 int requant_q8_0_blocks_launch(int format, const void *raw, void *out, uint64_t rows, uint32_t cols, cudaStream_t stream);
 int dequant_gather_launch(int format, const uint32_t *indices, const void *raw, float *out, uint32_t n, uint32_t rows, uint32_t cols,
                           uint32_t ldo, int *status, cudaStream_t stream);
+int copy_batch_launch(const cutb_copy_range *table, uint32_t n, uint32_t blocks_per_range, cudaStream_t stream);
 int argreduce_launch(int is_max, const float *v, float *out, uint32_t n, cudaStream_t stream);
 // Decode-step attention (attention.cu).
 int rope_kv_write_launch(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params, const float *cosT,

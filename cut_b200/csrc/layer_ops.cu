@@ -307,4 +307,28 @@ int argreduce_launch(int is_max, const float *v, float *out, uint32_t n, cudaStr
   return CUTB_OK;
 }
 
+// ---- batched device copies ----------------------------------------------------------------------
+// One launch moves n byte ranges device -> device: blockIdx.y = range, blockIdx.x strides over its 16-byte
+// vectors.  A backend uses it to scatter one coalesced host upload into the tensors it belongs to, and to gather
+// a step's results into one block for a single download.  The table may live in host-mapped pinned memory (it
+// is read once per block).
+__global__ void __launch_bounds__(256) copy_batch_kernel(const cutb_copy_range *__restrict__ table) {
+  const cutb_copy_range r = table[blockIdx.y];
+  const uint64_t vecs = r.bytes / 16;
+  const uint4 *src = reinterpret_cast<const uint4 *>(r.src);
+  uint4 *dst = reinterpret_cast<uint4 *>(r.dst);
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += (uint64_t)gridDim.x * blockDim.x) dst[i] = src[i];
+  if (blockIdx.x == 0) {  // tail bytes (ranges need not be multiples of 16)
+    const uint8_t *s8 = reinterpret_cast<const uint8_t *>(r.src);
+    uint8_t *d8 = reinterpret_cast<uint8_t *>(r.dst);
+    for (uint64_t i = vecs * 16 + threadIdx.x; i < r.bytes; i += blockDim.x) d8[i] = s8[i];
+  }
+}
+
+int copy_batch_launch(const cutb_copy_range *table, uint32_t n, uint32_t blocks_per_range, cudaStream_t stream) {
+  copy_batch_kernel<<<dim3(blocks_per_range, n), 256, 0, stream>>>(table);
+  CUTB_CUDA_TRY(cudaGetLastError());
+  return CUTB_OK;
+}
+
 }  // namespace cutb

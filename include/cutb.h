@@ -386,6 +386,19 @@ CUTB_API int cutb_batched_attention(int kv_dtype, const float *q_in, uint32_t q_
                                     const uint32_t *positions, const float *cos_table, const float *sin_table, float *out,
                                     uint32_t out_stride, uint32_t n_tokens, uint32_t n_heads, uint32_t n_kv_heads, uint32_t head_dim,
                                     uint64_t ld, uint32_t max_seq, float scale, int *status, void *stream);
+/*
+ * n device-to-device byte copies in one launch (no counterpart in the reference).  `table` holds n ranges
+ * {src, dst, bytes}; src and dst 16-byte aligned, ranges must not overlap each other.  The table is read by the
+ * kernel: device memory or host-mapped pinned memory (pass its device address), unchanged until the launch has run.
+ * A backend scatters one coalesced upload into its tensors with it, and gathers a step's results for one download.
+ */
+typedef struct cutb_copy_range {
+  const void *src;
+  void *dst;
+  uint64_t bytes;
+} cutb_copy_range;
+CUTB_API int cutb_copy_batch(const cutb_copy_range *table, uint32_t n, uint64_t max_bytes, void *stream);
+
 CUTB_API int cutb_glu_pairs(const float *in, float *out, uint32_t rows, uint32_t cols_out, uint64_t ldi, uint64_t ldo, int unary_op,
                             void *stream);
 CUTB_API int cutb_rope_attention_decode(int kv_dtype, const float *q, const float *k, const float *v, const uint32_t *params,

@@ -166,3 +166,24 @@ def test_embedding_blocks_equals_dequantised_rows(fmt):
     out = ops.embedding_blocks(torch.tensor([rows], dtype=torch.int32, device="cuda"), torch.from_numpy(raw).cuda(), fmt, rows, cols,
                                status=status)
     assert int(status.item()) == L.ERR_INVALID and bool((out == 0).all())
+
+
+@pytest.mark.gpu
+def test_copy_batch_moves_every_range():
+    """cutb_copy_batch: n device-to-device byte ranges in one launch (sizes that are not multiples of 16, an empty
+    range, a range larger than one block's stride), table in device memory."""
+    import torch
+
+    from cut_b200 import _lib as L
+
+    rng = np.random.default_rng(8)
+    sizes = [44032, 8192, 4, 0, 1000003, 17, 16]
+    src = [torch.from_numpy(rng.integers(0, 256, max(s, 16), dtype=np.uint8)).cuda() for s in sizes]
+    dst = [torch.full((max(s, 16) + 16,), 7, dtype=torch.uint8, device="cuda") for s in sizes]
+    table = torch.tensor([[a.data_ptr(), b.data_ptr(), s] for a, b, s in zip(src, dst, sizes)], dtype=torch.int64, device="cuda")
+    L.check(L.lib().cutb_copy_batch(table.data_ptr(), len(sizes), max(sizes), None))
+    torch.cuda.synchronize()
+    for a, b, s in zip(src, dst, sizes):
+        assert torch.equal(b[:s], a[:s]) and bool((b[s:] == 7).all())
+    assert L.lib().cutb_copy_batch(None, 3, 16, None) == L.ERR_INVALID
+    assert L.lib().cutb_copy_batch(None, 0, 0, None) == L.OK
