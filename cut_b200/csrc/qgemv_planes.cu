@@ -204,7 +204,8 @@ GpPlan gp_plan(const cutb_qmatmul_desc &d, int sm_count) {
   const uint32_t blocksK = (d.K + 31) / 32;
   // about sixteen resident warps per SM, and at least one 32-row block per warp
   const uint32_t want_ctas = (uint32_t)sm_count * 2;
-  uint32_t ks = pl.grid_x >= want_ctas ? 1 : (want_ctas + pl.grid_x - 1) / pl.grid_x;
+  // (rounded down: two blocks fit an SM, and a handful of blocks beyond 2 x SMs would run as a wave of their own)
+  uint32_t ks = pl.grid_x >= want_ctas ? 1 : want_ctas / pl.grid_x;
   const uint32_t max_ks = (blocksK + GP_WARPS - 1) / GP_WARPS;
   if (ks > max_ks) ks = max_ks;
   if (ks < 1) ks = 1;

@@ -195,8 +195,30 @@ def main(argv=None) -> int:
     ap.add_argument("--out", default="-", help="where the op_bench JSON goes (default: stdout)")
     ap.add_argument("--rules", default=None, help="also write tuning_data.json rules derived from the run")
     ap.add_argument("--reference-shapes-only", action="store_true")
+    ap.add_argument("--only", nargs=3, type=int, metavar=("M", "K", "N"),
+                    help="time one shape only and print its record (a small, fixed workload for a profiler)")
+    ap.add_argument("--format", choices=["q8_0", "q4_0", "q4_k"], default="q4_0", help="with --only: block format")
+    ap.add_argument("--layout", choices=["blocks", "planes"], default="blocks", help="with --only: weight layout")
+    ap.add_argument("--variant", type=int, default=None, help="with --only: force this variant (default: the built-in choice)")
     args = ap.parse_args(argv)
     import torch
+
+    if args.only:
+        from . import _lib as L
+
+        if not torch.cuda.is_available():
+            raise SystemExit("op_bench needs a CUDA device")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        M, K, N = args.only
+        if args.layout == "planes":
+            v = 3 if args.variant is None else args.variant
+            us = time_planes(torch, dev, args.format != "q8_0", M, K, N, False, v)
+        else:
+            fmt = {"q8_0": L.Q8_0, "q4_0": L.Q4_0, "q4_k": L.Q4_K}[args.format]
+            v = builtin_block_variant(M, K, N, False) if args.variant is None else args.variant
+            us = time_blocks(torch, dev, fmt, M, K, N, v, False)
+        print(json.dumps({"shape": [M, K, N], "format": args.format, "layout": args.layout, "variant": v, "median_us": us}))
+        return 0
 
     shapes = REFERENCE_SHAPES if args.reference_shapes_only else REFERENCE_SHAPES + EXTRA_SHAPES
     records = run(shapes)
