@@ -51,7 +51,7 @@ WORKLOAD = f"configs[1]: {FMT_NAME} decode mat-vec {N_ROWS}x{K_COLS} (GGUF block
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one mat-vec launch of this workload, from an ncu
 # capture of this kernel (a profiler cannot run inside the timed region, so the figure is carried here and the
 # line says where it comes from).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 25408768
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 25_419_520
 
 
 def algorithmic_bytes(n_rows: int, k: int, batch: int) -> int:
