@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
   const uint32_t token0 = batched ? blockIdx.z * TQ : 0u;
   __shared__ uint32_t vseq[AT_MAX_REP];  // rows [0, vseq) attended by each virtual head
   pdl_enter();
-  const uint32_t seq_cap = batched ? min(p.max_seq, (uint32_t)AT_MAX_CHUNK) : p.max_seq;  // a batched block owns its whole range
+  const uint32_t seq_cap = p.max_seq;  // (a batched block walks its whole range in chunks of AT_MAX_CHUNK rows)
   uint32_t seqLen = 0;
   if (batched) {
     for (uint32_t tq = 0; tq < TQ; ++tq) {
@@ -190,8 +190,13 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
       seqLen = seq_cap;
     }
   }
-  const uint32_t chunk = (seqLen + S - 1) / S;  // <= AT_MAX_CHUNK by the launcher's choice of S
-  const uint32_t t0 = min(split * chunk, seqLen), t1 = min(t0 + chunk, seqLen), cnt = t1 - t0;
+  // Decode mode: this block's slice [t0, t1) of the range, at most AT_MAX_CHUNK rows by the launcher's choice of S,
+  // one pass.  Batched mode (S = 1): the block walks [0, seqLen) in chunks of AT_MAX_CHUNK rows with a running
+  // maximum and exp-sum per virtual head; the weighted V sums in registers are rescaled when the maximum moves.
+  const uint32_t chunk = batched ? (uint32_t)AT_MAX_CHUNK : (seqLen + S - 1) / S;
+  const uint32_t nchunks = batched ? max(1u, (seqLen + chunk - 1) / chunk) : 1u;
+  __shared__ float run_fac[AT_MAX_REP];
+  if (tid < AT_MAX_REP) head_m[tid] = AT_NEG, head_l[tid] = 0.f;
   const KV *kC = reinterpret_cast<const KV *>(p.kC) + (uint64_t)kvH * HD;
   const KV *vC = reinterpret_cast<const KV *>(p.vC) + (uint64_t)kvH * HD;
 
@@ -214,6 +219,15 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
   }
   __syncthreads();
 
+  constexpr uint32_t EV = VEC ? 2 : 1;
+  float acc[AT_MAX_REP][EV];
+#pragma unroll
+  for (int r = 0; r < AT_MAX_REP; ++r)
+#pragma unroll
+    for (uint32_t e = 0; e < EV; ++e) acc[r][e] = 0.f;
+  uint32_t t0 = 0, t1 = 0, cnt = 0;
+  for (uint32_t ci = 0; ci < nchunks; ++ci) {
+  t0 = min((batched ? ci : split) * chunk, seqLen), t1 = min(t0 + chunk, seqLen), cnt = t1 - t0;
   // scores: eight lanes per position, four positions per warp and pass; the loads of up to four
   // passes are issued before the first is used, so a slice costs one or two memory round trips
   {
@@ -296,11 +310,13 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
 
   // slice softmax: warp r owns query head r of the group
   for (uint32_t r = warp; r < nRep; r += AT_WARPS) {
-    const uint32_t cr = batched ? min(vseq[r], cnt) : cnt;  // a token of the tile sees the rows up to its own only
-    float m = AT_NEG;
+    // a token of the tile sees the rows up to its own only
+    const uint32_t cr = batched ? (vseq[r] > t0 ? min(vseq[r] - t0, cnt) : 0u) : cnt;
+    float m = head_m[r];  // the maximum so far (AT_NEG before the first chunk)
     for (uint32_t i = lane; i < cr; i += 32) m = fmaxf(m, sc[r * AT_MAX_CHUNK + i]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float fac = expf(head_m[r] - m);  // 1 while the maximum stands (and for the only chunk of the decode mode)
     float l = 0.f;
     for (uint32_t i = lane; i < cr; i += 32) {
       const float e = expf(sc[r * AT_MAX_CHUNK + i] - m);
@@ -310,20 +326,23 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
     for (uint32_t i = cr + lane; i < cnt; i += 32) sc[r * AT_MAX_CHUNK + i] = 0.f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-    if (lane == 0) head_m[r] = m, head_l[r] = l;
+    __syncwarp();
+    if (lane == 0) run_fac[r] = fac, head_l[r] = fmaf(head_l[r], fac, l), head_m[r] = m;
   }
   __syncthreads();
 
   // weighted V sum: thread (tg, tp) adds positions tg, tg + G, ... for EV dimensions of every head
   {
-    constexpr uint32_t EV = VEC ? 2 : 1;
     const uint32_t P = HD / EV, G = AT_THREADS / P;
     const uint32_t tp = tid % P, tg = tid / P;
-    float acc[AT_MAX_REP][EV];
+    if (nchunks > 1) {
 #pragma unroll
-    for (int r = 0; r < AT_MAX_REP; ++r)
+      for (int r = 0; r < AT_MAX_REP; ++r)
+        if (r < nRep) {
 #pragma unroll
-      for (uint32_t e = 0; e < EV; ++e) acc[r][e] = 0.f;
+          for (uint32_t e = 0; e < EV; ++e) acc[r][e] *= run_fac[r];
+        }
+    }
     if (tg < G) {
       constexpr uint32_t VU = 8;  // rows in flight per thread
       for (uint32_t ib = tg; ib < cnt; ib += G * VU) {
@@ -354,6 +373,15 @@ __global__ void __launch_bounds__(AT_THREADS) attention_decode_kernel(const Attn
           }
         }
       }
+    }
+  }
+  __syncthreads();  // the next chunk overwrites the scores
+  }  // chunks
+
+  {
+    const uint32_t P = HD / EV, G = AT_THREADS / P;
+    const uint32_t tp = tid % P, tg = tid / P;
+    if (tg < G) {
 #pragma unroll
       for (int r = 0; r < AT_MAX_REP; ++r)
         if (r < nRep) {

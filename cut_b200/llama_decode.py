@@ -272,13 +272,12 @@ class LlamaDecoder:
     def prefill(self, tokens, start: int = 0) -> torch.Tensor:
         """The prompt as one batch (interface/runner/llama/llama.cpp prefillBatched): every projection is one matmul over
         all T tokens (the tensor-core GEMM from 17 tokens up), K / V rows go to the cache through the batched RoPE
-        write and every token attends over the rows up to its own.  start + T <= 512 (one attention block holds a
-        token's whole range).  Leaves the cache as T decode steps would (up to rounding) and returns the last
+        write and every token attends over the rows up to its own (in chunks of 512 rows: start + T <= max_seq).  Leaves the cache as T decode steps would (up to rounding) and returns the last
         token's logits; the greedy pick is in next_tok."""
         cfg, dev = self.cfg, self.dev
         T = len(tokens)
-        if T == 0 or start + T > min(cfg.max_seq, 512):
-            raise ValueError("prefill: 1 .. 512 - start tokens per call")
+        if T == 0 or start + T > cfg.max_seq:
+            raise ValueError("prefill: 1 .. max_seq - start tokens per call")
         tok = torch.as_tensor(np.asarray(tokens, dtype=np.int32)).to(dev)
         pos = torch.arange(start, start + T, dtype=torch.int32, device=dev)
         q_dim, kv_dim = cfg.q_dim, cfg.kv_dim

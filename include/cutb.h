@@ -373,8 +373,9 @@ CUTB_API uint64_t cutb_attention_workspace_bytes(uint32_t n_heads, uint32_t n_kv
  *   k_in / v_in are k_stride / v_stride elements apart, so they may be columns of a fused QKV matrix
  *   (BatchedKVCacheWriteOpNode's dispatch, operators/impl/attention/BatchedKVCacheWrite.cu:33-62).
  * cutb_batched_attention: out[i] = attention of RoPE(q_in[i]) over cache rows [0, positions[i]], one block
- *   per (KV head, token) (operators/impl/attention/BatchedAttentionReadCache.cu).  positions[i] < 512:
- *   one block holds a token's whole range; longer prompts go in chunks.  Call after the cache write.
+ *   per (KV head, group of consecutive tokens) (operators/impl/attention/BatchedAttentionReadCache.cu).  A block
+ *   walks its tokens' range in chunks of 512 rows with a running maximum and exp-sum, so positions[i] < max_seq is
+ *   the only limit (a position past the cache is reported through `status`, never read).  Call after the cache write.
  * cutb_glu_pairs: out[r, i] = unary(op)(in[r, 2i]) * in[r, 2i + 1] (ldi even, 8-byte aligned `in`): the
  *   gated activation over a prefill GEMM whose weight rows are stored in (gate, up) pairs.
  */

@@ -162,7 +162,8 @@ def test_rope_attention_decode_equals_the_two_calls(gpu, kv, n_heads, n_kv, hd, 
 
 
 @pytest.mark.parametrize("kv", [np.float32, np.float16])
-@pytest.mark.parametrize("n_heads,n_kv,hd,max_seq,T,start", [(32, 8, 128, 600, 512, 0), (4, 2, 8, 16, 5, 3), (6, 3, 66, 64, 20, 7)])
+@pytest.mark.parametrize("n_heads,n_kv,hd,max_seq,T,start", [(32, 8, 128, 600, 512, 0), (4, 2, 8, 16, 5, 3), (6, 3, 66, 64, 20, 7),
+                                                              (8, 2, 64, 1400, 700, 650), (4, 4, 32, 2100, 90, 1990)])
 def test_batched_prefill_operators_match_checker(gpu, kv, n_heads, n_kv, hd, max_seq, T, start):
     """cutb_batched_kv_write (bit-exact cache rows, inputs as columns of one fused QKV matrix) and
     cutb_batched_attention (every token over the rows up to its own) against the checker run token by token."""
@@ -177,7 +178,9 @@ def test_batched_prefill_operators_match_checker(gpu, kv, n_heads, n_kv, hd, max
     vc = rng.normal(0, 1, (max_seq, ld)).astype(kv)
     kc_ref, vc_ref = kc.copy(), vc.copy()
     want = np.zeros((T, q_dim), np.float32)
-    sel = np.arange(T) if T <= 24 else np.array([0, 1, 100, 255, 256, 511])  # the float64 checker is slow on long ranges
+    # the float64 checker is slow on long ranges: a few tokens, the chunk borders of the 512-row walk among them
+    sel = np.arange(T) if T <= 24 else np.array([i for i in (0, 1, 100, 255, 256, 511, 512 - start, 1023 - start, 1024 - start, T - 1)
+                                                 if 0 <= i < T])
     q_ref = {}
     for i in range(T):
         q_ref[i] = O.rope_kv_write(qkv[i, :q_dim], qkv[i, q_dim:q_dim + kv_dim], qkv[i, q_dim + kv_dim:], start + i, cos_t, sin_t,
@@ -205,7 +208,9 @@ def test_batched_attention_range_limit_and_glu_pairs(gpu):
     q = torch.zeros((1, n_heads * hd), device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     gpu.batched_attention(q, kc, kc, _dev(np.array([600], np.int32)), _dev(cos_t), _dev(sin_t), n_heads, n_kv, hd, status=status)
-    assert int(status.item()) == 1  # a token past row 511: one block cannot hold its range, reported
+    assert int(status.item()) == 0  # rows past 511 are walked in further chunks
+    gpu.batched_attention(q, kc, kc, _dev(np.array([1024], np.int32)), _dev(cos_t), _dev(sin_t), n_heads, n_kv, hd, status=status)
+    assert int(status.item()) == 1  # a position past the cache is reported, never read
     x = np.random.default_rng(0).normal(0, 2, (7, 20)).astype(np.float32)
     got = gpu.glu_pairs(_dev(x)).cpu().numpy()
     want = np.array([[O.epilogue(float(x[r, 2 * i]), 1, 133) * np.float32(x[r, 2 * i + 1]) for i in range(10)] for r in range(7)], np.float32)
