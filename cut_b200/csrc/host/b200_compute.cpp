@@ -259,7 +259,7 @@ public:
     auto desc = KernelDesc::decode(words);
     if (!desc) throw std::runtime_error("B200Compute: not a kernel descriptor");
     switch (desc->op) {
-      case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case RequantQ8Blocks: case TransposeQ4: break;
+      case MatMulQ8: case MatMulQ4: case MatMulQBlocks: case Dequantize: case RequantQ8Blocks: case TransposeQ4: case GluPairs: break;
       case RMSNorm: case Embedding: case EmbeddingCol: case ReduceArgmax: case ReduceArgmin: case Attention: break;
       case CacheWrite:
         if (desc->variant != FusedRoPEKVWriteOpNode::kVariant && desc->variant != BatchedKVCacheWriteOpNode::kVariant) throw std::runtime_error("B200Compute: no kernel for this CacheWrite operator");
@@ -611,6 +611,12 @@ private:
         const DeviceBuffer &raw = buf(d, 0), &out = buf(d, 1);
         cutbCheck(cutb_requant_q8_0_blocks(cutbFormat(k.format), raw.data, raw.size(), out.data, pc.rows, pc.cols, stream_),
                   "RequantQ8Blocks");
+      } else if (k.op == GluPairs) {
+        struct PC {
+          uint32_t rows, colsOut, strideIn, strideOut;
+        } pc = pushConstants<PC>(d);
+        cutbCheck(cutb_glu_pairs((const float *)buf(d, 0).data, (float *)buf(d, 1).data, pc.rows, pc.colsOut, pc.strideIn, pc.strideOut,
+                                 (int)k.fusionOp, stream_), "GluPairs");
       } else if (k.op == TransposeQ4) {
         struct PC {
           uint32_t N, K, strideInHalf, strideOutHalf;

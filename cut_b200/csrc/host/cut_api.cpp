@@ -477,6 +477,37 @@ std::vector<uint8_t> RequantQ8BlocksOpNode::pushConstants() const {
   return toBytes(pc);
 }
 
+GluPairsOpNode::GluPairsOpNode(TensorStore &store, const Tensor &in, OperatorEnum unaryOp, std::optional<uint32_t> spec)
+    : OpNode(GluPairs, store, spec), unaryOp_(unaryOp) {
+  const auto &b = store.getTensor(in);
+  const auto sh = b.getShape();
+  if (b.getDtype() != DataType::Float32 || sh.empty() || sh.size() > 2) throw std::runtime_error("gluPairs: input must be Float32 [rows, 2F]");
+  rows_ = sh.size() == 2 ? sh[0] : 1;
+  const uint32_t colsIn = sh.back();
+  if (colsIn % 2) throw std::runtime_error("gluPairs: the input needs an even number of columns");
+  colsOut_ = colsIn / 2;
+  strideIn_ = b.innerDimPadded();
+  strideOut_ = (colsOut_ + 3) & ~3u;
+  inputs_ = {in};
+  output_ = store.createTensorEmpty(outputShape(), DataType::Float32);
+}
+
+std::optional<std::vector<uint32_t>> GluPairsOpNode::shader() const {
+  KernelDesc d;
+  d.op = GluPairs;
+  d.fusionType = (uint32_t)MatMulFusion::Unary;
+  d.fusionOp = (uint32_t)unaryOp_;
+  d.dtypeA = d.dtypeB = (uint32_t)DataType::Float32;
+  return d.encode();
+}
+
+std::vector<uint8_t> GluPairsOpNode::pushConstants() const {
+  struct {
+    uint32_t rows, colsOut, strideIn, strideOut;
+  } pc{rows_, colsOut_, strideIn_, strideOut_};
+  return toBytes(pc);
+}
+
 size_t DequantOpNode::shaderKey() const {
   return static_cast<size_t>(op_) | ((static_cast<size_t>(format_) & 0x1F) << 16);
 }
@@ -1101,6 +1132,10 @@ Tensor Operations::matmulBlocksFused(const Tensor &a, const Tensor &raw, Dequant
   if (fusion != MatMulFusion::None) node->setFusion(fusion, fusionOp, d);
   node->setBlockOptions(opt);
   return dispatch(std::move(node));
+}
+
+Tensor Operations::gluPairs(const Tensor &in, OperatorEnum unaryOp) {
+  return dispatch(std::make_unique<GluPairsOpNode>(*store_, in, unaryOp));
 }
 
 Tensor Operations::transposeQ4(const Tensor &packedInput, uint32_t N, uint32_t K) {

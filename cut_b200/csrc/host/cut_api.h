@@ -74,6 +74,7 @@ enum OperatorEnum : uint32_t {
   MatMulQBlocks = 375,  // new: weights as raw GGUF blocks
   Dequantize = 390,
   RequantQ8Blocks = 391,  // new: any block format -> Q8_0 GGUF blocks on the device
+  GluPairs = 392,         // new: out[r, i] = unary(in[r, 2i]) * in[r, 2i + 1] (gate / up stored as row pairs)
   TransposeQ4 = 401,
 };
 
@@ -403,6 +404,24 @@ private:
   uint32_t rows_, cols_;
 };
 
+/// The gated activation over a matmul whose weight rows are (gate_i, up_i) pairs: [rows, 2F] -> [rows, F],
+/// out[r, i] = unary(in[r, 2i]) * in[r, 2i + 1] (SiLU for the llama feed-forward, interface/runner/llama/llama.cpp:2455-2470).
+class GluPairsOpNode : public OpNode {
+public:
+  GluPairsOpNode(TensorStore &store, const Tensor &in, OperatorEnum unaryOp, std::optional<uint32_t> spec = {});
+  DataType outputDtype() const override { return DataType::Float32; }
+  size_t shaderKey() const override { return static_cast<size_t>(op_) | (static_cast<size_t>(unaryOp_) << 16); }
+  std::optional<std::vector<uint32_t>> shader() const override;
+  std::vector<uint32_t> outputShape() const override { return {rows_, colsOut_}; }
+  ThreadSize dispatchSize() const override { return {colsOut_, rows_, 1}; }
+  std::vector<uint8_t> pushConstants() const override;
+  std::string displayName() const override { return "GluPairs"; }
+
+private:
+  OperatorEnum unaryOp_;
+  uint32_t rows_ = 0, colsOut_ = 0, strideIn_ = 0, strideOut_ = 0;
+};
+
 class TransposeQ4NibbleOpNode : public OpNode {
 public:
   TransposeQ4NibbleOpNode(TensorStore &store, const Tensor &packedInput, uint32_t N, uint32_t K,
@@ -656,6 +675,8 @@ public:
   Tensor matmulBlocksFused(const Tensor &a, const Tensor &rawBlocks, DequantFormat format, uint32_t N,
                            const MatMulBlockOptions &opt, MatMulFusion fusion = MatMulFusion::None, OperatorEnum fusionOp = {},
                            const Tensor &d = {});
+  /// out[r, i] = unary(in[r, 2i]) * in[r, 2i + 1] for a Float32 [rows, 2F] input.
+  Tensor gluPairs(const Tensor &in, OperatorEnum unaryOp);
   Tensor transposeQ4(const Tensor &packedInput, uint32_t N, uint32_t K);
   Tensor dequantize(const Tensor &rawData, uint32_t format, uint32_t rows, uint32_t cols);
   /// Raw blocks of `format` -> Q8_0 GGUF blocks (a 1-D Int8 tensor matmulBlocks takes with DequantFormat::Q8_0).

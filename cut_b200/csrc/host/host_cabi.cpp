@@ -70,7 +70,9 @@ extern "C" __attribute__((visibility("default"))) int cut_host_e2e_matvec_blocks
 // Greedy decoding of a llama-style GGUF model through LlamaRunner (llama_runner.h): the prompt is fed one token
 // per step (positions 0, 1, ...), then `n_generate` tokens are generated from the arg-max of each step.
 //
-//   option_bits   1 fused RMSNorms, 2 paired gate / up rows, 4 activations staged at 16 bits, 8 fp16 KV cache
+//   option_bits   1 fused RMSNorms, 2 paired gate / up rows, 4 activations staged at 16 bits, 8 fp16 KV cache,
+//                 16 the prompt as ONE batch (LlamaRunner::prefill) instead of token by token: then only the last
+//                 prompt step's arg-max and logits exist (tokens_out / logits_out entries before it stay zero)
 //   tokens_out    [n_prompt + n_generate] the arg-max after every step (tokens_out[i] is what follows step i)
 //   logits_out    null, or [n_prompt + n_generate][vocab] the logits of every step
 //   seconds       wall time of the generation steps only (the prompt steps are warm-up)
@@ -102,9 +104,15 @@ extern "C" __attribute__((visibility("default"))) int cut_host_llama_generate(
         std::memcpy(logits_out + (size_t)step * vocab, l.data(), (size_t)vocab * sizeof(float));
       }
     };
-    for (uint32_t i = 0; i < n_prompt; ++i, ++pos) {
-      next = runner.forward(prompt[i], pos);
-      keep(i);
+    if (option_bits & 16u) {
+      next = runner.prefill(std::vector<uint32_t>(prompt, prompt + n_prompt), 0);
+      pos = n_prompt;
+      keep(n_prompt - 1);
+    } else {
+      for (uint32_t i = 0; i < n_prompt; ++i, ++pos) {
+        next = runner.forward(prompt[i], pos);
+        keep(i);
+      }
     }
     const auto t0 = std::chrono::steady_clock::now();
     for (uint32_t i = 0; i < n_generate; ++i, ++pos) {

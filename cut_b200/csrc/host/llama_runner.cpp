@@ -193,6 +193,7 @@ void LlamaRunner::record() {
     x = project(act, L.wdown, {}, MatMulFusion::Binary, BinaryAdd, x1, false, false);
   }
   logits_ = project(x, lmHead_, finalNorm_, MatMulFusion::None, {}, {}, false, false);
+  lastLogits_ = logits_;
   next_ = ops.reduce(ReduceArgmax, logits_);
   dispatches_ = iface.pendingDispatches();
   cb_ = iface.submitReusable();
@@ -209,12 +210,82 @@ uint32_t LlamaRunner::forward(uint32_t token, uint32_t pos) {
   rt_.iface().wait(cb_);
   float best = 0.f;
   rt_.copyFromTensor(next_, &best, sizeof(best));
+  lastLogits_ = logits_;
+  return (uint32_t)best;
+}
+
+uint32_t LlamaRunner::prefill(const std::vector<uint32_t> &tokens, uint32_t start) {
+  const uint32_t T = (uint32_t)tokens.size();
+  if (T == 0 || (uint64_t)start + T > cfg_.maxSeq) throw std::runtime_error("llama: prefill takes 1 .. maxSeq - start tokens");
+  for (uint32_t t : tokens)
+    if (t >= cfg_.vocab) throw std::runtime_error("llama: token id past the vocabulary");
+  Operations &ops = rt_.ops();
+  ComputeInterface &iface = rt_.iface();
+  const uint32_t qDim = cfg_.qDim(), kvDim = cfg_.kvDim();
+  std::vector<uint32_t> pos(T);
+  for (uint32_t i = 0; i < T; ++i) pos[i] = start + i;
+  Tensor tok = rt_.createTensor({T}, DataType::UInt32, tokens.data());
+  Tensor positions = rt_.createTensor({T}, DataType::UInt32, pos.data());
+  // batch projections: the tensor-core GEMM from 17 tokens up, the mat-vec below (no fusion flags: RMSNorm and the
+  // gated activation are operators of their own here)
+  auto mm = [&](const Tensor &a, const BlockWeight &w, MatMulFusion fusion, OperatorEnum op, const Tensor &d) {
+    if (fusion == MatMulFusion::Unary) return ops.matmulBlocksUnary(op, a, w.raw, w.format, w.N);
+    if (fusion == MatMulFusion::Binary) return ops.matmulBlocksBinary(op, a, w.raw, w.format, w.N, d);
+    return ops.matmulBlocks(a, w.raw, w.format, w.N);
+  };
+  Tensor x = ops.embedding(tok, table_);  // [T, dim]
+  for (uint32_t l = 0; l < cfg_.nLayers; ++l) {
+    Layer &L = layers_[l];
+    Tensor h = ops.rmsNorm(x, L.attnNorm, cfg_.normEps);
+    Tensor att;
+    if (fusedQkv_) {
+      Tensor qkv = mm(h, L.wqkv, MatMulFusion::None, {}, {});  // [T, qDim + 2 kvDim]: q, k, v are its columns
+      const uint32_t width = qDim + 2 * kvDim;
+      ops.batchedKVCacheWrite(qkv, qkv, L.kCache, L.vCache, positions, cosT_, sinT_, T, cfg_.nKvHeads, cfg_.headDim, width, width, qDim,
+                              qDim + kvDim);
+      ops.barrier();
+      att = ops.batchedAttentionReadCache(qkv, L.kCache, L.vCache, positions, cosT_, sinT_, T, cfg_.nHeads, cfg_.nKvHeads, cfg_.headDim,
+                                          width, 0);
+    } else {
+      Tensor q = mm(h, L.wq, MatMulFusion::None, {}, {}), k = mm(h, L.wk, MatMulFusion::None, {}, {}),
+             v = mm(h, L.wv, MatMulFusion::None, {}, {});
+      ops.batchedKVCacheWrite(k, v, L.kCache, L.vCache, positions, cosT_, sinT_, T, cfg_.nKvHeads, cfg_.headDim, kvDim, kvDim, 0, 0);
+      ops.barrier();
+      att = ops.batchedAttentionReadCache(q, L.kCache, L.vCache, positions, cosT_, sinT_, T, cfg_.nHeads, cfg_.nKvHeads, cfg_.headDim,
+                                          qDim, 0);
+    }
+    Tensor x1 = mm(att, L.wo, MatMulFusion::Binary, BinaryAdd, x);
+    Tensor h2 = ops.rmsNorm(x1, L.ffnNorm, cfg_.normEps);
+    Tensor act;
+    if (L.wgu.raw) {
+      act = ops.gluPairs(mm(h2, L.wgu, MatMulFusion::None, {}, {}), UnarySilu);
+    } else {
+      Tensor gate = mm(h2, L.wgate, MatMulFusion::Unary, UnarySilu, {});
+      act = mm(h2, L.wup, MatMulFusion::Binary, BinaryMul, gate);
+    }
+    x = mm(act, L.wdown, MatMulFusion::Binary, BinaryAdd, x1);
+  }
+  // the last token's row through the final norm and the head
+  const size_t rowBytes = (size_t)rt_.getTensor(x).innerDimPadded() * sizeof(float);
+  Tensor last;
+  if (((size_t)(T - 1) * rowBytes) % iface.bufferOffsetAlignment() == 0) {
+    last = iface.createBufferView(x, (size_t)(T - 1) * rowBytes, {cfg_.dim}, DataType::Float32);
+  } else {  // (a row that does not start on a view boundary: through the host, dim floats)
+    std::vector<float> all((size_t)T * cfg_.dim);
+    rt_.copyFromTensor(x, all.data(), all.size() * sizeof(float));
+    last = rt_.createTensor({cfg_.dim}, DataType::Float32, all.data() + (size_t)(T - 1) * cfg_.dim);
+  }
+  Tensor logits = ops.matmulBlocks(ops.rmsNorm(last, finalNorm_, cfg_.normEps), lmHead_.raw, lmHead_.format, lmHead_.N);
+  Tensor next = ops.reduce(ReduceArgmax, logits);
+  float best = 0.f;
+  rt_.copyFromTensor(next, &best, sizeof(best));  // flushes
+  lastLogits_ = logits;
   return (uint32_t)best;
 }
 
 std::vector<float> LlamaRunner::logits() {
   std::vector<float> out(cfg_.vocab);
-  rt_.copyFromTensor(logits_, out.data(), out.size() * sizeof(float));
+  rt_.copyFromTensor(lastLogits_, out.data(), out.size() * sizeof(float));
   return out;
 }
 

@@ -46,7 +46,12 @@ public:
   /// One token at position `pos` (rows [0, pos) of the KV cache must hold the tokens before it): writes the
   /// two small buffers, replays the recorded step, returns the arg-max of the logits.
   uint32_t forward(uint32_t token, uint32_t pos);
-  /// The logits of the last forward() (vocab floats).
+  /// The prompt as one batch (llama.cpp prefillBatched): every projection is one matmul over all T tokens, K / V
+  /// rows go to the cache through the batched RoPE write, every token attends over the rows up to its own.  Tokens
+  /// take positions start .. start + T - 1 (start + T <= maxSeq); returns the arg-max after the last token, whose
+  /// logits logits() then returns.  Not recorded: the dispatches run once.
+  uint32_t prefill(const std::vector<uint32_t> &tokens, uint32_t start = 0);
+  /// The logits of the last forward() or prefill() (vocab floats).
   std::vector<float> logits();
   /// Dispatches recorded per token (barriers not counted).
   size_t dispatchesPerToken() const { return dispatches_; }
@@ -70,6 +75,7 @@ private:
   bool fusedQkv_ = false;
   std::vector<Layer> layers_;
   Tensor table_, finalNorm_, cosT_, sinT_, params_, token_, logits_, next_;
+  Tensor lastLogits_;  ///< what logits() reads: the recorded step's or the last prefill's
   BlockWeight lmHead_;
   ComputeHandle cb_;
   size_t dispatches_ = 0;

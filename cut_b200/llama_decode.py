@@ -366,10 +366,12 @@ def write_model_gguf(path: str, cfg: LlamaConfig, weights: dict) -> None:
 
 
 def run_cpp_runner(path: str, prompt, n_generate: int, *, device: int = 0, max_seq: int = 512, fuse_norm: bool = True,
-                   glu_pairs: bool = True, act_16bit: bool = True, kv_half: bool = True, want_logits: bool = False) -> dict:
+                   glu_pairs: bool = True, act_16bit: bool = True, kv_half: bool = True, want_logits: bool = False,
+                   batch_prompt: bool = False) -> dict:
     """Greedy decoding through the C++ LlamaRunner of libcut_host.so (Runtime -> GGUFFile -> GGUFUploader -> the recorded
     per-token command buffer): the prompt token by token, then n_generate tokens.  Returns the arg-max after every step,
-    optionally every step's logits, the seconds spent on the generation steps and the runner's own counts."""
+    optionally every step's logits, the seconds spent on the generation steps and the runner's own counts.  With
+    batch_prompt the prompt runs as one batch (LlamaRunner::prefill); only its last step's entries are filled then."""
     from . import build
 
     lib = C.CDLL(build.build_host())
@@ -383,7 +385,7 @@ def run_cpp_runner(path: str, prompt, n_generate: int, *, device: int = 0, max_s
     vocab, disp = C.c_uint32(0), C.c_uint32(0)
     secs, wbytes = C.c_double(0.0), C.c_uint64(0)
     err = C.create_string_buffer(512)
-    bits = (1 if fuse_norm else 0) | (2 if glu_pairs else 0) | (4 if act_16bit else 0) | (8 if kv_half else 0)
+    bits = (1 if fuse_norm else 0) | (2 if glu_pairs else 0) | (4 if act_16bit else 0) | (8 if kv_half else 0) | (16 if batch_prompt else 0)
     logits = None
     if want_logits:
         # the vocabulary is in the file: token_embd's outer dimension; a first call without logits reports it

@@ -254,6 +254,65 @@ void blockNodesAndDequant() {
   CHECK(tp.N == 6 && tp.K == 32 && tp.sin == 16 && tp.sout == 4);
 }
 
+// The runner's extras of the block matmul node (fused RMSNorm of A, paired gate / up rows, staging and overlap
+// flags) and the GluPairs operator: descriptor words, bindings, push constants, output shapes, refusals.
+void blockMatmulOptionsAndGluPairs() {
+  Fixture f;
+  auto &s = f.rt.store();
+  const uint32_t K = 512, N = 12;
+  auto raw = s.createTensor({N * (K / 32) * 18}, DataType::Int8);
+  auto x = s.createTensor({K}, DataType::Float32);
+  auto nw = s.createTensor({K}, DataType::Float32);
+  MatMulOpNode plain(s, x, raw, DequantFormat::Q4_0, N);
+  CHECK(plain.shader()->size() == 9 && plain.blockFlags() == 0);  // no options: the nine-word descriptor as before
+  MatMulOpNode n1(s, x, raw, DequantFormat::Q4_0, N);
+  MatMulBlockOptions o;
+  o.flags = kBlockFlagRmsNorm | kBlockFlagAct16 | kBlockFlagNoOverlap;
+  o.normWeight = nw;
+  o.normEps = 1e-6f;
+  n1.setBlockOptions(o);
+  auto kd = KernelDesc::decode(*n1.shader());
+  CHECK(n1.shader()->size() == 10 && kd && kd->flags == o.flags && kd->op == MatMulQBlocks);
+  auto b = n1.bindings();  // A, raw blocks, the norm weight, dummy D, C, push constants (one more word: the epsilon)
+  CHECK(b.size() == 6 && b[2].handle == nw && b[4].handle == n1.output() && b[5].bytes.size() == 32);
+  float eps;
+  std::memcpy(&eps, b[5].bytes.data() + 28, 4);
+  CHECK(eps == 1e-6f);
+  CHECK(n1.shaderKey() != plain.shaderKey());
+  MatMulOpNode g(s, x, raw, DequantFormat::Q4_0, N);
+  g.setFusion(MatMulFusion::Unary, UnarySilu);
+  MatMulBlockOptions og;
+  og.flags = kBlockFlagGluPairs;
+  g.setBlockOptions(og);
+  CHECK(g.outputShape() == (std::vector<uint32_t>{1, N / 2}) && f.rt.getTensor(g.output()).getShape() == g.outputShape());
+  CHECK(pcOf(g).strideC == 8 && pcOf(g).N == N);  // the output row is N / 2 wide, padded to 4
+  MatMulOpNode bad(s, x, raw, DequantFormat::Q4_0, N);
+  CHECK_THROWS(bad.setBlockOptions(og), "need a unary fusion");
+  MatMulBlockOptions on;
+  on.flags = kBlockFlagRmsNorm;
+  CHECK_THROWS(bad.setBlockOptions(on), "needs its weight");
+  on.normWeight = s.createTensor({K + 4}, DataType::Float32);
+  CHECK_THROWS(bad.setBlockOptions(on), "must be Float32 [K]");
+  MatMulOpNode gemm(s, s.createTensor({64, K}, DataType::Float16), raw, DequantFormat::Q4_0, N);
+  on.normWeight = nw;
+  CHECK_THROWS(gemm.setBlockOptions(on), "decode mat-vec only");
+  auto fused = f.rt.ops().matmulBlocksFused(x, raw, DequantFormat::Q4_0, N, o);
+  CHECK(f.rt.getTensor(fused).getShape() == (std::vector<uint32_t>{1, N}));
+
+  GluPairsOpNode gp(s, s.createTensor({5, 14}, DataType::Float32), UnarySilu);
+  CHECK(gp.op() == GluPairs && gp.outputShape() == (std::vector<uint32_t>{5, 7}) && gp.displayName() == "GluPairs");
+  struct {
+    uint32_t rows, colsOut, strideIn, strideOut;
+  } gpc;
+  auto gb = gp.bindings();
+  std::memcpy(&gpc, gb.back().bytes.data(), sizeof(gpc));
+  CHECK(gpc.rows == 5 && gpc.colsOut == 7 && gpc.strideIn == 16 && gpc.strideOut == 8);
+  auto gkd = KernelDesc::decode(*gp.shader());
+  CHECK(gkd && gkd->op == GluPairs && gkd->fusionOp == (uint32_t)UnarySilu);
+  CHECK_THROWS(GluPairsOpNode(s, s.createTensor({5, 13}, DataType::Float32), UnarySilu), "even number of columns");
+  CHECK_THROWS(GluPairsOpNode(s, s.createTensor({5, 14}, DataType::Float16), UnarySilu), "must be Float32");
+}
+
 void dispatcherAndOperations() {
   Fixture f;
   auto &ops = f.rt.ops();
@@ -517,6 +576,7 @@ int main() {
   RUN(shapeErrors);
   RUN(pushConstantsBindingsAndKeys);
   RUN(blockNodesAndDequant);
+  RUN(blockMatmulOptionsAndGluPairs);
   RUN(dispatcherAndOperations);
   RUN(variantSelectorRules);
   RUN(ggufFileParsing);

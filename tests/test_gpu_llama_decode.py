@@ -191,3 +191,33 @@ def test_cpp_runner_over_a_gguf_file_matches_composed_checker(tmp_path, fmt, fus
         assert int(out["tokens"][step]) == int(np.argmax(out["logits"][step]))
         if step + 1 >= len(prompt):
             feed.append(int(out["tokens"][step]))  # generation continues with the runner's own greedy pick
+
+
+@pytest.mark.parametrize("fmt,T", [(2, 7), (0, 40), (1, 23)])
+def test_cpp_runner_batched_prefill_matches_composed_checker(tmp_path, fmt, T):
+    """LlamaRunner::prefill: the prompt as one batch through the operator API (GEMM projections from 17 tokens up, the
+    GluPairs operator over the paired gate / up rows, batched RoPE cache write and attention), then recorded decode
+    steps that read the cache the prefill wrote: the last prompt step's logits and every generated step's against the
+    float64 composition run token by token (3e-3 rel-L2: the prefill GEMM rounds its activations to fp16)."""
+    from cut_b200.llama_decode import LlamaConfig, run_cpp_runner, synthetic_weights, write_model_gguf
+
+    cfg = LlamaConfig(n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=512, max_seq=64, fmt=fmt)
+    w = synthetic_weights(cfg, seed=fmt + 11, scale_shift=4)
+    w["embedding"] = (w["embedding"] * 50).astype(np.float32)
+    path = str(tmp_path / "model.gguf")
+    write_model_gguf(path, cfg, w)
+    prompt = np.random.default_rng(T).integers(0, cfg.vocab, T)
+    n_gen = 4
+    out = run_cpp_runner(path, prompt, n_gen, max_seq=cfg.max_seq, want_logits=True, batch_prompt=True)
+    ref = Reference(cfg, w)
+    for pos, tok in enumerate(prompt):
+        want = ref.step(int(tok), pos)
+    feed = int(out["tokens"][T - 1])
+    for step in range(T - 1, T + n_gen):
+        if step >= T:
+            want = ref.step(feed, step)
+            feed = int(out["tokens"][step])
+        got = out["logits"][step].astype(np.float64)
+        rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+        assert np.isfinite(got).all() and rel <= 3e-3, (step, rel)
+        assert int(out["tokens"][step]) == int(np.argmax(out["logits"][step]))
