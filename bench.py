@@ -193,7 +193,104 @@ def run_reference(args) -> None:
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    try:
+        ref_gpu = reference_cuda_measurement()
+    except Exception as e:  # noqa: BLE001  (context only: the arm's number is the CPU one)
+        ref_gpu = {"error": f"{type(e).__name__}: {e}"}
+    if ref_gpu:
+        line["config"]["also_measured"] = {"reference_cuda_kernels_on_this_gpu": ref_gpu}
     print(json.dumps(line), flush=True)
+
+
+def reference_cuda_measurement() -> dict | None:
+    """The reference's OWN CUDA kernels on this GPU, as context for the reference arm (its decode path when its CUDA
+    backend runs: MatMulQ4GemvKPar8 / MatMulQ8GemvKPar8 over the [K, N] plane layout, compiled by NVRTC from the
+    reference tree into oracle/_ref/cuda by oracle/build_ref_cuda.py).  Same workloads as the GPU arm: configs[1]
+    (Q4_0 11008 x 4096, batch 1; the reference's kernels take fp32 activations) and configs[0] (Q8_0 4096 x 4096),
+    weights cycled over distinct copies so that L2 cannot serve them, one CUDA graph per pass.  None without a GPU or
+    without the cubins."""
+    try:
+        import torch
+
+        from oracle import ref_cuda
+    except Exception:  # noqa: BLE001
+        return None
+    if not torch.cuda.is_available() or not ref_cuda.have("MatMulQ4GemvKPar8"):
+        return None
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    out = {}
+    for key, kernel, fmt, n, k in (("configs[1]_q4_0_11008x4096_batch1", "MatMulQ4GemvKPar8", L.Q4_0, N_ROWS, K_COLS),
+                                   ("configs[0]_q8_0_4096x4096_batch1", "MatMulQ8GemvKPar8", L.Q8_0, 4096, 4096)):
+        if not ref_cuda.have(kernel):
+            continue
+        q4 = fmt == L.Q4_0
+        raw = torch.from_numpy(synth.make_weights(fmt, n, k, seed=71)).to(dev)
+        vals, scales = ops.separate_blocks(raw, fmt, n, k)
+        plane = ops.transpose_q4(vals, n, k) if q4 else ops.transpose_2d(vals, ldo=(n + 3) // 4 * 4)
+        scalesT = ops.transpose_2d(scales, ldo=(n + 3) // 4 * 4)
+        reps = max(2, int(600e6 // plane.numel()) + 1)
+        P = torch.stack([torch.roll(plane, shifts=13 * r, dims=1) for r in range(reps)])
+        A = torch.from_numpy(synth.make_activations(1, k, 72, np.float32)).to(dev)
+        C = torch.zeros((reps, 1, n), dtype=torch.float32, device=dev)
+
+        def sweep():
+            for r in range(reps):
+                ref_cuda.launch(kernel, A, P[r], scalesT, C[r], 1, k, n, stride_a=k, stride_b=plane.stride(0), stride_c=n,
+                                scale_stride=scalesT.stride(0))
+
+        sweep()
+        torch.cuda.synchronize()
+        want = ops.qmatmul(A, raw, fmt, n)  # replica 0 is not rotated: the block kernel on the same weights
+        rel = float(torch.linalg.norm(C[0] - want) / torch.linalg.norm(want))
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            sweep()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 10
+        a.record()
+        for _ in range(iters):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (iters * reps)
+        nbytes = plane.numel() + scalesT.numel() * 2 + k * 4 + n * 4
+        out[key] = {"kernel": kernel, "us_per_launch": us, "GB/s": nbytes / us / 1e3, "algorithmic_bytes": nbytes,
+                    "weight_copies": reps, "rel_l2_vs_block_kernel": rel}
+        del g, P, C
+        torch.cuda.empty_cache()
+    # prefill: its tensor-core tiled kernel on the configs[2] shape (Q4_0 planes; the GPU arm's GEMM reads Q4_K blocks
+    # of the same shape, and Q4_0 blocks in 60 us)
+    if ref_cuda.have("MatMulQ4CoopMatTiled"):
+        m, k, n = 512, 4096, 14336
+        raw = torch.from_numpy(synth.make_weights(L.Q4_0, n, k, seed=73)).to(dev)
+        vals, scales = ops.separate_blocks(raw, L.Q4_0, n, k)
+        plane, scalesT = ops.transpose_q4(vals, n, k), ops.transpose_2d(scales, ldo=n)
+        A = torch.from_numpy(synth.make_activations(m, k, 74, np.float32)).to(dev)
+        C = torch.zeros((m, n), dtype=torch.float32, device=dev)
+        run = lambda: ref_cuda.launch("MatMulQ4CoopMatTiled", A, plane, scalesT, C, m, k, n, stride_a=k, stride_b=plane.stride(0),
+                                      stride_c=n, scale_stride=n)
+        for _ in range(2):
+            run()
+        torch.cuda.synchronize()
+        want = ops.qmatmul(A, raw, L.Q4_0, n)
+        rel = float(torch.linalg.norm(C - want) / torch.linalg.norm(want))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(5):
+            run()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / 5
+        out["configs[2]_shape_q4_0_512x4096x14336"] = {"kernel": "MatMulQ4CoopMatTiled", "us_per_launch": us,
+                                                       "TFLOP/s": 2.0 * m * k * n / us / 1e6, "rel_l2_vs_block_gemm": rel}
+    return out or None
 
 
 def decode_measurement(dev, n_layers: int = 32, steps: int = 256, graph: bool = True, synthetic_cache: bool = False,

@@ -1,0 +1,67 @@
+"""Compiles the reference's own CUDA matmul kernels for sm_100a, as its backend does at run time.
+
+TEST / BASELINE INFRASTRUCTURE ONLY.  The reference hands `#include "cut_cuda_prelude.cuh"` + a kernel's .cu text
+to NVRTC with its headers by name and `--std=c++17` (core/backends/cuda/CudaContainers.cpp:94-222).  This script
+does the same from the sources where they lie in the reference tree (nothing is copied into this repository) and
+writes one cubin per kernel into oracle/_ref/cuda/ -- the checker the plane-layout kernels are compared with on the
+GPU, and the reference-GPU baseline `bench.py` times beside them.  NVRTC needs no GPU.
+
+    python oracle/build_ref_cuda.py /path/to/reference [out_dir]
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+KERNELS = ["MatMulQ4GemvKPar8", "MatMulQ8GemvKPar8", "MatMulQ4CoopMatTiled", "MatMulQ8CoopMatTiled"]
+HEADERS = {"cut_cuda_prelude.cuh": "operators/runtime/cuda/cut_cuda_prelude.cuh", "ComputeOpsShared.h": "operators/runtime/ComputeOpsShared.h",
+           "MatMulCommon.cuh": "operators/impl/matmul/MatMulCommon.cuh", "MatMulCoopMatCommon.cuh": "operators/impl/matmul/MatMulCoopMatCommon.cuh",
+           "MatMulQ4Common.cuh": "operators/impl/matmul/MatMulQ4Common.cuh", "MatMulQ8Common.cuh": "operators/impl/matmul/MatMulQ8Common.cuh"}
+
+
+def build(ref_root: str, out_dir: str) -> list[str]:
+    """Returns the cubins written (kernels NVRTC rejects are reported on stderr and skipped)."""
+    from cuda.bindings import nvrtc
+
+    def rd(rel: str) -> bytes:
+        with open(os.path.join(ref_root, rel), "rb") as f:
+            return f.read()
+
+    os.makedirs(out_dir, exist_ok=True)
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    opts = [b"--gpu-architecture=sm_100a", b"--std=c++17", f"-I{cuda_home}/include".encode(), f"-I{cuda_home}/include/cccl".encode()]
+    names = [n.encode() for n in HEADERS]
+    srcs = [rd(p) for p in HEADERS.values()]
+    written = []
+    for k in KERNELS:
+        src = b'#include "cut_cuda_prelude.cuh"\n' + rd(f"operators/impl/matmul/{k}.cu")
+        err, prog = nvrtc.nvrtcCreateProgram(src, b"cut_kernel.cu", len(names), srcs, names)
+        if int(err) != 0:
+            print(f"build_ref_cuda: nvrtcCreateProgram failed for {k}: {err}", file=sys.stderr)
+            continue
+        (res,) = nvrtc.nvrtcCompileProgram(prog, len(opts), opts)
+        if int(res) != 0:
+            _, n = nvrtc.nvrtcGetProgramLogSize(prog)
+            log = b" " * n
+            nvrtc.nvrtcGetProgramLog(prog, log)
+            print(f"build_ref_cuda: {k} does not compile here: {log.decode(errors='replace')[:400]}", file=sys.stderr)
+            nvrtc.nvrtcDestroyProgram(prog)
+            continue
+        _, size = nvrtc.nvrtcGetCUBINSize(prog)
+        cubin = b" " * size
+        nvrtc.nvrtcGetCUBIN(prog, cubin)
+        nvrtc.nvrtcDestroyProgram(prog)
+        path = os.path.join(out_dir, k + ".cubin")
+        with open(path, "wb") as f:
+            f.write(cubin)
+        written.append(path)
+    return written
+
+
+if __name__ == "__main__":
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REF_ROOT", "")
+    out = sys.argv[2] if len(sys.argv) > 2 else os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref", "cuda")
+    if not root or not os.path.isdir(root):
+        raise SystemExit("usage: build_ref_cuda.py <reference tree> [out dir]")
+    for p in build(root, out):
+        print(p)

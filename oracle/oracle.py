@@ -33,6 +33,18 @@ def build(force: bool = False) -> None:
     # environment, else the place this build keeps it); elsewhere the prebuilt files are used as they are
     ref_root = os.environ.get("REF_ROOT") or ("/root/reference" if os.path.isdir("/root/reference") else "")
     subprocess.run(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root}"], check=True, capture_output=True)
+    # the reference's own CUDA matmul kernels as cubins (NVRTC, as its backend compiles them; no GPU needed)
+    if ref_root:
+        try:
+            from . import build_ref_cuda
+        except ImportError:
+            import build_ref_cuda  # the module run from its own folder
+        cuda_dir = os.path.join(_HERE, "_ref", "cuda")
+        if force or not all(os.path.exists(os.path.join(cuda_dir, k + ".cubin")) for k in build_ref_cuda.KERNELS):
+            try:
+                build_ref_cuda.build(ref_root, cuda_dir)
+            except Exception as e:  # noqa: BLE001  (no NVRTC bindings here: the GPU-side checker is simply absent)
+                print(f"oracle: reference CUDA kernels not built: {e}")
 
 
 _lib = None

@@ -1,0 +1,78 @@
+"""The plane-layout kernels against the reference's OWN CUDA kernels run on this GPU (cubins compiled from the
+reference tree by oracle/build_ref_cuda.py, as its backend compiles them): same operands in the reference's
+run-time layout, outputs within fp32 summation-order noise of each other, and both within 1e-5 of the CPU checker.
+Skipped where the cubins were not built (no reference tree and no prebuilt files)."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from oracle import ref_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+def _operands(q4, M, K, N, seed):
+    rng = np.random.default_rng(seed)
+    ldb = (N // 2 if q4 else N)
+    B = rng.integers(0, 256, size=(K, ldb), dtype=np.uint8)
+    S = rng.uniform(0.002, 0.02, size=(K // 32, N)).astype(np.float16)
+    A = rng.normal(0, 1, (M, K)).astype(np.float32)
+    return A, B, S
+
+
+@pytest.mark.parametrize("q4,kernel", [(True, "MatMulQ4GemvKPar8"), (False, "MatMulQ8GemvKPar8")])
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (1, 4096, 11008), (3, 1024, 264), (1, 96, 8)])
+def test_plane_matvec_against_the_reference_cuda_matvec(q4, kernel, M, K, N):
+    import torch
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops
+
+    if not ref_cuda.have(kernel):
+        pytest.skip("reference cubins not built")
+    A, B, S = _operands(q4, M, K, N, K + N + M)
+    dA, dB, dS = (torch.from_numpy(x).cuda() for x in (A, B, S.view(np.uint16)))
+    ldb = B.shape[1]
+    ref_out = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    ref_cuda.launch(kernel, dA, dB, dS, ref_out, M, K, N, stride_a=K, stride_b=ldb, stride_c=N, scale_stride=N)
+    ours = ops.qmatmul(dA, dB, L.Q4_0 if q4 else L.Q8_0, N, layout=L.LAYOUT_KN_PLANES, scales=dS, ldb=ldb, lds=N,
+                       variant=L.VARIANT_GEMV_PLANES)
+    torch.cuda.synchronize()
+    got, ref = ours.cpu().numpy().astype(np.float64), ref_out.cpu().numpy().astype(np.float64)
+    want = O.qmatmul_planes(q4, False, A, B, S.view(np.uint16), M, K, N, acc64=True).astype(np.float64)
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    assert rel(ref, want) <= 1e-5   # the reference's kernel is what the checker restates
+    assert rel(got, want) <= 1e-5
+    assert rel(got, ref) <= 1e-5
+
+
+@pytest.mark.parametrize("q4,kernel", [(True, "MatMulQ4CoopMatTiled"), (False, "MatMulQ8CoopMatTiled")])
+def test_block_gemm_against_the_reference_tensor_core_kernel(q4, kernel):
+    """Prefill: the reference's tiled tensor-core kernel over planes against this library's GEMM over the same weights
+    as GGUF blocks (planes built from the blocks by the device repacks).  Both round operands to fp16: 3e-3."""
+    import torch
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    if not ref_cuda.have(kernel):
+        pytest.skip("reference cubins not built")
+    M, K, N = 64, 1024, 256
+    fmt = L.Q4_0 if q4 else L.Q8_0
+    raw = torch.from_numpy(synth.make_weights(fmt, N, K, seed=77)).cuda()
+    A = torch.from_numpy(synth.make_activations(M, K, 78, np.float32)).cuda()
+    vals, scales = ops.separate_blocks(raw, fmt, N, K)
+    if q4:
+        planeB = ops.transpose_q4(vals, N, K)                      # [K, pad4(N / 2)]
+    else:
+        planeB = ops.transpose_2d(vals, ldo=(N + 3) // 4 * 4)     # [K, pad4(N)]
+    planeS = ops.transpose_2d(scales, ldo=(N + 3) // 4 * 4)       # [K / 32, pad4(N)]
+    ref_out = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    ref_cuda.launch(kernel, A, planeB, planeS, ref_out, M, K, N, stride_a=K, stride_b=planeB.stride(0), stride_c=N,
+                    scale_stride=planeS.stride(0))
+    ours = ops.qmatmul(A, raw, fmt, N, variant=L.VARIANT_GEMM_TC)
+    torch.cuda.synchronize()
+    want = O.qmatmul_blocks(fmt, A.cpu().numpy(), raw.cpu().numpy(), M, K, N).astype(np.float64)
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    assert rel(ref_out.cpu().numpy().astype(np.float64), want) <= 3e-3
+    assert rel(ours.cpu().numpy().astype(np.float64), want) <= 3e-3
