@@ -491,6 +491,39 @@ def planes_chain_us(dev, n: int, k: int) -> dict:
             "rel_l2_vs_block_kernel": rel, "weight_copies": reps}
 
 
+def planes_gemm_us(dev, m: int, k: int, n: int) -> dict:
+    """Prefill over the reference's [K, N] planes (Q4_0 nibbles + fp16 scales, as its unchanged loader and Q4 transpose
+    produce them): the tcgen05 GEMM with plane converters, checked against the same GEMM over the GGUF blocks the planes
+    were made from."""
+    import torch
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    raw = torch.from_numpy(synth.make_weights(synth.Q4_0, n, k, seed=73)).to(dev)
+    vals, scales = ops.separate_blocks(raw, L.Q4_0, n, k)
+    plane, scalesT = ops.transpose_q4(vals, n, k), ops.transpose_2d(scales, ldo=(n + 3) // 4 * 4)
+    A = torch.from_numpy(synth.make_activations(m, k, 74, np.float16)).to(dev)
+    d, C, keep = ops.make_desc(A, plane, L.Q4_0, n, layout=L.LAYOUT_KN_PLANES, scales=scalesT, ldb=plane.stride(0), lds=scalesT.stride(0))
+    need = ops.workspace_bytes(d)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    d.workspace, d.workspace_bytes = ws.data_ptr(), need
+    for _ in range(3):
+        ops.launch(d)
+    torch.cuda.synchronize()
+    want = ops.qmatmul(A, raw, L.Q4_0, n)
+    rel = float(torch.linalg.norm(C - want) / torch.linalg.norm(want))
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        ops.launch(d)
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) * 1e3 / 20
+    return {"us_per_launch": us, "TFLOP/s": 2.0 * m * k * n / us / 1e6, "variant": L.lib().cutb_variant_name(ops.select_variant(d)).decode(),
+            "rel_l2_vs_block_gemm": rel}
+
+
 def projection_shapes_70b():
     """configs[4]: the projections of a 70B-shape decoder layer as (name, N rows, K) of Q4_0 weights."""
     return [("attn_q/o 8192x8192", 8192, 8192), ("ffn_gate/up 28672x8192", 28672, 8192), ("ffn_down 8192x28672", 8192, 28672)]
@@ -591,6 +624,7 @@ def secondary_measurements(dev) -> dict:
     out["configs[1]_q4_0_kn_planes_batch1"] = planes_chain_us(dev, N_ROWS, K_COLS)
     if hbm:
         out["configs[1]_q4_0_kn_planes_batch1"]["frac_of_measured_hbm"] = out["configs[1]_q4_0_kn_planes_batch1"]["GB/s"] / hbm
+    out["configs[2]_shape_q4_0_kn_planes_512x4096x14336"] = planes_gemm_us(dev, 512, 4096, 14336)
     # configs[4] on one GPU: the whole 70B-shape projections (the N > 1 runs shard these same tensors)
     proj = {}
     for name, n, k in projection_shapes_70b():

@@ -111,6 +111,8 @@ int select(const cutb_qmatmul_desc &d) {
     if (qgemm_tc_supported(d)) return CUTB_VARIANT_GEMM_TC;
   } else if (qgemv_planes_supported(d)) {
     return CUTB_VARIANT_GEMV_PLANES;
+  } else if (qgemm_tc_supported(d)) {
+    return CUTB_VARIANT_GEMM_TC;  // prefill over the planes: the tensor-core GEMM with plane converters
   }
   return CUTB_VARIANT_GENERIC;
 }

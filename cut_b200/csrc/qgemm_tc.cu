@@ -76,7 +76,17 @@ struct TcParams {
   uint32_t ksub;     // 64-k sub-tiles per stage (2 up to 256 tokens: the issuer's waits are paid per stage)
   int fusion_type, fusion_op;
   int *status;
+  // the reference's [K, N] plane layout (TC_PLANE_* formats): value plane row stride in bytes, fp16 scale plane and its
+  // row stride in elements, rows of the scale plane before the affine mins
+  const uint16_t *S;
+  uint32_t ldb, lds, blocksK;
 };
+
+// Weight sources of the converters besides the GGUF block formats: the reference's run-time planes
+// (operators/impl/matmul/MatMulOp.cpp:309-329), int8 [K, ldb], nibbles [K, ldb] with even n in the low nibble,
+// and the same with per-block mins behind the scales (the runner's affine re-encode of Q4_K).
+constexpr int TC_PLANE_Q8 = 100, TC_PLANE_Q4 = 101, TC_PLANE_Q4A = 102;
+__host__ __device__ constexpr bool tc_is_plane(int fmt) { return fmt >= TC_PLANE_Q8; }
 
 // ---- tcgen05 / descriptor helpers ----------------------------------------------
 // K-major operand tile, 64 fp16 (128 bytes) per row, 128-byte swizzle: rows are
@@ -174,6 +184,89 @@ template <int FMT> struct RawWindow {
   static constexpr int NV = FMT == CUTB_Q8_0 ? 5 : 3;
   uint4 v[NV];
 };
+// Plane layout: column n of 64 consecutive k rows is 64 separate bytes (a warp's 32 threads read 32 neighbouring
+// bytes of one k row per load).  They are packed four quants to a word as they arrive -- int8 as stored, nibbles as
+// one value per byte -- with the two block scales (and mins) of the 64 rows beside them.
+template <> struct RawWindow<TC_PLANE_Q8> {
+  static constexpr int NV = 4;
+  uint4 v[NV];
+  uint32_t sc;  // two f16 scales
+};
+template <> struct RawWindow<TC_PLANE_Q4> {
+  static constexpr int NV = 4;
+  uint4 v[NV];
+  uint32_t sc;
+};
+template <> struct RawWindow<TC_PLANE_Q4A> {
+  static constexpr int NV = 4;
+  uint4 v[NV];
+  uint32_t sc, mn;
+};
+
+template <int FMT> __device__ __forceinline__ void load_window_plane(const TcParams &p, uint32_t n, uint32_t k0, RawWindow<FMT> &r) {
+  constexpr bool Q4 = FMT != TC_PLANE_Q8;
+  const uint8_t *col = p.W + (size_t)k0 * p.ldb + (Q4 ? n >> 1 : n);
+  const uint32_t shift = Q4 ? (n & 1u) * 4u : 0u;
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    uint32_t b[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) b[j] = __ldg(col + (size_t)(4 * i + j) * p.ldb);
+    if constexpr (Q4) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = (b[j] >> shift) & 0xFu;
+    }
+    w[i] = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r.v[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+  const uint16_t *sp = p.S + (size_t)(k0 / 32) * p.lds + n;
+  r.sc = (uint32_t)__ldg(sp) | ((uint32_t)__ldg(sp + p.lds) << 16);
+  if constexpr (FMT == TC_PLANE_Q4A) {
+    const uint16_t *mp = sp + (size_t)p.blocksK * p.lds;
+    r.mn = (uint32_t)__ldg(mp) | ((uint32_t)__ldg(mp + p.lds) << 16);
+  }
+}
+
+// 64 plane weights -> 8 chunks of 8 halves: the exact integer times the fp16 block scale in fp16 (plus the fp16 min),
+// as the reference's tensor-core kernels widen them (MatMulQ8CoopMatTiled.cu:71-74, MatMulQ4CoopMatTiled.cu:84-87).
+template <int FMT> __device__ __forceinline__ void convert_window_plane(const RawWindow<FMT> &win, uint4 (&out)[8]) {
+  const uint32_t w[16] = {win.v[0].x, win.v[0].y, win.v[0].z, win.v[0].w, win.v[1].x, win.v[1].y, win.v[1].z, win.v[1].w,
+                          win.v[2].x, win.v[2].y, win.v[2].z, win.v[2].w, win.v[3].x, win.v[3].y, win.v[3].z, win.v[3].w};
+  const __half2 d0 = __half2half2(__ushort_as_half((unsigned short)(win.sc & 0xFFFFu)));
+  const __half2 d1 = __half2half2(__ushort_as_half((unsigned short)(win.sc >> 16)));
+  __half2 m0 = __float2half2_rn(0.f), m1 = m0;
+  if constexpr (FMT == TC_PLANE_Q4A) {
+    m0 = __half2half2(__ushort_as_half((unsigned short)(win.mn & 0xFFFFu)));
+    m1 = __half2half2(__ushort_as_half((unsigned short)(win.mn >> 16)));
+  }
+  const __half2 k8 = __float2half2_rn(8.f);
+  __half2 h[32];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const __half2 d = i < 8 ? d0 : d1;
+    __half2 a, c;
+    if constexpr (FMT == TC_PLANE_Q8) {
+      i8x4_to_h2(w[i], a, c);
+      h[2 * i] = __hmul2(a, d);
+      h[2 * i + 1] = __hmul2(c, d);
+    } else {
+      nib4_to_h2(w[i], a, c);
+      if constexpr (FMT == TC_PLANE_Q4A) {
+        const __half2 m = i < 8 ? m0 : m1;
+        h[2 * i] = __hfma2(__hsub2(a, k8), d, m);
+        h[2 * i + 1] = __hfma2(__hsub2(c, k8), d, m);
+      } else {
+        h[2 * i] = __hmul2(__hsub2(a, k8), d);
+        h[2 * i + 1] = __hmul2(__hsub2(c, k8), d);
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    out[c] = make_uint4(h2_as_u32(h[4 * c]), h2_as_u32(h[4 * c + 1]), h2_as_u32(h[4 * c + 2]), h2_as_u32(h[4 * c + 3]));
+}
 
 template <int FMT> __device__ __forceinline__ void load_window(const uint8_t *row, uint32_t k0, RawWindow<FMT> &r) {
   if constexpr (FMT == CUTB_Q4_K) {
@@ -417,12 +510,15 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
     const uint32_t G = (blockDim.x - TC_CTRL_THREADS) >> 7;
     const uint32_t ct = tid - TC_CTRL_THREADS, r = ct & 127u, g = ct >> 7, n = n0 + r;
     const bool live = n < p.N;
-    const uint8_t *wrow = p.W + (size_t)(live ? n : 0) * p.row_bytes;
+    const uint8_t *wrow = tc_is_plane(FMT) ? p.W : p.W + (size_t)(live ? n : 0) * p.row_bytes;
     bool dead = false;
     RawWindow<FMT> nxt;
 #pragma unroll
     for (int i = 0; i < RawWindow<FMT>::NV; ++i) nxt.v[i] = make_uint4(0, 0, 0, 0);
-    if (live && g < nk) load_window<FMT>(wrow, g * KS * TC_BK, nxt);
+    if (live && g < nk) {
+      if constexpr (tc_is_plane(FMT)) load_window_plane<FMT>(p, n, g * KS * TC_BK, nxt);
+      else load_window<FMT>(wrow, g * KS * TC_BK, nxt);
+    }
     // this group's slot sequence: start at slot g, advance by G modulo NB
     uint32_t sb = g % NB;
     uint32_t sc = 0, pc = 0;  // consumed barrier of stage ks - NB, once ks >= NB
@@ -434,10 +530,14 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
         const RawWindow<FMT> cur = nxt;
         // the chunk this thread converts next: the following sub-tile, or the first of the group's next stage
         const uint32_t nchunk = sub + 1 < KS ? chunk + 1 : (ks + G) * KS;
-        if (live && nchunk < nk * KS) load_window<FMT>(wrow, nchunk * TC_BK, nxt);
+        if (live && nchunk < nk * KS) {
+          if constexpr (tc_is_plane(FMT)) load_window_plane<FMT>(p, n, nchunk * TC_BK, nxt);
+          else load_window<FMT>(wrow, nchunk * TC_BK, nxt);
+        }
         uint4 out[8];
         if (live) {
-          convert_window<FMT>(cur, chunk * TC_BK, out);
+          if constexpr (tc_is_plane(FMT)) convert_window_plane<FMT>(cur, out);
+          else convert_window<FMT>(cur, chunk * TC_BK, out);
         } else {
 #pragma unroll
           for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
@@ -588,11 +688,19 @@ template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cuda
 }  // namespace
 
 bool qgemm_tc_supported(const cutb_qmatmul_desc &d) {
-  if (d.layout != CUTB_LAYOUT_GGUF_BLOCKS) return false;
-  if (d.K == 0 || d.K % 256 != 0 || d.M == 0 || d.N == 0) return false;
+  if (d.layout == CUTB_LAYOUT_KN_PLANES) {
+    // the converters walk whole 128-row stages of the planes; the scale plane must hold K / 32 (or 2 K / 32) rows
+    if (d.format != CUTB_Q8_0 && d.format != CUTB_Q4_0) return false;
+    if (d.K == 0 || d.K % 128 != 0 || d.M == 0 || d.N == 0 || !d.scales) return false;
+    const uint64_t row = d.format == CUTB_Q8_0 ? d.N : (d.N + 1) / 2;
+    if (d.ldb < row || d.lds < d.N) return false;
+  } else if (d.layout != CUTB_LAYOUT_GGUF_BLOCKS) {
+    return false;
+  }
+  if (d.K == 0 || (d.layout == CUTB_LAYOUT_GGUF_BLOCKS && d.K % 256 != 0) || d.M == 0 || d.N == 0) return false;
   // 16-byte vector loads of the activation rows and of Q4_K super-blocks
   const uintptr_t a = reinterpret_cast<uintptr_t>(d.A), w = reinterpret_cast<uintptr_t>(d.W);
-  if (a % 16 != 0 || w % 16 != 0) return false;
+  if (a % 16 != 0 || (d.layout == CUTB_LAYOUT_GGUF_BLOCKS && w % 16 != 0)) return false;
   if (d.a_dtype == CUTB_F32 ? d.lda % 4 != 0 : d.lda % 8 != 0) return false;
   DeviceInfo di;
   if (get_device_info(&di) != CUTB_OK) return true;  // shape check only (no device to ask)
@@ -620,6 +728,10 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.fusion_type = d.fusion_type;
   p.fusion_op = d.fusion_op;
   p.status = d.status;
+  p.S = reinterpret_cast<const uint16_t *>(d.scales);
+  p.ldb = d.ldb;
+  p.lds = d.lds;
+  p.blocksK = (d.K + 31) / 32;
   const uint32_t mblocks = (d.M + TC_BT - 1) / TC_BT;
   p.mb = mblocks < TC_MAX_MB ? mblocks : TC_MAX_MB;
   // Few weight rows (a 4096-row projection is 32 column tiles): fewer tokens per CTA until the grid covers at
@@ -669,6 +781,10 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   }
   CUtensorMap map;
   if (int rc = make_tmap_a(&map, a16, d.M, d.K, stride)) return rc;
+  if (d.layout == CUTB_LAYOUT_KN_PLANES) {
+    if (d.format == CUTB_Q8_0) return tc_launch<TC_PLANE_Q8>(map, p, stream);
+    return d.affine ? tc_launch<TC_PLANE_Q4A>(map, p, stream) : tc_launch<TC_PLANE_Q4>(map, p, stream);
+  }
   switch (d.format) {
     case CUTB_Q8_0: return tc_launch<CUTB_Q8_0>(map, p, stream);
     case CUTB_Q4_0: return tc_launch<CUTB_Q4_0>(map, p, stream);

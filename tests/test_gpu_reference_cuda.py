@@ -76,3 +76,38 @@ def test_block_gemm_against_the_reference_tensor_core_kernel(q4, kernel):
     rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))
     assert rel(ref_out.cpu().numpy().astype(np.float64), want) <= 3e-3
     assert rel(ours.cpu().numpy().astype(np.float64), want) <= 3e-3
+
+
+@pytest.mark.parametrize("q4,affine,kernel", [(True, False, "MatMulQ4CoopMatTiled"), (False, False, "MatMulQ8CoopMatTiled"), (True, True, None)])
+@pytest.mark.parametrize("M,K,N", [(64, 1024, 256), (13, 4096, 5120), (200, 512, 1000)])
+def test_plane_gemm_against_the_reference_tensor_core_kernel(q4, affine, kernel, M, K, N):
+    """Prefill over the reference's [K, N] planes: the tcgen05 GEMM with plane converters (what CUTB_VARIANT_AUTO
+    picks for this layout above four rows) against the reference's own tensor-core kernel on the same operands
+    (where its tile shape takes them: N % 32 == 0) and against the CPU checker; fp16 operands on both sides: 3e-3."""
+    import torch
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops
+
+    rng = np.random.default_rng(K + N + M)
+    ldb, lds = ((N // 2 if q4 else N) + 3) // 4 * 4, (N + 3) // 4 * 4
+    B = rng.integers(0, 256, size=(K, ldb), dtype=np.uint8)
+    S = np.zeros((K // 32 * (2 if affine else 1), lds), np.float16)
+    S[: K // 32] = rng.uniform(0.002, 0.02, size=(K // 32, lds)).astype(np.float16)
+    if affine:
+        S[K // 32:] = rng.uniform(-0.05, 0.05, size=(K // 32, lds)).astype(np.float16)
+    A = rng.normal(0, 1, (M, K)).astype(np.float32)
+    dA, dB, dS = (torch.from_numpy(x).cuda() for x in (A, B, S.view(np.uint16)))
+    d, C_out, keep = ops.make_desc(dA, dB, L.Q4_0 if q4 else L.Q8_0, N, layout=L.LAYOUT_KN_PLANES, scales=dS, affine=affine, ldb=ldb, lds=lds)
+    assert ops.select_variant(d) == L.VARIANT_GEMM_TC
+    ours = ops.qmatmul(dA, dB, L.Q4_0 if q4 else L.Q8_0, N, layout=L.LAYOUT_KN_PLANES, scales=dS, affine=affine, ldb=ldb, lds=lds)
+    torch.cuda.synchronize()
+    want = O.qmatmul_planes(q4, affine, A, B, S.view(np.uint16), M, K, N, lda=K, ldb=ldb, lds=lds, acc64=True).astype(np.float64)
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))
+    assert rel(ours.cpu().numpy().astype(np.float64), want) <= 3e-3
+    if kernel and N % 32 == 0 and ref_cuda.have(kernel):
+        ref_out = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+        ref_cuda.launch(kernel, dA, dB, dS, ref_out, M, K, N, stride_a=K, stride_b=ldb, stride_c=N, scale_stride=lds)
+        torch.cuda.synchronize()
+        assert rel(ref_out.cpu().numpy().astype(np.float64), want) <= 3e-3
+        assert rel(ours.cpu().numpy().astype(np.float64), ref_out.cpu().numpy().astype(np.float64)) <= 1e-3
