@@ -76,7 +76,8 @@ enum {
   CUTB_VARIANT_GENERIC = 0, /* any shape, SIMT, exact fp32 dequant + FMA */
   CUTB_VARIANT_GEMV_MMA = 1, /* decode: bulk-copy ring + int8 warp MMA, M <= 16 (fp16 A) / 8 (fp32 A) */
   CUTB_VARIANT_GEMM_TC = 2, /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory; its operands are fp16
-                               (see the operand-range note at cutb_qmatmul_desc) */
+                               (see the operand-range note at cutb_qmatmul_desc).  GGUF blocks (K % 256 == 0) and
+                               CUTB_LAYOUT_KN_PLANES (K % 128 == 0; above four rows what CUTB_VARIANT_AUTO picks there) */
   CUTB_VARIANT_GEMV_PLANES = 3 /* decode over CUTB_LAYOUT_KN_PLANES (the reference's run-time layout), M <= 4: coalesced
                                   column groups, K split over warps and blocks */
 };
