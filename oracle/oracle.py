@@ -31,7 +31,8 @@ def build(force: bool = False) -> None:
         subprocess.run(["make", "-C", _HERE, "_build/liboracle.so"], check=True, capture_output=True)
     # the reference helpers are rebuilt only where a checkout of the reference is named (REF_ROOT in the
     # environment, else the place this build keeps it); elsewhere the prebuilt files are used as they are
-    ref_root = os.environ.get("REF_ROOT") or ("/root/reference" if os.path.isdir("/root/reference") else "")
+    sibling = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")  # a checkout next to this repository
+    ref_root = os.environ.get("REF_ROOT") or (sibling if os.path.isdir(os.path.join(sibling, "interface", "loader", "gguf")) else "")
     subprocess.run(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root}"], check=True, capture_output=True)
     # the reference's own CUDA matmul kernels as cubins (NVRTC, as its backend compiles them; no GPU needed)
     if ref_root:
