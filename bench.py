@@ -290,6 +290,36 @@ def reference_cuda_measurement() -> dict | None:
         us = a.elapsed_time(b) * 1e3 / 5
         out["configs[2]_shape_q4_0_512x4096x14336"] = {"kernel": "MatMulQ4CoopMatTiled", "us_per_launch": us,
                                                        "TFLOP/s": 2.0 * m * k * n / us / 1e6, "rel_l2_vs_block_gemm": rel}
+    # decode attention at the configs[3] geometry (32 query / 8 KV heads of 128, fp16 cache, 515 populated rows)
+    if ref_cuda.have("Attention_f16"):
+        nh, nkv, hd, rows, seq = 32, 8, 128, 2048, 515
+        gen = torch.Generator(device=dev).manual_seed(7)
+        q = torch.randn(nh * hd, generator=gen, device=dev)
+        kc = torch.randn((rows, nkv * hd), generator=gen, device=dev).half()
+        vc = torch.randn((rows, nkv * hd), generator=gen, device=dev).half()
+        params = torch.tensor([seq - 1, seq], dtype=torch.int32, device=dev)
+        o_ref = torch.zeros(nh * hd, device=dev)
+        ws = ops.attention_workspace(nh, nkv, hd, rows, dev)
+        scale = 1.0 / float(np.sqrt(np.float32(hd)))
+
+        def time_us(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(50):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) * 1e3 / 50
+
+        us_ref = time_us(lambda: ref_cuda.attention(True, q, kc, vc, params, o_ref, nh, nkv, hd, scale))
+        o_own = ops.attention_decode(q, kc, vc, params, nh, nkv, hd, ws, scale=scale)
+        us_own = time_us(lambda: ops.attention_decode(q, kc, vc, params, nh, nkv, hd, ws, out=o_own, scale=scale))
+        out["configs[3]_decode_attention_515_rows"] = {"kernel": "Attention (Float16 cache)", "us_per_launch": us_ref,
+                                                       "this_library_us_per_launch": us_own,
+                                                       "max_abs_diff": float((o_own - o_ref).abs().max())}
     return out or None
 
 

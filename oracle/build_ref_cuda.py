@@ -1,4 +1,4 @@
-"""Compiles the reference's own CUDA matmul kernels for sm_100a, as its backend does at run time.
+"""Compiles the reference's own CUDA kernels of this path for sm_100a, as its backend does at run time.
 
 TEST / BASELINE INFRASTRUCTURE ONLY.  The reference hands `#include "cut_cuda_prelude.cuh"` + a kernel's .cu text
 to NVRTC with its headers by name and `--std=c++17` (core/backends/cuda/CudaContainers.cpp:94-222).  This script
@@ -13,10 +13,23 @@ from __future__ import annotations
 import os
 import sys
 
-KERNELS = ["MatMulQ4GemvKPar8", "MatMulQ8GemvKPar8", "MatMulQ4CoopMatTiled", "MatMulQ8CoopMatTiled"]
+# cubin name -> (kernel source in the reference tree, extra -D options: the per-variant defines of its kernel table)
+SOURCES = {
+    "MatMulQ4GemvKPar8": ("operators/impl/matmul/MatMulQ4GemvKPar8.cu", []),
+    "MatMulQ8GemvKPar8": ("operators/impl/matmul/MatMulQ8GemvKPar8.cu", []),
+    "MatMulQ4CoopMatTiled": ("operators/impl/matmul/MatMulQ4CoopMatTiled.cu", []),
+    "MatMulQ8CoopMatTiled": ("operators/impl/matmul/MatMulQ8CoopMatTiled.cu", []),
+    "Attention": ("operators/impl/attention/Attention.cu", []),
+    "Attention_f16": ("operators/impl/attention/Attention.cu", ["-DCUT_DTYPE_INPUT_IS_HALF=1"]),
+    "FusedRoPEKVWrite": ("operators/impl/attention/FusedRoPEKVWrite.cu", []),
+    "FusedRoPEKVWrite_f16": ("operators/impl/attention/FusedRoPEKVWrite.cu", ["-DCUT_DTYPE_INPUT_IS_HALF=1"]),
+    "DequantQ4K": ("operators/impl/dequant/DequantQ4K.cu", []),
+}
+KERNELS = list(SOURCES)
 HEADERS = {"cut_cuda_prelude.cuh": "operators/runtime/cuda/cut_cuda_prelude.cuh", "ComputeOpsShared.h": "operators/runtime/ComputeOpsShared.h",
            "MatMulCommon.cuh": "operators/impl/matmul/MatMulCommon.cuh", "MatMulCoopMatCommon.cuh": "operators/impl/matmul/MatMulCoopMatCommon.cuh",
-           "MatMulQ4Common.cuh": "operators/impl/matmul/MatMulQ4Common.cuh", "MatMulQ8Common.cuh": "operators/impl/matmul/MatMulQ8Common.cuh"}
+           "MatMulQ4Common.cuh": "operators/impl/matmul/MatMulQ4Common.cuh", "MatMulQ8Common.cuh": "operators/impl/matmul/MatMulQ8Common.cuh",
+           "AttentionCommon.cuh": "operators/impl/attention/AttentionCommon.cuh", "DequantCommon.cuh": "operators/impl/dequant/DequantCommon.cuh"}
 
 
 def build(ref_root: str, out_dir: str) -> list[str]:
@@ -34,12 +47,14 @@ def build(ref_root: str, out_dir: str) -> list[str]:
     srcs = [rd(p) for p in HEADERS.values()]
     written = []
     for k in KERNELS:
-        src = b'#include "cut_cuda_prelude.cuh"\n' + rd(f"operators/impl/matmul/{k}.cu")
+        rel, defines = SOURCES[k]
+        src = b'#include "cut_cuda_prelude.cuh"\n' + rd(rel)
         err, prog = nvrtc.nvrtcCreateProgram(src, b"cut_kernel.cu", len(names), srcs, names)
         if int(err) != 0:
             print(f"build_ref_cuda: nvrtcCreateProgram failed for {k}: {err}", file=sys.stderr)
             continue
-        (res,) = nvrtc.nvrtcCompileProgram(prog, len(opts), opts)
+        kopts = opts + [d.encode() for d in defines]
+        (res,) = nvrtc.nvrtcCompileProgram(prog, len(kopts), kopts)
         if int(res) != 0:
             _, n = nvrtc.nvrtcGetProgramLogSize(prog)
             log = b" " * n

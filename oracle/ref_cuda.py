@@ -1,4 +1,4 @@
-"""Launches the reference's own CUDA matmul kernels (cubins built by build_ref_cuda.py) on torch CUDA tensors.
+"""Launches the reference's own CUDA kernels of this path (cubins built by build_ref_cuda.py) on torch CUDA tensors.
 
 TEST / BASELINE INFRASTRUCTURE ONLY: the GPU-side checker of the plane-layout kernels and the reference-GPU
 baseline of bench.py.  Each kernel is the reference's `cut_main(dataA, packedB, scalesB, dataD, dataC, push)` with
@@ -67,3 +67,52 @@ def launch(kernel: str, A, B, S, Cout, M: int, K: int, N: int, *, stride_a: int,
     (err,) = driver.cuLaunchKernel(fn, *grid, *block, 0, torch.cuda.current_stream().cuda_stream, C.addressof(args), 0)
     if int(err) != 0:
         raise RuntimeError(f"cuLaunchKernel({kernel}): {err}")
+
+
+def _launch_raw(kernel: str, grid, block, tensors, push: C.Structure) -> None:
+    import torch
+    from cuda.bindings import driver
+
+    fn = _function(kernel)
+    ptrs = [C.c_void_p(t.data_ptr()) for t in tensors]
+    args = (C.c_void_p * (len(ptrs) + 1))(*[C.addressof(p) for p in ptrs], C.addressof(push))
+    (err,) = driver.cuLaunchKernel(fn, *grid, *block, 0, torch.cuda.current_stream().cuda_stream, C.addressof(args), 0)
+    if int(err) != 0:
+        raise RuntimeError(f"cuLaunchKernel({kernel}): {err}")
+
+
+class _AttnPush(C.Structure):
+    _fields_ = [("nHeads", C.c_uint32), ("nKvHeads", C.c_uint32), ("headDim", C.c_uint32), ("kvDim", C.c_uint32),
+                ("alignedKvDim", C.c_uint32), ("nRep", C.c_uint32), ("scale", C.c_float)]
+
+
+def attention(kv_half: bool, q, k_cache, v_cache, params, out, n_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> None:
+    """The reference's decode attention (operators/impl/attention/Attention.cu: one 256-thread block per query head,
+    scores in a 2048-entry shared array, so seqLen <= 2048 and head_dim <= 128).  Caches are [rows, alignedKvDim]."""
+    if head_dim > 128:
+        raise ValueError("the reference kernel holds one query head of at most 128 elements")
+    kv_dim = n_kv_heads * head_dim
+    push = _AttnPush(n_heads, n_kv_heads, head_dim, kv_dim, k_cache.stride(0), n_heads // n_kv_heads, scale)
+    _launch_raw("Attention_f16" if kv_half else "Attention", (n_heads, 1, 1), (256, 1, 1), (q, k_cache, v_cache, params, out), push)
+
+
+class _RopePush(C.Structure):
+    _fields_ = [("qDim", C.c_uint32), ("kvDim", C.c_uint32), ("headDim", C.c_uint32), ("halfDim", C.c_uint32), ("alignedKvDim", C.c_uint32)]
+
+
+def rope_kv_write(kv_half: bool, q, k, v, params, cos_t, sin_t, k_cache, v_cache, q_roped, q_dim: int, kv_dim: int, head_dim: int) -> None:
+    """The reference's fused RoPE + KV-cache write (operators/impl/attention/FusedRoPEKVWrite.cu: one thread per element
+    of q, k and v, 256 per block)."""
+    push = _RopePush(q_dim, kv_dim, head_dim, head_dim // 2, k_cache.stride(0))
+    total = q_dim + 2 * kv_dim
+    _launch_raw("FusedRoPEKVWrite_f16" if kv_half else "FusedRoPEKVWrite", ((total + 255) // 256, 1, 1), (256, 1, 1),
+                (q, k, v, params, cos_t, sin_t, k_cache, v_cache, q_roped), push)
+
+
+class _DequantPush(C.Structure):
+    _fields_ = [("rows", C.c_uint32), ("cols", C.c_uint32), ("outputStride", C.c_uint32)]
+
+
+def dequant_q4k(raw, out, rows: int, cols: int) -> None:
+    """The reference's Q4_K dequant operator (operators/impl/dequant/DequantQ4K.cu: 256 x 1 threads, one element each)."""
+    _launch_raw("DequantQ4K", ((cols + 255) // 256, rows, 1), (256, 1, 1), (raw, out), _DequantPush(rows, cols, out.stride(0)))

@@ -111,3 +111,98 @@ def test_plane_gemm_against_the_reference_tensor_core_kernel(q4, affine, kernel,
         torch.cuda.synchronize()
         assert rel(ref_out.cpu().numpy().astype(np.float64), want) <= 3e-3
         assert rel(ours.cpu().numpy().astype(np.float64), ref_out.cpu().numpy().astype(np.float64)) <= 1e-3
+
+
+def _rope_tables(max_seq, hd):
+    half = hd // 2
+    freq = (np.float32(1.0) / np.power(np.float32(10000.0), (2 * np.arange(half, dtype=np.float32)) / np.float32(hd)))
+    ang = np.arange(max_seq, dtype=np.float32)[:, None] * freq.astype(np.float32)[None, :]
+    return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+
+
+@pytest.mark.parametrize("kv", [np.float32, np.float16])
+@pytest.mark.parametrize("n_heads,n_kv,hd,max_seq,seq", [(32, 8, 128, 2048, 515), (32, 8, 128, 2048, 2048), (4, 2, 8, 16, 7), (6, 3, 66, 64, 40),
+                                                         (8, 8, 64, 256, 1)])
+def test_attention_against_the_reference_cuda_kernel(kv, n_heads, n_kv, hd, max_seq, seq):
+    """cutb_attention_decode (cluster or general kernel, whichever the shape selects) against the reference's own
+    Attention.cu on the same caches; both within the usual tolerance of the float64 checker."""
+    import torch
+
+    from cut_b200 import ops
+
+    name = "Attention_f16" if kv == np.float16 else "Attention"
+    if not ref_cuda.have(name):
+        pytest.skip("reference cubins not built")
+    rng = np.random.default_rng(seq + hd)
+    kv_dim = n_kv * hd
+    ld = (kv_dim + 3) // 4 * 4
+    q = rng.normal(0, 1, n_heads * hd).astype(np.float32)
+    kc = rng.normal(0, 1, (max_seq, ld)).astype(kv)
+    vc = rng.normal(0, 1, (max_seq, ld)).astype(kv)
+    dq, dkc, dvc = (torch.from_numpy(x).cuda() for x in (q, kc, vc))
+    params = torch.tensor([seq - 1, seq], dtype=torch.int32, device="cuda")
+    scale = 1.0 / float(np.sqrt(np.float32(hd)))
+    ref_out = torch.zeros(n_heads * hd, dtype=torch.float32, device="cuda")
+    ref_cuda.attention(kv == np.float16, dq, dkc, dvc, params, ref_out, n_heads, n_kv, hd, scale)
+    ws = ops.attention_workspace(n_heads, n_kv, hd, max_seq, "cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.attention_decode(dq, dkc, dvc, params, n_heads, n_kv, hd, ws, scale=scale, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = O.attention(q, kc, vc, seq, n_heads, n_kv, hd)
+    g, r = got.cpu().numpy(), ref_out.cpu().numpy()
+    assert np.all(np.abs(r - want) <= 1e-5 + 1e-4 * np.abs(want))   # the reference's kernel is what the checker restates
+    assert np.all(np.abs(g - want) <= 1e-5 + 1e-4 * np.abs(want))
+    assert np.all(np.abs(g - r) <= 2e-5 + 2e-4 * np.abs(r))
+
+
+@pytest.mark.parametrize("kv", [np.float32, np.float16])
+@pytest.mark.parametrize("n_heads,n_kv,hd,max_seq,pos", [(32, 8, 128, 600, 511), (4, 2, 8, 16, 0), (6, 3, 66, 64, 9)])
+def test_rope_cache_write_against_the_reference_cuda_kernel(kv, n_heads, n_kv, hd, max_seq, pos):
+    """cutb_rope_kv_write against the reference's FusedRoPEKVWrite.cu: the rotated query and the cache rows.  This
+    library rounds the two products of a rotation separately (what the CPU checker and plain C give); NVRTC contracts
+    the reference's `a * cos - b * sin` into a fused multiply-add, so the two differ by an ulp now and then."""
+    import torch
+
+    from cut_b200 import ops
+
+    name = "FusedRoPEKVWrite_f16" if kv == np.float16 else "FusedRoPEKVWrite"
+    if not ref_cuda.have(name):
+        pytest.skip("reference cubins not built")
+    rng = np.random.default_rng(pos + hd)
+    q_dim, kv_dim = n_heads * hd, n_kv * hd
+    ld = (kv_dim + 3) // 4 * 4
+    cos_t, sin_t = _rope_tables(max_seq, hd)
+    q, k, v = (rng.normal(0, 1, n).astype(np.float32) for n in (q_dim, kv_dim, kv_dim))
+    kc0, vc0 = rng.normal(0, 1, (max_seq, ld)).astype(kv), rng.normal(0, 1, (max_seq, ld)).astype(kv)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    params = torch.tensor([pos, pos + 1], dtype=torch.int32, device="cuda")
+    r_kc, r_vc, r_q = dev(kc0), dev(vc0), torch.zeros(q_dim, dtype=torch.float32, device="cuda")
+    ref_cuda.rope_kv_write(kv == np.float16, dev(q), dev(k), dev(v), params, dev(cos_t), dev(sin_t), r_kc, r_vc, r_q, q_dim, kv_dim, hd)
+    o_kc, o_vc = dev(kc0), dev(vc0)
+    o_q = ops.rope_kv_write(dev(q), dev(k), dev(v), params, dev(cos_t), dev(sin_t), o_kc, o_vc, hd)
+    torch.cuda.synchronize()
+    assert np.allclose(o_q.cpu().numpy(), r_q.cpu().numpy(), rtol=1e-6, atol=1e-6)
+    tol = dict(rtol=2e-3, atol=2e-3) if kv == np.float16 else dict(rtol=1e-6, atol=1e-6)
+    assert np.allclose(o_kc.float().cpu().numpy(), r_kc.float().cpu().numpy(), **tol)
+    assert torch.equal(o_vc, r_vc)                                    # v is stored as it is: identical
+    other = np.arange(max_seq) != pos
+    assert np.array_equal(o_kc.cpu().numpy()[other], kc0[other])      # only row pos is touched
+
+
+def test_q4k_dequant_against_the_reference_cuda_kernel():
+    """cutb_dequant (Q4_K) against the reference's DequantQ4K.cu, bit for bit."""
+    import torch
+
+    from cut_b200 import _lib as L
+    from cut_b200 import ops, synth
+
+    if not ref_cuda.have("DequantQ4K"):
+        pytest.skip("reference cubins not built")
+    rows, cols = 37, 1024
+    raw = torch.from_numpy(synth.make_weights(synth.Q4_K, rows, cols, seed=12)).cuda()
+    ref_out = torch.zeros((rows, cols), dtype=torch.float32, device="cuda")
+    ref_cuda.dequant_q4k(raw, ref_out, rows, cols)
+    ours = ops.dequantize(raw, L.Q4_K, rows, cols)
+    torch.cuda.synchronize()
+    assert np.array_equal(ours.cpu().numpy().view(np.uint32), ref_out.cpu().numpy().view(np.uint32))
