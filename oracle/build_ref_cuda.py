@@ -24,12 +24,22 @@ SOURCES = {
     "FusedRoPEKVWrite": ("operators/impl/attention/FusedRoPEKVWrite.cu", []),
     "FusedRoPEKVWrite_f16": ("operators/impl/attention/FusedRoPEKVWrite.cu", ["-DCUT_DTYPE_INPUT_IS_HALF=1"]),
     "DequantQ4K": ("operators/impl/dequant/DequantQ4K.cu", []),
+    "DequantQ5K": ("operators/impl/dequant/DequantQ5K.cu", []),
+    "DequantQ6K": ("operators/impl/dequant/DequantQ6K.cu", []),
+    "DequantBF16": ("operators/impl/dequant/DequantBF16.cu", []),
+    "RMSNorm": ("operators/impl/rmsnorm/RMSNorm.cu", []),
+    "ReduceArgmax": ("operators/impl/reduce/ReduceArg.cu", []),
+    "BatchedKVCacheWrite": ("operators/impl/attention/BatchedKVCacheWrite.cu", []),
+    "BatchedKVCacheWrite_f16": ("operators/impl/attention/BatchedKVCacheWrite.cu", ["-DCUT_DTYPE_INPUT_IS_HALF=1"]),
+    "BatchedAttentionReadCache": ("operators/impl/attention/BatchedAttentionReadCache.cu", []),
+    "BatchedAttentionReadCache_f16": ("operators/impl/attention/BatchedAttentionReadCache.cu", ["-DCUT_DTYPE_INPUT_IS_HALF=1"]),
 }
 KERNELS = list(SOURCES)
 HEADERS = {"cut_cuda_prelude.cuh": "operators/runtime/cuda/cut_cuda_prelude.cuh", "ComputeOpsShared.h": "operators/runtime/ComputeOpsShared.h",
            "MatMulCommon.cuh": "operators/impl/matmul/MatMulCommon.cuh", "MatMulCoopMatCommon.cuh": "operators/impl/matmul/MatMulCoopMatCommon.cuh",
            "MatMulQ4Common.cuh": "operators/impl/matmul/MatMulQ4Common.cuh", "MatMulQ8Common.cuh": "operators/impl/matmul/MatMulQ8Common.cuh",
-           "AttentionCommon.cuh": "operators/impl/attention/AttentionCommon.cuh", "DequantCommon.cuh": "operators/impl/dequant/DequantCommon.cuh"}
+           "AttentionCommon.cuh": "operators/impl/attention/AttentionCommon.cuh", "DequantCommon.cuh": "operators/impl/dequant/DequantCommon.cuh",
+           "RMSNormCommon.cuh": "operators/impl/rmsnorm/RMSNormCommon.cuh"}
 
 
 def build(ref_root: str, out_dir: str) -> list[str]:

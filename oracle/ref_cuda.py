@@ -113,6 +113,58 @@ class _DequantPush(C.Structure):
     _fields_ = [("rows", C.c_uint32), ("cols", C.c_uint32), ("outputStride", C.c_uint32)]
 
 
+def dequant(kernel: str, raw, out, rows: int, cols: int) -> None:
+    """The reference's dequant operators (operators/impl/dequant/DequantQ4K.cu, DequantQ5K.cu, DequantQ6K.cu, DequantBF16.cu:
+    256 x 1 threads, one element each)."""
+    _launch_raw(kernel, ((cols + 255) // 256, rows, 1), (256, 1, 1), (raw, out), _DequantPush(rows, cols, out.stride(0)))
+
+
 def dequant_q4k(raw, out, rows: int, cols: int) -> None:
-    """The reference's Q4_K dequant operator (operators/impl/dequant/DequantQ4K.cu: 256 x 1 threads, one element each)."""
-    _launch_raw("DequantQ4K", ((cols + 255) // 256, rows, 1), (256, 1, 1), (raw, out), _DequantPush(rows, cols, out.stride(0)))
+    dequant("DequantQ4K", raw, out, rows, cols)
+
+
+class _RmsPush(C.Structure):
+    _fields_ = [("dim", C.c_uint32), ("alignedDim", C.c_uint32), ("eps", C.c_float)]
+
+
+def rmsnorm(x, weight, out, rows: int, dim: int, eps: float) -> None:
+    """The reference's RMSNorm (operators/impl/rmsnorm/RMSNorm.cu: one 256-thread block per row, fp32)."""
+    _launch_raw("RMSNorm", (1, rows, 1), (256, 1, 1), (x, weight, out), _RmsPush(dim, x.stride(0) if x.dim() == 2 else (dim + 3) // 4 * 4, eps))
+
+
+class _ArgPush(C.Structure):
+    _fields_ = [("numElements", C.c_uint32)]
+
+
+def argmax(v, out, n: int) -> None:
+    """The reference's arg-max (operators/impl/reduce/ReduceArg.cu: one block of 256 threads, strided scan + tree)."""
+    _launch_raw("ReduceArgmax", (1, 1, 1), (256, 1, 1), (v, out), _ArgPush(n))
+
+
+class _BkvPush(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("batchSize", "kvDim", "alignedKvDim", "headDim", "halfDim", "kStride", "vStride", "kOffset", "vOffset")]
+
+
+def batched_kv_write(kv_half: bool, k_in, v_in, k_cache, v_cache, positions, cos_t, sin_t, batch: int, kv_dim: int, head_dim: int,
+                     k_stride: int, v_stride: int, k_offset: int, v_offset: int) -> None:
+    """The reference's batched RoPE + cache write (operators/impl/attention/BatchedKVCacheWrite.cu: one block per token)."""
+    push = _BkvPush(batch, kv_dim, k_cache.stride(0), head_dim, head_dim // 2, k_stride, v_stride, k_offset, v_offset)
+    _launch_raw("BatchedKVCacheWrite_f16" if kv_half else "BatchedKVCacheWrite", (1, batch, 1), (256, 1, 1),
+                (k_in, v_in, k_cache, v_cache, positions, cos_t, sin_t), push)
+
+
+class _BattPush(C.Structure):
+    _fields_ = [("batchSize", C.c_uint32), ("nHeads", C.c_uint32), ("nKvHeads", C.c_uint32), ("headDim", C.c_uint32),
+                ("alignedKvDim", C.c_uint32), ("nRep", C.c_uint32), ("scale", C.c_float), ("halfDim", C.c_uint32),
+                ("qStride", C.c_uint32), ("qOffset", C.c_uint32)]
+
+
+def batched_attention(kv_half: bool, q_in, k_cache, v_cache, positions, cos_t, sin_t, out, batch: int, n_heads: int, n_kv_heads: int,
+                      head_dim: int, scale: float, q_stride: int, q_offset: int) -> None:
+    """The reference's batched prefill attention (operators/impl/attention/BatchedAttentionReadCache.cu: one block per
+    (query head, token), positions < 2048, head_dim <= 128; output [batch, nHeads * headDim])."""
+    if head_dim > 128:
+        raise ValueError("the reference kernel holds one query head of at most 128 elements")
+    push = _BattPush(batch, n_heads, n_kv_heads, head_dim, k_cache.stride(0), n_heads // n_kv_heads, scale, head_dim // 2, q_stride, q_offset)
+    _launch_raw("BatchedAttentionReadCache_f16" if kv_half else "BatchedAttentionReadCache", (n_heads, batch, 1), (256, 1, 1),
+                (q_in, k_cache, v_cache, positions, cos_t, sin_t, out), push)
