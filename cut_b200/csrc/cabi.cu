@@ -194,8 +194,9 @@ int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
   }
   switch (v) {
     case CUTB_VARIANT_GEMV_MMA:
-      if (!qgemv_blocks_supported(*desc)) {
-        set_last_error("qmatmul: variant %s needs GGUF blocks, K %% 256 == 0, 16-byte aligned W and M <= 16 (fp16) / 8 (fp32)",
+      if (!qgemv_blocks_supported(*desc) && !qgemv_blocks_supported_in_groups(*desc)) {
+        set_last_error("qmatmul: variant %s needs GGUF blocks, K %% 256 == 0, 16-byte aligned W and M <= 64 (fp16) / 32 (fp32) "
+                       "(beyond 16 / 8 rows in groups, without paired rows)",
                        cutb_variant_name(v));
         return CUTB_ERR_UNSUPPORTED;
       }

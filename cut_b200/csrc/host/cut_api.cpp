@@ -1031,7 +1031,7 @@ bool VariantSelector::loadFromString(const std::string &content) {
 int VariantSelector::select(const std::string &op, const std::vector<uint32_t> &shape, int defaultVariant,
                             const std::string &backend) const {
   if (!loaded_) return defaultVariant;
-  auto eval = [&shape](const OperatorRules &r) {
+  auto eval = [&shape, defaultVariant](const OperatorRules &r) {
     int64_t total = 1;
     for (uint32_t d : shape) total *= d;
     for (const Rule &rule : r.rules) {
@@ -1045,7 +1045,9 @@ int VariantSelector::select(const std::string &op, const std::vector<uint32_t> &
       const bool maxOk = rule.totalElementsMax < 0 || total < rule.totalElementsMax;
       if (shapeOk && minOk && maxOk) return rule.variant;  // first match wins
     }
-    return r.defaultVariant;
+    // (a negative default_variant in the file leaves the caller's own choice in place: for the quantized matmuls
+    // that choice depends on the shape, so one fixed fallback index would be wrong for most of them)
+    return r.defaultVariant < 0 ? defaultVariant : r.defaultVariant;
   };
   if (!backend.empty())
     if (auto it = operators_.find(op + "@" + backend); it != operators_.end()) return eval(it->second);

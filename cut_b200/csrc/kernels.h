@@ -12,6 +12,8 @@ int check_qmatmul_desc(const cutb_qmatmul_desc *d);
 
 // Decode mat-vec over GGUF blocks (bulk-copy ring + warp MMA).
 bool qgemv_blocks_supported(const cutb_qmatmul_desc &d);
+// up to four row groups of the mat-vec (a forced variant only; CUTB_VARIANT_AUTO stays within one group)
+bool qgemv_blocks_supported_in_groups(const cutb_qmatmul_desc &d);
 uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d);
 // `scatter` (optional): store the output slice into every rank's full output instead of d.C.
 int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const cutb_peer_scatter *scatter = nullptr);

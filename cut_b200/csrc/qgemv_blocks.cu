@@ -1205,7 +1205,25 @@ bool qgemv_blocks_supported(const cutb_qmatmul_desc &d) {
   return true;
 }
 
+// A forced CUTB_VARIANT_GEMV_MMA also takes up to four groups of 16 virtual rows: the weights are streamed once per
+// group, which still beats the tensor-core GEMM's fixed cost on narrow weights (a row shard of a projection, a
+// 4096-row projection at batch 32).  CUTB_VARIANT_AUTO never picks this; tuning rules do where it measured faster.
+uint32_t qgemv_rows_per_group(const cutb_qmatmul_desc &d) { return gv_amode(d) == GV_A_F32_TWO ? 8u : 16u; }
+
+bool qgemv_blocks_supported_in_groups(const cutb_qmatmul_desc &d) {
+  if (d.M == 0) return false;
+  cutb_qmatmul_desc one = d;
+  one.M = d.M < qgemv_rows_per_group(d) ? d.M : qgemv_rows_per_group(d);
+  return d.M <= 4 * qgemv_rows_per_group(d) && qgemv_blocks_supported(one) && !(d.flags & CUTB_FLAG_GLU_PAIRS);
+}
+
 uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d) {
+  const uint32_t per = qgemv_rows_per_group(d);
+  if (d.M > per && qgemv_blocks_supported_in_groups(d)) {  // the groups run one after the other on one scratch block
+    cutb_qmatmul_desc one = d;
+    one.M = per;
+    return qgemv_blocks_workspace(one);
+  }
   DeviceInfo di;
   if (get_device_info(&di) != CUTB_OK) {
     // no device: report the bound for a 148-SM part so callers can size ahead of time
@@ -1218,6 +1236,19 @@ uint64_t qgemv_blocks_workspace(const cutb_qmatmul_desc &d) {
 }
 
 int qgemv_blocks_launch(const cutb_qmatmul_desc &d, cudaStream_t stream, const cutb_peer_scatter *sc) {
+  const uint32_t per = qgemv_rows_per_group(d);
+  if (d.M > per && !sc && qgemv_blocks_supported_in_groups(d)) {
+    const size_t a_elem = d.a_dtype == CUTB_F32 ? 4 : 2;
+    for (uint32_t m0 = 0; m0 < d.M; m0 += per) {
+      cutb_qmatmul_desc g = d;
+      g.M = d.M - m0 < per ? d.M - m0 : per;
+      g.A = reinterpret_cast<const uint8_t *>(d.A) + (size_t)m0 * d.lda * a_elem;
+      g.C = d.C + (size_t)m0 * d.ldc;
+      if (d.D) g.D = d.D + (size_t)m0 * d.ldd;
+      if (int rc = qgemv_blocks_launch(g, stream, nullptr)) return rc;
+    }
+    return CUTB_OK;
+  }
   DeviceInfo di;
   if (int rc = get_device_info(&di)) return rc;
   GvPlan pl;

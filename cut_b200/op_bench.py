@@ -31,7 +31,11 @@ import numpy as np
 REFERENCE_SHAPES = [(1, 2048, 2048), (1, 4096, 4096), (1, 4096, 11008), (8, 2048, 2048), (8, 2048, 5632), (32, 2048, 2048),
                     (32, 2048, 5632), (128, 2048, 2048), (128, 2048, 5632), (512, 2048, 2048), (512, 2048, 5632)]
 EXTRA_SHAPES = [(8, 4096, 11008), (16, 4096, 11008), (32, 4096, 11008), (1, 4096, 14336), (512, 4096, 14336), (1, 8192, 8192),
-                (8, 8192, 8192), (16, 8192, 8192), (32, 8192, 8192), (1, 28672, 8192), (8, 28672, 8192)]
+                (8, 8192, 8192), (16, 8192, 8192), (32, 8192, 8192), (1, 28672, 8192), (8, 28672, 8192),
+                # batch 32 and 64 on the 70B projections and on their row shards over 8 GPUs: where the mat-vec in row groups
+                # can beat the GEMM's fixed cost
+                (32, 8192, 28672), (32, 28672, 8192), (32, 8192, 1024), (32, 8192, 3584), (32, 28672, 1024), (64, 8192, 1024),
+                (32, 4096, 4096), (24, 4096, 11008)]
 BLOCK_VARIANT_NAMES = {0: "QMatMulGeneric", 1: "QGemvBulkMma", 2: "QGemmTcgen05"}
 PLANE_VARIANT_NAMES = {0: "QMatMulGeneric", 3: "QGemvPlanes"}
 OPERATOR = "MatMulQBlocks"
@@ -48,9 +52,10 @@ def builtin_block_variant(M: int, K: int, N: int, a_is_f32: bool) -> int:
     return 0
 
 
-def derive_rules(records: list[dict], key: str = "blocks_q4_0") -> dict:
+def derive_rules(records: list[dict], key: str = "blocks_q4_0", min_gain: float = 0.10) -> dict:
     """tuning_data.json content from op_bench records: one exact-shape rule for every shape whose fastest
-    variant under `key` differs from the built-in choice (fp16 activations, as the records are timed)."""
+    variant under `key` differs from the built-in choice (fp16 activations, as the records are timed) and beats it
+    by at least `min_gain` (a rule is not worth a run-to-run wobble)."""
     rules = []
     for rec in records:
         rows = rec.get(key) or []
@@ -58,10 +63,16 @@ def derive_rules(records: list[dict], key: str = "blocks_q4_0") -> dict:
             continue
         best = min(rows, key=lambda r: r["median_us"])
         M, K, N = rec["shape"]
-        if best["variant"] != builtin_block_variant(M, K, N, False):
+        builtin = builtin_block_variant(M, K, N, False)
+        if best["variant"] != builtin:
+            base = next((r["median_us"] for r in rows if r["variant"] == builtin), None)
+            if base is not None and best["median_us"] > (1.0 - min_gain) * base:
+                continue
+            was = f" (built-in {BLOCK_VARIANT_NAMES[builtin]} {base:.2f} us)" if base is not None else ""
             rules.append({"variant": best["variant"], "conditions": {"shape": [M, K, N]},
-                          "comment": f"{best['name']} {best['median_us']:.2f} us"})
-    return {"operators": {OPERATOR: {"backends": {"cuda": {"default_variant": 1, "rules": rules}}}}}
+                          "comment": f"{best['name']} {best['median_us']:.2f} us{was}"})
+    # default_variant -1: shapes without a rule keep the operator's built-in choice (it depends on the shape)
+    return {"operators": {OPERATOR: {"backends": {"cuda": {"default_variant": -1, "rules": rules}}}}}
 
 
 def _time_graph(torch, launch_all, launches: int, rounds: int = 5) -> float:

@@ -74,7 +74,9 @@ enum { CUTB_FUSION_NONE = 0, CUTB_FUSION_UNARY = 1, CUTB_FUSION_BINARY = 2 };
 enum {
   CUTB_VARIANT_AUTO = -1,
   CUTB_VARIANT_GENERIC = 0, /* any shape, SIMT, exact fp32 dequant + FMA */
-  CUTB_VARIANT_GEMV_MMA = 1, /* decode: bulk-copy ring + int8 warp MMA, M <= 16 (fp16 A) / 8 (fp32 A) */
+  CUTB_VARIANT_GEMV_MMA = 1, /* decode: bulk-copy ring + int8 warp MMA, M <= 16 (fp16 A) / 8 (fp32 A); when forced, up to
+                                four such row groups one after the other (M <= 64 / 32): faster than the GEMM on narrow
+                                weights, which is what tuning rules are for */
   CUTB_VARIANT_GEMM_TC = 2, /* prefill: tcgen05 tensor-core GEMM, accumulators in tensor memory; its operands are fp16
                                (see the operand-range note at cutb_qmatmul_desc).  GGUF blocks (K % 256 == 0) and
                                CUTB_LAYOUT_KN_PLANES (K % 128 == 0; above four rows what CUTB_VARIANT_AUTO picks there) */

@@ -428,6 +428,57 @@ void resultCopiesFollowReplaysAndWrites() {
   CHECK(relErr(A1) <= 1e-3);
 }
 
+// A tuning rule (runtime/VariantSelector.cpp:283-428) sends a 32-token matmul over a narrow weight to the decode
+// mat-vec, which then runs two groups of 16 rows; without the rule the same call takes the tensor-core GEMM.  Both
+// against the checker.
+void tunedVariantRunsRowGroups() {
+  const uint32_t M = 32, K = 1024, N = 264;
+  std::vector<uint8_t> raw((size_t)N * (K / 32) * 18);
+  std::mt19937 gen(31);
+  for (auto &b : raw) b = (uint8_t)gen();
+  for (size_t blk = 0; blk < raw.size() / 18; ++blk) { uint16_t d = 0x2000; std::memcpy(&raw[blk * 18], &d, 2); }
+  std::vector<float> A((size_t)M * K), want((size_t)M * N), got((size_t)M * N);
+  for (auto &a : A) a = (float)((int)(gen() % 17) - 8) / 8.0f;
+  orc_qmatmul_blocks(1, A.data(), raw.data(), want.data(), nullptr, M, K, N, K, N, 0, 0, 0, 0);
+  auto tA = rt->createTensor({M, K}, DataType::Float16, nullptr);
+  {  // fp16 activations: 32 rows are two groups of 16
+    std::vector<uint16_t> h(A.size());
+    for (size_t i = 0; i < A.size(); ++i) {  // multiples of 1/8 up to 1: exact in fp16
+      const float v = A[i];
+      uint32_t bits;
+      std::memcpy(&bits, &v, 4);
+      const uint32_t sign = (bits >> 16) & 0x8000u, exp = (bits >> 23) & 0xFFu, man = bits & 0x7FFFFFu;
+      h[i] = (uint16_t)(exp == 0 ? sign : sign | ((exp - 112u) << 10) | (man >> 13));
+    }
+    rt->copyToTensor(tA, h.data(), h.size() * 2);
+  }
+  auto tW = rt->createTensor({(uint32_t)raw.size()}, DataType::Int8, raw.data());
+  auto relErr = [&]() {
+    double num = 0, den = 0;
+    for (size_t i = 0; i < got.size(); ++i) num += (got[i] - want[i]) * (double)(got[i] - want[i]), den += want[i] * (double)want[i];
+    return std::sqrt(num / den);
+  };
+  auto &vs = VariantSelector::instance();
+  vs.clear();
+  {
+    MatMulOpNode n0(rt->store(), tA, tW, DequantFormat::Q4_0, N);
+    CHECK(*n0.spec() == 2);  // built-in: the GEMM
+  }
+  CHECK(vs.loadFromString(R"({"operators": {"MatMulQBlocks": {"backends": {"cuda": {"default_variant": 1,
+        "rules": [{"variant": 1, "conditions": {"shape": [32, 1024, 264]}}]}}}}})"));
+  {
+    MatMulOpNode n1(rt->store(), tA, tW, DequantFormat::Q4_0, N);
+    CHECK(*n1.spec() == 1);  // the rule: mat-vec in row groups
+  }
+  auto tC = rt->ops().matmulBlocks(tA, tW, DequantFormat::Q4_0, N);
+  rt->copyFromTensor(tC, got.data(), got.size() * sizeof(float));
+  CHECK(relErr() <= 1e-3);
+  vs.clear();
+  auto tC2 = rt->ops().matmulBlocks(tA, tW, DequantFormat::Q4_0, N);
+  rt->copyFromTensor(tC2, got.data(), got.size() * sizeof(float));
+  CHECK(relErr() <= 3e-3);
+}
+
 // GGUF file -> device weights without the CPU detour (interface/runner/llama/llama.cpp:831-866, 934-1027): raw blocks
 // are uploaded as they lie in the file; fused QKV is a concatenation of rows, gate / up become alternating rows for the
 // paired mat-vec, a Q6_K tensor is re-encoded to Q8_0 blocks on the device.  Every product is checked against the CPU
@@ -796,6 +847,7 @@ int main() {
     RUN(reusableCommandBuffer);
     RUN(reusableSurvivesWorkspaceGrowth);
     RUN(resultCopiesFollowReplaysAndWrites);
+    RUN(tunedVariantRunsRowGroups);
     RUN(ggufUploadAndMatmul);
     RUN(errorBehaviour);
     RUN(rmsNormCases);

@@ -272,6 +272,29 @@ def test_activations_staged_once_equal_per_block_staging(fmt, dtype, flags, M, K
 
 
 @pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("dtype,M", [(np.float16, 17), (np.float16, 32), (np.float16, 64), (np.float32, 20), (np.float32, 32)])
+def test_forced_matvec_runs_row_groups(fmt, dtype, M):
+    """CUTB_VARIANT_GEMV_MMA forced beyond one group of activation rows: up to four groups, one after the other, each
+    with its own residual rows (binary fusion); refused beyond that.  CUTB_VARIANT_AUTO keeps sending these shapes
+    to the GEMM."""
+    from gpu_util import rel_l2, run_blocks
+
+    K, N = 1024, 264
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M + fmt)
+    D = synth.make_activations(M, N, 99)
+    got, used, st = run_blocks(fmt, A, W, N, variant=L.VARIANT_GEMV_MMA, D_np=D, fusion_type=2, fusion_op=0)
+    assert used == L.VARIANT_GEMV_MMA and st == 0
+    assert rel_l2(got, _ref(fmt, A, W, M, K, N, D=D, fusion_type=2, fusion_op=0)) <= TOL
+    _, auto, _ = run_blocks(fmt, A, W, N)
+    assert auto == L.VARIANT_GEMM_TC
+    big = 65 if dtype == np.float16 else 33
+    Ab, _ = _inputs(fmt, big, K, N, dtype, seed=1)
+    with pytest.raises(L.CutbError) as e:
+        run_blocks(fmt, Ab, W, N, variant=L.VARIANT_GEMV_MMA)
+    assert e.value.status == L.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("fmt", FMTS)
 def test_long_k_and_few_rows_use_split_k(fmt):
     """70B-shape slices: K = 28672 with N/8 rows per GPU -> K is split across CTAs
     and summed in a fixed order from the workspace."""

@@ -19,6 +19,7 @@ def _row(v, us):
 RECORDS = [
     {"shape": [1, 4096, 11008], "blocks_q4_0": [_row(0, 900.0), _row(1, 7.7)]},                      # built-in wins: no rule
     {"shape": [16, 4096, 11008], "blocks_q4_0": [_row(0, 9000.0), _row(1, 40.0), _row(2, 30.0)]},    # GEMM beats the mat-vec
+    {"shape": [24, 4096, 11008], "blocks_q4_0": [_row(1, 40.1), _row(2, 40.6)]},                       # a 1 % edge: no rule
     {"shape": [32, 2048, 2048], "blocks_q4_0": [_row(1, 0.0)] and [_row(0, 5.0), _row(2, 9.0)]},     # SIMT beats the GEMM
     {"shape": [8, 2048, 5632], "blocks_q4_0": []},                                                    # nothing timed
 ]
@@ -35,7 +36,7 @@ def test_builtin_choice_matches_the_operator_node():
 def test_rules_only_where_the_measured_best_differs():
     doc = op_bench.derive_rules(RECORDS)
     cuda = doc["operators"]["MatMulQBlocks"]["backends"]["cuda"]
-    assert cuda["default_variant"] == 1
+    assert cuda["default_variant"] == -1  # unmatched shapes keep the operator's own shape-dependent choice
     got = {tuple(r["conditions"]["shape"]): r["variant"] for r in cuda["rules"]}
     assert got == {(16, 4096, 11008): 2, (32, 2048, 2048): 0}
 
@@ -56,7 +57,8 @@ def test_derived_file_drives_the_cpp_selector(tmp_path):
 
     assert select(1, 16, 4096, 11008) == 2   # rule
     assert select(2, 32, 2048, 2048) == 0    # rule
-    assert select(0, 1, 4096, 11008) == 1    # no rule for the shape: the file's default for the operator
+    assert select(0, 1, 4096, 11008) == 0    # no rule for the shape: the caller's own choice stands
+    assert select(2, 512, 4096, 14336) == 2
     # the committed rule file parses too
     shipped = os.path.join(ROOT, "cut_b200", "tuning_data.json")
     if os.path.exists(shipped):
