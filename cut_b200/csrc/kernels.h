@@ -32,6 +32,10 @@ int qgemv_planes_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
 bool qgemm_tc_supported(const cutb_qmatmul_desc &d);
 uint64_t qgemm_tc_workspace(const cutb_qmatmul_desc &d);
 int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
+// the same GEMM for up to 128 activation rows (operand roles swapped, K stages dealt over all SMs); reached through qgemm_tc_*
+bool qgemm_skinny_applies(const cutb_qmatmul_desc &d);
+uint64_t qgemm_skinny_workspace(const cutb_qmatmul_desc &d);
+int qgemm_skinny_launch(const cutb_qmatmul_desc &d, cudaStream_t stream);
 
 int dequant_launch(int format, const void *raw, float *out, uint32_t rows, uint32_t cols, uint32_t ldo,
                    cudaStream_t stream);

@@ -641,6 +641,45 @@ def test_gemm_tc_matches_checker(fmt, dtype, M, K, N):
     assert rel_l2(got, _ref(fmt, A, W, M, K, N)) <= TOL
 
 
+@pytest.mark.parametrize("fmt,dtype,M,K,N", [
+    (synth.Q4_0, np.float16, 32, 4096, 11008),   # 43 tiles of 256 rows over the SMs: most CTAs end one tile and begin the next
+    (synth.Q8_0, np.float32, 33, 1024, 25600),   # 100 tiles, runs of 3 units of a tile's 4
+    (synth.Q4_K, np.float16, 128, 2048, 1024),   # few tiles, many CTAs per tile; all 128 tokens
+    (synth.Q4_0, np.float16, 24, 256, 38400),    # more tiles than SMs: no split, one unit per tile
+    (synth.Q4_K, np.float32, 5, 512, 700),       # a last tile that ends inside its third granule
+    (synth.Q4_0, np.float16, 96, 1024, 18944)])  # 65..128 tokens with enough 128-row tiles: the prefill kernel
+def test_gemm_tc_splits_k_stages_over_the_sms(fmt, dtype, M, K, N):
+    """Up to 128 tokens (tokens = MMA M operand, 256 weight rows = N operand) the 256-k units of all weight tiles
+    are dealt evenly to the SMs; a tile shared by several CTAs is summed from their workspace slots in a fixed
+    order, with the fused op applied after the sum."""
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M + N)
+    D = synth.make_activations(M, N, 5)
+    got, used, st = run_blocks(fmt, A, W, N, D_np=D, fusion_type=2, fusion_op=0, variant=L.VARIANT_GEMM_TC)
+    assert used == L.VARIANT_GEMM_TC and st == 0
+    rb = synth.row_bytes(fmt, K)
+    for lo, hi in ((0, 300), (N // 2 - 150, N // 2 + 150), (N - 300, N)):
+        ref = _ref(fmt, A, W[lo * rb:hi * rb], M, K, hi - lo, D=np.ascontiguousarray(D[:, lo:hi]), fusion_type=2, fusion_op=0)
+        assert rel_l2(got[:, lo:hi], ref) <= TOL
+    again, _, _ = run_blocks(fmt, A, W, N, D_np=D, fusion_type=2, fusion_op=0, variant=L.VARIANT_GEMM_TC)
+    assert np.array_equal(got, again)  # fixed summation order
+
+
+def test_gemm_tc_without_room_for_the_split_runs_one_tile_per_cta():
+    import torch
+    from cut_b200 import ops
+    from gpu_util import dev, rel_l2
+
+    M, K, N = 48, 1024, 1280
+    A_np, W_np = _inputs(synth.Q4_0, M, K, N, np.float16, seed=12)
+    d, C_out, keep = ops.make_desc(dev(A_np), dev(W_np), synth.Q4_0, N, variant=L.VARIANT_GEMM_TC)
+    assert ops.workspace_bytes(d) > 0  # the split's slots
+    ops.launch(d)  # no workspace given
+    torch.cuda.synchronize()
+    assert rel_l2(C_out.cpu().numpy(), _ref(synth.Q4_0, A_np, W_np, M, K, N)) <= TOL
+
+
 @pytest.mark.parametrize("ftype,fop", [(1, 133), (2, 0)])
 def test_gemm_tc_fused_epilogues(ftype, fop):
     from gpu_util import run_blocks
