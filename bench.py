@@ -649,6 +649,12 @@ def secondary_measurements(dev) -> dict:
     b8 = chain_us(dev, synth.Q4_0, N_ROWS, K_COLS, 8, np.float16)
     b8["frac_of_measured_hbm"] = b8["GB/s"] / hbm if hbm else None
     out["configs[1]_q4_0_11008x4096_batch8"] = b8
+    # the same weight with 16 .. 128 activation rows: what CUTB_VARIANT_AUTO runs there (the mat-vec up to 16 fp16
+    # rows, the tensor-core GEMM for up to 128 tokens, the prefill GEMM beyond); bound = the same weight traffic
+    for m in (16, 32, 64, 128):
+        r = chain_us(dev, synth.Q4_0, N_ROWS, K_COLS, m, np.float16, total_mb=300.0)
+        r["frac_of_measured_hbm"] = r["GB/s"] / hbm if hbm else None
+        out[f"configs[1]_q4_0_11008x4096_batch{m}"] = r
     # the layout the reference's unchanged loader and runner hand over: [K, N] planes (nibbles [K, N / 2] after its
     # Q4 transpose, fp16 scales [K / 32, N]), batch 1, against the block layout above
     out["configs[1]_q4_0_kn_planes_batch1"] = planes_chain_us(dev, N_ROWS, K_COLS)

@@ -397,22 +397,35 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
           if (n >= p.N) continue;
           float *dst = p.C + (size_t)m * p.ldc + n;
           const float *dsrc = p.fusion_type == CUTB_FUSION_BINARY ? p.D + (size_t)m * p.ldd + n : nullptr;
-          if (p.vec_ok && n + 32 <= p.N) {
+          const bool vec = p.vec_ok && n + 32 <= p.N;
+          // 16 values at a time, the fused op selected once per group (apply_epilogue_n), not once per value
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              float4 dv = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (dsrc) dv = __ldg(reinterpret_cast<const float4 *>(dsrc) + i);
-              float4 o;
-              o.x = apply_epilogue(__uint_as_float(v[4 * i]), p.fusion_type, p.fusion_op, dv.x);
-              o.y = apply_epilogue(__uint_as_float(v[4 * i + 1]), p.fusion_type, p.fusion_op, dv.y);
-              o.z = apply_epilogue(__uint_as_float(v[4 * i + 2]), p.fusion_type, p.fusion_op, dv.z);
-              o.w = apply_epilogue(__uint_as_float(v[4 * i + 3]), p.fusion_type, p.fusion_op, dv.w);
-              reinterpret_cast<float4 *>(dst)[i] = o;
+          for (int hh = 0; hh < 2; ++hh) {
+            float x[16], dd[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = __uint_as_float(v[16 * hh + i]);
+            if (p.fusion_type != CUTB_FUSION_NONE) {
+              if (dsrc && vec) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float4 t = __ldg(reinterpret_cast<const float4 *>(dsrc) + 4 * hh + i);
+                  dd[4 * i] = t.x, dd[4 * i + 1] = t.y, dd[4 * i + 2] = t.z, dd[4 * i + 3] = t.w;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) dd[i] = (dsrc && n + 16 * hh + i < p.N) ? dsrc[16 * hh + i] : 0.f;
+              }
+              apply_epilogue_n<16>(x, dd, p.fusion_type, p.fusion_op);
             }
-          } else {
+            if (vec) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (n + i < p.N) dst[i] = apply_epilogue(__uint_as_float(v[i]), p.fusion_type, p.fusion_op, dsrc ? dsrc[i] : 0.f);
+              for (int i = 0; i < 4; ++i)
+                reinterpret_cast<float4 *>(dst)[4 * hh + i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (n + 16 * hh + i < p.N) dst[16 * hh + i] = x[i];
+            }
           }
         }
       }

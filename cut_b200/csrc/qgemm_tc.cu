@@ -260,18 +260,25 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
           const uint32_t mbase = m0 + c0;
           if (mbase >= p.M) continue;
           float *dst = p.C + (size_t)mbase * p.ldc + nn;
-          if (p.fusion_type == CUTB_FUSION_NONE) {
+          float x[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (n_ok && mbase + i < p.M) dst[(size_t)i * p.ldc] = __uint_as_float(v[i]);
-          } else {
-            const float *dsrc = p.fusion_type == CUTB_FUSION_BINARY ? p.D + (size_t)mbase * p.ldd + nn : nullptr;
+          for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
+          if (p.fusion_type != CUTB_FUSION_NONE) {
+            // the op is selected once for the 32 values (apply_epilogue_n), not once per value
+            float dd[32];
+            if (p.fusion_type == CUTB_FUSION_BINARY) {
+              const float *dsrc = p.D + (size_t)mbase * p.ldd + nn;
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (n_ok && mbase + i < p.M)
-                dst[(size_t)i * p.ldc] = apply_epilogue(__uint_as_float(v[i]), p.fusion_type, p.fusion_op,
-                                                        dsrc ? dsrc[(size_t)i * p.ldd] : 0.f);
+              for (int i = 0; i < 32; ++i) dd[i] = (n_ok && mbase + i < p.M) ? dsrc[(size_t)i * p.ldd] : 0.f;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) dd[i] = 0.f;
+            }
+            apply_epilogue_n<32>(x, dd, p.fusion_type, p.fusion_op);
           }
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (n_ok && mbase + i < p.M) dst[(size_t)i * p.ldc] = x[i];
         }
       }
     }

@@ -211,6 +211,7 @@ def main(argv=None) -> int:
     ap.add_argument("--format", choices=["q8_0", "q4_0", "q4_k"], default="q4_0", help="with --only: block format")
     ap.add_argument("--layout", choices=["blocks", "planes"], default="blocks", help="with --only: weight layout")
     ap.add_argument("--variant", type=int, default=None, help="with --only: force this variant (default: the built-in choice)")
+    ap.add_argument("--silu", action="store_true", help="with --only: fuse SiLU into the epilogue (the *_silu records)")
     args = ap.parse_args(argv)
     import torch
 
@@ -223,12 +224,12 @@ def main(argv=None) -> int:
         M, K, N = args.only
         if args.layout == "planes":
             v = 3 if args.variant is None else args.variant
-            us = time_planes(torch, dev, args.format != "q8_0", M, K, N, False, v)
+            us = time_planes(torch, dev, args.format != "q8_0", M, K, N, args.silu, v)
         else:
             fmt = {"q8_0": L.Q8_0, "q4_0": L.Q4_0, "q4_k": L.Q4_K}[args.format]
             v = builtin_block_variant(M, K, N, False) if args.variant is None else args.variant
-            us = time_blocks(torch, dev, fmt, M, K, N, v, False)
-        print(json.dumps({"shape": [M, K, N], "format": args.format, "layout": args.layout, "variant": v, "median_us": us}))
+            us = time_blocks(torch, dev, fmt, M, K, N, v, args.silu)
+        print(json.dumps({"shape": [M, K, N], "format": args.format, "layout": args.layout, "variant": v, "silu": args.silu, "median_us": us}))
         return 0
 
     shapes = REFERENCE_SHAPES if args.reference_shapes_only else REFERENCE_SHAPES + EXTRA_SHAPES

@@ -133,6 +133,10 @@ enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2, CUTB_FLAG_A_RMSNORM = 
  * CUTB_ERR_RANGE in *status (the output then holds inf / NaN where such a value took part);
  * weight products below 6e-8 flush to zero.  Callers whose activations can exceed the fp16
  * range select CUTB_VARIANT_GENERIC, or scale A down and C up.  Accumulation and C are fp32.
+ * Up to 128 activation rows the same variant runs a kernel of its own (tokens as the MMA's M
+ * operand, K shared out over all SMs); it is launched with programmatic stream serialization
+ * like the decode mat-vec (it waits for the previous kernel only before it reads A and before it
+ * stores), which CUTB_FLAG_NO_OVERLAP switches off.
  */
 typedef struct cutb_qmatmul_desc {
   int32_t format;      /* CUTB_Q8_0 / CUTB_Q4_0 / CUTB_Q4_K */
@@ -163,8 +167,11 @@ typedef struct cutb_qmatmul_desc {
   float a_norm_eps;           /* CUTB_FLAG_A_RMSNORM */
 } cutb_qmatmul_desc;
 
-/* Scratch bytes cutb_qmatmul needs for this descriptor (0 for most shapes;
- * split-K decode shapes stage partial sums there).  Never allocates. */
+/* Scratch bytes cutb_qmatmul needs for this descriptor.  Never allocates.  What the variants keep there: the
+ * decode mat-vec its staged activations (three rows and up) and split-K partial sums; the tensor-core GEMM the
+ * fp16 copy of fp32 activations and, up to 128 activation rows, the partial tiles of weight tiles whose K is shared
+ * by several blocks (summed in a fixed order by a second small kernel; without that room every weight tile goes
+ * whole to one block, which is slower but needs nothing). */
 CUTB_API uint64_t cutb_qmatmul_workspace_bytes(const cutb_qmatmul_desc *desc);
 
 /* Variant the library would run for this descriptor (resolves CUTB_VARIANT_AUTO);
