@@ -453,16 +453,23 @@ __global__ void __launch_bounds__(SK_BW) tc_skinny_fixup_kernel(const SkParams p
   const uint32_t n = t * SK_BW + c;
   if (n >= p.N) return;
   const uint32_t head_tile_first = (c_first * p.per) / nk;  // only the first sharer can have begun in an earlier tile
+  const uint32_t m0 = blockIdx.y * SK_FIX_ROWS;
+  float sum[SK_FIX_ROWS];
+#pragma unroll
+  for (uint32_t mm = 0; mm < SK_FIX_ROWS; ++mm) sum[mm] = 0.f;
+  for (uint32_t cta = c_first; cta <= c_last; ++cta) {
+    const uint32_t tail = (cta == c_first && head_tile_first != t) ? 1u : 0u;  // not the CTA's first tile
+    const float *slot = p.partial + ((size_t)(2 * cta + tail) * p.bt + m0) * SK_BW + c;
+#pragma unroll
+    for (uint32_t mm = 0; mm < SK_FIX_ROWS; ++mm)  // the rows' loads are independent of one another
+      if (m0 + mm < p.M) sum[mm] += slot[(size_t)mm * SK_BW];
+  }
+#pragma unroll
   for (uint32_t mm = 0; mm < SK_FIX_ROWS; ++mm) {
-    const uint32_t m = blockIdx.y * SK_FIX_ROWS + mm;
+    const uint32_t m = m0 + mm;
     if (m >= p.M) break;
-    float sum = 0.f;
-    for (uint32_t cta = c_first; cta <= c_last; ++cta) {
-      const uint32_t tail = (cta == c_first && head_tile_first != t) ? 1u : 0u;  // not the CTA's first tile
-      sum += p.partial[((size_t)(2 * cta + tail) * p.bt + m) * SK_BW + c];
-    }
     const float dv = p.fusion_type == CUTB_FUSION_BINARY ? p.D[(size_t)m * p.ldd + n] : 0.f;
-    p.C[(size_t)m * p.ldc + n] = apply_epilogue(sum, p.fusion_type, p.fusion_op, dv);
+    p.C[(size_t)m * p.ldc + n] = apply_epilogue(sum[mm], p.fusion_type, p.fusion_op, dv);
   }
 }
 

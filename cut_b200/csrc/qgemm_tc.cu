@@ -260,25 +260,28 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
           const uint32_t mbase = m0 + c0;
           if (mbase >= p.M) continue;
           float *dst = p.C + (size_t)mbase * p.ldc + nn;
-          float x[32];
+          if (p.fusion_type == CUTB_FUSION_NONE) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) x[i] = __uint_as_float(v[i]);
-          if (p.fusion_type != CUTB_FUSION_NONE) {
-            // the op is selected once for the 32 values (apply_epilogue_n), not once per value
-            float dd[32];
-            if (p.fusion_type == CUTB_FUSION_BINARY) {
-              const float *dsrc = p.D + (size_t)mbase * p.ldd + nn;
+            for (int i = 0; i < 32; ++i)
+              if (n_ok && mbase + i < p.M) dst[(size_t)i * p.ldc] = __uint_as_float(v[i]);
+          } else {
+            // eight values at a time, the op selected once per group (apply_epilogue_n) rather than once per value;
+            // small groups keep the fused path from setting the kernel's register allocation
+            const float *dsrc = p.fusion_type == CUTB_FUSION_BINARY ? p.D + (size_t)mbase * p.ldd + nn : nullptr;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) dd[i] = (n_ok && mbase + i < p.M) ? dsrc[(size_t)i * p.ldd] : 0.f;
-            } else {
+            for (int g8 = 0; g8 < 4; ++g8) {
+              float x[8], dd[8];
 #pragma unroll
-              for (int i = 0; i < 32; ++i) dd[i] = 0.f;
+              for (int i = 0; i < 8; ++i) {
+                x[i] = __uint_as_float(v[8 * g8 + i]);
+                dd[i] = (dsrc && n_ok && mbase + 8 * g8 + i < p.M) ? dsrc[(size_t)(8 * g8 + i) * p.ldd] : 0.f;
+              }
+              apply_epilogue_n<8>(x, dd, p.fusion_type, p.fusion_op);
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (n_ok && mbase + 8 * g8 + i < p.M) dst[(size_t)(8 * g8 + i) * p.ldc] = x[i];
             }
-            apply_epilogue_n<32>(x, dd, p.fusion_type, p.fusion_op);
           }
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (n_ok && mbase + i < p.M) dst[(size_t)i * p.ldc] = x[i];
         }
       }
     }
