@@ -3,30 +3,34 @@
 // C[M, N] = epilogue(A[M, K] * dequant(W)^T).  Same contract and arithmetic as the prefill GEMM (fp16
 // operands, the dequantised weight rounded to fp16 as the reference's tensor-core variants round it,
 // MatMulQ4CoopMatTiled.cu:84-87 / MatMulQ8CoopMatTiled.cu:71-74; fp32 accumulation), but the operand roles
-// are the other way round.  A tcgen05.mma of shape M x N x 16 occupies the tensor core for about M cycles
-// whatever N is, so with few tokens the prefill kernel's "weights = M operand, tokens = N operand" spends
-// 128 cycles per 128 weight rows x 16 k on a nearly empty N.  Here the tokens are the M operand (one token
-// per tensor-memory lane, 128 lanes, only the rows that exist are loaded) and 256 weight rows are the N
-// operand: 128 cycles per 256 rows x 16 k, and the accumulator comes back token-major, so a thread of the
-// epilogue stores 32 consecutive output columns of its token.
+// are the other way round.  In the prefill kernel (weights = the MMA's M operand, tokens = its N operand) the
+// issuer spent the same 95-140 cycles per tcgen05.mma with 32 tokens as with 256, so with few tokens almost all
+// of an instruction is empty.  Here the tokens are the M operand (one token per tensor-memory lane, 128 lanes,
+// only the rows that exist are loaded) and 256 weight rows are the N operand: one instruction covers twice the
+// weights, and the accumulator comes back token-major, so a thread of the epilogue stores 32 consecutive output
+// columns of its token.
 //
-// The range is bound by what each SM pulls through its L2 port (weights once, the activation rows once per
-// weight tile) and by the converters' instruction issue, so every SM must have work: the K stages of all
-// weight tiles are numbered tile by tile and dealt in equal contiguous runs to one CTA per SM (stream-K).
-// A CTA touches at most two tiles; each accumulates in its own 256 tensor-memory columns.  A tile whose K a
-// CTA covered whole is finished there (fused epilogue, written to C); a shared tile goes raw to the CTA's
-// head / tail slot in the workspace and tc_skinny_fixup_kernel adds the slots in CTA order and applies the
-// epilogue (fixed summation order for a shape and a device).
+// Few tokens mean few tiles, so every SM must be given work: the 256-k units of all weight tiles are numbered
+// tile by tile and dealt in equal contiguous runs to one CTA per SM (stream-K).  A CTA touches at most two
+// tiles; each accumulates in its own 256 tensor-memory columns.  A tile whose K a CTA covered whole is finished
+// there (fused epilogue, written to C); a shared tile goes raw to the CTA's head / tail slot in the workspace
+// and tc_skinny_fixup_kernel adds the slots in CTA order and applies the epilogue (fixed summation order for a
+// shape and a device).
 //
-//   warp 0      allocates tensor memory; one lane issues the MMAs of every stage and commits them to the
-//               stage's "consumed" barrier (frees the activation stage and the weight slot)
+//   warp 0      allocates tensor memory; one lane issues the MMAs of every 64-k stage and commits them to the
+//               stage's "consumed" barrier (frees the activation stage and the fp16 weight slot)
 //   warp 1      one lane issues the TMA tensor copies of the activation rows (64 k x tokens, fp16,
 //               128-byte swizzle, no cluster multicast)
-//   warps 4-11  converters, one weight row of the 256 per thread: raw block bytes of the next 64-k chunk
-//               in flight in registers, widened with half2 arithmetic, stored K-major with the 128-byte
-//               swizzle; then the epilogue (tcgen05.ld, lane = token, 32 columns = 32 weight rows)
-// Every wait is bounded; on expiry the CTA records CUTB_ERR_TIMEOUT, drains its copies, frees its tensor
-// memory and returns.
+//   warp 2      block formats: one lane issues the TMA copies of raw weight granules (64 rows x 256 k of block
+//               bytes, a 2-D tensor map over the weight, no swizzle, no multicast) into a ring
+//   warps 4-19  block formats: two converter groups of 256 threads, one weight row per thread; a group widens
+//               every other 64-k stage from the raw granule (conflict-free 16-byte shared loads, half2
+//               arithmetic) into the K-major, 128-byte-swizzled fp16 slot.  Plane formats: warps 4-11, one
+//               group, raw bytes of the next chunk in flight in registers as in the prefill kernel.
+//               The same warps run the epilogue (tcgen05.ld, lane = token, 32 columns = 32 weight rows).
+// Programmatic dependent launch: the kernel lets its successor start at once and waits for its predecessor only
+// before the first activation copy and before the first store.  Every wait is bounded; on expiry the CTA records
+// CUTB_ERR_TIMEOUT, drains its copies, frees its tensor memory and returns.
 #include "qgemm_tc_common.cuh"
 
 namespace cutb {
