@@ -107,7 +107,15 @@ int validate(const cutb_qmatmul_desc *d) {
 int select(const cutb_qmatmul_desc &d) {
   if (d.variant != CUTB_VARIANT_AUTO) return d.variant;
   if (d.layout == CUTB_LAYOUT_GGUF_BLOCKS) {
-    if (qgemv_blocks_supported(d)) return CUTB_VARIANT_GEMV_MMA;
+    if (qgemv_blocks_supported(d)) {
+      // 13 to 16 fp16 rows need the mat-vec's fourth column tile; from 16 M weights up the tensor-core GEMM for few
+      // tokens is faster there (16 rows: 4096 x 4096 15.0 against 11.2 us, 11008 x 4096 28.0 against 22.1 us; at
+      // 2048 x 2048 the mat-vec wins, 6.1 against 7.5 us).  The fused RMSNorm and paired rows exist in the mat-vec only.
+      const bool matvec_only = d.flags & (CUTB_FLAG_A_RMSNORM | CUTB_FLAG_GLU_PAIRS);
+      if (d.a_dtype == CUTB_F16 && d.M >= 13 && (uint64_t)d.K * d.N >= (1ull << 24) && !matvec_only && qgemm_tc_supported(d))
+        return CUTB_VARIANT_GEMM_TC;
+      return CUTB_VARIANT_GEMV_MMA;
+    }
     if (qgemm_tc_supported(d)) return CUTB_VARIANT_GEMM_TC;
   } else if (qgemv_planes_supported(d)) {
     return CUTB_VARIANT_GEMV_PLANES;

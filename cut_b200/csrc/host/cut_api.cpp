@@ -292,6 +292,11 @@ MatMulOpNode::MatMulOpNode(TensorStore &store, const Tensor &a, const Tensor &ra
   uint32_t builtin = 0;
   if (K_ % 256 == 0 && vrows <= 16) builtin = 1;
   else if (K_ % 256 == 0 && M_ > 1 && store.caps().cooperativeMatrix) builtin = 2;
+  // 13 to 16 fp16 rows on 16 M weights or more: the tensor-core GEMM for few tokens beats the mat-vec's fourth
+  // column tile (the library's own automatic choice makes the same cut)
+  if (builtin == 1 && dtypeA_ == DataType::Float16 && M_ >= 13 && (uint64_t)K_ * N_ >= (1ull << 24) &&
+      store.caps().cooperativeMatrix)
+    builtin = 2;
   fusionFallbackSpec_ = builtin;
   if (spec.has_value()) spec_ = *spec;
   else
@@ -323,7 +328,10 @@ void MatMulOpNode::setBlockOptions(const MatMulBlockOptions &opt) {
   if (opt.flags & ~(kBlockFlagNoOverlap | kBlockFlagAct16 | kBlockFlagRmsNorm | kBlockFlagGluPairs))
     throw std::runtime_error("matmul: unknown block option bits");
   if (opt.flags & (kBlockFlagRmsNorm | kBlockFlagGluPairs)) {
-    // only the decode mat-vec has these (variant 1: K % 256 == 0, at most 16 virtual activation rows)
+    // only the decode mat-vec has these (variant 1: K % 256 == 0, at most 16 virtual activation rows); an automatic
+    // choice that went elsewhere for speed comes back to it
+    const uint32_t vrows = dtypeA_ == DataType::Float32 ? 2 * M_ : M_;
+    if (*spec_ != 1 && autoSpec_ && K_ % 256 == 0 && vrows <= 16) spec_ = 1;
     if (*spec_ != 1) throw std::runtime_error("matmul: fused RMSNorm / paired rows exist in the decode mat-vec only");
   }
   if (opt.flags & kBlockFlagGluPairs) {

@@ -46,6 +46,8 @@ def builtin_block_variant(M: int, K: int, N: int, a_is_f32: bool) -> int:
     """The choice MatMulOpNode makes without tuning data for raw GGUF blocks."""
     vrows = 2 * M if a_is_f32 else M
     if K % 256 == 0 and vrows <= 16:
+        if not a_is_f32 and M >= 13 and K * N >= 1 << 24:
+            return 2  # the mat-vec's fourth column tile loses to the GEMM for few tokens on 16 M weights and more
         return 1
     if K % 256 == 0 and M > 1:
         return 2

@@ -666,6 +666,23 @@ def test_gemm_tc_splits_k_stages_over_the_sms(fmt, dtype, M, K, N):
     assert np.array_equal(got, again)  # fixed summation order
 
 
+def test_thirteen_to_sixteen_rows_on_a_large_weight_take_the_gemm():
+    """The automatic choice: up to 12 fp16 rows, small weights and fp32 rows stay on the mat-vec; 13 to 16 fp16 rows on
+    16 M weights and more go to the tensor-core GEMM for few tokens."""
+    from gpu_util import rel_l2, run_blocks
+
+    K, N = 4096, 4096
+    for M, want in ((12, L.VARIANT_GEMV_MMA), (13, L.VARIANT_GEMM_TC), (16, L.VARIANT_GEMM_TC)):
+        A, W = _inputs(synth.Q4_K, M, K, N, np.float16, seed=M)
+        got, used, st = run_blocks(synth.Q4_K, A, W, N)
+        assert used == want and st == 0
+        ref = _ref(synth.Q4_K, A, W[:256 * synth.row_bytes(synth.Q4_K, K)], M, K, 256)
+        assert rel_l2(got[:, :256], ref) <= TOL
+    A, W = _inputs(synth.Q4_K, 8, K, N, np.float32, seed=3)
+    _, used, _ = run_blocks(synth.Q4_K, A, W, N)
+    assert used == L.VARIANT_GEMV_MMA
+
+
 def test_gemm_tc_without_room_for_the_split_runs_one_tile_per_cta():
     import torch
     from cut_b200 import ops

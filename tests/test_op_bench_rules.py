@@ -18,7 +18,7 @@ def _row(v, us):
 
 RECORDS = [
     {"shape": [1, 4096, 11008], "blocks_q4_0": [_row(0, 900.0), _row(1, 7.7)]},                      # built-in wins: no rule
-    {"shape": [16, 4096, 11008], "blocks_q4_0": [_row(0, 9000.0), _row(1, 40.0), _row(2, 30.0)]},    # GEMM beats the mat-vec
+    {"shape": [12, 4096, 11008], "blocks_q4_0": [_row(0, 9000.0), _row(1, 40.0), _row(2, 30.0)]},    # GEMM beats the mat-vec
     {"shape": [24, 4096, 11008], "blocks_q4_0": [_row(1, 40.1), _row(2, 40.6)]},                       # a 1 % edge: no rule
     {"shape": [32, 2048, 2048], "blocks_q4_0": [_row(1, 0.0)] and [_row(0, 5.0), _row(2, 9.0)]},     # SIMT beats the GEMM
     {"shape": [8, 2048, 5632], "blocks_q4_0": []},                                                    # nothing timed
@@ -27,7 +27,10 @@ RECORDS = [
 
 def test_builtin_choice_matches_the_operator_node():
     assert op_bench.builtin_block_variant(1, 4096, 11008, False) == 1
-    assert op_bench.builtin_block_variant(16, 4096, 11008, False) == 1
+    assert op_bench.builtin_block_variant(12, 4096, 11008, False) == 1
+    assert op_bench.builtin_block_variant(16, 4096, 11008, False) == 2  # the fourth column tile on a large weight
+    assert op_bench.builtin_block_variant(16, 2048, 2048, False) == 1
+    assert op_bench.builtin_block_variant(8, 4096, 11008, True) == 1    # fp32 rows stay on the mat-vec
     assert op_bench.builtin_block_variant(9, 4096, 11008, True) == 2  # 18 virtual rows
     assert op_bench.builtin_block_variant(17, 4096, 11008, False) == 2
     assert op_bench.builtin_block_variant(4, 96, 8, False) == 0
@@ -38,7 +41,7 @@ def test_rules_only_where_the_measured_best_differs():
     cuda = doc["operators"]["MatMulQBlocks"]["backends"]["cuda"]
     assert cuda["default_variant"] == -1  # unmatched shapes keep the operator's own shape-dependent choice
     got = {tuple(r["conditions"]["shape"]): r["variant"] for r in cuda["rules"]}
-    assert got == {(16, 4096, 11008): 2, (32, 2048, 2048): 0}
+    assert got == {(12, 4096, 11008): 2, (32, 2048, 2048): 0}
 
 
 def test_derived_file_drives_the_cpp_selector(tmp_path):
@@ -55,7 +58,7 @@ def test_derived_file_drives_the_cpp_selector(tmp_path):
         assert out.returncode == 0, out.stdout + out.stderr
         return int(out.stdout.strip().splitlines()[-1])
 
-    assert select(1, 16, 4096, 11008) == 2   # rule
+    assert select(1, 12, 4096, 11008) == 2   # rule
     assert select(2, 32, 2048, 2048) == 0    # rule
     assert select(0, 1, 4096, 11008) == 0    # no rule for the shape: the caller's own choice stands
     assert select(2, 512, 4096, 14336) == 2
