@@ -122,9 +122,13 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * SA + 2 * NB + 1 + 2 * RS);
   uint32_t *abort_flag = tmem_slot + 1;
 
-  // programmatic dependent launch: the next kernel of the stream may start its prologue now; this one waits for
-  // the kernel before it only where it first touches what that kernel may have written (activations, C, D)
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Programmatic dependent launch: this kernel waits for the kernel before it only where it first touches what that
+  // kernel may have written (activations, C, D).  Without the K split the next kernel of the stream may start its
+  // prologue at once.  With it the next kernel is the fix-up, whose blocks would become resident wherever an SM has
+  // room and sit there until this grid is done -- which keeps the CTAs of the GEMM after it off those SMs (a trace
+  // showed a fifth of them entering 8 us late and the grid ending 5 us after its median CTA); so the trigger moves
+  // to the end of the CTA.
+  if (!p.partial) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t nk = p.K / SK_UNIT_K;  // units of one tile
   // this CTA's run of units: [u0, u0 + nunits), numbered tile by tile
@@ -436,6 +440,7 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
     }
   }
 
+  if (p.partial) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // release the tensor memory once every reader is done with it
   tc_fence_before();
   __syncthreads();
