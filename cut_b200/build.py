@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcutb.so")
 SOURCES = ["cabi.cu", "common.cu", "qgemv_blocks.cu", "qmatmul_generic.cu", "dequant.cu", "transpose_q4.cu",
-           "qgemm_tc.cu", "qgemm_skinny.cu", "repack.cu", "layer_ops.cu", "attention.cu", "qgemv_planes.cu"]
+           "qgemm_tc.cu", "qgemm_skinny.cu", "repack.cu", "layer_ops.cu", "attention.cu", "attention_prefill.cu", "qgemv_planes.cu"]
 HEADERS = ["common.cuh", "kernels.h", "qgemm_tc_common.cuh", os.path.join("..", "..", "include", "cutb.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden"]

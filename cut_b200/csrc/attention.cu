@@ -850,6 +850,9 @@ int batched_attention_launch(int kv_dtype, const float *q_in, uint32_t q_stride,
                              float scale, int *status, cudaStream_t stream) {
   if (int rc = check_ld(ld, "batched_attention_launch")) return rc;
   if (n_tokens == 0) return CUTB_OK;
+  if (batched_attention_tc_applies(kv_dtype, q_in, q_stride, kC, vC, out, out_stride, n_tokens, nHeads, nKvHeads, headDim, ld))
+    return batched_attention_tc_launch(q_in, q_stride, kC, vC, positions, cosT, sinT, out, out_stride, n_tokens, nHeads, nKvHeads,
+                                       headDim, ld, max_seq, scale, status, stream);
   AttnParams p{};
   p.q = q_in, p.kC = kC, p.vC = vC, p.out = out, p.status = status, p.positions = positions, p.cosT = cosT, p.sinT = sinT;
   p.q_stride = q_stride, p.out_stride = out_stride;

@@ -67,6 +67,14 @@ int batched_attention_launch(int kv_dtype, const float *q_in, uint32_t q_stride,
                              const uint32_t *positions, const float *cosT, const float *sinT, float *out, uint32_t out_stride,
                              uint32_t n_tokens, uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq,
                              float scale, int *status, cudaStream_t stream);
+// the same on the tensor cores (fp16 cache, head_dim 64 / 128, 16 tokens and more); batched_attention_launch hands over
+bool batched_attention_tc_applies(int kv_dtype, const float *q_in, uint32_t q_stride, const void *kC, const void *vC, const float *out,
+                                  uint32_t out_stride, uint32_t n_tokens, uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim,
+                                  uint64_t ld);
+int batched_attention_tc_launch(const float *q_in, uint32_t q_stride, const void *kC, const void *vC, const uint32_t *positions,
+                                const float *cosT, const float *sinT, float *out, uint32_t out_stride, uint32_t n_tokens,
+                                uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint64_t ld, uint32_t max_seq, float scale,
+                                int *status, cudaStream_t stream);
 int glu_pairs_launch(const float *in, float *out, uint32_t rows, uint32_t cols_out, uint64_t ldi, uint64_t ldo, int unary_op,
                      cudaStream_t stream);
 uint64_t attention_workspace_bytes(uint32_t nHeads, uint32_t nKvHeads, uint32_t headDim, uint32_t max_seq);

@@ -163,7 +163,9 @@ def test_rope_attention_decode_equals_the_two_calls(gpu, kv, n_heads, n_kv, hd, 
 
 @pytest.mark.parametrize("kv", [np.float32, np.float16])
 @pytest.mark.parametrize("n_heads,n_kv,hd,max_seq,T,start", [(32, 8, 128, 600, 512, 0), (4, 2, 8, 16, 5, 3), (6, 3, 66, 64, 20, 7),
-                                                              (8, 2, 64, 1400, 700, 650), (4, 4, 32, 2100, 90, 1990)])
+                                                              (8, 2, 64, 1400, 700, 650), (4, 4, 32, 2100, 90, 1990),
+                                                              (8, 4, 128, 300, 77, 101),   # a ragged last tile of tokens and of rows
+                                                              (4, 1, 64, 128, 16, 0)])     # the smallest batch the tensor-core kernel takes
 def test_batched_prefill_operators_match_checker(gpu, kv, n_heads, n_kv, hd, max_seq, T, start):
     """cutb_batched_kv_write (bit-exact cache rows, inputs as columns of one fused QKV matrix) and
     cutb_batched_attention (every token over the rows up to its own) against the checker run token by token."""
@@ -196,7 +198,12 @@ def test_batched_prefill_operators_match_checker(gpu, kv, n_heads, n_kv, hd, max
     assert np.array_equal(dvc.cpu().numpy().view(bits), vc_ref.view(bits))
     got = gpu.batched_attention(dq[:, :q_dim], dkc, dvc, pos, _dev(cos_t), _dev(sin_t), n_heads, n_kv, hd, status=status).cpu().numpy()
     assert int(status.item()) == 0
-    assert np.all(np.abs(got[sel] - want[sel]) <= 1e-5 + 1e-4 * np.abs(want[sel]))
+    if kv == np.float16 and hd in (64, 128) and T >= 16:
+        # the tensor-core kernel: rotated queries and probabilities rounded to fp16 (the cache already is), fp32 sums
+        assert np.all(np.abs(got[sel] - want[sel]) <= 2e-3 + 2e-3 * np.abs(want[sel]))
+        assert np.linalg.norm(got[sel] - want[sel]) / np.linalg.norm(want[sel]) <= 1e-3
+    else:
+        assert np.all(np.abs(got[sel] - want[sel]) <= 1e-5 + 1e-4 * np.abs(want[sel]))
 
 
 def test_batched_attention_range_limit_and_glu_pairs(gpu):
