@@ -386,6 +386,10 @@ CUTB_API uint64_t cutb_attention_workspace_bytes(uint32_t n_heads, uint32_t n_kv
  *   per (KV head, group of consecutive tokens) (operators/impl/attention/BatchedAttentionReadCache.cu).  A block
  *   walks its tokens' range in chunks of 512 rows with a running maximum and exp-sum, so positions[i] < max_seq is
  *   the only limit (a position past the cache is reported through `status`, never read).  Call after the cache write.
+ *   With an fp16 cache, head_dim 64 or 128, 16-byte aligned cache rows and 16 tokens or more the products run on the
+ *   tensor cores (64 tokens of a query head per block, K / V tiles of 64 rows, online softmax): the rotated queries
+ *   and the probabilities are rounded to fp16 there, sums stay fp32 -- within about 1e-3 of the output's magnitude of
+ *   the fp32 arithmetic of the other shapes.
  * cutb_glu_pairs: out[r, i] = unary(op)(in[r, 2i]) * in[r, 2i + 1] (ldi even, 8-byte aligned `in`): the
  *   gated activation over a prefill GEMM whose weight rows are stored in (gate, up) pairs.
  */
