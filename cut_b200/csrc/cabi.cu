@@ -110,8 +110,8 @@ int select(const cutb_qmatmul_desc &d) {
     if (qgemv_blocks_supported(d)) {
       // 13 to 16 fp16 rows need the mat-vec's fourth column tile; from 16 M weights up the tensor-core GEMM for few
       // tokens is faster there (16 rows: 4096 x 4096 15.0 against 11.2 us, 11008 x 4096 28.0 against 22.1 us; at
-      // 2048 x 2048 the mat-vec wins, 6.1 against 7.5 us).  The fused RMSNorm and paired rows exist in the mat-vec only.
-      const bool matvec_only = d.flags & (CUTB_FLAG_A_RMSNORM | CUTB_FLAG_GLU_PAIRS);
+      // 2048 x 2048 the mat-vec wins, 6.1 against 7.5 us).  The fused RMSNorm exists in the mat-vec only.
+      const bool matvec_only = d.flags & CUTB_FLAG_A_RMSNORM;
       if (d.a_dtype == CUTB_F16 && d.M >= 13 && (uint64_t)d.K * d.N >= (1ull << 24) && !matvec_only && qgemm_tc_supported(d))
         return CUTB_VARIANT_GEMM_TC;
       return CUTB_VARIANT_GEMV_MMA;
@@ -186,8 +186,9 @@ int cutb_qmatmul(const cutb_qmatmul_desc *desc, void *stream) {
   if (int rc = validate(desc)) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int v = select(*desc);
-  if ((desc->flags & CUTB_FLAG_GLU_PAIRS) && v != CUTB_VARIANT_GEMV_MMA) {  // (the mat-vec launcher refuses shapes that split K)
-    set_last_error("qmatmul: paired gate/up rows exist in the decode mat-vec only, for shapes that do not split K");
+  if ((desc->flags & CUTB_FLAG_GLU_PAIRS) && v != CUTB_VARIANT_GEMV_MMA && v != CUTB_VARIANT_GEMM_TC) {
+    // (the mat-vec launcher refuses shapes that split K; the tensor-core GEMMs take every shape they support)
+    set_last_error("qmatmul: paired gate/up rows exist in the decode mat-vec and the tensor-core GEMM only");
     return CUTB_ERR_UNSUPPORTED;
   }
   if (desc->flags & CUTB_FLAG_A_RMSNORM) {

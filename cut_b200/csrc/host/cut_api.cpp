@@ -327,13 +327,15 @@ void MatMulOpNode::setBlockOptions(const MatMulBlockOptions &opt) {
   if (format_ != QuantFormat::Blocks) throw std::runtime_error("matmul: block options need the raw-block constructor");
   if (opt.flags & ~(kBlockFlagNoOverlap | kBlockFlagAct16 | kBlockFlagRmsNorm | kBlockFlagGluPairs))
     throw std::runtime_error("matmul: unknown block option bits");
-  if (opt.flags & (kBlockFlagRmsNorm | kBlockFlagGluPairs)) {
-    // only the decode mat-vec has these (variant 1: K % 256 == 0, at most 16 virtual activation rows); an automatic
+  if (opt.flags & kBlockFlagRmsNorm) {
+    // only the decode mat-vec has it (variant 1: K % 256 == 0, at most 16 virtual activation rows); an automatic
     // choice that went elsewhere for speed comes back to it
     const uint32_t vrows = dtypeA_ == DataType::Float32 ? 2 * M_ : M_;
     if (*spec_ != 1 && autoSpec_ && K_ % 256 == 0 && vrows <= 16) spec_ = 1;
-    if (*spec_ != 1) throw std::runtime_error("matmul: fused RMSNorm / paired rows exist in the decode mat-vec only");
+    if (*spec_ != 1) throw std::runtime_error("matmul: the fused RMSNorm exists in the decode mat-vec only");
   }
+  if ((opt.flags & kBlockFlagGluPairs) && *spec_ != 1 && *spec_ != 2)
+    throw std::runtime_error("matmul: paired rows exist in the decode mat-vec and the tensor-core GEMM only");
   if (opt.flags & kBlockFlagGluPairs) {
     if (fusion_ != MatMulFusion::Unary) throw std::runtime_error("matmul: paired gate/up rows need a unary fusion");
     if (N_ % 2) throw std::runtime_error("matmul: paired gate/up rows need an even N");

@@ -258,6 +258,7 @@ uint32_t LlamaRunner::prefill(const std::vector<uint32_t> &tokens, uint32_t star
     Tensor h2 = ops.rmsNorm(x1, L.ffnNorm, cfg_.normEps);
     Tensor act;
     if (L.wgu.raw) {
+      // (the GEMM's own paired epilogue, kBlockFlagGluPairs, is slower at prefill sizes than this bandwidth-bound pass)
       act = ops.gluPairs(mm(h2, L.wgu, MatMulFusion::None, {}, {}), UnarySilu);
     } else {
       Tensor gate = mm(h2, L.wgate, MatMulFusion::Unary, UnarySilu, {});

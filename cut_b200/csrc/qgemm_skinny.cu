@@ -69,6 +69,7 @@ struct SkParams {
   uint32_t per;       // units (256 k of one tile) per CTA
   uint32_t tmem_cols;
   int fusion_type, fusion_op;
+  int glu;  // rows in (gate, up) pairs: C[m, n / 2] = unary(acc[m, n]) * acc[m, n + 1], n even
   int *status;
   float *partial;     // stream-K slots [2 * CTAs][bt][256]
   int vec_ok;         // C (and D) rows allow 16-byte accesses
@@ -403,6 +404,30 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
           }
           const uint32_t n = (tile0 + seg) * SK_BW + c0;
           if (n >= p.N) continue;
+          if (p.glu) {
+            // gate and up rows are neighbouring columns of this token: 16 outputs from the thread's 32 accumulators
+            float *dstp = p.C + (size_t)m * p.ldc + (n >> 1);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              float x[8], up[8], dd[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                x[i] = __uint_as_float(v[16 * hh + 2 * i]);
+                up[i] = __uint_as_float(v[16 * hh + 2 * i + 1]);
+                dd[i] = 0.f;
+              }
+              apply_epilogue_n<8>(x, dd, CUTB_FUSION_UNARY, p.fusion_op);
+              if (p.vec_ok && n + 32 <= p.N) {
+                reinterpret_cast<float4 *>(dstp)[2 * hh] = make_float4(x[0] * up[0], x[1] * up[1], x[2] * up[2], x[3] * up[3]);
+                reinterpret_cast<float4 *>(dstp)[2 * hh + 1] = make_float4(x[4] * up[4], x[5] * up[5], x[6] * up[6], x[7] * up[7]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  if (n + 16 * hh + 2 * i < p.N) dstp[8 * hh + i] = x[i] * up[i];
+              }
+            }
+            continue;
+          }
           float *dst = p.C + (size_t)m * p.ldc + n;
           const float *dsrc = p.fusion_type == CUTB_FUSION_BINARY ? p.D + (size_t)m * p.ldd + n : nullptr;
           const bool vec = p.vec_ok && n + 32 <= p.N;
@@ -460,7 +485,7 @@ __global__ void __launch_bounds__(SK_BW) tc_skinny_fixup_kernel(const SkParams p
   const uint32_t c_first = t * nk / p.per, c_last = ((t + 1) * nk - 1) / p.per;
   if (c_first == c_last) return;  // one CTA covered the tile and wrote it
   const uint32_t n = t * SK_BW + c;
-  if (n >= p.N) return;
+  const bool in_n = n < p.N;  // (the slots are 256 columns wide whatever N is; only the stores look at it)
   const uint32_t head_tile_first = (c_first * p.per) / nk;  // only the first sharer can have begun in an earlier tile
   const uint32_t m0 = blockIdx.y * SK_FIX_ROWS;
   float sum[SK_FIX_ROWS];
@@ -473,10 +498,19 @@ __global__ void __launch_bounds__(SK_BW) tc_skinny_fixup_kernel(const SkParams p
     for (uint32_t mm = 0; mm < SK_FIX_ROWS; ++mm)  // the rows' loads are independent of one another
       if (m0 + mm < p.M) sum[mm] += slot[(size_t)mm * SK_BW];
   }
+  if (p.glu) {  // gate and up columns sit in neighbouring threads; the even one stores the pair's output
+#pragma unroll
+    for (uint32_t mm = 0; mm < SK_FIX_ROWS; ++mm) {
+      const float up = __shfl_xor_sync(0xffffffffu, sum[mm], 1);
+      if (in_n && !(c & 1u) && m0 + mm < p.M)
+        p.C[(size_t)(m0 + mm) * p.ldc + (n >> 1)] = apply_epilogue(sum[mm], CUTB_FUSION_UNARY, p.fusion_op, 0.f) * up;
+    }
+    return;
+  }
 #pragma unroll
   for (uint32_t mm = 0; mm < SK_FIX_ROWS; ++mm) {
     const uint32_t m = m0 + mm;
-    if (m >= p.M) break;
+    if (m >= p.M || !in_n) break;
     const float dv = p.fusion_type == CUTB_FUSION_BINARY ? p.D[(size_t)m * p.ldd + n] : 0.f;
     p.C[(size_t)m * p.ldc + n] = apply_epilogue(sum[mm], p.fusion_type, p.fusion_op, dv);
   }
@@ -642,6 +676,7 @@ int qgemm_skinny_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.tmem_cols = pl.tmem_cols;
   p.fusion_type = d.fusion_type;
   p.fusion_op = d.fusion_op;
+  p.glu = (d.flags & CUTB_FLAG_GLU_PAIRS) ? 1 : 0;
   p.status = d.status;
   p.partial = nullptr;
   p.vec_ok = reinterpret_cast<uintptr_t>(d.C) % 16 == 0 && d.ldc % 4 == 0 &&

@@ -259,6 +259,28 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
           tmem_ld32(tmem_base + ((q * 32) << 16) + c0, v);
           const uint32_t mbase = m0 + c0;
           if (mbase >= p.M) continue;
+          if (p.glu) {
+            // gate and up rows are neighbouring lanes: the even lane takes its partner's accumulator, applies the
+            // gate's activation to its own and stores one output column for the pair
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              float x[8], up[8], dd[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                x[i] = __uint_as_float(v[8 * g8 + i]);
+                up[i] = __shfl_xor_sync(0xffffffffu, x[i], 1);
+                dd[i] = 0.f;
+              }
+              apply_epilogue_n<8>(x, dd, CUTB_FUSION_UNARY, p.fusion_op);
+              if (n_ok && !(lane & 1u)) {
+                float *dstp = p.C + (size_t)mbase * p.ldc + (nn >> 1);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  if (mbase + 8 * g8 + i < p.M) dstp[(size_t)(8 * g8 + i) * p.ldc] = x[i] * up[i];
+              }
+            }
+            continue;
+          }
           float *dst = p.C + (size_t)mbase * p.ldc + nn;
           if (p.fusion_type == CUTB_FUSION_NONE) {
 #pragma unroll
@@ -360,6 +382,7 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.N = d.N;
   p.fusion_type = d.fusion_type;
   p.fusion_op = d.fusion_op;
+  p.glu = (d.flags & CUTB_FLAG_GLU_PAIRS) ? 1 : 0;
   p.status = d.status;
   p.S = reinterpret_cast<const uint16_t *>(d.scales);
   p.ldb = d.ldb;

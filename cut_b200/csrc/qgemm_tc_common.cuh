@@ -35,6 +35,7 @@ struct TcParams {
   uint32_t issuers;  // MMA issuer threads (1..2, at most one per token pair)
   uint32_t ksub;     // 64-k sub-tiles per stage (2 up to 256 tokens: the issuer's waits are paid per stage)
   int fusion_type, fusion_op;
+  int glu;  // rows in (gate, up) pairs: C[m, n / 2] = unary(acc[m, n]) * acc[m, n + 1], n even
   int *status;
   // the reference's [K, N] plane layout (TC_PLANE_* formats): value plane row stride in bytes, fp16 scale plane and its
   // row stride in elements, rows of the scale plane before the affine mins

@@ -36,8 +36,8 @@ def make_desc(A: torch.Tensor, W: torch.Tensor, fmt: int, N: int, *, layout=L.LA
     if A.stride(1) != 1:
         A = A.contiguous()
     M, K = A.shape
-    if C_out is None:
-        C_out = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    if C_out is None:  # paired gate / up rows give one output column per pair
+        C_out = torch.empty((M, N // 2 if flags & L.FLAG_GLU_PAIRS else N), dtype=torch.float32, device=A.device)
     d = L.QMatmulDesc()
     d.format, d.layout, d.affine = fmt, layout, int(affine)
     d.a_dtype = L.F32 if A.dtype == torch.float32 else L.F16

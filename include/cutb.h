@@ -107,8 +107,8 @@ enum {
  *     gate matrix, row 2i + 1 of the up matrix -- and the output has N / 2 columns:
  *     C[m, i] = unary(fusion_op)(acc[m, 2i]) * acc[m, 2i + 1] (fusion_type CUTB_FUSION_UNARY; with
  *     SiLU this is the SwiGLU feed-forward the runner builds from matmulUnary + a multiply,
- *     interface/runner/llama/llama.cpp:2455-2470).  ldc >= N / 2.  Decode mat-vec only, shapes that
- *     do not split K; anything else returns CUTB_ERR_UNSUPPORTED.
+ *     interface/runner/llama/llama.cpp:2455-2470).  ldc >= N / 2.  The decode mat-vec (shapes that do
+ *     not split K) and the tensor-core GEMM have it; anything else returns CUTB_ERR_UNSUPPORTED.
  *   CUTB_FLAG_STAGE_PER_CTA: from three activation rows up the decode mat-vec quantises its
  *     activations once per call, in a small launch of its own, into the workspace
  *     (cutb_qmatmul_workspace_bytes counts the room), and every block copies the result.  With this

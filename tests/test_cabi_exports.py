@@ -81,10 +81,13 @@ def test_select_variant_and_workspace_plan_without_device():
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 1, 4096, 11008))) == L.VARIANT_GEMV_MMA
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 12, 4096, 11008))) == L.VARIANT_GEMV_MMA
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 16, 2048, 2048))) == L.VARIANT_GEMV_MMA
-    # 13 to 16 fp16 rows on 16 M weights and more: the tensor-core GEMM for few tokens, unless the mat-vec's own flags are set
+    # 13 to 16 fp16 rows on 16 M weights and more: the tensor-core GEMM for few tokens (paired rows included), unless the
+    # fused RMSNorm, which only the mat-vec has, is asked for
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 16, 4096, 11008))) == L.VARIANT_GEMM_TC
     flagged = desc(L.Q4_0, 16, 4096, 11008)
     flagged.flags, flagged.fusion_type, flagged.fusion_op = L.FLAG_GLU_PAIRS, L.FUSION_UNARY, 133
+    assert lib.cutb_qmatmul_select_variant(C.byref(flagged)) == L.VARIANT_GEMM_TC
+    flagged.flags, flagged.a_norm_weight = L.FLAG_A_RMSNORM, 256
     assert lib.cutb_qmatmul_select_variant(C.byref(flagged)) == L.VARIANT_GEMV_MMA
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q8_0, 8, 4096, 11008, L.F32))) == L.VARIANT_GEMV_MMA
     assert lib.cutb_qmatmul_select_variant(C.byref(desc(L.Q4_0, 17, 4096, 11008))) != L.VARIANT_GEMV_MMA

@@ -128,8 +128,9 @@ def test_paired_rows_are_refused_where_no_kernel_has_them():
     from cut_b200 import ops
     from gpu_util import dev
 
-    A, W = _inputs(synth.Q8_0, 64, 512, 128, np.float16, seed=1)  # prefill shape
-    d, _, keep = ops.make_desc(dev(A), dev(W), synth.Q8_0, 128, fusion_type=1, fusion_op=133, flags=L.FLAG_GLU_PAIRS)
+    A, W = _inputs(synth.Q8_0, 64, 512, 128, np.float16, seed=1)  # the any-shape kernel has no paired epilogue
+    d, _, keep = ops.make_desc(dev(A), dev(W), synth.Q8_0, 128, fusion_type=1, fusion_op=133, flags=L.FLAG_GLU_PAIRS,
+                               variant=L.VARIANT_GENERIC)
     with pytest.raises(L.CutbError) as e:
         ops.launch(d)
     assert e.value.status == 2
@@ -664,6 +665,26 @@ def test_gemm_tc_splits_k_stages_over_the_sms(fmt, dtype, M, K, N):
         assert rel_l2(got[:, lo:hi], ref) <= TOL
     again, _, _ = run_blocks(fmt, A, W, N, D_np=D, fusion_type=2, fusion_op=0, variant=L.VARIANT_GEMM_TC)
     assert np.array_equal(got, again)  # fixed summation order
+
+
+@pytest.mark.parametrize("fmt,dtype,M,K,N", [
+    (synth.Q4_K, np.float16, 40, 1024, 1000),    # the GEMM for few tokens, K split over the SMs (fix-up pairs the columns)
+    (synth.Q4_0, np.float32, 24, 256, 38400),    # the same with whole tiles (the kernel's own epilogue pairs them)
+    (synth.Q8_0, np.float16, 100, 512, 33000),   # 65..128 tokens on enough tiles: the prefill kernel
+    (synth.Q4_K, np.float16, 300, 512, 264)])    # the prefill kernel, three token blocks
+def test_paired_gate_up_rows_in_the_gemm_epilogues(fmt, dtype, M, K, N):
+    """CUTB_FLAG_GLU_PAIRS on the tensor-core GEMMs: C[m, i] = SiLU(acc[m, 2i]) * acc[m, 2i + 1], N / 2 output columns."""
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M + N)
+    got, used, st = run_blocks(fmt, A, W, N, fusion_type=1, fusion_op=133, flags=L.FLAG_GLU_PAIRS)
+    assert used == L.VARIANT_GEMM_TC and st == 0
+    assert got.shape == (M, N // 2)
+    rb = synth.row_bytes(fmt, K)
+    for lo, hi in ((0, 256), (N - 256, N)):
+        acc = _ref(fmt, A, W[lo * rb:hi * rb], M, K, hi - lo).astype(np.float64)
+        want = acc[:, 0::2] / (1.0 + np.exp(-acc[:, 0::2])) * acc[:, 1::2]
+        assert rel_l2(got[:, lo // 2:hi // 2], want) <= 2 * TOL
 
 
 def test_thirteen_to_sixteen_rows_on_a_large_weight_take_the_gemm():
