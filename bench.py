@@ -320,6 +320,39 @@ def reference_cuda_measurement() -> dict | None:
         out["configs[3]_decode_attention_515_rows"] = {"kernel": "Attention (Float16 cache)", "us_per_launch": us_ref,
                                                        "this_library_us_per_launch": us_own,
                                                        "max_abs_diff": float((o_own - o_ref).abs().max())}
+    # prefill attention at the same geometry: a 512-token prompt over an empty cache (the reference serves one token
+    # and query head per block; this library 64 tokens of a head per block on the tensor cores)
+    if ref_cuda.have("BatchedAttentionReadCache_f16"):
+        nh, nkv, hd, rows, T = 32, 8, 128, 1024, 512
+        gen = torch.Generator(device=dev).manual_seed(8)
+        q = torch.randn((T, nh * hd), generator=gen, device=dev)
+        kc = torch.randn((rows, nkv * hd), generator=gen, device=dev).half()
+        vc = torch.randn((rows, nkv * hd), generator=gen, device=dev).half()
+        ang = torch.rand((rows, hd // 2), generator=gen, device=dev) * 6.28
+        cos_t, sin_t = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+        pos = torch.arange(0, T, dtype=torch.int32, device=dev)
+        scale = 1.0 / float(np.sqrt(np.float32(hd)))
+        o_ref = torch.zeros((T, nh * hd), device=dev)
+
+        def time_us2(fn, n=20):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) * 1e3 / n
+
+        us_ref = time_us2(lambda: ref_cuda.batched_attention(True, q, kc, vc, pos, cos_t, sin_t, o_ref, T, nh, nkv, hd, scale, nh * hd, 0))
+        o_own = ops.batched_attention(q, kc, vc, pos, cos_t, sin_t, nh, nkv, hd)
+        us_own = time_us2(lambda: ops.batched_attention(q, kc, vc, pos, cos_t, sin_t, nh, nkv, hd, out=o_own))
+        out["configs[3]_prefill_attention_512_tokens"] = {
+            "kernel": "BatchedAttentionReadCache (Float16 cache)", "us_per_launch": us_ref, "this_library_us_per_launch": us_own,
+            "max_abs_diff": float((o_own - o_ref).abs().max()),
+            "note": "this library rounds rotated queries and probabilities to fp16 for the tensor cores; sums are fp32"}
     return out or None
 
 
