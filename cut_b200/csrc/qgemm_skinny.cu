@@ -547,7 +547,7 @@ bool sk_plan(const cutb_qmatmul_desc &d, uint32_t sm_count, size_t smem_optin, b
   } else {
     uint32_t sa = (32u * 1024u) / (pl->bt * 128u);
     sa = sa < 3 ? 3 : (sa > 8 ? 8 : sa);
-    for (uint32_t nb = 3; nb >= 2 && !pl->sa; --nb)
+    for (uint32_t nb = 3; nb >= 2 && !pl->sa; --nb)  // (four and five slots measured the same as three)
       for (uint32_t rs = 16; rs >= SK_GRANS && !pl->sa; --rs)
         if (sk_smem_bytes(d.format, false, pl->bt, sa, nb, rs) <= smem_optin) pl->sa = sa, pl->nb = nb, pl->rs = rs;
   }

@@ -37,7 +37,7 @@
 //               = token), fused op, stores to C coalesced along n.
 // fp32 activations are first rounded to fp16 into the caller's workspace by a
 // small cast kernel (the copy engine cannot convert).  Shared memory holds a ring
-// of activation stages (three at 512 tokens) and a ring of two weight tiles.
+// of activation stages (three at 512 tokens) and a ring of two weight tiles (three up to 256 tokens per CTA).
 //
 // Every wait is bounded; on expiry the CTA records CUTB_ERR_TIMEOUT in the
 // caller's status word, skips its remaining work, frees its tensor memory and

@@ -107,6 +107,17 @@ def test_select_variant_and_workspace_plan_without_device():
     d.flags = L.FLAG_STAGE_PER_CTA
     ws = lib.cutb_qmatmul_workspace_bytes(C.byref(d))
     assert ws > 0 and ws % (8 * 1024 * 4) == 0
+    # the tensor-core GEMM for few tokens: head / tail slots of every CTA of its K split (43 tiles of 256 rows x 16 units
+    # of 256 k over 148 SMs -> runs of 5 units, 138 CTAs), [2 x CTAs][tokens rounded to 8][256] floats
+    g = desc(L.Q4_0, 32, 4096, 11008)
+    g.variant = L.VARIANT_GEMM_TC
+    assert lib.cutb_qmatmul_workspace_bytes(C.byref(g)) == 2 * 138 * 32 * 256 * 4
+    g = desc(L.Q4_0, 30, 4096, 11008, L.F32)   # fp32 rows: their fp16 copy comes first
+    g.variant = L.VARIANT_GEMM_TC
+    assert lib.cutb_qmatmul_workspace_bytes(C.byref(g)) == 30 * 4096 * 2 + 2 * 138 * 32 * 256 * 4
+    g = desc(L.Q4_0, 32, 256, 38400)           # more tiles than SMs: no split, no slots
+    g.variant = L.VARIANT_GEMM_TC
+    assert lib.cutb_qmatmul_workspace_bytes(C.byref(g)) == 0
     # three rows and more: the activations are quantised once per call into the workspace as well
     d.flags = 0
     assert lib.cutb_qmatmul_workspace_bytes(C.byref(d)) > ws
