@@ -70,7 +70,11 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
 
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t n0 = blockIdx.x * TC_BW, m0 = blockIdx.y * (p.mb * TC_BT);
-  const uint32_t nk = p.K / (TC_BK * KS);  // K stages
+  // K stages: all of them, or this CTA's share when K is split over blockIdx.z (long K on few weight rows)
+  const uint32_t nk_all = p.K / (TC_BK * KS), nk_per = (nk_all + p.ksplit - 1) / p.ksplit;
+  const uint32_t kb = blockIdx.z * nk_per;                                     // first stage
+  const uint32_t nk = kb < nk_all ? (kb + nk_per < nk_all ? nk_per : nk_all - kb) : 0;
+  const uint32_t kc0 = kb * KS;                                                // first 64-k chunk
   const uint32_t fulla_u = smem_u32(bars), fullb_u = fulla_u + SA * 8, cons_u = fullb_u + NB * 8, accum_u = cons_u + NC * 8;
   const uint32_t tmem_cols = MB == 1 ? 128u : (MB == 2 ? 256u : 512u);
 
@@ -158,7 +162,7 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
         mbar_arrive_expect_tx(bar, a_stage_bytes);
         for (uint32_t sub = 0; sub < KS; ++sub)
           for (uint32_t mb = 0; mb < MB; ++mb)
-            tma_load_2d(dst + (sub * MB + mb) * TC_TILE_BYTES, &tmapA, (ks * KS + sub) * TC_BK, m0 + mb * TC_BT, bar);
+            tma_load_2d(dst + (sub * MB + mb) * TC_TILE_BYTES, &tmapA, (kc0 + ks * KS + sub) * TC_BK, m0 + mb * TC_BT, bar);
         ++issued;
         if (++sa == SA) sa = 0, pa ^= 1u;
       }
@@ -186,8 +190,8 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
 #pragma unroll
     for (int i = 0; i < RawWindow<FMT>::NV; ++i) nxt.v[i] = make_uint4(0, 0, 0, 0);
     if (live && g < nk) {
-      if constexpr (tc_is_plane(FMT)) load_window_plane<FMT>(p, n, g * KS * TC_BK, nxt);
-      else load_window<FMT>(wrow, g * KS * TC_BK, nxt);
+      if constexpr (tc_is_plane(FMT)) load_window_plane<FMT>(p, n, (kc0 + g * KS) * TC_BK, nxt);
+      else load_window<FMT>(wrow, (kc0 + g * KS) * TC_BK, nxt);
     }
     // this group's slot sequence: start at slot g, advance by G modulo NB
     uint32_t sb = g % NB;
@@ -196,11 +200,11 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
     for (uint32_t ks = g; ks < nk && !dead; ks += G) {
       uint8_t *slot = b_ring + sb * b_slot_bytes;
       for (uint32_t sub = 0; sub < KS; ++sub) {
-        const uint32_t chunk = ks * KS + sub;  // 64-k chunk of the row
+        const uint32_t chunk = kc0 + ks * KS + sub;  // 64-k chunk of the row
         const RawWindow<FMT> cur = nxt;
         // the chunk this thread converts next: the following sub-tile, or the first of the group's next stage
-        const uint32_t nchunk = sub + 1 < KS ? chunk + 1 : (ks + G) * KS;
-        if (live && nchunk < nk * KS) {
+        const uint32_t nchunk = sub + 1 < KS ? chunk + 1 : kc0 + (ks + G) * KS;
+        if (live && nchunk < kc0 + nk * KS) {
           if constexpr (tc_is_plane(FMT)) load_window_plane<FMT>(p, n, nchunk * TC_BK, nxt);
           else load_window<FMT>(wrow, nchunk * TC_BK, nxt);
         }
@@ -259,6 +263,13 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
           tmem_ld32(tmem_base + ((q * 32) << 16) + c0, v);
           const uint32_t mbase = m0 + c0;
           if (mbase >= p.M) continue;
+          if (p.ksplit > 1) {  // this CTA's share of K: raw sums to its plane of the workspace; tc_splitk_reduce_kernel finishes
+            float *dstp = p.partial + ((size_t)blockIdx.z * p.M + mbase) * p.N + nn;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (n_ok && mbase + i < p.M) dstp[(size_t)i * p.N] = __uint_as_float(v[i]);
+            continue;
+          }
           if (p.glu) {
             // gate and up rows are neighbouring lanes: the even lane takes its partner's accumulator, applies the
             // gate's activation to its own and stores one output column for the pair
@@ -318,6 +329,27 @@ __global__ void __launch_bounds__(TC_MAX_THREADS, 1) qgemm_tc_kernel(const __gri
   }
 }
 
+// K split: the planes of partial sums added in a fixed order, then the fused epilogue (paired rows included).
+__global__ void tc_splitk_reduce_kernel(const TcParams p) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t total = (size_t)p.M * p.N;
+  float sum = 0.f;
+  uint32_t m = 0, n = 0;
+  const bool in = idx < total;
+  if (in) {
+    m = (uint32_t)(idx / p.N), n = (uint32_t)(idx % p.N);
+    for (uint32_t z = 0; z < p.ksplit; ++z) sum += p.partial[(size_t)z * total + idx];
+  }
+  if (p.glu) {  // gate and up columns sit in neighbouring threads (N is even, so a pair never straddles a row)
+    const float up = __shfl_xor_sync(0xffffffffu, sum, 1);
+    if (in && !(n & 1u)) p.C[(size_t)m * p.ldc + (n >> 1)] = apply_epilogue(sum, CUTB_FUSION_UNARY, p.fusion_op, 0.f) * up;
+    return;
+  }
+  if (!in) return;
+  const float dv = p.fusion_type == CUTB_FUSION_BINARY ? p.D[(size_t)m * p.ldd + n] : 0.f;
+  p.C[(size_t)m * p.ldc + n] = apply_epilogue(sum, p.fusion_type, p.fusion_op, dv);
+}
+
 size_t tc_smem_bytes(uint32_t mb, uint32_t sa, uint32_t nb, uint32_t ksub) {
   return 1024 + (size_t)(sa * mb + nb) * ksub * TC_TILE_BYTES + (2 * sa + 2 * nb + 1) * 8 + 16;  // fullA, fullB, consumed[sa + nb], accum
 }
@@ -332,7 +364,7 @@ template <int FMT> int tc_launch(const CUtensorMap &map, const TcParams &p, cuda
     CUTB_CUDA_TRY(cudaFuncSetAttribute(qgemm_tc_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)di.smem_optin));
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  dim3 grid((p.N + TC_BW - 1) / TC_BW, (p.M + p.mb * TC_BT - 1) / (p.mb * TC_BT));
+  dim3 grid((p.N + TC_BW - 1) / TC_BW, (p.M + p.mb * TC_BT - 1) / (p.mb * TC_BT), p.ksplit);
   qgemm_tc_kernel<FMT><<<grid, TC_CTRL_THREADS + 128 * p.groups, tc_smem_bytes(p.mb, p.sa, p.nb, p.ksub), stream>>>(map, p);
   CUTB_CUDA_TRY(cudaGetLastError());
   return CUTB_OK;
@@ -360,10 +392,42 @@ bool qgemm_tc_supported(const cutb_qmatmul_desc &d) {
   return di.cc_major == 10;
 }
 
+namespace {
+// Token blocks per CTA and K split.  Few weight rows (a 4096-row projection is 32 column tiles) would leave most SMs
+// idle at 512 tokens per CTA.  With a long K (the down projection, K = 14336) the K stages are shared out over
+// blockIdx.z instead: every weight is still dequantised once, 512 tokens amortise it, and the partial sums meet in
+// the workspace (512 x 14336 x 4096: 112 us with 128 tokens per CTA).  Otherwise fewer tokens per CTA until the grid
+// covers at least half of the SMs: each weight tile is then dequantised once per token group, which costs far less
+// than the idle SMs.
+void tc_shape_plan(const cutb_qmatmul_desc &d, uint32_t sm_count, uint32_t *mb_out, uint32_t *ksplit_out) {
+  const uint32_t mblocks = (d.M + TC_BT - 1) / TC_BT, ctiles = (d.N + TC_BW - 1) / TC_BW;
+  uint32_t mb = mblocks < TC_MAX_MB ? mblocks : TC_MAX_MB, ksplit = 1;
+  const uint32_t ctas = ctiles * ((mblocks + mb - 1) / mb);
+  const uint32_t nk_all = d.K / TC_BK;  // (such CTAs run 64-k stages)
+  if (mb == TC_MAX_MB && d.K >= 8192 && ctas * 2 <= sm_count) {
+    uint32_t want = sm_count / ctas;
+    if (want > 8) want = 8;
+    const uint32_t per = (nk_all + want - 1) / want;
+    ksplit = (nk_all + per - 1) / per;  // no empty share
+  } else {
+    while (mb > 1 && ctiles * ((mblocks + mb - 1) / mb) * 2 <= sm_count) mb = (mb + 1) / 2;
+  }
+  *mb_out = mb;
+  *ksplit_out = ksplit;
+}
+uint64_t tc_cast_bytes(const cutb_qmatmul_desc &d) {
+  return d.a_dtype == CUTB_F32 ? (((uint64_t)d.M * d.K * sizeof(__half) + 15) & ~(uint64_t)15) : 0;
+}
+}  // namespace
+
 uint64_t qgemm_tc_workspace(const cutb_qmatmul_desc &d) {
   if (qgemm_skinny_applies(d)) return qgemm_skinny_workspace(d);
-  // fp32 activations are rounded to fp16 rows of K elements first
-  return d.a_dtype == CUTB_F32 ? (uint64_t)d.M * d.K * sizeof(__half) : 0;
+  // fp32 activations are rounded to fp16 rows of K elements first; a K split adds its planes of partial sums
+  DeviceInfo di;
+  const uint32_t sms = get_device_info(&di) == CUTB_OK ? (uint32_t)di.sm_count : 148u;
+  uint32_t mb, ksplit;
+  tc_shape_plan(d, sms, &mb, &ksplit);
+  return tc_cast_bytes(d) + (ksplit > 1 ? (uint64_t)ksplit * d.M * d.N * sizeof(float) : 0);
 }
 
 int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
@@ -388,14 +452,18 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   p.ldb = d.ldb;
   p.lds = d.lds;
   p.blocksK = (d.K + 31) / 32;
-  const uint32_t mblocks = (d.M + TC_BT - 1) / TC_BT;
-  p.mb = mblocks < TC_MAX_MB ? mblocks : TC_MAX_MB;
-  // Few weight rows (a 4096-row projection is 32 column tiles): fewer tokens per CTA until the grid covers at
-  // least half of the SMs.  Each weight tile is then dequantised once per token group, which costs far less than
-  // leaving three quarters of the SMs idle.
-  {
-    const uint32_t ctiles = (d.N + TC_BW - 1) / TC_BW;
-    while (p.mb > 1 && ctiles * ((mblocks + p.mb - 1) / p.mb) * 2 <= (uint32_t)di.sm_count) p.mb = (p.mb + 1) / 2;
+  tc_shape_plan(d, (uint32_t)di.sm_count, &p.mb, &p.ksplit);
+  const uint64_t cast_bytes = tc_cast_bytes(d), partial_bytes = p.ksplit > 1 ? (uint64_t)p.ksplit * d.M * d.N * sizeof(float) : 0;
+  p.partial = nullptr;
+  if (p.ksplit > 1) {
+    // without room for the partial sums: the tokens-per-CTA rule (a K split of one never asks for any)
+    if (!d.workspace || d.workspace_bytes < cast_bytes + partial_bytes || reinterpret_cast<uintptr_t>(d.workspace) % 16 != 0) {
+      const uint32_t mblocks = (d.M + TC_BT - 1) / TC_BT, ctiles = (d.N + TC_BW - 1) / TC_BW;
+      p.ksplit = 1;
+      while (p.mb > 1 && ctiles * ((mblocks + p.mb - 1) / p.mb) * 2 <= (uint32_t)di.sm_count) p.mb = (p.mb + 1) / 2;
+    } else {
+      p.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(d.workspace) + cast_bytes);
+    }
   }
   // weight slots: two (one per converter group) when the activation stages need the room; up to 256 tokens per
   // CTA a third one loosens the hand-off chain converter -> issuer -> tensor core -> converter (512 x 4096 x 4096
@@ -423,7 +491,7 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   const void *a16 = d.A;
   uint64_t stride = (uint64_t)d.lda * sizeof(__half);
   if (d.a_dtype == CUTB_F32) {
-    const uint64_t need = qgemm_tc_workspace(d);
+    const uint64_t need = cast_bytes;
     if (!d.workspace || d.workspace_bytes < need || reinterpret_cast<uintptr_t>(d.workspace) % 16 != 0) {
       set_last_error("qgemm: fp32 activations need %llu bytes of 16-byte aligned workspace, got %llu",
                      (unsigned long long)need, (unsigned long long)d.workspace_bytes);
@@ -439,15 +507,22 @@ int qgemm_tc_launch(const cutb_qmatmul_desc &d, cudaStream_t stream) {
   }
   CUtensorMap map;
   if (int rc = make_tmap_a(&map, a16, d.M, d.K, stride)) return rc;
+  int rc;
   if (d.layout == CUTB_LAYOUT_KN_PLANES) {
-    if (d.format == CUTB_Q8_0) return tc_launch<TC_PLANE_Q8>(map, p, stream);
-    return d.affine ? tc_launch<TC_PLANE_Q4A>(map, p, stream) : tc_launch<TC_PLANE_Q4>(map, p, stream);
+    if (d.format == CUTB_Q8_0) rc = tc_launch<TC_PLANE_Q8>(map, p, stream);
+    else rc = d.affine ? tc_launch<TC_PLANE_Q4A>(map, p, stream) : tc_launch<TC_PLANE_Q4>(map, p, stream);
+  } else {
+    switch (d.format) {
+      case CUTB_Q8_0: rc = tc_launch<CUTB_Q8_0>(map, p, stream); break;
+      case CUTB_Q4_0: rc = tc_launch<CUTB_Q4_0>(map, p, stream); break;
+      default: rc = tc_launch<CUTB_Q4_K>(map, p, stream); break;
+    }
   }
-  switch (d.format) {
-    case CUTB_Q8_0: return tc_launch<CUTB_Q8_0>(map, p, stream);
-    case CUTB_Q4_0: return tc_launch<CUTB_Q4_0>(map, p, stream);
-    default: return tc_launch<CUTB_Q4_K>(map, p, stream);
-  }
+  if (rc != CUTB_OK || p.ksplit <= 1) return rc;
+  const size_t total = (size_t)d.M * d.N;
+  tc_splitk_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p);
+  CUTB_CUDA_TRY(cudaGetLastError());
+  return CUTB_OK;
 }
 
 }  // namespace cutb

@@ -41,6 +41,9 @@ struct TcParams {
   // row stride in elements, rows of the scale plane before the affine mins
   const uint16_t *S;
   uint32_t ldb, lds, blocksK;
+  // long K on few weight rows: K stages shared out over blockIdx.z, partial sums [ksplit][M][N] in the workspace
+  uint32_t ksplit;
+  float *partial;
 };
 
 // Weight sources of the converters besides the GGUF block formats: the reference's run-time planes

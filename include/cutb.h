@@ -171,7 +171,8 @@ typedef struct cutb_qmatmul_desc {
  * decode mat-vec its staged activations (three rows and up) and split-K partial sums; the tensor-core GEMM the
  * fp16 copy of fp32 activations and, up to 128 activation rows, the partial tiles of weight tiles whose K is shared
  * by several blocks (summed in a fixed order by a second small kernel; without that room every weight tile goes
- * whole to one block, which is slower but needs nothing). */
+ * whole to one block, which is slower but needs nothing); with 512 rows and more on few weight rows and K >= 8192,
+ * planes of partial sums of a K split (same rule: optional, faster with them). */
 CUTB_API uint64_t cutb_qmatmul_workspace_bytes(const cutb_qmatmul_desc *desc);
 
 /* Variant the library would run for this descriptor (resolves CUTB_VARIANT_AUTO);

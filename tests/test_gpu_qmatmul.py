@@ -687,6 +687,30 @@ def test_paired_gate_up_rows_in_the_gemm_epilogues(fmt, dtype, M, K, N):
         assert rel_l2(got[:, lo // 2:hi // 2], want) <= 2 * TOL
 
 
+@pytest.mark.parametrize("fmt,dtype,M,K,N,glu", [
+    (synth.Q4_K, np.float16, 512, 8192, 1024, False),   # 8 weight tiles, K shared out eight ways
+    (synth.Q4_0, np.float32, 600, 8192, 520, False),    # two token groups, a ragged last tile, the fp16 copy in front
+    (synth.Q8_0, np.float16, 512, 14336, 512, True)])   # paired rows finished by the reduction
+def test_gemm_tc_splits_a_long_k_over_ctas(fmt, dtype, M, K, N, glu):
+    """512 tokens and more on few weight rows with K >= 8192: the K stages are shared out over blockIdx.z, the planes of
+    partial sums are added in a fixed order and the fused op follows the sum."""
+    from gpu_util import rel_l2, run_blocks
+
+    A, W = _inputs(fmt, M, K, N, dtype, seed=M + K)
+    if glu:
+        got, used, st = run_blocks(fmt, A, W, N, fusion_type=1, fusion_op=133, flags=L.FLAG_GLU_PAIRS)
+        acc = _ref(fmt, A, W, M, K, N).astype(np.float64)
+        want = acc[:, 0::2] / (1.0 + np.exp(-acc[:, 0::2])) * acc[:, 1::2]
+        tol = 2 * TOL
+    else:
+        D = synth.make_activations(M, N, 7)
+        got, used, st = run_blocks(fmt, A, W, N, D_np=D, fusion_type=2, fusion_op=0)
+        want = _ref(fmt, A, W, M, K, N, D=D, fusion_type=2, fusion_op=0)
+        tol = TOL
+    assert used == L.VARIANT_GEMM_TC and st == 0
+    assert rel_l2(got, want) <= tol
+
+
 def test_thirteen_to_sixteen_rows_on_a_large_weight_take_the_gemm():
     """The automatic choice: up to 12 fp16 rows, small weights and fp32 rows stay on the mat-vec; 13 to 16 fp16 rows on
     16 M weights and more go to the tensor-core GEMM for few tokens."""
