@@ -404,6 +404,7 @@ void tc_shape_plan(const cutb_qmatmul_desc &d, uint32_t sm_count, uint32_t *mb_o
   uint32_t mb = mblocks < TC_MAX_MB ? mblocks : TC_MAX_MB, ksplit = 1;
   const uint32_t ctas = ctiles * ((mblocks + mb - 1) / mb);
   const uint32_t nk_all = d.K / TC_BK;  // (such CTAs run 64-k stages)
+  // (K = 4096 measured no better split than not: 512 x 4096 x 4096 35.3 against 36.2 us, 6144 rows 51 against 38)
   if (mb == TC_MAX_MB && d.K >= 8192 && ctas * 2 <= sm_count) {
     uint32_t want = sm_count / ctas;
     if (want > 8) want = 8;
