@@ -296,6 +296,30 @@ void blockMatmulOptionsAndGluPairs() {
   MatMulOpNode gemm(s, s.createTensor({64, K}, DataType::Float16), raw, DequantFormat::Q4_0, N);
   on.normWeight = nw;
   CHECK_THROWS(gemm.setBlockOptions(on), "decode mat-vec only");
+  {
+    // paired rows also run on the tensor-core GEMM (variant 2); the any-shape kernel (variant 0) has no such epilogue
+    MatMulOpNode gg(s, s.createTensor({64, K}, DataType::Float16), raw, DequantFormat::Q4_0, N);
+    gg.setFusion(MatMulFusion::Unary, UnarySilu);
+    gg.setBlockOptions(og);
+    CHECK(gg.outputShape() == (std::vector<uint32_t>{64, N / 2}));
+    MatMulOpNode g0(s, x, raw, DequantFormat::Q4_0, N, 0u);
+    g0.setFusion(MatMulFusion::Unary, UnarySilu);
+    CHECK_THROWS(g0.setBlockOptions(og), "tensor-core GEMM only");
+    // 13 to 16 fp16 rows on 16 M weights and more: the automatic choice is the GEMM; asking for the fused RMSNorm,
+    // which only the mat-vec has, brings it back
+    const uint32_t Kb = 4096, Nb = 4096;
+    auto rawb = s.createTensor({Nb * (Kb / 32) * 18}, DataType::Int8);
+    auto nwb = s.createTensor({Kb}, DataType::Float32);
+    MatMulOpNode big(s, s.createTensor({16, Kb}, DataType::Float16), rawb, DequantFormat::Q4_0, Nb);
+    CHECK(KernelDesc::decode(*big.shader())->variant == 2);
+    MatMulOpNode small(s, s.createTensor({12, Kb}, DataType::Float16), rawb, DequantFormat::Q4_0, Nb);
+    CHECK(KernelDesc::decode(*small.shader())->variant == 1);
+    MatMulBlockOptions onb;
+    onb.flags = kBlockFlagRmsNorm;
+    onb.normWeight = nwb;
+    big.setBlockOptions(onb);
+    CHECK(KernelDesc::decode(*big.shader())->variant == 1);
+  }
   auto fused = f.rt.ops().matmulBlocksFused(x, raw, DequantFormat::Q4_0, N, o);
   CHECK(f.rt.getTensor(fused).getShape() == (std::vector<uint32_t>{1, N}));
 
