@@ -126,7 +126,8 @@ enum { CUTB_FLAG_NO_OVERLAP = 1, CUTB_FLAG_ACT_16BIT = 2, CUTB_FLAG_A_RMSNORM = 
  *
  * Operand range.  The generic and the decode variants dequantise exactly and take fp32
  * activations at full range.  CUTB_VARIANT_GEMM_TC (what CUTB_VARIANT_AUTO picks above 8 fp32 /
- * 16 fp16 activation rows over GGUF blocks) feeds the tensor cores fp16 operands, as the
+ * 16 fp16 activation rows over GGUF blocks, and from 13 fp16 rows on weights of 16 M elements
+ * and more) feeds the tensor cores fp16 operands, as the
  * reference's tensor-core variants do (MatMulQ4CoopMatTiled.cu:37-75): fp32 activations are
  * rounded to fp16 first, and a dequantised weight d * q (d * sc * q - dmin * m for Q4_K) is
  * rounded to fp16 too.  |A| above 65504 therefore becomes infinity, and the launch records
